@@ -1,0 +1,148 @@
+"""Pins the CPU oracle (oracle/pbg_step.py) to the reference.
+
+(1) every operator / comparator / loss call made by the reference's own known-answer
+    tests (recorded in tests/golden/reference_unit_calls.json by make_golden.py);
+(2) composed training steps produced by the reference Trainer (tests/golden/step_*.npz).
+Runs on CPU only."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import pbg_step as O
+from golden_util import GOLDEN, batch_of, load_step, oracle_config, oracle_state, step_fixture_names
+
+
+def _arr(d):
+    return None if d is None else np.asarray(d["data"], np.float64).reshape(d["shape"])
+
+
+with open(os.path.join(GOLDEN, "reference_unit_calls.json")) as f:
+    UNIT = json.load(f)["records"]
+
+
+def _op_table(rec):
+    p = {k: _arr(v) for k, v in rec["params"].items()}
+    name, dyn = rec["name"], rec["kind"] == "dynamic_operator"
+    if name == "none":
+        return None
+    if name in ("diagonal", "translation"):
+        t = next(iter(p.values()))
+    elif name == "complex_diagonal":
+        t = np.concatenate([p["real"], p["imag"]], -1)
+    else:
+        a = p["linear_transformations" if dyn else "linear_transformation"]
+        t = a.reshape(a.shape[:-2] + (-1,))
+        if name == "affine":
+            t = np.concatenate([t, p["translations" if dyn else "translation"]], -1)
+    return t if t.ndim == 2 else t[None]
+
+
+@pytest.mark.parametrize("i", range(len(UNIT)), ids=[f"{r['kind']}-{r['name']}-{k}" for k, r in enumerate(UNIT)])
+def test_reference_unit_vectors(i):
+    rec = UNIT[i]
+    outs = [_arr(o) for o in rec["outputs"]]
+    if rec["kind"] in ("operator", "dynamic_operator"):
+        x = _arr(rec["inputs"][0])
+        tab = _op_table(rec)
+        flat = x.reshape(-1, x.shape[-1])
+        if rec["kind"] == "dynamic_operator":
+            idx = np.asarray(rec["inputs"][1]["data"], np.int64).reshape(rec["inputs"][1]["shape"]).reshape(-1)
+            p = None if tab is None else tab[idx]
+        else:
+            p = None if tab is None else tab[:1]
+        got = O.op_forward(rec["name"], flat, p).reshape(x.shape)
+        np.testing.assert_allclose(got, outs[0], rtol=1e-6, atol=1e-6)
+        for a in rec["asserted"]:
+            np.testing.assert_allclose(got, _arr(a), rtol=5e-5, atol=5e-5)
+    elif rec["kind"] == "comparator":
+        lp, rp, ln, rn = (_arr(a) for a in rec["inputs"])  # already "prepared" by the reference test
+        C = lp.shape[0]
+        pos = np.stack([O.compare_pos(rec["name"], lp[c], rp[c]) for c in range(C)])
+        lneg = np.stack([O.compare_neg(rec["name"], rp[c], ln[c]) for c in range(C)])
+        rneg = np.stack([O.compare_neg(rec["name"], lp[c], rn[c]) for c in range(C)])
+        for got, want in zip((pos, lneg, rneg), outs):
+            np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+        for got, a in zip((pos, lneg, rneg), rec["asserted"]):
+            np.testing.assert_allclose(got, _arr(a), rtol=5e-5, atol=5e-5)
+    else:
+        s, S, w = (_arr(a) for a in rec["inputs"])
+        val, ds, dS = O.loss_forward_backward(rec["name"], rec.get("margin", 0.0), s, S, w)
+        np.testing.assert_allclose(val, outs[0], rtol=2e-6, atol=1e-6)
+        for a in rec["asserted"]:
+            np.testing.assert_allclose(val, _arr(a), rtol=5e-5, atol=5e-5)
+
+
+def test_cos_prepare_matches_reference_inputs():
+    # the comparator fixtures of the cos tests hold prepared (unit-norm) rows
+    recs = [r for r in UNIT if r["kind"] == "comparator" and r["name"] == "cos"]
+    assert recs
+    for r in recs:
+        x = _arr(r["inputs"][0])
+        n = np.linalg.norm(x, axis=-1)
+        assert np.allclose(n[n > 0], 1.0, atol=1e-5)
+
+
+@pytest.mark.parametrize("name", step_fixture_names())
+def test_composed_step_matches_reference(name):
+    c, z = load_step(name)
+    cfg = oracle_config(c)
+    st = oracle_state(c, z)
+    for step in range(c["steps"]):
+        stats = O.train_batch(cfg, st, *batch_of(c, z, step))
+        assert stats["loss"] == pytest.approx(float(z[f"loss_{step}"]), rel=2e-5, abs=1e-4)
+        # `neg > pos` is decided by fp32 rounding where a negative ties with its positive
+        assert abs(stats["violators_lhs"] - int(z[f"violators_lhs_{step}"])) <= stats["ties_lhs"]
+        assert abs(stats["violators_rhs"] - int(z[f"violators_rhs_{step}"])) <= stats["ties_rhs"]
+        np.testing.assert_allclose(st.W_lhs, z[f"W_lhs_after_{step}"], rtol=2e-5, atol=2e-6)
+        np.testing.assert_allclose(st.G_lhs, z[f"G_lhs_after_{step}"], rtol=2e-5, atol=1e-7)
+        if c["separate"]:
+            np.testing.assert_allclose(st.W_rhs, z[f"W_rhs_after_{step}"], rtol=2e-5, atol=2e-6)
+            np.testing.assert_allclose(st.G_rhs, z[f"G_rhs_after_{step}"], rtol=2e-5, atol=1e-7)
+        for side in ("rhs", "lhs"):
+            key = f"theta_{side}_after_{step}"
+            if key in z and getattr(st, f"theta_{side}") is not None:
+                np.testing.assert_allclose(getattr(st, f"theta_{side}"), z[key], rtol=2e-5, atol=2e-6)
+                np.testing.assert_allclose(getattr(st, f"acc_{side}"), z[f"acc_{side}_after_{step}"], rtol=5e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("name", step_fixture_names())
+def test_forward_scores_match_reference(name):
+    c, z = load_step(name)
+    cfg = oracle_config(c)
+    st = oracle_state(c, z)
+    for step in range(c["steps"]):
+        O.train_batch(cfg, st, *batch_of(c, z, step))
+    rel = z["fw_rel"] if c["dyn"] else int(z["fw_rel"])
+    ul = None if c["disable_lhs"] else z["fw_ul"]
+    ur = None if c["disable_rhs"] else z["fw_ur"]
+    sc = O.score_batch(cfg, st, z["fw_lhs"], z["fw_rhs"], rel, ul, ur)
+    for k in ("lhs_pos", "rhs_pos", "lhs_neg", "rhs_neg"):
+        want = z[f"fw_{k}"]
+        assert sc[k].shape == want.shape, k
+        np.testing.assert_allclose(sc[k], want, rtol=3e-5, atol=3e-5)
+
+
+def test_wave_of_one_is_a_plain_batch():
+    c, z = load_step("sequence_3_batches")
+    cfg = oracle_config(c)
+    a, b = oracle_state(c, z), oracle_state(c, z)
+    for step in range(3):
+        s1 = O.train_batch(cfg, a, *batch_of(c, z, step))
+        s2 = O.train_wave(cfg, b, [batch_of(c, z, step)])[0]
+        assert s1 == s2
+    assert np.array_equal(a.W_lhs, b.W_lhs) and np.array_equal(a.G_lhs, b.G_lhs)
+
+
+def test_wave_reads_the_snapshot():
+    c, z = load_step("sequence_3_batches")
+    cfg = oracle_config(c)
+    a, b = oracle_state(c, z), oracle_state(c, z)
+    batches = [batch_of(c, z, s) for s in range(3)]
+    O.train_wave(cfg, a, batches)
+    for bt in batches:
+        O.train_batch(cfg, b, *bt)
+    # same rows are touched, values differ slightly (stale reads), accumulators too
+    assert not np.array_equal(a.W_lhs, b.W_lhs)
+    assert np.array_equal(a.W_lhs != z["W_lhs0"], b.W_lhs != z["W_lhs0"])
