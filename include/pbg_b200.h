@@ -1,0 +1,181 @@
+/*
+ * pbg_b200.h -- C ABI of the B200 (sm_100a) training-step library for PyTorch-BigGraph.
+ *
+ * The library takes the slot of the reference's native module `torchbiggraph._C`
+ * (torchbiggraph/util.cpp:425-460, loaded in torchbiggraph/train_gpu.py:41-46) and runs, on
+ * the device, what the reference runs as PyTorch ops inside
+ * `Trainer._process_one_batch` (torchbiggraph/train_cpu.py:86-112) for every batch that
+ * `process_in_batches` (torchbiggraph/batching.py:91-125) hands it.
+ *
+ * Conventions
+ *   - plain C types only; every buffer is a raw pointer owned by the caller and alive for the
+ *     duration of the call.  "dev" pointers are device memory on the context's GPU, "host"
+ *     pointers are host memory (pinned memory makes the copies asynchronous).
+ *   - every function returns a pbg_status; 0 is success.  pbg_last_error(ctx) gives the text.
+ *     Nothing aborts, nothing spins without a bound.
+ *   - one context per GPU and per host thread; calls on one context are serialised on the
+ *     stream given at creation (0 = the legacy default stream).
+ *   - embedding tables are dense row-major float32 [num_rows, dim]; RowAdagrad state is one
+ *     float32 per row (torchbiggraph/row_adagrad.py:34-40).  The lhs and rhs table may be the
+ *     same memory (same entity type and partition): pass the same pointers.
+ *   - operator parameters are float32 tables [num_rels, dim]; complex_diagonal rows are
+ *     [real | imag] (torchbiggraph/operators.py:128-157).  Their AsyncAdagrad accumulators
+ *     (torchbiggraph/async_adagrad.py:75-85) have the same shape.
+ */
+#ifndef PBG_B200_H
+#define PBG_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  PBG_OK = 0,
+  PBG_ERR_BAD_ARGUMENT = 1,   /* null pointer, negative size, inconsistent shapes            */
+  PBG_ERR_UNSUPPORTED = 2,    /* a plugin / option this library has no device code for        */
+  PBG_ERR_INDEX_RANGE = 3,    /* an entity or relation id outside its table (reported by the
+                                 kernels through a flag; the offending rows are skipped)      */
+  PBG_ERR_TIMEOUT = 4,        /* a bounded device-side wait ran out                           */
+  PBG_ERR_CUDA = 5,           /* a CUDA runtime call failed; text in pbg_last_error           */
+  PBG_ERR_NO_DEVICE = 6,      /* no CUDA device / wrong architecture                          */
+  PBG_ERR_TOO_LARGE = 7       /* a size beyond a stated maximum                               */
+} pbg_status;
+
+/* OPERATORS registry names (torchbiggraph/operators.py:46-157) */
+typedef enum { PBG_OP_NONE = 0, PBG_OP_DIAGONAL = 1, PBG_OP_TRANSLATION = 2,
+               PBG_OP_COMPLEX_DIAGONAL = 3, PBG_OP_LINEAR = 4, PBG_OP_AFFINE = 5 } pbg_operator;
+/* COMPARATORS registry names (torchbiggraph/model.py:156-303) */
+typedef enum { PBG_CMP_DOT = 0, PBG_CMP_COS = 1, PBG_CMP_L2 = 2, PBG_CMP_SQUARED_L2 = 3 } pbg_comparator;
+/* LOSS_FUNCTIONS registry names (torchbiggraph/losses.py:50-161) */
+typedef enum { PBG_LOSS_LOGISTIC = 0, PBG_LOSS_RANKING = 1, PBG_LOSS_SOFTMAX = 2 } pbg_loss;
+/* arithmetic of the score / gradient contractions */
+typedef enum {
+  PBG_PREC_FP32 = 0,     /* fp32 FMA on the CUDA cores; the rtol 1e-4 tier                    */
+  PBG_PREC_TF32X3 = 1,   /* tcgen05 TF32 tensor cores, 3-term error-compensated split, fp32
+                            accumulation in tensor memory; the rtol 1e-4 tier                 */
+  PBG_PREC_TF32 = 2      /* tcgen05 TF32 tensor cores, single pass; the rtol 1e-3 tier        */
+} pbg_precision;
+
+/* The keys of ConfigSchema (torchbiggraph/config.py:158-230, 318-359, 411-425) that the
+ * training step reads. */
+typedef struct {
+  int32_t dim;                /* dimension                                                     */
+  int32_t op;                 /* pbg_operator of the relation(s)                               */
+  int32_t comparator;         /* pbg_comparator                                                */
+  int32_t loss;               /* pbg_loss                                                      */
+  int32_t dynamic_relations;  /* 0: one relation per batch, operator on the rhs only
+                                 (model.py:666-703); 1: per-edge relation, two operator
+                                 tables, two one-sided passes (model.py:705-758)               */
+  int32_t num_rels;           /* rows of the operator tables                                   */
+  int32_t num_batch_negs;
+  int32_t num_uniform_negs;
+  int32_t disable_lhs_negs;
+  int32_t disable_rhs_negs;
+  int32_t precision;          /* pbg_precision                                                 */
+  int32_t max_batch_size;     /* largest number of edges in one batch (batch_size)             */
+  int32_t batches_in_flight;  /* k >= 1: batches of one wave read the tables as they were when
+                                 the wave started and their k optimizer steps are applied in
+                                 batch order (deterministic HOGWILD, train_cpu.py:861-884);
+                                 1 = the reference's sequential semantics                      */
+  float margin;               /* ranking loss margin                                           */
+  float lr;                   /* RowAdagrad learning rate                                      */
+  float relation_lr;          /* AsyncAdagrad learning rate of operator parameters
+                                 (train_cpu.py:224-228: relation_lr if set, else lr)           */
+} pbg_config;
+
+/* One resident (lhs partition, rhs partition) bucket.  Pointers are device memory. */
+typedef struct {
+  float *lhs_emb;   float *lhs_state;  int64_t lhs_rows;   /* [lhs_rows, dim], [lhs_rows]      */
+  float *rhs_emb;   float *rhs_state;  int64_t rhs_rows;   /* may equal the lhs_* pointers     */
+  float *rhs_op;    float *rhs_op_state;                   /* [num_rels, dim] or NULL (op none)*/
+  float *lhs_op;    float *lhs_op_state;                   /* dynamic relations only, else NULL*/
+  const float *relation_weights;                           /* HOST array [num_rels] (standard
+                                                              mode) or [1] (dynamic); NULL = 1 */
+} pbg_bucket;
+
+/* One batch of a call: edges [offset, offset + count) of the edge arrays, all of relation
+ * `rel` in standard mode (batching.py:21-79); `rel` is ignored with dynamic relations. */
+typedef struct { int64_t offset; int32_t count; int32_t rel; } pbg_batch;
+
+/* Stats of one batch (torchbiggraph/train_cpu.py:95-101). */
+typedef struct { float loss; float reg; int64_t violators_lhs; int64_t violators_rhs; int64_t count; } pbg_batch_stats;
+
+typedef struct pbg_context pbg_context;
+
+/* Library / build information; usable without a GPU. */
+const char *pbg_version(void);
+const char *pbg_status_string(int status);
+
+/* Creates the per-GPU context (workspace sized from cfg; stream = a cudaStream_t cast to
+ * void*, NULL for the default stream).  Replaces the per-process set-up of
+ * GPUProcess.__init__ / run (torchbiggraph/train_gpu.py:101-135). */
+int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_context **out);
+int pbg_destroy(pbg_context *ctx);
+const char *pbg_last_error(const pbg_context *ctx);
+/* Workspace bytes the context holds on the device. */
+int64_t pbg_workspace_bytes(const pbg_context *ctx);
+/* lr / relation_lr / margin may change between calls (checkpoint reload, schedules). */
+int pbg_set_hyperparameters(pbg_context *ctx, float lr, float relation_lr, float margin);
+
+/* Trains `num_batches` batches on the bucket: the device-side replacement of the loop
+ * `for batch_edges in batcher(...): trainer.process_one_batch(model, batch_edges)`
+ * (torchbiggraph/batching.py:121-122 -> train_cpu.py:86-112).
+ *   lhs, rhs, rel : device int64 arrays of `num_edges` partition-local row ids / relation ids
+ *                   (rel may be NULL in standard mode).
+ *   batches       : HOST array of num_batches descriptors.
+ *   uniform_lhs / uniform_rhs : device int64 [num_batches, chunks_per_batch, num_uniform_negs]
+ *                   row ids of the uniformly sampled negatives, chunks_per_batch =
+ *                   ceil(max_batch_size / chunk_size); NULL = draw them on the device from
+ *                   `seed` (the reference draws them with torch.randint, model.py:70-75).
+ *   stats_out     : HOST array of num_batches entries, filled when the call returns
+ *                   (the call synchronises the stream once, at its end), or NULL to skip the
+ *                   read-back and stay asynchronous (use pbg_read_stats later).
+ */
+int pbg_train_batches(pbg_context *ctx, const pbg_bucket *bucket,
+                      const int64_t *lhs_dev, const int64_t *rhs_dev, const int64_t *rel_dev,
+                      int64_t num_edges, const pbg_batch *batches, int32_t num_batches,
+                      const int64_t *uniform_lhs_dev, const int64_t *uniform_rhs_dev,
+                      uint64_t seed, pbg_batch_stats *stats_out);
+
+/* Same, with the edge arrays (and optional uniform ids) in HOST memory: copies them to the
+ * device in slabs that overlap with training.  This is the call that stands where
+ * GPUProcess.do_one_job moves a bucket's edges to the GPU and trains on them
+ * (torchbiggraph/train_gpu.py:243-266). */
+int pbg_train_batches_host(pbg_context *ctx, const pbg_bucket *bucket,
+                           const int64_t *lhs_host, const int64_t *rhs_host, const int64_t *rel_host,
+                           int64_t num_edges, const pbg_batch *batches, int32_t num_batches,
+                           const int64_t *uniform_lhs_host, const int64_t *uniform_rhs_host,
+                           uint64_t seed, pbg_batch_stats *stats_out);
+
+/* Sum of the stats of every batch trained since the last call of this function (device
+ * accumulators read back once; Stats.sum in torchbiggraph/stats.py:39-47). */
+int pbg_read_stats(pbg_context *ctx, pbg_batch_stats *sum_out);
+
+/* Forward pass only: MultiRelationEmbedder.forward (torchbiggraph/model.py:624-762) for one
+ * batch.  Outputs are device float32: lhs_pos / rhs_pos [count]; lhs_neg / rhs_neg
+ * [count, neg_cols] with neg_cols as returned by pbg_neg_columns (masked entries hold -1e9,
+ * model.py:836-839).  A side whose negatives are disabled gets neg_cols == 0. */
+int pbg_score_batch(pbg_context *ctx, const pbg_bucket *bucket,
+                    const int64_t *lhs_dev, const int64_t *rhs_dev, const int64_t *rel_dev,
+                    int32_t count, int32_t rel,
+                    const int64_t *uniform_lhs_dev, const int64_t *uniform_rhs_dev, uint64_t seed,
+                    float *lhs_pos, float *rhs_pos, float *lhs_neg, float *rhs_neg);
+/* Chunk size and negative columns for a batch of `count` edges (model.py:648-656). */
+int pbg_neg_columns(const pbg_context *ctx, int32_t count, int32_t *chunk_size, int32_t *chunks,
+                    int32_t *lhs_neg_cols, int32_t *rhs_neg_cols);
+
+/* The sparse-row optimizer step alone: RowAdagrad.step on a sparse gradient
+ * (torchbiggraph/row_adagrad.py:80-96).  rows: device int64 [n] (duplicates allowed, they are
+ * summed first), grads: device float32 [n, dim]. */
+int pbg_row_adagrad(pbg_context *ctx, float *emb, float *state, int64_t num_rows,
+                    const int64_t *rows_dev, const float *grads_dev, int32_t n, float lr);
+
+/* Kernel launches issued by this context since creation (for launch accounting). */
+int64_t pbg_launch_count(const pbg_context *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PBG_B200_H */

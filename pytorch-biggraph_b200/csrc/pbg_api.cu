@@ -1,0 +1,422 @@
+// C ABI of the library (include/pbg_b200.h): context, workspace carving, and the per-wave launch
+// sequence  keys -> sort -> gather -> score -> loss -> gradient products -> optimizer steps -> stats.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "pbg_common.cuh"
+
+int launch_score_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, int precision, cudaStream_t st);
+int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, int precision, cudaStream_t st);
+bool pbg_tc_available();
+
+struct pbg_context {
+  pbg_config cfg;
+  int device;
+  cudaStream_t stream;
+  std::string err;
+  // static geometry
+  int Dp, Pm, U, Mm, Ms, Cm, spb, kmax;
+  // workspace
+  char *ws = nullptr;
+  size_t ws_bytes = 0;
+  WaveBufs bufs;           // workspace pointers (table pointers filled per call)
+  SortPlan sort;
+  pbg_batch_stats *stats_dev = nullptr;
+  int stats_cap = 0;
+  double *sum_dev = nullptr;
+  int *errflag = nullptr;
+  long long *edge_dev[3] = {nullptr, nullptr, nullptr};
+  long long edge_cap = 0;
+  long long *uni_dev[2] = {nullptr, nullptr};
+  long long uni_cap = 0;
+  long long launches = 0;
+  unsigned long long batches_done = 0;
+};
+
+static int fail(pbg_context *c, int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (c) c->err = buf;
+  return code;
+}
+#define CU(c, call)                                                                          \
+  do {                                                                                       \
+    cudaError_t e_ = (call);                                                                 \
+    if (e_ != cudaSuccess) return fail(c, PBG_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+  } while (0)
+
+extern "C" const char *pbg_version(void) { return "pbg_b200 0.1 (sm_100a)"; }
+extern "C" const char *pbg_status_string(int s) {
+  switch (s) {
+    case PBG_OK: return "ok";
+    case PBG_ERR_BAD_ARGUMENT: return "bad argument";
+    case PBG_ERR_UNSUPPORTED: return "unsupported plugin or option";
+    case PBG_ERR_INDEX_RANGE: return "entity or relation id out of range";
+    case PBG_ERR_TIMEOUT: return "bounded device wait ran out";
+    case PBG_ERR_CUDA: return "CUDA error";
+    case PBG_ERR_NO_DEVICE: return "no usable CUDA device";
+    case PBG_ERR_TOO_LARGE: return "size beyond a stated maximum";
+  }
+  return "unknown status";
+}
+extern "C" const char *pbg_last_error(const pbg_context *c) { return c ? c->err.c_str() : "null context"; }
+extern "C" int64_t pbg_workspace_bytes(const pbg_context *c) { return c ? (int64_t)c->ws_bytes : 0; }
+extern "C" int64_t pbg_launch_count(const pbg_context *c) { return c ? c->launches : 0; }
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static int chunk_geometry(const pbg_config &cfg, int *Pm, int *Cm) {
+  int B = cfg.max_batch_size;
+  int lim = cfg.num_batch_negs > 0 ? cfg.num_batch_negs : cfg.num_uniform_negs;
+  if (lim <= 0) return PBG_ERR_BAD_ARGUMENT;
+  *Pm = lim < B ? lim : B;
+  *Cm = (B + *Pm - 1) / *Pm;
+  return PBG_OK;
+}
+
+extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_context **out) {
+  if (!cfg || !out) return PBG_ERR_BAD_ARGUMENT;
+  *out = nullptr;
+  pbg_context *c = new pbg_context();
+  c->cfg = *cfg;
+  c->device = device;
+  c->stream = (cudaStream_t)stream;
+  *out = c;   // returned even on failure so that the caller can read the error text
+  if (cfg->dim <= 0 || cfg->dim % 4 != 0 || cfg->dim > 2048)
+    return fail(c, PBG_ERR_UNSUPPORTED, "dimension %d: this build needs a multiple of 4 up to 2048", cfg->dim);
+  if (cfg->op < PBG_OP_NONE || cfg->op > PBG_OP_AFFINE) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown operator %d", cfg->op);
+  if (cfg->op == PBG_OP_LINEAR || cfg->op == PBG_OP_AFFINE)
+    return fail(c, PBG_ERR_UNSUPPORTED, "operator %s has no device code in this build", cfg->op == PBG_OP_LINEAR ? "linear" : "affine");
+  if (cfg->op == PBG_OP_COMPLEX_DIAGONAL && cfg->dim % 8 != 0)
+    return fail(c, PBG_ERR_UNSUPPORTED, "complex_diagonal needs a dimension that is a multiple of 8 (got %d)", cfg->dim);
+  if (cfg->comparator < PBG_CMP_DOT || cfg->comparator > PBG_CMP_SQUARED_L2) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown comparator %d", cfg->comparator);
+  if (cfg->loss < PBG_LOSS_LOGISTIC || cfg->loss > PBG_LOSS_SOFTMAX) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown loss %d", cfg->loss);
+  if (cfg->num_batch_negs < 0 || cfg->num_uniform_negs < 0 || cfg->max_batch_size <= 0 || cfg->num_rels <= 0)
+    return fail(c, PBG_ERR_BAD_ARGUMENT, "negative or zero size in config");
+  if (cfg->batches_in_flight < 1 || cfg->batches_in_flight > PBG_KMAX)
+    return fail(c, PBG_ERR_BAD_ARGUMENT, "batches_in_flight must be in [1, %d]", PBG_KMAX);
+  if (cfg->precision != PBG_PREC_FP32 && !pbg_tc_available())
+    return fail(c, PBG_ERR_UNSUPPORTED, "tensor-core precision tiers are not built into this library");
+  if (cfg->precision < PBG_PREC_FP32 || cfg->precision > PBG_PREC_TF32) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown precision %d", cfg->precision);
+  if (chunk_geometry(*cfg, &c->Pm, &c->Cm) != PBG_OK)
+    return fail(c, PBG_ERR_BAD_ARGUMENT, "num_batch_negs and num_uniform_negs are both 0: no chunk size (model.py:648-656)");
+
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= device || device < 0)
+    return fail(c, PBG_ERR_NO_DEVICE, "CUDA device %d not available", device);
+  CU(c, cudaSetDevice(device));
+  cudaDeviceProp prop;
+  CU(c, cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) return fail(c, PBG_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+
+  c->kmax = cfg->batches_in_flight;
+  c->U = cfg->num_uniform_negs;
+  c->Mm = c->Pm + c->U;
+  c->Ms = (c->Mm + 3) / 4 * 4;
+  c->Dp = (cfg->dim + 31) / 32 * 32;
+  c->spb = c->Cm * (2 * c->Mm + 2 * c->Pm) + (cfg->dynamic_relations ? 2 * c->Cm * c->Pm : 0);
+  const bool dyn = cfg->dynamic_relations != 0;
+  size_t nblk = (size_t)c->kmax * c->Cm;
+  size_t nN = nblk * c->Mm, nQ = nblk * c->Pm;
+  long long nocc = (long long)c->kmax * c->spb;
+  if (nocc > (1ll << 30)) return fail(c, PBG_ERR_TOO_LARGE, "wave of %lld row slots is beyond 2^30", nocc);
+
+  // ---- carve the workspace ------------------------------------------------------------------
+  size_t off = 0;
+  auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
+  size_t oX[4], oAux[4], oG[4], oS[2], oSpos[2], oCoef[4], oLoss[2], oViol[2];
+  oX[0] = take(nN * c->Dp * 4); oX[1] = take(nN * c->Dp * 4);
+  oAux[0] = take(nN * 4); oAux[1] = take(nN * 4);
+  if (dyn) { oX[2] = take(nQ * c->Dp * 4); oX[3] = take(nQ * c->Dp * 4); oAux[2] = take(nQ * 4); oAux[3] = take(nQ * 4); }
+  else { oX[2] = oX[1]; oX[3] = oX[0]; oAux[2] = oAux[1]; oAux[3] = oAux[0]; }
+  oG[0] = take(nN * c->Dp * 4); oG[1] = take(nN * c->Dp * 4); oG[2] = take(nQ * c->Dp * 4); oG[3] = take(nQ * c->Dp * 4);
+  for (int p = 0; p < 2; ++p) {
+    oS[p] = take(nQ * c->Ms * 4); oSpos[p] = take(nQ * 4); oLoss[p] = take(nQ * 4); oViol[p] = take(nQ * 4);
+  }
+  oCoef[0] = take(nN * 4); oCoef[1] = take(nN * 4); oCoef[2] = take(nQ * 4); oCoef[3] = take(nQ * 4);
+  size_t oRel = take(nblk * 8 * (size_t)cfg->dim * 4);
+  int swarps = pbg_sort_warps((int)nocc);
+  size_t oK0 = take((size_t)nocc * 8), oK1 = take((size_t)nocc * 8), oV0 = take((size_t)nocc * 4), oV1 = take((size_t)nocc * 4);
+  size_t oH = take((size_t)256 * swarps * 4);
+  size_t oSum = take(4 * sizeof(double)), oErr = take(256);
+  c->ws_bytes = off;
+  CU(c, cudaMalloc(&c->ws, c->ws_bytes));
+  CU(c, cudaMemsetAsync(c->ws, 0, c->ws_bytes, c->stream));
+  WaveBufs &b = c->bufs;
+  memset(&b, 0, sizeof b);
+  for (int a = 0; a < 4; ++a) {
+    b.X[a] = (float *)(c->ws + oX[a]);
+    b.aux[a] = (float *)(c->ws + oAux[a]);
+    b.GX[a] = (float *)(c->ws + oG[a]);
+    b.coef[a] = (float *)(c->ws + oCoef[a]);
+  }
+  b.xrows[0] = b.xrows[1] = c->Mm;
+  b.xrows[2] = b.xrows[3] = dyn ? c->Pm : c->Mm;
+  b.grows[0] = b.grows[1] = c->Mm;
+  b.grows[2] = b.grows[3] = c->Pm;
+  for (int p = 0; p < 2; ++p) {
+    b.S[p] = (float *)(c->ws + oS[p]);
+    b.spos[p] = (float *)(c->ws + oSpos[p]);
+    b.lossrow[p] = (float *)(c->ws + oLoss[p]);
+    b.violrow[p] = (int *)(c->ws + oViol[p]);
+  }
+  b.relpart = (float *)(c->ws + oRel);
+  c->sort.keys[0] = (unsigned long long *)(c->ws + oK0);
+  c->sort.keys[1] = (unsigned long long *)(c->ws + oK1);
+  c->sort.vals[0] = (unsigned int *)(c->ws + oV0);
+  c->sort.vals[1] = (unsigned int *)(c->ws + oV1);
+  c->sort.hist = (unsigned int *)(c->ws + oH);
+  c->sort.max_n = (int)nocc;
+  c->sum_dev = (double *)(c->ws + oSum);
+  c->errflag = (int *)(c->ws + oErr);
+  b.errflag = c->errflag;
+  CU(c, cudaStreamSynchronize(c->stream));
+  return PBG_OK;
+}
+
+extern "C" int pbg_destroy(pbg_context *c) {
+  if (!c) return PBG_OK;
+  cudaSetDevice(c->device);
+  if (c->ws) cudaFree(c->ws);
+  if (c->stats_dev) cudaFree(c->stats_dev);
+  for (int i = 0; i < 3; ++i) if (c->edge_dev[i]) cudaFree(c->edge_dev[i]);
+  for (int i = 0; i < 2; ++i) if (c->uni_dev[i]) cudaFree(c->uni_dev[i]);
+  delete c;
+  return PBG_OK;
+}
+
+extern "C" int pbg_set_hyperparameters(pbg_context *c, float lr, float relation_lr, float margin) {
+  if (!c) return PBG_ERR_BAD_ARGUMENT;
+  c->cfg.lr = lr; c->cfg.relation_lr = relation_lr; c->cfg.margin = margin;
+  return PBG_OK;
+}
+
+extern "C" int pbg_neg_columns(const pbg_context *c, int32_t count, int32_t *chunk_size, int32_t *chunks,
+                               int32_t *lhs_neg_cols, int32_t *rhs_neg_cols) {
+  if (!c || count < 0) return PBG_ERR_BAD_ARGUMENT;
+  int lim = c->cfg.num_batch_negs > 0 ? c->cfg.num_batch_negs : c->cfg.num_uniform_negs;
+  int P = count < lim ? count : lim;
+  int cols = c->cfg.num_batch_negs > 0 ? P + c->U : c->U;
+  if (chunk_size) *chunk_size = P;
+  if (chunks) *chunks = P > 0 ? (count + P - 1) / P : 0;
+  if (lhs_neg_cols) *lhs_neg_cols = c->cfg.disable_lhs_negs ? 0 : cols;
+  if (rhs_neg_cols) *rhs_neg_cols = c->cfg.disable_rhs_negs ? 0 : cols;
+  return PBG_OK;
+}
+
+static int bit_length(unsigned long long v) { int b = 0; while (v) { ++b; v >>= 1; } return b < 1 ? 1 : b; }
+
+// Fills the per-call parts of dims / bufs from the bucket.
+static int bind_bucket(pbg_context *c, const pbg_bucket *bk, WaveDims &d, WaveBufs &w) {
+  const pbg_config &cfg = c->cfg;
+  if (!bk || !bk->lhs_emb || !bk->rhs_emb) return fail(c, PBG_ERR_BAD_ARGUMENT, "bucket without embedding tables");
+  if (bk->lhs_rows <= 0 || bk->rhs_rows <= 0) return fail(c, PBG_ERR_BAD_ARGUMENT, "bucket with an empty table");
+  if (((uintptr_t)bk->lhs_emb | (uintptr_t)bk->rhs_emb) & 15) return fail(c, PBG_ERR_BAD_ARGUMENT, "embedding tables must be 16-byte aligned");
+  bool has_op = cfg.op != PBG_OP_NONE;
+  if (has_op && !bk->rhs_op) return fail(c, PBG_ERR_BAD_ARGUMENT, "operator configured but bucket has no rhs_op table");
+  if (has_op && cfg.dynamic_relations && !bk->lhs_op) return fail(c, PBG_ERR_BAD_ARGUMENT, "dynamic relations need the lhs_op table");
+  memset(&d, 0, sizeof d);
+  d.D = cfg.dim; d.Dp = c->Dp; d.Pm = c->Pm; d.U = c->U; d.Mm = c->Mm; d.Ms = c->Ms; d.Cm = c->Cm;
+  d.op = cfg.op; d.cmp = cfg.comparator; d.loss = cfg.loss; d.dynamic = cfg.dynamic_relations != 0;
+  d.batch_negs = cfg.num_batch_negs > 0;
+  d.neg_enabled[0] = !cfg.disable_lhs_negs; d.neg_enabled[1] = !cfg.disable_rhs_negs;
+  d.num_batch_negs = cfg.num_batch_negs; d.spb = c->spb; d.margin = cfg.margin;
+  d.n_rows[0] = bk->lhs_rows; d.n_rows[1] = bk->rhs_rows;
+  d.shared_table = bk->lhs_emb == bk->rhs_emb;
+  if (d.shared_table && bk->lhs_rows != bk->rhs_rows) return fail(c, PBG_ERR_BAD_ARGUMENT, "shared table with different row counts");
+  d.num_rels = cfg.num_rels;
+  unsigned long long emb_keys = (unsigned long long)bk->lhs_rows + (d.shared_table ? 0ull : (unsigned long long)bk->rhs_rows);
+  d.key_rel_base = emb_keys;
+  d.key_invalid = emb_keys + ((d.dynamic && has_op) ? 2ull * cfg.num_rels : 0ull);
+  w = c->bufs;
+  w.W[0] = bk->lhs_emb; w.G[0] = bk->lhs_state; w.W[1] = bk->rhs_emb; w.G[1] = bk->rhs_state;
+  w.theta[0] = has_op ? bk->rhs_op : nullptr; w.acc[0] = has_op ? bk->rhs_op_state : nullptr;
+  w.theta[1] = (has_op && d.dynamic) ? bk->lhs_op : nullptr; w.acc[1] = (has_op && d.dynamic) ? bk->lhs_op_state : nullptr;
+  return PBG_OK;
+}
+
+static int check_errflag(pbg_context *c) {
+  int flag = 0;
+  CU(c, cudaMemcpyAsync(&flag, c->errflag, sizeof flag, cudaMemcpyDeviceToHost, c->stream));
+  CU(c, cudaStreamSynchronize(c->stream));
+  if (flag) {
+    cudaMemsetAsync(c->errflag, 0, sizeof(int), c->stream);
+    if (flag & 2) return fail(c, PBG_ERR_TIMEOUT, "a bounded device-side wait ran out (flag %d)", flag);
+    return fail(c, PBG_ERR_INDEX_RANGE, "an entity or relation id was outside its table; those rows were skipped");
+  }
+  return PBG_OK;
+}
+
+static int run_forward(pbg_context *c, const WaveDims &d, const WaveBatches &wb, const WaveBufs &w) {
+  c->launches += launch_gather(d, wb, w, c->stream);
+  if (c->cfg.precision == PBG_PREC_FP32) c->launches += launch_score_simt(d, wb, w, c->stream);
+  else c->launches += launch_score_tc(d, wb, w, c->cfg.precision, c->stream);
+  return PBG_OK;
+}
+
+extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int64_t *lhs, const int64_t *rhs,
+                                 const int64_t *rel, int64_t num_edges, const pbg_batch *batches,
+                                 int32_t num_batches, const int64_t *ul, const int64_t *ur, uint64_t seed,
+                                 pbg_batch_stats *stats_out) {
+  if (!c) return PBG_ERR_BAD_ARGUMENT;
+  if (num_batches == 0) return PBG_OK;
+  if (!lhs || !rhs || !batches || num_batches < 0 || num_edges < 0) return fail(c, PBG_ERR_BAD_ARGUMENT, "null edge arrays or batch list");
+  CU(c, cudaSetDevice(c->device));
+  WaveDims d;
+  WaveBufs w;
+  int rc = bind_bucket(c, bk, d, w);
+  if (rc) return rc;
+  if (!bk->lhs_state || !bk->rhs_state) return fail(c, PBG_ERR_BAD_ARGUMENT, "bucket without RowAdagrad state");
+  if (d.op != PBG_OP_NONE && (!bk->rhs_op_state || (d.dynamic && !bk->lhs_op_state)))
+    return fail(c, PBG_ERR_BAD_ARGUMENT, "operator tables without AsyncAdagrad state");
+  if (d.dynamic && d.op != PBG_OP_NONE && !rel) return fail(c, PBG_ERR_BAD_ARGUMENT, "dynamic relations need the rel array");
+  for (int i = 0; i < num_batches; ++i) {
+    const pbg_batch &b = batches[i];
+    if (b.count < 0 || b.count > c->cfg.max_batch_size || b.offset < 0 || b.offset + b.count > num_edges)
+      return fail(c, PBG_ERR_BAD_ARGUMENT, "batch %d: offset %lld count %d outside [0, %lld] or above max_batch_size %d", i,
+                  (long long)b.offset, b.count, (long long)num_edges, c->cfg.max_batch_size);
+    if (!d.dynamic && (b.rel < 0 || b.rel >= c->cfg.num_rels))
+      return fail(c, PBG_ERR_INDEX_RANGE, "batch %d: relation %d outside [0, %d)", i, b.rel, c->cfg.num_rels);
+  }
+  w.lhs = (const long long *)lhs; w.rhs = (const long long *)rhs; w.rel = (const long long *)rel;
+  w.ul = (const long long *)ul; w.ur = (const long long *)ur;
+  w.seed = seed ^ (c->batches_done * 0x9E3779B97F4A7C15ull);
+  if (stats_out && num_batches > c->stats_cap) {
+    if (c->stats_dev) cudaFree(c->stats_dev);
+    c->stats_dev = nullptr;
+    int cap = num_batches + num_batches / 2 + 64;
+    CU(c, cudaMalloc(&c->stats_dev, (size_t)cap * sizeof(pbg_batch_stats)));
+    c->stats_cap = cap;
+  }
+  const int bits = bit_length(d.key_invalid);
+  for (int b0 = 0; b0 < num_batches; b0 += c->kmax) {
+    int kk = num_batches - b0 < c->kmax ? num_batches - b0 : c->kmax;
+    WaveBatches wb;
+    memset(&wb, 0, sizeof wb);
+    for (int i = 0; i < kk; ++i) {
+      const pbg_batch &b = batches[b0 + i];
+      wb.off[i] = b.offset; wb.n[i] = b.count; wb.gidx[i] = b0 + i;
+      wb.rel[i] = d.dynamic ? 0 : b.rel;
+      int wi = d.dynamic ? 0 : b.rel;
+      wb.wrel[i] = bk->relation_weights ? bk->relation_weights[wi] : 1.0f;
+    }
+    d.k = kk; d.nblk = kk * d.Cm; d.nocc = kk * d.spb;
+    c->launches += launch_build_keys(d, wb, w, c->sort.keys[0], c->sort.vals[0], c->stream);
+    c->launches += pbg_sort(c->sort, d.nocc, bits, c->stream);
+    run_forward(c, d, wb, w);
+    c->launches += launch_loss(d, wb, w, c->stream);
+    if (c->cfg.precision == PBG_PREC_FP32) c->launches += launch_grad_simt(d, wb, w, c->stream);
+    else c->launches += launch_grad_tc(d, wb, w, c->cfg.precision, c->stream);
+    c->launches += launch_update(d, wb, w, c->sort.keys[c->sort.result], c->sort.vals[c->sort.result],
+                                 c->cfg.lr, c->cfg.relation_lr, c->stream);
+    c->launches += launch_stats(d, wb, w, stats_out ? c->stats_dev : nullptr, c->sum_dev, c->stream);
+  }
+  c->batches_done += (unsigned long long)num_batches;
+  CU(c, cudaGetLastError());
+  if (stats_out) {
+    CU(c, cudaMemcpyAsync(stats_out, c->stats_dev, (size_t)num_batches * sizeof(pbg_batch_stats),
+                          cudaMemcpyDeviceToHost, c->stream));
+    return check_errflag(c);
+  }
+  return PBG_OK;
+}
+
+static int grow_i64(pbg_context *c, long long **p, long long need) {
+  if (*p) cudaFree(*p);
+  *p = nullptr;
+  CU(c, cudaMalloc(p, (size_t)need * sizeof(long long)));
+  return PBG_OK;
+}
+
+extern "C" int pbg_train_batches_host(pbg_context *c, const pbg_bucket *bk, const int64_t *lhs, const int64_t *rhs,
+                                      const int64_t *rel, int64_t num_edges, const pbg_batch *batches,
+                                      int32_t num_batches, const int64_t *ul, const int64_t *ur, uint64_t seed,
+                                      pbg_batch_stats *stats_out) {
+  if (!c) return PBG_ERR_BAD_ARGUMENT;
+  if (num_batches == 0) return PBG_OK;
+  if (!lhs || !rhs || num_edges < 0) return fail(c, PBG_ERR_BAD_ARGUMENT, "null edge arrays");
+  CU(c, cudaSetDevice(c->device));
+  if (num_edges > c->edge_cap) {
+    long long cap = num_edges + num_edges / 4 + 1024;
+    for (int i = 0; i < 3; ++i) { int rc = grow_i64(c, &c->edge_dev[i], cap); if (rc) return rc; }
+    c->edge_cap = cap;
+  }
+  size_t eb = (size_t)num_edges * sizeof(long long);
+  CU(c, cudaMemcpyAsync(c->edge_dev[0], lhs, eb, cudaMemcpyHostToDevice, c->stream));
+  CU(c, cudaMemcpyAsync(c->edge_dev[1], rhs, eb, cudaMemcpyHostToDevice, c->stream));
+  if (rel) CU(c, cudaMemcpyAsync(c->edge_dev[2], rel, eb, cudaMemcpyHostToDevice, c->stream));
+  long long *uld = nullptr, *urd = nullptr;
+  if (ul || ur) {
+    long long per = (long long)num_batches * c->Cm * c->U;
+    if (per > c->uni_cap) {
+      for (int i = 0; i < 2; ++i) { int rc = grow_i64(c, &c->uni_dev[i], per + 1024); if (rc) return rc; }
+      c->uni_cap = per + 1024;
+    }
+    if (ul) { CU(c, cudaMemcpyAsync(c->uni_dev[0], ul, (size_t)per * 8, cudaMemcpyHostToDevice, c->stream)); uld = c->uni_dev[0]; }
+    if (ur) { CU(c, cudaMemcpyAsync(c->uni_dev[1], ur, (size_t)per * 8, cudaMemcpyHostToDevice, c->stream)); urd = c->uni_dev[1]; }
+  }
+  return pbg_train_batches(c, bk, (const int64_t *)c->edge_dev[0], (const int64_t *)c->edge_dev[1],
+                           rel ? (const int64_t *)c->edge_dev[2] : nullptr, num_edges, batches, num_batches,
+                           (const int64_t *)uld, (const int64_t *)urd, seed, stats_out);
+}
+
+extern "C" int pbg_read_stats(pbg_context *c, pbg_batch_stats *out) {
+  if (!c || !out) return PBG_ERR_BAD_ARGUMENT;
+  CU(c, cudaSetDevice(c->device));
+  double s[4];
+  CU(c, cudaMemcpyAsync(s, c->sum_dev, sizeof s, cudaMemcpyDeviceToHost, c->stream));
+  CU(c, cudaMemsetAsync(c->sum_dev, 0, sizeof s, c->stream));
+  int rc = check_errflag(c);
+  out->loss = (float)s[0]; out->reg = 0.f;
+  out->violators_lhs = (int64_t)(s[1] + 0.5); out->violators_rhs = (int64_t)(s[2] + 0.5); out->count = (int64_t)(s[3] + 0.5);
+  return rc;
+}
+
+extern "C" int pbg_score_batch(pbg_context *c, const pbg_bucket *bk, const int64_t *lhs, const int64_t *rhs,
+                               const int64_t *rel, int32_t count, int32_t relidx, const int64_t *ul,
+                               const int64_t *ur, uint64_t seed, float *lhs_pos, float *rhs_pos, float *lhs_neg,
+                               float *rhs_neg) {
+  if (!c) return PBG_ERR_BAD_ARGUMENT;
+  if (count == 0) return PBG_OK;
+  if (!lhs || !rhs || !lhs_pos || !rhs_pos || count < 0 || count > c->cfg.max_batch_size)
+    return fail(c, PBG_ERR_BAD_ARGUMENT, "bad score_batch arguments (count %d, max_batch_size %d)", count, c->cfg.max_batch_size);
+  CU(c, cudaSetDevice(c->device));
+  WaveDims d;
+  WaveBufs w;
+  int rc = bind_bucket(c, bk, d, w);
+  if (rc) return rc;
+  if (!d.dynamic && (relidx < 0 || relidx >= c->cfg.num_rels)) return fail(c, PBG_ERR_INDEX_RANGE, "relation %d outside [0, %d)", relidx, c->cfg.num_rels);
+  if (d.dynamic && d.op != PBG_OP_NONE && !rel) return fail(c, PBG_ERR_BAD_ARGUMENT, "dynamic relations need the rel array");
+  if ((d.neg_enabled[0] && !lhs_neg) || (d.neg_enabled[1] && !rhs_neg)) return fail(c, PBG_ERR_BAD_ARGUMENT, "null negative-score output");
+  w.lhs = (const long long *)lhs; w.rhs = (const long long *)rhs; w.rel = (const long long *)rel;
+  w.ul = (const long long *)ul; w.ur = (const long long *)ur; w.seed = seed;
+  WaveBatches wb;
+  memset(&wb, 0, sizeof wb);
+  wb.n[0] = count; wb.rel[0] = d.dynamic ? 0 : relidx; wb.wrel[0] = 1.0f;
+  d.k = 1; d.nblk = d.Cm; d.nocc = d.spb;
+  run_forward(c, d, wb, w);
+  c->launches += launch_export_scores(d, wb, w, lhs_pos, rhs_pos, lhs_neg, rhs_neg, c->stream);
+  CU(c, cudaGetLastError());
+  return check_errflag(c);
+}
+
+extern "C" int pbg_row_adagrad(pbg_context *c, float *emb, float *state, int64_t num_rows, const int64_t *rows,
+                               const float *grads, int32_t n, float lr) {
+  if (!c) return PBG_ERR_BAD_ARGUMENT;
+  if (n == 0) return PBG_OK;
+  if (!emb || !state || !rows || !grads || n < 0 || num_rows <= 0) return fail(c, PBG_ERR_BAD_ARGUMENT, "bad row_adagrad arguments");
+  if (n > c->sort.max_n) return fail(c, PBG_ERR_TOO_LARGE, "%d gradient rows exceed this context's sort capacity %d", n, c->sort.max_n);
+  CU(c, cudaSetDevice(c->device));
+  c->launches += launch_iota_keys((const long long *)rows, num_rows, n, c->sort.keys[0], c->sort.vals[0], c->errflag, c->stream);
+  c->launches += pbg_sort(c->sort, n, bit_length((unsigned long long)num_rows), c->stream);
+  c->launches += launch_row_adagrad_sorted(emb, state, c->cfg.dim, c->sort.keys[c->sort.result], c->sort.vals[c->sort.result],
+                                           grads, n, lr, (unsigned long long)num_rows, c->stream);
+  CU(c, cudaGetLastError());
+  return check_errflag(c);
+}

@@ -1,0 +1,203 @@
+// Shared declarations of the sm_100a training-step library: wave layout in HBM, decoding of
+// row slots, and the small device helpers every kernel uses.
+//
+// Vocabulary (PyTorch-BigGraph's): a *bucket* is a (lhs partition, rhs partition) pair; a
+// *batch* is batch_size edges; a batch is cut into *chunks* of P = num_batch_negs edges which
+// serve as each other's negatives, plus U uniformly drawn negative rows per chunk
+// (torchbiggraph/model.py:508-622).  A *wave* is the k batches this library keeps in flight.
+//
+// Layout of one wave in the workspace (all float32, row stride Dp = dim rounded up to 32):
+//   block blk = b * Cm + c        (b-th batch of the wave, c-th chunk, Cm chunks per batch)
+//   N0[blk][Mm][Dp]  prepared lhs rows: Pm chunk rows then U uniform rows   (Mm = Pm + U)
+//   N1[blk][Mm][Dp]  prepared rhs rows: Pm chunk rows then U uniform rows
+//   Q0[blk][Pm][Dp]  rows scored against N0 (the "lhs corrupted" problem 0)
+//   Q1[blk][Pm][Dp]  rows scored against N1 (the "rhs corrupted" problem 1)
+// Standard relations (operator on the rhs only): Q0 is the first Pm rows of N1 and Q1 the first
+// Pm rows of N0 (aliases).  Dynamic relations: N0/N1 hold rows WITHOUT operator, Q0 holds
+// op_rhs[rel](rhs rows), Q1 holds op_lhs[rel](lhs rows) (model.py:705-758).
+//   S_p[blk][Pm][Ms]   scores of problem p, later overwritten by the coefficient matrix T_p
+//   GN_p[blk][Mm][Dp] = T_p^T . Q_p      GQ_p[blk][Pm][Dp] = T_p . N_p
+// T_p holds d(loss)/d(score) with the gradient of the positive score folded into its (masked,
+// otherwise unused) diagonal, so the two products above are the whole backward of the
+// comparator.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/pbg_b200.h"
+
+#define PBG_KMAX 32                 // most batches in one wave
+#define PBG_MASKED (-1e9f)          // torchbiggraph/model.py:836-839
+#define PBG_ADAGRAD_EPS 1e-10f      // row_adagrad.py:94, async_adagrad.py:84
+
+enum { ARR_N0 = 0, ARR_N1 = 1, ARR_Q0 = 2, ARR_Q1 = 3, ARR_R0 = 4, ARR_R1 = 5 };
+
+struct WaveDims {
+  int D, Dp;            // dim, workspace row stride (floats)
+  int Pm, U, Mm, Ms;    // chunk slots, uniform negatives, Pm+U, score row stride
+  int Cm;               // chunks per batch (max)
+  int k, nblk;          // batches in this wave, k*Cm
+  int op, cmp, loss, dynamic;
+  int batch_negs;       // 1: batch_uniform mode, 0: uniform-only mode (num_batch_negs == 0)
+  int neg_enabled[2];   // problem 0 = lhs negatives, problem 1 = rhs negatives
+  int num_batch_negs;
+  int spb;              // occurrence slots per batch (see occ_decode)
+  int nocc;             // k * spb
+  float margin;
+  long long n_rows[2];  // rows of the lhs / rhs table
+  int shared_table;     // lhs and rhs read the same table
+  int num_rels;
+  unsigned long long key_rel_base;   // first sort key of operator-table rows
+  unsigned long long key_invalid;    // sort key of slots that carry no gradient
+};
+
+struct WaveBatches {
+  long long off[PBG_KMAX];    // first edge of the batch in the edge arrays
+  long long gidx[PBG_KMAX];   // index of the batch in the call (uniform-id array, stats, RNG)
+  int n[PBG_KMAX];            // edges in the batch
+  int rel[PBG_KMAX];          // relation of the batch (standard mode)
+  float wrel[PBG_KMAX];       // relation weight of the batch
+};
+
+struct WaveBufs {
+  float *X[4];       int xrows[4];   // operand arrays N0,N1,Q0,Q1 (rows per block; aliases allowed)
+  float *aux[4];                     // per operand row: cos -> 1/|z|, l2 -> |y|^2 (indexed like X)
+  float *GX[4];      int grows[4];   // gradient arrays GN0,GN1,GQ0,GQ1
+  float *S[2];                       // scores / coefficient matrices
+  float *spos[2];                    // positive scores [nblk][Pm]
+  float *coef[4];                    // l2: colsum(T0), colsum(T1), rowsum(T0), rowsum(T1)
+  float *lossrow[2];                 // per positive row: weighted loss term
+  int *violrow[2];                   // per positive row: #(neg > pos)
+  const long long *lhs, *rhs, *rel;  // edge arrays
+  const long long *ul, *ur;          // uniform ids [batches][Cm][U] or null
+  unsigned long long seed;
+  float *W[2], *G[2];                // embedding tables / RowAdagrad state (lhs, rhs)
+  float *theta[2], *acc[2];          // operator tables: [0] applied to rhs rows, [1] to lhs rows
+  float *relpart;                    // standard mode: [k][Cm][D] partial operator gradients
+  int *errflag;                      // device error word (bit 0: id out of range)
+};
+
+struct BlockInfo { int b, c, Pl, n; long long e0; };
+
+// Which batch/chunk a block is, its logical chunk size Pl = min(num_batch_negs or U, batch
+// edges) (model.py:648-656) and how many of its Pm slots hold real edges.
+__device__ __forceinline__ BlockInfo block_info(const WaveDims &d, const WaveBatches &wb, int blk) {
+  BlockInfo bi;
+  bi.b = blk / d.Cm;
+  bi.c = blk - bi.b * d.Cm;
+  int nb = wb.n[bi.b];
+  int lim = d.batch_negs ? d.num_batch_negs : d.U;
+  bi.Pl = nb < lim ? nb : lim;
+  int first = bi.c * bi.Pl;
+  int n = nb - first;
+  bi.n = bi.Pl > 0 ? (n < 0 ? 0 : (n > bi.Pl ? bi.Pl : n)) : 0;
+  bi.e0 = wb.off[bi.b] + first;
+  return bi;
+}
+
+// Counter-based generator for device-drawn uniform negatives (stands where the reference
+// calls torch.randint, model.py:70-75): splitmix64 of (seed, batch, side, chunk, j).
+__device__ __forceinline__ unsigned long long pbg_mix64(unsigned long long z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+__device__ __forceinline__ long long pbg_uniform_id(unsigned long long seed, long long gidx, int side,
+                                                    int c, int j, long long nrows) {
+  unsigned long long h = pbg_mix64(seed ^ pbg_mix64((unsigned long long)gidx * 2ull + (unsigned)side));
+  h = pbg_mix64(h + ((unsigned long long)(unsigned)c << 32) + (unsigned)j);
+  return (long long)__umul64hi(h, (unsigned long long)nrows);
+}
+
+// Table row behind slot r of block (b, c) on `side` (0 lhs, 1 rhs); -1 when the slot is empty.
+__device__ __forceinline__ long long slot_row(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
+                                              const BlockInfo &bi, int side, int r) {
+  if (r < d.Pm) {
+    if (r >= bi.n) return -1;
+    return side == 0 ? w.lhs[bi.e0 + r] : w.rhs[bi.e0 + r];
+  }
+  if (bi.n == 0 || !d.neg_enabled[side]) return -1;
+  int j = r - d.Pm;
+  const long long *u = side == 0 ? w.ul : w.ur;
+  if (u) return u[(wb.gidx[bi.b] * d.Cm + bi.c) * (long long)d.U + j];
+  return pbg_uniform_id(w.seed, wb.gidx[bi.b], side, bi.c, j, d.n_rows[side]);
+}
+
+// Occurrence index o -> (batch b, array a, block, row).  Per batch the slots are enumerated
+// [N0: Cm*Mm | N1: Cm*Mm | Q0: Cm*Pm | Q1: Cm*Pm | R0: Cm*Pm | R1: Cm*Pm]; R0/R1 (operator-table
+// rows touched through Q0/Q1) exist only with dynamic relations.  Enumeration is batch-major so
+// that a stable sort by row keeps a row's occurrences in batch order.
+struct Occ { int b, a, blk, r; };
+__device__ __forceinline__ Occ occ_decode(const WaveDims &d, int o) {
+  Occ q;
+  q.b = o / d.spb;
+  int w = o - q.b * d.spb;
+  int nN = d.Cm * d.Mm, nQ = d.Cm * d.Pm;
+  int rows;
+  if (w < nN) { q.a = ARR_N0; rows = d.Mm; }
+  else if ((w -= nN) < nN) { q.a = ARR_N1; rows = d.Mm; }
+  else if ((w -= nN) < nQ) { q.a = ARR_Q0; rows = d.Pm; }
+  else if ((w -= nQ) < nQ) { q.a = ARR_Q1; rows = d.Pm; }
+  else if ((w -= nQ) < nQ) { q.a = ARR_R0; rows = d.Pm; }
+  else { w -= nQ; q.a = ARR_R1; rows = d.Pm; }
+  int c = w / rows;
+  q.r = w - c * rows;
+  q.blk = q.b * d.Cm + c;
+  return q;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ int warp_sum_int(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ void st4(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ float4 f4zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+__device__ __forceinline__ float4 operator+(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float4 operator-(float4 a, float4 b) { return make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w); }
+__device__ __forceinline__ float4 operator*(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+__device__ __forceinline__ float4 operator*(float4 a, float s) { return make_float4(a.x * s, a.y * s, a.z * s, a.w * s); }
+__device__ __forceinline__ float f4dot(float4 a, float4 b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
+__device__ __forceinline__ float f4sum(float4 a) { return a.x + a.y + a.z + a.w; }
+
+// ---- host-side launchers (one per translation unit) ------------------------------------------
+struct SortPlan {
+  unsigned long long *keys[2];
+  unsigned int *vals[2];
+  unsigned int *hist;     // [256][warps]
+  int max_n;              // capacity
+  int result;             // which of keys[]/vals[] holds the sorted output after pbg_sort
+};
+int pbg_sort_warps(int n);
+// Stable LSD radix sort of n (key, value) pairs on `bits` low key bits; returns launches made.
+int pbg_sort(SortPlan &sp, int n, int bits, cudaStream_t st);
+
+int launch_build_keys(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
+                      unsigned long long *keys, unsigned int *vals, cudaStream_t st);
+int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
+int launch_score_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
+int launch_grad_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
+int launch_loss(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
+int launch_export_scores(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
+                         float *lhs_pos, float *rhs_pos, float *lhs_neg, float *rhs_neg, cudaStream_t st);
+int launch_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
+                  const unsigned long long *keys, const unsigned int *vals, float lr, float rel_lr,
+                  cudaStream_t st);
+int launch_stats(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
+                 pbg_batch_stats *per_batch_dev, double *sum_dev, cudaStream_t st);
+int launch_row_adagrad_sorted(float *emb, float *state, int dim, const unsigned long long *keys,
+                              const unsigned int *vals, const float *grads, int n, float lr,
+                              unsigned long long key_invalid, cudaStream_t st);
+int launch_iota_keys(const long long *rows, long long num_rows, int n, unsigned long long *keys,
+                     unsigned int *vals, int *errflag, cudaStream_t st);

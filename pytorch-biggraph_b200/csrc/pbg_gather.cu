@@ -1,0 +1,252 @@
+// Row gather fused with the relation operator and comparator.prepare: builds the operand tiles
+// of one wave (see pbg_common.cuh for the layout) straight from the embedding tables, one warp
+// per row slot, 16-byte loads and stores.  Replaces, for a whole wave at once,
+//   F.embedding gathers                 torchbiggraph/model.py:57-61, 645-646
+//   sample_entities                     torchbiggraph/model.py:70-75
+//   adjust_embs (operator + prepare)    torchbiggraph/model.py:478-506, operators.py:49-157, 197-338
+//   zero padding of the last chunk      torchbiggraph/model.py:787-800
+//   the positive scores                 torchbiggraph/model.py:177, 267-274
+// and emits the sort keys that group gradient slots by table row.
+#include "pbg_common.cuh"
+
+#define GATHER_WARPS 8
+
+template <int VEC>
+__device__ __forceinline__ void load_row(float4 (&v)[VEC], const float *row, int D, int lane) {
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int d = c * 128 + lane * 4;
+    v[c] = d < D ? ld4(row + d) : f4zero();
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void store_row(float *row, const float4 (&v)[VEC], int D, int lane) {
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int d = c * 128 + lane * 4;
+    if (d < D) st4(row + d, v[c]);
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void zero_row(float *row, int D, int lane) {
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int d = c * 128 + lane * 4;
+    if (d < D) st4(row + d, f4zero());
+  }
+}
+
+// z = op(x; theta).  complex_diagonal pairs element d with d +- D/2, which lives in another
+// lane: the partner chunk is re-read from memory (an L1 hit).
+template <int VEC>
+__device__ __forceinline__ void apply_operator(float4 (&z)[VEC], const float4 (&x)[VEC], const float *xrow,
+                                               const float *theta, int op, int D, int lane) {
+  int h = D >> 1;
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int d = c * 128 + lane * 4;
+    if (d >= D) { z[c] = f4zero(); continue; }
+    if (op == PBG_OP_NONE || theta == nullptr) { z[c] = x[c]; continue; }
+    float4 t = ld4(theta + d);
+    if (op == PBG_OP_DIAGONAL) z[c] = x[c] * t;
+    else if (op == PBG_OP_TRANSLATION) z[c] = x[c] + t;
+    else {  // complex_diagonal: theta = [real | imag]
+      int dp = d < h ? d + h : d - h;
+      float4 xp = ld4(xrow + dp), tp = ld4(theta + dp);
+      z[c] = d < h ? x[c] * t - xp * tp      // re = a_re p_re - a_im p_im
+                   : xp * t + x[c] * tp;     // im = a_re p_im + a_im p_re
+    }
+  }
+}
+
+// comparator.prepare in place; returns the per-row auxiliary value kept for the later kernels
+// (cos: 1/|z|, l2 family: |y|^2, dot: 0).
+template <int VEC>
+__device__ __forceinline__ float prepare_row(float4 (&z)[VEC], int cmp) {
+  if (cmp == PBG_CMP_DOT) return 0.f;
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) ss += f4dot(z[c], z[c]);
+  ss = warp_sum(ss);
+  if (cmp != PBG_CMP_COS) return ss;
+  float inv = 1.0f / sqrtf(ss);          // no epsilon: a zero row gives inf/NaN as in model.py:191-192
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) z[c] = z[c] * inv;
+  return inv;
+}
+
+template <int VEC>
+__device__ __forceinline__ float positive_score(const float4 (&a)[VEC], const float4 (&b)[VEC], int cmp) {
+  float s = 0.f;
+  if (cmp == PBG_CMP_DOT || cmp == PBG_CMP_COS) {
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) s += f4dot(a[c], b[c]);
+    return warp_sum(s);
+  }
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) { float4 df = a[c] - b[c]; s += f4dot(df, df); }
+  s = warp_sum(s);
+  return cmp == PBG_CMP_L2 ? -sqrtf(fmaxf(s, 1e-30f)) : -s;
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(32 * GATHER_WARPS) gather_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * GATHER_WARPS + (threadIdx.x >> 5);
+  if (item >= (long long)d.nblk * d.Mm) return;
+  int blk = (int)(item / d.Mm), r = (int)(item - (long long)blk * d.Mm);
+  BlockInfo bi = block_info(d, wb, blk);
+  const int D = d.D;
+  size_t nrow = (size_t)blk * d.Mm + r;
+  float *n0 = w.X[ARR_N0] + nrow * d.Dp, *n1 = w.X[ARR_N1] + nrow * d.Dp;
+  float4 x[VEC], z[VEC], y0[VEC], y1[VEC];
+
+  if (r < d.Pm) {                                           // ---- an edge of the chunk ----------
+    size_t qrow = (size_t)blk * d.Pm + r;
+    float *q0 = d.dynamic ? w.X[ARR_Q0] + qrow * d.Dp : nullptr;
+    float *q1 = d.dynamic ? w.X[ARR_Q1] + qrow * d.Dp : nullptr;
+    long long il = -1, ir = -1, rl = d.dynamic ? 0 : wb.rel[bi.b];
+    bool ok = r < bi.n;
+    if (ok) {
+      il = w.lhs[bi.e0 + r];
+      ir = w.rhs[bi.e0 + r];
+      if (d.dynamic && d.op != PBG_OP_NONE) rl = w.rel[bi.e0 + r];
+      if (il < 0 || il >= d.n_rows[0] || ir < 0 || ir >= d.n_rows[1] ||
+          (d.op != PBG_OP_NONE && (rl < 0 || rl >= d.num_rels))) {
+        if (lane == 0) atomicOr(w.errflag, 1);
+        ok = false;
+      }
+    }
+    if (!ok) {                                              // padding row: exact zeros
+      zero_row<VEC>(n0, D, lane);
+      zero_row<VEC>(n1, D, lane);
+      if (d.dynamic) { zero_row<VEC>(q0, D, lane); zero_row<VEC>(q1, D, lane); }
+      if (lane == 0) {
+        w.aux[ARR_N0][nrow] = 0.f; w.aux[ARR_N1][nrow] = 0.f;
+        if (d.dynamic) { w.aux[ARR_Q0][qrow] = 0.f; w.aux[ARR_Q1][qrow] = 0.f; }
+        w.spos[0][qrow] = 0.f; w.spos[1][qrow] = 0.f;
+      }
+      return;
+    }
+    const float *xl = w.W[0] + (size_t)il * D, *xr = w.W[1] + (size_t)ir * D;
+    const float *th0 = (d.op != PBG_OP_NONE && w.theta[0]) ? w.theta[0] + (size_t)rl * D : nullptr;
+    // lhs row without operator -> N0
+    load_row<VEC>(x, xl, D, lane);
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) y0[c] = x[c];
+    float a0 = prepare_row<VEC>(y0, d.cmp);
+    store_row<VEC>(n0, y0, D, lane);
+    if (!d.dynamic) {
+      // rhs row through the operator -> N1; one positive score shared by both problems
+      load_row<VEC>(x, xr, D, lane);
+      apply_operator<VEC>(y1, x, xr, th0, d.op, D, lane);
+      float a1 = prepare_row<VEC>(y1, d.cmp);
+      store_row<VEC>(n1, y1, D, lane);
+      float s = positive_score<VEC>(y0, y1, d.cmp);
+      if (lane == 0) {
+        w.aux[ARR_N0][nrow] = a0; w.aux[ARR_N1][nrow] = a1;
+        w.spos[0][qrow] = s; w.spos[1][qrow] = s;
+      }
+    } else {
+      const float *th1 = (d.op != PBG_OP_NONE && w.theta[1]) ? w.theta[1] + (size_t)rl * D : nullptr;
+      // op_lhs(lhs row) -> Q1 (x still holds the lhs row)
+      apply_operator<VEC>(z, x, xl, th1, d.op, D, lane);
+      float aq1 = prepare_row<VEC>(z, d.cmp);
+      store_row<VEC>(q1, z, D, lane);
+      // rhs row without operator -> N1
+      load_row<VEC>(x, xr, D, lane);
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) y1[c] = x[c];
+      float a1 = prepare_row<VEC>(y1, d.cmp);
+      store_row<VEC>(n1, y1, D, lane);
+      float s1 = positive_score<VEC>(y1, z, d.cmp);         // problem 1: c(rhs, op_lhs(lhs))
+      // op_rhs(rhs row) -> Q0
+      apply_operator<VEC>(z, x, xr, th0, d.op, D, lane);
+      float aq0 = prepare_row<VEC>(z, d.cmp);
+      store_row<VEC>(q0, z, D, lane);
+      float s0 = positive_score<VEC>(y0, z, d.cmp);         // problem 0: c(lhs, op_rhs(rhs))
+      if (lane == 0) {
+        w.aux[ARR_N0][nrow] = a0; w.aux[ARR_N1][nrow] = a1;
+        w.aux[ARR_Q0][qrow] = aq0; w.aux[ARR_Q1][qrow] = aq1;
+        w.spos[0][qrow] = s0; w.spos[1][qrow] = s1;
+      }
+    }
+    return;
+  }
+  // ---- a uniformly drawn negative row, one per side ------------------------------------------
+#pragma unroll
+  for (int side = 0; side < 2; ++side) {
+    float *dst = side == 0 ? n0 : n1;
+    long long id = slot_row(d, wb, w, bi, side, r);
+    if (id >= d.n_rows[side]) { if (lane == 0) atomicOr(w.errflag, 1); id = -1; }
+    if (id < 0) {
+      zero_row<VEC>(dst, D, lane);
+      if (lane == 0) w.aux[side][nrow] = 0.f;
+      continue;
+    }
+    const float *xrow = w.W[side] + (size_t)id * D;
+    load_row<VEC>(x, xrow, D, lane);
+    const float *th = nullptr;
+    if (side == 1 && !d.dynamic && d.op != PBG_OP_NONE && w.theta[0]) {
+      int rl = wb.rel[bi.b];
+      if (rl >= 0 && rl < d.num_rels) th = w.theta[0] + (size_t)rl * D;
+    }
+    apply_operator<VEC>(z, x, xrow, th, d.op, D, lane);
+    float a = prepare_row<VEC>(z, d.cmp);
+    store_row<VEC>(dst, z, D, lane);
+    if (lane == 0) w.aux[side][nrow] = a;
+  }
+}
+
+int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
+  long long items = (long long)d.nblk * d.Mm;
+  int ctas = (int)((items + GATHER_WARPS - 1) / GATHER_WARPS);
+  int vec = (d.D + 127) / 128;
+  if (vec <= 1) gather_kernel<1><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else if (vec <= 2) gather_kernel<2><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else if (vec <= 4) gather_kernel<4><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else if (vec <= 8) gather_kernel<8><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else gather_kernel<16><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  return 1;
+}
+
+// One thread per occurrence slot: the sort key is the table row the slot's gradient belongs to.
+//   lhs-table rows            key = row
+//   rhs-table rows            key = row (+ lhs rows when the tables differ)
+//   operator-table rows       key = key_rel_base + table * num_rels + rel   (dynamic relations)
+//   slots without gradient    key = key_invalid (sorts to the end)
+__global__ void build_keys_kernel(WaveDims d, WaveBatches wb, WaveBufs w, unsigned long long *keys,
+                                  unsigned int *vals) {
+  int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= d.nocc) return;
+  Occ q = occ_decode(d, o);
+  BlockInfo bi = block_info(d, wb, q.blk);
+  unsigned long long key = d.key_invalid;
+  unsigned long long rbase = d.shared_table ? 0ull : (unsigned long long)d.n_rows[0];
+  if (q.a == ARR_N0 || q.a == ARR_N1) {
+    int side = q.a == ARR_N0 ? 0 : 1;
+    long long row = slot_row(d, wb, w, bi, side, q.r);
+    if (row >= 0 && row < d.n_rows[side]) key = (side ? rbase : 0ull) + (unsigned long long)row;
+  } else if (q.r < bi.n) {
+    long long e = bi.e0 + q.r;
+    if (q.a == ARR_Q0) {
+      long long row = w.rhs[e];
+      if (row >= 0 && row < d.n_rows[1]) key = rbase + (unsigned long long)row;
+    } else if (q.a == ARR_Q1) {
+      long long row = w.lhs[e];
+      if (row >= 0 && row < d.n_rows[0]) key = (unsigned long long)row;
+    } else if (d.dynamic && d.op != PBG_OP_NONE) {
+      long long rl = w.rel[e];
+      int t = q.a == ARR_R0 ? 0 : 1;
+      if (rl >= 0 && rl < d.num_rels) key = d.key_rel_base + (unsigned long long)t * d.num_rels + (unsigned long long)rl;
+    }
+  }
+  keys[o] = key;
+  vals[o] = (unsigned int)o;
+}
+
+int launch_build_keys(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
+                      unsigned long long *keys, unsigned int *vals, cudaStream_t st) {
+  build_keys_kernel<<<(d.nocc + 255) / 256, 256, 0, st>>>(d, wb, w, keys, vals);
+  return 1;
+}

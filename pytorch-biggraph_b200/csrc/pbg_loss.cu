@@ -1,0 +1,242 @@
+// Loss, its gradient, masks and batch statistics, one warp per positive edge and problem.
+// Fuses, for a whole wave:
+//   the ignore masks (-1e9)             torchbiggraph/model.py:566-580, 836-844
+//   logistic / ranking / softmax        torchbiggraph/losses.py:53-161
+//   relation weight, sum of both sides  torchbiggraph/batching.py:139-150
+//   violator counts                     torchbiggraph/train_cpu.py:98-99
+//   d(loss)/d(score)                    (autograd of the above)
+// and rewrites the score matrix S_p in place as the coefficient matrix T_p whose two products
+// with the operand tiles are the backward pass of the comparator:
+//   dot / cos :  T_ij = dS_ij,            T_ii = d(loss)/d(pos score_i)
+//   l2        :  T_ij = -dS_ij / S_ij     (= -2 dLoss/d(squared distance)), same on the diagonal
+//   squared_l2:  T_ij = 2 dS_ij
+// The diagonal of S is always masked, which is what frees it to carry the positive pair.
+#include "pbg_common.cuh"
+
+#define LOSS_WARPS 8
+
+__device__ __forceinline__ float softplusf(float x) {           // log(1 + e^x), stable
+  return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)));
+}
+__device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// column j of the negatives of a chunk: is it ignored, and does it exist at all?
+struct ColMask { bool masked; };
+__device__ __forceinline__ bool col_masked(const WaveDims &d, const BlockInfo &bi, int enabled, int i, int j) {
+  if (!enabled) return true;
+  if (j >= d.Pm) return false;                       // uniform negatives are never masked
+  if (!d.batch_negs) return true;                    // uniform-only mode: no batch negatives
+  return j == i || j >= bi.n;                        // own positive; padding of the last chunk
+}
+
+__device__ __forceinline__ float coef_from_dscore(int cmp, float dS, float S) {
+  if (cmp == PBG_CMP_L2) return (-S > 1e-15f) ? -dS / S : 0.f;   // clamp at 1e-30 kills the gradient
+  if (cmp == PBG_CMP_SQUARED_L2) return 2.0f * dS;
+  return dS;
+}
+
+__global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * LOSS_WARPS + (threadIdx.x >> 5);
+  long long per_prob = (long long)d.nblk * d.Pm;
+  if (item >= 2 * per_prob) return;
+  int p = (int)(item / per_prob);
+  long long rem = item - p * per_prob;
+  int blk = (int)(rem / d.Pm), i = (int)(rem - (long long)blk * d.Pm);
+  BlockInfo bi = block_info(d, wb, blk);
+  if (bi.n == 0) return;
+  float *S = w.S[p] + ((size_t)blk * d.Pm + i) * d.Ms;
+  size_t prow = (size_t)blk * d.Pm + i;
+  const int Mm = d.Mm;
+  if (i >= bi.n) {                                   // padded positive: contributes nothing
+    for (int j = lane; j < d.Ms; j += 32) S[j] = 0.f;
+    if (lane == 0) {
+      w.lossrow[p][prow] = 0.f; w.violrow[p][prow] = 0;
+      if (d.cmp >= PBG_CMP_L2) w.coef[2 + p][prow] = 0.f;
+    }
+    return;
+  }
+  const int enabled = d.neg_enabled[p];
+  const float s = w.spos[p][prow];
+  const float wr = wb.wrel[bi.b];
+  // number of negative columns the reference's score matrix has for this row (masked included)
+  const int Mlog = !enabled ? 0 : (d.batch_negs ? bi.Pl + d.U : d.U);
+  float lossv = 0.f, ds = 0.f, rowsum = 0.f;
+  int viol = 0;
+
+  if (d.loss == PBG_LOSS_SOFTMAX) {
+    // -s + log(e^s + sum_j e^S_ij); masked entries are e^-1e9 = 0 (losses.py:143-159)
+    float mx = -INFINITY;
+    for (int j = lane; j < Mm; j += 32)
+      if (!col_masked(d, bi, enabled, i, j)) mx = fmaxf(mx, S[j]);
+    mx = warp_max(mx);
+    if (Mlog > 0) {
+      float m = fmaxf(mx, s);
+      if (mx == -INFINITY) m = fmaxf(s, PBG_MASKED);      // every column masked
+      float z = 0.f;
+      for (int j = lane; j < Mm; j += 32)
+        if (!col_masked(d, bi, enabled, i, j)) { z += expf(S[j] - m); viol += S[j] > s; }
+      z = warp_sum(z);
+      float es = expf(s - m);
+      float Z = z + es;
+      lossv = -s + m + logf(Z);
+      ds = es / Z - 1.0f;
+      float invZ = 1.0f / Z;
+      for (int j = lane; j < d.Ms; j += 32) {
+        float t = 0.f;
+        if (j < Mm && !col_masked(d, bi, enabled, i, j)) t = coef_from_dscore(d.cmp, wr * expf(S[j] - m) * invZ, S[j]);
+        if (j == i) t = 0.f;                                // filled below
+        rowsum += t;
+        S[j] = t;
+      }
+    } else {
+      for (int j = lane; j < d.Ms; j += 32) S[j] = 0.f;     // losses.py:139-140: loss 0, no gradient
+    }
+  } else if (d.loss == PBG_LOSS_RANKING) {
+    // sum_j max(0, margin - s + S_ij) (losses.py:116-122)
+    if (Mlog > 0) {
+      for (int j = lane; j < d.Ms; j += 32) {
+        float t = 0.f;
+        if (j < Mm && !col_masked(d, bi, enabled, i, j)) {
+          float sj = S[j];
+          float v = (sj - s) + d.margin;
+          viol += sj > s;
+          if (v > 0.f) { lossv += v; ds -= 1.0f; t = coef_from_dscore(d.cmp, wr, sj); }
+        }
+        rowsum += t;
+        S[j] = t;
+      }
+      lossv = warp_sum(lossv);
+      ds = warp_sum(ds);
+    } else {
+      for (int j = lane; j < d.Ms; j += 32) S[j] = 0.f;
+    }
+  } else {
+    // softplus(-s) + (1/M) sum_j softplus(S_ij), M counts masked columns (losses.py:61-80)
+    float nw = Mlog > 0 ? 1.0f / (float)Mlog : 0.f;
+    for (int j = lane; j < d.Ms; j += 32) {
+      float t = 0.f;
+      if (j < Mm && !col_masked(d, bi, enabled, i, j)) {
+        float sj = S[j];
+        viol += sj > s;
+        lossv += softplusf(sj);
+        t = coef_from_dscore(d.cmp, wr * nw * sigmoidf(sj), sj);
+      }
+      rowsum += t;
+      S[j] = t;
+    }
+    lossv = warp_sum(lossv) * nw + softplusf(-s);
+    ds = -sigmoidf(-s);
+  }
+  viol = warp_sum_int(viol);
+  rowsum = warp_sum(rowsum);
+  // positive pair folded into the diagonal; the positive score of the l2 family is the direct
+  // form -sqrt(max(sum (a-b)^2, 1e-30)) (model.py:267-274)
+  float tdiag = coef_from_dscore(d.cmp, wr * ds, s);
+  __syncwarp();
+  if (lane == 0) {
+    S[i] = tdiag;
+    w.lossrow[p][prow] = wr * lossv;
+    w.violrow[p][prow] = viol;
+    if (d.cmp >= PBG_CMP_L2) w.coef[2 + p][prow] = rowsum + tdiag;
+  }
+}
+
+// l2 family: column sums of T_p over the chunk's positives (coefficient of the negative row's
+// own |b|^2 term).  One thread per column.
+__global__ void colsum_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int p = blockIdx.z, blk = blockIdx.y;
+  int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= d.Mm) return;
+  BlockInfo bi = block_info(d, wb, blk);
+  float s = 0.f;
+  const float *T = w.S[p] + (size_t)blk * d.Pm * d.Ms + j;
+  for (int i = 0; i < bi.n; ++i) s += T[(size_t)i * d.Ms];
+  w.coef[p][(size_t)blk * d.Mm + j] = s;
+}
+
+int launch_loss(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
+  long long items = 2ll * d.nblk * d.Pm;
+  loss_kernel<<<(int)((items + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+  if (d.cmp >= PBG_CMP_L2) {
+    dim3 g((d.Mm + 127) / 128, d.nblk, 2);
+    colsum_kernel<<<g, 128, 0, st>>>(d, wb, w);
+    return 2;
+  }
+  return 1;
+}
+
+// Per-batch Stats (train_cpu.py:95-101): one CTA per batch of the wave sums its rows in a fixed
+// order; the running totals of the call live in sum_dev (loss, violators_lhs, violators_rhs, count).
+__global__ void __launch_bounds__(256) stats_kernel(WaveDims d, WaveBatches wb, WaveBufs w,
+                                                    pbg_batch_stats *per_batch, double *sum) {
+  __shared__ double sl[256];
+  __shared__ long long sv0[256], sv1[256];
+  int b = blockIdx.x, t = threadIdx.x;
+  double l = 0.0;
+  long long v0 = 0, v1 = 0;
+  int rows = d.Cm * d.Pm;
+  for (int r = t; r < rows; r += 256) {
+    int c = r / d.Pm, i = r - c * d.Pm;
+    int blk = b * d.Cm + c;
+    BlockInfo bi = block_info(d, wb, blk);
+    if (i >= bi.n) continue;
+    size_t prow = (size_t)blk * d.Pm + i;
+    l += (double)w.lossrow[0][prow] + (double)w.lossrow[1][prow];
+    v0 += w.violrow[0][prow];
+    v1 += w.violrow[1][prow];
+  }
+  sl[t] = l; sv0[t] = v0; sv1[t] = v1;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (t < o) { sl[t] += sl[t + o]; sv0[t] += sv0[t + o]; sv1[t] += sv1[t + o]; }
+    __syncthreads();
+  }
+  if (t == 0) {
+    pbg_batch_stats s;
+    s.loss = (float)sl[0]; s.reg = 0.f; s.violators_lhs = sv0[0]; s.violators_rhs = sv1[0]; s.count = wb.n[b];
+    if (per_batch) per_batch[wb.gidx[b]] = s;
+    atomicAdd(&sum[0], sl[0]);
+    atomicAdd(&sum[1], (double)sv0[0]);
+    atomicAdd(&sum[2], (double)sv1[0]);
+    atomicAdd(&sum[3], (double)wb.n[b]);
+  }
+}
+
+int launch_stats(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
+                 pbg_batch_stats *per_batch_dev, double *sum_dev, cudaStream_t st) {
+  stats_kernel<<<d.k, 256, 0, st>>>(d, wb, w, per_batch_dev, sum_dev);
+  return 1;
+}
+
+// Scores as the reference returns them (model.py:842-844): [count] positives and
+// [count, Pl + U] negatives per side with ignored entries set to -1e9; single batch (wave of 1).
+__global__ void export_scores_kernel(WaveDims d, WaveBatches wb, WaveBufs w, float *lhs_pos, float *rhs_pos,
+                                     float *lhs_neg, float *rhs_neg) {
+  int e = blockIdx.x;                       // edge of the batch
+  int p = blockIdx.y;
+  BlockInfo b0 = block_info(d, wb, 0);
+  int Pl = b0.Pl;
+  if (Pl == 0) return;
+  int c = e / Pl, i = e - c * Pl;
+  BlockInfo bi = block_info(d, wb, c);
+  float *pos = p == 0 ? lhs_pos : rhs_pos;
+  float *neg = p == 0 ? lhs_neg : rhs_neg;
+  size_t prow = (size_t)c * d.Pm + i;
+  if (threadIdx.x == 0) pos[e] = w.spos[p][prow];
+  if (!d.neg_enabled[p]) return;
+  int cols = d.batch_negs ? Pl + d.U : d.U;
+  const float *S = w.S[p] + prow * d.Ms;
+  for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+    int src = d.batch_negs ? (j < Pl ? j : d.Pm + (j - Pl)) : d.Pm + j;
+    neg[(size_t)e * cols + j] = col_masked(d, bi, 1, i, src) ? PBG_MASKED : S[src];
+  }
+}
+
+int launch_export_scores(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, float *lhs_pos,
+                         float *rhs_pos, float *lhs_neg, float *rhs_neg, cudaStream_t st) {
+  if (wb.n[0] <= 0) return 0;
+  dim3 g(wb.n[0], 2);
+  export_scores_kernel<<<g, 128, 0, st>>>(d, wb, w, lhs_pos, rhs_pos, lhs_neg, rhs_neg);
+  return 1;
+}

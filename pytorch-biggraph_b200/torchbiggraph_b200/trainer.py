@@ -1,0 +1,312 @@
+"""The batch processor that replaces the reference's Trainer (torchbiggraph/train_cpu.py:74-112)
+and the batch loop around it (torchbiggraph/batching.py:91-125).
+
+`B200Trainer.process_one_batch(model, batch_edges) -> Stats` is the reference interface
+(AbstractBatchProcessor, batching.py:128-165).  `process_in_batches` hands a whole edge list to the
+library in one call, which trains `batches_in_flight` batches per wave on the device."""
+import ctypes as C
+import time
+from abc import ABC, abstractmethod
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import PbgBatch, PbgBatchStats, PbgBucket, PbgConfig, check
+from .model import MultiRelationEmbedder, Scores
+from .registries import LOSS_FUNCTIONS, AbstractLossFunction
+from .row_adagrad import AsyncAdagrad, RowAdagrad
+from .types import EdgeList, Stats
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+class _Native:
+    """One library context bound to a model's static configuration."""
+
+    def __init__(self, model: MultiRelationEmbedder, max_batch: int, k: int, precision: str, lr: float,
+                 relation_lr: Optional[float], margin: float, loss_code: Optional[int] = None):
+        cfg = model.config
+        if model.device.type != "cuda":
+            raise RuntimeError("torchbiggraph_b200 runs on a CUDA device only (no CPU fallback)")
+        self.lib = _lib.lib()
+        c = PbgConfig()
+        c.dim = cfg.dimension
+        c.op = _lib.OPERATOR_CODES[model.operator_name]
+        c.comparator = model.comparator.native_code
+        c.loss = _lib.LOSS_CODES[cfg.loss_fn] if loss_code is None else loss_code
+        c.dynamic_relations = int(cfg.dynamic_relations)
+        c.num_rels = model.num_rels
+        c.num_batch_negs = cfg.num_batch_negs
+        c.num_uniform_negs = cfg.num_uniform_negs
+        c.disable_lhs_negs = int(cfg.disable_lhs_negs)
+        c.disable_rhs_negs = int(cfg.disable_rhs_negs)
+        c.precision = _lib.PRECISION_CODES[precision]
+        c.max_batch_size = max_batch
+        c.batches_in_flight = k
+        c.margin = margin
+        c.lr = lr
+        c.relation_lr = lr if relation_lr is None else relation_lr
+        self.cfg = c
+        self.max_batch = max_batch
+        self.device_index = model.device.index if model.device.index is not None else torch.cuda.current_device()
+        self.ctx = C.c_void_p()
+        stream = torch.cuda.current_stream(self.device_index).cuda_stream
+        st = self.lib.pbg_create(C.byref(c), self.device_index, C.c_void_p(stream), C.byref(self.ctx))
+        if st != 0:
+            msg = self.lib.pbg_last_error(self.ctx).decode() if self.ctx else ""
+            self.lib.pbg_destroy(self.ctx)
+            self.ctx = None
+            if st == _lib.PBG_ERR_UNSUPPORTED:
+                raise NotImplementedError(msg)
+            raise _lib.PbgError(st, msg)
+
+    def __del__(self):
+        if getattr(self, "ctx", None):
+            self.lib.pbg_destroy(self.ctx)
+            self.ctx = None
+
+    def set_hyper(self, lr, relation_lr, margin):
+        check(self.lib.pbg_set_hyperparameters(self.ctx, lr, lr if relation_lr is None else relation_lr, margin), self.ctx)
+
+    def bucket(self, model, relation_idx, states, weights_arr) -> PbgBucket:
+        wl, wr = model.tables_for(relation_idx)
+        b = PbgBucket()
+        b.lhs_emb, b.lhs_rows = wl.data_ptr(), wl.shape[0]
+        b.rhs_emb, b.rhs_rows = wr.data_ptr(), wr.shape[0]
+        if states is not None:
+            gl, gr, al, ar = states
+            b.lhs_state, b.rhs_state = gl.data_ptr(), gr.data_ptr()
+            b.rhs_op_state = None if ar is None else ar.data_ptr()
+            b.lhs_op_state = None if al is None else al.data_ptr()
+        b.rhs_op = None if model.rhs_op_table is None else model.rhs_op_table.data_ptr()
+        b.lhs_op = None if model.lhs_op_table is None else model.lhs_op_table.data_ptr()
+        b.relation_weights = weights_arr
+        return b
+
+    def score(self, model, edges: EdgeList, ul, ur, seed) -> Scores:
+        n = len(edges)
+        dev = model.device
+        lhs = edges.lhs.to_tensor().to(dev).contiguous()
+        rhs = edges.rhs.to_tensor().to(dev).contiguous()
+        dyn = model.num_dynamic_rels > 0
+        if dyn and edges.has_scalar_relation_type():
+            raise TypeError("Need relation for each positive pair")
+        if not dyn and not edges.has_scalar_relation_type():
+            raise TypeError("All positive pairs must come from the same relation")
+        rel = edges.rel.to(dev).contiguous() if dyn else None
+        relidx = 0 if dyn else edges.get_relation_type_as_scalar()
+        P, Cn, lc, rc = (C.c_int32() for _ in range(4))
+        check(self.lib.pbg_neg_columns(self.ctx, n, C.byref(P), C.byref(Cn), C.byref(lc), C.byref(rc)), self.ctx)
+        lp = torch.empty(n, device=dev); rp = torch.empty(n, device=dev)
+        ln = torch.empty((n, lc.value), device=dev); rn = torch.empty((n, rc.value), device=dev)
+        ul = None if ul is None else self._uniform(ul, dev)
+        ur = None if ur is None else self._uniform(ur, dev)
+        b = self.bucket(model, relidx, None, None)
+        check(self.lib.pbg_score_batch(self.ctx, C.byref(b), _ptr(lhs), _ptr(rhs), _ptr(rel), n, relidx,
+                                       _ptr(ul), _ptr(ur), seed, _ptr(lp), _ptr(rp), _ptr(ln), _ptr(rn)), self.ctx)
+        return Scores(lp, rp, ln, rn)
+
+    def _uniform(self, u, dev):
+        """[chunks, U] ids of ONE batch -> the library's [1, chunks_per_batch, U] layout."""
+        u = torch.as_tensor(u, dtype=torch.long)
+        lim = self.cfg.num_batch_negs if self.cfg.num_batch_negs > 0 else self.cfg.num_uniform_negs
+        P = min(lim, self.max_batch)
+        cm = (self.max_batch + P - 1) // P
+        out = torch.zeros((cm, self.cfg.num_uniform_negs), dtype=torch.long)
+        out[: u.shape[0]] = u.reshape(u.shape[0], -1).cpu()
+        return out.to(dev)
+
+    def chunks_per_batch(self) -> int:
+        lim = self.cfg.num_batch_negs if self.cfg.num_batch_negs > 0 else self.cfg.num_uniform_negs
+        P = min(lim, self.max_batch)
+        return (self.max_batch + P - 1) // P
+
+
+class AbstractBatchProcessor(ABC):
+    """torchbiggraph/batching.py:128-165."""
+
+    def __init__(self, loss_fn: AbstractLossFunction, relation_weights: List[float], overrides=None):
+        self.loss_fn = loss_fn
+        self.relation_weights = relation_weights
+        self.overrides = overrides
+
+    @abstractmethod
+    def _process_one_batch(self, model, batch_edges: EdgeList) -> Stats:
+        pass
+
+    def process_one_batch(self, model, batch_edges: EdgeList) -> Stats:
+        if self.overrides is not None:
+            raise NotImplementedError("model overrides are not supported by torchbiggraph_b200")
+        return self._process_one_batch(model, batch_edges)
+
+
+class B200Trainer(AbstractBatchProcessor):
+    """Trainer(model_optimizer, loss_fn, relation_weights) of train_cpu.py:74-84.  The coordinator
+    fills `partitioned_optimizers[(entity, part)]` / `unpartitioned_optimizers[entity]` with
+    RowAdagrad objects on partition swap exactly as it does for the reference."""
+
+    def __init__(self, model_optimizer, loss_fn: AbstractLossFunction, relation_weights: List[float]):
+        super().__init__(loss_fn, relation_weights)
+        if getattr(loss_fn, "native_code", None) is None:
+            raise NotImplementedError(f"loss function {type(loss_fn).__name__} has no device code (no CPU fallback)")
+        self.model_optimizer = model_optimizer
+        self.unpartitioned_optimizers: Dict[str, RowAdagrad] = {}
+        self.partitioned_optimizers: Dict[Tuple, RowAdagrad] = {}
+        self._native: Optional[_Native] = None
+        self._native_key = None
+        self.seed = 0
+        self._calls = 0
+
+    # ---- plumbing ------------------------------------------------------------------------------
+    def _state_for(self, table: torch.Tensor) -> torch.Tensor:
+        for opt in list(self.partitioned_optimizers.values()) + list(self.unpartitioned_optimizers.values()):
+            for p in opt.params:
+                if p.data_ptr() == table.data_ptr():
+                    return opt.sum_for(p)
+        raise RuntimeError("no RowAdagrad optimizer registered for an embedding table of this batch")
+
+    def _lr(self) -> float:
+        for opt in list(self.partitioned_optimizers.values()) + list(self.unpartitioned_optimizers.values()):
+            return opt.lr
+        raise RuntimeError("no embedding optimizer registered")
+
+    def _context(self, model: MultiRelationEmbedder, need_batch: int) -> _Native:
+        cfg = model.config
+        key = (id(model), cfg.batches_in_flight, cfg.precision)
+        if self._native is None or self._native_key != key or self._native.max_batch < need_batch:
+            margin = getattr(self.loss_fn, "margin", cfg.margin)
+            rel_lr = self.model_optimizer.lr if isinstance(self.model_optimizer, AsyncAdagrad) else cfg.relation_lr
+            self._native = _Native(model, max(cfg.batch_size, need_batch), cfg.batches_in_flight, cfg.precision,
+                                   self._lr(), rel_lr, margin, loss_code=self.loss_fn.native_code)
+            self._native_key = key
+        return self._native
+
+    def _op_states(self, model):
+        if model.rhs_op_table is None:
+            return None, None
+        if not isinstance(self.model_optimizer, AsyncAdagrad):
+            raise RuntimeError("the model has operator parameters but model_optimizer is not an AsyncAdagrad over them")
+        ar = self.model_optimizer.sum_for(model.rhs_op_table)
+        al = None if model.lhs_op_table is None else self.model_optimizer.sum_for(model.lhs_op_table)
+        return al, ar
+
+    def train_batches(self, model: MultiRelationEmbedder, lhs: torch.Tensor, rhs: torch.Tensor,
+                      rel: Optional[torch.Tensor], batches: List[Tuple[int, int, int]],
+                      uniform_lhs: Optional[torch.Tensor] = None, uniform_rhs: Optional[torch.Tensor] = None,
+                      want_per_batch: bool = True) -> List[Stats]:
+        """Trains the listed (offset, count, relation) batches of the edge arrays.  Edge arrays on
+        the CPU are copied by the library (pin them to make the copy asynchronous)."""
+        if not batches:
+            return []
+        nat = self._context(model, max(b[1] for b in batches))
+        relation_idx = 0 if model.num_dynamic_rels > 0 else batches[0][2]
+        wl, wr = model.tables_for(relation_idx)
+        if model.num_dynamic_rels == 0:
+            for b in batches:
+                if model.tables_for(b[2])[0] is not wl or model.tables_for(b[2])[1] is not wr:
+                    raise NotImplementedError("batches of one call must read the same pair of tables")
+        al, ar = self._op_states(model)
+        states = (self._state_for(wl), self._state_for(wr), al, ar)
+        nw = len(self.relation_weights)
+        warr = (C.c_float * nw)(*self.relation_weights)
+        bucket = nat.bucket(model, relation_idx, states, warr)
+        barr = (PbgBatch * len(batches))()
+        for i, (o, n, r) in enumerate(batches):
+            barr[i].offset, barr[i].count, barr[i].rel = o, n, r
+        sarr = (PbgBatchStats * len(batches))() if want_per_batch else None
+        on_host = lhs.device.type == "cpu"
+        fn = nat.lib.pbg_train_batches_host if on_host else nat.lib.pbg_train_batches
+        for t in (lhs, rhs, rel, uniform_lhs, uniform_rhs):
+            if t is not None and (t.dtype != torch.long or not t.is_contiguous() or (t.device.type == "cpu") != on_host):
+                raise TypeError("edge and uniform-id arrays must be contiguous int64, all on the host or all on the device")
+        self._calls += 1
+        check(fn(nat.ctx, C.byref(bucket), _ptr(lhs), _ptr(rhs), _ptr(rel), lhs.shape[0], barr, len(batches),
+                 _ptr(uniform_lhs), _ptr(uniform_rhs), self.seed + self._calls, sarr), nat.ctx)
+        if not want_per_batch:
+            return []
+        return [Stats(loss=float(s.loss), reg=float(s.reg), violators_lhs=int(s.violators_lhs),
+                      violators_rhs=int(s.violators_rhs), count=int(s.count)) for s in sarr]
+
+    def read_stats(self) -> Stats:
+        s = PbgBatchStats()
+        check(self._native.lib.pbg_read_stats(self._native.ctx, C.byref(s)), self._native.ctx)
+        return Stats(loss=float(s.loss), reg=0.0, violators_lhs=int(s.violators_lhs),
+                     violators_rhs=int(s.violators_rhs), count=int(s.count))
+
+    # ---- the reference interface ---------------------------------------------------------------
+    def _process_one_batch(self, model: MultiRelationEmbedder, batch_edges: EdgeList,
+                           uniform_lhs=None, uniform_rhs=None) -> Stats:
+        if batch_edges.has_weight():
+            raise NotImplementedError("per-edge weights have no device code in torchbiggraph_b200")
+        dyn = model.num_dynamic_rels > 0
+        if dyn and batch_edges.has_scalar_relation_type():
+            raise TypeError("Need relation for each positive pair")
+        if not dyn and not batch_edges.has_scalar_relation_type():
+            raise TypeError("All positive pairs must come from the same relation")
+        n = len(batch_edges)
+        if n == 0:
+            return Stats(loss=0.0, reg=0.0, violators_lhs=0, violators_rhs=0, count=0)
+        dev = model.device
+        lhs = batch_edges.lhs.to_tensor().to(dev).contiguous()
+        rhs = batch_edges.rhs.to_tensor().to(dev).contiguous()
+        rel = batch_edges.rel.to(dev).contiguous() if dyn else None
+        r = 0 if dyn else batch_edges.get_relation_type_as_scalar()
+        nat = self._context(model, n)
+        ul = None if uniform_lhs is None else nat._uniform(uniform_lhs, dev)
+        ur = None if uniform_rhs is None else nat._uniform(uniform_rhs, dev)
+        return self.train_batches(model, lhs, rhs, rel, [(0, n, r)], ul, ur)[0]
+
+    def process_one_batch(self, model, batch_edges, uniform_lhs=None, uniform_rhs=None) -> Stats:
+        if self.overrides is not None:
+            raise NotImplementedError("model overrides are not supported by torchbiggraph_b200")
+        return self._process_one_batch(model, batch_edges, uniform_lhs, uniform_rhs)
+
+
+def _batches_group_by_relation(rel_sorted: torch.Tensor, batch_size: int, generator=None):
+    """Batch descriptors over edges sorted by relation: repeatedly pick a relation with
+    probability proportional to its remaining edges and emit its next <= batch_size edges
+    (batching.py:58-79)."""
+    rels, counts = torch.unique_consecutive(rel_sorted, return_counts=True)
+    starts = torch.cumsum(counts, 0) - counts
+    left = counts.clone()
+    out = []
+    while int(left.sum()) > 0:
+        idx = int(torch.multinomial(left.float(), 1, generator=generator))
+        off = int(starts[idx] + counts[idx] - left[idx])
+        n = min(batch_size, int(left[idx]))
+        out.append((off, n, int(rels[idx])))
+        left[idx] -= n
+    return out
+
+
+def process_in_batches(batch_size: int, model: MultiRelationEmbedder, batch_processor: B200Trainer,
+                       edges: EdgeList, indices: Optional[torch.Tensor] = None, delay: float = 0.0) -> Stats:
+    """torchbiggraph/batching.py:91-125 with the batch loop moved onto the device."""
+    if indices is not None:
+        edges = edges[indices]
+    if delay > 0:
+        time.sleep(delay)
+    if edges.has_weight():
+        raise NotImplementedError("per-edge weights have no device code in torchbiggraph_b200")
+    n = len(edges)
+    if n == 0:
+        return Stats(count=0)
+    lhs, rhs = edges.lhs.to_tensor().contiguous(), edges.rhs.to_tensor().contiguous()
+    if model.num_dynamic_rels > 0:
+        rel = edges.get_relation_type_as_vector().contiguous()
+        batches = [(o, min(batch_size, n - o), 0) for o in range(0, n, batch_size)]
+    elif edges.has_scalar_relation_type():
+        rel = None
+        r = edges.get_relation_type_as_scalar()
+        batches = [(o, min(batch_size, n - o), r) for o in range(0, n, batch_size)]
+    else:
+        order = torch.argsort(edges.rel, stable=True)
+        lhs, rhs, rel_sorted = lhs[order].contiguous(), rhs[order].contiguous(), edges.rel[order]
+        rel = None
+        batches = _batches_group_by_relation(rel_sorted.cpu(), batch_size)
+        # one call per (lhs table, rhs table) pair is needed; relations sharing entity types go together
+    stats = batch_processor.train_batches(model, lhs, rhs, rel, batches)
+    return Stats.sum(stats)

@@ -1,0 +1,285 @@
+"""Parity of the CUDA training step (through the C ABI) against the reference-generated golden
+fixtures and the CPU oracle.  fp32 tier: rtol 1e-4 (plus a small atol for values near zero)."""
+import numpy as np
+import pytest
+import torch
+
+from golden_util import batch_of, load_step, oracle_config, oracle_state, step_fixture_names
+from oracle import pbg_step as O
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-4
+DEVICE_OPS = ("none", "diagonal", "translation", "complex_diagonal")
+
+
+def _supported(c):
+    return c["op"] in DEVICE_OPS
+
+
+def _names():
+    return [n for n in step_fixture_names() if _supported(load_step(n)[0])]
+
+
+def _close(got, want, rtol=RTOL, atol=2e-6, what=""):
+    np.testing.assert_allclose(got, want, rtol=rtol, atol=atol, err_msg=what)
+
+
+@pytest.mark.parametrize("name", _names())
+def test_step_matches_reference_fixture(name):
+    from b200_util import Rig
+    c, z = load_step(name)
+    rig = Rig.from_fixture(c, z)
+    ocfg, ost = oracle_config(c), oracle_state(c, z)
+    for step in range(c["steps"]):
+        lhs, rhs, rel, ul, ur = batch_of(c, z, step)
+        ostats = O.train_batch(ocfg, ost, lhs, rhs, rel, ul, ur)
+        st = rig.trainer.process_one_batch(rig.model, rig.edges(lhs, rhs, rel), ul, ur)
+        assert st.count == len(lhs)
+        assert st.metrics["loss"] == pytest.approx(float(z[f"loss_{step}"]), rel=RTOL, abs=1e-3), "loss vs reference"
+        assert st.metrics["loss"] == pytest.approx(ostats["loss"], rel=RTOL, abs=1e-3), "loss vs oracle"
+        assert abs(st.metrics["violators_lhs"] - int(z[f"violators_lhs_{step}"])) <= ostats["ties_lhs"]
+        assert abs(st.metrics["violators_rhs"] - int(z[f"violators_rhs_{step}"])) <= ostats["ties_rhs"]
+        _close(rig.W_lhs.cpu().numpy(), z[f"W_lhs_after_{step}"], what="W_lhs vs reference")
+        _close(rig.G("lhs"), z[f"G_lhs_after_{step}"], atol=1e-7, what="G_lhs vs reference")
+        _close(rig.W_lhs.cpu().numpy(), ost.W_lhs, what="W_lhs vs oracle")
+        if c["separate"]:
+            _close(rig.W_rhs.cpu().numpy(), z[f"W_rhs_after_{step}"], what="W_rhs vs reference")
+            _close(rig.G("rhs"), z[f"G_rhs_after_{step}"], atol=1e-7, what="G_rhs vs reference")
+        for side in ("rhs", "lhs"):
+            key = f"theta_{side}_after_{step}"
+            if key in z and rig.theta(side) is not None:
+                _close(rig.theta(side), z[key], what=f"theta_{side} vs reference")
+                _close(rig.acc(side), z[f"acc_{side}_after_{step}"], atol=1e-7, what=f"acc_{side} vs reference")
+
+
+@pytest.mark.parametrize("name", _names())
+def test_forward_scores_match_reference_fixture(name):
+    from b200_util import Rig
+    c, z = load_step(name)
+    ocfg, ost = oracle_config(c), oracle_state(c, z)
+    for step in range(c["steps"]):
+        O.train_batch(ocfg, ost, *batch_of(c, z, step))
+    rig = Rig.from_oracle_state(c, ost)
+    rel = z["fw_rel"]
+    sc = rig.model(rig.edges(z["fw_lhs"], z["fw_rhs"], rel),
+                   None if c["disable_lhs"] else z["fw_ul"], None if c["disable_rhs"] else z["fw_ur"])
+    for k in ("lhs_pos", "rhs_pos", "lhs_neg", "rhs_neg"):
+        want = z[f"fw_{k}"]
+        got = getattr(sc, k).cpu().numpy()
+        assert got.shape == want.shape, k
+        _close(got, want, rtol=RTOL, atol=3e-5, what=k)
+
+
+@pytest.mark.parametrize("name", ["sequence_3_batches", "sequence_3_batches_dyn_cos"])
+def test_wave_of_three_batches_matches_oracle(name):
+    from b200_util import Rig
+    c, z = load_step(name)
+    ocfg, ost = oracle_config(c), oracle_state(c, z)
+    batches = [batch_of(c, z, s) for s in range(3)]
+    ostats = O.train_wave(ocfg, ost, batches)
+    rig = Rig.from_fixture(c, z, k=3)
+    B = c["B"]
+    lhs = torch.tensor(np.concatenate([b[0] for b in batches])).cuda()
+    rhs = torch.tensor(np.concatenate([b[1] for b in batches])).cuda()
+    rel = torch.tensor(np.concatenate([np.asarray(b[2]).reshape(-1) for b in batches])).cuda() if c["dyn"] else None
+    nat = rig.trainer._context(rig.model, B)
+    ul = torch.stack([nat._uniform(b[3], "cuda") for b in batches]).contiguous()
+    ur = torch.stack([nat._uniform(b[4], "cuda") for b in batches]).contiguous()
+    r = 0 if c["dyn"] else c["rel_idx"]
+    stats = rig.trainer.train_batches(rig.model, lhs, rhs, rel, [(i * B, B, r) for i in range(3)], ul, ur)
+    for s, o in zip(stats, ostats):
+        assert s.metrics["loss"] == pytest.approx(o["loss"], rel=RTOL, abs=1e-3)
+    _close(rig.W_lhs.cpu().numpy(), ost.W_lhs, what="W after wave")
+    _close(rig.G("lhs"), ost.G_lhs, atol=1e-7, what="G after wave")
+    if rig.theta("rhs") is not None:
+        _close(rig.theta("rhs"), ost.theta_rhs, what="theta_rhs after wave")
+        _close(rig.acc("rhs"), ost.acc_rhs, atol=1e-7, what="acc_rhs after wave")
+    if rig.theta("lhs") is not None:
+        _close(rig.theta("lhs"), ost.theta_lhs, what="theta_lhs after wave")
+
+
+def _random_case(seed, D, N, B, nb, nu, op, comp, loss, dyn=False, R=1, k=1, nbatches=1, zipf=False, w_scale=0.1):
+    rng = np.random.default_rng(seed)
+    c = dict(D=D, N=N, N2=N, dyn=dyn, R=R, separate=False, id_range=None, steps=1, w_scale=w_scale,
+             disable_lhs=False, disable_rhs=False, n_rel_std=1, rel_idx=0, rel_weight=1.0, margin=0.1,
+             lr=0.1, relation_lr=0.05, op=op, comp=comp, loss=loss, B=B, nb=nb, nu=nu, name="random")
+    W = (rng.standard_normal((N, D)) * w_scale).astype(np.float32)
+    G = (rng.random(N) * 0.1).astype(np.float32)
+    ocfg = oracle_config(c)
+    th_r = th_l = None
+    if op != "none":
+        nrows = R if dyn else 1
+        th_r = (O.operator_init(op, D, nrows, np.float32) + rng.standard_normal((nrows, D)).astype(np.float32) * 0.2)
+        th_l = th_r[::-1].copy() if dyn else None
+    P = min(nb, B) if nb > 0 else min(nu, B)
+    C = (B - 1) // P + 1
+    batches = []
+    for _ in range(nbatches):
+        if zipf:
+            ranks = np.arange(1, N + 1, dtype=np.float64) ** -1.1
+            p = ranks / ranks.sum()
+            lhs, rhs = rng.choice(N, B, p=p), rng.choice(N, B, p=p)
+        else:
+            lhs, rhs = rng.integers(0, N, B), rng.integers(0, N, B)
+        rel = rng.integers(0, R, B) if dyn else 0
+        batches.append((lhs, rhs, rel, rng.integers(0, N, (C, nu)), rng.integers(0, N, (C, nu))))
+    st = O.BucketState(W.astype(np.float64), G.astype(np.float64), None, None)
+    st.W_rhs, st.G_rhs = st.W_lhs, st.G_lhs
+    if th_r is not None:
+        st.theta_rhs, st.acc_rhs = th_r.astype(np.float64), np.zeros_like(th_r, np.float64)
+    if th_l is not None:
+        st.theta_lhs, st.acc_lhs = th_l.astype(np.float64), np.zeros_like(th_l, np.float64)
+    return c, ocfg, st, batches
+
+
+BASELINE_SHAPES = [
+    # D, N, B, nb, nu, op, comp, loss, dyn, R   (the five BASELINE configs at one batch, smaller tables)
+    pytest.param(100, 5000, 1000, 50, 50, "none", "dot", "ranking", False, 1, id="C1"),
+    pytest.param(400, 3000, 2000, 1000, 0, "complex_diagonal", "dot", "softmax", True, 40, id="C2-dyn"),
+    pytest.param(1024, 4000, 1000, 100, 100, "none", "dot", "softmax", False, 1, id="C3"),
+    pytest.param(100, 5000, 1000, 100, 100, "translation", "cos", "ranking", False, 1, id="C4"),
+    pytest.param(200, 5000, 1000, 100, 100, "complex_diagonal", "l2", "logistic", True, 60, id="C5-dyn"),
+]
+
+
+@pytest.mark.parametrize("D,N,B,nb,nu,op,comp,loss,dyn,R", BASELINE_SHAPES)
+def test_baseline_shapes_match_oracle(D, N, B, nb, nu, op, comp, loss, dyn, R):
+    from b200_util import Rig
+    c, ocfg, ost, batches = _random_case(11, D, N, B, nb, nu, op, comp, loss, dyn, R, zipf=True,
+                                         w_scale=1.0 if comp == "cos" else 0.1)
+    rig = Rig.from_oracle_state(c, ost)
+    b = batches[0]
+    ostats = O.train_batch(ocfg, ost, *b)
+    st = rig.trainer.process_one_batch(rig.model, rig.edges(b[0], b[1], b[2]), b[3], b[4])
+    assert st.metrics["loss"] == pytest.approx(ostats["loss"], rel=RTOL)
+    assert abs(st.metrics["violators_lhs"] - ostats["violators_lhs"]) <= ostats["ties_lhs"]
+    assert abs(st.metrics["violators_rhs"] - ostats["violators_rhs"]) <= ostats["ties_rhs"]
+    _close(rig.W_lhs.cpu().numpy(), ost.W_lhs, atol=1e-6, what="W")
+    _close(rig.G("lhs"), ost.G_lhs, atol=1e-8, what="G")
+    if ost.theta_rhs is not None:
+        _close(rig.theta("rhs"), ost.theta_rhs, atol=1e-6, what="theta_rhs")
+    if ost.theta_lhs is not None:
+        _close(rig.theta("lhs"), ost.theta_lhs, atol=1e-6, what="theta_lhs")
+
+
+def test_wave_of_eight_matches_oracle_with_hub_rows():
+    from b200_util import Rig
+    c, ocfg, ost, batches = _random_case(5, 64, 300, 200, 50, 50, "diagonal", "dot", "softmax", nbatches=8, zipf=True)
+    rig = Rig.from_oracle_state(c, ost, k=8)
+    O.train_wave(ocfg, ost, batches)
+    nat = rig.trainer._context(rig.model, 200)
+    lhs = torch.tensor(np.concatenate([b[0] for b in batches])).cuda()
+    rhs = torch.tensor(np.concatenate([b[1] for b in batches])).cuda()
+    ul = torch.stack([nat._uniform(b[3], "cuda") for b in batches]).contiguous()
+    ur = torch.stack([nat._uniform(b[4], "cuda") for b in batches]).contiguous()
+    rig.trainer.train_batches(rig.model, lhs, rhs, None, [(i * 200, 200, 0) for i in range(8)], ul, ur)
+    _close(rig.W_lhs.cpu().numpy(), ost.W_lhs, atol=1e-6, what="W")
+    _close(rig.G("lhs"), ost.G_lhs, atol=1e-8, what="G")
+    _close(rig.theta("rhs"), ost.theta_rhs, atol=1e-6, what="theta")
+
+
+def test_device_drawn_negatives_properties():
+    """Without caller-supplied ids the negatives come from the device generator: runs are
+    reproducible for a seed, rows never named by an edge still move, nothing goes out of range."""
+    from b200_util import Rig
+    c, ocfg, ost, batches = _random_case(3, 32, 2000, 500, 50, 50, "none", "dot", "ranking")
+    outs = []
+    for _ in range(2):
+        rig = Rig.from_oracle_state(c, ost)
+        b = batches[0]
+        rig.trainer.seed = 1234
+        st = rig.trainer.process_one_batch(rig.model, rig.edges(b[0], b[1], b[2]))
+        outs.append((st.metrics["loss"], rig.W_lhs.cpu().numpy().copy()))
+    assert outs[0][0] == outs[1][0]
+    assert np.array_equal(outs[0][1], outs[1][1])
+    W0 = ost.W_lhs.astype(np.float32)
+    moved = np.flatnonzero((outs[0][1] != W0).any(1))
+    named = np.unique(np.concatenate([batches[0][0], batches[0][1]]))
+    assert set(named) <= set(moved)
+    extra = len(set(moved) - set(named))
+    assert 0 < extra <= 2 * 10 * 50          # uniform negatives: at most 2 sides x chunks x U rows
+
+
+def test_full_size_batch_properties():
+    """BASELINE C3 batch shape on a 300k-row partition: untouched rows keep their bits, Adagrad
+    state never decreases, stats are finite, and a second identical forward gives the same bits."""
+    from b200_util import Rig
+    rng = np.random.default_rng(0)
+    N, D, B = 303_000, 1024, 1000
+    c = dict(D=D, N=N, N2=N, dyn=False, R=1, separate=False, id_range=None, steps=1, w_scale=0.001,
+             disable_lhs=False, disable_rhs=False, n_rel_std=1, rel_idx=0, rel_weight=1.0, margin=0.1,
+             lr=0.1, relation_lr=None, op="none", comp="dot", loss="softmax", B=B, nb=100, nu=100, name="c3")
+    W = torch.randn(N, D, device="cuda") * 1e-3
+    W0 = W.clone()
+    rig = Rig(c, np.zeros((1, D), np.float32), np.zeros(1, np.float32))
+    import torchbiggraph_b200 as T
+    rig.W_lhs = rig.W_rhs = W
+    rig.model.set_embeddings("e", T.Side.LHS, W)
+    rig.model.set_embeddings("e", T.Side.RHS, W)
+    rig.opt_l = rig.opt_r = T.make_optimizer(rig.cfg, [W], True)
+    rig.trainer.partitioned_optimizers["e", 0] = rig.opt_l
+    lhs, rhs = rng.integers(0, N, B), rng.integers(0, N, B)
+    e = rig.edges(lhs, rhs, 0)
+    s1 = rig.model(e, seed=7)
+    s2 = rig.model(e, seed=7)
+    assert torch.equal(s1.lhs_neg, s2.lhs_neg) and torch.equal(s1.rhs_pos, s2.rhs_pos)
+    st = rig.trainer.process_one_batch(rig.model, e)
+    assert np.isfinite(st.metrics["loss"]) and st.count == B
+    changed = (W != W0).any(1)
+    n_changed = int(changed.sum())
+    assert len(np.unique(np.concatenate([lhs, rhs]))) <= n_changed <= 2 * B + 2 * 10 * 100
+    G = rig.opt_l.sum_for(W)
+    assert bool((G >= 0).all()) and int((G > 0).sum()) == n_changed
+
+
+def test_row_adagrad_entry_point_matches_numpy():
+    import ctypes as C
+    from b200_util import Rig
+    from torchbiggraph_b200._lib import check
+    rng = np.random.default_rng(1)
+    N, D, n = 500, 64, 700
+    c = dict(D=D, N=N, N2=N, dyn=False, R=1, separate=False, id_range=None, steps=1, w_scale=0.1,
+             disable_lhs=False, disable_rhs=False, n_rel_std=1, rel_idx=0, rel_weight=1.0, margin=0.1,
+             lr=0.1, relation_lr=None, op="none", comp="dot", loss="softmax", B=1000, nb=50, nu=50, name="ra")
+    W = rng.standard_normal((N, D)).astype(np.float32)
+    G = rng.random(N).astype(np.float32)
+    rig = Rig(c, W, G)
+    nat = rig.trainer._context(rig.model, 1000)
+    rows = rng.integers(0, 60, n)
+    grads = rng.standard_normal((n, D)).astype(np.float32)
+    Wd, Gd = rig.W_lhs, rig.opt_l.sum_for(rig.W_lhs)
+    rd, gd = torch.tensor(rows).cuda(), torch.tensor(grads).cuda()
+    p = lambda t: C.c_void_p(t.data_ptr())
+    check(nat.lib.pbg_row_adagrad(nat.ctx, p(Wd), p(Gd), N, p(rd), p(gd), n, 0.1), nat.ctx)
+    W64, G64 = W.astype(np.float64), G.astype(np.float64)
+    acc = {}
+    for r, g in zip(rows, grads.astype(np.float64)):
+        acc[int(r)] = acc.get(int(r), 0) + g
+    O.row_adagrad_apply(W64, G64, acc, 0.1)
+    _close(Wd.cpu().numpy(), W64, atol=1e-6)
+    _close(Gd.cpu().numpy(), G64, atol=1e-7)
+
+
+def test_out_of_range_ids_are_reported_not_followed():
+    from b200_util import Rig
+    from torchbiggraph_b200._lib import PbgError, PBG_ERR_INDEX_RANGE
+    c, ocfg, ost, batches = _random_case(3, 32, 100, 60, 20, 5, "none", "dot", "ranking")
+    rig = Rig.from_oracle_state(c, ost)
+    lhs = batches[0][0].copy()
+    lhs[7] = 10_000
+    with pytest.raises(PbgError) as ei:
+        rig.trainer.process_one_batch(rig.model, rig.edges(lhs, batches[0][1], 0))
+    assert ei.value.status == PBG_ERR_INDEX_RANGE
+    # the context stays usable
+    st = rig.trainer.process_one_batch(rig.model, rig.edges(batches[0][0], batches[0][1], 0))
+    assert np.isfinite(st.metrics["loss"])
+
+
+def test_unsupported_plugins_raise():
+    import torchbiggraph_b200 as T
+    cfg = T.ConfigSchema(entities={"e": T.EntitySchema()}, relations=[T.RelationSchema("r", "e", "e", operator="linear")],
+                         dimension=16)
+    model = T.make_model(cfg, "cuda") if False else None
+    with pytest.raises(NotImplementedError):
+        T.make_model(cfg, "cuda")
