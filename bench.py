@@ -1,0 +1,491 @@
+#!/usr/bin/env python3
+"""Benchmark of the per-bucket training step: edges/sec trained.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload c3|c1|c4]
+
+Workload (default): the social-graph-shaped configuration ("c3"): 4,847,571 entities in 16
+partitions, dimension 1024, no operator / dot / softmax, batch 1000, 100 batch + 100 uniform
+negatives, RowAdagrad lr 0.1.  The graph is synthetic: endpoints drawn from a Chung-Lu power law
+(exponent 2.3) over seeded, randomly permuted entity ids; embeddings N(0, 1e-3).  One *step* is
+one bucket of the 16 x 16 grid: 68,993,773 / 256 = 269,507 edges = 270 batches handed to the
+library in one call (what process_in_batches does per bucket in the reference).
+
+Prints ONE JSON line.  `value`: edges already in HBM, CUDA events around K steps.  `e2e`: the same
+through the host-buffer call (edges in pinned host memory, host->device copy and per-batch stats
+read-back inside the timed region).  `roofline`: the dominant kernel class, timed with CUDA events
+on the library's stream in a separate short pass.  `cpu_baseline` / `--impl reference`: the
+PyTorch-CPU port of the reference trainer (oracle/pbg_step_torch.py), one HOGWILD process per host core.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "pytorch-biggraph_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+WORKLOADS = {
+    # name: entities, edges, partitions, dim, operator, comparator, loss, batch, batch negs, uniform negs, degree exponent
+    "c3": dict(entities=4_847_571, edges=68_993_773, partitions=16, dim=1024, op="none", comp="dot", loss="softmax",
+               batch=1000, nb=100, nu=100, gamma=2.3, desc="social-graph shaped, Chung-Lu exponent 2.3"),
+    "c4": dict(entities=41_652_230, edges=1_468_365_182, partitions=16, dim=100, op="translation", comp="cos",
+               loss="ranking", batch=1000, nb=100, nu=100, gamma=2.0, desc="follower-graph shaped, Chung-Lu exponent 2.0"),
+    "c1": dict(entities=100_000, edges=1_000_000, partitions=1, dim=100, op="none", comp="dot", loss="ranking",
+               batch=1000, nb=50, nu=50, gamma=None, desc="plumbing graph, Zipf(1.1) endpoints"),
+}
+EDGES_PER_STEP_CAP = 269_507
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], tflops=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
+
+
+def algorithmic(w):
+    """Per trained edge: flops = 12 D (P+U); bytes = (2 + 2U/P)(12 D + 8) + 24."""
+    D, P, U = w["dim"], w["nb"], w["nu"]
+    rho = U / P
+    return dict(flops=12.0 * D * (P + U), bytes=(2 + 2 * rho) * (12 * D + 8) + 24,
+                fwd_flops=4.0 * D * (P + U), bwd_flops=8.0 * D * (P + U),
+                gather_bytes=(2 + 2 * rho) * 8 * D + 24, update_bytes=(2 + 2 * rho) * (12 * D + 8))
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic graph
+# ------------------------------------------------------------------------------------------------
+class Sampler:
+    """Endpoint sampler of one partition: P(node) proportional to its Chung-Lu weight."""
+
+    def __init__(self, weights):
+        import torch
+        c = torch.cumsum(weights.double(), 0)
+        self.cdf = (c / c[-1]).float()
+        self.n = weights.shape[0]
+
+    def draw(self, n, gen):
+        import torch
+        u = torch.rand(n, device=self.cdf.device, generator=gen)
+        return torch.searchsorted(self.cdf, u).clamp_(max=self.n - 1)
+
+
+def make_samplers(w, device, seed):
+    """Per-partition samplers after a seeded random permutation of entity ids."""
+    import torch
+    from torchbiggraph_b200.buckets import partition_bounds
+    N, P = w["entities"], w["partitions"]
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    ranks = torch.arange(1, N + 1, device=device, dtype=torch.float32)
+    expo = 1.1 if w["gamma"] is None else 1.0 / (w["gamma"] - 1.0)
+    weight_by_rank = ranks.pow(-expo)
+    perm = torch.randperm(N, device=device, generator=g)      # rank -> entity id
+    weight_by_id = torch.empty_like(weight_by_rank)
+    weight_by_id[perm] = weight_by_rank
+    bounds = partition_bounds(N, P)
+    return [Sampler(weight_by_id[bounds[p]:bounds[p + 1]]) for p in range(P)], bounds, g
+
+
+def bucket_sequence(P):
+    from torchbiggraph_b200.buckets import round_robin_rounds
+    return [b for rnd in round_robin_rounds(P) for b in rnd]
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm = sorted(int(float(r[0])) for r in self.rows if r and r[0].replace(".", "").isdigit())
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[3 + i].lower().startswith("active") for r in self.rows)]
+        mx = max(int(float(r[1])) for r in self.rows if len(r) > 1)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the PyTorch-CPU port of the reference trainer, one HOGWILD process per core
+# ------------------------------------------------------------------------------------------------
+def _cpu_worker(i, w, W, G, theta, acc, cdf, cmd_q, start, finish):
+    """One HOGWILD worker process: trains batches on the shared tables without locks, as the
+    reference's worker pool does (torchbiggraph/train_cpu.py:861-884, util.py:294-314)."""
+    import torch
+    from oracle.pbg_step_torch import StepModel
+    torch.set_num_threads(1)
+    torch.manual_seed(1000 + i)
+    m = StepModel(w["dim"], w["op"], w["comp"], w["loss"], 0.1, 0.1, None, w["nb"], w["nu"], False, 1)
+    m.attach(W[0], G[0], W[1], G[1])
+    if theta is not None:
+        m.theta, m.acc = {"rhs": torch.nn.Parameter(theta)}, {"rhs": acc}
+    rows, B = W[0].shape[0], w["batch"]
+    while True:
+        n = cmd_q.get()
+        if n <= 0:
+            return
+        work = [(torch.searchsorted(cdf, torch.rand(B)).clamp_(max=rows - 1),
+                 torch.searchsorted(cdf, torch.rand(B)).clamp_(max=rows - 1)) for _ in range(n)]
+        start.wait()
+        for lhs, rhs in work:
+            m.train_batch(lhs, rhs, 0)
+        finish.wait()
+
+
+class CpuTrainer:
+    """All host cores as HOGWILD worker processes (forked before CUDA is touched) over embedding
+    tables in shared memory."""
+
+    def __init__(self, w, rows, seed=7):
+        import torch
+        import torch.multiprocessing as mp
+        torch.manual_seed(seed)
+        self.w, self.rows = w, rows
+        self.cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        D = w["dim"]
+        self.shared = True
+        W = [torch.randn(rows, D) * 1e-3 for _ in range(2)]
+        G = [torch.zeros(rows) for _ in range(2)]
+        try:
+            for t in W + G:
+                t.share_memory_()
+        except Exception:
+            self.shared = False        # no room in shared memory: forked workers update private copies
+        theta = acc = None
+        if w["op"] != "none":
+            theta = torch.zeros(1, D)
+            if w["op"] == "diagonal":
+                theta.fill_(1.0)
+            acc = torch.zeros(1, D)
+            if self.shared:
+                theta.share_memory_(); acc.share_memory_()
+        ranks = torch.arange(1, rows + 1, dtype=torch.float32)
+        expo = 1.1 if w["gamma"] is None else 1.0 / (w["gamma"] - 1.0)
+        c = torch.cumsum(ranks.pow(-expo)[torch.randperm(rows)].double(), 0)
+        cdf = (c / c[-1]).float()
+        ctx = mp.get_context("fork")
+        self.start, self.finish = ctx.Barrier(self.cores + 1), ctx.Barrier(self.cores + 1)
+        self.queues = [ctx.Queue() for _ in range(self.cores)]
+        self.procs = [ctx.Process(target=_cpu_worker, daemon=True,
+                                  args=(i, w, W, G, theta, acc, cdf, self.queues[i], self.start, self.finish))
+                      for i in range(self.cores)]
+        for p in self.procs:
+            p.start()
+
+    def run(self, batches_per_worker):
+        """Every worker trains `batches_per_worker` batches concurrently; returns (edges, seconds)."""
+        for q in self.queues:
+            q.put(batches_per_worker)
+        self.start.wait(timeout=600)
+        t0 = time.perf_counter()
+        self.finish.wait(timeout=3600)
+        dt = time.perf_counter() - t0
+        return self.cores * batches_per_worker * self.w["batch"], dt
+
+    def close(self):
+        for q in self.queues:
+            q.put(0)
+        for p in self.procs:
+            p.join(timeout=10)
+
+
+def cpu_baseline(w, budget_s=15.0):
+    rows = min(-(-w["entities"] // w["partitions"]), 400_000)
+    tr = CpuTrainer(w, rows)
+    tr.run(1)                                    # warm-up: allocator, autograd, thread start
+    e1, t1 = tr.run(1)
+    n = max(1, min(50, int(budget_s / max(t1, 1e-3))))
+    edges, dt = tr.run(n)
+    tr.close()
+    return {"value": edges / dt, "unit": "edges/sec", "cores": tr.cores, "kind": "port",
+            "sample": f"{tr.cores} HOGWILD processes x {n} batches of {w['batch']} edges on one bucket "
+                      f"({rows} rows per side, dim {w['dim']}); fp32 PyTorch-CPU port of the reference trainer"}
+
+
+def run_reference(args, w):
+    """`--impl reference`: K timed steps of the CPU port; a step = 1 batch per host core."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = min(-(-w["entities"] // w["partitions"]), 400_000)
+    tr = CpuTrainer(w, rows)
+    for _ in range(max(args.warmup, 1)):
+        tr.run(1)
+    edges = 0
+    total = 0.0
+    for _ in range(args.steps):
+        e, t = tr.run(1)
+        edges += e
+        total += t
+    tr.close()
+    v = edges / total
+    sample = f"{tr.cores} HOGWILD processes x 1 batch of {w['batch']} edges per step, one bucket of {rows} rows per side"
+    line = {"impl": "reference", "metric": "edges/sec trained", "value": v, "unit": "edges/sec", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, w, step_edges=tr.cores * w["batch"]),
+            "cpu_baseline": {"value": v, "unit": "edges/sec", "cores": tr.cores, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": "edges/sec", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, w, step_edges):
+    return {"workload": f"{args.workload}: {w['desc']}; {w['entities']} entities, {w['partitions']} partitions, dim {w['dim']}, "
+                        f"{w['op']}/{w['comp']}/{w['loss']}, batch {w['batch']}, {w['nb']} batch + {w['nu']} uniform negs",
+            "step": f"one bucket: {step_edges} edges", "l2": "inputs_larger_than_l2",
+            "batches_in_flight": args.k, "precision": args.precision}
+
+
+# ------------------------------------------------------------------------------------------------
+# the B200 arm
+# ------------------------------------------------------------------------------------------------
+def run_b200(args, w):
+    import torch
+    import torch.distributed as dist
+    import torchbiggraph_b200 as T
+    from torchbiggraph_b200 import _lib
+    from torchbiggraph_b200.buckets import ring_exchange
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(w)                    # before CUDA is initialised in this process
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    P, D, B = w["partitions"], w["dim"], w["batch"]
+    step_edges = min(EDGES_PER_STEP_CAP, max(B, w["edges"] // (P * P)))
+    samplers, bounds, gen = make_samplers(w, dev, seed=3)
+    # resident partitions: all of them on one GPU; two per GPU (lhs stays, rhs travels round the ring) otherwise
+    if world == 1:
+        mine = list(range(P))
+    else:
+        mine = [(2 * rank) % P, (2 * rank + 1) % P]
+    tables, states = {}, {}
+    for p in mine:
+        rows = bounds[p + 1] - bounds[p]
+        tables[p] = torch.randn(rows, D, device=dev, generator=gen) * 1e-3
+        states[p] = torch.zeros(rows, device=dev)
+    spare = None
+    if world > 1:
+        rows = max(bounds[p + 1] - bounds[p] for p in range(P))
+        spare = (torch.empty(rows, D, device=dev), torch.empty(rows, device=dev))
+
+    cfg = T.ConfigSchema(entities={"e": T.EntitySchema(num_partitions=P)},
+                         relations=[T.RelationSchema("r", "e", "e", operator=w["op"])], dimension=D,
+                         comparator=w["comp"], loss_fn=w["loss"], margin=0.1, lr=0.1, batch_size=B,
+                         num_batch_negs=w["nb"], num_uniform_negs=w["nu"], precision=args.precision,
+                         batches_in_flight=args.k)
+    model = T.make_model(cfg, dev)
+    trainer = T.B200Trainer(T.make_optimizer(cfg, model.parameters(), False),
+                            T.LOSS_FUNCTIONS.get_class(w["loss"])(margin=0.1), [1.0])
+    opts = {p: T.RowAdagrad([tables[p]], lr=0.1) for p in mine}
+    for p in mine:
+        opts[p].state[id(tables[p])]["sum"] = states[p]
+
+    seq = bucket_sequence(P) if world == 1 else None
+    total_steps = args.warmup + args.steps
+    nprof = 2
+
+    def bucket_for(step):
+        if world == 1:
+            return seq[step % len(seq)]
+        return mine[0], mine[1]
+
+    def bind(bk):
+        pl, pr = bk
+        model.clear_all_embeddings()
+        model.set_embeddings("e", T.Side.LHS, tables[pl])
+        model.set_embeddings("e", T.Side.RHS, tables[pr])
+        trainer.partitioned_optimizers.clear()
+        trainer.partitioned_optimizers["e", pl] = opts[pl]
+        trainer.partitioned_optimizers["e", pr] = opts[pr]
+
+    batches = [(o, min(B, step_edges - o), 0) for o in range(0, step_edges, B)]
+
+    def draw_edges(bk):
+        pl, pr = bk
+        return samplers[pl].draw(step_edges, gen), samplers[pr].draw(step_edges, gen)
+
+    # ---- device-resident pass: `value` -------------------------------------------------------
+    dev_edges = [draw_edges(bucket_for(s)) for s in range(total_steps + nprof)]
+    host_edges = [(l.cpu().pin_memory(), r.cpu().pin_memory()) for l, r in dev_edges[: total_steps]]
+
+    def step_device(s):
+        bind(bucket_for(s))
+        l, r = dev_edges[s]
+        trainer.train_batches(model, l, r, None, batches, want_per_batch=False)
+        if world > 1:
+            ring_exchange([tables[mine[1]], states[mine[1]]], list(spare))
+            tables[mine[1]].copy_(spare[0][: tables[mine[1]].shape[0]])
+            states[mine[1]].copy_(spare[1][: states[mine[1]].shape[0]])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for s in range(args.warmup):
+        step_device(s)
+    barrier()
+    nat = trainer._native
+    launches0 = nat.lib.pbg_launch_count(nat.ctx)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        e0.record()
+        for s in range(args.warmup, total_steps):
+            step_device(s)
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    launches = nat.lib.pbg_launch_count(nat.ctx) - launches0
+    trainer.read_stats()
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t)
+    value = world * args.steps * step_edges / (ms / 1e3)
+
+    # ---- end-to-end pass: host edges, copies and stats read-back inside the timed region --------
+    def step_host(s):
+        bind(bucket_for(s))
+        l, r = host_edges[s]
+        return trainer.train_batches(model, l, r, None, batches, want_per_batch=True)
+
+    for s in range(min(args.warmup, 2)):
+        step_host(s)
+    barrier()
+    e0.record()
+    last = None
+    for s in range(args.warmup, total_steps):
+        last = step_host(s)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t)
+    e2e = {"value": world * args.steps * step_edges / (ms_e2e / 1e3), "unit": "edges/sec",
+           "h2d_bytes_per_step": 2 * 8 * step_edges, "d2h_bytes_per_step": 32 * len(batches) + 4,
+           "last_batch_loss": last[-1].metrics["loss"] if last else None}
+
+    # ---- per-kernel-class timing pass ----------------------------------------------------------
+    import ctypes as C
+    check = _lib.check
+    check(nat.lib.pbg_set_profiling(nat.ctx, 1), nat.ctx)
+    for s in range(total_steps, total_steps + nprof):
+        bind(bucket_for(s))
+        l, r = dev_edges[s]
+        trainer.train_batches(model, l, r, None, batches, want_per_batch=False)
+    msc = (C.c_double * 7)()
+    lc = (C.c_int64 * 7)()
+    check(nat.lib.pbg_kernel_times(nat.ctx, msc, lc), nat.ctx)
+    check(nat.lib.pbg_set_profiling(nat.ctx, 0), nat.ctx)
+    alg = algorithmic(w)
+    pk = peaks()
+    edges_prof = nprof * step_edges
+    per_class = {}
+    model_bytes = {"gather": alg["gather_bytes"], "update": alg["update_bytes"]}
+    model_flops = {"score": alg["fwd_flops"], "grad": alg["bwd_flops"]}
+    for i, name in enumerate(_lib.KERNEL_CLASSES):
+        t_ms = msc[i]
+        ent = {"ms": round(t_ms, 3), "launches": int(lc[i]), "share": None}
+        if t_ms > 0 and name in model_bytes:
+            ent["GBps"] = round(model_bytes[name] * edges_prof / (t_ms / 1e3) / 1e9, 1)
+        if t_ms > 0 and name in model_flops:
+            ent["TFLOPs"] = round(model_flops[name] * edges_prof / (t_ms / 1e3) / 1e12, 2)
+        per_class[name] = ent
+    tot = sum(v["ms"] for v in per_class.values()) or 1.0
+    for v in per_class.values():
+        v["share"] = round(v["ms"] / tot, 3)
+    dom = max((n for n in per_class if n in model_bytes or n in model_flops), key=lambda n: per_class[n]["ms"])
+    if dom in model_flops:
+        ach = per_class[dom]["TFLOPs"]
+        roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
+                "frac": round(ach / pk["tflops"], 4), "traffic": None,
+                "peak_source": pk["source"] + " (cuBLAS bf16, sustained); the contraction runs in " + args.precision}
+    else:
+        ach = per_class[dom]["GBps"]
+        roof = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(ach / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"]}
+
+    if rank == 0:
+        line = {"metric": "edges/sec trained", "value": value, "unit": "edges/sec", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32" if args.precision == "fp32" else args.precision, "data": "synthetic",
+                "config": workload_config(args, w, step_edges), "e2e": e2e, "gpu_launches": int(launches),
+                "clocks": clocks.summary(), "roofline": roof, "kernels": per_class,
+                "algorithmic_per_edge": {"flops": alg["flops"], "bytes": alg["bytes"]},
+                "edges_per_sec_hbm_bound": pk["hbm_gbs"] * 1e9 / alg["bytes"]}
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--k", type=int, default=8, help="batches in flight (1 = sequential batches)")
+    ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32x3", "tf32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_b200(args, w)
+
+
+if __name__ == "__main__":
+    main()

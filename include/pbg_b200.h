@@ -175,6 +175,18 @@ int pbg_row_adagrad(pbg_context *ctx, float *emb, float *state, int64_t num_rows
 /* Kernel launches issued by this context since creation (for launch accounting). */
 int64_t pbg_launch_count(const pbg_context *ctx);
 
+/* Per-kernel-class device timing with CUDA events on the context's stream (the reference only
+ * keeps wall-clock sections per bucket, torchbiggraph/train_cpu.py:614-703).  While enabled every
+ * class of launches of every wave is bracketed by an event pair, which costs a little
+ * throughput: switch it on for a measuring pass only.  pbg_kernel_times synchronises the
+ * stream, adds up the pairs recorded since the last read and clears them.
+ * Classes: 0 sort keys + radix sort, 1 gather/operator/prepare, 2 score contraction, 3 loss,
+ * 4 gradient contractions, 5 optimizer updates, 6 stats.  ms_out / launches_out: HOST arrays of
+ * PBG_NUM_KERNEL_CLASSES entries. */
+#define PBG_NUM_KERNEL_CLASSES 7
+int pbg_set_profiling(pbg_context *ctx, int enable);
+int pbg_kernel_times(pbg_context *ctx, double *ms_out, int64_t *launches_out);
+
 #ifdef __cplusplus
 }
 #endif

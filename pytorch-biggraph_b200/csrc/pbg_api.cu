@@ -34,6 +34,29 @@ struct pbg_context {
   long long uni_cap = 0;
   long long launches = 0;
   unsigned long long batches_done = 0;
+  // optional event timing per kernel class
+  bool profiling = false;
+  struct Span { int cls; int launches; cudaEvent_t a, b; };
+  std::vector<Span> spans;
+  std::vector<cudaEvent_t> event_pool;
+};
+
+// Brackets the launches of one kernel class with an event pair when profiling is on.
+struct ClassTimer {
+  pbg_context *c; int cls; cudaEvent_t a = nullptr, b = nullptr;
+  static cudaEvent_t get(pbg_context *c) {
+    cudaEvent_t e;
+    if (!c->event_pool.empty()) { e = c->event_pool.back(); c->event_pool.pop_back(); return e; }
+    cudaEventCreate(&e);
+    return e;
+  }
+  ClassTimer(pbg_context *c_, int cls_) : c(c_), cls(cls_) {
+    if (c->profiling) { a = get(c); b = get(c); cudaEventRecord(a, c->stream); }
+  }
+  void done(int launches) {
+    c->launches += launches;
+    if (c->profiling) { cudaEventRecord(b, c->stream); c->spans.push_back({cls, launches, a, b}); }
+  }
 };
 
 static int fail(pbg_context *c, int code, const char *fmt, ...) {
@@ -187,6 +210,8 @@ extern "C" int pbg_destroy(pbg_context *c) {
   if (c->stats_dev) cudaFree(c->stats_dev);
   for (int i = 0; i < 3; ++i) if (c->edge_dev[i]) cudaFree(c->edge_dev[i]);
   for (int i = 0; i < 2; ++i) if (c->uni_dev[i]) cudaFree(c->uni_dev[i]);
+  for (auto &s : c->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
+  for (auto e : c->event_pool) cudaEventDestroy(e);
   delete c;
   return PBG_OK;
 }
@@ -254,9 +279,31 @@ static int check_errflag(pbg_context *c) {
 }
 
 static int run_forward(pbg_context *c, const WaveDims &d, const WaveBatches &wb, const WaveBufs &w) {
-  c->launches += launch_gather(d, wb, w, c->stream);
-  if (c->cfg.precision == PBG_PREC_FP32) c->launches += launch_score_simt(d, wb, w, c->stream);
-  else c->launches += launch_score_tc(d, wb, w, c->cfg.precision, c->stream);
+  { ClassTimer t(c, 1); t.done(launch_gather(d, wb, w, c->stream)); }
+  ClassTimer t(c, 2);
+  if (c->cfg.precision == PBG_PREC_FP32) t.done(launch_score_simt(d, wb, w, c->stream));
+  else t.done(launch_score_tc(d, wb, w, c->cfg.precision, c->stream));
+  return PBG_OK;
+}
+
+extern "C" int pbg_set_profiling(pbg_context *c, int enable) {
+  if (!c) return PBG_ERR_BAD_ARGUMENT;
+  c->profiling = enable != 0;
+  return PBG_OK;
+}
+
+extern "C" int pbg_kernel_times(pbg_context *c, double *ms_out, int64_t *launches_out) {
+  if (!c || !ms_out || !launches_out) return PBG_ERR_BAD_ARGUMENT;
+  CU(c, cudaSetDevice(c->device));
+  CU(c, cudaStreamSynchronize(c->stream));
+  for (int i = 0; i < PBG_NUM_KERNEL_CLASSES; ++i) { ms_out[i] = 0.0; launches_out[i] = 0; }
+  for (auto &s : c->spans) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, s.a, s.b) == cudaSuccess) { ms_out[s.cls] += ms; launches_out[s.cls] += s.launches; }
+    c->event_pool.push_back(s.a);
+    c->event_pool.push_back(s.b);
+  }
+  c->spans.clear();
   return PBG_OK;
 }
 
@@ -307,15 +354,24 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
       wb.wrel[i] = bk->relation_weights ? bk->relation_weights[wi] : 1.0f;
     }
     d.k = kk; d.nblk = kk * d.Cm; d.nocc = kk * d.spb;
-    c->launches += launch_build_keys(d, wb, w, c->sort.keys[0], c->sort.vals[0], c->stream);
-    c->launches += pbg_sort(c->sort, d.nocc, bits, c->stream);
+    {
+      ClassTimer t(c, 0);
+      int n = launch_build_keys(d, wb, w, c->sort.keys[0], c->sort.vals[0], c->stream);
+      t.done(n + pbg_sort(c->sort, d.nocc, bits, c->stream));
+    }
     run_forward(c, d, wb, w);
-    c->launches += launch_loss(d, wb, w, c->stream);
-    if (c->cfg.precision == PBG_PREC_FP32) c->launches += launch_grad_simt(d, wb, w, c->stream);
-    else c->launches += launch_grad_tc(d, wb, w, c->cfg.precision, c->stream);
-    c->launches += launch_update(d, wb, w, c->sort.keys[c->sort.result], c->sort.vals[c->sort.result],
-                                 c->cfg.lr, c->cfg.relation_lr, c->stream);
-    c->launches += launch_stats(d, wb, w, stats_out ? c->stats_dev : nullptr, c->sum_dev, c->stream);
+    { ClassTimer t(c, 3); t.done(launch_loss(d, wb, w, c->stream)); }
+    {
+      ClassTimer t(c, 4);
+      if (c->cfg.precision == PBG_PREC_FP32) t.done(launch_grad_simt(d, wb, w, c->stream));
+      else t.done(launch_grad_tc(d, wb, w, c->cfg.precision, c->stream));
+    }
+    {
+      ClassTimer t(c, 5);
+      t.done(launch_update(d, wb, w, c->sort.keys[c->sort.result], c->sort.vals[c->sort.result],
+                           c->cfg.lr, c->cfg.relation_lr, c->stream));
+    }
+    { ClassTimer t(c, 6); t.done(launch_stats(d, wb, w, stats_out ? c->stats_dev : nullptr, c->sum_dev, c->stream)); }
   }
   c->batches_done += (unsigned long long)num_batches;
   CU(c, cudaGetLastError());

@@ -146,3 +146,40 @@ def test_wave_reads_the_snapshot():
     # same rows are touched, values differ slightly (stale reads), accumulators too
     assert not np.array_equal(a.W_lhs, b.W_lhs)
     assert np.array_equal(a.W_lhs != z["W_lhs0"], b.W_lhs != z["W_lhs0"])
+
+
+def _torch_port_cases():
+    out = []
+    for n in step_fixture_names():
+        c, _ = load_step(n)
+        if c["op"] in ("linear", "affine") or c["disable_lhs"] or c["disable_rhs"]:
+            continue
+        out.append(n)
+    return out
+
+
+@pytest.mark.parametrize("name", _torch_port_cases())
+def test_torch_port_matches_reference(name):
+    """The fp32 PyTorch port that bench.py times as the CPU baseline reproduces the reference."""
+    import torch
+    from oracle.pbg_step_torch import StepModel
+    torch.set_num_threads(1)
+    c, z = load_step(name)
+    weights = [1.0] if c["dyn"] else [c["rel_weight"] if i == c["rel_idx"] else 1.0 for i in range(c["n_rel_std"])]
+    m = StepModel(c["D"], c["op"], c["comp"], c["loss"], c["margin"], c["lr"], c["relation_lr"], c["nb"], c["nu"],
+                  c["dyn"], c["R"] if c["dyn"] else c["n_rel_std"], weights)
+    W = torch.tensor(z["W_lhs0"]); G = torch.tensor(z["G_lhs0"])
+    W2, G2 = (torch.tensor(z["W_rhs0"]), torch.tensor(z["G_rhs0"])) if c["separate"] else (W, G)
+    m.attach(W, G, W2, G2)
+    with torch.no_grad():
+        for side in m.theta:
+            m.theta[side].copy_(torch.tensor(z[f"theta_{side}0"]))
+    for step in range(c["steps"]):
+        lhs, rhs, rel, ul, ur = batch_of(c, z, step)
+        rel_t = torch.tensor(rel) if c["dyn"] else rel
+        st = m.train_batch(torch.tensor(lhs), torch.tensor(rhs), rel_t, torch.tensor(ul), torch.tensor(ur))
+        assert st["loss"] == pytest.approx(float(z[f"loss_{step}"]), rel=1e-5, abs=1e-4)
+        np.testing.assert_allclose(W.detach().numpy(), z[f"W_lhs_after_{step}"], rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose(G.numpy(), z[f"G_lhs_after_{step}"], rtol=1e-5, atol=1e-7)
+        for side in m.theta:
+            np.testing.assert_allclose(m.theta[side].detach().numpy(), z[f"theta_{side}_after_{step}"], rtol=1e-5, atol=1e-6)
