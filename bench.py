@@ -300,7 +300,7 @@ def run_b200(args, w):
     samplers, bounds, gen = make_samplers(w, dev, seed=3)
     # resident partitions: all of them on one GPU; two per GPU (lhs stays, rhs travels round the ring) otherwise
     if world == 1:
-        mine = list(range(P))
+        mine = list(range(min(P, args.resident) if args.resident > 0 else P))
     else:
         mine = [(2 * rank) % P, (2 * rank + 1) % P]
     tables, states = {}, {}
@@ -325,7 +325,7 @@ def run_b200(args, w):
     for p in mine:
         opts[p].state[id(tables[p])]["sum"] = states[p]
 
-    seq = bucket_sequence(P) if world == 1 else None
+    seq = bucket_sequence(len(mine)) if world == 1 else None
     total_steps = args.warmup + args.steps
     nprof = 2
 
@@ -478,6 +478,8 @@ def main():
     ap.add_argument("--k", type=int, default=8, help="batches in flight (1 = sequential batches)")
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32x3", "tf32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--resident", type=int, default=0,
+                    help="partitions kept on the device at N=1 (0 = all); a small number keeps profiler captures small")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     w = WORKLOADS[args.workload]
