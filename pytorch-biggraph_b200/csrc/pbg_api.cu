@@ -23,11 +23,16 @@ struct pbg_context {
   char *ws = nullptr;
   size_t ws_bytes = 0;
   WaveBufs bufs;           // workspace pointers (table pointers filled per call)
-  SortPlan sort;
+  SortPlan sort[2];        // double-buffered: wave w+1 is sorted on `side` while wave w trains
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_sorted[2] = {nullptr, nullptr}, ev_updated[2] = {nullptr, nullptr}, ev_inputs = nullptr;
   pbg_batch_stats *stats_dev = nullptr;
   int stats_cap = 0;
   double *sum_dev = nullptr;
   int *errflag = nullptr;
+  float *psum = nullptr;        // partial gradient rows of hub rows, indexed by slot position
+  long long *hublist = nullptr;
+  int *hubcnt = nullptr;
   long long *edge_dev[3] = {nullptr, nullptr, nullptr};
   long long edge_cap = 0;
   long long *uni_dev[2] = {nullptr, nullptr};
@@ -50,12 +55,13 @@ struct ClassTimer {
     cudaEventCreate(&e);
     return e;
   }
-  ClassTimer(pbg_context *c_, int cls_) : c(c_), cls(cls_) {
-    if (c->profiling) { a = get(c); b = get(c); cudaEventRecord(a, c->stream); }
+  cudaStream_t st;
+  ClassTimer(pbg_context *c_, int cls_, cudaStream_t st_ = nullptr) : c(c_), cls(cls_), st(st_ ? st_ : c_->stream) {
+    if (c->profiling) { a = get(c); b = get(c); cudaEventRecord(a, st); }
   }
   void done(int launches) {
     c->launches += launches;
-    if (c->profiling) { cudaEventRecord(b, c->stream); c->spans.push_back({cls, launches, a, b}); }
+    if (c->profiling) { cudaEventRecord(b, st); c->spans.push_back({cls, launches, a, b}); }
   }
 };
 
@@ -165,9 +171,14 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   oCoef[0] = take(nN * 4); oCoef[1] = take(nN * 4); oCoef[2] = take(nQ * 4); oCoef[3] = take(nQ * 4);
   size_t oRel = take(nblk * 8 * (size_t)cfg->dim * 4);
   int swarps = pbg_sort_warps((int)nocc);
-  size_t oK0 = take((size_t)nocc * 8), oK1 = take((size_t)nocc * 8), oV0 = take((size_t)nocc * 4), oV1 = take((size_t)nocc * 4);
-  size_t oH = take((size_t)256 * swarps * 4);
+  size_t oK[2][2], oV[2][2], oH[2];
+  for (int s = 0; s < 2; ++s) {
+    oK[s][0] = take((size_t)nocc * 8); oK[s][1] = take((size_t)nocc * 8);
+    oV[s][0] = take((size_t)nocc * 4); oV[s][1] = take((size_t)nocc * 4);
+    oH[s] = take((size_t)256 * swarps * 4);
+  }
   size_t oSum = take(4 * sizeof(double)), oErr = take(256);
+  size_t oPsum = take((size_t)nocc * c->Dp * 4), oHub = take(((size_t)nocc / 8 + 64) * 8), oHubCnt = take(256);
   c->ws_bytes = off;
   CU(c, cudaMalloc(&c->ws, c->ws_bytes));
   CU(c, cudaMemsetAsync(c->ws, 0, c->ws_bytes, c->stream));
@@ -190,15 +201,25 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     b.violrow[p] = (int *)(c->ws + oViol[p]);
   }
   b.relpart = (float *)(c->ws + oRel);
-  c->sort.keys[0] = (unsigned long long *)(c->ws + oK0);
-  c->sort.keys[1] = (unsigned long long *)(c->ws + oK1);
-  c->sort.vals[0] = (unsigned int *)(c->ws + oV0);
-  c->sort.vals[1] = (unsigned int *)(c->ws + oV1);
-  c->sort.hist = (unsigned int *)(c->ws + oH);
-  c->sort.max_n = (int)nocc;
+  for (int s = 0; s < 2; ++s) {
+    c->sort[s].keys[0] = (unsigned long long *)(c->ws + oK[s][0]);
+    c->sort[s].keys[1] = (unsigned long long *)(c->ws + oK[s][1]);
+    c->sort[s].vals[0] = (unsigned int *)(c->ws + oV[s][0]);
+    c->sort[s].vals[1] = (unsigned int *)(c->ws + oV[s][1]);
+    c->sort[s].hist = (unsigned int *)(c->ws + oH[s]);
+    c->sort[s].max_n = (int)nocc;
+    c->sort[s].result = 0;
+    CU(c, cudaEventCreateWithFlags(&c->ev_sorted[s], cudaEventDisableTiming));
+    CU(c, cudaEventCreateWithFlags(&c->ev_updated[s], cudaEventDisableTiming));
+  }
+  CU(c, cudaEventCreateWithFlags(&c->ev_inputs, cudaEventDisableTiming));
+  CU(c, cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking));
   c->sum_dev = (double *)(c->ws + oSum);
   c->errflag = (int *)(c->ws + oErr);
   b.errflag = c->errflag;
+  c->psum = (float *)(c->ws + oPsum);
+  c->hublist = (long long *)(c->ws + oHub);
+  c->hubcnt = (int *)(c->ws + oHubCnt);
   CU(c, cudaStreamSynchronize(c->stream));
   return PBG_OK;
 }
@@ -210,6 +231,12 @@ extern "C" int pbg_destroy(pbg_context *c) {
   if (c->stats_dev) cudaFree(c->stats_dev);
   for (int i = 0; i < 3; ++i) if (c->edge_dev[i]) cudaFree(c->edge_dev[i]);
   for (int i = 0; i < 2; ++i) if (c->uni_dev[i]) cudaFree(c->uni_dev[i]);
+  for (int s = 0; s < 2; ++s) {
+    if (c->ev_sorted[s]) cudaEventDestroy(c->ev_sorted[s]);
+    if (c->ev_updated[s]) cudaEventDestroy(c->ev_updated[s]);
+  }
+  if (c->ev_inputs) cudaEventDestroy(c->ev_inputs);
+  if (c->side) cudaStreamDestroy(c->side);
   for (auto &s : c->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
   for (auto e : c->event_pool) cudaEventDestroy(e);
   delete c;
@@ -342,7 +369,12 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
     c->stats_cap = cap;
   }
   const int bits = bit_length(d.key_invalid);
-  for (int b0 = 0; b0 < num_batches; b0 += c->kmax) {
+  // The sort keys depend on the edge and negative ids only, never on the tables: the key build
+  // and radix sort of a wave run on the side stream and overlap the previous wave's kernels.
+  CU(c, cudaEventRecord(c->ev_inputs, c->stream));
+  CU(c, cudaStreamWaitEvent(c->side, c->ev_inputs, 0));
+  int wave = 0;
+  for (int b0 = 0; b0 < num_batches; b0 += c->kmax, ++wave) {
     int kk = num_batches - b0 < c->kmax ? num_batches - b0 : c->kmax;
     WaveBatches wb;
     memset(&wb, 0, sizeof wb);
@@ -354,10 +386,13 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
       wb.wrel[i] = bk->relation_weights ? bk->relation_weights[wi] : 1.0f;
     }
     d.k = kk; d.nblk = kk * d.Cm; d.nocc = kk * d.spb;
+    SortPlan &sp = c->sort[wave & 1];
     {
-      ClassTimer t(c, 0);
-      int n = launch_build_keys(d, wb, w, c->sort.keys[0], c->sort.vals[0], c->stream);
-      t.done(n + pbg_sort(c->sort, d.nocc, bits, c->stream));
+      if (wave >= 2) CU(c, cudaStreamWaitEvent(c->side, c->ev_updated[wave & 1], 0));   // buffers free again
+      ClassTimer t(c, 0, c->side);
+      int n = launch_build_keys(d, wb, w, sp.keys[0], sp.vals[0], c->side);
+      t.done(n + pbg_sort(sp, d.nocc, bits, c->side));
+      CU(c, cudaEventRecord(c->ev_sorted[wave & 1], c->side));
     }
     run_forward(c, d, wb, w);
     { ClassTimer t(c, 3); t.done(launch_loss(d, wb, w, c->stream)); }
@@ -366,11 +401,13 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
       if (c->cfg.precision == PBG_PREC_FP32) t.done(launch_grad_simt(d, wb, w, c->stream));
       else t.done(launch_grad_tc(d, wb, w, c->cfg.precision, c->stream));
     }
+    CU(c, cudaStreamWaitEvent(c->stream, c->ev_sorted[wave & 1], 0));
     {
       ClassTimer t(c, 5);
-      t.done(launch_update(d, wb, w, c->sort.keys[c->sort.result], c->sort.vals[c->sort.result],
-                           c->cfg.lr, c->cfg.relation_lr, c->stream));
+      t.done(launch_update(d, wb, w, sp.keys[sp.result], sp.vals[sp.result],
+                           c->cfg.lr, c->cfg.relation_lr, c->psum, c->hublist, c->hubcnt, c->stream));
     }
+    CU(c, cudaEventRecord(c->ev_updated[wave & 1], c->stream));
     { ClassTimer t(c, 6); t.done(launch_stats(d, wb, w, stats_out ? c->stats_dev : nullptr, c->sum_dev, c->stream)); }
   }
   c->batches_done += (unsigned long long)num_batches;
@@ -467,11 +504,12 @@ extern "C" int pbg_row_adagrad(pbg_context *c, float *emb, float *state, int64_t
   if (!c) return PBG_ERR_BAD_ARGUMENT;
   if (n == 0) return PBG_OK;
   if (!emb || !state || !rows || !grads || n < 0 || num_rows <= 0) return fail(c, PBG_ERR_BAD_ARGUMENT, "bad row_adagrad arguments");
-  if (n > c->sort.max_n) return fail(c, PBG_ERR_TOO_LARGE, "%d gradient rows exceed this context's sort capacity %d", n, c->sort.max_n);
+  SortPlan &sp = c->sort[0];
+  if (n > sp.max_n) return fail(c, PBG_ERR_TOO_LARGE, "%d gradient rows exceed this context's sort capacity %d", n, sp.max_n);
   CU(c, cudaSetDevice(c->device));
-  c->launches += launch_iota_keys((const long long *)rows, num_rows, n, c->sort.keys[0], c->sort.vals[0], c->errflag, c->stream);
-  c->launches += pbg_sort(c->sort, n, bit_length((unsigned long long)num_rows), c->stream);
-  c->launches += launch_row_adagrad_sorted(emb, state, c->cfg.dim, c->sort.keys[c->sort.result], c->sort.vals[c->sort.result],
+  c->launches += launch_iota_keys((const long long *)rows, num_rows, n, sp.keys[0], sp.vals[0], c->errflag, c->stream);
+  c->launches += pbg_sort(sp, n, bit_length((unsigned long long)num_rows), c->stream);
+  c->launches += launch_row_adagrad_sorted(emb, state, c->cfg.dim, sp.keys[sp.result], sp.vals[sp.result],
                                            grads, n, lr, (unsigned long long)num_rows, c->stream);
   CU(c, cudaGetLastError());
   return check_errflag(c);

@@ -193,7 +193,7 @@ int launch_export_scores(const WaveDims &d, const WaveBatches &wb, const WaveBuf
                          float *lhs_pos, float *rhs_pos, float *lhs_neg, float *rhs_neg, cudaStream_t st);
 int launch_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                   const unsigned long long *keys, const unsigned int *vals, float lr, float rel_lr,
-                  cudaStream_t st);
+                  float *psum, long long *hublist, int *hubcnt, cudaStream_t st);
 int launch_stats(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                  pbg_batch_stats *per_batch_dev, double *sum_dev, cudaStream_t st);
 int launch_row_adagrad_sorted(float *emb, float *state, int dim, const unsigned long long *keys,

@@ -1,9 +1,9 @@
-// Optimizer steps of one wave, one warp per touched table row.
+// Optimizer steps of one wave.
 //
 // The sorted occurrence list (pbg_sort.cu) puts all gradient slots of a table row next to each
-// other, in batch order.  A warp owns a row: it keeps the row in registers, and for every batch of
-// the wave that touched it sums the slots' gradients -- each taken back through
-// comparator.prepare and the relation operator on the fly -- and applies one optimizer step:
+// other, in batch order.  A warp keeps a row in registers, and for every batch of the wave that
+// touched it sums the slots' gradients -- each taken back through comparator.prepare and the
+// relation operator on the fly -- and applies one optimizer step:
 //   embedding rows  RowAdagrad   G += mean(g^2); w -= lr g / (sqrt(G) + 1e-10)
 //                                (torchbiggraph/row_adagrad.py:84-96; duplicates are summed first,
 //                                 the `coalesce` of line 83)
@@ -15,7 +15,6 @@
 #include "pbg_common.cuh"
 
 #define UPD_WARPS 8
-#define UPD_RUN 2          // sorted positions whose segment heads one warp looks after
 
 // Everything needed to pull one gradient slot back to the embedding row it came from.
 template <int VEC>
@@ -79,64 +78,6 @@ struct SlotGrad {
   }
 };
 
-template <int VEC>
-__global__ void __launch_bounds__(32 * UPD_WARPS)
-emb_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long long *__restrict__ keys,
-                  const unsigned int *__restrict__ vals, float lr) {
-  int lane = threadIdx.x & 31;
-  long long wid = (long long)blockIdx.x * UPD_WARPS + (threadIdx.x >> 5);
-  long long p0 = wid * UPD_RUN;
-  const int D = d.D;
-  const float invD = 1.0f / (float)D;
-  for (long long pos = p0; pos < p0 + UPD_RUN && pos < d.nocc; ++pos) {
-    unsigned long long key = keys[pos];
-    if (key >= d.key_rel_base) return;                       // operator rows and empty slots follow
-    if (pos > 0 && keys[pos - 1] == key) continue;           // not the head of a segment
-    int side = (!d.shared_table && key >= (unsigned long long)d.n_rows[0]) ? 1 : 0;
-    long long row = (long long)(side ? key - (unsigned long long)d.n_rows[0] : key);
-    float *wrow = w.W[side] + (size_t)row * D;
-    float4 wv[VEC], acc[VEC];
-#pragma unroll
-    for (int c = 0; c < VEC; ++c) {
-      int dd = c * 128 + lane * 4;
-      wv[c] = dd < D ? ld4(wrow + dd) : f4zero();
-      acc[c] = f4zero();
-    }
-    float G = w.G[side][row];
-    int cur_b = -1;
-    for (long long q = pos; q <= d.nocc; ++q) {
-      bool same = q < d.nocc && keys[q] == key;
-      Occ oc;
-      if (same) oc = occ_decode(d, (int)vals[q]);
-      if (cur_b >= 0 && (!same || oc.b != cur_b)) {          // close the batch: one RowAdagrad step
-        float ss = 0.f;
-#pragma unroll
-        for (int c = 0; c < VEC; ++c) ss += f4dot(acc[c], acc[c]);
-        ss = warp_sum(ss);
-        G += ss * invD;
-        float stepv = lr / (sqrtf(G) + PBG_ADAGRAD_EPS);
-#pragma unroll
-        for (int c = 0; c < VEC; ++c) { wv[c] = wv[c] - acc[c] * stepv; acc[c] = f4zero(); }
-      }
-      if (!same) break;
-      cur_b = oc.b;
-      SlotGrad<VEC> sg;
-      sg.init(d, wb, w, oc.a, oc.blk, oc.r, oc.b, lane);
-#pragma unroll
-      for (int c = 0; c < VEC; ++c) {
-        int dd = c * 128 + lane * 4;
-        if (dd < D) acc[c] = acc[c] + sg.gx(dd);
-      }
-    }
-#pragma unroll
-    for (int c = 0; c < VEC; ++c) {
-      int dd = c * 128 + lane * 4;
-      if (dd < D) st4(wrow + dd, wv[c]);
-    }
-    if (lane == 0) w.G[side][row] = G;
-  }
-}
-
 // d(loss)/d(operator row) contributed by one slot whose operand went through the operator:
 // needs the gradient at the operator output (gz) and the raw embedding row x.
 template <int VEC>
@@ -152,71 +93,242 @@ __device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC> &sg, const f
   return dd < h ? v * xv + vp * xp : v * xp - vp * xv;
 }
 
-// Dynamic relations: operator-table rows are sort keys of their own (key >= key_rel_base); the
-// raw embedding row of a slot is its operator-free copy in N0 / N1 (times |x| for cos).
-template <int VEC>
-__global__ void __launch_bounds__(32 * UPD_WARPS)
-rel_update_dyn_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long long *__restrict__ keys,
-                      const unsigned int *__restrict__ vals, float lr) {
-  int lane = threadIdx.x & 31;
-  long long wid = (long long)blockIdx.x * UPD_WARPS + (threadIdx.x >> 5);
-  long long p0 = wid * UPD_RUN;
-  const int D = d.D;
-  for (long long pos = p0; pos < p0 + UPD_RUN && pos < d.nocc; ++pos) {
-    unsigned long long key = keys[pos];
-    if (key >= d.key_invalid) return;
-    if (key < d.key_rel_base) continue;
-    if (pos > 0 && keys[pos - 1] == key) continue;
-    unsigned long long rk = key - d.key_rel_base;
-    int t = rk >= (unsigned long long)d.num_rels ? 1 : 0;
-    long long rl = (long long)(rk - (unsigned long long)t * d.num_rels);
-    float *th = w.theta[t] + (size_t)rl * D, *ac = w.acc[t] + (size_t)rl * D;
-    float4 tv[VEC], av[VEC], acc[VEC];
-#pragma unroll
-    for (int c = 0; c < VEC; ++c) {
-      int dd = c * 128 + lane * 4;
-      tv[c] = dd < D ? ld4(th + dd) : f4zero();
-      av[c] = dd < D ? ld4(ac + dd) : f4zero();
-      acc[c] = f4zero();
-    }
-    int cur_b = -1;
-    for (long long q = pos; q <= d.nocc; ++q) {
-      bool same = q < d.nocc && keys[q] == key;
-      Occ oc;
-      if (same) oc = occ_decode(d, (int)vals[q]);
-      if (cur_b >= 0 && (!same || oc.b != cur_b)) {          // one AsyncAdagrad step
-#pragma unroll
-        for (int c = 0; c < VEC; ++c) {
-          float4 g = acc[c];
-          av[c] = av[c] + g * g;
-          tv[c].x -= lr * g.x / (sqrtf(av[c].x) + PBG_ADAGRAD_EPS);
-          tv[c].y -= lr * g.y / (sqrtf(av[c].y) + PBG_ADAGRAD_EPS);
-          tv[c].z -= lr * g.z / (sqrtf(av[c].z) + PBG_ADAGRAD_EPS);
-          tv[c].w -= lr * g.w / (sqrtf(av[c].w) + PBG_ADAGRAD_EPS);
-          acc[c] = f4zero();
-        }
-      }
-      if (!same) break;
-      cur_b = oc.b;
-      int qa = oc.a == ARR_R0 ? ARR_Q0 : ARR_Q1;             // slot that carried the operator
-      int na = oc.a == ARR_R0 ? ARR_N1 : ARR_N0;             // its operator-free copy
-      SlotGrad<VEC> sg;
-      sg.init(d, wb, w, qa, oc.blk, oc.r, oc.b, lane);
-      size_t nrow = (size_t)oc.blk * w.xrows[na] + oc.r;
-      const float *x = w.X[na] + nrow * d.Dp;
-      float xscale = d.cmp == PBG_CMP_COS ? 1.0f / w.aux[na][nrow] : 1.0f;
-#pragma unroll
-      for (int c = 0; c < VEC; ++c) {
-        int dd = c * 128 + lane * 4;
-        if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, xscale, dd);
-      }
+// ------------------------------------------------------------------------------------------------
+// Segmented optimizer step over the sorted slot list.
+//
+// The list is cut into tiles of TILE slots, one warp per tile; the warp reads the keys of slots
+// [t0-32, t0+32) and the values of [t0, t0+32) in two coalesced loads and finds segment (= table
+// row) boundaries with ballots.
+//   * a row with at most SHORT_MAX slots is handled entirely by the warp whose tile holds its first
+//     slot: row and state in registers, one optimizer step per batch that touched it;
+//   * a longer row (a hub of the graph) is summed tile by tile: every warp writes, for each
+//     (batch, tile) run of its slots, one partial gradient row to psum[first slot of the run]; the
+//     warp that holds the head registers the row in hublist, and hub_update_kernel finishes it
+//     with one CTA per row (eight warps add the partial rows of a batch in a fixed order).
+// RULE selects the table and its optimizer: embedding rows / RowAdagrad, or (dynamic relations)
+// operator rows / AsyncAdagrad.
+// ------------------------------------------------------------------------------------------------
+#define TILE 8
+#define SHORT_MAX 24
+enum { RULE_EMB = 0, RULE_REL = 1 };
+
+template <int VEC, int RULE>
+struct RowState {
+  float4 v[VEC], a[VEC];     // row; per-element accumulator (RULE_REL only)
+  float G;                   // per-row accumulator (RULE_EMB only)
+  float *prow, *pacc;
+
+  __device__ __forceinline__ void load(const WaveDims &d, const WaveBufs &w, unsigned long long key, int lane) {
+    const int D = d.D;
+    if (RULE == RULE_EMB) {
+      int side = (!d.shared_table && key >= (unsigned long long)d.n_rows[0]) ? 1 : 0;
+      long long row = (long long)(side ? key - (unsigned long long)d.n_rows[0] : key);
+      prow = w.W[side] + (size_t)row * D;
+      pacc = w.G[side] + row;
+      G = *pacc;
+    } else {
+      unsigned long long rk = key - d.key_rel_base;
+      int t = rk >= (unsigned long long)d.num_rels ? 1 : 0;
+      long long rl = (long long)(rk - (unsigned long long)t * d.num_rels);
+      prow = w.theta[t] + (size_t)rl * D;
+      pacc = w.acc[t] + (size_t)rl * D;
     }
 #pragma unroll
     for (int c = 0; c < VEC; ++c) {
       int dd = c * 128 + lane * 4;
-      if (dd < D) { st4(th + dd, tv[c]); st4(ac + dd, av[c]); }
+      v[c] = dd < D ? ld4(prow + dd) : f4zero();
+      if (RULE == RULE_REL) a[c] = dd < D ? ld4(pacc + dd) : f4zero();
     }
   }
+  // one optimizer step with the summed gradient g of one batch
+  __device__ __forceinline__ void step(const float4 (&g)[VEC], float lr, float invD) {
+    if (RULE == RULE_EMB) {
+      float ss = 0.f;
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) ss += f4dot(g[c], g[c]);
+      ss = warp_sum(ss);
+      G += ss * invD;
+      float stepv = lr / (sqrtf(G) + PBG_ADAGRAD_EPS);
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) v[c] = v[c] - g[c] * stepv;
+    } else {
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) {
+        a[c] = a[c] + g[c] * g[c];
+        v[c].x -= lr * g[c].x / (sqrtf(a[c].x) + PBG_ADAGRAD_EPS);
+        v[c].y -= lr * g[c].y / (sqrtf(a[c].y) + PBG_ADAGRAD_EPS);
+        v[c].z -= lr * g[c].z / (sqrtf(a[c].z) + PBG_ADAGRAD_EPS);
+        v[c].w -= lr * g[c].w / (sqrtf(a[c].w) + PBG_ADAGRAD_EPS);
+      }
+    }
+  }
+  __device__ __forceinline__ void store(int D, int lane) {
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) {
+      int dd = c * 128 + lane * 4;
+      if (dd < D) { st4(prow + dd, v[c]); if (RULE == RULE_REL) st4(pacc + dd, a[c]); }
+    }
+    if (RULE == RULE_EMB && lane == 0) *pacc = G;
+  }
+};
+
+// acc += the contribution of one slot to its row's gradient
+template <int VEC, int RULE>
+__device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, const WaveBatches &wb,
+                                         const WaveBufs &w, const Occ &oc, int lane) {
+  const int D = d.D;
+  SlotGrad<VEC> sg;
+  if (RULE == RULE_EMB) {
+    sg.init(d, wb, w, oc.a, oc.blk, oc.r, oc.b, lane);
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) {
+      int dd = c * 128 + lane * 4;
+      if (dd < D) acc[c] = acc[c] + sg.gx(dd);
+    }
+  } else {
+    int qa = oc.a == ARR_R0 ? ARR_Q0 : ARR_Q1;             // slot that carried the operator
+    int na = oc.a == ARR_R0 ? ARR_N1 : ARR_N0;             // its operator-free copy (raw row)
+    sg.init(d, wb, w, qa, oc.blk, oc.r, oc.b, lane);
+    size_t nrow = (size_t)oc.blk * w.xrows[na] + oc.r;
+    const float *x = w.X[na] + nrow * d.Dp;
+    float xscale = d.cmp == PBG_CMP_COS ? 1.0f / w.aux[na][nrow] : 1.0f;
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) {
+      int dd = c * 128 + lane * 4;
+      if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, xscale, dd);
+    }
+  }
+}
+
+template <int VEC, int RULE>
+__global__ void __launch_bounds__(32 * UPD_WARPS, 2)
+tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long long *__restrict__ keys,
+                   const unsigned int *__restrict__ vals, float lr, float *__restrict__ psum,
+                   long long *__restrict__ hublist, int *__restrict__ hubcnt) {
+  const unsigned FULL = 0xffffffffu;
+  const unsigned long long SENT = ~0ull;
+  int lane = threadIdx.x & 31;
+  long long t0 = ((long long)blockIdx.x * UPD_WARPS + (threadIdx.x >> 5)) * TILE;
+  if (t0 >= d.nocc) return;
+  const int D = d.D;
+  const float invD = 1.0f / (float)D;
+  const unsigned long long lo = RULE == RULE_EMB ? 0ull : d.key_rel_base;
+  const unsigned long long hi = RULE == RULE_EMB ? d.key_rel_base : d.key_invalid;
+  long long pa = t0 - 32 + lane, pb = t0 + lane;
+  unsigned long long kA = pa >= 0 ? keys[pa] : SENT;
+  unsigned long long kB = pb < d.nocc ? keys[pb] : SENT;
+  unsigned int vB = pb < d.nocc ? vals[pb] : 0u;
+  if (__shfl_sync(FULL, kB, TILE - 1) < lo) return;          // tile holds only the other rule's rows
+  int i = 0;
+  while (i < TILE) {
+    unsigned long long key = __shfl_sync(FULL, kB, i);
+    if (key >= hi) return;                                   // sorted: nothing of this rule follows
+    if (key < lo) { ++i; continue; }
+    unsigned fm = __ballot_sync(FULL, kB == key);
+    unsigned rest = ~(fm >> i);
+    int run = rest ? __ffs(rest) - 1 : 32 - i;               // slots i .. i+run-1 of the window share the key
+    bool hits_end = i + run >= 32;
+    int back = 0;
+    if (i == 0) back = __clz(~__ballot_sync(FULL, kA == key)); // slots of this row just before the tile
+    bool head_here = back == 0;
+    bool hub = hits_end || back == 32 || back + run > SHORT_MAX;
+    if (!hub && !head_here) { i += run; continue; }          // short row owned by an earlier tile
+    int nproc = hub ? (run < TILE - i ? run : TILE - i) : run;
+    RowState<VEC, RULE> rs;
+    if (!hub) rs.load(d, w, key, lane);
+    float4 acc[VEC];
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) acc[c] = f4zero();
+    int cur_b = -1, run_start = 0;
+    for (int j = i; j <= i + nproc; ++j) {
+      bool in = j < i + nproc;
+      Occ oc;
+      if (in) oc = occ_decode(d, (int)__shfl_sync(FULL, vB, j));
+      if (cur_b >= 0 && (!in || oc.b != cur_b)) {             // a batch of this row is complete
+        if (hub) {
+          float *dst = psum + (size_t)(t0 + run_start) * d.Dp;
+#pragma unroll
+          for (int c = 0; c < VEC; ++c) {
+            int dd = c * 128 + lane * 4;
+            if (dd < D) st4(dst + dd, acc[c]);
+          }
+        } else {
+          rs.step(acc, lr, invD);
+        }
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) acc[c] = f4zero();
+      }
+      if (!in) break;
+      if (oc.b != cur_b) { cur_b = oc.b; run_start = j; }
+      add_slot<VEC, RULE>(acc, d, wb, w, oc, lane);
+    }
+    if (!hub) rs.store(D, lane);
+    else if (head_here && lane == 0) hublist[atomicAdd(hubcnt, 1)] = t0 + i;
+    i += nproc;
+  }
+}
+
+// One CTA per hub row: adds the partial rows the tile warps left in psum, batch by batch.  A batch's
+// slots [q, eb) were summed in runs that start at q and at every multiple of TILE inside (q, eb).
+template <int VEC, int RULE>
+__global__ void __launch_bounds__(32 * UPD_WARPS)
+hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long long *__restrict__ keys,
+                  const unsigned int *__restrict__ vals, float lr, const float *__restrict__ psum,
+                  const long long *__restrict__ hublist, const int *__restrict__ hubcnt) {
+  extern __shared__ __align__(16) float red[];               // [UPD_WARPS][VEC * 128]
+  __shared__ float wsum[UPD_WARPS];
+  const int lane = threadIdx.x & 31, wl = threadIdx.x >> 5;
+  const int D = d.D;
+  const float invD = 1.0f / (float)D;
+  const int nh = *hubcnt;
+  for (int h = blockIdx.x; h < nh; h += gridDim.x) {
+    long long head = hublist[h];
+    unsigned long long key = keys[head];
+    long long a = head + 1, b = d.nocc;
+    while (a < b) { long long m = (a + b) >> 1; if (keys[m] <= key) a = m + 1; else b = m; }
+    const long long end = a;
+    // warp 0 owns the row (same register layout as the tile warps); the others only add partials
+    RowState<VEC, RULE> rs;
+    if (wl == 0) rs.load(d, w, key, lane);
+    long long q = head;
+    while (q < end) {
+      int bq = occ_decode(d, (int)vals[q]).b;
+      long long x = q + 1, y = end;
+      while (x < y) { long long m = (x + y) >> 1; if (occ_decode(d, (int)vals[m]).b <= bq) x = m + 1; else y = m; }
+      const long long eb = x;
+      long long ftb = (q / TILE + 1) * TILE;
+      long long nruns = 1 + (eb > ftb ? (eb - 1 - ftb) / TILE + 1 : 0);
+      float4 acc[VEC];
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) acc[c] = f4zero();
+      for (long long r = wl; r < nruns; r += UPD_WARPS) {
+        long long start = r == 0 ? q : ftb + (r - 1) * TILE;
+        const float *src = psum + (size_t)start * d.Dp;
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) {
+          int dd = c * 128 + lane * 4;
+          if (dd < D) acc[c] = acc[c] + ld4(src + dd);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) st4(&red[(size_t)wl * VEC * 128 + c * 128 + lane * 4], acc[c]);
+      __syncthreads();
+      if (wl == 0) {
+        float4 g[VEC];
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) {
+          g[c] = f4zero();
+#pragma unroll
+          for (int k = 0; k < UPD_WARPS; ++k) g[c] = g[c] + ld4(&red[(size_t)k * VEC * 128 + c * 128 + lane * 4]);
+        }
+        rs.step(g, lr, invD);
+      }
+      __syncthreads();
+      q = eb;
+    }
+    if (wl == 0) rs.store(D, lane);
+  }
+  (void)wsum;
 }
 
 // Standard relations: every rhs row of a batch went through the same operator row.  Stage 1: one
@@ -273,36 +385,59 @@ __global__ void relupdate_std_kernel(WaveDims d, WaveBatches wb, WaveBufs w, flo
   }
 }
 
+struct UpdateScratch { float *psum; long long *hublist; int *hubcnt; };
+
 template <int VEC>
 static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                              const unsigned long long *keys, const unsigned int *vals, float lr, float rel_lr,
-                             cudaStream_t st) {
+                             const UpdateScratch &us, cudaStream_t st) {
   int launches = 0;
-  long long warps = ((long long)d.nocc + UPD_RUN - 1) / UPD_RUN;
+  long long warps = ((long long)d.nocc + TILE - 1) / TILE;
   int ctas = (int)((warps + UPD_WARPS - 1) / UPD_WARPS);
+  const int hub_ctas = 296;
+  size_t hub_smem = (size_t)UPD_WARPS * VEC * 128 * sizeof(float);
+  static bool attr_done[2] = {false, false};
   bool has_op = d.op != PBG_OP_NONE && w.theta[0] != nullptr;
   if (has_op && !d.dynamic) {
     relgrad_std_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, 0, st>>>(d, wb, w);
     ++launches;
   }
-  emb_update_kernel<VEC><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, lr);
-  ++launches;
+  if (!attr_done[0]) {
+    cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem);
+    attr_done[0] = true;
+  }
+  cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
+  tile_update_kernel<VEC, RULE_EMB><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  hub_update_kernel<VEC, RULE_EMB><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  launches += 2;
   if (has_op) {
-    if (d.dynamic) rel_update_dyn_kernel<VEC><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr);
-    else relupdate_std_kernel<<<(d.D + 127) / 128, 128, 0, st>>>(d, wb, w, rel_lr);
-    ++launches;
+    if (d.dynamic) {
+      if (!attr_done[1]) {
+        cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_REL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem);
+        attr_done[1] = true;
+      }
+      cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
+      tile_update_kernel<VEC, RULE_REL><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      hub_update_kernel<VEC, RULE_REL><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      launches += 2;
+    } else {
+      relupdate_std_kernel<<<(d.D + 127) / 128, 128, 0, st>>>(d, wb, w, rel_lr);
+      ++launches;
+    }
   }
   return launches;
 }
 
 int launch_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, const unsigned long long *keys,
-                  const unsigned int *vals, float lr, float rel_lr, cudaStream_t st) {
+                  const unsigned int *vals, float lr, float rel_lr, float *psum, long long *hublist, int *hubcnt,
+                  cudaStream_t st) {
+  UpdateScratch us{psum, hublist, hubcnt};
   int vec = (d.D + 127) / 128;
-  if (vec <= 1) return launch_update_vec<1>(d, wb, w, keys, vals, lr, rel_lr, st);
-  if (vec <= 2) return launch_update_vec<2>(d, wb, w, keys, vals, lr, rel_lr, st);
-  if (vec <= 4) return launch_update_vec<4>(d, wb, w, keys, vals, lr, rel_lr, st);
-  if (vec <= 8) return launch_update_vec<8>(d, wb, w, keys, vals, lr, rel_lr, st);
-  return launch_update_vec<16>(d, wb, w, keys, vals, lr, rel_lr, st);
+  if (vec <= 1) return launch_update_vec<1>(d, wb, w, keys, vals, lr, rel_lr, us, st);
+  if (vec <= 2) return launch_update_vec<2>(d, wb, w, keys, vals, lr, rel_lr, us, st);
+  if (vec <= 4) return launch_update_vec<4>(d, wb, w, keys, vals, lr, rel_lr, us, st);
+  if (vec <= 8) return launch_update_vec<8>(d, wb, w, keys, vals, lr, rel_lr, us, st);
+  return launch_update_vec<16>(d, wb, w, keys, vals, lr, rel_lr, us, st);
 }
 
 // Stand-alone sparse RowAdagrad step (row_adagrad.py:80-96): rows sorted with duplicates adjacent,
