@@ -8,9 +8,6 @@
 
 #include "pbg_common.cuh"
 
-int launch_score_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, int precision, cudaStream_t st);
-int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, int precision, cudaStream_t st);
-bool pbg_tc_available();
 
 struct pbg_context {
   pbg_config cfg;
@@ -30,6 +27,7 @@ struct pbg_context {
   int stats_cap = 0;
   double *sum_dev = nullptr;
   int *errflag = nullptr;
+  void *tcplan = nullptr;       // tensor maps of the tcgen05 contractions
   float *psum = nullptr;        // partial gradient rows of hub rows, indexed by slot position
   long long *hublist = nullptr;
   int *hubcnt = nullptr;
@@ -159,11 +157,18 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   // ---- carve the workspace ------------------------------------------------------------------
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
-  size_t oX[4], oAux[4], oG[4], oS[2], oSpos[2], oCoef[4], oLoss[2], oViol[2];
+  size_t oX[4], oAux[4], oG[4], oS[2], oSpos[2], oCoef[4], oLoss[2], oViol[2], oXL[4] = {0, 0, 0, 0}, oSL[2] = {0, 0};
+  const bool split = cfg->precision == PBG_PREC_TF32X3;
   oX[0] = take(nN * c->Dp * 4); oX[1] = take(nN * c->Dp * 4);
   oAux[0] = take(nN * 4); oAux[1] = take(nN * 4);
   if (dyn) { oX[2] = take(nQ * c->Dp * 4); oX[3] = take(nQ * c->Dp * 4); oAux[2] = take(nQ * 4); oAux[3] = take(nQ * 4); }
   else { oX[2] = oX[1]; oX[3] = oX[0]; oAux[2] = oAux[1]; oAux[3] = oAux[0]; }
+  if (split) {
+    oXL[0] = take(nN * c->Dp * 4); oXL[1] = take(nN * c->Dp * 4);
+    if (dyn) { oXL[2] = take(nQ * c->Dp * 4); oXL[3] = take(nQ * c->Dp * 4); }
+    else { oXL[2] = oXL[1]; oXL[3] = oXL[0]; }
+    oSL[0] = take(nQ * c->Ms * 4); oSL[1] = take(nQ * c->Ms * 4);
+  }
   oG[0] = take(nN * c->Dp * 4); oG[1] = take(nN * c->Dp * 4); oG[2] = take(nQ * c->Dp * 4); oG[3] = take(nQ * c->Dp * 4);
   for (int p = 0; p < 2; ++p) {
     oS[p] = take(nQ * c->Ms * 4); oSpos[p] = take(nQ * 4); oLoss[p] = take(nQ * 4); oViol[p] = take(nQ * 4);
@@ -189,7 +194,9 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     b.aux[a] = (float *)(c->ws + oAux[a]);
     b.GX[a] = (float *)(c->ws + oG[a]);
     b.coef[a] = (float *)(c->ws + oCoef[a]);
+    b.XL[a] = split ? (float *)(c->ws + oXL[a]) : nullptr;
   }
+  for (int p = 0; p < 2; ++p) b.SL[p] = split ? (float *)(c->ws + oSL[p]) : nullptr;
   b.xrows[0] = b.xrows[1] = c->Mm;
   b.xrows[2] = b.xrows[3] = dyn ? c->Pm : c->Mm;
   b.grows[0] = b.grows[1] = c->Mm;
@@ -220,6 +227,13 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   c->psum = (float *)(c->ws + oPsum);
   c->hublist = (long long *)(c->ws + oHub);
   c->hubcnt = (int *)(c->ws + oHubCnt);
+  if (cfg->precision != PBG_PREC_FP32) {
+    WaveDims gd;
+    memset(&gd, 0, sizeof gd);
+    gd.D = cfg->dim; gd.Dp = c->Dp; gd.Pm = c->Pm; gd.U = c->U; gd.Mm = c->Mm; gd.Ms = c->Ms; gd.Cm = c->Cm;
+    c->tcplan = pbg_tc_plan_create(gd, b, (int)nblk, cfg->precision);
+    if (!c->tcplan) return fail(c, PBG_ERR_CUDA, "could not encode the TMA tensor maps of the tensor-core contractions");
+  }
   CU(c, cudaStreamSynchronize(c->stream));
   return PBG_OK;
 }
@@ -228,6 +242,7 @@ extern "C" int pbg_destroy(pbg_context *c) {
   if (!c) return PBG_OK;
   cudaSetDevice(c->device);
   if (c->ws) cudaFree(c->ws);
+  if (c->tcplan) pbg_tc_plan_destroy(c->tcplan);
   if (c->stats_dev) cudaFree(c->stats_dev);
   for (int i = 0; i < 3; ++i) if (c->edge_dev[i]) cudaFree(c->edge_dev[i]);
   for (int i = 0; i < 2; ++i) if (c->uni_dev[i]) cudaFree(c->uni_dev[i]);
@@ -279,6 +294,7 @@ static int bind_bucket(pbg_context *c, const pbg_bucket *bk, WaveDims &d, WaveBu
   d.batch_negs = cfg.num_batch_negs > 0;
   d.neg_enabled[0] = !cfg.disable_lhs_negs; d.neg_enabled[1] = !cfg.disable_rhs_negs;
   d.num_batch_negs = cfg.num_batch_negs; d.spb = c->spb; d.margin = cfg.margin;
+  d.split = cfg.precision == PBG_PREC_TF32X3;
   d.n_rows[0] = bk->lhs_rows; d.n_rows[1] = bk->rhs_rows;
   d.shared_table = bk->lhs_emb == bk->rhs_emb;
   if (d.shared_table && bk->lhs_rows != bk->rhs_rows) return fail(c, PBG_ERR_BAD_ARGUMENT, "shared table with different row counts");
@@ -309,7 +325,7 @@ static int run_forward(pbg_context *c, const WaveDims &d, const WaveBatches &wb,
   { ClassTimer t(c, 1); t.done(launch_gather(d, wb, w, c->stream)); }
   ClassTimer t(c, 2);
   if (c->cfg.precision == PBG_PREC_FP32) t.done(launch_score_simt(d, wb, w, c->stream));
-  else t.done(launch_score_tc(d, wb, w, c->cfg.precision, c->stream));
+  else t.done(launch_score_tc(d, wb, w, c->tcplan, c->stream));
   return PBG_OK;
 }
 
@@ -399,7 +415,7 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
     {
       ClassTimer t(c, 4);
       if (c->cfg.precision == PBG_PREC_FP32) t.done(launch_grad_simt(d, wb, w, c->stream));
-      else t.done(launch_grad_tc(d, wb, w, c->cfg.precision, c->stream));
+      else t.done(launch_grad_tc(d, wb, w, c->tcplan, c->stream));
     }
     CU(c, cudaStreamWaitEvent(c->stream, c->ev_sorted[wave & 1], 0));
     {

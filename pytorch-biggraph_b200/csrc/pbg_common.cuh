@@ -46,6 +46,7 @@ struct WaveDims {
   long long n_rows[2];  // rows of the lhs / rhs table
   int shared_table;     // lhs and rhs read the same table
   int num_rels;
+  int split;            // TF32X3: operands and coefficient matrices are stored as hi + lo
   unsigned long long key_rel_base;   // first sort key of operator-table rows
   unsigned long long key_invalid;    // sort key of slots that carry no gradient
 };
@@ -60,9 +61,11 @@ struct WaveBatches {
 
 struct WaveBufs {
   float *X[4];       int xrows[4];   // operand arrays N0,N1,Q0,Q1 (rows per block; aliases allowed)
+  float *XL[4];                      // split mode: low parts (x - tf32(x)) of the operand arrays
   float *aux[4];                     // per operand row: cos -> 1/|z|, l2 -> |y|^2 (indexed like X)
   float *GX[4];      int grows[4];   // gradient arrays GN0,GN1,GQ0,GQ1
   float *S[2];                       // scores / coefficient matrices
+  float *SL[2];                      // split mode: low parts of the coefficient matrices
   float *spos[2];                    // positive scores [nblk][Pm]
   float *coef[4];                    // l2: colsum(T0), colsum(T1), rowsum(T0), rowsum(T1)
   float *lossrow[2];                 // per positive row: weighted loss term
@@ -170,6 +173,13 @@ __device__ __forceinline__ float4 operator*(float4 a, float4 b) { return make_fl
 __device__ __forceinline__ float4 operator*(float4 a, float s) { return make_float4(a.x * s, a.y * s, a.z * s, a.w * s); }
 __device__ __forceinline__ float f4dot(float4 a, float4 b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
 __device__ __forceinline__ float f4sum(float4 a) { return a.x + a.y + a.z + a.w; }
+// tf32(x): round to nearest, 10 mantissa bits kept -- the part of x a kind::tf32 MMA sees exactly
+__device__ __forceinline__ float tf32_hi(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+__device__ __forceinline__ float4 tf32_hi4(float4 v) { return make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w)); }
 
 // ---- host-side launchers (one per translation unit) ------------------------------------------
 struct SortPlan {
@@ -186,6 +196,11 @@ int pbg_sort(SortPlan &sp, int n, int bits, cudaStream_t st);
 int launch_build_keys(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                       unsigned long long *keys, unsigned int *vals, cudaStream_t st);
 int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
+void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int precision);
+void pbg_tc_plan_destroy(void *plan);
+bool pbg_tc_available();
+int launch_score_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st);
+int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st);
 int launch_score_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
 int launch_grad_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
 int launch_loss(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);

@@ -27,6 +27,24 @@ __device__ __forceinline__ void store_row(float *row, const float4 (&v)[VEC], in
     if (d < D) st4(row + d, v[c]);
   }
 }
+// hi = tf32(v) to `row`, lo = v - hi (exact in fp32) to `row_lo`
+template <int VEC>
+__device__ __forceinline__ void store_row_split(float *row, float *row_lo, const float4 (&v)[VEC], int D, int lane) {
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int d = c * 128 + lane * 4;
+    if (d < D) {
+      float4 h = tf32_hi4(v[c]);
+      st4(row + d, h);
+      st4(row_lo + d, v[c] - h);
+    }
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void put_row(float *base, float *base_lo, size_t off, const float4 (&v)[VEC], int D, int lane) {
+  if (base_lo) store_row_split<VEC>(base + off, base_lo + off, v, D, lane);
+  else store_row<VEC>(base + off, v, D, lane);
+}
 template <int VEC>
 __device__ __forceinline__ void zero_row(float *row, int D, int lane) {
 #pragma unroll
@@ -98,13 +116,17 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS) gather_kernel(WaveDims d, W
   BlockInfo bi = block_info(d, wb, blk);
   const int D = d.D;
   size_t nrow = (size_t)blk * d.Mm + r;
-  float *n0 = w.X[ARR_N0] + nrow * d.Dp, *n1 = w.X[ARR_N1] + nrow * d.Dp;
+  const size_t noff = nrow * d.Dp;
+  float *n0 = w.X[ARR_N0] + noff, *n1 = w.X[ARR_N1] + noff;
+  float *const *XL = d.split ? w.XL : nullptr;
+  auto lo = [&](int a) -> float * { return XL ? XL[a] : nullptr; };
   float4 x[VEC], z[VEC], y0[VEC], y1[VEC];
 
   if (r < d.Pm) {                                           // ---- an edge of the chunk ----------
     size_t qrow = (size_t)blk * d.Pm + r;
-    float *q0 = d.dynamic ? w.X[ARR_Q0] + qrow * d.Dp : nullptr;
-    float *q1 = d.dynamic ? w.X[ARR_Q1] + qrow * d.Dp : nullptr;
+    const size_t qoff = qrow * d.Dp;
+    float *q0 = d.dynamic ? w.X[ARR_Q0] + qoff : nullptr;
+    float *q1 = d.dynamic ? w.X[ARR_Q1] + qoff : nullptr;
     long long il = -1, ir = -1, rl = d.dynamic ? 0 : wb.rel[bi.b];
     bool ok = r < bi.n;
     if (ok) {
@@ -121,6 +143,11 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS) gather_kernel(WaveDims d, W
       zero_row<VEC>(n0, D, lane);
       zero_row<VEC>(n1, D, lane);
       if (d.dynamic) { zero_row<VEC>(q0, D, lane); zero_row<VEC>(q1, D, lane); }
+      if (XL) {
+        zero_row<VEC>(XL[ARR_N0] + noff, D, lane);
+        zero_row<VEC>(XL[ARR_N1] + noff, D, lane);
+        if (d.dynamic) { zero_row<VEC>(XL[ARR_Q0] + qoff, D, lane); zero_row<VEC>(XL[ARR_Q1] + qoff, D, lane); }
+      }
       if (lane == 0) {
         w.aux[ARR_N0][nrow] = 0.f; w.aux[ARR_N1][nrow] = 0.f;
         if (d.dynamic) { w.aux[ARR_Q0][qrow] = 0.f; w.aux[ARR_Q1][qrow] = 0.f; }
@@ -135,13 +162,13 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS) gather_kernel(WaveDims d, W
 #pragma unroll
     for (int c = 0; c < VEC; ++c) y0[c] = x[c];
     float a0 = prepare_row<VEC>(y0, d.cmp);
-    store_row<VEC>(n0, y0, D, lane);
+    put_row<VEC>(w.X[ARR_N0], lo(ARR_N0), noff, y0, D, lane);
     if (!d.dynamic) {
       // rhs row through the operator -> N1; one positive score shared by both problems
       load_row<VEC>(x, xr, D, lane);
       apply_operator<VEC>(y1, x, xr, th0, d.op, D, lane);
       float a1 = prepare_row<VEC>(y1, d.cmp);
-      store_row<VEC>(n1, y1, D, lane);
+      put_row<VEC>(w.X[ARR_N1], lo(ARR_N1), noff, y1, D, lane);
       float s = positive_score<VEC>(y0, y1, d.cmp);
       if (lane == 0) {
         w.aux[ARR_N0][nrow] = a0; w.aux[ARR_N1][nrow] = a1;
@@ -152,18 +179,18 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS) gather_kernel(WaveDims d, W
       // op_lhs(lhs row) -> Q1 (x still holds the lhs row)
       apply_operator<VEC>(z, x, xl, th1, d.op, D, lane);
       float aq1 = prepare_row<VEC>(z, d.cmp);
-      store_row<VEC>(q1, z, D, lane);
+      put_row<VEC>(w.X[ARR_Q1], lo(ARR_Q1), qoff, z, D, lane);
       // rhs row without operator -> N1
       load_row<VEC>(x, xr, D, lane);
 #pragma unroll
       for (int c = 0; c < VEC; ++c) y1[c] = x[c];
       float a1 = prepare_row<VEC>(y1, d.cmp);
-      store_row<VEC>(n1, y1, D, lane);
+      put_row<VEC>(w.X[ARR_N1], lo(ARR_N1), noff, y1, D, lane);
       float s1 = positive_score<VEC>(y1, z, d.cmp);         // problem 1: c(rhs, op_lhs(lhs))
       // op_rhs(rhs row) -> Q0
       apply_operator<VEC>(z, x, xr, th0, d.op, D, lane);
       float aq0 = prepare_row<VEC>(z, d.cmp);
-      store_row<VEC>(q0, z, D, lane);
+      put_row<VEC>(w.X[ARR_Q0], lo(ARR_Q0), qoff, z, D, lane);
       float s0 = positive_score<VEC>(y0, z, d.cmp);         // problem 0: c(lhs, op_rhs(rhs))
       if (lane == 0) {
         w.aux[ARR_N0][nrow] = a0; w.aux[ARR_N1][nrow] = a1;
@@ -181,6 +208,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS) gather_kernel(WaveDims d, W
     if (id >= d.n_rows[side]) { if (lane == 0) atomicOr(w.errflag, 1); id = -1; }
     if (id < 0) {
       zero_row<VEC>(dst, D, lane);
+      if (XL) zero_row<VEC>(XL[side] + noff, D, lane);
       if (lane == 0) w.aux[side][nrow] = 0.f;
       continue;
     }
@@ -193,7 +221,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS) gather_kernel(WaveDims d, W
     }
     apply_operator<VEC>(z, x, xrow, th, d.op, D, lane);
     float a = prepare_row<VEC>(z, d.cmp);
-    store_row<VEC>(dst, z, D, lane);
+    put_row<VEC>(w.X[side], lo(side), noff, z, D, lane);
     if (lane == 0) w.aux[side][nrow] = a;
   }
 }

@@ -1,6 +1,342 @@
-// tcgen05 tensor-core contractions (precision tiers PBG_PREC_TF32X3 / PBG_PREC_TF32).
+// Score and gradient contractions on the 5th-generation tensor cores (tcgen05) with fp32
+// accumulation in tensor memory -- precision tiers PBG_PREC_TF32X3 and PBG_PREC_TF32.  They take
+// the place of torch.bmm / baddbmm in the reference comparators (torchbiggraph/model.py:179-180,
+// 226-236) and of the bmm calls autograd issues for their backward.
+//
+//   score  : S_p[blk] (Pm x Mm) = Q_p[blk] (Pm x D) . N_p[blk]^T      A, B both K-major
+//   grad Q : GQ_p[blk] (Pm x D) = T_p[blk] (Pm x Mm) . N_p[blk]        A K-major, B MN-major
+//   grad N : GN_p[blk] (Mm x D) = T_p[blk]^T . Q_p[blk]                A, B both MN-major
+//
+// One CTA computes one 128 x BN output tile (BN <= 256) of one (chunk, problem):
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles of 32 k-values into a ring of
+//               shared-memory stages, completion on an mbarrier per stage
+//   warp 1      allocates tensor memory, issues tcgen05.mma.kind::tf32 (one elected lane) and
+//               commits to the stage's "empty" barrier / the final "accumulator ready" barrier
+//   warps 2-5   epilogue: tcgen05.ld 32 columns at a time (each warp its 32 TMEM lanes = 32
+//               rows), comparator epilogue for scores, 128-byte row-segment stores
+// K-major operands use the 128-byte swizzle; MN-major tf32 operands must use the 128-byte swizzle
+// with 32-byte atoms (descriptor layout type 1, TMA swizzle 128B_ATOM_32B), 32 x 32 element boxes.
+//
+// TF32X3: every operand exists as hi = tf32(x) and lo = x - hi (written by the producing kernels);
+// the tile is lo.hi + hi.lo + hi.hi accumulated in fp32, which restores fp32-level accuracy.
+//
+// Every wait on an mbarrier is bounded; when one runs out the CTA raises bit 1 of the error word,
+// stops issuing work, releases its tensor memory and returns.  Every TMA load is CTA-local.
+#include <cuda.h>
+
 #include "pbg_common.cuh"
 
-bool pbg_tc_available() { return false; }
-int launch_score_tc(const WaveDims &, const WaveBatches &, const WaveBufs &, int, cudaStream_t) { return 0; }
-int launch_grad_tc(const WaveDims &, const WaveBatches &, const WaveBufs &, int, cudaStream_t) { return 0; }
+#define TC_THREADS 192
+#define TC_WAIT_LIMIT 4000000
+
+struct TcMaps { CUtensorMap a[2][2]; CUtensorMap b[2][2]; };   // [problem][0 = hi, 1 = lo]
+
+struct TcGeom {
+  int M, N, K;          // output rows, columns, contraction length (per block)
+  int BN;               // tile columns (multiple of 16, <= 256)
+  int ldc;
+  long long c_blk;
+  float *C[2];
+  const float *auxA[2]; long long auxa_blk;   // score epilogue (l2 family): |a|^2, |b|^2
+  const float *auxB[2]; long long auxb_blk;
+  int cmp, score;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *errflag) {
+  for (int it = 0; it < TC_WAIT_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  atomicOr(errflag, 2);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               :: "r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
+  return ((uint64_t)((addr >> 4) & 0x3FFF)) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
+         ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
+}
+
+template <bool A_MN, bool B_MN, int NTERMS>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBatches wb, int *errflag) {
+  constexpr int PARTS = NTERMS == 3 ? 2 : 1;
+  constexpr int STAGES = NTERMS == 3 ? 2 : 4;
+  constexpr uint32_t A_BYTES = 128 * 128, B_BYTES = 256 * 128;          // one 32-k tile of 128 / 256 rows
+  constexpr uint32_t STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
+  const int p = blockIdx.z & 1, blk = blockIdx.z >> 1;
+  {
+    BlockInfo bi = block_info(d, wb, blk);
+    if (bi.n == 0) return;
+    if (g.score && !d.neg_enabled[p]) return;
+  }
+  const int m0 = blockIdx.y * 128, n0 = blockIdx.x * g.BN;
+  if (m0 >= g.M || n0 >= g.N) return;
+
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int failed;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar0 = smem_u32(&bars[0]);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  const uint32_t acc_bar = bar0 + 8u * (2 * STAGES);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2 * STAGES + 1; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar0 + 8u * i));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    failed = 0;
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" :: "r"(smem_u32(&tmem_base_s)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_base_s;
+  const int nkb = (g.K + 31) / 32;
+  const int b_atoms = (g.BN + 31) / 32;
+  const uint32_t stage_tx = PARTS * (A_BYTES + (B_MN ? (uint32_t)b_atoms * 4096u : (uint32_t)g.BN * 128u));
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer ----------------
+    for (int it = 0; it < nkb; ++it) {
+      int s = it % STAGES;
+      if (it >= STAGES && !mbar_wait(empty_bar(s), ((it / STAGES) - 1) & 1, errflag)) { failed = 1; break; }
+      uint32_t fb = full_bar(s);
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(fb), "r"(stage_tx) : "memory");
+      unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+      int k0 = it * 32;
+#pragma unroll
+      for (int part = 0; part < PARTS; ++part) {
+        uint32_t dA = smem_u32(st + part * A_BYTES);
+        uint32_t dB = smem_u32(st + PARTS * A_BYTES + part * B_BYTES);
+        if (!A_MN) tma_load_3d(dA, &maps.a[p][part], k0, m0, blk, fb);
+        else
+          for (int mb = 0; mb < 4; ++mb) tma_load_3d(dA + mb * 4096, &maps.a[p][part], m0 + mb * 32, k0, blk, fb);
+        if (!B_MN) tma_load_3d(dB, &maps.b[p][part], k0, n0, blk, fb);
+        else
+          for (int nb = 0; nb < b_atoms; ++nb) tma_load_3d(dB + nb * 4096, &maps.b[p][part], n0 + nb * 32, k0, blk, fb);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- MMA issuer ----------------
+    // instruction descriptor: D fp32, A/B tf32, operand majors, N >> 3, M >> 4
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                           ((uint32_t)(g.BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    bool ok = true;
+    for (int it = 0; it < nkb && ok; ++it) {
+      int s = it % STAGES;
+      if (!mbar_wait(full_bar(s), (it / STAGES) & 1, errflag)) { failed = 1; ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+      uint32_t aH = smem_u32(st), aL = smem_u32(st + A_BYTES);
+      uint32_t bH = smem_u32(st + PARTS * A_BYTES), bL = smem_u32(st + PARTS * A_BYTES + B_BYTES);
+#pragma unroll
+      for (int k8 = 0; k8 < 4; ++k8) {
+        uint32_t ao = A_MN ? k8 * 1024 : k8 * 32, bo = B_MN ? k8 * 1024 : k8 * 32;
+        uint64_t dAh = A_MN ? smem_desc(aH + ao, 4096, 512, 1) : smem_desc(aH + ao, 0, 1024, 2);
+        uint64_t dBh = B_MN ? smem_desc(bH + bo, 4096, 512, 1) : smem_desc(bH + bo, 0, 1024, 2);
+        uint32_t acc = (it > 0 || k8 > 0) ? 1u : 0u;
+        if (NTERMS == 3) {
+          uint64_t dAl = A_MN ? smem_desc(aL + ao, 4096, 512, 1) : smem_desc(aL + ao, 0, 1024, 2);
+          uint64_t dBl = B_MN ? smem_desc(bL + bo, 4096, 512, 1) : smem_desc(bL + bo, 0, 1024, 2);
+          asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                       :: "r"(tmem), "l"(dAl), "l"(dBh), "r"(idesc), "r"(acc) : "memory");
+          asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                       :: "r"(tmem), "l"(dAh), "l"(dBl), "r"(idesc), "r"(1u) : "memory");
+          acc = 1u;
+        }
+        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                     :: "r"(tmem), "l"(dAh), "l"(dBh), "r"(idesc), "r"(acc) : "memory");
+      }
+      // frees the stage for the producer once the MMAs above have read it
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(empty_bar(s)) : "memory");
+    }
+    if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(acc_bar) : "memory");
+  } else if (warp >= 2) {
+    // ---------------- epilogue ----------------
+    bool ok = mbar_wait(acc_bar, 0, errflag);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const int q = warp & 3;                       // the 32 TMEM lanes this warp may read
+      const int m = m0 + q * 32 + lane;
+      float *C = g.C[p] + (size_t)blk * g.c_blk + (size_t)m * g.ldc;
+      float an = 0.f;
+      const bool l2 = g.score && g.cmp >= PBG_CMP_L2;
+      if (l2 && m < g.M) an = g.auxA[p][(size_t)blk * g.auxa_blk + m];
+      const float *bn = l2 ? g.auxB[p] + (size_t)blk * g.auxb_blk : nullptr;
+      for (int c0 = 0; c0 < g.BN; c0 += 32) {
+        uint32_t r[32];
+        uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                       "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+                       "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+                       "=r"(r[30]), "=r"(r[31]) : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (m < g.M) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            int n = n0 + c0 + j;
+            if (n >= g.N || c0 + j >= g.BN) break;
+            float v[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              v[t] = __uint_as_float(r[j + t]);
+              if (l2 && n + t < g.N) {
+                float qv = (bn[n + t] - 2.0f * v[t]) + an;     // model.py:226-246
+                v[t] = g.cmp == PBG_CMP_L2 ? -sqrtf(fmaxf(qv, 1e-30f)) : -qv;
+              }
+            }
+            if (n + 3 < g.N) st4(C + n, make_float4(v[0], v[1], v[2], v[3]));
+            else
+              for (int t = 0; t < 4 && n + t < g.N; ++t) C[n + t] = v[t];
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    // If a wait ran out the asynchronous copies / MMAs may still be in flight: give them a
+    // bounded grace period before the tensor memory goes back.
+    if (failed) for (int i = 0; i < 200000; ++i) __nanosleep(20);
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" :: "r"(tmem) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side: tensor maps (encoded once per context) and launchers
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn get_encode() {
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    cudaDriverEntryPointQueryResult q;
+    void *p = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess) fn = (EncodeFn)p;
+  }
+  return fn;
+}
+
+bool pbg_tc_available() { return true; }
+
+// 3-D map over an array laid out [nblk][rows][ld] floats: dims {inner extent, rows, nblk}.
+static bool encode3(CUtensorMap *tm, const float *base, int inner, int rows, int nblk, int ld, long long blk_stride,
+                    int box_inner, int box_rows, bool mn_major) {
+  EncodeFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)nblk};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)blk_stride * 4};
+  cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+struct TcPlan {
+  TcMaps score, gradq, gradn;
+  int bn_score, bn_grad;
+  int nterms;
+};
+
+static int tile_cols(int n) {
+  int tiles = (n + 255) / 256;
+  int bn = ((n + tiles - 1) / tiles + 15) / 16 * 16;
+  return bn > 256 ? 256 : bn;
+}
+
+// Builds the tensor maps for the context's workspace.  Returns null when the driver entry point
+// is missing or an encode fails.
+void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int precision) {
+  TcPlan *pl = new TcPlan();
+  pl->nterms = precision == PBG_PREC_TF32X3 ? 3 : 1;
+  pl->bn_score = tile_cols(d.Mm);
+  pl->bn_grad = tile_cols(d.D);
+  bool ok = true;
+  for (int p = 0; p < 2; ++p) {
+    int q = ARR_Q0 + p, n = ARR_N0 + p;
+    for (int part = 0; part < (pl->nterms == 3 ? 2 : 1); ++part) {
+      const float *Xq = part ? w.XL[q] : w.X[q], *Xn = part ? w.XL[n] : w.X[n];
+      const float *T = part ? w.SL[p] : w.S[p];
+      long long qblk = (long long)w.xrows[q] * d.Dp, nblk_s = (long long)w.xrows[n] * d.Dp, tblk = (long long)d.Pm * d.Ms;
+      // score: A = Q (K-major, k = D), B = N (K-major)
+      ok &= encode3(&pl->score.a[p][part], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 128, false);
+      ok &= encode3(&pl->score.b[p][part], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, pl->bn_score, false);
+      // grad Q: A = T (K-major, k = Mm), B = N (MN-major: k rows = Mm, contiguous D)
+      ok &= encode3(&pl->gradq.a[p][part], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 128, false);
+      ok &= encode3(&pl->gradq.b[p][part], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, 32, true);
+      // grad N: A = T^T (MN-major: k rows = Pm, contiguous Mm), B = Q (MN-major: k rows = Pm, contiguous D)
+      ok &= encode3(&pl->gradn.a[p][part], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 32, true);
+      ok &= encode3(&pl->gradn.b[p][part], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 32, true);
+    }
+  }
+  if (!ok) { delete pl; return nullptr; }
+  return pl;
+}
+
+void pbg_tc_plan_destroy(void *plan) { delete (TcPlan *)plan; }
+
+template <bool A_MN, bool B_MN>
+static void launch_tc(const TcMaps &maps, const TcGeom &g, int nterms, const WaveDims &d, const WaveBatches &wb, int *errflag,
+                      cudaStream_t st) {
+  dim3 grid((g.N + g.BN - 1) / g.BN, (g.M + 127) / 128, d.nblk * 2);
+  size_t smem = 2 * 2 * (128 * 128 + 256 * 128) + 1024;       // 2 stages x (hi, lo) or 4 stages x hi
+  if (nterms == 3) {
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(tc_gemm_kernel<A_MN, B_MN, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+    tc_gemm_kernel<A_MN, B_MN, 3><<<grid, TC_THREADS, smem, st>>>(maps, g, d, wb, errflag);
+  } else {
+    static bool done = false;
+    if (!done) { cudaFuncSetAttribute(tc_gemm_kernel<A_MN, B_MN, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
+    tc_gemm_kernel<A_MN, B_MN, 1><<<grid, TC_THREADS, smem, st>>>(maps, g, d, wb, errflag);
+  }
+}
+
+int launch_score_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st) {
+  TcPlan *pl = (TcPlan *)plan;
+  TcGeom g;
+  memset(&g, 0, sizeof g);
+  g.M = d.Pm; g.N = d.Mm; g.K = d.D; g.BN = pl->bn_score; g.ldc = d.Ms; g.c_blk = (long long)d.Pm * d.Ms;
+  g.cmp = d.cmp; g.score = 1;
+  for (int p = 0; p < 2; ++p) {
+    g.C[p] = w.S[p];
+    g.auxA[p] = w.aux[ARR_Q0 + p]; g.auxB[p] = w.aux[ARR_N0 + p];
+  }
+  g.auxa_blk = w.xrows[ARR_Q0]; g.auxb_blk = w.xrows[ARR_N0];
+  launch_tc<false, false>(pl->score, g, pl->nterms, d, wb, w.errflag, st);
+  return 1;
+}
+
+int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st) {
+  TcPlan *pl = (TcPlan *)plan;
+  TcGeom g;
+  memset(&g, 0, sizeof g);
+  g.N = d.D; g.BN = pl->bn_grad; g.ldc = d.Dp;
+  // GQ_p = T_p . N_p
+  g.M = d.Pm; g.K = d.Mm; g.c_blk = (long long)w.grows[ARR_Q0] * d.Dp;
+  for (int p = 0; p < 2; ++p) g.C[p] = w.GX[ARR_Q0 + p];
+  launch_tc<false, true>(pl->gradq, g, pl->nterms, d, wb, w.errflag, st);
+  // GN_p = T_p^T . Q_p
+  g.M = d.Mm; g.K = d.Pm; g.c_blk = (long long)w.grows[ARR_N0] * d.Dp;
+  for (int p = 0; p < 2; ++p) g.C[p] = w.GX[ARR_N0 + p];
+  launch_tc<true, true>(pl->gradn, g, pl->nterms, d, wb, w.errflag, st);
+  return 2;
+}

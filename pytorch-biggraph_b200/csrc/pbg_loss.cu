@@ -46,10 +46,16 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
   BlockInfo bi = block_info(d, wb, blk);
   if (bi.n == 0) return;
   float *S = w.S[p] + ((size_t)blk * d.Pm + i) * d.Ms;
+  float *SLo = d.split ? w.SL[p] + ((size_t)blk * d.Pm + i) * d.Ms : nullptr;
+  // coefficient t stored as tf32(t) + remainder when the gradient contractions run as TF32X3
+  auto put = [&](int j, float t) {
+    if (SLo) { float h = tf32_hi(t); S[j] = h; SLo[j] = t - h; }
+    else S[j] = t;
+  };
   size_t prow = (size_t)blk * d.Pm + i;
   const int Mm = d.Mm;
   if (i >= bi.n) {                                   // padded positive: contributes nothing
-    for (int j = lane; j < d.Ms; j += 32) S[j] = 0.f;
+    for (int j = lane; j < d.Ms; j += 32) put(j, 0.f);
     if (lane == 0) {
       w.lossrow[p][prow] = 0.f; w.violrow[p][prow] = 0;
       if (d.cmp >= PBG_CMP_L2) w.coef[2 + p][prow] = 0.f;
@@ -87,10 +93,10 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
         if (j < Mm && !col_masked(d, bi, enabled, i, j)) t = coef_from_dscore(d.cmp, wr * expf(S[j] - m) * invZ, S[j]);
         if (j == i) t = 0.f;                                // filled below
         rowsum += t;
-        S[j] = t;
+        put(j, t);
       }
     } else {
-      for (int j = lane; j < d.Ms; j += 32) S[j] = 0.f;     // losses.py:139-140: loss 0, no gradient
+      for (int j = lane; j < d.Ms; j += 32) put(j, 0.f);    // losses.py:139-140: loss 0, no gradient
     }
   } else if (d.loss == PBG_LOSS_RANKING) {
     // sum_j max(0, margin - s + S_ij) (losses.py:116-122)
@@ -104,12 +110,12 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
           if (v > 0.f) { lossv += v; ds -= 1.0f; t = coef_from_dscore(d.cmp, wr, sj); }
         }
         rowsum += t;
-        S[j] = t;
+        put(j, t);
       }
       lossv = warp_sum(lossv);
       ds = warp_sum(ds);
     } else {
-      for (int j = lane; j < d.Ms; j += 32) S[j] = 0.f;
+      for (int j = lane; j < d.Ms; j += 32) put(j, 0.f);
     }
   } else {
     // softplus(-s) + (1/M) sum_j softplus(S_ij), M counts masked columns (losses.py:61-80)
@@ -123,7 +129,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
         t = coef_from_dscore(d.cmp, wr * nw * sigmoidf(sj), sj);
       }
       rowsum += t;
-      S[j] = t;
+      put(j, t);
     }
     lossv = warp_sum(lossv) * nw + softplusf(-s);
     ds = -sigmoidf(-s);
@@ -135,7 +141,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
   float tdiag = coef_from_dscore(d.cmp, wr * ds, s);
   __syncwarp();
   if (lane == 0) {
-    S[i] = tdiag;
+    put(i, tdiag);
     w.lossrow[p][prow] = wr * lossv;
     w.violrow[p][prow] = viol;
     if (d.cmp >= PBG_CMP_L2) w.coef[2 + p][prow] = rowsum + tdiag;
@@ -151,7 +157,8 @@ __global__ void colsum_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
   BlockInfo bi = block_info(d, wb, blk);
   float s = 0.f;
   const float *T = w.S[p] + (size_t)blk * d.Pm * d.Ms + j;
-  for (int i = 0; i < bi.n; ++i) s += T[(size_t)i * d.Ms];
+  const float *TL = d.split ? w.SL[p] + (size_t)blk * d.Pm * d.Ms + j : nullptr;
+  for (int i = 0; i < bi.n; ++i) s += T[(size_t)i * d.Ms] + (TL ? TL[(size_t)i * d.Ms] : 0.f);
   w.coef[p][(size_t)blk * d.Mm + j] = s;
 }
 

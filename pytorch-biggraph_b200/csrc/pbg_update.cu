@@ -19,7 +19,7 @@
 // Everything needed to pull one gradient slot back to the embedding row it came from.
 template <int VEC>
 struct SlotGrad {
-  const float *g, *y;      // gradient row, prepared operand row
+  const float *g, *y, *ylo; // gradient row, prepared operand row (+ its low part in split mode)
   const float *theta;      // operator row or null
   float dotgy, inv, cf;    // cos: <g', y> and 1/|z|; l2 family: coefficient of y
   int op, cmp, D;
@@ -29,6 +29,7 @@ struct SlotGrad {
     D = d.D; op = d.op; cmp = d.cmp;
     size_t xr = (size_t)blk * w.xrows[a] + r, gr = (size_t)blk * w.grows[a] + r;
     y = w.X[a] + xr * d.Dp;
+    ylo = d.split ? w.XL[a] + xr * d.Dp : nullptr;
     g = w.GX[a] + gr * d.Dp;
     theta = nullptr;
     if (op != PBG_OP_NONE) {
@@ -52,16 +53,20 @@ struct SlotGrad {
 #pragma unroll
       for (int c = 0; c < VEC; ++c) {
         int dd = c * 128 + lane * 4;
-        if (dd < D) s += f4dot(ld4(g + dd), ld4(y + dd));
+        if (dd < D) s += f4dot(ld4(g + dd), yv(dd));
       }
       dotgy = warp_sum(s);
     }
   }
+  __device__ __forceinline__ float4 yv(int dd) const {
+    float4 v = ld4(y + dd);
+    return ylo ? v + ld4(ylo + dd) : v;
+  }
   // gradient w.r.t. the operator output z at elements [dd, dd+4)
   __device__ __forceinline__ float4 gz(int dd) const {
     float4 v = ld4(g + dd);
-    if (cmp >= PBG_CMP_L2) v = v - ld4(y + dd) * cf;
-    else if (cmp == PBG_CMP_COS) v = (v - ld4(y + dd) * dotgy) * inv;   // (g - y <g,y>) / |z|
+    if (cmp >= PBG_CMP_L2) v = v - yv(dd) * cf;
+    else if (cmp == PBG_CMP_COS) v = (v - yv(dd) * dotgy) * inv;   // (g - y <g,y>) / |z|
     return v;
   }
   // gradient w.r.t. the embedding row at elements [dd, dd+4)
@@ -81,14 +86,14 @@ struct SlotGrad {
 // d(loss)/d(operator row) contributed by one slot whose operand went through the operator:
 // needs the gradient at the operator output (gz) and the raw embedding row x.
 template <int VEC>
-__device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC> &sg, const float *x, float xscale, int dd) {
+__device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC> &sg, const float *x, const float *xlo, float xscale, int dd) {
   float4 v = sg.gz(dd);
   if (sg.op == PBG_OP_TRANSLATION) return v;
-  float4 xv = ld4(x + dd) * xscale;
+  float4 xv = (xlo ? ld4(x + dd) + ld4(xlo + dd) : ld4(x + dd)) * xscale;
   if (sg.op == PBG_OP_DIAGONAL) return v * xv;
   int h = sg.D >> 1;
   int dp = dd < h ? dd + h : dd - h;
-  float4 vp = sg.gz(dp), xp = ld4(x + dp) * xscale;
+  float4 vp = sg.gz(dp), xp = (xlo ? ld4(x + dp) + ld4(xlo + dp) : ld4(x + dp)) * xscale;
   // d real = g_re a_re + g_im a_im ;  d imag = -g_re a_im + g_im a_re
   return dd < h ? v * xv + vp * xp : v * xp - vp * xv;
 }
@@ -191,11 +196,12 @@ __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, 
     sg.init(d, wb, w, qa, oc.blk, oc.r, oc.b, lane);
     size_t nrow = (size_t)oc.blk * w.xrows[na] + oc.r;
     const float *x = w.X[na] + nrow * d.Dp;
+    const float *xlo = d.split ? w.XL[na] + nrow * d.Dp : nullptr;
     float xscale = d.cmp == PBG_CMP_COS ? 1.0f / w.aux[na][nrow] : 1.0f;
 #pragma unroll
     for (int c = 0; c < VEC; ++c) {
       int dd = c * 128 + lane * 4;
-      if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, xscale, dd);
+      if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, xlo, xscale, dd);
     }
   }
 }
@@ -357,7 +363,7 @@ __global__ void __launch_bounds__(32 * UPD_WARPS) relgrad_std_kernel(WaveDims d,
 #pragma unroll
       for (int c = 0; c < VEC; ++c) {
         int dd = c * 128 + lane * 4;
-        if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, 1.0f, dd);
+        if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, nullptr, 1.0f, dd);
       }
     }
   }

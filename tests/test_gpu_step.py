@@ -25,11 +25,15 @@ def _close(got, want, rtol=RTOL, atol=2e-6, what=""):
     np.testing.assert_allclose(got, want, rtol=rtol, atol=atol, err_msg=what)
 
 
+PRECISIONS = ["fp32", "tf32x3"]      # both are the rtol 1e-4 tier
+
+
+@pytest.mark.parametrize("precision", PRECISIONS)
 @pytest.mark.parametrize("name", _names())
-def test_step_matches_reference_fixture(name):
+def test_step_matches_reference_fixture(name, precision):
     from b200_util import Rig
     c, z = load_step(name)
-    rig = Rig.from_fixture(c, z)
+    rig = Rig.from_fixture(c, z, precision=precision)
     ocfg, ost = oracle_config(c), oracle_state(c, z)
     for step in range(c["steps"]):
         lhs, rhs, rel, ul, ur = batch_of(c, z, step)
@@ -56,14 +60,15 @@ def test_step_matches_reference_fixture(name):
                 _close(rig.acc(side), want_acc, atol=2e-6 * float(np.abs(want_acc).max()), what=f"acc_{side} vs reference")
 
 
+@pytest.mark.parametrize("precision", PRECISIONS)
 @pytest.mark.parametrize("name", _names())
-def test_forward_scores_match_reference_fixture(name):
+def test_forward_scores_match_reference_fixture(name, precision):
     from b200_util import Rig
     c, z = load_step(name)
     ocfg, ost = oracle_config(c), oracle_state(c, z)
     for step in range(c["steps"]):
         O.train_batch(ocfg, ost, *batch_of(c, z, step))
-    rig = Rig.from_oracle_state(c, ost)
+    rig = Rig.from_oracle_state(c, ost, precision=precision)
     rel = z["fw_rel"]
     sc = rig.model(rig.edges(z["fw_lhs"], z["fw_rhs"], rel),
                    None if c["disable_lhs"] else z["fw_ul"], None if c["disable_rhs"] else z["fw_ur"])
@@ -74,14 +79,15 @@ def test_forward_scores_match_reference_fixture(name):
         _close(got, want, rtol=RTOL, atol=3e-5, what=k)
 
 
+@pytest.mark.parametrize("precision", PRECISIONS)
 @pytest.mark.parametrize("name", ["sequence_3_batches", "sequence_3_batches_dyn_cos"])
-def test_wave_of_three_batches_matches_oracle(name):
+def test_wave_of_three_batches_matches_oracle(name, precision):
     from b200_util import Rig
     c, z = load_step(name)
     ocfg, ost = oracle_config(c), oracle_state(c, z)
     batches = [batch_of(c, z, s) for s in range(3)]
     ostats = O.train_wave(ocfg, ost, batches)
-    rig = Rig.from_fixture(c, z, k=3)
+    rig = Rig.from_fixture(c, z, k=3, precision=precision)
     B = c["B"]
     lhs = torch.tensor(np.concatenate([b[0] for b in batches])).cuda()
     rhs = torch.tensor(np.concatenate([b[1] for b in batches])).cuda()
@@ -146,12 +152,13 @@ BASELINE_SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("precision", PRECISIONS)
 @pytest.mark.parametrize("D,N,B,nb,nu,op,comp,loss,dyn,R", BASELINE_SHAPES)
-def test_baseline_shapes_match_oracle(D, N, B, nb, nu, op, comp, loss, dyn, R):
+def test_baseline_shapes_match_oracle(D, N, B, nb, nu, op, comp, loss, dyn, R, precision):
     from b200_util import Rig
     c, ocfg, ost, batches = _random_case(11, D, N, B, nb, nu, op, comp, loss, dyn, R, zipf=True,
                                          w_scale=1.0 if comp == "cos" else 0.1)
-    rig = Rig.from_oracle_state(c, ost)
+    rig = Rig.from_oracle_state(c, ost, precision=precision)
     b = batches[0]
     ostats = O.train_batch(ocfg, ost, *b)
     st = rig.trainer.process_one_batch(rig.model, rig.edges(b[0], b[1], b[2]), b[3], b[4])
@@ -166,10 +173,11 @@ def test_baseline_shapes_match_oracle(D, N, B, nb, nu, op, comp, loss, dyn, R):
         _close(rig.theta("lhs"), ost.theta_lhs, atol=1e-6, what="theta_lhs")
 
 
-def test_wave_of_eight_matches_oracle_with_hub_rows():
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_wave_of_eight_matches_oracle_with_hub_rows(precision):
     from b200_util import Rig
     c, ocfg, ost, batches = _random_case(5, 64, 300, 200, 50, 50, "diagonal", "dot", "softmax", nbatches=8, zipf=True)
-    rig = Rig.from_oracle_state(c, ost, k=8)
+    rig = Rig.from_oracle_state(c, ost, k=8, precision=precision)
     O.train_wave(ocfg, ost, batches)
     nat = rig.trainer._context(rig.model, 200)
     lhs = torch.tensor(np.concatenate([b[0] for b in batches])).cuda()
@@ -180,6 +188,23 @@ def test_wave_of_eight_matches_oracle_with_hub_rows():
     _close(rig.W_lhs.cpu().numpy(), ost.W_lhs, atol=1e-6, what="W")
     _close(rig.G("lhs"), ost.G_lhs, atol=1e-8, what="G")
     _close(rig.theta("rhs"), ost.theta_rhs, atol=1e-6, what="theta")
+
+
+@pytest.mark.parametrize("D,N,B,nb,nu,op,comp,loss,dyn,R", BASELINE_SHAPES)
+def test_single_pass_tf32_is_the_1e3_tier(D, N, B, nb, nu, op, comp, loss, dyn, R):
+    """precision="tf32": operands truncated to TF32 once (10 mantissa bits), rtol 1e-3 on the loss;
+    row updates are compared on the scale of the largest update (scores carry 1e-3 errors)."""
+    from b200_util import Rig
+    c, ocfg, ost, batches = _random_case(11, D, N, B, nb, nu, op, comp, loss, dyn, R, zipf=True,
+                                         w_scale=1.0 if comp == "cos" else 0.1)
+    W0 = ost.W_lhs.copy()
+    rig = Rig.from_oracle_state(c, ost, precision="tf32")
+    b = batches[0]
+    ostats = O.train_batch(ocfg, ost, *b)
+    st = rig.trainer.process_one_batch(rig.model, rig.edges(b[0], b[1], b[2]), b[3], b[4])
+    assert st.metrics["loss"] == pytest.approx(ostats["loss"], rel=1e-3)
+    step = np.abs(ost.W_lhs - W0).max()
+    np.testing.assert_allclose(rig.W_lhs.cpu().numpy(), ost.W_lhs, rtol=1e-3, atol=0.02 * step)
 
 
 def test_device_drawn_negatives_properties():
