@@ -172,6 +172,25 @@ int pbg_neg_columns(const pbg_context *ctx, int32_t count, int32_t *chunk_size, 
 int pbg_row_adagrad(pbg_context *ctx, float *emb, float *state, int64_t num_rows,
                     const int64_t *rows_dev, const float *grads_dev, int32_t n, float lr);
 
+/* The same sparse RowAdagrad step for callers that cannot allocate device memory: a trainer that
+ * has given all of HBM to its partitions, a process under an allocator that owns the device, or
+ * code that cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply.  It has no
+ * counterpart in the reference (there the step is RowAdagrad.step on tensors PyTorch allocates).
+ * It takes no context and calls no allocating routine: its scratch (sort buffers, digit
+ * counters, error word; about 0.5 MB) is a fixed array inside the library that every GPU which
+ * loads the library holds until the process exits.
+ *   - at most 16384 gradient rows per call (n <= 16384), dim a multiple of 4 up to 2048; larger
+ *     sizes return PBG_ERR_TOO_LARGE / PBG_ERR_UNSUPPORTED and touch nothing;
+ *   - the first call on a device looks up the array's device address (with that device
+ *     current); make that first call before any stream capture is begun;
+ *   - all calls on a device share the one array: two calls whose kernels overlap on the GPU
+ *     (different streams or host threads) race.  Serialise them.
+ *   - the call returns after synchronising `stream` (a cudaStream_t, NULL = default stream);
+ *     PBG_ERR_INDEX_RANGE reports row ids outside [0, num_rows), which are skipped. */
+int pbg_row_adagrad_static(float *emb, float *state, int64_t num_rows, int32_t dim,
+                           const int64_t *rows_dev, const float *grads_dev, int32_t n, float lr,
+                           void *stream);
+
 /* Kernel launches issued by this context since creation (for launch accounting). */
 int64_t pbg_launch_count(const pbg_context *ctx);
 
