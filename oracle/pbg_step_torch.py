@@ -158,7 +158,7 @@ class StepModel:
             rp, sr, _ = self._direction("rhs", "lhs", rhs, lhs, rel, ur, None, False)
             w = self.relation_weights[0]
         loss = w * (self._loss(lp, sl) + self._loss(rp, sr))
-        stats = {"loss": float(loss), "violators_lhs": int((sl > lp.unsqueeze(1)).sum()),
+        stats = {"loss": float(loss.detach()), "violators_lhs": int((sl > lp.unsqueeze(1)).sum()),
                  "violators_rhs": int((sr > rp.unsqueeze(1)).sum()), "count": B}
         loss.backward()
         with torch.no_grad():

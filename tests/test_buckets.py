@@ -1,0 +1,65 @@
+"""Bucket scheduling and the partition hand-off between ranks (CPU: gloo, world size 2)."""
+import os
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from torchbiggraph_b200.buckets import (assign_round, average_relation_parameters, partition_bounds, partition_of,
+                                        ring_exchange, round_robin_rounds)
+
+
+@pytest.mark.parametrize("P", [1, 2, 3, 4, 7, 16])
+def test_rounds_cover_every_bucket_once_without_sharing_partitions(P):
+    rounds = round_robin_rounds(P)
+    seen = [b for r in rounds for b in r]
+    assert sorted(seen) == sorted((a, b) for a in range(P) for b in range(P))
+    for r in rounds[1:]:
+        parts = [p for b in r for p in b]
+        assert len(parts) == len(set(parts)), "two buckets of a round share a partition"
+
+
+def test_partition_bounds_follow_the_ceil_split():
+    b = partition_bounds(4_847_571, 16)
+    assert b[0] == 0 and b[-1] == 4_847_571 and len(b) == 17
+    sizes = [b[i + 1] - b[i] for i in range(16)]
+    assert max(sizes) - min(sizes) <= 1
+    ids = torch.tensor([0, b[1] - 1, b[1], 4_847_570])
+    part, off = partition_of(ids, b)
+    assert part.tolist() == [0, 0, 1, 15] and off.tolist() == [0, b[1] - 1, 0, 4_847_570 - b[15]]
+
+
+def test_assign_round_deals_buckets_to_ranks():
+    rnd = [(0, 1), (2, 3), (4, 5), (6, 7)]
+    assert assign_round(rnd, 2) == [[(0, 1), (4, 5)], [(2, 3), (6, 7)]]
+
+
+def _worker(rank, world, initfile, out):
+    dist.init_process_group("gloo", init_method=f"file://{initfile}", rank=rank, world_size=world)
+    emb = torch.full((4, 3), float(rank + 1))
+    state = torch.full((4,), float(10 * (rank + 1)))
+    r_emb, r_state = torch.empty_like(emb), torch.empty_like(state)
+    ring_exchange([emb, state], [r_emb, r_state])
+    theta = torch.full((2, 3), float(rank))
+    average_relation_parameters([theta])
+    out.put((rank, r_emb[0, 0].item(), r_state[0].item(), theta[0, 0].item()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ring_exchange_and_parameter_average_world_size_2():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        init = os.path.join(d, "init")
+        procs = [ctx.Process(target=_worker, args=(r, 2, init, q)) for r in range(2)]
+        for p in procs:
+            p.start()
+        res = sorted(q.get(timeout=120) for _ in range(2))
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    # rank 0 received rank 1's partition and vice versa; the shared table is the mean of 0 and 1
+    assert res == [(0, 2.0, 20.0, 0.5), (1, 1.0, 10.0, 0.5)]
