@@ -147,7 +147,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   c->Mm = c->Pm + c->U;
   c->Ms = (c->Mm + 3) / 4 * 4;
   c->Dp = (cfg->dim + 31) / 32 * 32;
-  c->spb = c->Cm * (2 * c->Mm + 2 * c->Pm) + (cfg->dynamic_relations ? 2 * c->Cm * c->Pm : 0);
+  c->spb = cfg->dynamic_relations ? c->Cm * (2 * c->Mm + 4 * c->Pm) : c->Cm * 2 * c->Mm;
   const bool dyn = cfg->dynamic_relations != 0;
   size_t nblk = (size_t)c->kmax * c->Cm;
   size_t nN = nblk * c->Mm, nQ = nblk * c->Pm;
@@ -169,7 +169,17 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     else { oXL[2] = oXL[1]; oXL[3] = oXL[0]; }
     oSL[0] = take(nQ * c->Ms * 4); oSL[1] = take(nQ * c->Ms * 4);
   }
-  oG[0] = take(nN * c->Dp * 4); oG[1] = take(nN * c->Dp * 4); oG[2] = take(nQ * c->Dp * 4); oG[3] = take(nQ * c->Dp * 4);
+  oG[0] = take(nN * c->Dp * 4); oG[1] = take(nN * c->Dp * 4);
+  if (dyn) { oG[2] = take(nQ * c->Dp * 4); oG[3] = take(nQ * c->Dp * 4); }
+  else { oG[2] = oG[0]; oG[3] = oG[1]; }            // standard relations have no GQ arrays
+  const int Ma = (c->Mm + 3) / 4 * 4;
+  size_t oA[2] = {0, 0}, oAL[2] = {0, 0};
+  if (!dyn) {
+    for (int s2 = 0; s2 < 2; ++s2) {
+      oA[s2] = take(nN * Ma * 4);
+      if (split) oAL[s2] = take(nN * Ma * 4);
+    }
+  }
   for (int p = 0; p < 2; ++p) {
     oS[p] = take(nQ * c->Ms * 4); oSpos[p] = take(nQ * 4); oLoss[p] = take(nQ * 4); oViol[p] = take(nQ * 4);
   }
@@ -196,7 +206,12 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     b.coef[a] = (float *)(c->ws + oCoef[a]);
     b.XL[a] = split ? (float *)(c->ws + oXL[a]) : nullptr;
   }
-  for (int p = 0; p < 2; ++p) b.SL[p] = split ? (float *)(c->ws + oSL[p]) : nullptr;
+  for (int p = 0; p < 2; ++p) {
+    b.SL[p] = split ? (float *)(c->ws + oSL[p]) : nullptr;
+    b.A[p] = dyn ? nullptr : (float *)(c->ws + oA[p]);
+    b.AL[p] = (!dyn && split) ? (float *)(c->ws + oAL[p]) : nullptr;
+  }
+  b.Ma = Ma;
   b.xrows[0] = b.xrows[1] = c->Mm;
   b.xrows[2] = b.xrows[3] = dyn ? c->Pm : c->Mm;
   b.grows[0] = b.grows[1] = c->Mm;
@@ -231,6 +246,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     WaveDims gd;
     memset(&gd, 0, sizeof gd);
     gd.D = cfg->dim; gd.Dp = c->Dp; gd.Pm = c->Pm; gd.U = c->U; gd.Mm = c->Mm; gd.Ms = c->Ms; gd.Cm = c->Cm;
+    gd.dynamic = dyn;
     c->tcplan = pbg_tc_plan_create(gd, b, (int)nblk, cfg->precision);
     if (!c->tcplan) return fail(c, PBG_ERR_CUDA, "could not encode the TMA tensor maps of the tensor-core contractions");
   }

@@ -16,7 +16,8 @@
 // Pm rows of N0 (aliases).  Dynamic relations: N0/N1 hold rows WITHOUT operator, Q0 holds
 // op_rhs[rel](rhs rows), Q1 holds op_lhs[rel](lhs rows) (model.py:705-758).
 //   S_p[blk][Pm][Ms]   scores of problem p, later overwritten by the coefficient matrix T_p
-//   GN_p[blk][Mm][Dp] = T_p^T . Q_p      GQ_p[blk][Pm][Dp] = T_p . N_p
+//   dynamic relations:  GN_p[blk][Mm][Dp] = T_p^T . Q_p      GQ_p[blk][Pm][Dp] = T_p . N_p
+//   standard relations: GN0 = A[0] . N1,  GN1 = A[1] . N0  with the combined matrices A (WaveBufs)
 // T_p holds d(loss)/d(score) with the gradient of the positive score folded into its (masked,
 // otherwise unused) diagonal, so the two products above are the whole backward of the
 // comparator.
@@ -66,6 +67,11 @@ struct WaveBufs {
   float *GX[4];      int grows[4];   // gradient arrays GN0,GN1,GQ0,GQ1
   float *S[2];                       // scores / coefficient matrices
   float *SL[2];                      // split mode: low parts of the coefficient matrices
+  // Standard relations: combined coefficient matrices, one per side, [nblk][Mm][Ma]:
+  //   A[0][m][j] = (j < Pm ? T0[j][m] : 0) + (m < Pm ? T1[m][j] : 0)   gradient of the lhs rows  = A[0] . N1
+  //   A[1][m][j] = (j < Pm ? T1[j][m] : 0) + (m < Pm ? T0[m][j] : 0)   gradient of the rhs rows  = A[1] . N0
+  float *A[2], *AL[2];
+  int Ma;                            // row stride of A (Mm rounded up to 4)
   float *spos[2];                    // positive scores [nblk][Pm]
   float *coef[4];                    // l2: colsum(T0), colsum(T1), rowsum(T0), rowsum(T1)
   float *lossrow[2];                 // per positive row: weighted loss term
@@ -127,15 +133,16 @@ __device__ __forceinline__ long long slot_row(const WaveDims &d, const WaveBatch
 }
 
 // Occurrence index o -> (batch b, array a, block, row).  Per batch the slots are enumerated
-// [N0: Cm*Mm | N1: Cm*Mm | Q0: Cm*Pm | Q1: Cm*Pm | R0: Cm*Pm | R1: Cm*Pm]; R0/R1 (operator-table
-// rows touched through Q0/Q1) exist only with dynamic relations.  Enumeration is batch-major so
-// that a stable sort by row keeps a row's occurrences in batch order.
+// [N0: Cm*Mm | N1: Cm*Mm | Q0: Cm*Pm | Q1: Cm*Pm | R0: Cm*Pm | R1: Cm*Pm]; the Q slots and R0/R1
+// (operator-table rows touched through Q0/Q1) exist only with dynamic relations -- with standard
+// relations a chunk row has ONE gradient slot, in GN0 / GN1.  Enumeration is batch-major so that
+// a stable sort by row keeps a row's occurrences in batch order.
 struct Occ { int b, a, blk, r; };
 __device__ __forceinline__ Occ occ_decode(const WaveDims &d, int o) {
   Occ q;
   q.b = o / d.spb;
   int w = o - q.b * d.spb;
-  int nN = d.Cm * d.Mm, nQ = d.Cm * d.Pm;
+  int nN = d.Cm * d.Mm, nQ = d.dynamic ? d.Cm * d.Pm : 0;   // standard relations: N slots only
   int rows;
   if (w < nN) { q.a = ARR_N0; rows = d.Mm; }
   else if ((w -= nN) < nN) { q.a = ARR_N1; rows = d.Mm; }

@@ -179,6 +179,20 @@ int launch_score_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &
 }
 
 int launch_grad_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
+  if (!d.dynamic) {            // GN_side = A[side] . N_(1-side): one product per side, K = Mm
+    GemmTasks tm;
+    for (int side = 0; side < 2; ++side) {
+      GemmTask &t = tm.t[side];
+      int o = ARR_N0 + (1 - side);
+      t.A = w.A[side]; t.a_blk = (long long)d.Mm * w.Ma; t.lda = w.Ma;
+      t.B = w.X[o]; t.b_blk = (long long)w.xrows[o] * d.Dp; t.ldb = d.Dp;
+      t.C = w.GX[ARR_N0 + side]; t.c_blk = (long long)d.Mm * d.Dp; t.ldc = d.Dp;
+      t.M = d.Mm; t.N = d.D; t.K = d.Mm;
+      t.auxA = t.auxB = nullptr; t.auxa_blk = t.auxb_blk = 0; t.cmp = 0;
+    }
+    launch_tiles<true, false, false>(tm, d, wb, st);
+    return 1;
+  }
   GemmTasks tq, tn;
   for (int p = 0; p < 2; ++p) {
     int q = ARR_Q0 + p, n = ARR_N0 + p;

@@ -252,7 +252,8 @@ static bool encode3(CUtensorMap *tm, const float *base, int inner, int rows, int
 }
 
 struct TcPlan {
-  TcMaps score, gradq, gradn;
+  TcMaps score, gradq, gradn, gradm;
+  bool dynamic;
   int bn_score, bn_grad;
   int nterms;
 };
@@ -267,6 +268,7 @@ static int tile_cols(int n) {
 // is missing or an encode fails.
 void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int precision) {
   TcPlan *pl = new TcPlan();
+  pl->dynamic = d.dynamic != 0;
   pl->nterms = precision == PBG_PREC_TF32X3 ? 3 : 1;
   pl->bn_score = tile_cols(d.Mm);
   pl->bn_grad = tile_cols(d.D);
@@ -280,12 +282,21 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
       // score: A = Q (K-major, k = D), B = N (K-major)
       ok &= encode3(&pl->score.a[p][part], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 128, false);
       ok &= encode3(&pl->score.b[p][part], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, pl->bn_score, false);
-      // grad Q: A = T (K-major, k = Mm), B = N (MN-major: k rows = Mm, contiguous D)
-      ok &= encode3(&pl->gradq.a[p][part], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 128, false);
-      ok &= encode3(&pl->gradq.b[p][part], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, 32, true);
-      // grad N: A = T^T (MN-major: k rows = Pm, contiguous Mm), B = Q (MN-major: k rows = Pm, contiguous D)
-      ok &= encode3(&pl->gradn.a[p][part], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 32, true);
-      ok &= encode3(&pl->gradn.b[p][part], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 32, true);
+      if (pl->dynamic) {
+        // grad Q: A = T (K-major, k = Mm), B = N (MN-major: k rows = Mm, contiguous D)
+        ok &= encode3(&pl->gradq.a[p][part], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 128, false);
+        ok &= encode3(&pl->gradq.b[p][part], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, 32, true);
+        // grad N: A = T^T (MN-major: k rows = Pm, contiguous Mm), B = Q (MN-major: k rows = Pm, contiguous D)
+        ok &= encode3(&pl->gradn.a[p][part], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 32, true);
+        ok &= encode3(&pl->gradn.b[p][part], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 32, true);
+      } else {
+        // merged: side p: A = A[p] (K-major, k = Mm), B = the other side's operand rows (MN-major)
+        const float *Am = part ? w.AL[p] : w.A[p];
+        int o = ARR_N0 + (1 - p);
+        const float *Xo = part ? w.XL[o] : w.X[o];
+        ok &= encode3(&pl->gradm.a[p][part], Am, d.Mm, d.Mm, nblk_max, w.Ma, (long long)d.Mm * w.Ma, 32, 128, false);
+        ok &= encode3(&pl->gradm.b[p][part], Xo, d.D, w.xrows[o], nblk_max, d.Dp, (long long)w.xrows[o] * d.Dp, 32, 32, true);
+      }
     }
   }
   if (!ok) { delete pl; return nullptr; }
@@ -330,6 +341,12 @@ int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, 
   TcGeom g;
   memset(&g, 0, sizeof g);
   g.N = d.D; g.BN = pl->bn_grad; g.ldc = d.Dp;
+  if (!pl->dynamic) {          // GN_side = A[side] . N_(1-side)
+    g.M = d.Mm; g.K = d.Mm; g.c_blk = (long long)d.Mm * d.Dp;
+    for (int p = 0; p < 2; ++p) g.C[p] = w.GX[ARR_N0 + p];
+    launch_tc<false, true>(pl->gradm, g, pl->nterms, d, wb, w.errflag, st);
+    return 1;
+  }
   // GQ_p = T_p . N_p
   g.M = d.Pm; g.K = d.Mm; g.c_blk = (long long)w.grows[ARR_Q0] * d.Dp;
   for (int p = 0; p < 2; ++p) g.C[p] = w.GX[ARR_Q0 + p];

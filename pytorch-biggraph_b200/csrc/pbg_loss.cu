@@ -46,7 +46,8 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
   BlockInfo bi = block_info(d, wb, blk);
   if (bi.n == 0) return;
   float *S = w.S[p] + ((size_t)blk * d.Pm + i) * d.Ms;
-  float *SLo = d.split ? w.SL[p] + ((size_t)blk * d.Pm + i) * d.Ms : nullptr;
+  // only with dynamic relations is T itself an MMA operand; otherwise coef_kernel splits A
+  float *SLo = (d.split && d.dynamic) ? w.SL[p] + ((size_t)blk * d.Pm + i) * d.Ms : nullptr;
   // coefficient t stored as tf32(t) + remainder when the gradient contractions run as TF32X3
   auto put = [&](int j, float t) {
     if (SLo) { float h = tf32_hi(t); S[j] = h; SLo[j] = t - h; }
@@ -162,9 +163,52 @@ __global__ void colsum_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
   w.coef[p][(size_t)blk * d.Mm + j] = s;
 }
 
+// Standard relations: a chunk row is scored in both problems (as a negative of one, as the
+// scored side of the other), and both gradients land on the same prepared row.  One warp per
+// (side, block, row m) merges them into the combined coefficient matrix A[side] (see WaveBufs), so
+// that the backward pass is ONE product per side with K = Mm, and keeps the row sum of A for the
+// l2 family (coefficient of the row's own |y|^2 term).
+__global__ void __launch_bounds__(32 * LOSS_WARPS) coef_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * LOSS_WARPS + (threadIdx.x >> 5);
+  long long per_side = (long long)d.nblk * d.Mm;
+  if (item >= 2 * per_side) return;
+  int side = (int)(item / per_side);
+  long long rem = item - side * per_side;
+  int blk = (int)(rem / d.Mm), m = (int)(rem - (long long)blk * d.Mm);
+  BlockInfo bi = block_info(d, wb, blk);
+  if (bi.n == 0) return;
+  // side 0 (lhs rows): negatives of problem 0 (columns of T0), scored side of problem 1 (rows of T1)
+  const float *Tcol = w.S[side] + (size_t)blk * d.Pm * d.Ms;        // T_side[j][m], j < Pm
+  const float *Trow = w.S[1 - side] + ((size_t)blk * d.Pm + m) * d.Ms;   // T_other[m][j], m < Pm
+  size_t arow = ((size_t)blk * d.Mm + m) * w.Ma;
+  float *A = w.A[side] + arow;
+  float *AL = d.split ? w.AL[side] + arow : nullptr;
+  float rowsum = 0.f;
+  for (int j = lane; j < w.Ma; j += 32) {
+    float a = 0.f;
+    if (j < d.Mm) {
+      if (j < bi.n) a += Tcol[(size_t)j * d.Ms + m];
+      if (m < bi.n) a += Trow[j];
+    }
+    rowsum += a;
+    if (AL) { float h = tf32_hi(a); A[j] = h; AL[j] = a - h; }
+    else A[j] = a;
+  }
+  if (d.cmp >= PBG_CMP_L2) {
+    rowsum = warp_sum(rowsum);
+    if (lane == 0) w.coef[side][(size_t)blk * d.Mm + m] = rowsum;
+  }
+}
+
 int launch_loss(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
   long long items = 2ll * d.nblk * d.Pm;
   loss_kernel<<<(int)((items + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+  if (!d.dynamic) {
+    long long rows = 2ll * d.nblk * d.Mm;
+    coef_kernel<<<(int)((rows + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+    return 2;
+  }
   if (d.cmp >= PBG_CMP_L2) {
     dim3 g((d.Mm + 127) / 128, d.nblk, 2);
     colsum_kernel<<<g, 128, 0, st>>>(d, wb, w);

@@ -44,7 +44,7 @@ struct SlotGrad {
     }
     cf = 0.f; inv = 1.f; dotgy = 0.f;
     if (cmp >= PBG_CMP_L2) {
-      // ga = T.N - rowsum(T) a ;  gb = T^T.Q - colsum(T) b
+      // dynamic: ga = T.N - rowsum(T) a ;  gb = T^T.Q - colsum(T) b.  standard: g = A.N' - rowsum(A) y
       const float *cp = (a == ARR_N0) ? w.coef[0] : (a == ARR_N1) ? w.coef[1] : (a == ARR_Q0) ? w.coef[2] : w.coef[3];
       cf = cp[gr];
     } else if (cmp == PBG_CMP_COS) {
@@ -338,7 +338,7 @@ hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long lo
 }
 
 // Standard relations: every rhs row of a batch went through the same operator row.  Stage 1: one
-// CTA per chunk sums the parameter gradient of its rows (N1 rows: chunk + uniform; Q0 rows: chunk)
+// CTA per chunk sums the parameter gradient of its rows (N1 slots: chunk rows + uniform rows)
 // into relpart[b][c][warp][D]; the raw rows are re-read from the rhs table, which this wave has not
 // updated yet.  Stage 2 (relupdate_std_kernel) adds the chunks up and steps theta, batch by batch.
 template <int VEC>
@@ -350,11 +350,11 @@ __global__ void __launch_bounds__(32 * UPD_WARPS) relgrad_std_kernel(WaveDims d,
   float4 acc[VEC];
 #pragma unroll
   for (int c = 0; c < VEC; ++c) acc[c] = f4zero();
-  int items = d.Mm + d.Pm;                                   // N1 slots then Q0 slots
+  int items = d.Mm;                                          // the chunk's rhs rows: GN1 slots
   if (bi.n > 0) {
     for (int it = wl; it < items; it += UPD_WARPS) {
-      int a = it < d.Mm ? ARR_N1 : ARR_Q0;
-      int r = it < d.Mm ? it : it - d.Mm;
+      int a = ARR_N1;
+      int r = it;
       long long row = slot_row(d, wb, w, bi, 1, r);
       if (row < 0 || row >= d.n_rows[1]) continue;
       SlotGrad<VEC> sg;
