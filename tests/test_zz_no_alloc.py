@@ -29,7 +29,7 @@ def test_static_entry_point_matches_context_entry_point_twice_in_a_row():
              lr=0.1, relation_lr=None, op="none", comp="dot", loss="softmax", B=1000, nb=50, nu=50, name="na")
     W0 = rng.standard_normal((N, D)).astype(np.float32)
     G0 = rng.random(N).astype(np.float32)
-    rig = Rig(c, W0, G0, k=4)                              # owns a context (sort capacity 24000 rows)
+    rig = Rig(c, W0, G0, k=5)                              # owns a context (sort capacity 20000 rows)
     nat = rig.trainer._context(rig.model, 1000)
     Wa, Ga = rig.W_lhs, rig.opt_l.sum_for(rig.W_lhs)       # updated through the context
     Wb, Gb = Wa.clone(), Ga.clone()                        # updated through the static entry point
