@@ -475,7 +475,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
-    ap.add_argument("--k", type=int, default=8, help="batches in flight (1 = sequential batches)")
+    ap.add_argument("--k", type=int, default=7,
+                    help="batches in flight (1 = sequential batches); 7 makes the 20 contraction tiles per batch of "
+                         "workload c3 fill 140 of the 148 SMs in one round")
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32x3", "tf32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--resident", type=int, default=0,

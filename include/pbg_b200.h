@@ -177,7 +177,7 @@ int pbg_row_adagrad(pbg_context *ctx, float *emb, float *state, int64_t num_rows
  * code that cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply.  It has no
  * counterpart in the reference (there the step is RowAdagrad.step on tensors PyTorch allocates).
  * It takes no context and calls no allocating routine: its scratch (sort buffers, digit
- * counters, error word; about 0.5 MB) is a fixed array inside the library that every GPU which
+ * counters, error word; about 1 MB) is a fixed array inside the library that every GPU which
  * loads the library holds until the process exits.
  *   - at most 16384 gradient rows per call (n <= 16384), dim a multiple of 4 up to 2048; larger
  *     sizes return PBG_ERR_TOO_LARGE / PBG_ERR_UNSUPPORTED and touch nothing;

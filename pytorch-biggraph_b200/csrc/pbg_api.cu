@@ -185,12 +185,11 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   }
   oCoef[0] = take(nN * 4); oCoef[1] = take(nN * 4); oCoef[2] = take(nQ * 4); oCoef[3] = take(nQ * 4);
   size_t oRel = take(nblk * 8 * (size_t)cfg->dim * 4);
-  int swarps = pbg_sort_warps((int)nocc);
   size_t oK[2][2], oV[2][2], oH[2];
   for (int s = 0; s < 2; ++s) {
     oK[s][0] = take((size_t)nocc * 8); oK[s][1] = take((size_t)nocc * 8);
     oV[s][0] = take((size_t)nocc * 4); oV[s][1] = take((size_t)nocc * 4);
-    oH[s] = take((size_t)256 * swarps * 4);
+    oH[s] = take(pbg_sort_hist_entries((int)nocc) * 4);
   }
   size_t oSum = take(4 * sizeof(double)), oErr = take(256);
   size_t oPsum = take((size_t)nocc * c->Dp * 4), oHub = take(((size_t)nocc / 8 + 64) * 8), oHubCnt = take(256);

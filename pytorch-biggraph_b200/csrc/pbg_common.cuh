@@ -192,11 +192,12 @@ __device__ __forceinline__ float4 tf32_hi4(float4 v) { return make_float4(tf32_h
 struct SortPlan {
   unsigned long long *keys[2];
   unsigned int *vals[2];
-  unsigned int *hist;     // [256][warps]
+  unsigned int *hist;     // pbg_sort_hist_entries(max_n) counters
   int max_n;              // capacity
   int result;             // which of keys[]/vals[] holds the sorted output after pbg_sort
 };
 int pbg_sort_warps(int n);
+size_t pbg_sort_hist_entries(int n);   // digit counters (unsigned int) a sort of n pairs needs
 // Stable LSD radix sort of n (key, value) pairs on `bits` low key bits; returns launches made.
 int pbg_sort(SortPlan &sp, int n, int bits, cudaStream_t st);
 

@@ -108,7 +108,7 @@ __device__ __forceinline__ float positive_score(const float4 (&a)[VEC], const fl
 }
 
 template <int VEC>
-__global__ void __launch_bounds__(32 * GATHER_WARPS) gather_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+__global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
   int lane = threadIdx.x & 31;
   long long item = (long long)blockIdx.x * GATHER_WARPS + (threadIdx.x >> 5);
   if (item >= (long long)d.nblk * d.Mm) return;

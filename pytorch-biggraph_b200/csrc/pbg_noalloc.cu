@@ -16,7 +16,7 @@
 // scratch layout (bytes): 2 x keys | 2 x values | digit counters | error word
 #define NA_KEYS_BYTES (NOALLOC_MAX_ROWS * 8)
 #define NA_VALS_BYTES (NOALLOC_MAX_ROWS * 4)
-#define NA_HIST_BYTES (256 * ((NOALLOC_MAX_ROWS + 255) / 256) * 4)
+#define NA_HIST_BYTES ((2048 * ((NOALLOC_MAX_ROWS + 255) / 256) + 2048) * 4)   // pbg_sort_hist_entries(16384) counters
 #define NA_TOTAL_BYTES (2 * NA_KEYS_BYTES + 2 * NA_VALS_BYTES + NA_HIST_BYTES + 256)
 
 static __device__ __align__(256) unsigned char pbg_noalloc_scratch[NA_TOTAL_BYTES];

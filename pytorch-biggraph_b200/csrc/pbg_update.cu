@@ -101,7 +101,8 @@ __device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC> &sg, const f
 // ------------------------------------------------------------------------------------------------
 // Segmented optimizer step over the sorted slot list.
 //
-// The list is cut into tiles of TILE slots, one warp per tile; the warp reads the keys of slots
+// The list is cut into tiles of TILE slots, one warp per tile (after issuing L2 prefetches for the
+// gradient and table rows of its slots); the warp reads the keys of slots
 // [t0-32, t0+32) and the values of [t0, t0+32) in two coalesced loads and finds segment (= table
 // row) boundaries with ballots.
 //   * a row with at most SHORT_MAX slots is handled entirely by the warp whose tile holds its first
@@ -113,7 +114,7 @@ __device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC> &sg, const f
 // RULE selects the table and its optimizer: embedding rows / RowAdagrad, or (dynamic relations)
 // operator rows / AsyncAdagrad.
 // ------------------------------------------------------------------------------------------------
-#define TILE 8
+#define TILE 4
 #define SHORT_MAX 24
 enum { RULE_EMB = 0, RULE_REL = 1 };
 
@@ -225,6 +226,22 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
   unsigned long long kB = pb < d.nocc ? keys[pb] : SENT;
   unsigned int vB = pb < d.nocc ? vals[pb] : 0u;
   if (__shfl_sync(FULL, kB, TILE - 1) < lo) return;          // tile holds only the other rule's rows
+  if (RULE == RULE_EMB) {
+    // get the rows this tile will need moving towards L2 before the dependent loads start
+#pragma unroll
+    for (int i = 0; i < TILE; ++i) {
+      unsigned long long key = __shfl_sync(FULL, kB, i);
+      if (key >= hi) break;
+      Occ oc = occ_decode(d, (int)__shfl_sync(FULL, vB, i));
+      const float *g = w.GX[oc.a] + ((size_t)oc.blk * w.grows[oc.a] + oc.r) * d.Dp;
+      int side = (!d.shared_table && key >= (unsigned long long)d.n_rows[0]) ? 1 : 0;
+      const float *wr = w.W[side] + (size_t)(side ? key - (unsigned long long)d.n_rows[0] : key) * D;
+      for (int f = lane * 32; f < D; f += 1024) {
+        asm volatile("prefetch.global.L2 [%0];" :: "l"(g + f));
+        asm volatile("prefetch.global.L2 [%0];" :: "l"(wr + f));
+      }
+    }
+  }
   int i = 0;
   while (i < TILE) {
     unsigned long long key = __shfl_sync(FULL, kB, i);
