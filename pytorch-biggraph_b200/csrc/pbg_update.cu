@@ -24,13 +24,14 @@ struct SlotGrad {
   float dotgy, inv, cf;    // cos: <g', y> and 1/|z|; l2 family: coefficient of y
   int op, cmp, D;
 
+  // gstage: the gradient row already staged in shared memory (null: read it from global memory)
   __device__ __forceinline__ void init(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
-                                       int a, int blk, int r, int b, int lane) {
+                                       int a, int blk, int r, int b, int lane, const float *gstage = nullptr) {
     D = d.D; op = d.op; cmp = d.cmp;
     size_t xr = (size_t)blk * w.xrows[a] + r, gr = (size_t)blk * w.grows[a] + r;
     y = w.X[a] + xr * d.Dp;
     ylo = d.split ? w.XL[a] + xr * d.Dp : nullptr;
-    g = w.GX[a] + gr * d.Dp;
+    g = gstage ? gstage : w.GX[a] + gr * d.Dp;
     theta = nullptr;
     if (op != PBG_OP_NONE) {
       if (!d.dynamic) {
@@ -181,11 +182,11 @@ struct RowState {
 // acc += the contribution of one slot to its row's gradient
 template <int VEC, int RULE>
 __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, const WaveBatches &wb,
-                                         const WaveBufs &w, const Occ &oc, int lane) {
+                                         const WaveBufs &w, const Occ &oc, int lane, const float *gstage = nullptr) {
   const int D = d.D;
   SlotGrad<VEC> sg;
   if (RULE == RULE_EMB) {
-    sg.init(d, wb, w, oc.a, oc.blk, oc.r, oc.b, lane);
+    sg.init(d, wb, w, oc.a, oc.blk, oc.r, oc.b, lane, gstage);
 #pragma unroll
     for (int c = 0; c < VEC; ++c) {
       int dd = c * 128 + lane * 4;
@@ -207,16 +208,38 @@ __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, 
   }
 }
 
+// Embedding rows: 4 warps per CTA, each with TILE row buffers in shared memory that it fills with
+// bulk asynchronous copies (cp.async.bulk, completion on the warp's mbarrier): the gradient rows
+// of a whole tile are in flight at once instead of one dependent 16-byte-per-lane load at a time.
+#define TILE_WARPS_EMB 4
+#define UPD_WAIT_LIMIT 4000000
+
 template <int VEC, int RULE>
-__global__ void __launch_bounds__(32 * UPD_WARPS, 2)
+__global__ void __launch_bounds__(32 * (RULE == RULE_EMB ? TILE_WARPS_EMB : UPD_WARPS), RULE == RULE_EMB ? 3 : 2)
 tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long long *__restrict__ keys,
                    const unsigned int *__restrict__ vals, float lr, float *__restrict__ psum,
                    long long *__restrict__ hublist, int *__restrict__ hubcnt) {
+  constexpr int WARPS = RULE == RULE_EMB ? TILE_WARPS_EMB : UPD_WARPS;
+  constexpr bool STAGED = RULE == RULE_EMB;
+  extern __shared__ __align__(128) float stage_all[];        // [WARPS][TILE][Dp] (STAGED only)
+  __shared__ __align__(8) unsigned long long sbar[WARPS];
   const unsigned FULL = 0xffffffffu;
   const unsigned long long SENT = ~0ull;
   int lane = threadIdx.x & 31;
-  long long t0 = ((long long)blockIdx.x * UPD_WARPS + (threadIdx.x >> 5)) * TILE;
+  const int wl = threadIdx.x >> 5;
+  long long t0 = ((long long)blockIdx.x * WARPS + wl) * TILE;
   if (t0 >= d.nocc) return;
+  float *stage = STAGED ? stage_all + (size_t)wl * TILE * d.Dp : nullptr;
+  const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&sbar[wl]);
+  uint32_t phase = 0;
+  int staged_lo = 0, staged_hi = 0;                           // window slots whose rows are in `stage`
+  if (STAGED) {
+    if (lane == 0) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar));
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+  }
   const int D = d.D;
   const float invD = 1.0f / (float)D;
   const unsigned long long lo = RULE == RULE_EMB ? 0ull : d.key_rel_base;
@@ -226,21 +249,46 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
   unsigned long long kB = pb < d.nocc ? keys[pb] : SENT;
   unsigned int vB = pb < d.nocc ? vals[pb] : 0u;
   if (__shfl_sync(FULL, kB, TILE - 1) < lo) return;          // tile holds only the other rule's rows
+  // Copies the gradient rows of window slots j0 .. j0+cnt-1 (cnt <= TILE) into the stage buffers and
+  // waits for them; the wait is bounded (bit 1 of the error word when it runs out).
+  auto stage_rows = [&](int j0, int cnt) {
+    __syncwarp();                                            // everyone is done with the old rows
+    unsigned int v = __shfl_sync(FULL, vB, j0 + (lane < cnt ? lane : 0));
+    if (lane == 0) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"((uint32_t)(cnt * d.D * 4)) : "memory");
+    }
+    __syncwarp();
+    if (lane < cnt) {
+      Occ oc = occ_decode(d, (int)v);
+      const float *g = w.GX[oc.a] + ((size_t)oc.blk * w.grows[oc.a] + oc.r) * d.Dp;
+      uint32_t dst = (uint32_t)__cvta_generic_to_shared(stage + (size_t)lane * d.Dp);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   :: "r"(dst), "l"(g), "r"((uint32_t)(d.D * 4)), "r"(bar) : "memory");
+    }
+    bool done = false;
+    for (int it = 0; it < UPD_WAIT_LIMIT && !done; ++it) {
+      uint32_t ok;
+      asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                   : "=r"(ok) : "r"(bar), "r"(phase) : "memory");
+      done = ok != 0;
+    }
+    if (!done && lane == 0) atomicOr(w.errflag, 2);
+    phase ^= 1u;
+    staged_lo = j0; staged_hi = j0 + cnt;
+  };
   if (RULE == RULE_EMB) {
     // get the rows this tile will need moving towards L2 before the dependent loads start
 #pragma unroll
     for (int i = 0; i < TILE; ++i) {
       unsigned long long key = __shfl_sync(FULL, kB, i);
       if (key >= hi) break;
-      Occ oc = occ_decode(d, (int)__shfl_sync(FULL, vB, i));
-      const float *g = w.GX[oc.a] + ((size_t)oc.blk * w.grows[oc.a] + oc.r) * d.Dp;
       int side = (!d.shared_table && key >= (unsigned long long)d.n_rows[0]) ? 1 : 0;
       const float *wr = w.W[side] + (size_t)(side ? key - (unsigned long long)d.n_rows[0] : key) * D;
-      for (int f = lane * 32; f < D; f += 1024) {
-        asm volatile("prefetch.global.L2 [%0];" :: "l"(g + f));
-        asm volatile("prefetch.global.L2 [%0];" :: "l"(wr + f));
-      }
+      for (int f = lane * 32; f < D; f += 1024) asm volatile("prefetch.global.L2 [%0];" :: "l"(wr + f));
     }
+    int nvalid = __popc(__ballot_sync(FULL, lane < TILE && kB < hi));
+    if (nvalid > 0) stage_rows(0, nvalid);
   }
   int i = 0;
   while (i < TILE) {
@@ -283,7 +331,15 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
       }
       if (!in) break;
       if (oc.b != cur_b) { cur_b = oc.b; run_start = j; }
-      add_slot<VEC, RULE>(acc, d, wb, w, oc, lane);
+      const float *gs = nullptr;
+      if (STAGED) {
+        if (j >= staged_hi) {                                 // a short row that runs past the tile
+          int left = i + nproc - j;
+          stage_rows(j, left < TILE ? left : TILE);
+        }
+        gs = stage + (size_t)(j - staged_lo) * d.Dp;
+      }
+      add_slot<VEC, RULE>(acc, d, wb, w, oc, lane, gs);
     }
     if (!hub) rs.store(D, lane);
     else if (head_here && lane == 0) hublist[atomicAdd(hubcnt, 1)] = t0 + i;
@@ -417,6 +473,8 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   int launches = 0;
   long long warps = ((long long)d.nocc + TILE - 1) / TILE;
   int ctas = (int)((warps + UPD_WARPS - 1) / UPD_WARPS);
+  int ctas_emb = (int)((warps + TILE_WARPS_EMB - 1) / TILE_WARPS_EMB);
+  size_t stage_smem = (size_t)TILE_WARPS_EMB * TILE * d.Dp * sizeof(float);
   const int hub_ctas = 296;
   size_t hub_smem = (size_t)UPD_WARPS * VEC * 128 * sizeof(float);
   static bool attr_done[2] = {false, false};
@@ -427,10 +485,12 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   }
   if (!attr_done[0]) {
     cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem);
+    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
     attr_done[0] = true;
   }
   cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
-  tile_update_kernel<VEC, RULE_EMB><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  tile_update_kernel<VEC, RULE_EMB><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   hub_update_kernel<VEC, RULE_EMB><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   launches += 2;
   if (has_op) {
