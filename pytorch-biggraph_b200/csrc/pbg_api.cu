@@ -158,7 +158,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
   size_t oX[4], oAux[4], oG[4], oS[2], oSpos[2], oCoef[4], oLoss[2], oViol[2], oXL[4] = {0, 0, 0, 0}, oSL[2] = {0, 0};
-  const bool split = cfg->precision == PBG_PREC_TF32X3;
+  const bool split = false;   // TF32X3 splits operands inside the contraction kernel: no low-part arrays
   oX[0] = take(nN * c->Dp * 4); oX[1] = take(nN * c->Dp * 4);
   oAux[0] = take(nN * 4); oAux[1] = take(nN * 4);
   if (dyn) { oX[2] = take(nQ * c->Dp * 4); oX[3] = take(nQ * c->Dp * 4); oAux[2] = take(nQ * 4); oAux[3] = take(nQ * 4); }
@@ -309,7 +309,7 @@ static int bind_bucket(pbg_context *c, const pbg_bucket *bk, WaveDims &d, WaveBu
   d.batch_negs = cfg.num_batch_negs > 0;
   d.neg_enabled[0] = !cfg.disable_lhs_negs; d.neg_enabled[1] = !cfg.disable_rhs_negs;
   d.num_batch_negs = cfg.num_batch_negs; d.spb = c->spb; d.margin = cfg.margin;
-  d.split = cfg.precision == PBG_PREC_TF32X3;
+  d.split = 0;
   d.n_rows[0] = bk->lhs_rows; d.n_rows[1] = bk->rhs_rows;
   d.shared_table = bk->lhs_emb == bk->rhs_emb;
   if (d.shared_table && bk->lhs_rows != bk->rhs_rows) return fail(c, PBG_ERR_BAD_ARGUMENT, "shared table with different row counts");

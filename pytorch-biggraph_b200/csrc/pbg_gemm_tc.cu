@@ -17,8 +17,10 @@
 // K-major operands use the 128-byte swizzle; MN-major tf32 operands must use the 128-byte swizzle
 // with 32-byte atoms (descriptor layout type 1, TMA swizzle 128B_ATOM_32B), 32 x 32 element boxes.
 //
-// TF32X3: every operand exists as hi = tf32(x) and lo = x - hi (written by the producing kernels);
-// the tile is lo.hi + hi.lo + hi.hi accumulated in fp32, which restores fp32-level accuracy.
+// TF32X3: the fp32 tiles TMA brings in are split in shared memory by the four epilogue warps
+// (idle during the main loop): hi = tf32(x) in place, lo = x - hi into a second buffer of the
+// stage; the tile is lo.hi + hi.lo + hi.hi accumulated in fp32, which restores fp32-level
+// accuracy while every operand crosses HBM/L2 once, as plain fp32.
 //
 // Every wait on an mbarrier is bounded; when one runs out the CTA raises bit 1 of the error word,
 // stops issuing work, releases its tensor memory and returns.  Every TMA load is CTA-local.
@@ -29,7 +31,7 @@
 #define TC_THREADS 192
 #define TC_WAIT_LIMIT 4000000
 
-struct TcMaps { CUtensorMap a[2][2]; CUtensorMap b[2][2]; };   // [problem][0 = hi, 1 = lo]
+struct TcMaps { CUtensorMap a[2]; CUtensorMap b[2]; };   // [problem]
 
 struct TcGeom {
   int M, N, K;          // output rows, columns, contraction length (per block)
@@ -68,10 +70,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
 template <bool A_MN, bool B_MN, int NTERMS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBatches wb, int *errflag) {
-  constexpr int PARTS = NTERMS == 3 ? 2 : 1;
-  constexpr int STAGES = NTERMS == 3 ? 2 : 4;
+  constexpr bool SPLIT = NTERMS == 3;
+  constexpr int STAGES = SPLIT ? 2 : 4;
   constexpr uint32_t A_BYTES = 128 * 128, B_BYTES = 256 * 128;          // one 32-k tile of 128 / 256 rows
-  constexpr uint32_t STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
+  constexpr uint32_t RAW_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t STAGE_BYTES = SPLIT ? 2 * RAW_BYTES : RAW_BYTES;   // [A hi][B hi] ([A lo][B lo])
   const int p = blockIdx.z & 1, blk = blockIdx.z >> 1;
   {
     BlockInfo bi = block_info(d, wb, blk);
@@ -83,16 +86,19 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+  __shared__ __align__(8) unsigned long long bars[3 * STAGES + 1];
   __shared__ uint32_t tmem_base_s;
   __shared__ int failed;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = smem_u32(&bars[0]);
-  auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  const uint32_t acc_bar = bar0 + 8u * (2 * STAGES);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };                 // TMA landed
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };     // MMAs have read the stage
+  auto conv_bar = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };  // hi / lo written (SPLIT)
+  const uint32_t acc_bar = bar0 + 8u * (3 * STAGES);
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2 * STAGES + 1; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar0 + 8u * i));
+    for (int i = 0; i < 2 * STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar0 + 8u * i));
+    for (int i = 0; i < STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" :: "r"(conv_bar(i)));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(acc_bar));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     failed = 0;
   }
@@ -106,7 +112,8 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   const uint32_t tmem = tmem_base_s;
   const int nkb = (g.K + 31) / 32;
   const int b_atoms = (g.BN + 31) / 32;
-  const uint32_t stage_tx = PARTS * (A_BYTES + (B_MN ? (uint32_t)b_atoms * 4096u : (uint32_t)g.BN * 128u));
+  const uint32_t b_used = B_MN ? (uint32_t)b_atoms * 4096u : (uint32_t)g.BN * 128u;
+  const uint32_t stage_tx = A_BYTES + b_used;
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer ----------------
@@ -117,17 +124,13 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
       asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(fb), "r"(stage_tx) : "memory");
       unsigned char *st = smem + (size_t)s * STAGE_BYTES;
       int k0 = it * 32;
-#pragma unroll
-      for (int part = 0; part < PARTS; ++part) {
-        uint32_t dA = smem_u32(st + part * A_BYTES);
-        uint32_t dB = smem_u32(st + PARTS * A_BYTES + part * B_BYTES);
-        if (!A_MN) tma_load_3d(dA, &maps.a[p][part], k0, m0, blk, fb);
-        else
-          for (int mb = 0; mb < 4; ++mb) tma_load_3d(dA + mb * 4096, &maps.a[p][part], m0 + mb * 32, k0, blk, fb);
-        if (!B_MN) tma_load_3d(dB, &maps.b[p][part], k0, n0, blk, fb);
-        else
-          for (int nb = 0; nb < b_atoms; ++nb) tma_load_3d(dB + nb * 4096, &maps.b[p][part], n0 + nb * 32, k0, blk, fb);
-      }
+      uint32_t dA = smem_u32(st), dB = smem_u32(st + A_BYTES);
+      if (!A_MN) tma_load_3d(dA, &maps.a[p], k0, m0, blk, fb);
+      else
+        for (int mb = 0; mb < 4; ++mb) tma_load_3d(dA + mb * 4096, &maps.a[p], m0 + mb * 32, k0, blk, fb);
+      if (!B_MN) tma_load_3d(dB, &maps.b[p], k0, n0, blk, fb);
+      else
+        for (int nb = 0; nb < b_atoms; ++nb) tma_load_3d(dB + nb * 4096, &maps.b[p], n0 + nb * 32, k0, blk, fb);
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer ----------------
@@ -137,18 +140,18 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
     bool ok = true;
     for (int it = 0; it < nkb && ok; ++it) {
       int s = it % STAGES;
-      if (!mbar_wait(full_bar(s), (it / STAGES) & 1, errflag)) { failed = 1; ok = false; break; }
+      if (!mbar_wait(SPLIT ? conv_bar(s) : full_bar(s), (it / STAGES) & 1, errflag)) { failed = 1; ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       unsigned char *st = smem + (size_t)s * STAGE_BYTES;
-      uint32_t aH = smem_u32(st), aL = smem_u32(st + A_BYTES);
-      uint32_t bH = smem_u32(st + PARTS * A_BYTES), bL = smem_u32(st + PARTS * A_BYTES + B_BYTES);
+      uint32_t aH = smem_u32(st), bH = smem_u32(st + A_BYTES);
+      uint32_t aL = aH + RAW_BYTES, bL = bH + RAW_BYTES;
 #pragma unroll
       for (int k8 = 0; k8 < 4; ++k8) {
         uint32_t ao = A_MN ? k8 * 1024 : k8 * 32, bo = B_MN ? k8 * 1024 : k8 * 32;
         uint64_t dAh = A_MN ? smem_desc(aH + ao, 4096, 512, 1) : smem_desc(aH + ao, 0, 1024, 2);
         uint64_t dBh = B_MN ? smem_desc(bH + bo, 4096, 512, 1) : smem_desc(bH + bo, 0, 1024, 2);
         uint32_t acc = (it > 0 || k8 > 0) ? 1u : 0u;
-        if (NTERMS == 3) {
+        if (SPLIT) {
           uint64_t dAl = A_MN ? smem_desc(aL + ao, 4096, 512, 1) : smem_desc(aL + ao, 0, 1024, 2);
           uint64_t dBl = B_MN ? smem_desc(bL + bo, 4096, 512, 1) : smem_desc(bL + bo, 0, 1024, 2);
           asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
@@ -164,7 +167,27 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(empty_bar(s)) : "memory");
     }
     if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(acc_bar) : "memory");
-  } else if (warp >= 2) {
+  }
+  if (SPLIT && warp >= 2) {
+    // ---------------- hi / lo split of every landed stage (the epilogue warps) ----------------
+    const int ct = threadIdx.x - 64;                              // 0..127
+    const uint32_t nchunks = stage_tx / 16;
+    for (int it = 0; it < nkb; ++it) {
+      int s = it % STAGES;
+      if (!mbar_wait(full_bar(s), (it / STAGES) & 1, errflag)) { failed = 1; break; }
+      unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+      for (uint32_t c = ct; c < nchunks; c += 128) {
+        float4 *hi = reinterpret_cast<float4 *>(st + (size_t)c * 16);
+        float4 v = *hi;
+        float4 h = tf32_hi4(v);
+        *hi = h;
+        *reinterpret_cast<float4 *>(st + RAW_BYTES + (size_t)c * 16) = v - h;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(conv_bar(s)) : "memory");
+    }
+  }
+  if (warp >= 2) {
     // ---------------- epilogue ----------------
     bool ok = mbar_wait(acc_bar, 0, errflag);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -275,28 +298,23 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
   bool ok = true;
   for (int p = 0; p < 2; ++p) {
     int q = ARR_Q0 + p, n = ARR_N0 + p;
-    for (int part = 0; part < (pl->nterms == 3 ? 2 : 1); ++part) {
-      const float *Xq = part ? w.XL[q] : w.X[q], *Xn = part ? w.XL[n] : w.X[n];
-      const float *T = part ? w.SL[p] : w.S[p];
-      long long qblk = (long long)w.xrows[q] * d.Dp, nblk_s = (long long)w.xrows[n] * d.Dp, tblk = (long long)d.Pm * d.Ms;
-      // score: A = Q (K-major, k = D), B = N (K-major)
-      ok &= encode3(&pl->score.a[p][part], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 128, false);
-      ok &= encode3(&pl->score.b[p][part], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, pl->bn_score, false);
-      if (pl->dynamic) {
-        // grad Q: A = T (K-major, k = Mm), B = N (MN-major: k rows = Mm, contiguous D)
-        ok &= encode3(&pl->gradq.a[p][part], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 128, false);
-        ok &= encode3(&pl->gradq.b[p][part], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, 32, true);
-        // grad N: A = T^T (MN-major: k rows = Pm, contiguous Mm), B = Q (MN-major: k rows = Pm, contiguous D)
-        ok &= encode3(&pl->gradn.a[p][part], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 32, true);
-        ok &= encode3(&pl->gradn.b[p][part], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 32, true);
-      } else {
-        // merged: side p: A = A[p] (K-major, k = Mm), B = the other side's operand rows (MN-major)
-        const float *Am = part ? w.AL[p] : w.A[p];
-        int o = ARR_N0 + (1 - p);
-        const float *Xo = part ? w.XL[o] : w.X[o];
-        ok &= encode3(&pl->gradm.a[p][part], Am, d.Mm, d.Mm, nblk_max, w.Ma, (long long)d.Mm * w.Ma, 32, 128, false);
-        ok &= encode3(&pl->gradm.b[p][part], Xo, d.D, w.xrows[o], nblk_max, d.Dp, (long long)w.xrows[o] * d.Dp, 32, 32, true);
-      }
+    const float *Xq = w.X[q], *Xn = w.X[n], *T = w.S[p];
+    long long qblk = (long long)w.xrows[q] * d.Dp, nblk_s = (long long)w.xrows[n] * d.Dp, tblk = (long long)d.Pm * d.Ms;
+    // score: A = Q (K-major, k = D), B = N (K-major)
+    ok &= encode3(&pl->score.a[p], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 128, false);
+    ok &= encode3(&pl->score.b[p], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, pl->bn_score, false);
+    if (pl->dynamic) {
+      // grad Q: A = T (K-major, k = Mm), B = N (MN-major: k rows = Mm, contiguous D)
+      ok &= encode3(&pl->gradq.a[p], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 128, false);
+      ok &= encode3(&pl->gradq.b[p], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, 32, true);
+      // grad N: A = T^T (MN-major: k rows = Pm, contiguous Mm), B = Q (MN-major: k rows = Pm, contiguous D)
+      ok &= encode3(&pl->gradn.a[p], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 32, true);
+      ok &= encode3(&pl->gradn.b[p], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 32, true);
+    } else {
+      // merged: side p: A = A[p] (K-major, k = Mm), B = the other side's operand rows (MN-major)
+      int o = ARR_N0 + (1 - p);
+      ok &= encode3(&pl->gradm.a[p], w.A[p], d.Mm, d.Mm, nblk_max, w.Ma, (long long)d.Mm * w.Ma, 32, 128, false);
+      ok &= encode3(&pl->gradm.b[p], w.X[o], d.D, w.xrows[o], nblk_max, d.Dp, (long long)w.xrows[o] * d.Dp, 32, 32, true);
     }
   }
   if (!ok) { delete pl; return nullptr; }
@@ -309,7 +327,7 @@ template <bool A_MN, bool B_MN>
 static void launch_tc(const TcMaps &maps, const TcGeom &g, int nterms, const WaveDims &d, const WaveBatches &wb, int *errflag,
                       cudaStream_t st) {
   dim3 grid((g.N + g.BN - 1) / g.BN, (g.M + 127) / 128, d.nblk * 2);
-  size_t smem = 2 * 2 * (128 * 128 + 256 * 128) + 1024;       // 2 stages x (hi, lo) or 4 stages x hi
+  size_t smem = 4 * (128 * 128 + 256 * 128) + 1024;           // 2 stages x (hi, lo) or 4 stages x raw
   if (nterms == 3) {
     static bool done = false;
     if (!done) { cudaFuncSetAttribute(tc_gemm_kernel<A_MN, B_MN, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
