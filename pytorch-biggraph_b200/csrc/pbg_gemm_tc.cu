@@ -12,13 +12,13 @@
 //               shared-memory stages, completion on an mbarrier per stage
 //   warp 1      allocates tensor memory, issues tcgen05.mma.kind::tf32 (one elected lane) and
 //               commits to the stage's "empty" barrier / the final "accumulator ready" barrier
+//   warps 2-9   TF32X3 only: split every landed stage into hi / lo (see below)
 //   warps 2-5   epilogue: tcgen05.ld 32 columns at a time (each warp its 32 TMEM lanes = 32
 //               rows), comparator epilogue for scores, 128-byte row-segment stores
 // K-major operands use the 128-byte swizzle; MN-major tf32 operands must use the 128-byte swizzle
 // with 32-byte atoms (descriptor layout type 1, TMA swizzle 128B_ATOM_32B), 32 x 32 element boxes.
 //
-// TF32X3: the fp32 tiles TMA brings in are split in shared memory by the four epilogue warps
-// (idle during the main loop): hi = tf32(x) in place, lo = x - hi into a second buffer of the
+// TF32X3: the fp32 tiles TMA brings in are split in shared memory by eight warps: hi = tf32(x) in place, lo = x - hi into a second buffer of the
 // stage; the tile is lo.hi + hi.lo + hi.hi accumulated in fp32, which restores fp32-level
 // accuracy while every operand crosses HBM/L2 once, as plain fp32.
 //
@@ -28,7 +28,8 @@
 
 #include "pbg_common.cuh"
 
-#define TC_THREADS 192
+#define TC_THREADS 320          // warp 0 TMA, warp 1 MMA, warps 2-9 split operands, warps 2-5 also run the epilogue
+#define TC_SPLIT_THREADS 256
 #define TC_WAIT_LIMIT 4000000
 
 struct TcMaps { CUtensorMap a[2]; CUtensorMap b[2]; };   // [problem]
@@ -97,7 +98,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   const uint32_t acc_bar = bar0 + 8u * (3 * STAGES);
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2 * STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar0 + 8u * i));
-    for (int i = 0; i < STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" :: "r"(conv_bar(i)));
+    for (int i = 0; i < STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(conv_bar(i)), "r"(TC_SPLIT_THREADS));
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(acc_bar));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     failed = 0;
@@ -170,24 +171,34 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   }
   if (SPLIT && warp >= 2) {
     // ---------------- hi / lo split of every landed stage (the epilogue warps) ----------------
-    const int ct = threadIdx.x - 64;                              // 0..127
+    const int ct = threadIdx.x - 64;                              // 0..255
     const uint32_t nchunks = stage_tx / 16;
     for (int it = 0; it < nkb; ++it) {
       int s = it % STAGES;
       if (!mbar_wait(full_bar(s), (it / STAGES) & 1, errflag)) { failed = 1; break; }
       unsigned char *st = smem + (size_t)s * STAGE_BYTES;
-      for (uint32_t c = ct; c < nchunks; c += 128) {
-        float4 *hi = reinterpret_cast<float4 *>(st + (size_t)c * 16);
-        float4 v = *hi;
-        float4 h = tf32_hi4(v);
-        *hi = h;
-        *reinterpret_cast<float4 *>(st + RAW_BYTES + (size_t)c * 16) = v - h;
+      for (uint32_t c0 = ct; c0 < nchunks; c0 += 4 * TC_SPLIT_THREADS) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint32_t c = c0 + u * TC_SPLIT_THREADS;
+          if (c < nchunks) v[u] = *reinterpret_cast<const float4 *>(st + (size_t)c * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          uint32_t c = c0 + u * TC_SPLIT_THREADS;
+          if (c < nchunks) {
+            float4 h = tf32_hi4(v[u]);
+            *reinterpret_cast<float4 *>(st + (size_t)c * 16) = h;
+            *reinterpret_cast<float4 *>(st + RAW_BYTES + (size_t)c * 16) = v[u] - h;
+          }
+        }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(conv_bar(s)) : "memory");
     }
   }
-  if (warp >= 2) {
+  if (warp >= 2 && warp < 6) {
     // ---------------- epilogue ----------------
     bool ok = mbar_wait(acc_bar, 0, errflag);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
