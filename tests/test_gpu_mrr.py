@@ -1,0 +1,48 @@
+"""End-to-end quality: held-out MRR on planted-structure graphs after training on the GPU path is
+within 0.01 of what the reference CPU trainer reaches (tests/golden/mrr_planted.json, recorded by
+tests/golden/make_mrr_golden.py from the reference itself; mean over three negative-sampling
+seeds, whose own spread is about +-0.005)."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from golden_util import GOLDEN
+from mrr_util import CASES, COMMON, epoch_order, mrr_rhs, planted_graph
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("k,precision", [(1, "fp32"), (1, "tf32x3"), (8, "tf32x3")])
+@pytest.mark.parametrize("case", sorted(CASES))
+def test_held_out_mrr_matches_reference_trainer(case, k, precision):
+    import torchbiggraph_b200 as T
+    with open(os.path.join(GOLDEN, "mrr_planted.json")) as f:
+        want = json.load(f)["mrr"][case]
+    c = CASES[case]
+    (lhs, rhs, rel), test, W0 = planted_graph(case)
+    cfg = T.ConfigSchema(entities={"e": T.EntitySchema()}, relations=[T.RelationSchema("r", "e", "e", operator=c["op"])],
+                         dimension=c["D"], comparator=COMMON["comp"], loss_fn=COMMON["loss"], lr=COMMON["lr"],
+                         batch_size=COMMON["batch"], num_batch_negs=COMMON["nb"], num_uniform_negs=COMMON["nu"],
+                         dynamic_relations=c["dyn"], num_dynamic_rels=c["R"] if c["dyn"] else 0,
+                         precision=precision, batches_in_flight=k)
+    model = T.make_model(cfg, "cuda")
+    trainer = T.B200Trainer(T.make_optimizer(cfg, model.parameters(), False),
+                            T.LOSS_FUNCTIONS.get_class(COMMON["loss"])(margin=0.1), [1.0])
+    W = torch.tensor(W0, device="cuda")
+    model.set_embeddings("e", T.Side.LHS, W)
+    model.set_embeddings("e", T.Side.RHS, W)
+    trainer.partitioned_optimizers["e", 0] = T.make_optimizer(cfg, [W], True)
+    trainer.seed = 17
+    B = COMMON["batch"]
+    for ep in range(c["epochs"]):
+        order = epoch_order(len(lhs), ep)
+        edges = T.EdgeList(T.EntityList.from_tensor(torch.tensor(lhs[order])), T.EntityList.from_tensor(torch.tensor(rhs[order])),
+                           torch.tensor(rel[order]) if c["dyn"] else torch.tensor(0))
+        stats = T.process_in_batches(B, model, trainer, edges.to("cuda"))
+        assert stats.count == len(order) and np.isfinite(stats.metrics["loss"])
+    th = (model.lhs_op_table if c["dyn"] else model.rhs_op_table).cpu().numpy()
+    got = mrr_rhs(case, W.cpu().numpy(), th, test)
+    assert abs(got - want) <= 0.01, f"MRR {got:.4f} vs reference {want:.4f}"
