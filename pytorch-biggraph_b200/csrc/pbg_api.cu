@@ -128,6 +128,9 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     return fail(c, PBG_ERR_BAD_ARGUMENT, "negative or zero size in config");
   if (cfg->batches_in_flight < 1 || cfg->batches_in_flight > PBG_KMAX)
     return fail(c, PBG_ERR_BAD_ARGUMENT, "batches_in_flight must be in [1, %d]", PBG_KMAX);
+  if ((size_t)cfg->batches_in_flight * ((cfg->dim + 127) / 128) * 512 > 227 * 1024)
+    return fail(c, PBG_ERR_TOO_LARGE, "batches_in_flight %d with dimension %d: the per-batch totals of a hub row exceed shared memory (at most 28 batches above dimension 1024)",
+                cfg->batches_in_flight, cfg->dim);
   if (cfg->precision != PBG_PREC_FP32 && !pbg_tc_available())
     return fail(c, PBG_ERR_UNSUPPORTED, "tensor-core precision tiers are not built into this library");
   if (cfg->precision < PBG_PREC_FP32 || cfg->precision > PBG_PREC_TF32) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown precision %d", cfg->precision);

@@ -347,40 +347,51 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
   }
 }
 
-// One CTA per hub row: adds the partial rows the tile warps left in psum, batch by batch.  A batch's
-// slots [q, eb) were summed in runs that start at q and at every multiple of TILE inside (q, eb).
+// One CTA per hub row.  Its slots [head, end) are in batch order; every thread looks at a strided
+// share of them to find where each batch starts (bstart[]), then warp w adds up the partial rows of
+// batches w, w+8, ... (a batch's slots [q, eb) were summed by the tile warps in runs that start at
+// q and at every multiple of TILE inside (q, eb)) into tot[batch][], and warp 0 applies the
+// optimizer steps in batch order.  All sums run in a fixed order.
 template <int VEC, int RULE>
 __global__ void __launch_bounds__(32 * UPD_WARPS)
 hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long long *__restrict__ keys,
                   const unsigned int *__restrict__ vals, float lr, const float *__restrict__ psum,
                   const long long *__restrict__ hublist, const int *__restrict__ hubcnt) {
-  extern __shared__ __align__(16) float red[];               // [UPD_WARPS][VEC * 128]
-  __shared__ float wsum[UPD_WARPS];
+  extern __shared__ __align__(16) float tot[];               // [k][VEC * 128]
+  __shared__ long long bstart[PBG_KMAX + 1];
+  __shared__ long long seg_end;
   const int lane = threadIdx.x & 31, wl = threadIdx.x >> 5;
   const int D = d.D;
   const float invD = 1.0f / (float)D;
   const int nh = *hubcnt;
   for (int h = blockIdx.x; h < nh; h += gridDim.x) {
-    long long head = hublist[h];
-    unsigned long long key = keys[head];
-    long long a = head + 1, b = d.nocc;
-    while (a < b) { long long m = (a + b) >> 1; if (keys[m] <= key) a = m + 1; else b = m; }
-    const long long end = a;
-    // warp 0 owns the row (same register layout as the tile warps); the others only add partials
-    RowState<VEC, RULE> rs;
-    if (wl == 0) rs.load(d, w, key, lane);
-    long long q = head;
-    while (q < end) {
-      int bq = occ_decode(d, (int)vals[q]).b;
-      long long x = q + 1, y = end;
-      while (x < y) { long long m = (x + y) >> 1; if (occ_decode(d, (int)vals[m]).b <= bq) x = m + 1; else y = m; }
-      const long long eb = x;
+    const long long head = hublist[h];
+    const unsigned long long key = keys[head];
+    if (threadIdx.x == 0) {
+      long long a = head + 1, b = d.nocc;
+      while (a < b) { long long m = (a + b) >> 1; if (keys[m] <= key) a = m + 1; else b = m; }
+      seg_end = a;
+    }
+    for (int i = threadIdx.x; i <= PBG_KMAX; i += blockDim.x) bstart[i] = -1;
+    __syncthreads();
+    const long long end = seg_end;
+    for (long long q = head + threadIdx.x; q < end; q += blockDim.x) {
+      int bq = (int)(vals[q] / (unsigned int)d.spb);
+      if (q == head || (int)(vals[q - 1] / (unsigned int)d.spb) != bq) bstart[bq] = q;   // first slot of batch bq
+    }
+    __syncthreads();
+    // ---- per-batch totals ----
+    for (int bq = wl; bq < d.k; bq += UPD_WARPS) {
+      long long q = bstart[bq];
+      if (q < 0) continue;
+      long long eb = end;
+      for (int nb = bq + 1; nb < d.k; ++nb) if (bstart[nb] >= 0) { eb = bstart[nb]; break; }
       long long ftb = (q / TILE + 1) * TILE;
       long long nruns = 1 + (eb > ftb ? (eb - 1 - ftb) / TILE + 1 : 0);
       float4 acc[VEC];
 #pragma unroll
       for (int c = 0; c < VEC; ++c) acc[c] = f4zero();
-      for (long long r = wl; r < nruns; r += UPD_WARPS) {
+      for (long long r = 0; r < nruns; ++r) {
         long long start = r == 0 ? q : ftb + (r - 1) * TILE;
         const float *src = psum + (size_t)start * d.Dp;
 #pragma unroll
@@ -390,24 +401,24 @@ hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long lo
         }
       }
 #pragma unroll
-      for (int c = 0; c < VEC; ++c) st4(&red[(size_t)wl * VEC * 128 + c * 128 + lane * 4], acc[c]);
-      __syncthreads();
-      if (wl == 0) {
+      for (int c = 0; c < VEC; ++c) st4(&tot[(size_t)bq * VEC * 128 + c * 128 + lane * 4], acc[c]);
+    }
+    __syncthreads();
+    // ---- optimizer steps in batch order ----
+    if (wl == 0) {
+      RowState<VEC, RULE> rs;
+      rs.load(d, w, key, lane);
+      for (int bq = 0; bq < d.k; ++bq) {
+        if (bstart[bq] < 0) continue;
         float4 g[VEC];
 #pragma unroll
-        for (int c = 0; c < VEC; ++c) {
-          g[c] = f4zero();
-#pragma unroll
-          for (int k = 0; k < UPD_WARPS; ++k) g[c] = g[c] + ld4(&red[(size_t)k * VEC * 128 + c * 128 + lane * 4]);
-        }
+        for (int c = 0; c < VEC; ++c) g[c] = ld4(&tot[(size_t)bq * VEC * 128 + c * 128 + lane * 4]);
         rs.step(g, lr, invD);
       }
-      __syncthreads();
-      q = eb;
+      rs.store(D, lane);
     }
-    if (wl == 0) rs.store(D, lane);
+    __syncthreads();
   }
-  (void)wsum;
 }
 
 // Standard relations: every rhs row of a batch went through the same operator row.  Stage 1: one
@@ -476,15 +487,18 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   int ctas_emb = (int)((warps + TILE_WARPS_EMB - 1) / TILE_WARPS_EMB);
   size_t stage_smem = (size_t)TILE_WARPS_EMB * TILE * d.Dp * sizeof(float);
   const int hub_ctas = 296;
-  size_t hub_smem = (size_t)UPD_WARPS * VEC * 128 * sizeof(float);
+  size_t hub_smem = (size_t)d.k * VEC * 128 * sizeof(float);            // per-batch totals of one hub row
   static bool attr_done[2] = {false, false};
+  // the attribute is set once for the largest wave this row width allows in 227 KB
+  size_t hub_smem_max = (size_t)PBG_KMAX * VEC * 128 * sizeof(float);
+  if (hub_smem_max > 227 * 1024) hub_smem_max = 227 * 1024;
   bool has_op = d.op != PBG_OP_NONE && w.theta[0] != nullptr;
   if (has_op && !d.dynamic) {
     relgrad_std_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, 0, st>>>(d, wb, w);
     ++launches;
   }
   if (!attr_done[0]) {
-    cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem);
+    cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem_max);
     cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
     attr_done[0] = true;
@@ -496,7 +510,7 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   if (has_op) {
     if (d.dynamic) {
       if (!attr_done[1]) {
-        cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_REL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem);
+        cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_REL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem_max);
         attr_done[1] = true;
       }
       cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
