@@ -304,14 +304,16 @@ def run_b200(args, w):
     else:
         mine = [(2 * rank) % P, (2 * rank + 1) % P]
     tables, states = {}, {}
+    max_rows = max(bounds[p + 1] - bounds[p] for p in range(P))
     for p in mine:
-        rows = bounds[p + 1] - bounds[p]
+        rows = bounds[p + 1] - bounds[p] if world == 1 else max_rows     # equal shapes for the ring
         tables[p] = torch.randn(rows, D, device=dev, generator=gen) * 1e-3
         states[p] = torch.zeros(rows, device=dev)
     spare = None
     if world > 1:
-        rows = max(bounds[p + 1] - bounds[p] for p in range(P))
-        spare = (torch.empty(rows, D, device=dev), torch.empty(rows, device=dev))
+        # the rhs partition travels round the ring: a second buffer of the same shape receives the
+        # incoming partition while the outgoing one is being sent; the two then swap roles
+        spare = (torch.empty_like(tables[mine[1]]), torch.empty_like(states[mine[1]]))
 
     cfg = T.ConfigSchema(entities={"e": T.EntitySchema(num_partitions=P)},
                          relations=[T.RelationSchema("r", "e", "e", operator=w["op"])], dimension=D,
@@ -321,9 +323,12 @@ def run_b200(args, w):
     model = T.make_model(cfg, dev)
     trainer = T.B200Trainer(T.make_optimizer(cfg, model.parameters(), False),
                             T.LOSS_FUNCTIONS.get_class(w["loss"])(margin=0.1), [1.0])
-    opts = {p: T.RowAdagrad([tables[p]], lr=0.1) for p in mine}
-    for p in mine:
-        opts[p].state[id(tables[p])]["sum"] = states[p]
+    def optimizer_for(table, state):
+        o = T.RowAdagrad([table], lr=0.1)
+        o.state[id(table)]["sum"] = state
+        return o
+
+    opts = {p: optimizer_for(tables[p], states[p]) for p in mine}
 
     seq = bucket_sequence(len(mine)) if world == 1 else None
     total_steps = args.warmup + args.steps
@@ -358,9 +363,11 @@ def run_b200(args, w):
         l, r = dev_edges[s]
         trainer.train_batches(model, l, r, None, batches, want_per_batch=False)
         if world > 1:
-            ring_exchange([tables[mine[1]], states[mine[1]]], list(spare))
-            tables[mine[1]].copy_(spare[0][: tables[mine[1]].shape[0]])
-            states[mine[1]].copy_(spare[1][: states[mine[1]].shape[0]])
+            nonlocal spare
+            p = mine[1]
+            ring_exchange([tables[p], states[p]], list(spare))
+            (tables[p], states[p]), spare = spare, (tables[p], states[p])     # swap roles, no copy
+            opts[p] = optimizer_for(tables[p], states[p])
 
     def barrier():
         if world > 1:

@@ -7,14 +7,16 @@
 //   grad Q : GQ_p[blk] (Pm x D) = T_p[blk] (Pm x Mm) . N_p[blk]        A K-major, B MN-major
 //   grad N : GN_p[blk] (Mm x D) = T_p[blk]^T . Q_p[blk]                A, B both MN-major
 //
-// One CTA computes one 128 x BN output tile (BN <= 256) of one (chunk, problem):
+// Persistent CTAs (one per SM) walk the list of 128 x BN output tiles (BN <= 256) of all (chunk,
+// problem) pairs; two 256-column accumulators in tensor memory alternate, so the epilogue of one
+// tile overlaps the main loop of the next:
 //   warp 0      TMA producer: cp.async.bulk.tensor tiles of 32 k-values into a ring of
 //               shared-memory stages, completion on an mbarrier per stage
 //   warp 1      allocates tensor memory, issues tcgen05.mma.kind::tf32 (one elected lane) and
 //               commits to the stage's "empty" barrier / the final "accumulator ready" barrier
-//   warps 2-9   TF32X3 only: split every landed stage into hi / lo (see below)
 //   warps 2-5   epilogue: tcgen05.ld 32 columns at a time (each warp its 32 TMEM lanes = 32
 //               rows), comparator epilogue for scores, 128-byte row-segment stores
+//   warps 6-13  TF32X3 only: split every landed stage into hi / lo (see below)
 // K-major operands use the 128-byte swizzle; MN-major tf32 operands must use the 128-byte swizzle
 // with 32-byte atoms (descriptor layout type 1, TMA swizzle 128B_ATOM_32B), 32 x 32 element boxes.
 //
@@ -28,7 +30,7 @@
 
 #include "pbg_common.cuh"
 
-#define TC_THREADS 320          // warp 0 TMA, warp 1 MMA, warps 2-9 split operands, warps 2-5 also run the epilogue
+#define TC_THREADS 448          // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-13 split operands (TF32X3)
 #define TC_SPLIT_THREADS 256
 #define TC_WAIT_LIMIT 4000000
 
@@ -76,35 +78,31 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   constexpr uint32_t A_BYTES = 128 * 128, B_BYTES = 256 * 128;          // one 32-k tile of 128 / 256 rows
   constexpr uint32_t RAW_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t STAGE_BYTES = SPLIT ? 2 * RAW_BYTES : RAW_BYTES;   // [A hi][B hi] ([A lo][B lo])
-  const int p = blockIdx.z & 1, blk = blockIdx.z >> 1;
-  {
-    BlockInfo bi = block_info(d, wb, blk);
-    if (bi.n == 0) return;
-    if (g.score && !d.neg_enabled[p]) return;
-  }
-  const int m0 = blockIdx.y * 128, n0 = blockIdx.x * g.BN;
-  if (m0 >= g.M || n0 >= g.N) return;
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ __align__(8) unsigned long long bars[3 * STAGES + 1];
+  __shared__ __align__(8) unsigned long long bars[3 * STAGES + 4];
   __shared__ uint32_t tmem_base_s;
-  __shared__ int failed;
+  __shared__ volatile int failed;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };                 // TMA landed
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };     // MMAs have read the stage
   auto conv_bar = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };  // hi / lo written (SPLIT)
-  const uint32_t acc_bar = bar0 + 8u * (3 * STAGES);
+  auto accf_bar = [&](int a) { return bar0 + 8u * (3 * STAGES + a); };      // accumulator a complete
+  auto acce_bar = [&](int a) { return bar0 + 8u * (3 * STAGES + 2 + a); };  // accumulator a drained
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2 * STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar0 + 8u * i));
     for (int i = 0; i < STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(conv_bar(i)), "r"(TC_SPLIT_THREADS));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(acc_bar));
+    for (int a = 0; a < 2; ++a) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(accf_bar(a)));
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" :: "r"(acce_bar(a)));
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     failed = 0;
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" :: "r"(smem_u32(&tmem_base_s)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" :: "r"(smem_u32(&tmem_base_s)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -115,95 +113,133 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   const int b_atoms = (g.BN + 31) / 32;
   const uint32_t b_used = B_MN ? (uint32_t)b_atoms * 4096u : (uint32_t)g.BN * 128u;
   const uint32_t stage_tx = A_BYTES + b_used;
+  // persistent tile loop: tile t -> (n tile, m tile, chunk block, problem); every role walks the same list
+  const int tiles_n = (g.N + g.BN - 1) / g.BN, tiles_m = (g.M + 127) / 128;
+  const long long ntiles = (long long)tiles_n * tiles_m * d.nblk * 2;
+  auto tile_live = [&](long long t, int &p, int &blk, int &m0, int &n0) {
+    int x = (int)(t % tiles_n);
+    long long r = t / tiles_n;
+    int y = (int)(r % tiles_m);
+    int z = (int)(r / tiles_m);
+    p = z & 1; blk = z >> 1; m0 = y * 128; n0 = x * g.BN;
+    BlockInfo bi = block_info(d, wb, blk);
+    return bi.n != 0 && !(g.score && !d.neg_enabled[p]);
+  };
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer ----------------
-    for (int it = 0; it < nkb; ++it) {
-      int s = it % STAGES;
-      if (it >= STAGES && !mbar_wait(empty_bar(s), ((it / STAGES) - 1) & 1, errflag)) { failed = 1; break; }
-      uint32_t fb = full_bar(s);
-      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(fb), "r"(stage_tx) : "memory");
-      unsigned char *st = smem + (size_t)s * STAGE_BYTES;
-      int k0 = it * 32;
-      uint32_t dA = smem_u32(st), dB = smem_u32(st + A_BYTES);
-      if (!A_MN) tma_load_3d(dA, &maps.a[p], k0, m0, blk, fb);
-      else
-        for (int mb = 0; mb < 4; ++mb) tma_load_3d(dA + mb * 4096, &maps.a[p], m0 + mb * 32, k0, blk, fb);
-      if (!B_MN) tma_load_3d(dB, &maps.b[p], k0, n0, blk, fb);
-      else
-        for (int nb = 0; nb < b_atoms; ++nb) tma_load_3d(dB + nb * 4096, &maps.b[p], n0 + nb * 32, k0, blk, fb);
+    long long git = 0;
+    for (long long t = blockIdx.x; t < ntiles && !failed; t += gridDim.x) {
+      int p, blk, m0, n0;
+      if (!tile_live(t, p, blk, m0, n0)) continue;
+      for (int kb = 0; kb < nkb; ++kb, ++git) {
+        int s = (int)(git % STAGES);
+        if (git >= STAGES && !mbar_wait(empty_bar(s), (uint32_t)((git / STAGES) - 1) & 1, errflag)) { failed = 1; break; }
+        uint32_t fb = full_bar(s);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(fb), "r"(stage_tx) : "memory");
+        unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+        int k0 = kb * 32;
+        uint32_t dA = smem_u32(st), dB = smem_u32(st + A_BYTES);
+        if (!A_MN) tma_load_3d(dA, &maps.a[p], k0, m0, blk, fb);
+        else
+          for (int mb = 0; mb < 4; ++mb) tma_load_3d(dA + mb * 4096, &maps.a[p], m0 + mb * 32, k0, blk, fb);
+        if (!B_MN) tma_load_3d(dB, &maps.b[p], k0, n0, blk, fb);
+        else
+          for (int nb = 0; nb < b_atoms; ++nb) tma_load_3d(dB + nb * 4096, &maps.b[p], n0 + nb * 32, k0, blk, fb);
+      }
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer ----------------
     // instruction descriptor: D fp32, A/B tf32, operand majors, N >> 3, M >> 4
     const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                            ((uint32_t)(g.BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-    bool ok = true;
-    for (int it = 0; it < nkb && ok; ++it) {
-      int s = it % STAGES;
-      if (!mbar_wait(SPLIT ? conv_bar(s) : full_bar(s), (it / STAGES) & 1, errflag)) { failed = 1; ok = false; break; }
+    long long git = 0, j = 0;
+    for (long long t = blockIdx.x; t < ntiles && !failed; t += gridDim.x) {
+      int p, blk, m0, n0;
+      if (!tile_live(t, p, blk, m0, n0)) continue;
+      const int ab = (int)(j & 1);
+      if (j >= 2 && !mbar_wait(acce_bar(ab), (uint32_t)((j >> 1) - 1) & 1, errflag)) { failed = 1; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      unsigned char *st = smem + (size_t)s * STAGE_BYTES;
-      uint32_t aH = smem_u32(st), bH = smem_u32(st + A_BYTES);
-      uint32_t aL = aH + RAW_BYTES, bL = bH + RAW_BYTES;
+      const uint32_t tacc = tmem + (uint32_t)ab * 256u;
+      bool ok = true;
+      for (int kb = 0; kb < nkb; ++kb, ++git) {
+        int s = (int)(git % STAGES);
+        if (!mbar_wait(SPLIT ? conv_bar(s) : full_bar(s), (uint32_t)(git / STAGES) & 1, errflag)) { failed = 1; ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+        uint32_t aH = smem_u32(st), bH = smem_u32(st + A_BYTES);
+        uint32_t aL = aH + RAW_BYTES, bL = bH + RAW_BYTES;
 #pragma unroll
-      for (int k8 = 0; k8 < 4; ++k8) {
-        uint32_t ao = A_MN ? k8 * 1024 : k8 * 32, bo = B_MN ? k8 * 1024 : k8 * 32;
-        uint64_t dAh = A_MN ? smem_desc(aH + ao, 4096, 512, 1) : smem_desc(aH + ao, 0, 1024, 2);
-        uint64_t dBh = B_MN ? smem_desc(bH + bo, 4096, 512, 1) : smem_desc(bH + bo, 0, 1024, 2);
-        uint32_t acc = (it > 0 || k8 > 0) ? 1u : 0u;
-        if (SPLIT) {
-          uint64_t dAl = A_MN ? smem_desc(aL + ao, 4096, 512, 1) : smem_desc(aL + ao, 0, 1024, 2);
-          uint64_t dBl = B_MN ? smem_desc(bL + bo, 4096, 512, 1) : smem_desc(bL + bo, 0, 1024, 2);
+        for (int k8 = 0; k8 < 4; ++k8) {
+          uint32_t ao = A_MN ? k8 * 1024 : k8 * 32, bo = B_MN ? k8 * 1024 : k8 * 32;
+          uint64_t dAh = A_MN ? smem_desc(aH + ao, 4096, 512, 1) : smem_desc(aH + ao, 0, 1024, 2);
+          uint64_t dBh = B_MN ? smem_desc(bH + bo, 4096, 512, 1) : smem_desc(bH + bo, 0, 1024, 2);
+          uint32_t acc = (kb > 0 || k8 > 0) ? 1u : 0u;
+          if (SPLIT) {
+            uint64_t dAl = A_MN ? smem_desc(aL + ao, 4096, 512, 1) : smem_desc(aL + ao, 0, 1024, 2);
+            uint64_t dBl = B_MN ? smem_desc(bL + bo, 4096, 512, 1) : smem_desc(bL + bo, 0, 1024, 2);
+            asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                         :: "r"(tacc), "l"(dAl), "l"(dBh), "r"(idesc), "r"(acc) : "memory");
+            asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
+                         :: "r"(tacc), "l"(dAh), "l"(dBl), "r"(idesc), "r"(1u) : "memory");
+            acc = 1u;
+          }
           asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
-                       :: "r"(tmem), "l"(dAl), "l"(dBh), "r"(idesc), "r"(acc) : "memory");
-          asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
-                       :: "r"(tmem), "l"(dAh), "l"(dBl), "r"(idesc), "r"(1u) : "memory");
-          acc = 1u;
+                       :: "r"(tacc), "l"(dAh), "l"(dBh), "r"(idesc), "r"(acc) : "memory");
         }
-        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
-                     :: "r"(tmem), "l"(dAh), "l"(dBh), "r"(idesc), "r"(acc) : "memory");
+        // frees the stage for the producer once the MMAs above have read it
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(empty_bar(s)) : "memory");
       }
-      // frees the stage for the producer once the MMAs above have read it
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(empty_bar(s)) : "memory");
+      if (!ok) break;
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(accf_bar(ab)) : "memory");
+      ++j;
     }
-    if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(acc_bar) : "memory");
-  }
-  if (SPLIT && warp >= 2) {
-    // ---------------- hi / lo split of every landed stage (the epilogue warps) ----------------
-    const int ct = threadIdx.x - 64;                              // 0..255
+  } else if (SPLIT && warp >= 6) {
+    // ---------------- hi / lo split of every landed stage (warps 6-13) ----------------
+    const int ct = threadIdx.x - 192;                             // 0..255
     const uint32_t nchunks = stage_tx / 16;
-    for (int it = 0; it < nkb; ++it) {
-      int s = it % STAGES;
-      if (!mbar_wait(full_bar(s), (it / STAGES) & 1, errflag)) { failed = 1; break; }
-      unsigned char *st = smem + (size_t)s * STAGE_BYTES;
-      for (uint32_t c0 = ct; c0 < nchunks; c0 += 4 * TC_SPLIT_THREADS) {
-        float4 v[4];
+    long long git = 0;
+    bool stop = false;
+    for (long long t = blockIdx.x; t < ntiles && !stop; t += gridDim.x) {
+      int p, blk, m0, n0;
+      if (__any_sync(0xffffffffu, failed != 0)) break;           // warp-uniform exit
+      if (!tile_live(t, p, blk, m0, n0)) continue;
+      for (int kb = 0; kb < nkb; ++kb, ++git) {
+        int s = (int)(git % STAGES);
+        if (!__all_sync(0xffffffffu, mbar_wait(full_bar(s), (uint32_t)(git / STAGES) & 1, errflag))) { failed = 1; stop = true; break; }
+        unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+        for (uint32_t c0 = ct; c0 < nchunks; c0 += 4 * TC_SPLIT_THREADS) {
+          float4 v[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint32_t c = c0 + u * TC_SPLIT_THREADS;
-          if (c < nchunks) v[u] = *reinterpret_cast<const float4 *>(st + (size_t)c * 16);
-        }
+          for (int u = 0; u < 4; ++u) {
+            uint32_t c = c0 + u * TC_SPLIT_THREADS;
+            if (c < nchunks) v[u] = *reinterpret_cast<const float4 *>(st + (size_t)c * 16);
+          }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint32_t c = c0 + u * TC_SPLIT_THREADS;
-          if (c < nchunks) {
-            float4 h = tf32_hi4(v[u]);
-            *reinterpret_cast<float4 *>(st + (size_t)c * 16) = h;
-            *reinterpret_cast<float4 *>(st + RAW_BYTES + (size_t)c * 16) = v[u] - h;
+          for (int u = 0; u < 4; ++u) {
+            uint32_t c = c0 + u * TC_SPLIT_THREADS;
+            if (c < nchunks) {
+              float4 h = tf32_hi4(v[u]);
+              *reinterpret_cast<float4 *>(st + (size_t)c * 16) = h;
+              *reinterpret_cast<float4 *>(st + RAW_BYTES + (size_t)c * 16) = v[u] - h;
+            }
           }
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(conv_bar(s)) : "memory");
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
-      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(conv_bar(s)) : "memory");
     }
-  }
-  if (warp >= 2 && warp < 6) {
-    // ---------------- epilogue ----------------
-    bool ok = mbar_wait(acc_bar, 0, errflag);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      const int q = warp & 3;                       // the 32 TMEM lanes this warp may read
+  } else if (warp >= 2 && warp < 6) {
+    // ---------------- epilogue: drains accumulator j & 1 while the next tile is being multiplied ----------------
+    long long j = 0;
+    const int q = warp & 3;                           // the 32 TMEM lanes this warp may read
+    for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+      int p, blk, m0, n0;
+      if (__any_sync(0xffffffffu, failed != 0)) break;           // warp-uniform exit (tcgen05.ld is warp-wide)
+      if (!tile_live(t, p, blk, m0, n0)) continue;
+      const int ab = (int)(j & 1);
+      if (!__all_sync(0xffffffffu, mbar_wait(accf_bar(ab), (uint32_t)(j >> 1) & 1, errflag))) { failed = 1; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m = m0 + q * 32 + lane;
       float *C = g.C[p] + (size_t)blk * g.c_blk + (size_t)m * g.ldc;
       float an = 0.f;
@@ -212,7 +248,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
       const float *bn = l2 ? g.auxB[p] + (size_t)blk * g.auxb_blk : nullptr;
       for (int c0 = 0; c0 < g.BN; c0 += 32) {
         uint32_t r[32];
-        uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        uint32_t taddr = tmem + (uint32_t)ab * 256u + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
         asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
                        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
@@ -221,24 +257,31 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (m < g.M) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            int n = n0 + c0 + j;
-            if (n >= g.N || c0 + j >= g.BN) break;
-            float v[4];
+          for (int jj = 0; jj < 32; jj += 4) {
+            int n = n0 + c0 + jj;
+            if (n < g.N && c0 + jj < g.BN) {
+              float v[4];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              v[t] = __uint_as_float(r[j + t]);
-              if (l2 && n + t < g.N) {
-                float qv = (bn[n + t] - 2.0f * v[t]) + an;     // model.py:226-246
-                v[t] = g.cmp == PBG_CMP_L2 ? -sqrtf(fmaxf(qv, 1e-30f)) : -qv;
+              for (int tt = 0; tt < 4; ++tt) {
+                v[tt] = __uint_as_float(r[jj + tt]);
+                if (l2 && n + tt < g.N) {
+                  float qv = (bn[n + tt] - 2.0f * v[tt]) + an;     // model.py:226-246
+                  v[tt] = g.cmp == PBG_CMP_L2 ? -sqrtf(fmaxf(qv, 1e-30f)) : -qv;
+                }
+              }
+              if (n + 3 < g.N) st4(C + n, make_float4(v[0], v[1], v[2], v[3]));
+              else {
+                if (n < g.N) C[n] = v[0];
+                if (n + 1 < g.N) C[n + 1] = v[1];
+                if (n + 2 < g.N) C[n + 2] = v[2];
               }
             }
-            if (n + 3 < g.N) st4(C + n, make_float4(v[0], v[1], v[2], v[3]));
-            else
-              for (int t = 0; t < 4 && n + t < g.N; ++t) C[n + t] = v[t];
           }
         }
       }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(acce_bar(ab)) : "memory");
+      ++j;
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -247,7 +290,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
     // If a wait ran out the asynchronous copies / MMAs may still be in flight: give them a
     // bounded grace period before the tensor memory goes back.
     if (failed) for (int i = 0; i < 200000; ++i) __nanosleep(20);
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" :: "r"(tmem) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" :: "r"(tmem) : "memory");
   }
 }
 
@@ -337,7 +380,10 @@ void pbg_tc_plan_destroy(void *plan) { delete (TcPlan *)plan; }
 template <bool A_MN, bool B_MN>
 static void launch_tc(const TcMaps &maps, const TcGeom &g, int nterms, const WaveDims &d, const WaveBatches &wb, int *errflag,
                       cudaStream_t st) {
-  dim3 grid((g.N + g.BN - 1) / g.BN, (g.M + 127) / 128, d.nblk * 2);
+  long long tiles = (long long)((g.N + g.BN - 1) / g.BN) * ((g.M + 127) / 128) * d.nblk * 2;
+  static int sms = 0;
+  if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   size_t smem = 4 * (128 * 128 + 256 * 128) + 1024;           // 2 stages x (hi, lo) or 4 stages x raw
   if (nterms == 3) {
     static bool done = false;
