@@ -36,6 +36,9 @@ WORKLOADS = {
                batch=1000, nb=100, nu=100, gamma=2.3, desc="social-graph shaped, Chung-Lu exponent 2.3"),
     "c4": dict(entities=41_652_230, edges=1_468_365_182, partitions=16, dim=100, op="translation", comp="cos",
                loss="ranking", batch=1000, nb=100, nu=100, gamma=2.0, desc="follower-graph shaped, Chung-Lu exponent 2.0"),
+    "c2": dict(entities=14_951, edges=483_142, partitions=1, dim=400, op="complex_diagonal", comp="dot", loss="softmax",
+               batch=5000, nb=1000, nu=0, gamma=None, rels=1345, dynamic=True,
+               desc="15k-entity multi-relation KG shaped, 1345 relations Zipf(1.0), planted permutation maps + 20% noise, dynamic relations"),
     "c1": dict(entities=100_000, edges=1_000_000, partitions=1, dim=100, op="none", comp="dot", loss="ranking",
                batch=1000, nb=50, nu=50, gamma=None, desc="plumbing graph, Zipf(1.1) endpoints"),
 }
@@ -296,7 +299,7 @@ def run_b200(args, w):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     P, D, B = w["partitions"], w["dim"], w["batch"]
-    step_edges = min(EDGES_PER_STEP_CAP, max(B, w["edges"] // (P * P)))
+    step_edges = min(EDGES_PER_STEP_CAP if P > 1 else w["edges"], max(B, w["edges"] // (P * P)))
     samplers, bounds, gen = make_samplers(w, dev, seed=3)
     # resident partitions: all of them on one GPU; two per GPU (lhs stays, rhs travels round the ring) otherwise
     if world == 1:
@@ -315,11 +318,12 @@ def run_b200(args, w):
         # incoming partition while the outgoing one is being sent; the two then swap roles
         spare = (torch.empty_like(tables[mine[1]]), torch.empty_like(states[mine[1]]))
 
+    dyn = bool(w.get("dynamic"))
     cfg = T.ConfigSchema(entities={"e": T.EntitySchema(num_partitions=P)},
                          relations=[T.RelationSchema("r", "e", "e", operator=w["op"])], dimension=D,
                          comparator=w["comp"], loss_fn=w["loss"], margin=0.1, lr=0.1, batch_size=B,
                          num_batch_negs=w["nb"], num_uniform_negs=w["nu"], precision=args.precision,
-                         batches_in_flight=args.k)
+                         batches_in_flight=args.k, dynamic_relations=dyn, num_dynamic_rels=w.get("rels", 0) if dyn else 0)
     model = T.make_model(cfg, dev)
     trainer = T.B200Trainer(T.make_optimizer(cfg, model.parameters(), False),
                             T.LOSS_FUNCTIONS.get_class(w["loss"])(margin=0.1), [1.0])
@@ -350,18 +354,33 @@ def run_b200(args, w):
 
     batches = [(o, min(B, step_edges - o), 0) for o in range(0, step_edges, B)]
 
+    rel_cdf = None
+    if dyn:
+        rw = torch.arange(1, w["rels"] + 1, device=dev, dtype=torch.float64).pow(-1.0)      # Zipf(1.0) relation frequencies
+        rel_cdf = (torch.cumsum(rw, 0) / rw.sum()).float()
+        rel_a = torch.randint(1, w["entities"], (w["rels"],), device=dev, generator=gen)     # planted maps v = a_r u + b_r mod N
+        rel_b = torch.randint(0, w["entities"], (w["rels"],), device=dev, generator=gen)
+
     def draw_edges(bk):
         pl, pr = bk
-        return samplers[pl].draw(step_edges, gen), samplers[pr].draw(step_edges, gen)
+        if not dyn:
+            return samplers[pl].draw(step_edges, gen), samplers[pr].draw(step_edges, gen), None
+        n = w["entities"]
+        rel = torch.searchsorted(rel_cdf, torch.rand(step_edges, device=dev, generator=gen)).clamp_(max=w["rels"] - 1)
+        u = torch.randint(0, n, (step_edges,), device=dev, generator=gen)
+        v = (rel_a[rel] * u + rel_b[rel]) % n
+        noisy = torch.rand(step_edges, device=dev, generator=gen) < 0.2
+        v = torch.where(noisy, torch.randint(0, n, (step_edges,), device=dev, generator=gen), v)
+        return u, v, rel
 
     # ---- device-resident pass: `value` -------------------------------------------------------
     dev_edges = [draw_edges(bucket_for(s)) for s in range(total_steps + nprof)]
-    host_edges = [(l.cpu().pin_memory(), r.cpu().pin_memory()) for l, r in dev_edges[: total_steps]]
+    host_edges = [tuple(None if t is None else t.cpu().pin_memory() for t in e) for e in dev_edges[: total_steps]]
 
     def step_device(s):
         bind(bucket_for(s))
-        l, r = dev_edges[s]
-        trainer.train_batches(model, l, r, None, batches, want_per_batch=False)
+        l, r, rl = dev_edges[s]
+        trainer.train_batches(model, l, r, rl, batches, want_per_batch=False)
         if world > 1:
             nonlocal spare
             p = mine[1]
@@ -399,8 +418,8 @@ def run_b200(args, w):
     # ---- end-to-end pass: host edges, copies and stats read-back inside the timed region --------
     def step_host(s):
         bind(bucket_for(s))
-        l, r = host_edges[s]
-        return trainer.train_batches(model, l, r, None, batches, want_per_batch=True)
+        l, r, rl = host_edges[s]
+        return trainer.train_batches(model, l, r, rl, batches, want_per_batch=True)
 
     for s in range(min(args.warmup, 2)):
         step_host(s)
@@ -417,7 +436,7 @@ def run_b200(args, w):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_e2e = float(t)
     e2e = {"value": world * args.steps * step_edges / (ms_e2e / 1e3), "unit": "edges/sec",
-           "h2d_bytes_per_step": 2 * 8 * step_edges, "d2h_bytes_per_step": 32 * len(batches) + 4,
+           "h2d_bytes_per_step": (3 if dyn else 2) * 8 * step_edges, "d2h_bytes_per_step": 32 * len(batches) + 4,
            "last_batch_loss": last[-1].metrics["loss"] if last else None}
 
     # ---- per-kernel-class timing pass ----------------------------------------------------------
@@ -426,8 +445,8 @@ def run_b200(args, w):
     check(nat.lib.pbg_set_profiling(nat.ctx, 1), nat.ctx)
     for s in range(total_steps, total_steps + nprof):
         bind(bucket_for(s))
-        l, r = dev_edges[s]
-        trainer.train_batches(model, l, r, None, batches, want_per_batch=False)
+        l, r, rl = dev_edges[s]
+        trainer.train_batches(model, l, r, rl, batches, want_per_batch=False)
     msc = (C.c_double * 7)()
     lc = (C.c_int64 * 7)()
     check(nat.lib.pbg_kernel_times(nat.ctx, msc, lc), nat.ctx)
@@ -482,9 +501,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
-    ap.add_argument("--k", type=int, default=7,
-                    help="batches in flight (1 = sequential batches); 7 makes the 20 contraction tiles per batch of "
-                         "workload c3 fill 140 of the 148 SMs in one round")
+    ap.add_argument("--lr", type=float, default=0.1)
+    ap.add_argument("--k", type=int, default=14, help="batches in flight (1 = sequential batches, the reference's GPU semantics)")
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32x3", "tf32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--resident", type=int, default=0,
