@@ -43,6 +43,7 @@ WORKLOADS = {
                batch=1000, nb=50, nu=50, gamma=None, desc="plumbing graph, Zipf(1.1) endpoints"),
 }
 EDGES_PER_STEP_CAP = 269_507
+REF_BATCHES = 5          # batches per worker in one step of the CPU reference arm
 
 
 def peaks():
@@ -244,7 +245,7 @@ def cpu_baseline(w, budget_s=15.0):
 
 
 def run_reference(args, w):
-    """`--impl reference`: K timed steps of the CPU port; a step = 1 batch per host core."""
+    """`--impl reference`: K timed steps of the CPU port; a step = REF_BATCHES batches per host core."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -255,16 +256,17 @@ def run_reference(args, w):
     edges = 0
     total = 0.0
     for _ in range(args.steps):
-        e, t = tr.run(1)
+        e, t = tr.run(REF_BATCHES)
         edges += e
         total += t
     tr.close()
     v = edges / total
-    sample = f"{tr.cores} HOGWILD processes x 1 batch of {w['batch']} edges per step, one bucket of {rows} rows per side"
+    sample = (f"{tr.cores} HOGWILD processes x {REF_BATCHES} batches of {w['batch']} edges per step, one bucket of {rows} rows "
+              f"per side; fp32 PyTorch-CPU port of the reference trainer")
     line = {"impl": "reference", "metric": "edges/sec trained", "value": v, "unit": "edges/sec", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(args, w, step_edges=tr.cores * w["batch"]),
+            "config": workload_config(args, w, step_edges=tr.cores * w["batch"] * REF_BATCHES),
             "cpu_baseline": {"value": v, "unit": "edges/sec", "cores": tr.cores, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": "edges/sec", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -503,7 +505,9 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--lr", type=float, default=0.1)
     ap.add_argument("--k", type=int, default=14, help="batches in flight (1 = sequential batches, the reference's GPU semantics)")
-    ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32x3", "tf32"])
+    ap.add_argument("--precision", default="tf32x3", choices=["fp32", "tf32x3", "tf32"],
+                    help="tf32x3 (default): tcgen05 tensor cores with 3-term split, the rtol 1e-4 tier; fp32: CUDA cores; "
+                         "tf32: single pass, the rtol 1e-3 tier")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--resident", type=int, default=0,
                     help="partitions kept on the device at N=1 (0 = all); a small number keeps profiler captures small")
