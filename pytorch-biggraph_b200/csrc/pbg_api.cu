@@ -21,7 +21,9 @@ struct pbg_context {
   size_t ws_bytes = 0;
   WaveBufs bufs;           // workspace pointers (table pointers filled per call)
   SortPlan sort[2];        // double-buffered: wave w+1 is sorted on `side` while wave w trains
-  cudaStream_t side = nullptr;
+  cudaStream_t side = nullptr;      // key build + sort of the next wave
+  cudaStream_t part2 = nullptr;     // second half of a wave's gather / score / loss / gradient kernels
+  cudaEvent_t ev_wave = nullptr, ev_part2 = nullptr;
   cudaEvent_t ev_sorted[2] = {nullptr, nullptr}, ev_updated[2] = {nullptr, nullptr}, ev_inputs = nullptr;
   pbg_batch_stats *stats_dev = nullptr;
   int stats_cap = 0;
@@ -238,6 +240,9 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   }
   CU(c, cudaEventCreateWithFlags(&c->ev_inputs, cudaEventDisableTiming));
   CU(c, cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking));
+  CU(c, cudaStreamCreateWithFlags(&c->part2, cudaStreamNonBlocking));
+  CU(c, cudaEventCreateWithFlags(&c->ev_wave, cudaEventDisableTiming));
+  CU(c, cudaEventCreateWithFlags(&c->ev_part2, cudaEventDisableTiming));
   c->sum_dev = (double *)(c->ws + oSum);
   c->errflag = (int *)(c->ws + oErr);
   b.errflag = c->errflag;
@@ -270,6 +275,9 @@ extern "C" int pbg_destroy(pbg_context *c) {
   }
   if (c->ev_inputs) cudaEventDestroy(c->ev_inputs);
   if (c->side) cudaStreamDestroy(c->side);
+  if (c->part2) cudaStreamDestroy(c->part2);
+  if (c->ev_wave) cudaEventDestroy(c->ev_wave);
+  if (c->ev_part2) cudaEventDestroy(c->ev_part2);
   for (auto &s : c->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
   for (auto e : c->event_pool) cudaEventDestroy(e);
   delete c;
@@ -339,12 +347,21 @@ static int check_errflag(pbg_context *c) {
   return PBG_OK;
 }
 
-static int run_forward(pbg_context *c, const WaveDims &d, const WaveBatches &wb, const WaveBufs &w) {
-  { ClassTimer t(c, 1); t.done(launch_gather(d, wb, w, c->stream)); }
-  ClassTimer t(c, 2);
-  if (c->cfg.precision == PBG_PREC_FP32) t.done(launch_score_simt(d, wb, w, c->stream));
-  else t.done(launch_score_tc(d, wb, w, c->tcplan, c->stream));
+static int run_forward(pbg_context *c, const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
+  { ClassTimer t(c, 1, st); t.done(launch_gather(d, wb, w, st)); }
+  ClassTimer t(c, 2, st);
+  if (c->cfg.precision == PBG_PREC_FP32) t.done(launch_score_simt(d, wb, w, st));
+  else t.done(launch_score_tc(d, wb, w, c->tcplan, st));
   return PBG_OK;
+}
+
+// gather -> score -> loss -> gradient products of the chunk blocks [d.blk0, d.blk0 + d.nblk) on `st`
+static void run_part(pbg_context *c, const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
+  run_forward(c, d, wb, w, st);
+  { ClassTimer t(c, 3, st); t.done(launch_loss(d, wb, w, st)); }
+  ClassTimer t(c, 4, st);
+  if (c->cfg.precision == PBG_PREC_FP32) t.done(launch_grad_simt(d, wb, w, st));
+  else t.done(launch_grad_tc(d, wb, w, c->tcplan, st));
 }
 
 extern "C" int pbg_set_profiling(pbg_context *c, int enable) {
@@ -428,12 +445,23 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
       t.done(n + pbg_sort(sp, d.nocc, bits, c->side));
       CU(c, cudaEventRecord(c->ev_sorted[wave & 1], c->side));
     }
-    run_forward(c, d, wb, w);
-    { ClassTimer t(c, 3); t.done(launch_loss(d, wb, w, c->stream)); }
-    {
-      ClassTimer t(c, 4);
-      if (c->cfg.precision == PBG_PREC_FP32) t.done(launch_grad_simt(d, wb, w, c->stream));
-      else t.done(launch_grad_tc(d, wb, w, c->tcplan, c->stream));
+    // The batches of a wave all read the tables as the wave found them, so its forward / backward
+    // kernels can run as two independent halves on two streams: the memory-bound kernels of one
+    // half fill the SMs' idle issue slots while the other half's contractions run.
+    d.blk0 = 0;
+    if (kk >= 2) {
+      int ka = (kk + 1) / 2;
+      WaveDims da = d, db = d;
+      da.nblk = ka * d.Cm;
+      db.blk0 = ka * d.Cm; db.nblk = (kk - ka) * d.Cm;
+      CU(c, cudaEventRecord(c->ev_wave, c->stream));          // previous wave's update is in front of this
+      CU(c, cudaStreamWaitEvent(c->part2, c->ev_wave, 0));
+      run_part(c, db, wb, w, c->part2);
+      CU(c, cudaEventRecord(c->ev_part2, c->part2));
+      run_part(c, da, wb, w, c->stream);
+      CU(c, cudaStreamWaitEvent(c->stream, c->ev_part2, 0));
+    } else {
+      run_part(c, d, wb, w, c->stream);
     }
     CU(c, cudaStreamWaitEvent(c->stream, c->ev_sorted[wave & 1], 0));
     {
@@ -527,7 +555,8 @@ extern "C" int pbg_score_batch(pbg_context *c, const pbg_bucket *bk, const int64
   memset(&wb, 0, sizeof wb);
   wb.n[0] = count; wb.rel[0] = d.dynamic ? 0 : relidx; wb.wrel[0] = 1.0f;
   d.k = 1; d.nblk = d.Cm; d.nocc = d.spb;
-  run_forward(c, d, wb, w);
+  d.blk0 = 0;
+  run_forward(c, d, wb, w, c->stream);
   c->launches += launch_export_scores(d, wb, w, lhs_pos, rhs_pos, lhs_neg, rhs_neg, c->stream);
   CU(c, cudaGetLastError());
   return check_errflag(c);

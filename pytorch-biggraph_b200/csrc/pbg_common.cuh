@@ -36,7 +36,8 @@ struct WaveDims {
   int D, Dp;            // dim, workspace row stride (floats)
   int Pm, U, Mm, Ms;    // chunk slots, uniform negatives, Pm+U, score row stride
   int Cm;               // chunks per batch (max)
-  int k, nblk;          // batches in this wave, k*Cm
+  int k, nblk;          // batches in this wave; chunk blocks THIS LAUNCH covers (k*Cm for a whole wave)
+  int blk0;             // first chunk block of this launch (a wave may be launched in two parts)
   int op, cmp, loss, dynamic;
   int batch_negs;       // 1: batch_uniform mode, 0: uniform-only mode (num_batch_negs == 0)
   int neg_enabled[2];   // problem 0 = lhs negatives, problem 1 = rhs negatives

@@ -112,7 +112,8 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
   int lane = threadIdx.x & 31;
   long long item = (long long)blockIdx.x * GATHER_WARPS + (threadIdx.x >> 5);
   if (item >= (long long)d.nblk * d.Mm) return;
-  int blk = (int)(item / d.Mm), r = (int)(item - (long long)blk * d.Mm);
+  int lb = (int)(item / d.Mm), r = (int)(item - (long long)lb * d.Mm);
+  const int blk = d.blk0 + lb;
   BlockInfo bi = block_info(d, wb, blk);
   const int D = d.D;
   size_t nrow = (size_t)blk * d.Mm + r;

@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(256) gemm_tile_kernel(GemmTasks tasks, WaveDim
   constexpr int TM = BM / 16;
   __shared__ __align__(16) float As[BK][BM + 4];
   __shared__ __align__(16) float Bs[BK][BN + 4];
-  int p = blockIdx.z & 1, blk = blockIdx.z >> 1;
+  int p = blockIdx.z & 1, blk = d.blk0 + (blockIdx.z >> 1);
   {
     BlockInfo bi = block_info(d, wb, blk);
     if (bi.n == 0) return;                          // chunk without edges

@@ -121,7 +121,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
     long long r = t / tiles_n;
     int y = (int)(r % tiles_m);
     int z = (int)(r / tiles_m);
-    p = z & 1; blk = z >> 1; m0 = y * 128; n0 = x * g.BN;
+    p = z & 1; blk = d.blk0 + (z >> 1); m0 = y * 128; n0 = x * g.BN;
     BlockInfo bi = block_info(d, wb, blk);
     return bi.n != 0 && !(g.score && !d.neg_enabled[p]);
   };

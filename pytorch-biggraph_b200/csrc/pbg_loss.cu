@@ -42,7 +42,8 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
   if (item >= 2 * per_prob) return;
   int p = (int)(item / per_prob);
   long long rem = item - p * per_prob;
-  int blk = (int)(rem / d.Pm), i = (int)(rem - (long long)blk * d.Pm);
+  int lb = (int)(rem / d.Pm), i = (int)(rem - (long long)lb * d.Pm);
+  const int blk = d.blk0 + lb;
   BlockInfo bi = block_info(d, wb, blk);
   if (bi.n == 0) return;
   float *S = w.S[p] + ((size_t)blk * d.Pm + i) * d.Ms;
@@ -152,7 +153,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
 // l2 family: column sums of T_p over the chunk's positives (coefficient of the negative row's
 // own |b|^2 term).  One thread per column.
 __global__ void colsum_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
-  int p = blockIdx.z, blk = blockIdx.y;
+  int p = blockIdx.z, blk = d.blk0 + blockIdx.y;
   int j = blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= d.Mm) return;
   BlockInfo bi = block_info(d, wb, blk);
@@ -175,7 +176,8 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_kernel(WaveDims d, WaveB
   if (item >= 2 * per_side) return;
   int side = (int)(item / per_side);
   long long rem = item - side * per_side;
-  int blk = (int)(rem / d.Mm), m = (int)(rem - (long long)blk * d.Mm);
+  int lb = (int)(rem / d.Mm), m = (int)(rem - (long long)lb * d.Mm);
+  const int blk = d.blk0 + lb;
   BlockInfo bi = block_info(d, wb, blk);
   if (bi.n == 0) return;
   // side 0 (lhs rows): negatives of problem 0 (columns of T0), scored side of problem 1 (rows of T1)
