@@ -43,6 +43,9 @@ WORKLOADS = {
                batch=1000, nb=50, nu=50, gamma=None, desc="plumbing graph, Zipf(1.1) endpoints"),
 }
 EDGES_PER_STEP_CAP = 269_507
+# DRAM bytes per trained edge of each kernel class, from the ncu capture summarised in
+# profiles/kernels_c3_tf32x3.md (workload c3, tf32x3); dram__bytes_read.sum + dram__bytes_write.sum per launch / edges per launch
+NCU_TRAFFIC_PER_EDGE = {("c3", "tf32x3"): {"gather": 23.9e3, "score": 17.8e3, "grad": 29.8e3, "update": 40.5e3}}
 REF_BATCHES = 5          # batches per worker in one step of the CPU reference arm
 
 
@@ -471,15 +474,19 @@ def run_b200(args, w):
     for v in per_class.values():
         v["share"] = round(v["ms"] / tot, 3)
     dom = max((n for n in per_class if n in model_bytes or n in model_flops), key=lambda n: per_class[n]["ms"])
+    launches_dom = max(per_class[dom]["launches"], 1)
+    per_edge = NCU_TRAFFIC_PER_EDGE.get((args.workload, args.precision), {}).get(dom)
+    # ncu's DRAM bytes of the dominant class, per launch of this run (edges of the timing pass / its launches)
+    traffic = None if per_edge is None else per_edge * edges_prof / (launches_dom if dom != "update" else launches_dom / 2)
     if dom in model_flops:
         ach = per_class[dom]["TFLOPs"]
         roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
-                "frac": round(ach / pk["tflops"], 4), "traffic": None,
+                "frac": round(ach / pk["tflops"], 4), "traffic": traffic,
                 "peak_source": pk["source"] + " (cuBLAS bf16, sustained); the contraction runs in " + args.precision}
     else:
         ach = per_class[dom]["GBps"]
         roof = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": round(ach / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"]}
+                "frac": round(ach / pk["hbm_gbs"], 4), "traffic": traffic, "peak_source": pk["source"]}
 
     if rank == 0:
         line = {"metric": "edges/sec trained", "value": value, "unit": "edges/sec", "n_gpus": world, "steps": args.steps,
