@@ -120,8 +120,10 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   if (cfg->dim <= 0 || cfg->dim % 4 != 0 || cfg->dim > 2048)
     return fail(c, PBG_ERR_UNSUPPORTED, "dimension %d: this build needs a multiple of 4 up to 2048", cfg->dim);
   if (cfg->op < PBG_OP_NONE || cfg->op > PBG_OP_AFFINE) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown operator %d", cfg->op);
-  if (cfg->op == PBG_OP_LINEAR || cfg->op == PBG_OP_AFFINE)
-    return fail(c, PBG_ERR_UNSUPPORTED, "operator %s has no device code in this build", cfg->op == PBG_OP_LINEAR ? "linear" : "affine");
+  const bool matrix_op = cfg->op == PBG_OP_LINEAR || cfg->op == PBG_OP_AFFINE;
+  if (matrix_op && cfg->dynamic_relations)
+    return fail(c, PBG_ERR_UNSUPPORTED, "operator %s with dynamic relations (one matrix per edge) has no device code",
+                cfg->op == PBG_OP_LINEAR ? "linear" : "affine");
   if (cfg->op == PBG_OP_COMPLEX_DIAGONAL && cfg->dim % 8 != 0)
     return fail(c, PBG_ERR_UNSUPPORTED, "complex_diagonal needs a dimension that is a multiple of 8 (got %d)", cfg->dim);
   if (cfg->comparator < PBG_CMP_DOT || cfg->comparator > PBG_CMP_SQUARED_L2) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown comparator %d", cfg->comparator);
@@ -190,6 +192,9 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   }
   oCoef[0] = take(nN * 4); oCoef[1] = take(nN * 4); oCoef[2] = take(nQ * 4); oCoef[3] = take(nQ * 4);
   size_t oRel = take(nblk * 8 * (size_t)cfg->dim * 4);
+  const size_t opw = matrix_op ? (size_t)cfg->dim * cfg->dim + (cfg->op == PBG_OP_AFFINE ? cfg->dim : 0) : (size_t)cfg->dim;
+  size_t oR1 = 0, oR2 = 0, oDA = 0;
+  if (matrix_op) { oR1 = take(nN * c->Dp * 4); oR2 = take(nN * c->Dp * 4); oDA = take((size_t)c->kmax * opw * 4); }
   size_t oK[2][2], oV[2][2], oH[2];
   for (int s = 0; s < 2; ++s) {
     oK[s][0] = take((size_t)nocc * 8); oK[s][1] = take((size_t)nocc * 8);
@@ -227,6 +232,9 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     b.violrow[p] = (int *)(c->ws + oViol[p]);
   }
   b.relpart = (float *)(c->ws + oRel);
+  b.R1 = matrix_op ? (float *)(c->ws + oR1) : nullptr;
+  b.R2 = matrix_op ? (float *)(c->ws + oR2) : nullptr;
+  b.dA = matrix_op ? (float *)(c->ws + oDA) : nullptr;
   for (int s = 0; s < 2; ++s) {
     c->sort[s].keys[0] = (unsigned long long *)(c->ws + oK[s][0]);
     c->sort[s].keys[1] = (unsigned long long *)(c->ws + oK[s][1]);
@@ -321,6 +329,8 @@ static int bind_bucket(pbg_context *c, const pbg_bucket *bk, WaveDims &d, WaveBu
   d.neg_enabled[0] = !cfg.disable_lhs_negs; d.neg_enabled[1] = !cfg.disable_rhs_negs;
   d.num_batch_negs = cfg.num_batch_negs; d.spb = c->spb; d.margin = cfg.margin;
   d.split = 0;
+  d.matrix_op = cfg.op == PBG_OP_LINEAR || cfg.op == PBG_OP_AFFINE;
+  d.opw = d.matrix_op ? cfg.dim * cfg.dim + (cfg.op == PBG_OP_AFFINE ? cfg.dim : 0) : cfg.dim;
   d.n_rows[0] = bk->lhs_rows; d.n_rows[1] = bk->rhs_rows;
   d.shared_table = bk->lhs_emb == bk->rhs_emb;
   if (d.shared_table && bk->lhs_rows != bk->rhs_rows) return fail(c, PBG_ERR_BAD_ARGUMENT, "shared table with different row counts");
@@ -348,7 +358,12 @@ static int check_errflag(pbg_context *c) {
 }
 
 static int run_forward(pbg_context *c, const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
-  { ClassTimer t(c, 1, st); t.done(launch_gather(d, wb, w, st)); }
+  {
+    ClassTimer t(c, 1, st);
+    int n = launch_gather(d, wb, w, st);
+    if (d.matrix_op) n += launch_matrix_forward(d, wb, w, st) + launch_postop(d, wb, w, st);   // z = A x (+ t), prepare, positive score
+    t.done(n);
+  }
   ClassTimer t(c, 2, st);
   if (c->cfg.precision == PBG_PREC_FP32) t.done(launch_score_simt(d, wb, w, st));
   else t.done(launch_score_tc(d, wb, w, c->tcplan, st));
@@ -360,8 +375,9 @@ static void run_part(pbg_context *c, const WaveDims &d, const WaveBatches &wb, c
   run_forward(c, d, wb, w, st);
   { ClassTimer t(c, 3, st); t.done(launch_loss(d, wb, w, st)); }
   ClassTimer t(c, 4, st);
-  if (c->cfg.precision == PBG_PREC_FP32) t.done(launch_grad_simt(d, wb, w, st));
-  else t.done(launch_grad_tc(d, wb, w, c->tcplan, st));
+  int n = c->cfg.precision == PBG_PREC_FP32 ? launch_grad_simt(d, wb, w, st) : launch_grad_tc(d, wb, w, c->tcplan, st);
+  if (d.matrix_op) n += launch_gz_rows(d, wb, w, st) + launch_matrix_backward(d, wb, w, st);   // back through A
+  t.done(n);
 }
 
 extern "C" int pbg_set_profiling(pbg_context *c, int enable) {

@@ -48,6 +48,8 @@ struct WaveDims {
   long long n_rows[2];  // rows of the lhs / rhs table
   int shared_table;     // lhs and rhs read the same table
   int num_rels;
+  int matrix_op;        // operator is linear / affine (standard relations): applied by contractions, not in the gather
+  int opw;              // floats per operator-table row: D, or D*D (+ D) for linear (affine)
   int split;            // TF32X3: operands and coefficient matrices are stored as hi + lo
   unsigned long long key_rel_base;   // first sort key of operator-table rows
   unsigned long long key_invalid;    // sort key of slots that carry no gradient
@@ -82,6 +84,9 @@ struct WaveBufs {
   unsigned long long seed;
   float *W[2], *G[2];                // embedding tables / RowAdagrad state (lhs, rhs)
   float *theta[2], *acc[2];          // operator tables: [0] applied to rhs rows, [1] to lhs rows
+  // linear / affine operators: R1 = raw rhs rows, R2 = A.x (forward) then g.A (backward), both laid
+  // out like N1; dA = per-batch gradient of the operator row [k][opw]
+  float *R1, *R2, *dA;
   float *relpart;                    // standard mode: [k][Cm][D] partial operator gradients
   int *errflag;                      // device error word (bit 0: id out of range)
 };
@@ -210,6 +215,11 @@ void pbg_tc_plan_destroy(void *plan);
 bool pbg_tc_available();
 int launch_score_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st);
 int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st);
+int launch_matrix_forward(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
+int launch_matrix_backward(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
+int launch_matrix_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, float lr, cudaStream_t st);
+int launch_postop(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
+int launch_gz_rows(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
 int launch_score_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
 int launch_grad_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
 int launch_loss(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);

@@ -143,6 +143,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     if (!ok) {                                              // padding row: exact zeros
       zero_row<VEC>(n0, D, lane);
       zero_row<VEC>(n1, D, lane);
+      if (d.matrix_op) zero_row<VEC>(w.R1 + noff, D, lane);
       if (d.dynamic) { zero_row<VEC>(q0, D, lane); zero_row<VEC>(q1, D, lane); }
       if (XL) {
         zero_row<VEC>(XL[ARR_N0] + noff, D, lane);
@@ -164,7 +165,13 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     for (int c = 0; c < VEC; ++c) y0[c] = x[c];
     float a0 = prepare_row<VEC>(y0, d.cmp);
     put_row<VEC>(w.X[ARR_N0], lo(ARR_N0), noff, y0, D, lane);
-    if (!d.dynamic) {
+    if (d.matrix_op) {
+      // linear / affine: the raw rhs row goes to R1; operator, prepare and the positive score
+      // follow in the contraction and postop_kernel
+      load_row<VEC>(x, xr, D, lane);
+      store_row<VEC>(w.R1 + noff, x, D, lane);
+      if (lane == 0) w.aux[ARR_N0][nrow] = a0;
+    } else if (!d.dynamic) {
       // rhs row through the operator -> N1; one positive score shared by both problems
       load_row<VEC>(x, xr, D, lane);
       apply_operator<VEC>(y1, x, xr, th0, d.op, D, lane);
@@ -210,11 +217,13 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     if (id < 0) {
       zero_row<VEC>(dst, D, lane);
       if (XL) zero_row<VEC>(XL[side] + noff, D, lane);
+      if (side == 1 && d.matrix_op) zero_row<VEC>(w.R1 + noff, D, lane);
       if (lane == 0) w.aux[side][nrow] = 0.f;
       continue;
     }
     const float *xrow = w.W[side] + (size_t)id * D;
     load_row<VEC>(x, xrow, D, lane);
+    if (side == 1 && d.matrix_op) { store_row<VEC>(w.R1 + noff, x, D, lane); continue; }
     const float *th = nullptr;
     if (side == 1 && !d.dynamic && d.op != PBG_OP_NONE && w.theta[0]) {
       int rl = wb.rel[bi.b];
@@ -225,6 +234,66 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     put_row<VEC>(w.X[side], lo(side), noff, z, D, lane);
     if (lane == 0) w.aux[side][nrow] = a;
   }
+}
+
+// linear / affine operators: R2 holds A.x for every rhs row of the chunk blocks; this kernel adds
+// the translation (affine), applies comparator.prepare, writes the operand row to N1 and, for the
+// chunk's edges, the positive score against the lhs row already in N0.
+template <int VEC>
+__global__ void __launch_bounds__(32 * GATHER_WARPS) postop_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * GATHER_WARPS + (threadIdx.x >> 5);
+  if (item >= (long long)d.nblk * d.Mm) return;
+  int lb = (int)(item / d.Mm), r = (int)(item - (long long)lb * d.Mm);
+  const int blk = d.blk0 + lb;
+  BlockInfo bi = block_info(d, wb, blk);
+  const int D = d.D;
+  size_t nrow = (size_t)blk * d.Mm + r, noff = nrow * d.Dp;
+  long long id = slot_row(d, wb, w, bi, 1, r);
+  bool ok = id >= 0 && id < d.n_rows[1];
+  if (ok && r < d.Pm) {                         // the edge's lhs id must be valid too (gather zeroed the rows otherwise)
+    long long il = w.lhs[bi.e0 + r];
+    ok = il >= 0 && il < d.n_rows[0];
+  }
+  float4 z[VEC], y0[VEC];
+  if (!ok) {
+    zero_row<VEC>(w.X[ARR_N1] + noff, D, lane);
+    if (lane == 0) {
+      w.aux[ARR_N1][nrow] = 0.f;
+      if (r < d.Pm) { size_t q = (size_t)blk * d.Pm + r; w.spos[0][q] = 0.f; w.spos[1][q] = 0.f; }
+    }
+    return;
+  }
+  load_row<VEC>(z, w.R2 + noff, D, lane);
+  if (d.op == PBG_OP_AFFINE) {
+    const float *t = w.theta[0] + (size_t)wb.rel[bi.b] * d.opw + (size_t)D * D;
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) {
+      int dd = c * 128 + lane * 4;
+      if (dd < D) z[c] = z[c] + ld4(t + dd);
+    }
+  }
+  float a1 = prepare_row<VEC>(z, d.cmp);
+  store_row<VEC>(w.X[ARR_N1] + noff, z, D, lane);
+  if (lane == 0) w.aux[ARR_N1][nrow] = a1;
+  if (r < d.Pm) {
+    load_row<VEC>(y0, w.X[ARR_N0] + noff, D, lane);
+    float s = positive_score<VEC>(y0, z, d.cmp);
+    size_t q = (size_t)blk * d.Pm + r;
+    if (lane == 0) { w.spos[0][q] = s; w.spos[1][q] = s; }
+  }
+}
+
+int launch_postop(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
+  long long items = (long long)d.nblk * d.Mm;
+  int ctas = (int)((items + GATHER_WARPS - 1) / GATHER_WARPS);
+  int vec = (d.D + 127) / 128;
+  if (vec <= 1) postop_kernel<1><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else if (vec <= 2) postop_kernel<2><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else if (vec <= 4) postop_kernel<4><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else if (vec <= 8) postop_kernel<8><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else postop_kernel<16><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  return 1;
 }
 
 int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {

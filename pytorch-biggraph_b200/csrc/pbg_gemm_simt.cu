@@ -10,6 +10,8 @@
 // operands staged through shared memory as [k][m] / [k][n] so that the inner product reads
 // 16-byte vectors without bank conflicts.  Either operand may be stored k-contiguous (transposed
 // while staging) or m/n-contiguous (copied as is).
+#include <cstring>
+
 #include "pbg_common.cuh"
 
 #define BN 64
@@ -18,6 +20,7 @@
 struct GemmTask {
   const float *A; long long a_blk; int lda;   // per-block stride (floats), leading dimension
   const float *B; long long b_blk; int ldb;
+  long long b_rel;                            // added to B per block: relation of the block's batch * b_rel (operator tables)
   float *C; long long c_blk; int ldc;
   int M, N, K;
   // score epilogue
@@ -39,7 +42,9 @@ __global__ void __launch_bounds__(256) gemm_tile_kernel(GemmTasks tasks, WaveDim
     if (SCORE && !d.neg_enabled[p]) return;         // no negatives on this side: nothing to score
   }
   const GemmTask &t = tasks.t[p];
+  if (t.M <= 0) return;
   const float *A = t.A + (size_t)blk * t.a_blk, *B = t.B + (size_t)blk * t.b_blk;
+  if (t.b_rel) B += (size_t)wb.rel[blk / d.Cm] * t.b_rel;
   float *C = t.C + (size_t)blk * t.c_blk;
   const int M = t.M, N = t.N, K = t.K;
   int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -170,6 +175,7 @@ int launch_score_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &
     t.B = w.X[n]; t.b_blk = (long long)w.xrows[n] * d.Dp; t.ldb = d.Dp;
     t.C = w.S[p]; t.c_blk = (long long)d.Pm * d.Ms; t.ldc = d.Ms;
     t.M = d.Pm; t.N = d.Mm; t.K = d.D;
+    t.b_rel = 0;
     t.auxA = w.aux[q]; t.auxa_blk = w.xrows[q];
     t.auxB = w.aux[n]; t.auxb_blk = w.xrows[n];
     t.cmp = d.cmp;
@@ -188,6 +194,7 @@ int launch_grad_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w
       t.B = w.X[o]; t.b_blk = (long long)w.xrows[o] * d.Dp; t.ldb = d.Dp;
       t.C = w.GX[ARR_N0 + side]; t.c_blk = (long long)d.Mm * d.Dp; t.ldc = d.Dp;
       t.M = d.Mm; t.N = d.D; t.K = d.Mm;
+      t.b_rel = 0;
       t.auxA = t.auxB = nullptr; t.auxa_blk = t.auxb_blk = 0; t.cmp = 0;
     }
     launch_tiles<true, false, false>(tm, d, wb, st);
@@ -201,15 +208,54 @@ int launch_grad_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w
     a.B = w.X[n]; a.b_blk = (long long)w.xrows[n] * d.Dp; a.ldb = d.Dp;
     a.C = w.GX[q]; a.c_blk = (long long)w.grows[q] * d.Dp; a.ldc = d.Dp;
     a.M = d.Pm; a.N = d.D; a.K = d.Mm;
+    a.b_rel = 0;
     a.auxA = a.auxB = nullptr; a.auxa_blk = a.auxb_blk = 0; a.cmp = 0;
     GemmTask &b = tn.t[p];       // GN_p = T_p^T . Q_p
     b.A = w.S[p]; b.a_blk = (long long)d.Pm * d.Ms; b.lda = d.Ms;
     b.B = w.X[q]; b.b_blk = (long long)w.xrows[q] * d.Dp; b.ldb = d.Dp;
     b.C = w.GX[n]; b.c_blk = (long long)w.grows[n] * d.Dp; b.ldc = d.Dp;
     b.M = d.Mm; b.N = d.D; b.K = d.Pm;
+    b.b_rel = 0;
     b.auxA = b.auxB = nullptr; b.auxa_blk = b.auxb_blk = 0; b.cmp = 0;
   }
   launch_tiles<true, false, false>(tq, d, wb, st);
   launch_tiles<false, false, false>(tn, d, wb, st);
+  return 2;
+}
+
+// ---- linear / affine operators (standard relations): the operator is a D x D matrix A per relation ----
+static void matrix_task(GemmTasks &ts, const float *A, long long a_blk, int lda, const float *B, long long b_blk, int ldb,
+                        long long b_rel, float *C, long long c_blk, int ldc, int M, int N, int K) {
+  memset(&ts, 0, sizeof ts);
+  GemmTask &t = ts.t[0];
+  t.A = A; t.a_blk = a_blk; t.lda = lda; t.B = B; t.b_blk = b_blk; t.ldb = ldb; t.b_rel = b_rel;
+  t.C = C; t.c_blk = c_blk; t.ldc = ldc; t.M = M; t.N = N; t.K = K;
+  ts.t[1] = t;
+  ts.t[1].M = 0;                                  // only "problem 0" does work
+}
+
+// R2[blk] (Mm x D) = R1[blk] (raw rhs rows) . A^T : z_i = sum_j A[i][j] x_j  (operators.py:88-99)
+int launch_matrix_forward(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
+  GemmTasks ts;
+  long long blk = (long long)d.Mm * d.Dp;
+  matrix_task(ts, w.R1, blk, d.Dp, w.theta[0], 0, d.D, d.opw, w.R2, blk, d.Dp, d.Mm, d.D, d.D);
+  launch_tiles<true, true, false>(ts, d, wb, st);
+  return 1;
+}
+
+// GN1 holds d(loss)/dz for every rhs row (after launch_gz_rows):
+//   R2[blk] = GN1[blk] . A          gradient w.r.t. the raw rows      (gx_j = sum_i gz_i A[i][j])
+//   dA[b]   = GN1[b]^T . R1[b]      gradient of the operator matrix   (dA[i][j] = sum_rows gz_i x_j), one product per batch
+int launch_matrix_backward(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
+  GemmTasks ts;
+  long long blk = (long long)d.Mm * d.Dp;
+  matrix_task(ts, w.GX[ARR_N1], blk, d.Dp, w.theta[0], 0, d.D, d.opw, w.R2, blk, d.Dp, d.Mm, d.D, d.D);
+  launch_tiles<true, false, false>(ts, d, wb, st);
+  // per batch: treat the Cm chunk blocks of a batch as one block of Cm*Mm rows
+  WaveDims db = d;
+  db.Cm = 1; db.blk0 = d.blk0 / d.Cm; db.nblk = d.nblk / d.Cm;
+  long long bstride = (long long)d.Cm * d.Mm * d.Dp;
+  matrix_task(ts, w.GX[ARR_N1], bstride, d.Dp, w.R1, bstride, d.Dp, 0, w.dA, d.opw, d.D, d.D, d.D, d.Cm * d.Mm);
+  launch_tiles<false, false, false>(ts, db, wb, st);
   return 2;
 }

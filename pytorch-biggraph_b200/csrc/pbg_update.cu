@@ -25,14 +25,26 @@ struct SlotGrad {
   int op, cmp, D;
 
   // gstage: the gradient row already staged in shared memory (null: read it from global memory)
+  // pre_op: (linear / affine only) stop at the operator output instead of reading the finished
+  //         gradient of the raw row from R2
   __device__ __forceinline__ void init(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
-                                       int a, int blk, int r, int b, int lane, const float *gstage = nullptr) {
+                                       int a, int blk, int r, int b, int lane, const float *gstage = nullptr,
+                                       bool pre_op = false) {
     D = d.D; op = d.op; cmp = d.cmp;
     size_t xr = (size_t)blk * w.xrows[a] + r, gr = (size_t)blk * w.grows[a] + r;
     y = w.X[a] + xr * d.Dp;
     ylo = d.split ? w.XL[a] + xr * d.Dp : nullptr;
     g = gstage ? gstage : w.GX[a] + gr * d.Dp;
     theta = nullptr;
+    cf = 0.f; inv = 1.f; dotgy = 0.f;
+    if (d.matrix_op) {
+      op = PBG_OP_NONE;
+      if (a == ARR_N1 && !pre_op) {            // R2 already holds d(loss)/d(raw row)
+        if (!gstage) g = w.R2 + gr * d.Dp;
+        cmp = PBG_CMP_DOT;
+        return;
+      }
+    }
     if (op != PBG_OP_NONE) {
       if (!d.dynamic) {
         if ((a == ARR_N1 || a == ARR_Q0) && w.theta[0]) theta = w.theta[0] + (size_t)wb.rel[b] * D;
@@ -43,7 +55,6 @@ struct SlotGrad {
         if (tab && rl >= 0 && rl < d.num_rels) theta = tab + (size_t)rl * D;
       }
     }
-    cf = 0.f; inv = 1.f; dotgy = 0.f;
     if (cmp >= PBG_CMP_L2) {
       // dynamic: ga = T.N - rowsum(T) a ;  gb = T^T.Q - colsum(T) b.  standard: g = A.N' - rowsum(A) y
       const float *cp = (a == ARR_N0) ? w.coef[0] : (a == ARR_N1) ? w.coef[1] : (a == ARR_Q0) ? w.coef[2] : w.coef[3];
@@ -261,7 +272,8 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
     __syncwarp();
     if (lane < cnt) {
       Occ oc = occ_decode(d, (int)v);
-      const float *g = w.GX[oc.a] + ((size_t)oc.blk * w.grows[oc.a] + oc.r) * d.Dp;
+      const float *gbase = (d.matrix_op && oc.a == ARR_N1) ? w.R2 : w.GX[oc.a];
+      const float *g = gbase + ((size_t)oc.blk * w.grows[oc.a] + oc.r) * d.Dp;
       uint32_t dst = (uint32_t)__cvta_generic_to_shared(stage + (size_t)lane * d.Dp);
       asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                    :: "r"(dst), "l"(g), "r"((uint32_t)(d.D * 4)), "r"(bar) : "memory");
@@ -391,13 +403,25 @@ hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long lo
       float4 acc[VEC];
 #pragma unroll
       for (int c = 0; c < VEC; ++c) acc[c] = f4zero();
-      for (long long r = 0; r < nruns; ++r) {
-        long long start = r == 0 ? q : ftb + (r - 1) * TILE;
-        const float *src = psum + (size_t)start * d.Dp;
+      // four partial rows in flight at a time; they are still added in run order
+      for (long long r0 = 0; r0 < nruns; r0 += 4) {
+        const float *src[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          long long r = r0 + u;
+          long long start = r == 0 ? q : ftb + (r - 1) * TILE;
+          src[u] = r < nruns ? psum + (size_t)start * d.Dp : nullptr;
+        }
 #pragma unroll
         for (int c = 0; c < VEC; ++c) {
           int dd = c * 128 + lane * 4;
-          if (dd < D) acc[c] = acc[c] + ld4(src + dd);
+          if (dd < D) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = src[u] ? ld4(src[u] + dd) : f4zero();
+#pragma unroll
+            for (int u = 0; u < 4; ++u) acc[c] = acc[c] + v[u];
+          }
         }
       }
 #pragma unroll
@@ -475,6 +499,82 @@ __global__ void relupdate_std_kernel(WaveDims d, WaveBatches wb, WaveBufs w, flo
   }
 }
 
+// linear / affine operators: turns GN1 rows (gradient w.r.t. the prepared operand) into the
+// gradient w.r.t. the operator output, in place; slots without a row get zeros.  The two
+// contractions of launch_matrix_backward read the result.
+template <int VEC>
+__global__ void __launch_bounds__(32 * UPD_WARPS) gz_rows_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * UPD_WARPS + (threadIdx.x >> 5);
+  if (item >= (long long)d.nblk * d.Mm) return;
+  int lb = (int)(item / d.Mm), r = (int)(item - (long long)lb * d.Mm);
+  const int blk = d.blk0 + lb;
+  BlockInfo bi = block_info(d, wb, blk);
+  const int D = d.D;
+  float *row = w.GX[ARR_N1] + ((size_t)blk * d.Mm + r) * d.Dp;
+  long long id = slot_row(d, wb, w, bi, 1, r);
+  float4 v[VEC];
+  if (id < 0 || id >= d.n_rows[1]) {
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) v[c] = f4zero();
+  } else {
+    SlotGrad<VEC> sg;
+    sg.init(d, wb, w, ARR_N1, blk, r, bi.b, lane, nullptr, true);
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) {
+      int dd = c * 128 + lane * 4;
+      v[c] = dd < D ? sg.gz(dd) : f4zero();
+    }
+  }
+  __syncwarp();
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int dd = c * 128 + lane * 4;
+    if (dd < D) st4(row + dd, v[c]);
+  }
+}
+
+int launch_gz_rows(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
+  long long items = (long long)d.nblk * d.Mm;
+  int ctas = (int)((items + UPD_WARPS - 1) / UPD_WARPS);
+  int vec = (d.D + 127) / 128;
+#define GZ(V) gz_rows_kernel<V><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w)
+  if (vec <= 1) GZ(1); else if (vec <= 2) GZ(2); else if (vec <= 4) GZ(4); else if (vec <= 8) GZ(8); else GZ(16);
+#undef GZ
+  return 1;
+}
+
+// AsyncAdagrad on the matrix (and translation) of the batch's relation, batch by batch
+// (async_adagrad.py:75-85).  dA[b] comes from launch_matrix_backward; the gradient of an affine
+// translation is the column sum of the batch's GN1 rows.
+__global__ void relupdate_matrix_kernel(WaveDims d, WaveBatches wb, WaveBufs w, float lr) {
+  long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= d.opw) return;
+  const long long DD = (long long)d.D * d.D;
+  for (int b = 0; b < d.k; ++b) {
+    if (wb.n[b] <= 0) continue;
+    int rl = wb.rel[b];
+    if (rl < 0 || rl >= d.num_rels) continue;
+    float g;
+    if (e < DD) g = w.dA[(size_t)b * d.opw + e];
+    else {
+      int dd = (int)(e - DD);
+      g = 0.f;
+      const float *rows = w.GX[ARR_N1] + (size_t)b * d.Cm * d.Mm * d.Dp + dd;
+      for (int r = 0; r < d.Cm * d.Mm; ++r) g += rows[(size_t)r * d.Dp];
+    }
+    size_t idx = (size_t)rl * d.opw + e;
+    float a = w.acc[0][idx] + g * g;
+    w.acc[0][idx] = a;
+    w.theta[0][idx] -= lr * g / (sqrtf(a) + PBG_ADAGRAD_EPS);
+  }
+}
+
+int launch_matrix_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, float lr, cudaStream_t st) {
+  relupdate_matrix_kernel<<<(d.opw + 255) / 256, 256, 0, st>>>(d, wb, w, lr);
+  return 1;
+}
+
 struct UpdateScratch { float *psum; long long *hublist; int *hubcnt; };
 
 template <int VEC>
@@ -493,7 +593,7 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   size_t hub_smem_max = (size_t)PBG_KMAX * VEC * 128 * sizeof(float);
   if (hub_smem_max > 227 * 1024) hub_smem_max = 227 * 1024;
   bool has_op = d.op != PBG_OP_NONE && w.theta[0] != nullptr;
-  if (has_op && !d.dynamic) {
+  if (has_op && !d.dynamic && !d.matrix_op) {
     relgrad_std_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, 0, st>>>(d, wb, w);
     ++launches;
   }
@@ -517,6 +617,8 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
       tile_update_kernel<VEC, RULE_REL><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
       hub_update_kernel<VEC, RULE_REL><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
       launches += 2;
+    } else if (d.matrix_op) {
+      launches += launch_matrix_update(d, wb, w, rel_lr, st);
     } else {
       relupdate_std_kernel<<<(d.D + 127) / 128, 128, 0, st>>>(d, wb, w, rel_lr);
       ++launches;

@@ -42,6 +42,8 @@ class MultiRelationEmbedder:
         if self.comparator.native_code is None:
             raise NotImplementedError(f"comparator '{config.comparator}' has no device code")
         op_name = config.relations[0].operator
+        if config.dynamic_relations and op_name in ("linear", "affine"):
+            raise NotImplementedError(f"operator '{op_name}' with dynamic relations has no device code (and no CPU fallback)")
         self.operator_name = op_name
         D = config.dimension
         rows = self.num_dynamic_rels if config.dynamic_relations else len(config.relations)
@@ -52,7 +54,8 @@ class MultiRelationEmbedder:
             raise NotImplementedError(f"operator '{op_name}' has no device code")
         proto = op_cls(D, rows) if config.dynamic_relations else op_cls(D)
         init = proto.init_table(rows)
-        # one [num_rels, dim] table per side; standard relations only have the rhs one
+        # one [num_rels, width] table per side (width = dim; dim*dim (+dim) for linear (affine));
+        # standard relations only have the rhs one
         self.rhs_op_table: Optional[torch.Tensor] = None if init is None else init.to(self.device)
         self.lhs_op_table: Optional[torch.Tensor] = (
             None if init is None or not config.dynamic_relations else init.clone().to(self.device))

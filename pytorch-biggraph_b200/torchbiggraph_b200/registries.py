@@ -58,7 +58,18 @@ def _complex_init(rows, dim):
     return t
 
 
-_INIT = {"none": lambda r, d: None, "diagonal": _ones, "translation": _zeros, "complex_diagonal": _complex_init}
+def _linear_init(rows, dim):
+    # one row-major D x D matrix per relation, identity at the start (operators.py:91-92)
+    return torch.eye(dim, dtype=torch.float32).reshape(1, -1).repeat(rows, 1)
+
+
+def _affine_init(rows, dim):
+    # [matrix | translation], identity and zero at the start (operators.py:105-107)
+    return torch.cat([_linear_init(rows, dim), torch.zeros((rows, dim), dtype=torch.float32)], dim=1)
+
+
+_INIT = {"none": lambda r, d: None, "diagonal": _ones, "translation": _zeros, "complex_diagonal": _complex_init,
+         "linear": _linear_init, "affine": _affine_init}
 
 
 def _make(name, base, registry):

@@ -59,7 +59,7 @@ def test_config_validation_precedes_device_use():
     assert b"multiple of 4" in L.pbg_last_error(ctx)
     L.pbg_destroy(ctx)
     lin = _lib.PbgConfig(dim=16, op=4, comparator=0, loss=1, num_rels=1, num_batch_negs=4, num_uniform_negs=4,
-                         max_batch_size=8, batches_in_flight=1)
+                         max_batch_size=8, batches_in_flight=1, dynamic_relations=1)      # one matrix per edge: refused
     assert L.pbg_create(ctypes.byref(lin), 0, None, ctypes.byref(ctx)) == _lib.PBG_ERR_UNSUPPORTED
     L.pbg_destroy(ctx)
     k0 = _lib.PbgConfig(dim=16, op=0, comparator=0, loss=1, num_rels=1, num_batch_negs=4, num_uniform_negs=4,

@@ -10,7 +10,7 @@ from oracle import pbg_step as O
 pytestmark = pytest.mark.gpu
 
 RTOL = 1e-4
-DEVICE_OPS = ("none", "diagonal", "translation", "complex_diagonal")
+DEVICE_OPS = ("none", "diagonal", "translation", "complex_diagonal", "linear", "affine")
 
 
 def _supported(c):
@@ -313,6 +313,6 @@ def test_out_of_range_ids_are_reported_not_followed():
 def test_unsupported_plugins_raise():
     import torchbiggraph_b200 as T
     cfg = T.ConfigSchema(entities={"e": T.EntitySchema()}, relations=[T.RelationSchema("r", "e", "e", operator="linear")],
-                         dimension=16)
+                         dimension=16, dynamic_relations=True, num_dynamic_rels=3)
     with pytest.raises(NotImplementedError):
         T.make_model(cfg, "cuda")
