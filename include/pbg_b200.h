@@ -166,6 +166,20 @@ int pbg_score_batch(pbg_context *ctx, const pbg_bucket *bucket,
 int pbg_neg_columns(const pbg_context *ctx, int32_t count, int32_t *chunk_size, int32_t *chunks,
                     int32_t *lhs_neg_cols, int32_t *rhs_neg_cols);
 
+/* Evaluation of one batch: RankingEvaluator._process_one_batch (torchbiggraph/eval.py:43-81).
+ * Forward pass as pbg_score_batch, then per side rank = 1 + #(neg >= pos) of every edge, and the
+ * Stats the reference returns, as sums over the batch (the caller averages over count, as
+ * Stats.average does): loss (calc_loss, batching.py:139-150), pos_rank, mrr, r1, r10, r50 are the
+ * mean over the enabled sides of the per-side sums (average_of_sums, stats.py:19-20); auc is
+ * count x the mean of the per-side randomized AUCs (util.py:415-428: `count` random
+ * positive / negative pairs per side, drawn on the device from `seed`).  Nothing is updated. */
+typedef struct { float loss; double pos_rank, mrr, r1, r10, r50, auc; int64_t count; } pbg_eval_stats;
+int pbg_eval_batch(pbg_context *ctx, const pbg_bucket *bucket,
+                   const int64_t *lhs_dev, const int64_t *rhs_dev, const int64_t *rel_dev,
+                   int32_t count, int32_t rel,
+                   const int64_t *uniform_lhs_dev, const int64_t *uniform_rhs_dev, uint64_t seed,
+                   pbg_eval_stats *stats_out);
+
 /* The sparse-row optimizer step alone: RowAdagrad.step on a sparse gradient
  * (torchbiggraph/row_adagrad.py:80-96).  rows: device int64 [n] (duplicates allowed, they are
  * summed first), grads: device float32 [n, dim]. */

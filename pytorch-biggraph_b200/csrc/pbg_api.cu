@@ -28,6 +28,7 @@ struct pbg_context {
   pbg_batch_stats *stats_dev = nullptr;
   int stats_cap = 0;
   double *sum_dev = nullptr;
+  double *eval_dev = nullptr;
   int *errflag = nullptr;
   void *tcplan = nullptr;       // tensor maps of the tcgen05 contractions
   float *psum = nullptr;        // partial gradient rows of hub rows, indexed by slot position
@@ -164,7 +165,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   // ---- carve the workspace ------------------------------------------------------------------
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
-  size_t oX[4], oAux[4], oG[4], oS[2], oSpos[2], oCoef[4], oLoss[2], oViol[2], oXL[4] = {0, 0, 0, 0}, oSL[2] = {0, 0};
+  size_t oX[4], oAux[4], oG[4], oS[2], oSpos[2], oCoef[4], oLoss[2], oViol[2], oRank[2], oXL[4] = {0, 0, 0, 0}, oSL[2] = {0, 0};
   const bool split = false;   // TF32X3 splits operands inside the contraction kernel: no low-part arrays
   oX[0] = take(nN * c->Dp * 4); oX[1] = take(nN * c->Dp * 4);
   oAux[0] = take(nN * 4); oAux[1] = take(nN * 4);
@@ -189,6 +190,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   }
   for (int p = 0; p < 2; ++p) {
     oS[p] = take(nQ * c->Ms * 4); oSpos[p] = take(nQ * 4); oLoss[p] = take(nQ * 4); oViol[p] = take(nQ * 4);
+    oRank[p] = take(nQ * 4);
   }
   oCoef[0] = take(nN * 4); oCoef[1] = take(nN * 4); oCoef[2] = take(nQ * 4); oCoef[3] = take(nQ * 4);
   size_t oRel = take(nblk * 8 * (size_t)cfg->dim * 4);
@@ -201,7 +203,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     oV[s][0] = take((size_t)nocc * 4); oV[s][1] = take((size_t)nocc * 4);
     oH[s] = take(pbg_sort_hist_entries((int)nocc) * 4);
   }
-  size_t oSum = take(4 * sizeof(double)), oErr = take(256);
+  size_t oSum = take(4 * sizeof(double)), oErr = take(256), oEval = take(8 * sizeof(double));
   size_t oPsum = take((size_t)nocc * c->Dp * 4), oHub = take(((size_t)nocc / 8 + 64) * 8), oHubCnt = take(256);
   c->ws_bytes = off;
   CU(c, cudaMalloc(&c->ws, c->ws_bytes));
@@ -230,6 +232,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     b.spos[p] = (float *)(c->ws + oSpos[p]);
     b.lossrow[p] = (float *)(c->ws + oLoss[p]);
     b.violrow[p] = (int *)(c->ws + oViol[p]);
+    b.rankrow[p] = (int *)(c->ws + oRank[p]);
   }
   b.relpart = (float *)(c->ws + oRel);
   b.R1 = matrix_op ? (float *)(c->ws + oR1) : nullptr;
@@ -253,6 +256,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   CU(c, cudaEventCreateWithFlags(&c->ev_part2, cudaEventDisableTiming));
   c->sum_dev = (double *)(c->ws + oSum);
   c->errflag = (int *)(c->ws + oErr);
+  c->eval_dev = (double *)(c->ws + oEval);
   b.errflag = c->errflag;
   c->psum = (float *)(c->ws + oPsum);
   c->hublist = (long long *)(c->ws + oHub);
@@ -576,6 +580,44 @@ extern "C" int pbg_score_batch(pbg_context *c, const pbg_bucket *bk, const int64
   c->launches += launch_export_scores(d, wb, w, lhs_pos, rhs_pos, lhs_neg, rhs_neg, c->stream);
   CU(c, cudaGetLastError());
   return check_errflag(c);
+}
+
+extern "C" int pbg_eval_batch(pbg_context *c, const pbg_bucket *bk, const int64_t *lhs, const int64_t *rhs,
+                              const int64_t *rel, int32_t count, int32_t relidx, const int64_t *ul, const int64_t *ur,
+                              uint64_t seed, pbg_eval_stats *out) {
+  if (!c || !out) return PBG_ERR_BAD_ARGUMENT;
+  memset(out, 0, sizeof *out);
+  if (count == 0) return PBG_OK;
+  if (!lhs || !rhs || count < 0 || count > c->cfg.max_batch_size)
+    return fail(c, PBG_ERR_BAD_ARGUMENT, "bad eval_batch arguments (count %d, max_batch_size %d)", count, c->cfg.max_batch_size);
+  CU(c, cudaSetDevice(c->device));
+  WaveDims d;
+  WaveBufs w;
+  int rc = bind_bucket(c, bk, d, w);
+  if (rc) return rc;
+  if (!d.dynamic && (relidx < 0 || relidx >= c->cfg.num_rels)) return fail(c, PBG_ERR_INDEX_RANGE, "relation %d outside [0, %d)", relidx, c->cfg.num_rels);
+  if (d.dynamic && d.op != PBG_OP_NONE && !rel) return fail(c, PBG_ERR_BAD_ARGUMENT, "dynamic relations need the rel array");
+  w.lhs = (const long long *)lhs; w.rhs = (const long long *)rhs; w.rel = (const long long *)rel;
+  w.ul = (const long long *)ul; w.ur = (const long long *)ur; w.seed = seed;
+  WaveBatches wb;
+  memset(&wb, 0, sizeof wb);
+  wb.n[0] = count; wb.rel[0] = d.dynamic ? 0 : relidx;
+  wb.wrel[0] = bk->relation_weights ? bk->relation_weights[d.dynamic ? 0 : relidx] : 1.0f;
+  d.k = 1; d.nblk = d.Cm; d.nocc = d.spb; d.blk0 = 0;
+  run_forward(c, d, wb, w, c->stream);
+  c->launches += launch_eval(d, wb, w, c->eval_dev, c->stream);
+  CU(c, cudaGetLastError());
+  double h[8];
+  CU(c, cudaMemcpyAsync(h, c->eval_dev, sizeof h, cudaMemcpyDeviceToHost, c->stream));
+  rc = check_errflag(c);
+  int sides = (d.neg_enabled[0] ? 1 : 0) + (d.neg_enabled[1] ? 1 : 0);
+  double div = sides > 0 ? sides : 1;
+  // the reference averages the two sides' sums (average_of_sums) and averages the two AUCs
+  out->loss = (float)h[0];
+  out->pos_rank = h[1] / div; out->mrr = h[2] / div; out->r1 = h[3] / div; out->r10 = h[4] / div; out->r50 = h[5] / div;
+  out->auc = sides > 0 ? (h[6] + h[7]) / div : 0.0;          // = count * mean(side AUCs): averaged over count by the caller
+  out->count = count;
+  return rc;
 }
 
 extern "C" int pbg_row_adagrad(pbg_context *c, float *emb, float *state, int64_t num_rows, const int64_t *rows,

@@ -79,6 +79,7 @@ struct WaveBufs {
   float *coef[4];                    // l2: colsum(T0), colsum(T1), rowsum(T0), rowsum(T1)
   float *lossrow[2];                 // per positive row: weighted loss term
   int *violrow[2];                   // per positive row: #(neg > pos)
+  int *rankrow[2];                   // evaluation: per positive row, 1 + #(neg >= pos)
   const long long *lhs, *rhs, *rel;  // edge arrays
   const long long *ul, *ur;          // uniform ids [batches][Cm][U] or null
   unsigned long long seed;
@@ -228,6 +229,7 @@ int launch_export_scores(const WaveDims &d, const WaveBatches &wb, const WaveBuf
 int launch_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                   const unsigned long long *keys, const unsigned int *vals, float lr, float rel_lr,
                   float *psum, long long *hublist, int *hubcnt, cudaStream_t st);
+int launch_eval(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, double *out8_dev, cudaStream_t st);
 int launch_stats(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                  pbg_batch_stats *per_batch_dev, double *sum_dev, cudaStream_t st);
 int launch_row_adagrad_sorted(float *emb, float *state, int dim, const unsigned long long *keys,

@@ -293,3 +293,89 @@ int launch_export_scores(const WaveDims &d, const WaveBatches &wb, const WaveBuf
   export_scores_kernel<<<g, 128, 0, st>>>(d, wb, w, lhs_pos, rhs_pos, lhs_neg, rhs_neg);
   return 1;
 }
+
+// ---- evaluation (RankingEvaluator, torchbiggraph/eval.py:43-81), one batch at a time -------------
+// rank of every positive among its negatives, before the loss kernel turns S into coefficients
+__global__ void __launch_bounds__(32 * LOSS_WARPS) rank_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * LOSS_WARPS + (threadIdx.x >> 5);
+  long long per_prob = (long long)d.nblk * d.Pm;
+  if (item >= 2 * per_prob) return;
+  int p = (int)(item / per_prob);
+  long long rem = item - p * per_prob;
+  int blk = (int)(rem / d.Pm), i = (int)(rem - (long long)blk * d.Pm);
+  BlockInfo bi = block_info(d, wb, blk);
+  size_t prow = (size_t)blk * d.Pm + i;
+  if (i >= bi.n || !d.neg_enabled[p]) { if (lane == 0) w.rankrow[p][prow] = 0; return; }
+  const float *S = w.S[p] + prow * d.Ms;
+  const float s = w.spos[p][prow];
+  int ge = 0;
+  for (int j = lane; j < d.Mm; j += 32) {
+    if (j < d.Pm && (!d.batch_negs || j >= bi.Pl)) continue;             // column does not exist in the reference's matrix
+    float v = col_masked(d, bi, 1, i, j) ? PBG_MASKED : S[j];
+    ge += v >= s;
+  }
+  ge = warp_sum_int(ge);
+  if (lane == 0) w.rankrow[p][prow] = ge + 1;
+}
+
+// randomized AUC (torchbiggraph/util.py:415-428): `count` random (positive, negative) pairs per side
+__global__ void auc_kernel(WaveDims d, WaveBatches wb, WaveBufs w, double *out8) {
+  int p = blockIdx.y;
+  int smp = blockIdx.x * blockDim.x + threadIdx.x;
+  int count = wb.n[0];
+  if (smp >= count || !d.neg_enabled[p]) return;
+  BlockInfo b0 = block_info(d, wb, 0);
+  int Pl = b0.Pl, cols = d.batch_negs ? Pl + d.U : d.U;
+  if (Pl == 0 || cols == 0) return;
+  unsigned long long h = pbg_mix64(w.seed ^ pbg_mix64(0xA0C0FFEEull + (unsigned long long)p * 0x10001ull + smp));
+  int ei = (int)(h % (unsigned long long)count);
+  h = pbg_mix64(h);
+  long long flat = (long long)(h % ((unsigned long long)count * cols));
+  int er = (int)(flat / cols), j = (int)(flat - (long long)er * cols);
+  int src = d.batch_negs ? (j < Pl ? j : d.Pm + (j - Pl)) : d.Pm + j;
+  int c = er / Pl, i = er - c * Pl;
+  BlockInfo bi = block_info(d, wb, c);
+  float neg = col_masked(d, bi, 1, i, src) ? PBG_MASKED : w.S[p][((size_t)c * d.Pm + i) * d.Ms + src];
+  float pos = w.spos[p][(size_t)(ei / Pl) * d.Pm + (ei % Pl)];
+  if (pos > neg) atomicAdd(&out8[6 + 0], p == 0 ? 1.0 : 0.0), atomicAdd(&out8[7], p == 1 ? 1.0 : 0.0);
+}
+
+// out8: loss, pos_rank, mrr, r1, r10, r50 (sums over both sides' ranks), then AUC hit counts per side
+__global__ void __launch_bounds__(256) eval_reduce_kernel(WaveDims d, WaveBatches wb, WaveBufs w, double *out8) {
+  __shared__ double sm[6][256];
+  int t = threadIdx.x;
+  double acc[6] = {0, 0, 0, 0, 0, 0};
+  int rows = d.Cm * d.Pm;
+  for (int r = t; r < rows; r += 256) {
+    int c = r / d.Pm, i = r - c * d.Pm;
+    BlockInfo bi = block_info(d, wb, c);
+    if (i >= bi.n) continue;
+    size_t prow = (size_t)c * d.Pm + i;
+    acc[0] += (double)w.lossrow[0][prow] + (double)w.lossrow[1][prow];
+    for (int p = 0; p < 2; ++p) {
+      int rk = w.rankrow[p][prow];
+      if (rk <= 0) continue;
+      acc[1] += rk; acc[2] += 1.0 / rk; acc[3] += rk <= 1; acc[4] += rk <= 10; acc[5] += rk <= 50;
+    }
+  }
+  for (int k = 0; k < 6; ++k) sm[k][t] = acc[k];
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (t < o) for (int k = 0; k < 6; ++k) sm[k][t] += sm[k][t + o];
+    __syncthreads();
+  }
+  if (t < 6) out8[t] = sm[t][0];
+}
+
+// call order: gather, score, launch_eval_ranks (this), launch_loss, launch_eval_reduce
+int launch_eval(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, double *out8_dev, cudaStream_t st) {
+  long long items = 2ll * d.nblk * d.Pm;
+  cudaMemsetAsync(out8_dev, 0, 8 * sizeof(double), st);
+  rank_kernel<<<(int)((items + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+  dim3 g((wb.n[0] + 127) / 128, 2);
+  auc_kernel<<<g, 128, 0, st>>>(d, wb, w, out8_dev);
+  loss_kernel<<<(int)((items + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+  eval_reduce_kernel<<<1, 256, 0, st>>>(d, wb, w, out8_dev);
+  return 4;
+}

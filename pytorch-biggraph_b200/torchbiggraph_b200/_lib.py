@@ -42,6 +42,10 @@ class PbgBatchStats(C.Structure):
                 ("violators_rhs", C.c_int64), ("count", C.c_int64)]
 
 
+class PbgEvalStats(C.Structure):
+    _fields_ = [("loss", C.c_float)] + [(n, C.c_double) for n in ("pos_rank", "mrr", "r1", "r10", "r50", "auc")] + [("count", C.c_int64)]
+
+
 # every symbol include/pbg_b200.h declares: (name, restype, argtypes)
 _P = C.c_void_p
 SYMBOLS = [
@@ -59,6 +63,8 @@ SYMBOLS = [
     ("pbg_read_stats", C.c_int, [_P, C.POINTER(PbgBatchStats)]),
     ("pbg_score_batch", C.c_int, [_P, C.POINTER(PbgBucket), _P, _P, _P, C.c_int32, C.c_int32, _P, _P,
                                   C.c_uint64, _P, _P, _P, _P]),
+    ("pbg_eval_batch", C.c_int, [_P, C.POINTER(PbgBucket), _P, _P, _P, C.c_int32, C.c_int32, _P, _P,
+                                 C.c_uint64, C.POINTER(PbgEvalStats)]),
     ("pbg_neg_columns", C.c_int, [_P, C.c_int32] + [C.POINTER(C.c_int32)] * 4),
     ("pbg_row_adagrad", C.c_int, [_P, _P, _P, C.c_int64, _P, _P, C.c_int32, C.c_float]),
     ("pbg_row_adagrad_static", C.c_int, [_P, _P, C.c_int64, C.c_int32, _P, _P, C.c_int32, C.c_float, _P]),

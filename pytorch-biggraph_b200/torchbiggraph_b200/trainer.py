@@ -27,7 +27,8 @@ class _Native:
     """One library context bound to a model's static configuration."""
 
     def __init__(self, model: MultiRelationEmbedder, max_batch: int, k: int, precision: str, lr: float,
-                 relation_lr: Optional[float], margin: float, loss_code: Optional[int] = None):
+                 relation_lr: Optional[float], margin: float, loss_code: Optional[int] = None,
+                 num_batch_negs: Optional[int] = None, num_uniform_negs: Optional[int] = None):
         cfg = model.config
         if model.device.type != "cuda":
             raise RuntimeError("torchbiggraph_b200 runs on a CUDA device only (no CPU fallback)")
@@ -39,8 +40,8 @@ class _Native:
         c.loss = _lib.LOSS_CODES[cfg.loss_fn] if loss_code is None else loss_code
         c.dynamic_relations = int(cfg.dynamic_relations)
         c.num_rels = model.num_rels
-        c.num_batch_negs = cfg.num_batch_negs
-        c.num_uniform_negs = cfg.num_uniform_negs
+        c.num_batch_negs = cfg.num_batch_negs if num_batch_negs is None else num_batch_negs
+        c.num_uniform_negs = cfg.num_uniform_negs if num_uniform_negs is None else num_uniform_negs
         c.disable_lhs_negs = int(cfg.disable_lhs_negs)
         c.disable_rhs_negs = int(cfg.disable_rhs_negs)
         c.precision = _lib.PRECISION_CODES[precision]
@@ -262,6 +263,68 @@ class B200Trainer(AbstractBatchProcessor):
     def process_one_batch(self, model, batch_edges, uniform_lhs=None, uniform_rhs=None) -> Stats:
         if self.overrides is not None:
             raise NotImplementedError("model overrides are not supported by torchbiggraph_b200")
+        return self._process_one_batch(model, batch_edges, uniform_lhs, uniform_rhs)
+
+
+class B200RankingEvaluator(AbstractBatchProcessor):
+    """RankingEvaluator (torchbiggraph/eval.py:43-81) on the device: per batch the forward pass, the
+    rank of every positive among its negatives on both sides, and Stats(loss, pos_rank, mrr, r1,
+    r10, r50, auc, count) as sums the caller averages with Stats.average().  `overrides` takes the
+    two keys the reference's evaluator overrides on the model (eval.py:165-172): num_batch_negs and
+    num_uniform_negs."""
+
+    def __init__(self, loss_fn: AbstractLossFunction, relation_weights: List[float], overrides=None):
+        super().__init__(loss_fn, relation_weights, None)
+        if getattr(loss_fn, "native_code", None) is None:
+            raise NotImplementedError(f"loss function {type(loss_fn).__name__} has no device code (no CPU fallback)")
+        unknown = set(overrides or {}) - {"num_batch_negs", "num_uniform_negs"}
+        if unknown:
+            raise NotImplementedError(f"model overrides {sorted(unknown)} are not supported by torchbiggraph_b200")
+        self.neg_overrides = dict(overrides or {})
+        self._native: Optional[_Native] = None
+        self._key = None
+        self.seed = 0
+        self._calls = 0
+
+    def _context(self, model, need_batch):
+        key = (id(model),)
+        if self._native is None or self._key != key or self._native.max_batch < need_batch:
+            cfg = model.config
+            self._native = _Native(model, max(cfg.batch_size, need_batch), 1, cfg.precision, cfg.lr, cfg.relation_lr,
+                                   getattr(self.loss_fn, "margin", cfg.margin), loss_code=self.loss_fn.native_code,
+                                   num_batch_negs=self.neg_overrides.get("num_batch_negs"),
+                                   num_uniform_negs=self.neg_overrides.get("num_uniform_negs"))
+            self._key = key
+        return self._native
+
+    def _process_one_batch(self, model: MultiRelationEmbedder, batch_edges: EdgeList, uniform_lhs=None, uniform_rhs=None) -> Stats:
+        dyn = model.num_dynamic_rels > 0
+        if dyn and batch_edges.has_scalar_relation_type():
+            raise TypeError("Need relation for each positive pair")
+        if not dyn and not batch_edges.has_scalar_relation_type():
+            raise TypeError("All positive pairs must come from the same relation")
+        n = len(batch_edges)
+        if n == 0:
+            return Stats(loss=0.0, pos_rank=0.0, mrr=0.0, r1=0.0, r10=0.0, r50=0.0, auc=0.0, count=0)
+        dev = model.device
+        nat = self._context(model, n)
+        lhs = batch_edges.lhs.to_tensor().to(dev).contiguous()
+        rhs = batch_edges.rhs.to_tensor().to(dev).contiguous()
+        rel = batch_edges.rel.to(dev).contiguous() if dyn else None
+        r = 0 if dyn else batch_edges.get_relation_type_as_scalar()
+        ul = None if uniform_lhs is None else nat._uniform(uniform_lhs, dev)
+        ur = None if uniform_rhs is None else nat._uniform(uniform_rhs, dev)
+        nw = len(self.relation_weights)
+        warr = (C.c_float * nw)(*self.relation_weights)
+        bucket = nat.bucket(model, r, None, warr)
+        out = _lib.PbgEvalStats()
+        self._calls += 1
+        check(nat.lib.pbg_eval_batch(nat.ctx, C.byref(bucket), _ptr(lhs), _ptr(rhs), _ptr(rel), n, r, _ptr(ul), _ptr(ur),
+                                     self.seed + self._calls, C.byref(out)), nat.ctx)
+        return Stats(loss=float(out.loss), pos_rank=out.pos_rank, mrr=out.mrr, r1=out.r1, r10=out.r10, r50=out.r50,
+                     auc=out.auc, count=int(out.count))
+
+    def process_one_batch(self, model, batch_edges, uniform_lhs=None, uniform_rhs=None) -> Stats:
         return self._process_one_batch(model, batch_edges, uniform_lhs, uniform_rhs)
 
 
