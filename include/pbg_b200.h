@@ -140,7 +140,8 @@ int pbg_train_batches(pbg_context *ctx, const pbg_bucket *bucket,
                       uint64_t seed, pbg_batch_stats *stats_out);
 
 /* Same, with the edge arrays (and optional uniform ids) in HOST memory: copies them to the
- * device in slabs that overlap with training.  This is the call that stands where
+ * device asynchronously on the context's stream ahead of the first wave (8 to 24 bytes per
+ * edge, against ~50 KB per edge of table traffic).  This is the call that stands where
  * GPUProcess.do_one_job moves a bucket's edges to the GPU and trains on them
  * (torchbiggraph/train_gpu.py:243-266). */
 int pbg_train_batches_host(pbg_context *ctx, const pbg_bucket *bucket,
