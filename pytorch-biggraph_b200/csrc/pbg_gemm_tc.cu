@@ -15,7 +15,9 @@
 //   warp 1      allocates tensor memory, issues tcgen05.mma.kind::tf32 (one elected lane) and
 //               commits to the stage's "empty" barrier / the final "accumulator ready" barrier
 //   warps 2-5   epilogue: tcgen05.ld 32 columns at a time (each warp its 32 TMEM lanes = 32
-//               rows), comparator epilogue for scores, 128-byte row-segment stores
+//               rows), comparator epilogue for scores; the 32 x 32 block goes through a private
+//               swizzled shared-memory buffer (two per warp) and leaves as one bulk tensor
+//               store, which writes whole 128-byte row segments and clips at the matrix edge
 //   warps 6-13  TF32X3 only: split every landed stage into hi / lo (see below)
 // K-major operands use the 128-byte swizzle; MN-major tf32 operands must use the 128-byte swizzle
 // with 32-byte atoms (descriptor layout type 1, TMA swizzle 128B_ATOM_32B), 32 x 32 element boxes.
@@ -34,7 +36,7 @@
 #define TC_SPLIT_THREADS 256
 #define TC_WAIT_LIMIT 4000000
 
-struct TcMaps { CUtensorMap a[2]; CUtensorMap b[2]; };   // [problem]
+struct TcMaps { CUtensorMap a[2]; CUtensorMap b[2]; CUtensorMap c[2]; };   // [problem]; c = output (stores)
 
 struct TcGeom {
   int M, N, K;          // output rows, columns, contraction length (per block)
@@ -81,6 +83,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char *ostage = smem + (size_t)STAGES * STAGE_BYTES;          // [4 warps][2][32 rows x 128 B], epilogue staging
   __shared__ __align__(8) unsigned long long bars[3 * STAGES + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int failed;
@@ -231,7 +234,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
     }
   } else if (warp >= 2 && warp < 6) {
     // ---------------- epilogue: drains accumulator j & 1 while the next tile is being multiplied ----------------
-    long long j = 0;
+    long long j = 0, nst = 0;
     const int q = warp & 3;                           // the 32 TMEM lanes this warp may read
     for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
       int p, blk, m0, n0;
@@ -240,8 +243,8 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
       const int ab = (int)(j & 1);
       if (!__all_sync(0xffffffffu, mbar_wait(accf_bar(ab), (uint32_t)(j >> 1) & 1, errflag))) { failed = 1; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int m = m0 + q * 32 + lane;
-      float *C = g.C[p] + (size_t)blk * g.c_blk + (size_t)m * g.ldc;
+      const int mrow0 = m0 + q * 32;                 // first output row of this warp's block
+      const int m = mrow0 + lane;
       float an = 0.f;
       const bool l2 = g.score && g.cmp >= PBG_CMP_L2;
       if (l2 && m < g.M) an = g.auxA[p][(size_t)blk * g.auxa_blk + m];
@@ -255,34 +258,41 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
                        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
                        "=r"(r[30]), "=r"(r[31]) : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (m < g.M) {
+        const int ncol0 = n0 + c0;
+        if (mrow0 >= g.M || ncol0 >= g.N) continue;    // block entirely outside the matrix (warp-uniform)
+        // the buffer used two blocks ago must have been read by its store before it is rewritten
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
+        unsigned char *buf = ostage + (size_t)(q * 2 + (int)(nst & 1)) * 4096;
+        ++nst;
 #pragma unroll
-          for (int jj = 0; jj < 32; jj += 4) {
-            int n = n0 + c0 + jj;
-            if (n < g.N && c0 + jj < g.BN) {
-              float v[4];
+        for (int jj = 0; jj < 32; jj += 4) {
+          float v[4];
 #pragma unroll
-              for (int tt = 0; tt < 4; ++tt) {
-                v[tt] = __uint_as_float(r[jj + tt]);
-                if (l2 && n + tt < g.N) {
-                  float qv = (bn[n + tt] - 2.0f * v[tt]) + an;     // model.py:226-246
-                  v[tt] = g.cmp == PBG_CMP_L2 ? -sqrtf(fmaxf(qv, 1e-30f)) : -qv;
-                }
-              }
-              if (n + 3 < g.N) st4(C + n, make_float4(v[0], v[1], v[2], v[3]));
-              else {
-                if (n < g.N) C[n] = v[0];
-                if (n + 1 < g.N) C[n + 1] = v[1];
-                if (n + 2 < g.N) C[n + 2] = v[2];
-              }
+          for (int tt = 0; tt < 4; ++tt) {
+            v[tt] = __uint_as_float(r[jj + tt]);
+            if (l2) {
+              int n = ncol0 + jj + tt;
+              float qv = ((n < g.N ? bn[n] : 0.f) - 2.0f * v[tt]) + an;     // model.py:226-246
+              v[tt] = g.cmp == PBG_CMP_L2 ? -sqrtf(fmaxf(qv, 1e-30f)) : -qv;
             }
           }
+          // row `lane` of the block, 16-byte unit jj / 4, in the 128-byte swizzle the store map expects
+          *reinterpret_cast<float4 *>(buf + lane * 128 + (((jj >> 2) ^ (lane & 7)) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic writes -> bulk store reads
+        __syncwarp();
+        if (lane == 0) {
+          asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                       :: "l"(&maps.c[p]), "r"(ncol0), "r"(mrow0), "r"(blk), "r"(smem_u32(buf)) : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(acce_bar(ab)) : "memory");
       ++j;
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the stores have left shared memory and are performed
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -335,9 +345,13 @@ struct TcPlan {
   int nterms;
 };
 
+// Columns per tile: equal tiles of at most 256.  With more than one tile the width is a multiple of
+// 32, the width of the epilogue's store blocks (a block must not reach into the next tile); a single
+// tile may end on a multiple of 16, what lies beyond it is outside the matrix and clipped.
 static int tile_cols(int n) {
   int tiles = (n + 255) / 256;
-  int bn = ((n + tiles - 1) / tiles + 15) / 16 * 16;
+  int unit = tiles > 1 ? 32 : 16;
+  int bn = ((n + tiles - 1) / tiles + unit - 1) / unit * unit;
   return bn > 256 ? 256 : bn;
 }
 
@@ -357,6 +371,8 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
     // score: A = Q (K-major, k = D), B = N (K-major)
     ok &= encode3(&pl->score.a[p], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 128, false);
     ok &= encode3(&pl->score.b[p], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, pl->bn_score, false);
+    // outputs leave through 32 x 32 bulk stores (128-byte swizzle in shared memory), clipped at the matrix edge
+    ok &= encode3(&pl->score.c[p], w.S[p], d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 32, false);
     if (pl->dynamic) {
       // grad Q: A = T (K-major, k = Mm), B = N (MN-major: k rows = Mm, contiguous D)
       ok &= encode3(&pl->gradq.a[p], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 128, false);
@@ -364,11 +380,14 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
       // grad N: A = T^T (MN-major: k rows = Pm, contiguous Mm), B = Q (MN-major: k rows = Pm, contiguous D)
       ok &= encode3(&pl->gradn.a[p], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 32, true);
       ok &= encode3(&pl->gradn.b[p], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 32, true);
+      ok &= encode3(&pl->gradq.c[p], w.GX[q], d.D, d.Pm, nblk_max, d.Dp, (long long)w.grows[q] * d.Dp, 32, 32, false);
+      ok &= encode3(&pl->gradn.c[p], w.GX[n], d.D, d.Mm, nblk_max, d.Dp, (long long)w.grows[n] * d.Dp, 32, 32, false);
     } else {
       // merged: side p: A = A[p] (K-major, k = Mm), B = the other side's operand rows (MN-major)
       int o = ARR_N0 + (1 - p);
       ok &= encode3(&pl->gradm.a[p], w.A[p], d.Mm, d.Mm, nblk_max, w.Ma, (long long)d.Mm * w.Ma, 32, 128, false);
       ok &= encode3(&pl->gradm.b[p], w.X[o], d.D, w.xrows[o], nblk_max, d.Dp, (long long)w.xrows[o] * d.Dp, 32, 32, true);
+      ok &= encode3(&pl->gradm.c[p], w.GX[n], d.D, d.Mm, nblk_max, d.Dp, (long long)d.Mm * d.Dp, 32, 32, false);
     }
   }
   if (!ok) { delete pl; return nullptr; }
@@ -384,7 +403,7 @@ static void launch_tc(const TcMaps &maps, const TcGeom &g, int nterms, const Wav
   static int sms = 0;
   if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));
-  size_t smem = 4 * (128 * 128 + 256 * 128) + 1024;           // 2 stages x (hi, lo) or 4 stages x raw
+  size_t smem = 4 * (128 * 128 + 256 * 128) + 4 * 2 * 4096 + 1024;   // 2 stages x (hi, lo) or 4 stages x raw; epilogue staging
   if (nterms == 3) {
     static bool done = false;
     if (!done) { cudaFuncSetAttribute(tc_gemm_kernel<A_MN, B_MN, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
