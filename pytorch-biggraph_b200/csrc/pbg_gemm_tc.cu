@@ -72,7 +72,7 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
          ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
 }
 
-template <bool A_MN, bool B_MN, int NTERMS>
+template <bool A_MN, bool B_MN, int NTERMS, bool L2EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBatches wb, int *errflag) {
   constexpr bool SPLIT = NTERMS == 3;
@@ -246,7 +246,9 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
       const int mrow0 = m0 + q * 32;                 // first output row of this warp's block
       const int m = mrow0 + lane;
       float an = 0.f;
-      const bool l2 = g.score && g.cmp >= PBG_CMP_L2;
+      // comparator epilogue of the l2 family: compiled in only where it is used (predicated-off
+      // copies of it in the unrolled loop cost more issue slots than the stores themselves)
+      constexpr bool l2 = L2EPI;
       if (l2 && m < g.M) an = g.auxA[p][(size_t)blk * g.auxa_blk + m];
       const float *bn = l2 ? g.auxB[p] + (size_t)blk * g.auxb_blk : nullptr;
       for (int c0 = 0; c0 < g.BN; c0 += 32) {
@@ -396,6 +398,17 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
 
 void pbg_tc_plan_destroy(void *plan) { delete (TcPlan *)plan; }
 
+template <bool A_MN, bool B_MN, int NTERMS, bool L2EPI>
+static void launch_tc_inst(const TcMaps &maps, const TcGeom &g, const WaveDims &d, const WaveBatches &wb, int *errflag,
+                           dim3 grid, size_t smem, cudaStream_t st) {
+  static bool done = false;
+  if (!done) {
+    cudaFuncSetAttribute(tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    done = true;
+  }
+  tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI><<<grid, TC_THREADS, smem, st>>>(maps, g, d, wb, errflag);
+}
+
 template <bool A_MN, bool B_MN>
 static void launch_tc(const TcMaps &maps, const TcGeom &g, int nterms, const WaveDims &d, const WaveBatches &wb, int *errflag,
                       cudaStream_t st) {
@@ -404,15 +417,17 @@ static void launch_tc(const TcMaps &maps, const TcGeom &g, int nterms, const Wav
   if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   size_t smem = 4 * (128 * 128 + 256 * 128) + 4 * 2 * 4096 + 1024;   // 2 stages x (hi, lo) or 4 stages x raw; epilogue staging
-  if (nterms == 3) {
-    static bool done = false;
-    if (!done) { cudaFuncSetAttribute(tc_gemm_kernel<A_MN, B_MN, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
-    tc_gemm_kernel<A_MN, B_MN, 3><<<grid, TC_THREADS, smem, st>>>(maps, g, d, wb, errflag);
-  } else {
-    static bool done = false;
-    if (!done) { cudaFuncSetAttribute(tc_gemm_kernel<A_MN, B_MN, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); done = true; }
-    tc_gemm_kernel<A_MN, B_MN, 1><<<grid, TC_THREADS, smem, st>>>(maps, g, d, wb, errflag);
+  // the comparator epilogue of the l2 family exists only in the score kernels (both operands K-major)
+  const bool l2 = !A_MN && !B_MN && g.score && g.cmp >= PBG_CMP_L2;
+  if constexpr (!A_MN && !B_MN) {
+    if (l2) {
+      if (nterms == 3) launch_tc_inst<A_MN, B_MN, 3, true>(maps, g, d, wb, errflag, grid, smem, st);
+      else launch_tc_inst<A_MN, B_MN, 1, true>(maps, g, d, wb, errflag, grid, smem, st);
+      return;
+    }
   }
+  if (nterms == 3) launch_tc_inst<A_MN, B_MN, 3, false>(maps, g, d, wb, errflag, grid, smem, st);
+  else launch_tc_inst<A_MN, B_MN, 1, false>(maps, g, d, wb, errflag, grid, smem, st);
 }
 
 int launch_score_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st) {
