@@ -194,6 +194,11 @@ __device__ __forceinline__ float tf32_hi(float x) {
   return __uint_as_float(u);
 }
 __device__ __forceinline__ float4 tf32_hi4(float4 v) { return make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w)); }
+// The same rounding with two integer instructions (add half an ulp of the 10-bit mantissa, clear the
+// low 13 bits): cvt runs at a fraction of the ALU rate, which is what bounds a kernel that splits
+// whole operand tiles.  Differs from cvt only on NaN payloads and when rounding carries into Inf.
+__device__ __forceinline__ float tf32_round(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
+__device__ __forceinline__ float4 tf32_round4(float4 v) { return make_float4(tf32_round(v.x), tf32_round(v.y), tf32_round(v.z), tf32_round(v.w)); }
 
 // ---- host-side launchers (one per translation unit) ------------------------------------------
 struct SortPlan {

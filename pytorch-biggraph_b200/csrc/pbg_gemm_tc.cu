@@ -129,26 +129,37 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
     return bi.n != 0 && !(g.score && !d.neg_enabled[p]);
   };
 
-  if (warp == 0 && lane == 0) {
-    // ---------------- TMA producer ----------------
+  if (warp == 0) {
+    // ---------------- TMA producer (whole warp: every box of a stage is issued by its own lane) ----------------
+    // Issuing one cp.async.bulk.tensor costs the issuing thread a few hundred cycles; an MN-major
+    // B tile is up to eight 32 x 32 boxes, which issued from one lane made the producer the
+    // longest link of the stage's chain.
+    const int a_boxes = A_MN ? 4 : 1, b_boxes = B_MN ? b_atoms : 1;
     long long git = 0;
-    for (long long t = blockIdx.x; t < ntiles && !failed; t += gridDim.x) {
+    bool stop = false;
+    for (long long t = blockIdx.x; t < ntiles && !stop; t += gridDim.x) {
       int p, blk, m0, n0;
+      if (__any_sync(0xffffffffu, failed != 0)) break;
       if (!tile_live(t, p, blk, m0, n0)) continue;
       for (int kb = 0; kb < nkb; ++kb, ++git) {
         int s = (int)(git % STAGES);
-        if (git >= STAGES && !mbar_wait(empty_bar(s), (uint32_t)((git / STAGES) - 1) & 1, errflag)) { failed = 1; break; }
+        bool okw = true;
+        if (git >= STAGES && lane == 0) okw = mbar_wait(empty_bar(s), (uint32_t)((git / STAGES) - 1) & 1, errflag);
+        if (!__all_sync(0xffffffffu, okw)) { failed = 1; stop = true; break; }
         uint32_t fb = full_bar(s);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(fb), "r"(stage_tx) : "memory");
+        if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(fb), "r"(stage_tx) : "memory");
+        __syncwarp();
         unsigned char *st = smem + (size_t)s * STAGE_BYTES;
         int k0 = kb * 32;
         uint32_t dA = smem_u32(st), dB = smem_u32(st + A_BYTES);
-        if (!A_MN) tma_load_3d(dA, &maps.a[p], k0, m0, blk, fb);
-        else
-          for (int mb = 0; mb < 4; ++mb) tma_load_3d(dA + mb * 4096, &maps.a[p], m0 + mb * 32, k0, blk, fb);
-        if (!B_MN) tma_load_3d(dB, &maps.b[p], k0, n0, blk, fb);
-        else
-          for (int nb = 0; nb < b_atoms; ++nb) tma_load_3d(dB + nb * 4096, &maps.b[p], n0 + nb * 32, k0, blk, fb);
+        if (lane < a_boxes) {
+          if (!A_MN) tma_load_3d(dA, &maps.a[p], k0, m0, blk, fb);
+          else tma_load_3d(dA + lane * 4096, &maps.a[p], m0 + lane * 32, k0, blk, fb);
+        } else if (lane < a_boxes + b_boxes) {
+          int nb = lane - a_boxes;
+          if (!B_MN) tma_load_3d(dB, &maps.b[p], k0, n0, blk, fb);
+          else tma_load_3d(dB + nb * 4096, &maps.b[p], n0 + nb * 32, k0, blk, fb);
+        }
       }
     }
   } else if (warp == 1 && lane == 0) {
@@ -222,7 +233,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
           for (int u = 0; u < 4; ++u) {
             uint32_t c = c0 + u * TC_SPLIT_THREADS;
             if (c < nchunks) {
-              float4 h = tf32_hi4(v[u]);
+              float4 h = tf32_round4(v[u]);
               *reinterpret_cast<float4 *>(st + (size_t)c * 16) = h;
               *reinterpret_cast<float4 *>(st + RAW_BYTES + (size_t)c * 16) = v[u] - h;
             }
@@ -371,7 +382,8 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
     const float *Xq = w.X[q], *Xn = w.X[n], *T = w.S[p];
     long long qblk = (long long)w.xrows[q] * d.Dp, nblk_s = (long long)w.xrows[n] * d.Dp, tblk = (long long)d.Pm * d.Ms;
     // score: A = Q (K-major, k = D), B = N (K-major)
-    ok &= encode3(&pl->score.a[p], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 128, false);
+    // only the Pm scored rows exist for the map: the rest of the 128-row box is filled with zeros without touching L2
+    ok &= encode3(&pl->score.a[p], Xq, d.D, d.Pm, nblk_max, d.Dp, qblk, 32, 128, false);
     ok &= encode3(&pl->score.b[p], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, pl->bn_score, false);
     // outputs leave through 32 x 32 bulk stores (128-byte swizzle in shared memory), clipped at the matrix edge
     ok &= encode3(&pl->score.c[p], w.S[p], d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 32, false);
