@@ -371,7 +371,6 @@ hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long lo
                   const long long *__restrict__ hublist, const int *__restrict__ hubcnt) {
   extern __shared__ __align__(16) float tot[];               // [k][VEC * 128]
   __shared__ long long bstart[PBG_KMAX + 1];
-  __shared__ long long seg_end;
   const int lane = threadIdx.x & 31, wl = threadIdx.x >> 5;
   const int D = d.D;
   const float invD = 1.0f / (float)D;
@@ -379,14 +378,23 @@ hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long lo
   for (int h = blockIdx.x; h < nh; h += gridDim.x) {
     const long long head = hublist[h];
     const unsigned long long key = keys[head];
-    if (threadIdx.x == 0) {
-      long long a = head + 1, b = d.nocc;
-      while (a < b) { long long m = (a + b) >> 1; if (keys[m] <= key) a = m + 1; else b = m; }
-      seg_end = a;
+    // end of the row's slots: the whole CTA probes blockDim.x evenly spaced positions per round (the
+    // slots that still carry the key are a prefix of the sorted list), two rounds for any wave size
+    // instead of a chain of ~16 dependent loads by one thread
+    long long lo = head + 1, hi = d.nocc;
+    while (lo < hi) {
+      long long stride = (hi - lo + blockDim.x - 1) / blockDim.x;
+      long long pos = lo + (long long)threadIdx.x * stride;
+      int cnt = __syncthreads_count(pos < hi && keys[pos] == key);
+      if (cnt == 0) { hi = lo; break; }
+      long long nhi = lo + (long long)cnt * stride;
+      lo = lo + (long long)(cnt - 1) * stride + 1;
+      if (nhi < hi) hi = nhi;
+      if (stride == 1) { lo = hi; break; }
     }
     for (int i = threadIdx.x; i <= PBG_KMAX; i += blockDim.x) bstart[i] = -1;
     __syncthreads();
-    const long long end = seg_end;
+    const long long end = hi;
     for (long long q = head + threadIdx.x; q < end; q += blockDim.x) {
       int bq = (int)(vals[q] / (unsigned int)d.spb);
       if (q == head || (int)(vals[q - 1] / (unsigned int)d.spb) != bq) bstart[bq] = q;   // first slot of batch bq
