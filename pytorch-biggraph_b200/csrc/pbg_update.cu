@@ -359,6 +359,76 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
   }
 }
 
+// End of the prefix of [lo, hi) on which pred holds (pred must hold on a prefix only).  The whole CTA
+// probes blockDim.x evenly spaced positions per round: two rounds for any wave size instead of a
+// chain of ~16 dependent loads by one thread.  Every thread returns the same value.
+template <class Pred>
+__device__ __forceinline__ long long coop_prefix_end(long long lo, long long hi, Pred pred) {
+  while (lo < hi) {
+    long long stride = (hi - lo + blockDim.x - 1) / blockDim.x;
+    long long pos = lo + (long long)threadIdx.x * stride;
+    int cnt = __syncthreads_count(pos < hi && pred(pos));
+    if (cnt == 0) return lo;
+    long long nhi = lo + (long long)cnt * stride;
+    lo = lo + (long long)(cnt - 1) * stride + 1;
+    if (nhi < hi) hi = nhi;
+    if (stride == 1) return hi;
+  }
+  return hi;
+}
+
+#define HUB_BIG 256     // rows with at least this many slots in a wave get their batches summed by separate CTAs
+
+// The few rows that collect hundreds of slots per wave (the top nodes of a power-law partition)
+// would keep one CTA of hub_update_kernel busy long after every other row is done.  One CTA per
+// (big row, batch) adds that batch's partial rows up first -- warp w takes runs w, w + 8, ..., the
+// eight sums are added in warp order -- and leaves the total in the batch's first partial row, so
+// that hub_update_kernel reads one row per batch of a big row.
+template <int VEC>
+__global__ void __launch_bounds__(32 * UPD_WARPS)
+hub_reduce_kernel(WaveDims d, const unsigned long long *__restrict__ keys, const unsigned int *__restrict__ vals,
+                  float *__restrict__ psum, const long long *__restrict__ hublist, const int *__restrict__ hubcnt) {
+  extern __shared__ __align__(16) float part[];              // [UPD_WARPS][VEC * 128]
+  const int lane = threadIdx.x & 31, wl = threadIdx.x >> 5;
+  const int D = d.D;
+  const long long items = (long long)(*hubcnt) * d.k;
+  for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+    const int h = (int)(item / d.k), b = (int)(item % d.k);
+    const long long head = hublist[h];
+    const unsigned long long key = keys[head];
+    const long long end = coop_prefix_end(head + 1, (long long)d.nocc, [&](long long pos) { return keys[pos] == key; });
+    if (end - head < HUB_BIG) continue;
+    const long long q = coop_prefix_end(head, end, [&](long long pos) { return (int)(vals[pos] / (unsigned int)d.spb) < b; });
+    const long long eb = coop_prefix_end(q, end, [&](long long pos) { return (int)(vals[pos] / (unsigned int)d.spb) <= b; });
+    if (q >= eb) continue;
+    const long long ftb = (q / TILE + 1) * TILE;
+    const long long nruns = 1 + (eb > ftb ? (eb - 1 - ftb) / TILE + 1 : 0);
+    if (nruns == 1) continue;
+    float4 acc[VEC];
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) acc[c] = f4zero();
+    for (long long r = wl; r < nruns; r += UPD_WARPS) {
+      const float *src = psum + (size_t)(r == 0 ? q : ftb + (r - 1) * TILE) * d.Dp;
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) {
+        int dd = c * 128 + lane * 4;
+        if (dd < D) acc[c] = acc[c] + ld4(src + dd);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) st4(&part[(size_t)wl * VEC * 128 + c * 128 + lane * 4], acc[c]);
+    __syncthreads();
+    float *dst = psum + (size_t)q * d.Dp;
+    for (int dd = threadIdx.x * 4; dd < D; dd += 4 * blockDim.x) {
+      float4 t = ld4(&part[dd]);
+#pragma unroll
+      for (int u = 1; u < UPD_WARPS; ++u) t = t + ld4(&part[(size_t)u * VEC * 128 + dd]);
+      st4(dst + dd, t);
+    }
+    __syncthreads();
+  }
+}
+
 // One CTA per hub row.  Its slots [head, end) are in batch order; every thread looks at a strided
 // share of them to find where each batch starts (bstart[]), then warp w adds up the partial rows of
 // batches w, w+8, ... (a batch's slots [q, eb) were summed by the tile warps in runs that start at
@@ -378,23 +448,10 @@ hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long lo
   for (int h = blockIdx.x; h < nh; h += gridDim.x) {
     const long long head = hublist[h];
     const unsigned long long key = keys[head];
-    // end of the row's slots: the whole CTA probes blockDim.x evenly spaced positions per round (the
-    // slots that still carry the key are a prefix of the sorted list), two rounds for any wave size
-    // instead of a chain of ~16 dependent loads by one thread
-    long long lo = head + 1, hi = d.nocc;
-    while (lo < hi) {
-      long long stride = (hi - lo + blockDim.x - 1) / blockDim.x;
-      long long pos = lo + (long long)threadIdx.x * stride;
-      int cnt = __syncthreads_count(pos < hi && keys[pos] == key);
-      if (cnt == 0) { hi = lo; break; }
-      long long nhi = lo + (long long)cnt * stride;
-      lo = lo + (long long)(cnt - 1) * stride + 1;
-      if (nhi < hi) hi = nhi;
-      if (stride == 1) { lo = hi; break; }
-    }
+    const long long end = coop_prefix_end(head + 1, (long long)d.nocc, [&](long long pos) { return keys[pos] == key; });
+    const bool big = end - head >= HUB_BIG;                  // hub_reduce_kernel left one row per batch
     for (int i = threadIdx.x; i <= PBG_KMAX; i += blockDim.x) bstart[i] = -1;
     __syncthreads();
-    const long long end = hi;
     for (long long q = head + threadIdx.x; q < end; q += blockDim.x) {
       int bq = (int)(vals[q] / (unsigned int)d.spb);
       if (q == head || (int)(vals[q - 1] / (unsigned int)d.spb) != bq) bstart[bq] = q;   // first slot of batch bq
@@ -407,7 +464,7 @@ hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long lo
       long long eb = end;
       for (int nb = bq + 1; nb < d.k; ++nb) if (bstart[nb] >= 0) { eb = bstart[nb]; break; }
       long long ftb = (q / TILE + 1) * TILE;
-      long long nruns = 1 + (eb > ftb ? (eb - 1 - ftb) / TILE + 1 : 0);
+      long long nruns = big ? 1 : 1 + (eb > ftb ? (eb - 1 - ftb) / TILE + 1 : 0);
       float4 acc[VEC];
 #pragma unroll
       for (int c = 0; c < VEC; ++c) acc[c] = f4zero();
@@ -596,6 +653,7 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   size_t stage_smem = (size_t)TILE_WARPS_EMB * TILE * d.Dp * sizeof(float);
   const int hub_ctas = 296;
   size_t hub_smem = (size_t)d.k * VEC * 128 * sizeof(float);            // per-batch totals of one hub row
+  size_t red_smem = (size_t)UPD_WARPS * VEC * 128 * sizeof(float);       // eight partial sums of one batch of a big row
   static bool attr_done[2] = {false, false};
   // the attribute is set once for the largest wave this row width allows in 227 KB
   size_t hub_smem_max = (size_t)PBG_KMAX * VEC * 128 * sizeof(float);
@@ -607,13 +665,16 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   }
   if (!attr_done[0]) {
     cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem_max);
+    cudaFuncSetAttribute(hub_reduce_kernel<VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_smem);
     cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
     attr_done[0] = true;
   }
   cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
   tile_update_kernel<VEC, RULE_EMB><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt);
   hub_update_kernel<VEC, RULE_EMB><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  ++launches;
   launches += 2;
   if (has_op) {
     if (d.dynamic) {
@@ -623,7 +684,9 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
       }
       cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
       tile_update_kernel<VEC, RULE_REL><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt);
       hub_update_kernel<VEC, RULE_REL><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      ++launches;
       launches += 2;
     } else if (d.matrix_op) {
       launches += launch_matrix_update(d, wb, w, rel_lr, st);
