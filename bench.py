@@ -78,6 +78,11 @@ class Sampler:
         c = torch.cumsum(weights.double(), 0)
         self.cdf = (c / c[-1]).float()
         self.n = weights.shape[0]
+        self.weights = weights
+
+    def part(self, lo, hi):
+        """Sampler of the rows [lo, hi) of the partition; ids count from lo."""
+        return Sampler(self.weights[lo:hi])
 
     def draw(self, n, gen):
         import torch
@@ -116,24 +121,36 @@ class ClockSampler:
 
     def __init__(self, index):
         self.rows, self.proc, self.index = [], None, index
+        self.t0 = self.t1 = None
 
-    def __enter__(self):
+    def start(self):
+        """nvidia-smi takes a few hundred ms to come up (longer with eight ranks starting one each):
+        it is started before the warm-up steps so that it is already sampling when the timed
+        region begins."""
+        if self.proc is not None:
+            return self
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.index), "-lms", "50"], stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
             self.proc = None
         return self
 
+    def __enter__(self):
+        self.start()
+        self.t0 = time.time()
+        return self
+
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
 
     def __exit__(self, *a):
+        self.t1 = time.time()
         if self.proc:
-            time.sleep(0.15)
+            time.sleep(0.12)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -141,13 +158,20 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm = sorted(int(float(r[0])) for r in self.rows if r and r[0].replace(".", "").isdigit())
+        def ok(r):
+            return r and r[0].replace(".", "").isdigit()
+        inside = [r for t, r in self.rows if ok(r) and self.t0 is not None and self.t0 <= t <= (self.t1 or t) + 0.06]
+        window = "timed region"
+        if not inside:          # a timed region shorter than the sampling period: the warm-up steps ran the same load
+            inside = [r for t, r in self.rows if ok(r)]
+            window = "warm-up and timed region"
+        sm = sorted(int(float(r[0])) for r in inside)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[3 + i].lower().startswith("active") for r in self.rows)]
-        mx = max(int(float(r[1])) for r in self.rows if len(r) > 1)
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[3 + i].lower().startswith("active") for r in inside)]
+        mx = max(int(float(r[1])) for r in inside if len(r) > 1)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm), "window": window}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -276,7 +300,16 @@ def run_reference(args, w):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(args, w, step_edges):
+def workload_config(args, w, step_edges, halves=False):
+    cfg = _workload_config(args, w, step_edges)
+    if halves:
+        cfg["step"] += " as two sub-buckets (rhs partition cut in two row ranges)"
+        cfg["hand_off"] = ("rhs partition travels to the next GPU in two halves over NCCL send/recv (NVLink), each half "
+                           "beside the training of the other; inside the timed region")
+    return cfg
+
+
+def _workload_config(args, w, step_edges):
     return {"workload": f"{args.workload}: {w['desc']}; {w['entities']} entities, {w['partitions']} partitions, dim {w['dim']}, "
                         f"{w['op']}/{w['comp']}/{w['loss']}, batch {w['batch']}, {w['nb']} batch + {w['nu']} uniform negs",
             "step": f"one bucket: {step_edges} edges", "l2": "inputs_larger_than_l2",
@@ -291,7 +324,7 @@ def run_b200(args, w):
     import torch.distributed as dist
     import torchbiggraph_b200 as T
     from torchbiggraph_b200 import _lib
-    from torchbiggraph_b200.buckets import ring_exchange
+    from torchbiggraph_b200.buckets import OverlappedRing, ring_exchange
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -378,37 +411,108 @@ def run_b200(args, w):
         v = torch.where(noisy, torch.randint(0, n, (step_edges,), device=dev, generator=gen), v)
         return u, v, rel
 
+    # ---- several GPUs: the rhs partition travels round the ring in two halves, beside training ------
+    # A bucket (A, B) is trained as the sub-buckets (A, B[:cut]) and (A, B[cut:]) (edges grouped by the
+    # half of their rhs row, as the reference's GPU trainer groups edges by sub-partition); the half
+    # just trained leaves for the next rank while the other half trains, and arrives in the other
+    # buffer of the receiver before the bucket after next needs it.
+    halves_on = world > 1 and P > 1 and not dyn
+    if halves_on:
+        ring = OverlappedRing(dev)
+        pr0 = mine[1]
+        real_rows = bounds[pr0 + 1] - bounds[pr0]
+        cut = real_rows // 2
+        cuts = [(0, cut), (cut, tables[pr0].shape[0])]
+        half_samplers = [samplers[pr0].part(0, cut), samplers[pr0].part(cut, real_rows)]
+        bufs = [(tables[pr0], states[pr0]), spare]
+        views = [[(b[0][lo:hi], b[1][lo:hi]) for lo, hi in cuts] for b in bufs]
+        half_opts = [[optimizer_for(t, st) for t, st in vb] for vb in views]
+        sub_edges = step_edges // 2
+        step_edges = 2 * sub_edges
+        sub_batches = [(o, min(B, sub_edges - o), 0) for o in range(0, sub_edges, B)]
+        ring_state = {"cur": 0, "pend": [None, None]}
+
+        def draw_edges(bk):                       # noqa: F811  (two sub-buckets per bucket)
+            pl, _ = bk
+            return [(samplers[pl].draw(sub_edges, gen), half_samplers[h].draw(sub_edges, gen), None) for h in (0, 1)]
+
+        def train_bucket(edges, want_per_batch):
+            cur, pend = ring_state["cur"], ring_state["pend"]
+            out = []
+            for h in (0, 1):
+                OverlappedRing.finish(pend[h])    # this half has arrived (and the other buffer's half has left)
+                tv, _ = views[cur][h]
+                model.clear_all_embeddings()
+                model.set_embeddings("e", T.Side.LHS, tables[mine[0]])
+                model.set_embeddings("e", T.Side.RHS, tv)
+                trainer.partitioned_optimizers.clear()
+                trainer.partitioned_optimizers["e", mine[0]] = opts[mine[0]]
+                trainer.partitioned_optimizers["e", pr0] = half_opts[cur][h]
+                l, r, rl = edges[h]
+                res = trainer.train_batches(model, l, r, rl, sub_batches, want_per_batch=want_per_batch)
+                if want_per_batch:
+                    out.extend(res)
+                pend[h] = ring.start(list(views[cur][h]), list(views[1 - cur][h]))
+            ring_state["cur"] = 1 - cur
+            return out
+
+        def drain():
+            for h in (0, 1):
+                OverlappedRing.finish(ring_state["pend"][h])
+                ring_state["pend"][h] = None
+    else:
+        def train_bucket(edges, want_per_batch):
+            l, r, rl = edges
+            return trainer.train_batches(model, l, r, rl, batches, want_per_batch=want_per_batch)
+
+        def drain():
+            pass
+
     # ---- device-resident pass: `value` -------------------------------------------------------
     dev_edges = [draw_edges(bucket_for(s)) for s in range(total_steps + nprof)]
-    host_edges = [tuple(None if t is None else t.cpu().pin_memory() for t in e) for e in dev_edges[: total_steps]]
 
-    def step_device(s):
-        bind(bucket_for(s))
-        l, r, rl = dev_edges[s]
-        trainer.train_batches(model, l, r, rl, batches, want_per_batch=False)
-        if world > 1:
-            nonlocal spare
+    def to_host(e):
+        if isinstance(e, list):
+            return [to_host(x) for x in e]
+        return tuple(None if t is None else t.cpu().pin_memory() for t in e)
+
+    host_edges = [to_host(e) for e in dev_edges[: total_steps]]
+
+    def step_any(edges, want_per_batch):
+        if halves_on:
+            return train_bucket(edges, want_per_batch)
+        nonlocal spare
+        res = train_bucket(edges, want_per_batch)
+        if world > 1 and P > 1:
             p = mine[1]
             ring_exchange([tables[p], states[p]], list(spare))
             (tables[p], states[p]), spare = spare, (tables[p], states[p])     # swap roles, no copy
             opts[p] = optimizer_for(tables[p], states[p])
+        return res
+
+    def step_device(s):
+        if not halves_on:
+            bind(bucket_for(s))
+        step_any(dev_edges[s], False)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    clocks = ClockSampler(local).start()
     for s in range(args.warmup):
         step_device(s)
     barrier()
     nat = trainer._native
     launches0 = nat.lib.pbg_launch_count(nat.ctx)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
+    with clocks:
         barrier()
         e0.record()
         for s in range(args.warmup, total_steps):
             step_device(s)
+        drain()
         e1.record()
         barrier()
     ms = e0.elapsed_time(e1)
@@ -422,9 +526,9 @@ def run_b200(args, w):
 
     # ---- end-to-end pass: host edges, copies and stats read-back inside the timed region --------
     def step_host(s):
-        bind(bucket_for(s))
-        l, r, rl = host_edges[s]
-        return trainer.train_batches(model, l, r, rl, batches, want_per_batch=True)
+        if not halves_on:
+            bind(bucket_for(s))
+        return step_any(host_edges[s], True)
 
     for s in range(min(args.warmup, 2)):
         step_host(s)
@@ -433,6 +537,7 @@ def run_b200(args, w):
     last = None
     for s in range(args.warmup, total_steps):
         last = step_host(s)
+    drain()
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1)
@@ -449,9 +554,8 @@ def run_b200(args, w):
     check = _lib.check
     check(nat.lib.pbg_set_profiling(nat.ctx, 1), nat.ctx)
     for s in range(total_steps, total_steps + nprof):
-        bind(bucket_for(s))
-        l, r, rl = dev_edges[s]
-        trainer.train_batches(model, l, r, rl, batches, want_per_batch=False)
+        step_device(s)
+    drain()
     msc = (C.c_double * 7)()
     lc = (C.c_int64 * 7)()
     check(nat.lib.pbg_kernel_times(nat.ctx, msc, lc), nat.ctx)
@@ -492,7 +596,7 @@ def run_b200(args, w):
         line = {"metric": "edges/sec trained", "value": value, "unit": "edges/sec", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32" if args.precision == "fp32" else args.precision, "data": "synthetic",
-                "config": workload_config(args, w, step_edges), "e2e": e2e, "gpu_launches": int(launches),
+                "config": workload_config(args, w, step_edges, halves_on), "e2e": e2e, "gpu_launches": int(launches),
                 "clocks": clocks.summary(), "roofline": roof, "kernels": per_class,
                 "algorithmic_per_edge": {"flops": alg["flops"], "bytes": alg["bytes"]},
                 "edges_per_sec_hbm_bound": pk["hbm_gbs"] * 1e9 / alg["bytes"]}

@@ -77,6 +77,47 @@ def ring_exchange(send: Sequence[torch.Tensor], recv: Sequence[torch.Tensor], gr
         req.wait()
 
 
+class OverlappedRing:
+    """Partition hand-off that runs beside training instead of between buckets.
+
+    A bucket (lhs partition A, rhs partition B) is trained as two sub-buckets (A, B[:h]) and
+    (A, B[h:]), edges grouped by the half their rhs row falls in -- the reference's GPU trainer
+    cuts buckets into sub-partition jobs in the same way (torchbiggraph/train_gpu.py:77-100,
+    243-266).  As soon as the kernels of a sub-bucket are enqueued, `start` sends that half (rows +
+    RowAdagrad state) to the next rank and receives the previous rank's half into the spare
+    buffer, on a side stream; the other half trains meanwhile.  `finish` makes the current stream
+    wait for a transfer before the half it brought is trained on.  With the NCCL backend the
+    copies travel over NVLink into the receiver's own memory; with gloo (CPU tests) the calls are
+    the same without streams.  Every rank must call start/finish in the same order."""
+
+    def __init__(self, device=None, group=None):
+        self.group = group
+        self.cuda = device is not None and torch.device(device).type == "cuda"
+        self.stream = torch.cuda.Stream(device) if self.cuda else None
+
+    def start(self, send: Sequence[torch.Tensor], recv: Sequence[torch.Tensor]):
+        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        nxt, prv = (rank + 1) % world, (rank - 1) % world
+        ops = []
+        for s_, r_ in zip(send, recv):
+            ops.append(dist.P2POp(dist.isend, s_, nxt, self.group))
+            ops.append(dist.P2POp(dist.irecv, r_, prv, self.group))
+        if not self.cuda:
+            return dist.batch_isend_irecv(ops)
+        done = torch.cuda.Event()
+        done.record()                                # everything enqueued so far has written `send`
+        with torch.cuda.stream(self.stream):
+            self.stream.wait_event(done)
+            return dist.batch_isend_irecv(ops)
+
+    @staticmethod
+    def finish(handle) -> None:
+        if handle is None:
+            return
+        for req in handle:
+            req.wait()
+
+
 def average_relation_parameters(tensors: Sequence[torch.Tensor], group=None) -> None:
     """Shared operator tables and their AsyncAdagrad accumulators are averaged over the GPUs at
     round boundaries (one all-reduce each).  The reference's parameter server instead adds every

@@ -7,8 +7,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from torchbiggraph_b200.buckets import (assign_round, average_relation_parameters, partition_bounds, partition_of,
-                                        ring_exchange, round_robin_rounds)
+from torchbiggraph_b200.buckets import (OverlappedRing, assign_round, average_relation_parameters, partition_bounds,
+                                        partition_of, ring_exchange, round_robin_rounds)
 
 
 @pytest.mark.parametrize("P", [1, 2, 3, 4, 7, 16])
@@ -63,3 +63,46 @@ def test_ring_exchange_and_parameter_average_world_size_2():
             assert p.exitcode == 0
     # rank 0 received rank 1's partition and vice versa; the shared table is the mean of 0 and 1
     assert res == [(0, 2.0, 20.0, 0.5), (1, 1.0, 10.0, 0.5)]
+
+
+def _overlap_worker(rank, world, initfile, out):
+    """Three buckets in a row: the rhs partition travels in two halves; half h leaves as soon as
+    'training' on it (here: adding the rank's mark) is done and must have arrived, unchanged,
+    before the next bucket trains on it."""
+    dist.init_process_group("gloo", init_method=f"file://{initfile}", rank=rank, world_size=world)
+    ring = OverlappedRing()
+    rows = 6
+    cur = torch.full((rows, 2), float(100 * (rank + 1)))
+    other = torch.zeros_like(cur)
+    halves = [slice(0, 3), slice(3, 6)]
+    pend = [None, None]
+    seen = []
+    for step in range(3):
+        for h in (0, 1):
+            OverlappedRing.finish(pend[h])            # the half about to be trained on has arrived
+            cur[halves[h]] += 1.0                     # "train" on the half
+            seen.append(cur[halves[h]][0, 0].item())
+            pend[h] = ring.start([cur[halves[h]]], [other[halves[h]]])
+        cur, other = other, cur
+    for h in (0, 1):
+        OverlappedRing.finish(pend[h])
+    out.put((rank, seen, cur[0, 0].item(), cur[5, 0].item()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_overlapped_ring_hands_halves_on_in_order_world_size_2():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    with tempfile.TemporaryDirectory() as d:
+        init = os.path.join(d, "init")
+        procs = [ctx.Process(target=_overlap_worker, args=(r, 2, init, q)) for r in range(2)]
+        for p in procs:
+            p.start()
+        res = sorted(q.get(timeout=120) for _ in range(2))
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    # every bucket adds 1 to both halves; partitions alternate between the two ranks
+    assert res[0] == (0, [101.0, 101.0, 202.0, 202.0, 103.0, 103.0], 203.0, 203.0)
+    assert res[1] == (1, [201.0, 201.0, 102.0, 102.0, 203.0, 203.0], 103.0, 103.0)
