@@ -225,7 +225,10 @@ __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, 
 #define TILE_WARPS_EMB 4
 #define UPD_WAIT_LIMIT 4000000
 
-template <int VEC, int RULE>
+// PLAIN: the slot's gradient row is already the gradient of the table row (dot comparator, no operator
+// or a translation) -- compiled without the comparator / operator pull-back, whose predicated-off
+// copies in the unrolled loops cost more issue slots than the additions themselves.
+template <int VEC, int RULE, bool PLAIN>
 __global__ void __launch_bounds__(32 * (RULE == RULE_EMB ? TILE_WARPS_EMB : UPD_WARPS), RULE == RULE_EMB ? 3 : 2)
 tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long long *__restrict__ keys,
                    const unsigned int *__restrict__ vals, float lr, float *__restrict__ psum,
@@ -259,6 +262,7 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
   unsigned long long kA = pa >= 0 ? keys[pa] : SENT;
   unsigned long long kB = pb < d.nocc ? keys[pb] : SENT;
   unsigned int vB = pb < d.nocc ? vals[pb] : 0u;
+  const int bB = (int)(vB / (unsigned int)d.spb);              // batch of this lane's slot
   if (__shfl_sync(FULL, kB, TILE - 1) < lo) return;          // tile holds only the other rule's rows
   // Copies the gradient rows of window slots j0 .. j0+cnt-1 (cnt <= TILE) into the stage buffers and
   // waits for them; the wait is bounded (bit 1 of the error word when it runs out).
@@ -326,7 +330,10 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
     for (int j = i; j <= i + nproc; ++j) {
       bool in = j < i + nproc;
       Occ oc;
-      if (in) oc = occ_decode(d, (int)__shfl_sync(FULL, vB, j));
+      if (in) {
+        if (PLAIN) oc.b = __shfl_sync(FULL, bB, j);
+        else oc = occ_decode(d, (int)__shfl_sync(FULL, vB, j));
+      }
       if (cur_b >= 0 && (!in || oc.b != cur_b)) {             // a batch of this row is complete
         if (hub) {
           float *dst = psum + (size_t)(t0 + run_start) * d.Dp;
@@ -351,7 +358,15 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
         }
         gs = stage + (size_t)(j - staged_lo) * d.Dp;
       }
-      add_slot<VEC, RULE>(acc, d, wb, w, oc, lane, gs);
+      if (PLAIN) {
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) {
+          int dd = c * 128 + lane * 4;
+          if (dd < D) acc[c] = acc[c] + ld4(gs + dd);
+        }
+      } else {
+        add_slot<VEC, RULE>(acc, d, wb, w, oc, lane, gs);
+      }
     }
     if (!hub) rs.store(D, lane);
     else if (head_here && lane == 0) hublist[atomicAdd(hubcnt, 1)] = t0 + i;
@@ -666,12 +681,17 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   if (!attr_done[0]) {
     cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem_max);
     cudaFuncSetAttribute(hub_reduce_kernel<VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_smem);
-    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
+    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
     attr_done[0] = true;
   }
   cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
-  tile_update_kernel<VEC, RULE_EMB><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  // the gradient slot is the row's gradient as it stands: dot comparator, and no operator or a translation
+  const bool plain = d.cmp == PBG_CMP_DOT && !d.matrix_op && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION);
+  if (plain) tile_update_kernel<VEC, RULE_EMB, true><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  else tile_update_kernel<VEC, RULE_EMB, false><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt);
   hub_update_kernel<VEC, RULE_EMB><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   ++launches;
@@ -683,7 +703,7 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
         attr_done[1] = true;
       }
       cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
-      tile_update_kernel<VEC, RULE_REL><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      tile_update_kernel<VEC, RULE_REL, false><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
       hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt);
       hub_update_kernel<VEC, RULE_REL><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
       ++launches;
