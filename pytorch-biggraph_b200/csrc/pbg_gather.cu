@@ -236,6 +236,65 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
   }
 }
 
+// The same work when nothing has to be computed on the way -- standard relations, no operator, dot
+// comparator: the operand rows are plain copies of the table rows, and the positive score is their
+// dot product.  Both rows of a slot (lhs side, rhs side) are loaded at once, which doubles the bytes
+// a warp keeps in flight, and the kernel carries none of the operator / prepare code of the general
+// one (half the registers, three CTAs per SM instead of two).
+template <int VEC>
+__global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 16 ? 1 : VEC >= 8 ? 3 : 4) gather_plain_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * GATHER_WARPS + (threadIdx.x >> 5);
+  if (item >= (long long)d.nblk * d.Mm) return;
+  int lb = (int)(item / d.Mm), r = (int)(item - (long long)lb * d.Mm);
+  const int blk = d.blk0 + lb;
+  BlockInfo bi = block_info(d, wb, blk);
+  const int D = d.D;
+  size_t nrow = (size_t)blk * d.Mm + r;
+  const size_t noff = nrow * d.Dp;
+  float *n0 = w.X[ARR_N0] + noff, *n1 = w.X[ARR_N1] + noff;
+  long long i0, i1;
+  const bool edge = r < d.Pm;
+  if (edge) {
+    bool ok = r < bi.n;
+    i0 = ok ? w.lhs[bi.e0 + r] : -1;
+    i1 = ok ? w.rhs[bi.e0 + r] : -1;
+    if (ok && (i0 < 0 || i0 >= d.n_rows[0] || i1 < 0 || i1 >= d.n_rows[1])) {
+      if (lane == 0) atomicOr(w.errflag, 1);
+      ok = false;
+    }
+    if (!ok) i0 = i1 = -1;                                  // padding row: exact zeros on both sides
+  } else {
+    i0 = slot_row(d, wb, w, bi, 0, r);
+    i1 = slot_row(d, wb, w, bi, 1, r);
+    if (i0 >= d.n_rows[0]) { if (lane == 0) atomicOr(w.errflag, 1); i0 = -1; }
+    if (i1 >= d.n_rows[1]) { if (lane == 0) atomicOr(w.errflag, 1); i1 = -1; }
+  }
+  float4 a[VEC], b[VEC];
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int dd = c * 128 + lane * 4;
+    a[c] = (i0 >= 0 && dd < D) ? ld4(w.W[0] + (size_t)i0 * D + dd) : f4zero();
+  }
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int dd = c * 128 + lane * 4;
+    b[c] = (i1 >= 0 && dd < D) ? ld4(w.W[1] + (size_t)i1 * D + dd) : f4zero();
+  }
+  store_row<VEC>(n0, a, D, lane);
+  store_row<VEC>(n1, b, D, lane);
+  float s = 0.f;
+  if (edge) {
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) s += f4dot(a[c], b[c]);
+    s = warp_sum(s);
+  }
+  if (lane == 0) {
+    w.aux[ARR_N0][nrow] = 0.f; w.aux[ARR_N1][nrow] = 0.f;
+    if (edge) { size_t q = (size_t)blk * d.Pm + r; w.spos[0][q] = s; w.spos[1][q] = s; }
+  }
+}
+
 // linear / affine operators: R2 holds A.x for every rhs row of the chunk blocks; this kernel adds
 // the translation (affine), applies comparator.prepare, writes the operand row to N1 and, for the
 // chunk's edges, the positive score against the lhs row already in N0.
@@ -300,6 +359,15 @@ int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, c
   long long items = (long long)d.nblk * d.Mm;
   int ctas = (int)((items + GATHER_WARPS - 1) / GATHER_WARPS);
   int vec = (d.D + 127) / 128;
+  const bool plain = !d.dynamic && !d.matrix_op && !d.split && d.cmp == PBG_CMP_DOT && (d.op == PBG_OP_NONE || w.theta[0] == nullptr);
+  if (plain) {
+    if (vec <= 1) gather_plain_kernel<1><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 2) gather_plain_kernel<2><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 4) gather_plain_kernel<4><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 8) gather_plain_kernel<8><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else gather_plain_kernel<16><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    return 1;
+  }
   if (vec <= 1) gather_kernel<1><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
   else if (vec <= 2) gather_kernel<2><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
   else if (vec <= 4) gather_kernel<4><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
