@@ -17,7 +17,9 @@
 #define UPD_WARPS 8
 
 // Everything needed to pull one gradient slot back to the embedding row it came from.
-template <int VEC>
+// CMPK >= 0 fixes the comparator at compile time, OPK == 0 states that the operator does not scale
+// the gradient (none / translation): the kernels instantiated that way carry no dead branches.
+template <int VEC, int CMPK = -1, int OPK = -1>
 struct SlotGrad {
   const float *g, *y, *ylo; // gradient row, prepared operand row (+ its low part in split mode)
   const float *theta;      // operator row or null
@@ -30,7 +32,7 @@ struct SlotGrad {
   __device__ __forceinline__ void init(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                                        int a, int blk, int r, int b, int lane, const float *gstage = nullptr,
                                        bool pre_op = false) {
-    D = d.D; op = d.op; cmp = d.cmp;
+    D = d.D; op = OPK == 0 ? PBG_OP_NONE : d.op; cmp = CMPK >= 0 ? CMPK : d.cmp;
     size_t xr = (size_t)blk * w.xrows[a] + r, gr = (size_t)blk * w.grows[a] + r;
     y = w.X[a] + xr * d.Dp;
     ylo = d.split ? w.XL[a] + xr * d.Dp : nullptr;
@@ -45,7 +47,7 @@ struct SlotGrad {
         return;
       }
     }
-    if (op != PBG_OP_NONE) {
+    if (OPK != 0 && op != PBG_OP_NONE) {
       if (!d.dynamic) {
         if ((a == ARR_N1 || a == ARR_Q0) && w.theta[0]) theta = w.theta[0] + (size_t)wb.rel[b] * D;
       } else if (a == ARR_Q0 || a == ARR_Q1) {
@@ -55,6 +57,7 @@ struct SlotGrad {
         if (tab && rl >= 0 && rl < d.num_rels) theta = tab + (size_t)rl * D;
       }
     }
+    const int cmp = CMPK >= 0 ? CMPK : this->cmp;
     if (cmp >= PBG_CMP_L2) {
       // dynamic: ga = T.N - rowsum(T) a ;  gb = T^T.Q - colsum(T) b.  standard: g = A.N' - rowsum(A) y
       const float *cp = (a == ARR_N0) ? w.coef[0] : (a == ARR_N1) ? w.coef[1] : (a == ARR_Q0) ? w.coef[2] : w.coef[3];
@@ -77,6 +80,7 @@ struct SlotGrad {
   // gradient w.r.t. the operator output z at elements [dd, dd+4)
   __device__ __forceinline__ float4 gz(int dd) const {
     float4 v = ld4(g + dd);
+    const int cmp = CMPK >= 0 ? CMPK : this->cmp;
     if (cmp >= PBG_CMP_L2) v = v - yv(dd) * cf;
     else if (cmp == PBG_CMP_COS) v = (v - yv(dd) * dotgy) * inv;   // (g - y <g,y>) / |z|
     return v;
@@ -84,7 +88,7 @@ struct SlotGrad {
   // gradient w.r.t. the embedding row at elements [dd, dd+4)
   __device__ __forceinline__ float4 gx(int dd) const {
     float4 v = gz(dd);
-    if (theta == nullptr || op == PBG_OP_TRANSLATION) return v;
+    if (OPK == 0 || theta == nullptr || op == PBG_OP_TRANSLATION) return v;
     float4 t = ld4(theta + dd);
     if (op == PBG_OP_DIAGONAL) return v * t;
     int h = D >> 1;
@@ -98,7 +102,7 @@ struct SlotGrad {
 // d(loss)/d(operator row) contributed by one slot whose operand went through the operator:
 // needs the gradient at the operator output (gz) and the raw embedding row x.
 template <int VEC>
-__device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC> &sg, const float *x, const float *xlo, float xscale, int dd) {
+__device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC, -1, -1> &sg, const float *x, const float *xlo, float xscale, int dd) {
   float4 v = sg.gz(dd);
   if (sg.op == PBG_OP_TRANSLATION) return v;
   float4 xv = (xlo ? ld4(x + dd) + ld4(xlo + dd) : ld4(x + dd)) * xscale;
@@ -191,12 +195,12 @@ struct RowState {
 };
 
 // acc += the contribution of one slot to its row's gradient
-template <int VEC, int RULE>
+template <int VEC, int RULE, int CMPK = -1, int OPK = -1>
 __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, const WaveBatches &wb,
                                          const WaveBufs &w, const Occ &oc, int lane, const float *gstage = nullptr) {
   const int D = d.D;
-  SlotGrad<VEC> sg;
   if (RULE == RULE_EMB) {
+    SlotGrad<VEC, CMPK, OPK> sg;
     sg.init(d, wb, w, oc.a, oc.blk, oc.r, oc.b, lane, gstage);
 #pragma unroll
     for (int c = 0; c < VEC; ++c) {
@@ -204,6 +208,7 @@ __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, 
       if (dd < D) acc[c] = acc[c] + sg.gx(dd);
     }
   } else {
+    SlotGrad<VEC, -1, -1> sg;
     int qa = oc.a == ARR_R0 ? ARR_Q0 : ARR_Q1;             // slot that carried the operator
     int na = oc.a == ARR_R0 ? ARR_N1 : ARR_N0;             // its operator-free copy (raw row)
     sg.init(d, wb, w, qa, oc.blk, oc.r, oc.b, lane);
@@ -225,16 +230,19 @@ __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, 
 #define TILE_WARPS_EMB 4
 #define UPD_WAIT_LIMIT 4000000
 
-// PLAIN: the slot's gradient row is already the gradient of the table row (dot comparator, no operator
-// or a translation) -- compiled without the comparator / operator pull-back, whose predicated-off
-// copies in the unrolled loops cost more issue slots than the additions themselves.
-template <int VEC, int RULE, bool PLAIN>
+// MODE 1 (plain): the slot's gradient row is already the gradient of the table row (dot comparator, no
+// operator or a translation) -- compiled without the comparator / operator pull-back, whose
+// predicated-off copies in the unrolled loops cost more issue slots than the additions themselves.
+// MODE 2: cos comparator with no operator or a translation, comparator fixed at compile time.
+// MODE 0: everything decided at run time.
+template <int VEC, int RULE, int MODE>
 __global__ void __launch_bounds__(32 * (RULE == RULE_EMB ? TILE_WARPS_EMB : UPD_WARPS), RULE == RULE_EMB ? 3 : 2)
 tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long long *__restrict__ keys,
                    const unsigned int *__restrict__ vals, float lr, float *__restrict__ psum,
                    long long *__restrict__ hublist, int *__restrict__ hubcnt) {
   constexpr int WARPS = RULE == RULE_EMB ? TILE_WARPS_EMB : UPD_WARPS;
   constexpr bool STAGED = RULE == RULE_EMB;
+  constexpr bool PLAIN = MODE == 1;
   extern __shared__ __align__(128) float stage_all[];        // [WARPS][TILE][Dp] (STAGED only)
   __shared__ __align__(8) unsigned long long sbar[WARPS];
   const unsigned FULL = 0xffffffffu;
@@ -364,6 +372,8 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
           int dd = c * 128 + lane * 4;
           if (dd < D) acc[c] = acc[c] + ld4(gs + dd);
         }
+      } else if (MODE == 2) {
+        add_slot<VEC, RULE, PBG_CMP_COS, 0>(acc, d, wb, w, oc, lane, gs);
       } else {
         add_slot<VEC, RULE>(acc, d, wb, w, oc, lane, gs);
       }
@@ -681,17 +691,21 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   if (!attr_done[0]) {
     cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem_max);
     cudaFuncSetAttribute(hub_reduce_kernel<VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_smem);
-    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
-    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
+    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
     attr_done[0] = true;
   }
   cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
   // the gradient slot is the row's gradient as it stands: dot comparator, and no operator or a translation
   const bool plain = d.cmp == PBG_CMP_DOT && !d.matrix_op && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION);
-  if (plain) tile_update_kernel<VEC, RULE_EMB, true><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
-  else tile_update_kernel<VEC, RULE_EMB, false><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  if (plain) tile_update_kernel<VEC, RULE_EMB, 1><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  else if (d.cmp == PBG_CMP_COS && !d.matrix_op && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION))
+    tile_update_kernel<VEC, RULE_EMB, 2><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  else tile_update_kernel<VEC, RULE_EMB, 0><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt);
   hub_update_kernel<VEC, RULE_EMB><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   ++launches;
@@ -703,7 +717,7 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
         attr_done[1] = true;
       }
       cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
-      tile_update_kernel<VEC, RULE_REL, false><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      tile_update_kernel<VEC, RULE_REL, 0><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
       hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt);
       hub_update_kernel<VEC, RULE_REL><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
       ++launches;
