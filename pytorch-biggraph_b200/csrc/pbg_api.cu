@@ -23,7 +23,7 @@ struct pbg_context {
   SortPlan sort[2];        // double-buffered: wave w+1 is sorted on `side` while wave w trains
   cudaStream_t side = nullptr;      // key build + sort of the next wave
   cudaStream_t part2 = nullptr;     // second half of a wave's gather / score / loss / gradient kernels
-  cudaEvent_t ev_wave = nullptr, ev_part2 = nullptr;
+  cudaEvent_t ev_wave = nullptr, ev_part2 = nullptr, ev_joined = nullptr, ev_stats = nullptr;
   cudaEvent_t ev_sorted[2] = {nullptr, nullptr}, ev_updated[2] = {nullptr, nullptr}, ev_inputs = nullptr;
   pbg_batch_stats *stats_dev = nullptr;
   int stats_cap = 0;
@@ -254,6 +254,8 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   CU(c, cudaStreamCreateWithFlags(&c->part2, cudaStreamNonBlocking));
   CU(c, cudaEventCreateWithFlags(&c->ev_wave, cudaEventDisableTiming));
   CU(c, cudaEventCreateWithFlags(&c->ev_part2, cudaEventDisableTiming));
+  CU(c, cudaEventCreateWithFlags(&c->ev_joined, cudaEventDisableTiming));
+  CU(c, cudaEventCreateWithFlags(&c->ev_stats, cudaEventDisableTiming));
   c->sum_dev = (double *)(c->ws + oSum);
   c->errflag = (int *)(c->ws + oErr);
   c->eval_dev = (double *)(c->ws + oEval);
@@ -290,6 +292,8 @@ extern "C" int pbg_destroy(pbg_context *c) {
   if (c->part2) cudaStreamDestroy(c->part2);
   if (c->ev_wave) cudaEventDestroy(c->ev_wave);
   if (c->ev_part2) cudaEventDestroy(c->ev_part2);
+  if (c->ev_joined) cudaEventDestroy(c->ev_joined);
+  if (c->ev_stats) cudaEventDestroy(c->ev_stats);
   for (auto &s : c->spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
   for (auto e : c->event_pool) cudaEventDestroy(e);
   delete c;
@@ -483,6 +487,15 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
     } else {
       run_part(c, d, wb, w, c->stream);
     }
+    // The per-batch statistics need the loss rows of both halves and nothing of the update: they are
+    // summed on the second stream while the update runs on the first.
+    const bool stats_aside = kk >= 2;
+    if (stats_aside) {
+      CU(c, cudaEventRecord(c->ev_joined, c->stream));
+      CU(c, cudaStreamWaitEvent(c->part2, c->ev_joined, 0));
+      { ClassTimer t(c, 6, c->part2); t.done(launch_stats(d, wb, w, stats_out ? c->stats_dev : nullptr, c->sum_dev, c->part2)); }
+      CU(c, cudaEventRecord(c->ev_stats, c->part2));
+    }
     CU(c, cudaStreamWaitEvent(c->stream, c->ev_sorted[wave & 1], 0));
     {
       ClassTimer t(c, 5);
@@ -490,7 +503,8 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
                            c->cfg.lr, c->cfg.relation_lr, c->psum, c->hublist, c->hubcnt, c->stream));
     }
     CU(c, cudaEventRecord(c->ev_updated[wave & 1], c->stream));
-    { ClassTimer t(c, 6); t.done(launch_stats(d, wb, w, stats_out ? c->stats_dev : nullptr, c->sum_dev, c->stream)); }
+    if (stats_aside) CU(c, cudaStreamWaitEvent(c->stream, c->ev_stats, 0));   // the next wave rewrites the loss rows
+    else { ClassTimer t(c, 6); t.done(launch_stats(d, wb, w, stats_out ? c->stats_dev : nullptr, c->sum_dev, c->stream)); }
   }
   c->batches_done += (unsigned long long)num_batches;
   CU(c, cudaGetLastError());
