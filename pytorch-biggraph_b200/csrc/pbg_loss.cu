@@ -203,12 +203,126 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_kernel(WaveDims d, WaveB
   }
 }
 
+// Softmax under the dot / cos comparators with at most 32 NV negative columns: the warp keeps the
+// row in registers, so the scores are read once, the masks evaluated once and every exponential
+// taken once (the general kernel makes three passes).  Same arithmetic, same summation order.
+template <int NV>
+__global__ void __launch_bounds__(32 * LOSS_WARPS) loss_softmax_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * LOSS_WARPS + (threadIdx.x >> 5);
+  long long per_prob = (long long)d.nblk * d.Pm;
+  if (item >= 2 * per_prob) return;
+  int p = (int)(item / per_prob);
+  long long rem = item - p * per_prob;
+  int lb = (int)(rem / d.Pm), i = (int)(rem - (long long)lb * d.Pm);
+  const int blk = d.blk0 + lb;
+  BlockInfo bi = block_info(d, wb, blk);
+  if (bi.n == 0) return;
+  float *S = w.S[p] + ((size_t)blk * d.Pm + i) * d.Ms;
+  size_t prow = (size_t)blk * d.Pm + i;
+  const int Mm = d.Mm;
+  const int enabled = d.neg_enabled[p];
+  const int Mlog = !enabled ? 0 : (d.batch_negs ? bi.Pl + d.U : d.U);
+  if (i >= bi.n || Mlog == 0) {                      // padded positive, or no negatives at all: no loss, no gradient
+#pragma unroll
+    for (int u = 0; u < NV; ++u) { int j = lane + 32 * u; if (j < d.Ms) S[j] = 0.f; }
+    if (lane == 0) { w.lossrow[p][prow] = 0.f; w.violrow[p][prow] = 0; }
+    return;
+  }
+  const float s = w.spos[p][prow];
+  const float wr = wb.wrel[bi.b];
+  float sv[NV];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    int j = lane + 32 * u;
+    bool valid = j < Mm && !col_masked(d, bi, enabled, i, j);
+    sv[u] = valid ? S[j] : -INFINITY;
+    mx = fmaxf(mx, sv[u]);
+  }
+  mx = warp_max(mx);
+  float m = fmaxf(mx, s);
+  if (mx == -INFINITY) m = fmaxf(s, PBG_MASKED);      // every column masked
+  float z = 0.f;
+  int viol = 0;
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    bool valid = sv[u] != -INFINITY;
+    viol += valid && sv[u] > s;
+    sv[u] = valid ? expf(sv[u] - m) : 0.f;
+    z += sv[u];
+  }
+  z = warp_sum(z);
+  viol = warp_sum_int(viol);
+  float es = expf(s - m);
+  float Z = z + es;
+  float lossv = -s + m + logf(Z);
+  float invZ = 1.0f / Z;
+  float tdiag = wr * (es / Z - 1.0f);
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    int j = lane + 32 * u;
+    if (j < d.Ms) S[j] = j == i ? tdiag : wr * sv[u] * invZ;
+  }
+  if (lane == 0) { w.lossrow[p][prow] = wr * lossv; w.violrow[p][prow] = viol; }
+}
+
+// Combined coefficient matrices under the dot / cos comparators, one warp per 32 x 32 tile of
+// A[side]: lane l reads 32 consecutive values of row j0 + l of T_side (whole 128-byte lines, eight
+// 16-byte loads) and keeps them; value r of every lane is then column j0 + l of output row m0 + r,
+// so that both the transposed term and the direct term T_other[m][j] are read and A is written in
+// whole lines without a shuffle or shared memory.
+__global__ void __launch_bounds__(32 * LOSS_WARPS) coef_tile_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * LOSS_WARPS + (threadIdx.x >> 5);
+  const int tiles = (d.Mm + 31) / 32;
+  long long per_side = (long long)d.nblk * tiles * tiles;
+  if (item >= 2 * per_side) return;
+  int side = (int)(item / per_side);
+  long long rem = item - side * per_side;
+  int lb = (int)(rem / (tiles * tiles)), tt = (int)(rem - (long long)lb * tiles * tiles);
+  int m0 = (tt / tiles) * 32, j0 = (tt % tiles) * 32;
+  const int blk = d.blk0 + lb;
+  BlockInfo bi = block_info(d, wb, blk);
+  if (bi.n == 0) return;
+  const int j = j0 + lane;
+  float t[32];
+  const float *src = w.S[side] + ((size_t)blk * d.Pm + j) * d.Ms + m0;       // T_side[j][m0 ..]
+  const bool has = j < bi.n;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    float4 v = (has && m0 + 4 * q < d.Ms) ? ld4(src + 4 * q) : f4zero();
+    t[4 * q] = v.x; t[4 * q + 1] = v.y; t[4 * q + 2] = v.z; t[4 * q + 3] = v.w;
+  }
+  const float *orow = w.S[1 - side] + (size_t)blk * d.Pm * d.Ms;              // T_other[m][j]
+  float *A = w.A[side] + (size_t)blk * d.Mm * w.Ma;
+#pragma unroll
+  for (int r = 0; r < 32; ++r) {
+    int m = m0 + r;
+    if (m < d.Mm && j < w.Ma) {
+      float a = j < d.Mm ? t[r] : 0.f;
+      if (m < bi.n && j < d.Mm) a += orow[(size_t)m * d.Ms + j];
+      A[(size_t)m * w.Ma + j] = a;
+    }
+  }
+}
+
 int launch_loss(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
   long long items = 2ll * d.nblk * d.Pm;
-  loss_kernel<<<(int)((items + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+  const int loss_ctas = (int)((items + LOSS_WARPS - 1) / LOSS_WARPS);
+  const bool dotlike = d.cmp < PBG_CMP_L2 && !d.split;
+  if (dotlike && d.loss == PBG_LOSS_SOFTMAX && d.Ms <= 128) loss_softmax_kernel<4><<<loss_ctas, 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+  else if (dotlike && d.loss == PBG_LOSS_SOFTMAX && d.Ms <= 256) loss_softmax_kernel<8><<<loss_ctas, 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+  else loss_kernel<<<loss_ctas, 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
   if (!d.dynamic) {
-    long long rows = 2ll * d.nblk * d.Mm;
-    coef_kernel<<<(int)((rows + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+    if (dotlike) {
+      const int tiles = (d.Mm + 31) / 32;
+      long long warps = 2ll * d.nblk * tiles * tiles;
+      coef_tile_kernel<<<(int)((warps + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+    } else {
+      long long rows = 2ll * d.nblk * d.Mm;
+      coef_kernel<<<(int)((rows + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+    }
     return 2;
   }
   if (d.cmp >= PBG_CMP_L2) {
