@@ -220,7 +220,11 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
       if (!tile_live(t, p, blk, m0, n0)) continue;
       for (int kb = 0; kb < nkb; ++kb, ++git) {
         int s = (int)(git % STAGES);
-        if (!__all_sync(0xffffffffu, mbar_wait(full_bar(s), (uint32_t)(git / STAGES) & 1, errflag))) { failed = 1; stop = true; break; }
+        // one lane per warp polls the barrier (256 polling threads would take issue slots from the warps
+        // that have work); the warp-wide vote that follows orders the other lanes' reads after it
+        bool okw = true;
+        if (lane == 0) okw = mbar_wait(full_bar(s), (uint32_t)(git / STAGES) & 1, errflag);
+        if (!__all_sync(0xffffffffu, okw)) { failed = 1; stop = true; break; }
         unsigned char *st = smem + (size_t)s * STAGE_BYTES;
         for (uint32_t c0 = ct; c0 < nchunks; c0 += 4 * TC_SPLIT_THREADS) {
           float4 v[4];
@@ -252,7 +256,9 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
       if (__any_sync(0xffffffffu, failed != 0)) break;           // warp-uniform exit (tcgen05.ld is warp-wide)
       if (!tile_live(t, p, blk, m0, n0)) continue;
       const int ab = (int)(j & 1);
-      if (!__all_sync(0xffffffffu, mbar_wait(accf_bar(ab), (uint32_t)(j >> 1) & 1, errflag))) { failed = 1; break; }
+      bool okw = true;
+      if (lane == 0) okw = mbar_wait(accf_bar(ab), (uint32_t)(j >> 1) & 1, errflag);
+      if (!__all_sync(0xffffffffu, okw)) { failed = 1; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int mrow0 = m0 + q * 32;                 // first output row of this warp's block
       const int m = mrow0 + lane;
