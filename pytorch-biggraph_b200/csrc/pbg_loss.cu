@@ -313,6 +313,8 @@ int launch_loss(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cud
   const bool dotlike = d.cmp < PBG_CMP_L2 && !d.split;
   if (dotlike && d.loss == PBG_LOSS_SOFTMAX && d.Ms <= 128) loss_softmax_kernel<4><<<loss_ctas, 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
   else if (dotlike && d.loss == PBG_LOSS_SOFTMAX && d.Ms <= 256) loss_softmax_kernel<8><<<loss_ctas, 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+  else if (dotlike && d.loss == PBG_LOSS_SOFTMAX && d.Ms <= 512) loss_softmax_kernel<16><<<loss_ctas, 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+  else if (dotlike && d.loss == PBG_LOSS_SOFTMAX && d.Ms <= 1024) loss_softmax_kernel<32><<<loss_ctas, 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
   else loss_kernel<<<loss_ctas, 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
   if (!d.dynamic) {
     if (dotlike) {
