@@ -45,7 +45,7 @@ WORKLOADS = {
 EDGES_PER_STEP_CAP = 269_507
 # DRAM bytes per trained edge of each kernel class, from the ncu capture summarised in
 # profiles/kernels_c3_tf32x3.md (workload c3, tf32x3); dram__bytes_read.sum + dram__bytes_write.sum per launch / edges per launch
-NCU_TRAFFIC_PER_EDGE = {("c3", "tf32x3"): {"gather": 23.9e3, "score": 17.8e3, "grad": 29.8e3, "update": 40.5e3}}
+NCU_TRAFFIC_PER_EDGE = {("c3", "tf32x3"): {"gather": 22.7e3, "score": 17.0e3, "grad": 29.6e3, "update": 40.5e3}}
 REF_BATCHES = 5          # batches per worker in one step of the CPU reference arm
 
 
@@ -552,7 +552,7 @@ def run_b200(args, w):
     # ---- per-kernel-class timing pass ----------------------------------------------------------
     import ctypes as C
     check = _lib.check
-    check(nat.lib.pbg_set_profiling(nat.ctx, 1), nat.ctx)
+    check(nat.lib.pbg_set_profiling(nat.ctx, 2), nat.ctx)     # halves of a wave one after the other: a pair brackets its kernels alone
     for s in range(total_steps, total_steps + nprof):
         step_device(s)
     drain()
@@ -581,11 +581,16 @@ def run_b200(args, w):
     launches_dom = max(per_class[dom]["launches"], 1)
     per_edge = NCU_TRAFFIC_PER_EDGE.get((args.workload, args.precision), {}).get(dom)
     # ncu's DRAM bytes of the dominant class, per launch of this run (edges of the timing pass / its launches)
-    traffic = None if per_edge is None else per_edge * edges_prof / (launches_dom if dom != "update" else launches_dom / 2)
+    # (the update class is several kernels per wave, the tile kernel carries its traffic: one launch per wave, as the statistics kernel)
+    dom_kernel_launches = max(per_class["stats"]["launches"], 1) if dom == "update" else launches_dom
+    traffic = None if per_edge is None else per_edge * edges_prof / dom_kernel_launches
     if dom in model_flops:
         ach = per_class[dom]["TFLOPs"]
+        per_product = {"tf32x3": 6.0, "tf32": 2.0}.get(args.precision)     # TF32 runs at half the bf16 rate; TF32X3 issues three MMAs per product
         roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
                 "frac": round(ach / pk["tflops"], 4), "traffic": traffic,
+                "ceiling_for_precision": None if per_product is None else round(pk["tflops"] / per_product, 1),
+                "frac_of_ceiling": None if per_product is None else round(ach * per_product / pk["tflops"], 4),
                 "peak_source": pk["source"] + " (cuBLAS bf16, sustained); the contraction runs in " + args.precision}
     else:
         ach = per_class[dom]["GBps"]

@@ -214,6 +214,10 @@ int64_t pbg_launch_count(const pbg_context *ctx);
  * class of launches of every wave is bracketed by an event pair, which costs a little
  * throughput: switch it on for a measuring pass only.  pbg_kernel_times synchronises the
  * stream, adds up the pairs recorded since the last read and clears them.
+ * enable = 1: pairs on the streams as the library uses them (the two halves of a wave run on two
+ * streams and their classes overlap: a pair then spans whatever ran beside its kernels);
+ * enable = 2: the halves are launched one after the other on the context's stream, so that a pair
+ * brackets its kernels alone -- the durations to hold against a roofline.
  * Classes: 0 sort keys + radix sort, 1 gather/operator/prepare, 2 score contraction, 3 loss,
  * 4 gradient contractions, 5 optimizer updates, 6 stats.  ms_out / launches_out: HOST arrays of
  * PBG_NUM_KERNEL_CLASSES entries. */

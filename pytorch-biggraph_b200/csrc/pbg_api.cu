@@ -42,6 +42,7 @@ struct pbg_context {
   unsigned long long batches_done = 0;
   // optional event timing per kernel class
   bool profiling = false;
+  bool profile_serial = false;   // profiling mode 2: one stream, so that an event pair brackets one kernel class alone
   struct Span { int cls; int launches; cudaEvent_t a, b; };
   std::vector<Span> spans;
   std::vector<cudaEvent_t> event_pool;
@@ -391,6 +392,7 @@ static void run_part(pbg_context *c, const WaveDims &d, const WaveBatches &wb, c
 extern "C" int pbg_set_profiling(pbg_context *c, int enable) {
   if (!c) return PBG_ERR_BAD_ARGUMENT;
   c->profiling = enable != 0;
+  c->profile_serial = enable == 2;
   return PBG_OK;
 }
 
@@ -473,7 +475,14 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
     // kernels can run as two independent halves on two streams: the memory-bound kernels of one
     // half fill the SMs' idle issue slots while the other half's contractions run.
     d.blk0 = 0;
-    if (kk >= 2) {
+    if (kk >= 2 && c->profile_serial) {
+      int ka = (kk + 1) / 2;
+      WaveDims da = d, db = d;
+      da.nblk = ka * d.Cm;
+      db.blk0 = ka * d.Cm; db.nblk = (kk - ka) * d.Cm;
+      run_part(c, da, wb, w, c->stream);
+      run_part(c, db, wb, w, c->stream);
+    } else if (kk >= 2) {
       int ka = (kk + 1) / 2;
       WaveDims da = d, db = d;
       da.nblk = ka * d.Cm;
@@ -489,7 +498,7 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
     }
     // The per-batch statistics need the loss rows of both halves and nothing of the update: they are
     // summed on the second stream while the update runs on the first.
-    const bool stats_aside = kk >= 2;
+    const bool stats_aside = kk >= 2 && !c->profile_serial;
     if (stats_aside) {
       CU(c, cudaEventRecord(c->ev_joined, c->stream));
       CU(c, cudaStreamWaitEvent(c->part2, c->ev_joined, 0));
