@@ -44,7 +44,7 @@ WORKLOADS = {
 }
 EDGES_PER_STEP_CAP = 269_507
 # DRAM bytes per trained edge of each kernel class, from the ncu capture summarised in
-# profiles/kernels_c3_tf32x3.md (workload c3, tf32x3); dram__bytes_read.sum + dram__bytes_write.sum per launch / edges per launch
+# the profiles folder (workload c3, tf32x3); dram__bytes_read.sum + dram__bytes_write.sum per launch / edges per launch
 NCU_TRAFFIC_PER_EDGE = {("c3", "tf32x3"): {"gather": 22.7e3, "score": 17.0e3, "grad": 29.6e3, "update": 40.5e3}}
 REF_BATCHES = 5          # batches per worker in one step of the CPU reference arm
 

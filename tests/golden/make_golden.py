@@ -352,7 +352,7 @@ def run_case(case):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a PyTorch-BigGraph checkout")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     _bootstrap(args.reference)

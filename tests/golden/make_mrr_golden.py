@@ -70,7 +70,7 @@ def run(case, seed=0):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a PyTorch-BigGraph checkout")
     args = ap.parse_args()
     _bootstrap(args.reference)
     out, runs = {}, {}
