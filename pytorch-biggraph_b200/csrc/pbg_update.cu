@@ -421,8 +421,11 @@ hub_reduce_kernel(WaveDims d, const unsigned long long *__restrict__ keys, const
     const int h = (int)(item / d.k), b = (int)(item % d.k);
     const long long head = hublist[h];
     const unsigned long long key = keys[head];
-    const long long end = coop_prefix_end(head + 1, (long long)d.nocc, [&](long long pos) { return keys[pos] == key; });
-    if (end - head < HUB_BIG) continue;
+    // a row's slots are contiguous in the sorted list: it has HUB_BIG or more of them exactly when
+    // the slot HUB_BIG - 1 places after its head still carries its key (one load; the search for
+    // the end is only made for the few big rows)
+    if (head + HUB_BIG - 1 >= (long long)d.nocc || keys[head + HUB_BIG - 1] != key) continue;
+    const long long end = coop_prefix_end(head + HUB_BIG, (long long)d.nocc, [&](long long pos) { return keys[pos] == key; });
     const long long q = coop_prefix_end(head, end, [&](long long pos) { return (int)(vals[pos] / (unsigned int)d.spb) < b; });
     const long long eb = coop_prefix_end(q, end, [&](long long pos) { return (int)(vals[pos] / (unsigned int)d.spb) <= b; });
     if (q >= eb) continue;
