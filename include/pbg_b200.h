@@ -121,7 +121,9 @@ int pbg_set_hyperparameters(pbg_context *ctx, float lr, float relation_lr, float
 
 /* Trains `num_batches` batches on the bucket: the device-side replacement of the loop
  * `for batch_edges in batcher(...): trainer.process_one_batch(model, batch_edges)`
- * (torchbiggraph/batching.py:121-122 -> train_cpu.py:86-112).
+ * (torchbiggraph/batching.py:121-122 -> train_cpu.py:86-112).  The batches are taken in order
+ * in ceil(num_batches / batches_in_flight) waves of equal size (sizes differ by at most one, the
+ * larger waves first); a call with at most batches_in_flight batches is one wave.
  *   lhs, rhs, rel : device int64 arrays of `num_edges` partition-local row ids / relation ids
  *                   (rel may be NULL in standard mode).
  *   batches       : HOST array of num_batches descriptors.

@@ -450,9 +450,14 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
   // and radix sort of a wave run on the side stream and overlap the previous wave's kernels.
   CU(c, cudaEventRecord(c->ev_inputs, c->stream));
   CU(c, cudaStreamWaitEvent(c->side, c->ev_inputs, 0));
+  // The batches are dealt to the fewest waves that hold them, as evenly as possible: 270 batches at
+  // 14 in flight are 20 waves of 14 or 13 rather than 19 full ones and a wave of 4 that would pay
+  // the same launches and joins for a quarter of the work.
+  const int nwaves = (num_batches + c->kmax - 1) / c->kmax;
+  const int kbase = num_batches / nwaves, kextra = num_batches % nwaves;
   int wave = 0;
-  for (int b0 = 0; b0 < num_batches; b0 += c->kmax, ++wave) {
-    int kk = num_batches - b0 < c->kmax ? num_batches - b0 : c->kmax;
+  for (int b0 = 0; b0 < num_batches; ++wave) {
+    const int kk = kbase + (wave < kextra ? 1 : 0);
     WaveBatches wb;
     memset(&wb, 0, sizeof wb);
     for (int i = 0; i < kk; ++i) {
@@ -514,6 +519,7 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
     CU(c, cudaEventRecord(c->ev_updated[wave & 1], c->stream));
     if (stats_aside) CU(c, cudaStreamWaitEvent(c->stream, c->ev_stats, 0));   // the next wave rewrites the loss rows
     else { ClassTimer t(c, 6); t.done(launch_stats(d, wb, w, stats_out ? c->stats_dev : nullptr, c->sum_dev, c->stream)); }
+    b0 += kk;
   }
   c->batches_done += (unsigned long long)num_batches;
   CU(c, cudaGetLastError());

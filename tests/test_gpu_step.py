@@ -193,6 +193,25 @@ def test_wave_of_eight_matches_oracle_with_hub_rows(precision):
     _close(rig.theta("rhs"), ost.theta_rhs, atol=1e-6, what="theta")
 
 
+def test_batches_are_dealt_evenly_to_waves():
+    """Seven batches at three in flight are the waves [3, 2, 2] (not [3, 3, 1]): every wave reads the
+    tables as the previous wave left them."""
+    from b200_util import Rig
+    c, ocfg, ost, batches = _random_case(9, 64, 400, 120, 40, 40, "translation", "dot", "softmax", nbatches=7, zipf=True)
+    rig = Rig.from_oracle_state(c, ost, k=3, precision="fp32")
+    for lo, hi in ((0, 3), (3, 5), (5, 7)):
+        O.train_wave(ocfg, ost, batches[lo:hi])
+    nat = rig.trainer._context(rig.model, 120)
+    lhs = torch.tensor(np.concatenate([b[0] for b in batches])).cuda()
+    rhs = torch.tensor(np.concatenate([b[1] for b in batches])).cuda()
+    ul = torch.stack([nat._uniform(b[3], "cuda") for b in batches]).contiguous()
+    ur = torch.stack([nat._uniform(b[4], "cuda") for b in batches]).contiguous()
+    rig.trainer.train_batches(rig.model, lhs, rhs, None, [(i * 120, 120, 0) for i in range(7)], ul, ur)
+    _close(rig.W_lhs.cpu().numpy(), ost.W_lhs, atol=1e-6, what="W")
+    _close(rig.G("lhs"), ost.G_lhs, atol=1e-8, what="G")
+    _close(rig.theta("rhs"), ost.theta_rhs, atol=1e-6, what="theta")
+
+
 @pytest.mark.parametrize("D,N,B,nb,nu,op,comp,loss,dyn,R", BASELINE_SHAPES)
 def test_single_pass_tf32_is_the_1e3_tier(D, N, B, nb, nu, op, comp, loss, dyn, R):
     """precision="tf32": operands truncated to TF32 once (10 mantissa bits), rtol 1e-3 on the loss;
