@@ -152,6 +152,13 @@ int pbg_train_batches_host(pbg_context *ctx, const pbg_bucket *bucket,
                            const int64_t *uniform_lhs_host, const int64_t *uniform_rhs_host,
                            uint64_t seed, pbg_batch_stats *stats_out);
 
+/* Per-edge weights (EdgeList.weight of the reference: every loss multiplies the loss of a positive
+ * and of its negatives by the edge's weight, torchbiggraph/losses.py:65-78, 104-113, 145-157).
+ * weights_dev: DEVICE float array parallel to the edge arrays of the NEXT pbg_train_batches,
+ * pbg_train_batches_host or pbg_eval_batch call on this context; that call uses it and clears
+ * it.  NULL clears it at once.  Without this call every edge weighs 1. */
+int pbg_set_edge_weights(pbg_context *ctx, const float *weights_dev);
+
 /* Sum of the stats of every batch trained since the last call of this function (device
  * accumulators read back once; Stats.sum in torchbiggraph/stats.py:39-47). */
 int pbg_read_stats(pbg_context *ctx, pbg_batch_stats *sum_out);

@@ -41,6 +41,7 @@ struct pbg_context {
   long long launches = 0;
   unsigned long long batches_done = 0;
   // optional event timing per kernel class
+  const float *edge_w = nullptr;   // per-edge weights for the next train / eval call (pbg_set_edge_weights)
   bool profiling = false;
   bool profile_serial = false;   // profiling mode 2: one stream, so that an event pair brackets one kernel class alone
   struct Span { int cls; int launches; cudaEvent_t a, b; };
@@ -348,6 +349,7 @@ static int bind_bucket(pbg_context *c, const pbg_bucket *bk, WaveDims &d, WaveBu
   d.key_rel_base = emb_keys;
   d.key_invalid = emb_keys + ((d.dynamic && has_op) ? 2ull * cfg.num_rels : 0ull);
   w = c->bufs;
+  w.ew = nullptr;
   w.W[0] = bk->lhs_emb; w.G[0] = bk->lhs_state; w.W[1] = bk->rhs_emb; w.G[1] = bk->rhs_state;
   w.theta[0] = has_op ? bk->rhs_op : nullptr; w.acc[0] = has_op ? bk->rhs_op_state : nullptr;
   w.theta[1] = (has_op && d.dynamic) ? bk->lhs_op : nullptr; w.acc[1] = (has_op && d.dynamic) ? bk->lhs_op_state : nullptr;
@@ -437,6 +439,7 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
   }
   w.lhs = (const long long *)lhs; w.rhs = (const long long *)rhs; w.rel = (const long long *)rel;
   w.ul = (const long long *)ul; w.ur = (const long long *)ur;
+  w.ew = c->edge_w; c->edge_w = nullptr;                    // per-edge weights apply to one call
   w.seed = seed ^ (c->batches_done * 0x9E3779B97F4A7C15ull);
   if (stats_out && num_batches > c->stats_cap) {
     if (c->stats_dev) cudaFree(c->stats_dev);
@@ -570,6 +573,12 @@ extern "C" int pbg_train_batches_host(pbg_context *c, const pbg_bucket *bk, cons
                            (const int64_t *)uld, (const int64_t *)urd, seed, stats_out);
 }
 
+extern "C" int pbg_set_edge_weights(pbg_context *c, const float *weights_dev) {
+  if (!c) return PBG_ERR_BAD_ARGUMENT;
+  c->edge_w = weights_dev;
+  return PBG_OK;
+}
+
 extern "C" int pbg_read_stats(pbg_context *c, pbg_batch_stats *out) {
   if (!c || !out) return PBG_ERR_BAD_ARGUMENT;
   CU(c, cudaSetDevice(c->device));
@@ -627,6 +636,7 @@ extern "C" int pbg_eval_batch(pbg_context *c, const pbg_bucket *bk, const int64_
   if (!d.dynamic && (relidx < 0 || relidx >= c->cfg.num_rels)) return fail(c, PBG_ERR_INDEX_RANGE, "relation %d outside [0, %d)", relidx, c->cfg.num_rels);
   if (d.dynamic && d.op != PBG_OP_NONE && !rel) return fail(c, PBG_ERR_BAD_ARGUMENT, "dynamic relations need the rel array");
   w.lhs = (const long long *)lhs; w.rhs = (const long long *)rhs; w.rel = (const long long *)rel;
+  w.ew = c->edge_w; c->edge_w = nullptr;
   w.ul = (const long long *)ul; w.ur = (const long long *)ur; w.seed = seed;
   WaveBatches wb;
   memset(&wb, 0, sizeof wb);

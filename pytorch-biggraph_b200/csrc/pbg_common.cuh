@@ -81,6 +81,7 @@ struct WaveBufs {
   int *violrow[2];                   // per positive row: #(neg > pos)
   int *rankrow[2];                   // evaluation: per positive row, 1 + #(neg >= pos)
   const long long *lhs, *rhs, *rel;  // edge arrays
+  const float *ew;                  // per-edge weights parallel to the edge arrays, or null
   const long long *ul, *ur;          // uniform ids [batches][Cm][U] or null
   unsigned long long seed;
   float *W[2], *G[2];                // embedding tables / RowAdagrad state (lhs, rhs)

@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
   }
   const int enabled = d.neg_enabled[p];
   const float s = w.spos[p][prow];
-  const float wr = wb.wrel[bi.b];
+  const float wr = wb.wrel[bi.b] * (w.ew ? w.ew[bi.e0 + i] : 1.0f);   // relation weight x edge weight
   // number of negative columns the reference's score matrix has for this row (masked included)
   const int Mlog = !enabled ? 0 : (d.batch_negs ? bi.Pl + d.U : d.U);
   float lossv = 0.f, ds = 0.f, rowsum = 0.f;
@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_softmax_kernel(WaveDims 
     return;
   }
   const float s = w.spos[p][prow];
-  const float wr = wb.wrel[bi.b];
+  const float wr = wb.wrel[bi.b] * (w.ew ? w.ew[bi.e0 + i] : 1.0f);   // relation weight x edge weight
   float sv[NV];
   float mx = -INFINITY;
 #pragma unroll

@@ -69,6 +69,7 @@ SYMBOLS = [
     ("pbg_row_adagrad", C.c_int, [_P, _P, _P, C.c_int64, _P, _P, C.c_int32, C.c_float]),
     ("pbg_row_adagrad_static", C.c_int, [_P, _P, C.c_int64, C.c_int32, _P, _P, C.c_int32, C.c_float, _P]),
     ("pbg_launch_count", C.c_int64, [_P]),
+    ("pbg_set_edge_weights", C.c_int, [_P, C.c_void_p]),
     ("pbg_set_profiling", C.c_int, [_P, C.c_int]),
     ("pbg_kernel_times", C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
 ]

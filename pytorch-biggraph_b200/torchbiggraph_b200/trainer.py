@@ -197,9 +197,10 @@ class B200Trainer(AbstractBatchProcessor):
     def train_batches(self, model: MultiRelationEmbedder, lhs: torch.Tensor, rhs: torch.Tensor,
                       rel: Optional[torch.Tensor], batches: List[Tuple[int, int, int]],
                       uniform_lhs: Optional[torch.Tensor] = None, uniform_rhs: Optional[torch.Tensor] = None,
-                      want_per_batch: bool = True) -> List[Stats]:
+                      want_per_batch: bool = True, weights: Optional[torch.Tensor] = None) -> List[Stats]:
         """Trains the listed (offset, count, relation) batches of the edge arrays.  Edge arrays on
-        the CPU are copied by the library (pin them to make the copy asynchronous)."""
+        the CPU are copied by the library (pin them to make the copy asynchronous).  `weights`:
+        per-edge weights parallel to the edge arrays (EdgeList.weight), moved to the device here."""
         if not batches:
             return []
         nat = self._context(model, max(b[1] for b in batches))
@@ -224,6 +225,11 @@ class B200Trainer(AbstractBatchProcessor):
             if t is not None and (t.dtype != torch.long or not t.is_contiguous() or (t.device.type == "cpu") != on_host):
                 raise TypeError("edge and uniform-id arrays must be contiguous int64, all on the host or all on the device")
         self._calls += 1
+        if weights is not None:
+            if weights.shape[0] != lhs.shape[0]:
+                raise ValueError("one weight per edge is needed")
+            weights = weights.to(device=model.device, dtype=torch.float32).contiguous()     # kept alive until the call returns
+            check(nat.lib.pbg_set_edge_weights(nat.ctx, _ptr(weights)), nat.ctx)
         check(fn(nat.ctx, C.byref(bucket), _ptr(lhs), _ptr(rhs), _ptr(rel), lhs.shape[0], barr, len(batches),
                  _ptr(uniform_lhs), _ptr(uniform_rhs), self.seed + self._calls, sarr), nat.ctx)
         if not want_per_batch:
@@ -240,8 +246,6 @@ class B200Trainer(AbstractBatchProcessor):
     # ---- the reference interface ---------------------------------------------------------------
     def _process_one_batch(self, model: MultiRelationEmbedder, batch_edges: EdgeList,
                            uniform_lhs=None, uniform_rhs=None) -> Stats:
-        if batch_edges.has_weight():
-            raise NotImplementedError("per-edge weights have no device code in torchbiggraph_b200")
         dyn = model.num_dynamic_rels > 0
         if dyn and batch_edges.has_scalar_relation_type():
             raise TypeError("Need relation for each positive pair")
@@ -258,7 +262,8 @@ class B200Trainer(AbstractBatchProcessor):
         nat = self._context(model, n)
         ul = None if uniform_lhs is None else nat._uniform(uniform_lhs, dev)
         ur = None if uniform_rhs is None else nat._uniform(uniform_rhs, dev)
-        return self.train_batches(model, lhs, rhs, rel, [(0, n, r)], ul, ur)[0]
+        wgt = torch.as_tensor(batch_edges.weight) if batch_edges.has_weight() else None
+        return self.train_batches(model, lhs, rhs, rel, [(0, n, r)], ul, ur, weights=wgt)[0]
 
     def process_one_batch(self, model, batch_edges, uniform_lhs=None, uniform_rhs=None) -> Stats:
         if self.overrides is not None:
@@ -319,6 +324,9 @@ class B200RankingEvaluator(AbstractBatchProcessor):
         bucket = nat.bucket(model, r, None, warr)
         out = _lib.PbgEvalStats()
         self._calls += 1
+        if batch_edges.has_weight():                 # the evaluator's loss is weighted like the trainer's (eval.py:55-56)
+            wgt = torch.as_tensor(batch_edges.weight).to(device=dev, dtype=torch.float32).contiguous()
+            check(nat.lib.pbg_set_edge_weights(nat.ctx, _ptr(wgt)), nat.ctx)
         check(nat.lib.pbg_eval_batch(nat.ctx, C.byref(bucket), _ptr(lhs), _ptr(rhs), _ptr(rel), n, r, _ptr(ul), _ptr(ur),
                                      self.seed + self._calls, C.byref(out)), nat.ctx)
         return Stats(loss=float(out.loss), pos_rank=out.pos_rank, mrr=out.mrr, r1=out.r1, r10=out.r10, r50=out.r50,

@@ -71,9 +71,10 @@ class Rig:
         return cls(c, st.W_lhs, st.G_lhs, st.W_rhs if sep else None, st.G_rhs if sep else None,
                    st.theta_rhs, st.theta_lhs, st.acc_rhs, st.acc_lhs, **kw)
 
-    def edges(self, lhs, rhs, rel):
+    def edges(self, lhs, rhs, rel, weight=None):
         t = lambda a: torch.tensor(np.asarray(a, np.int64))
-        return T.EdgeList(T.EntityList.from_tensor(t(lhs)), T.EntityList.from_tensor(t(rhs)), t(rel))
+        w = None if weight is None else torch.tensor(np.asarray(weight, np.float32))
+        return T.EdgeList(T.EntityList.from_tensor(t(lhs)), T.EntityList.from_tensor(t(rhs)), t(rel), w)
 
     def G(self, side="lhs"):
         opt, w = (self.opt_l, self.W_lhs) if side == "lhs" else (self.opt_r, self.W_rhs)

@@ -161,6 +161,10 @@ CASES = [
     dict(name="sequence_3_batches", op="complex_diagonal", comp="dot", loss="softmax", B=130, nb=50, nu=20, steps=3),
     dict(name="sequence_3_batches_dyn_cos", op="diagonal", comp="cos", loss="ranking", B=110, nb=50, nu=10, dyn=True, R=6, steps=3, w_scale=1.0),
     dict(name="single_edge", op="none", comp="dot", loss="logistic", B=1, nb=50, nu=4),
+    # per-edge weights (EdgeList.weight; losses.py:65-78, 104-113, 145-157)
+    dict(name="edge_weights_softmax", op="none", comp="dot", loss="softmax", B=130, nb=50, nu=20, edge_weight=True),
+    dict(name="edge_weights_ranking_cos", op="translation", comp="cos", loss="ranking", B=130, nb=50, nu=20, w_scale=1.0, edge_weight=True, steps=2),
+    dict(name="edge_weights_logistic_dyn", op="diagonal", comp="dot", loss="logistic", B=110, nb=50, nu=10, dyn=True, R=5, edge_weight=True),
 ]
 
 
@@ -178,7 +182,7 @@ def run_case(case):
     torch.set_num_threads(1)
     c = dict(D=16, N=211, N2=157, dyn=False, R=1, separate=False, id_range=None, steps=1, w_scale=0.3,
              disable_lhs=False, disable_rhs=False, n_rel_std=1, rel_idx=0, rel_weight=1.0, margin=0.1,
-             lr=0.1, relation_lr=0.05)
+             lr=0.1, relation_lr=0.05, edge_weight=False)
     c.update(case)
     D, N, B, dyn = c["D"], c["N"], c["B"], c["dyn"]
     ents = {"e": EntitySchema(num_partitions=1)}
@@ -299,9 +303,12 @@ def run_case(case):
                 rel = torch.randint(5, (B,)) * 3  # most rows of the table never touched
         else:
             rel = torch.tensor(c["rel_idx"])
+        weight = torch.rand(B) * 2.0 + 0.1 if c["edge_weight"] else None
         draw_seed = seed + 1000 + step
         torch.manual_seed(draw_seed)
-        stats = trainer.process_one_batch(model, EdgeList(EntityList.from_tensor(lhs), EntityList.from_tensor(rhs), rel))
+        stats = trainer.process_one_batch(model, EdgeList(EntityList.from_tensor(lhs), EntityList.from_tensor(rhs), rel, weight))
+        if weight is not None:
+            out[f"weight_{step}"] = weight.numpy()
         # replay the uniform-negative draws: lhs side first, then rhs side (model.py:802-821)
         P = min(c["nu"], B) if c["nb"] == 0 else min(c["nb"], B)
         C = (B - 1) // P + 1
@@ -361,6 +368,10 @@ def main():
     if args.only in (None, "steps"):
         for case in CASES:
             run_case(case)
+    elif args.only not in ("unit",):          # --only <substring>: the step cases whose name contains it
+        for case in CASES:
+            if args.only in case["name"]:
+                run_case(case)
 
 
 if __name__ == "__main__":

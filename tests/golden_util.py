@@ -48,6 +48,12 @@ def oracle_state(c, z, dtype=np.float64):
     return st
 
 
+def weight_of(c, z, step):
+    """Per-edge weights of the step (EdgeList.weight), or None."""
+    key = f"weight_{step}"
+    return z[key] if key in z.files else None
+
+
 def batch_of(c, z, step):
     rel = z[f"rel_{step}"]
     rel = rel if c["dyn"] else int(rel)

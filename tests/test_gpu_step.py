@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from golden_util import batch_of, load_step, oracle_config, oracle_state, step_fixture_names
+from golden_util import batch_of, load_step, oracle_config, oracle_state, step_fixture_names, weight_of
 from oracle import pbg_step as O
 
 pytestmark = pytest.mark.gpu
@@ -37,8 +37,9 @@ def test_step_matches_reference_fixture(name, precision):
     ocfg, ost = oracle_config(c), oracle_state(c, z)
     for step in range(c["steps"]):
         lhs, rhs, rel, ul, ur = batch_of(c, z, step)
-        ostats = O.train_batch(ocfg, ost, lhs, rhs, rel, ul, ur)
-        st = rig.trainer.process_one_batch(rig.model, rig.edges(lhs, rhs, rel), ul, ur)
+        wgt = weight_of(c, z, step)
+        ostats = O.train_batch(ocfg, ost, lhs, rhs, rel, ul, ur, wgt)
+        st = rig.trainer.process_one_batch(rig.model, rig.edges(lhs, rhs, rel, wgt), ul, ur)
         assert st.count == len(lhs)
         assert st.metrics["loss"] == pytest.approx(float(z[f"loss_{step}"]), rel=RTOL, abs=1e-3), "loss vs reference"
         assert st.metrics["loss"] == pytest.approx(ostats["loss"], rel=RTOL, abs=1e-3), "loss vs oracle"
@@ -67,7 +68,7 @@ def test_forward_scores_match_reference_fixture(name, precision):
     c, z = load_step(name)
     ocfg, ost = oracle_config(c), oracle_state(c, z)
     for step in range(c["steps"]):
-        O.train_batch(ocfg, ost, *batch_of(c, z, step))
+        O.train_batch(ocfg, ost, *batch_of(c, z, step), weight_of(c, z, step))
     rig = Rig.from_oracle_state(c, ost, precision=precision)
     rel = z["fw_rel"]
     sc = rig.model(rig.edges(z["fw_lhs"], z["fw_rhs"], rel),

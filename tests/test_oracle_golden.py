@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 from oracle import pbg_step as O
-from golden_util import GOLDEN, batch_of, load_step, oracle_config, oracle_state, step_fixture_names
+from golden_util import GOLDEN, batch_of, load_step, oracle_config, oracle_state, step_fixture_names, weight_of
 
 
 def _arr(d):
@@ -90,7 +90,7 @@ def test_composed_step_matches_reference(name):
     cfg = oracle_config(c)
     st = oracle_state(c, z)
     for step in range(c["steps"]):
-        stats = O.train_batch(cfg, st, *batch_of(c, z, step))
+        stats = O.train_batch(cfg, st, *batch_of(c, z, step), weight_of(c, z, step))
         assert stats["loss"] == pytest.approx(float(z[f"loss_{step}"]), rel=2e-5, abs=1e-4)
         # `neg > pos` is decided by fp32 rounding where a negative ties with its positive
         assert abs(stats["violators_lhs"] - int(z[f"violators_lhs_{step}"])) <= stats["ties_lhs"]
@@ -113,7 +113,7 @@ def test_forward_scores_match_reference(name):
     cfg = oracle_config(c)
     st = oracle_state(c, z)
     for step in range(c["steps"]):
-        O.train_batch(cfg, st, *batch_of(c, z, step))
+        O.train_batch(cfg, st, *batch_of(c, z, step), weight_of(c, z, step))
     rel = z["fw_rel"] if c["dyn"] else int(z["fw_rel"])
     ul = None if c["disable_lhs"] else z["fw_ul"]
     ur = None if c["disable_rhs"] else z["fw_ur"]
@@ -129,7 +129,7 @@ def test_wave_of_one_is_a_plain_batch():
     cfg = oracle_config(c)
     a, b = oracle_state(c, z), oracle_state(c, z)
     for step in range(3):
-        s1 = O.train_batch(cfg, a, *batch_of(c, z, step))
+        s1 = O.train_batch(cfg, a, *batch_of(c, z, step), weight_of(c, z, step))
         s2 = O.train_wave(cfg, b, [batch_of(c, z, step)])[0]
         assert s1 == s2
     assert np.array_equal(a.W_lhs, b.W_lhs) and np.array_equal(a.G_lhs, b.G_lhs)
@@ -152,7 +152,7 @@ def _torch_port_cases():
     out = []
     for n in step_fixture_names():
         c, _ = load_step(n)
-        if c["op"] in ("linear", "affine") or c["disable_lhs"] or c["disable_rhs"]:
+        if c["op"] in ("linear", "affine") or c["disable_lhs"] or c["disable_rhs"] or c.get("edge_weight"):
             continue
         out.append(n)
     return out
