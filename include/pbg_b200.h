@@ -93,6 +93,13 @@ typedef struct {
   float *lhs_op;    float *lhs_op_state;                   /* dynamic relations only, else NULL*/
   const float *relation_weights;                           /* HOST array [num_rels] (standard
                                                               mode) or [1] (dynamic); NULL = 1 */
+  /* config.global_emb (torchbiggraph/model.py:433-441, 486-492): one trained vector per entity
+   * type, added to every row of that type before the operator; standard relations only.
+   * [dim] vector and its AsyncAdagrad accumulator per side, NULL = none.  The rhs pointers equal
+   * the lhs pointers when both sides are of one entity type (one vector, the gradients of both
+   * sides add up). */
+  float *lhs_global;  float *lhs_global_state;
+  float *rhs_global;  float *rhs_global_state;
 } pbg_bucket;
 
 /* One batch of a call: edges [offset, offset + count) of the edge arrays, all of relation

@@ -196,6 +196,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   }
   oCoef[0] = take(nN * 4); oCoef[1] = take(nN * 4); oCoef[2] = take(nQ * 4); oCoef[3] = take(nQ * 4);
   size_t oRel = take(nblk * 8 * (size_t)cfg->dim * 4);
+  size_t oGlobPart = take(nblk * 2 * 8 * (size_t)cfg->dim * 4);
   const size_t opw = matrix_op ? (size_t)cfg->dim * cfg->dim + (cfg->op == PBG_OP_AFFINE ? cfg->dim : 0) : (size_t)cfg->dim;
   size_t oR1 = 0, oR2 = 0, oDA = 0;
   if (matrix_op) { oR1 = take(nN * c->Dp * 4); oR2 = take(nN * c->Dp * 4); oDA = take((size_t)c->kmax * opw * 4); }
@@ -237,6 +238,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     b.rankrow[p] = (int *)(c->ws + oRank[p]);
   }
   b.relpart = (float *)(c->ws + oRel);
+  b.globpart = (float *)(c->ws + oGlobPart);
   b.R1 = matrix_op ? (float *)(c->ws + oR1) : nullptr;
   b.R2 = matrix_op ? (float *)(c->ws + oR2) : nullptr;
   b.dA = matrix_op ? (float *)(c->ws + oDA) : nullptr;
@@ -350,6 +352,14 @@ static int bind_bucket(pbg_context *c, const pbg_bucket *bk, WaveDims &d, WaveBu
   d.key_invalid = emb_keys + ((d.dynamic && has_op) ? 2ull * cfg.num_rels : 0ull);
   w = c->bufs;
   w.ew = nullptr;
+  w.glob[0] = bk->lhs_global; w.glob[1] = bk->rhs_global;
+  w.gacc[0] = bk->lhs_global_state; w.gacc[1] = bk->rhs_global_state;
+  w.glob_shared = bk->lhs_global != nullptr && bk->lhs_global == bk->rhs_global;
+  if ((bk->lhs_global || bk->rhs_global) && cfg.dynamic_relations)
+    return fail(c, PBG_ERR_UNSUPPORTED, "global embeddings cannot be combined with dynamic relations (model.py:488-489)");
+  if (((uintptr_t)bk->lhs_global | (uintptr_t)bk->rhs_global) & 15) return fail(c, PBG_ERR_BAD_ARGUMENT, "global embeddings must be 16-byte aligned");
+  if (bk->lhs_emb == bk->rhs_emb && bk->lhs_global != bk->rhs_global)
+    return fail(c, PBG_ERR_BAD_ARGUMENT, "one table read through two different global embeddings");
   w.W[0] = bk->lhs_emb; w.G[0] = bk->lhs_state; w.W[1] = bk->rhs_emb; w.G[1] = bk->rhs_state;
   w.theta[0] = has_op ? bk->rhs_op : nullptr; w.acc[0] = has_op ? bk->rhs_op_state : nullptr;
   w.theta[1] = (has_op && d.dynamic) ? bk->lhs_op : nullptr; w.acc[1] = (has_op && d.dynamic) ? bk->lhs_op_state : nullptr;
@@ -428,6 +438,8 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
   if (!bk->lhs_state || !bk->rhs_state) return fail(c, PBG_ERR_BAD_ARGUMENT, "bucket without RowAdagrad state");
   if (d.op != PBG_OP_NONE && (!bk->rhs_op_state || (d.dynamic && !bk->lhs_op_state)))
     return fail(c, PBG_ERR_BAD_ARGUMENT, "operator tables without AsyncAdagrad state");
+  if ((bk->lhs_global && !bk->lhs_global_state) || (bk->rhs_global && !bk->rhs_global_state))
+    return fail(c, PBG_ERR_BAD_ARGUMENT, "global embeddings without AsyncAdagrad state");
   if (d.dynamic && d.op != PBG_OP_NONE && !rel) return fail(c, PBG_ERR_BAD_ARGUMENT, "dynamic relations need the rel array");
   for (int i = 0; i < num_batches; ++i) {
     const pbg_batch &b = batches[i];

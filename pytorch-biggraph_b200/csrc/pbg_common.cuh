@@ -90,6 +90,9 @@ struct WaveBufs {
   // out like N1; dA = per-batch gradient of the operator row [k][opw]
   float *R1, *R2, *dA;
   float *relpart;                    // standard mode: [k][Cm][D] partial operator gradients
+  float *glob[2], *gacc[2];          // global embedding of the lhs / rhs entity type + AsyncAdagrad accumulator, or null
+  int glob_shared;                   // both sides are of one entity type: glob[0] == glob[1], one step per batch
+  float *globpart;                   // [blk][side][warp][D] partial sums of the row gradients (global-embedding gradient)
   int *errflag;                      // device error word (bit 0: id out of range)
 };
 

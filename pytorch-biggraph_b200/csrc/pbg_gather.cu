@@ -19,6 +19,16 @@ __device__ __forceinline__ void load_row(float4 (&v)[VEC], const float *row, int
     v[c] = d < D ? ld4(row + d) : f4zero();
   }
 }
+// row += the global embedding of the row's entity type (config.global_emb; model.py:486-492), if any
+template <int VEC>
+__device__ __forceinline__ void add_global(float4 (&v)[VEC], const float *glob, int D, int lane) {
+  if (!glob) return;
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int d = c * 128 + lane * 4;
+    if (d < D) v[c] = v[c] + ld4(glob + d);
+  }
+}
 template <int VEC>
 __device__ __forceinline__ void store_row(float *row, const float4 (&v)[VEC], int D, int lane) {
 #pragma unroll
@@ -58,7 +68,7 @@ __device__ __forceinline__ void zero_row(float *row, int D, int lane) {
 // lane: the partner chunk is re-read from memory (an L1 hit).
 template <int VEC>
 __device__ __forceinline__ void apply_operator(float4 (&z)[VEC], const float4 (&x)[VEC], const float *xrow,
-                                               const float *theta, int op, int D, int lane) {
+                                               const float *theta, int op, int D, int lane, const float *glob = nullptr) {
   int h = D >> 1;
 #pragma unroll
   for (int c = 0; c < VEC; ++c) {
@@ -71,6 +81,7 @@ __device__ __forceinline__ void apply_operator(float4 (&z)[VEC], const float4 (&
     else {  // complex_diagonal: theta = [real | imag]
       int dp = d < h ? d + h : d - h;
       float4 xp = ld4(xrow + dp), tp = ld4(theta + dp);
+      if (glob) xp = xp + ld4(glob + dp);
       z[c] = d < h ? x[c] * t - xp * tp      // re = a_re p_re - a_im p_im
                    : xp * t + x[c] * tp;     // im = a_re p_im + a_im p_re
     }
@@ -161,6 +172,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     const float *th0 = (d.op != PBG_OP_NONE && w.theta[0]) ? w.theta[0] + (size_t)rl * D : nullptr;
     // lhs row without operator -> N0
     load_row<VEC>(x, xl, D, lane);
+    add_global<VEC>(x, w.glob[0], D, lane);
 #pragma unroll
     for (int c = 0; c < VEC; ++c) y0[c] = x[c];
     float a0 = prepare_row<VEC>(y0, d.cmp);
@@ -169,12 +181,14 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
       // linear / affine: the raw rhs row goes to R1; operator, prepare and the positive score
       // follow in the contraction and postop_kernel
       load_row<VEC>(x, xr, D, lane);
+      add_global<VEC>(x, w.glob[1], D, lane);
       store_row<VEC>(w.R1 + noff, x, D, lane);
       if (lane == 0) w.aux[ARR_N0][nrow] = a0;
     } else if (!d.dynamic) {
       // rhs row through the operator -> N1; one positive score shared by both problems
       load_row<VEC>(x, xr, D, lane);
-      apply_operator<VEC>(y1, x, xr, th0, d.op, D, lane);
+      add_global<VEC>(x, w.glob[1], D, lane);
+      apply_operator<VEC>(y1, x, xr, th0, d.op, D, lane, w.glob[1]);
       float a1 = prepare_row<VEC>(y1, d.cmp);
       put_row<VEC>(w.X[ARR_N1], lo(ARR_N1), noff, y1, D, lane);
       float s = positive_score<VEC>(y0, y1, d.cmp);
@@ -223,13 +237,14 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     }
     const float *xrow = w.W[side] + (size_t)id * D;
     load_row<VEC>(x, xrow, D, lane);
+    add_global<VEC>(x, w.glob[side], D, lane);
     if (side == 1 && d.matrix_op) { store_row<VEC>(w.R1 + noff, x, D, lane); continue; }
     const float *th = nullptr;
     if (side == 1 && !d.dynamic && d.op != PBG_OP_NONE && w.theta[0]) {
       int rl = wb.rel[bi.b];
       if (rl >= 0 && rl < d.num_rels) th = w.theta[0] + (size_t)rl * D;
     }
-    apply_operator<VEC>(z, x, xrow, th, d.op, D, lane);
+    apply_operator<VEC>(z, x, xrow, th, d.op, D, lane, w.glob[side]);
     float a = prepare_row<VEC>(z, d.cmp);
     put_row<VEC>(w.X[side], lo(side), noff, z, D, lane);
     if (lane == 0) w.aux[side][nrow] = a;
@@ -281,6 +296,8 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 16 ? 1 : VEC >= 8 ? 
     int dd = c * 128 + lane * 4;
     b[c] = (i1 >= 0 && dd < D) ? ld4(w.W[1] + (size_t)i1 * D + dd) : f4zero();
   }
+  if (i0 >= 0) add_global<VEC>(a, w.glob[0], D, lane);       // padding rows stay exact zeros
+  if (i1 >= 0) add_global<VEC>(b, w.glob[1], D, lane);
   store_row<VEC>(n0, a, D, lane);
   store_row<VEC>(n1, b, D, lane);
   float s = 0.f;

@@ -102,14 +102,21 @@ struct SlotGrad {
 // d(loss)/d(operator row) contributed by one slot whose operand went through the operator:
 // needs the gradient at the operator output (gz) and the raw embedding row x.
 template <int VEC>
-__device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC, -1, -1> &sg, const float *x, const float *xlo, float xscale, int dd) {
+__device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC, -1, -1> &sg, const float *x, const float *xlo, float xscale, int dd,
+                                                const float *xadd = nullptr) {
+  // xadd: global embedding added to the raw row before the operator (null: none)
   float4 v = sg.gz(dd);
   if (sg.op == PBG_OP_TRANSLATION) return v;
-  float4 xv = (xlo ? ld4(x + dd) + ld4(xlo + dd) : ld4(x + dd)) * xscale;
+  auto raw = [&](int e) {
+    float4 r = xlo ? ld4(x + e) + ld4(xlo + e) : ld4(x + e);
+    if (xadd) r = r + ld4(xadd + e);
+    return r * xscale;
+  };
+  float4 xv = raw(dd);
   if (sg.op == PBG_OP_DIAGONAL) return v * xv;
   int h = sg.D >> 1;
   int dp = dd < h ? dd + h : dd - h;
-  float4 vp = sg.gz(dp), xp = (xlo ? ld4(x + dp) + ld4(xlo + dp) : ld4(x + dp)) * xscale;
+  float4 vp = sg.gz(dp), xp = raw(dp);
   // d real = g_re a_re + g_im a_im ;  d imag = -g_re a_im + g_im a_re
   return dd < h ? v * xv + vp * xp : v * xp - vp * xv;
 }
@@ -564,7 +571,7 @@ __global__ void __launch_bounds__(32 * UPD_WARPS) relgrad_std_kernel(WaveDims d,
 #pragma unroll
       for (int c = 0; c < VEC; ++c) {
         int dd = c * 128 + lane * 4;
-        if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, nullptr, 1.0f, dd);
+        if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, nullptr, 1.0f, dd, w.glob[1]);
       }
     }
   }
@@ -663,6 +670,67 @@ __global__ void relupdate_matrix_kernel(WaveDims d, WaveBatches wb, WaveBufs w, 
   }
 }
 
+// Global embeddings (config.global_emb): the vector of an entity type is added to every row of that
+// type before the operator, so its gradient is the sum of the row gradients of all slots of its
+// side(s).  Stage 1: one CTA per chunk block, warp w sums the slots w, w + 8, ... of the lhs and of
+// the rhs operand array into globpart[blk][side][warp][D]; stage 2 adds the partial sums of a batch
+// in a fixed order and applies the dense AsyncAdagrad step, batch after batch
+// (torchbiggraph/async_adagrad.py:75-85; the vector is one of model.parameters(), train_cpu.py:215-230).
+template <int VEC>
+__global__ void __launch_bounds__(32 * UPD_WARPS) globgrad_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int lane = threadIdx.x & 31, wl = threadIdx.x >> 5;
+  int blk = blockIdx.x;
+  BlockInfo bi = block_info(d, wb, blk);
+  const int D = d.D;
+#pragma unroll 1
+  for (int side = 0; side < 2; ++side) {
+    float4 acc[VEC];
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) acc[c] = f4zero();
+    if (bi.n > 0 && w.glob[side]) {
+      for (int r = wl; r < d.Mm; r += UPD_WARPS) {
+        long long row = slot_row(d, wb, w, bi, side, r);
+        if (row < 0 || row >= d.n_rows[side]) continue;
+        SlotGrad<VEC> sg;
+        sg.init(d, wb, w, side == 0 ? ARR_N0 : ARR_N1, blk, r, bi.b, lane);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) {
+          int dd = c * 128 + lane * 4;
+          if (dd < D) acc[c] = acc[c] + sg.gx(dd);
+        }
+      }
+    }
+    float *out = w.globpart + (((size_t)blk * 2 + side) * UPD_WARPS + wl) * D;
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) {
+      int dd = c * 128 + lane * 4;
+      if (dd < D) st4(out + dd, acc[c]);
+    }
+  }
+}
+
+__global__ void globupdate_kernel(WaveDims d, WaveBatches wb, WaveBufs w, float lr) {
+  int dd = blockIdx.x * blockDim.x + threadIdx.x;
+  if (dd >= d.D) return;
+  for (int b = 0; b < d.k; ++b) {
+    if (wb.n[b] <= 0) continue;
+    float g[2] = {0.f, 0.f};
+    for (int side = 0; side < 2; ++side) {
+      if (!w.glob[side]) continue;
+      for (int c = 0; c < d.Cm; ++c)
+        for (int u = 0; u < UPD_WARPS; ++u)
+          g[side] += w.globpart[((((size_t)b * d.Cm + c) * 2 + side) * UPD_WARPS + u) * d.D + dd];
+    }
+    if (w.glob_shared) { g[0] += g[1]; g[1] = 0.f; }
+    for (int side = 0; side < (w.glob_shared ? 1 : 2); ++side) {
+      if (!w.glob[side]) continue;
+      float a = w.gacc[side][dd] + g[side] * g[side];
+      w.gacc[side][dd] = a;
+      w.glob[side][dd] -= lr * g[side] / (sqrtf(a) + PBG_ADAGRAD_EPS);
+    }
+  }
+}
+
 int launch_matrix_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, float lr, cudaStream_t st) {
   relupdate_matrix_kernel<<<(d.opw + 255) / 256, 256, 0, st>>>(d, wb, w, lr);
   return 1;
@@ -689,6 +757,12 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   bool has_op = d.op != PBG_OP_NONE && w.theta[0] != nullptr;
   if (has_op && !d.dynamic && !d.matrix_op) {
     relgrad_std_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, 0, st>>>(d, wb, w);
+    ++launches;
+  }
+  // gradient sums of the global embeddings: before any operator parameter of this wave is stepped
+  const bool has_glob = w.glob[0] || w.glob[1];
+  if (has_glob) {
+    globgrad_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, 0, st>>>(d, wb, w);
     ++launches;
   }
   if (!attr_done[0]) {
@@ -731,6 +805,10 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
       relupdate_std_kernel<<<(d.D + 127) / 128, 128, 0, st>>>(d, wb, w, rel_lr);
       ++launches;
     }
+  }
+  if (has_glob) {
+    globupdate_kernel<<<(d.D + 127) / 128, 128, 0, st>>>(d, wb, w, rel_lr);
+    ++launches;
   }
   return launches;
 }

@@ -30,7 +30,9 @@ class PbgBucket(C.Structure):
                 ("rhs_emb", C.c_void_p), ("rhs_state", C.c_void_p), ("rhs_rows", C.c_int64),
                 ("rhs_op", C.c_void_p), ("rhs_op_state", C.c_void_p),
                 ("lhs_op", C.c_void_p), ("lhs_op_state", C.c_void_p),
-                ("relation_weights", C.POINTER(C.c_float))]
+                ("relation_weights", C.POINTER(C.c_float)),
+                ("lhs_global", C.c_void_p), ("lhs_global_state", C.c_void_p),
+                ("rhs_global", C.c_void_p), ("rhs_global_state", C.c_void_p)]
 
 
 class PbgBatch(C.Structure):

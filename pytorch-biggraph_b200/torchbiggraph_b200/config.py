@@ -3,8 +3,8 @@ step reads, with the same key names and meanings.  `from_reference` accepts the 
 ConfigSchema object (duck-typed) so that a stock config file drives this path unchanged.
 
 Keys with no device code are refused where the trainer is built (NotImplementedError), never
-silently ignored: global_emb, bias, max_norm, regularization_coef, half_precision, featurized
-entities, all_negs relations, per-entity dimensions."""
+silently ignored: bias, max_norm, regularization_coef, half_precision, featurized entities,
+all_negs relations, per-entity dimensions."""
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -43,9 +43,11 @@ class ConfigSchema:
     disable_rhs_negs: bool = False
     dynamic_relations: bool = False
     init_scale: float = 1e-3
-    # keys the reference has and this path refuses when set (the reference's default for
-    # global_emb is True; it has to be switched off explicitly to use this path)
+    # one trained vector per entity type added to every embedding of the type (model.py:433-441,
+    # 486-492).  The reference's default is True; here a config built by hand starts without,
+    # from_reference() copies whatever the reference config says.
     global_emb: bool = False
+    # keys the reference has and this path refuses when set
     bias: bool = False
     max_norm: Optional[float] = None
     regularization_coef: float = 0.0
@@ -72,8 +74,8 @@ class ConfigSchema:
 
     def check_supported(self) -> None:
         bad = []
-        if self.global_emb:
-            bad.append("global_emb=True")
+        if self.global_emb and self.dynamic_relations:
+            raise RuntimeError("Cannot have global embs with dynamic rels")          # model.py:488-489
         if self.bias:
             bad.append("bias=True")
         if self.max_norm is not None:

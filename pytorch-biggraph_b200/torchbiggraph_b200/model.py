@@ -77,11 +77,24 @@ class MultiRelationEmbedder:
                 self.lhs_operators.append(None)
         self.lhs_embs: Dict[str, torch.Tensor] = {}
         self.rhs_embs: Dict[str, torch.Tensor] = {}
+        # config.global_emb: one [dimension] vector per entity type, initialised to zero and trained
+        # by the model optimizer (model.py:433-441)
+        self.global_embs: Optional[Dict[str, torch.Tensor]] = None
+        if config.global_emb:
+            self.global_embs = {self.EMB_PREFIX + e: torch.zeros(D, device=self.device) for e in config.entities}
         self._scorer = None
 
     # ---- parameters other than embeddings: what model_optimizer steps (train_cpu.py:468) ----
     def parameters(self):
-        return [t for t in (self.rhs_op_table, self.lhs_op_table) if t is not None]
+        glob = [] if self.global_embs is None else list(self.global_embs.values())
+        return [t for t in (self.rhs_op_table, self.lhs_op_table) if t is not None] + glob
+
+    def globals_for(self, relation_idx: int):
+        """(lhs, rhs) global embedding of the relation's entity types, or (None, None)."""
+        if self.global_embs is None:
+            return None, None
+        rel = self.relations[relation_idx]
+        return self.global_embs[self.EMB_PREFIX + rel.lhs], self.global_embs[self.EMB_PREFIX + rel.rhs]
 
     def set_embeddings(self, entity: str, side: Side, weights: torch.Tensor) -> None:
         if weights.dim() != 2 or weights.shape[1] != self.config.dimension or weights.dtype != torch.float32:

@@ -78,13 +78,18 @@ class _Native:
         b.lhs_emb, b.lhs_rows = wl.data_ptr(), wl.shape[0]
         b.rhs_emb, b.rhs_rows = wr.data_ptr(), wr.shape[0]
         if states is not None:
-            gl, gr, al, ar = states
+            gl, gr, al, ar = states[:4]
             b.lhs_state, b.rhs_state = gl.data_ptr(), gr.data_ptr()
             b.rhs_op_state = None if ar is None else ar.data_ptr()
             b.lhs_op_state = None if al is None else al.data_ptr()
         b.rhs_op = None if model.rhs_op_table is None else model.rhs_op_table.data_ptr()
         b.lhs_op = None if model.lhs_op_table is None else model.lhs_op_table.data_ptr()
         b.relation_weights = weights_arr
+        gl_, gr_ = model.globals_for(relation_idx)
+        if gl_ is not None:
+            b.lhs_global, b.rhs_global = gl_.data_ptr(), gr_.data_ptr()
+            if states is not None and len(states) > 4:
+                b.lhs_global_state, b.rhs_global_state = states[4].data_ptr(), states[5].data_ptr()
         return b
 
     def score(self, model, edges: EdgeList, ul, ur, seed) -> Scores:
@@ -212,6 +217,11 @@ class B200Trainer(AbstractBatchProcessor):
                     raise NotImplementedError("batches of one call must read the same pair of tables")
         al, ar = self._op_states(model)
         states = (self._state_for(wl), self._state_for(wr), al, ar)
+        gl_, gr_ = model.globals_for(relation_idx)
+        if gl_ is not None:
+            if not isinstance(self.model_optimizer, AsyncAdagrad):
+                raise RuntimeError("the model has global embeddings but model_optimizer is not an AsyncAdagrad over them")
+            states = states + (self.model_optimizer.sum_for(gl_), self.model_optimizer.sum_for(gr_))
         nw = len(self.relation_weights)
         warr = (C.c_float * nw)(*self.relation_weights)
         bucket = nat.bucket(model, relation_idx, states, warr)

@@ -164,6 +164,11 @@ CASES = [
     # per-edge weights (EdgeList.weight; losses.py:65-78, 104-113, 145-157)
     dict(name="edge_weights_softmax", op="none", comp="dot", loss="softmax", B=130, nb=50, nu=20, edge_weight=True),
     dict(name="edge_weights_ranking_cos", op="translation", comp="cos", loss="ranking", B=130, nb=50, nu=20, w_scale=1.0, edge_weight=True, steps=2),
+    # config.global_emb (the reference's default): one trained vector per entity type added to every row
+    dict(name="global_emb_one_type", op="translation", comp="dot", loss="softmax", B=130, nb=50, nu=20, global_emb=True),
+    dict(name="global_emb_two_types", op="diagonal", comp="cos", loss="ranking", B=130, nb=50, nu=20, w_scale=1.0, separate=True, global_emb=True),
+    dict(name="global_emb_sequence", op="none", comp="dot", loss="logistic", B=110, nb=50, nu=10, steps=2, global_emb=True),
+    dict(name="global_emb_complex_l2", op="complex_diagonal", comp="l2", loss="softmax", B=90, nb=40, nu=10, global_emb=True),
     dict(name="edge_weights_logistic_dyn", op="diagonal", comp="dot", loss="logistic", B=110, nb=50, nu=10, dyn=True, R=5, edge_weight=True),
 ]
 
@@ -182,7 +187,7 @@ def run_case(case):
     torch.set_num_threads(1)
     c = dict(D=16, N=211, N2=157, dyn=False, R=1, separate=False, id_range=None, steps=1, w_scale=0.3,
              disable_lhs=False, disable_rhs=False, n_rel_std=1, rel_idx=0, rel_weight=1.0, margin=0.1,
-             lr=0.1, relation_lr=0.05, edge_weight=False)
+             lr=0.1, relation_lr=0.05, edge_weight=False, global_emb=False)
     c.update(case)
     D, N, B, dyn = c["D"], c["N"], c["B"], c["dyn"]
     ents = {"e": EntitySchema(num_partitions=1)}
@@ -198,7 +203,7 @@ def run_case(case):
     cfg_batch = max(B, 1) if c["nb"] == 0 else ((B - 1) // c["nb"] + 1) * c["nb"]
     cfg = ConfigSchema(entities=ents, relations=rels, dimension=D, entity_path="x", edge_paths=["y"],
                        checkpoint_path="z", comparator=c["comp"], loss_fn=c["loss"], margin=c["margin"],
-                       global_emb=False, batch_size=cfg_batch, num_batch_negs=c["nb"], num_uniform_negs=c["nu"],
+                       global_emb=c["global_emb"], batch_size=cfg_batch, num_batch_negs=c["nb"], num_uniform_negs=c["nu"],
                        lr=c["lr"], relation_lr=c["relation_lr"], dynamic_relations=dyn,
                        disable_lhs_negs=c["disable_lhs"], disable_rhs_negs=c["disable_rhs"])
     if dyn:
@@ -292,6 +297,17 @@ def run_case(case):
     for side in ("rhs", "lhs"):
         if t0[side] is not None:
             out[f"theta_{side}0"] = t0[side]
+
+    def glob_tables():
+        """{entity type: (vector, AsyncAdagrad accumulator)} of the model's global embeddings."""
+        if model.global_embs is None:
+            return {}
+        opt = trainer.model_optimizer
+        return {k[len(model.EMB_PREFIX):]: (p.detach().numpy().copy(), opt.state[p]["sum"].numpy().copy())
+                for k, p in model.global_embs.items()}
+
+    for ent, (g, _) in glob_tables().items():
+        out[f"glob_{ent}0"] = g
     hi_l = c["id_range"] or N
     hi_r = c["id_range"] or N2
     for step in range(c["steps"]):
@@ -331,6 +347,9 @@ def run_case(case):
         if c["separate"]:
             out[f"W_rhs_after_{step}"] = emb_r.detach().numpy().copy()
             out[f"G_rhs_after_{step}"] = opt_r.state[emb_r]["sum"].numpy().copy()
+        for ent, (g, a) in glob_tables().items():
+            out[f"glob_{ent}_after_{step}"] = g
+            out[f"gacc_{ent}_after_{step}"] = a
         t1, a1 = op_tables(), acc_tables()
         for side in ("rhs", "lhs"):
             if t1[side] is not None:

@@ -45,6 +45,14 @@ def oracle_state(c, z, dtype=np.float64):
     if "theta_lhs0" in z and c["dyn"]:
         st.theta_lhs = z["theta_lhs0"].astype(dtype)
         st.acc_lhs = np.zeros_like(st.theta_lhs)
+    if "glob_e0" in z.files:                       # global embeddings: lhs is entity type e, rhs is e or f
+        st.glob_lhs = z["glob_e0"].astype(dtype)
+        st.gacc_lhs = np.zeros_like(st.glob_lhs)
+        if c["separate"]:
+            st.glob_rhs = z["glob_f0"].astype(dtype)
+            st.gacc_rhs = np.zeros_like(st.glob_rhs)
+        else:
+            st.glob_rhs, st.gacc_rhs = st.glob_lhs, st.gacc_lhs
     return st
 
 

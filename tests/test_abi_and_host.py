@@ -111,12 +111,18 @@ def _cfg(**kw):
     return T.ConfigSchema(**base)
 
 
-@pytest.mark.parametrize("kw", [dict(global_emb=True), dict(bias=True), dict(max_norm=1.0), dict(regularization_coef=1e-3),
+@pytest.mark.parametrize("kw", [dict(bias=True), dict(max_norm=1.0), dict(regularization_coef=1e-3),
                                 dict(half_precision=True), dict(entities={"e": T.EntitySchema(featurized=True)}),
                                 dict(relations=[T.RelationSchema("r", "e", "e", all_negs=True)])])
 def test_unsupported_config_keys_raise(kw):
     with pytest.raises(NotImplementedError):
         _cfg(**kw).check_supported()
+
+
+def test_global_embeddings_need_standard_relations():
+    _cfg(global_emb=True).check_supported()
+    with pytest.raises(RuntimeError, match="global embs"):       # model.py:488-489
+        _cfg(global_emb=True, dynamic_relations=True, num_dynamic_rels=3).check_supported()
 
 
 def test_batch_size_must_be_multiple_of_batch_negs():

@@ -59,6 +59,12 @@ def test_step_matches_reference_fixture(name, precision):
                 # terms carries an absolute error set by the largest terms, hence the scaled atol
                 want_acc = z[f"acc_{side}_after_{step}"]
                 _close(rig.acc(side), want_acc, atol=2e-6 * float(np.abs(want_acc).max()), what=f"acc_{side} vs reference")
+        for ent in ("e", "f"):
+            key = f"glob_{ent}_after_{step}"
+            if key in z.files:
+                _close(rig.glob(ent), z[key], what=f"global embedding {ent} vs reference")
+                want_acc = z[f"gacc_{ent}_after_{step}"]
+                _close(rig.gacc(ent), want_acc, atol=2e-6 * float(np.abs(want_acc).max()), what=f"global accumulator {ent} vs reference")
 
 
 @pytest.mark.parametrize("precision", PRECISIONS)
@@ -191,6 +197,32 @@ def test_wave_of_eight_matches_oracle_with_hub_rows(precision):
     rig.trainer.train_batches(rig.model, lhs, rhs, None, [(i * 200, 200, 0) for i in range(8)], ul, ur)
     _close(rig.W_lhs.cpu().numpy(), ost.W_lhs, atol=1e-6, what="W")
     _close(rig.G("lhs"), ost.G_lhs, atol=1e-8, what="G")
+    _close(rig.theta("rhs"), ost.theta_rhs, atol=1e-6, what="theta")
+
+
+@pytest.mark.parametrize("precision", PRECISIONS)
+def test_wave_with_global_embeddings_matches_oracle(precision):
+    """Three batches in flight with config.global_emb: all of them read the vector as the wave found
+    it, its three AsyncAdagrad steps follow in batch order (one entity type on both sides: one
+    vector, the gradients of both sides add up)."""
+    from b200_util import Rig
+    c, ocfg, ost, batches = _random_case(21, 64, 500, 150, 50, 30, "diagonal", "dot", "softmax", nbatches=3, zipf=True)
+    c["global_emb"] = True
+    rng = np.random.default_rng(5)
+    ost.glob_lhs = rng.standard_normal(64) * 0.2
+    ost.gacc_lhs = rng.random(64) * 0.1
+    ost.glob_rhs, ost.gacc_rhs = ost.glob_lhs, ost.gacc_lhs
+    rig = Rig.from_oracle_state(c, ost, k=3, precision=precision)
+    O.train_wave(ocfg, ost, batches)
+    nat = rig.trainer._context(rig.model, 150)
+    lhs = torch.tensor(np.concatenate([b[0] for b in batches])).cuda()
+    rhs = torch.tensor(np.concatenate([b[1] for b in batches])).cuda()
+    ul = torch.stack([nat._uniform(b[3], "cuda") for b in batches]).contiguous()
+    ur = torch.stack([nat._uniform(b[4], "cuda") for b in batches]).contiguous()
+    rig.trainer.train_batches(rig.model, lhs, rhs, None, [(i * 150, 150, 0) for i in range(3)], ul, ur)
+    _close(rig.W_lhs.cpu().numpy(), ost.W_lhs, atol=1e-6, what="W")
+    _close(rig.glob("e"), ost.glob_lhs, atol=1e-6, what="global embedding")
+    _close(rig.gacc("e"), ost.gacc_lhs, atol=2e-6 * float(np.abs(ost.gacc_lhs).max()), what="global accumulator")
     _close(rig.theta("rhs"), ost.theta_rhs, atol=1e-6, what="theta")
 
 

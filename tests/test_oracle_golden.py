@@ -104,7 +104,13 @@ def test_composed_step_matches_reference(name):
             key = f"theta_{side}_after_{step}"
             if key in z and getattr(st, f"theta_{side}") is not None:
                 np.testing.assert_allclose(getattr(st, f"theta_{side}"), z[key], rtol=2e-5, atol=2e-6)
-                np.testing.assert_allclose(getattr(st, f"acc_{side}"), z[f"acc_{side}_after_{step}"], rtol=5e-5, atol=1e-7)
+                # accumulators are squares of fp32 sums with cancellation in the reference: a little looser
+                np.testing.assert_allclose(getattr(st, f"acc_{side}"), z[f"acc_{side}_after_{step}"], rtol=1e-4, atol=1e-7)
+        for ent, side in (("e", "lhs"), ("f", "rhs")):
+            key = f"glob_{ent}_after_{step}"
+            if key in z.files:
+                np.testing.assert_allclose(getattr(st, f"glob_{side}"), z[key], rtol=2e-5, atol=2e-6)
+                np.testing.assert_allclose(getattr(st, f"gacc_{side}"), z[f"gacc_{ent}_after_{step}"], rtol=1e-4, atol=1e-7)
 
 
 @pytest.mark.parametrize("name", step_fixture_names())
@@ -152,7 +158,7 @@ def _torch_port_cases():
     out = []
     for n in step_fixture_names():
         c, _ = load_step(n)
-        if c["op"] in ("linear", "affine") or c["disable_lhs"] or c["disable_rhs"] or c.get("edge_weight"):
+        if c["op"] in ("linear", "affine") or c["disable_lhs"] or c["disable_rhs"] or c.get("edge_weight") or c.get("global_emb"):
             continue
         out.append(n)
     return out
