@@ -92,6 +92,8 @@ def test_composed_step_matches_reference(name):
     for step in range(c["steps"]):
         stats = O.train_batch(cfg, st, *batch_of(c, z, step), weight_of(c, z, step))
         assert stats["loss"] == pytest.approx(float(z[f"loss_{step}"]), rel=2e-5, abs=1e-4)
+        if f"reg_{step}" in z.files:
+            assert stats["reg"] == pytest.approx(float(z[f"reg_{step}"]), rel=2e-5, abs=1e-6)
         # `neg > pos` is decided by fp32 rounding where a negative ties with its positive
         assert abs(stats["violators_lhs"] - int(z[f"violators_lhs_{step}"])) <= stats["ties_lhs"]
         assert abs(stats["violators_rhs"] - int(z[f"violators_rhs_{step}"])) <= stats["ties_rhs"]
@@ -158,7 +160,7 @@ def _torch_port_cases():
     out = []
     for n in step_fixture_names():
         c, _ = load_step(n)
-        if c["op"] in ("linear", "affine") or c["disable_lhs"] or c["disable_rhs"] or c.get("edge_weight") or c.get("global_emb"):
+        if c["op"] in ("linear", "affine") or c["disable_lhs"] or c["disable_rhs"] or c.get("edge_weight") or c.get("global_emb") or c.get("reg_coef"):
             continue
         out.append(n)
     return out
