@@ -83,6 +83,8 @@ typedef struct {
   float lr;                   /* RowAdagrad learning rate                                      */
   float relation_lr;          /* AsyncAdagrad learning rate of operator parameters
                                  (train_cpu.py:224-228: relation_lr if set, else lr)           */
+  float regularization_coef;  /* N3 regularizer weight (torchbiggraph/regularizers.py:51-97),
+                                 0 = off; not with linear / affine operators                   */
 } pbg_config;
 
 /* One resident (lhs partition, rhs partition) bucket.  Pointers are device memory. */

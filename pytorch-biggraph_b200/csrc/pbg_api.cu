@@ -127,6 +127,8 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   if (matrix_op && cfg->dynamic_relations)
     return fail(c, PBG_ERR_UNSUPPORTED, "operator %s with dynamic relations (one matrix per edge) has no device code",
                 cfg->op == PBG_OP_LINEAR ? "linear" : "affine");
+  if (matrix_op && cfg->regularization_coef != 0.f)
+    return fail(c, PBG_ERR_UNSUPPORTED, "Regularizer not implemented for this operator");   /* operators.py:39-40 */
   if (cfg->op == PBG_OP_COMPLEX_DIAGONAL && cfg->dim % 8 != 0)
     return fail(c, PBG_ERR_UNSUPPORTED, "complex_diagonal needs a dimension that is a multiple of 8 (got %d)", cfg->dim);
   if (cfg->comparator < PBG_CMP_DOT || cfg->comparator > PBG_CMP_SQUARED_L2) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown comparator %d", cfg->comparator);
@@ -167,6 +169,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   // ---- carve the workspace ------------------------------------------------------------------
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
+  size_t oReg = 0;
   size_t oX[4], oAux[4], oG[4], oS[2], oSpos[2], oCoef[4], oLoss[2], oViol[2], oRank[2], oXL[4] = {0, 0, 0, 0}, oSL[2] = {0, 0};
   const bool split = false;   // TF32X3 splits operands inside the contraction kernel: no low-part arrays
   oX[0] = take(nN * c->Dp * 4); oX[1] = take(nN * c->Dp * 4);
@@ -192,6 +195,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   }
   for (int p = 0; p < 2; ++p) {
     oS[p] = take(nQ * c->Ms * 4); oSpos[p] = take(nQ * 4); oLoss[p] = take(nQ * 4); oViol[p] = take(nQ * 4);
+    if (p == 0) oReg = take(nQ * 4);
     oRank[p] = take(nQ * 4);
   }
   oCoef[0] = take(nN * 4); oCoef[1] = take(nN * 4); oCoef[2] = take(nQ * 4); oCoef[3] = take(nQ * 4);
@@ -206,7 +210,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     oV[s][0] = take((size_t)nocc * 4); oV[s][1] = take((size_t)nocc * 4);
     oH[s] = take(pbg_sort_hist_entries((int)nocc) * 4);
   }
-  size_t oSum = take(4 * sizeof(double)), oErr = take(256), oEval = take(8 * sizeof(double));
+  size_t oSum = take(8 * sizeof(double)), oErr = take(256), oEval = take(8 * sizeof(double));
   size_t oPsum = take((size_t)nocc * c->Dp * 4), oHub = take(((size_t)nocc / 8 + 64) * 8), oHubCnt = take(256);
   c->ws_bytes = off;
   CU(c, cudaMalloc(&c->ws, c->ws_bytes));
@@ -234,6 +238,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     b.S[p] = (float *)(c->ws + oS[p]);
     b.spos[p] = (float *)(c->ws + oSpos[p]);
     b.lossrow[p] = (float *)(c->ws + oLoss[p]);
+    if (p == 0) b.regrow = (float *)(c->ws + oReg);
     b.violrow[p] = (int *)(c->ws + oViol[p]);
     b.rankrow[p] = (int *)(c->ws + oRank[p]);
   }
@@ -339,7 +344,7 @@ static int bind_bucket(pbg_context *c, const pbg_bucket *bk, WaveDims &d, WaveBu
   d.op = cfg.op; d.cmp = cfg.comparator; d.loss = cfg.loss; d.dynamic = cfg.dynamic_relations != 0;
   d.batch_negs = cfg.num_batch_negs > 0;
   d.neg_enabled[0] = !cfg.disable_lhs_negs; d.neg_enabled[1] = !cfg.disable_rhs_negs;
-  d.num_batch_negs = cfg.num_batch_negs; d.spb = c->spb; d.margin = cfg.margin;
+  d.num_batch_negs = cfg.num_batch_negs; d.spb = c->spb; d.margin = cfg.margin; d.reg_coef = cfg.regularization_coef;
   d.split = 0;
   d.matrix_op = cfg.op == PBG_OP_LINEAR || cfg.op == PBG_OP_AFFINE;
   d.opw = d.matrix_op ? cfg.dim * cfg.dim + (cfg.op == PBG_OP_AFFINE ? cfg.dim : 0) : cfg.dim;
@@ -394,7 +399,7 @@ static int run_forward(pbg_context *c, const WaveDims &d, const WaveBatches &wb,
 // gather -> score -> loss -> gradient products of the chunk blocks [d.blk0, d.blk0 + d.nblk) on `st`
 static void run_part(pbg_context *c, const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
   run_forward(c, d, wb, w, st);
-  { ClassTimer t(c, 3, st); t.done(launch_loss(d, wb, w, st)); }
+  { ClassTimer t(c, 3, st); t.done(launch_loss(d, wb, w, st) + (d.reg_coef != 0.f ? launch_reg_value(d, wb, w, st) : 0)); }
   ClassTimer t(c, 4, st);
   int n = c->cfg.precision == PBG_PREC_FP32 ? launch_grad_simt(d, wb, w, st) : launch_grad_tc(d, wb, w, c->tcplan, st);
   if (d.matrix_op) n += launch_gz_rows(d, wb, w, st) + launch_matrix_backward(d, wb, w, st);   // back through A
@@ -594,11 +599,11 @@ extern "C" int pbg_set_edge_weights(pbg_context *c, const float *weights_dev) {
 extern "C" int pbg_read_stats(pbg_context *c, pbg_batch_stats *out) {
   if (!c || !out) return PBG_ERR_BAD_ARGUMENT;
   CU(c, cudaSetDevice(c->device));
-  double s[4];
+  double s[5];
   CU(c, cudaMemcpyAsync(s, c->sum_dev, sizeof s, cudaMemcpyDeviceToHost, c->stream));
   CU(c, cudaMemsetAsync(c->sum_dev, 0, sizeof s, c->stream));
   int rc = check_errflag(c);
-  out->loss = (float)s[0]; out->reg = 0.f;
+  out->loss = (float)s[0]; out->reg = (float)s[4];
   out->violators_lhs = (int64_t)(s[1] + 0.5); out->violators_rhs = (int64_t)(s[2] + 0.5); out->count = (int64_t)(s[3] + 0.5);
   return rc;
 }

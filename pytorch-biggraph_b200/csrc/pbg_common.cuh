@@ -45,6 +45,7 @@ struct WaveDims {
   int spb;              // occurrence slots per batch (see occ_decode)
   int nocc;             // k * spb
   float margin;
+  float reg_coef;       // N3 regularizer weight, 0 = off
   long long n_rows[2];  // rows of the lhs / rhs table
   int shared_table;     // lhs and rhs read the same table
   int num_rels;
@@ -78,6 +79,7 @@ struct WaveBufs {
   float *spos[2];                    // positive scores [nblk][Pm]
   float *coef[4];                    // l2: colsum(T0), colsum(T1), rowsum(T0), rowsum(T1)
   float *lossrow[2];                 // per positive row: weighted loss term
+  float *regrow;                     // per positive row: its share of the N3 regularizer (reg_coef != 0)
   int *violrow[2];                   // per positive row: #(neg > pos)
   int *rankrow[2];                   // evaluation: per positive row, 1 + #(neg >= pos)
   const long long *lhs, *rhs, *rel;  // edge arrays
@@ -167,6 +169,27 @@ __device__ __forceinline__ Occ occ_decode(const WaveDims &d, int o) {
   return q;
 }
 
+// N3 regularizer pieces at elements [dd, dd + 4) of a row y: the term is sum m^3 with m = |y_d|, or for
+// complex_diagonal the modulus of the pair (y_d, y_{d +- D/2}) counted once per pair
+// (torchbiggraph/operators.py:42-43, 151-157).  n3_grad4: d(sum m^3)/dy = 3 m y.
+__device__ __forceinline__ float4 n3_grad4(const float *y, int dd, int D, bool cplx) {
+  float4 v = *reinterpret_cast<const float4 *>(y + dd);
+  if (!cplx) return make_float4(3.f * fabsf(v.x) * v.x, 3.f * fabsf(v.y) * v.y, 3.f * fabsf(v.z) * v.z, 3.f * fabsf(v.w) * v.w);
+  int h = D >> 1;
+  float4 p = *reinterpret_cast<const float4 *>(y + (dd < h ? dd + h : dd - h));
+  return make_float4(3.f * sqrtf(v.x * v.x + p.x * p.x) * v.x, 3.f * sqrtf(v.y * v.y + p.y * p.y) * v.y,
+                     3.f * sqrtf(v.z * v.z + p.z * p.z) * v.z, 3.f * sqrtf(v.w * v.w + p.w * p.w) * v.w);
+}
+__device__ __forceinline__ float n3_val4(const float *y, int dd, int D, bool cplx) {
+  float4 v = *reinterpret_cast<const float4 *>(y + dd);
+  if (!cplx) { float a = fabsf(v.x), b = fabsf(v.y), c = fabsf(v.z), e = fabsf(v.w); return a * a * a + b * b * b + c * c * c + e * e * e; }
+  int h = D >> 1;
+  if (dd >= h) return 0.f;                                  // the pair is counted at its real part
+  float4 p = *reinterpret_cast<const float4 *>(y + dd + h);
+  float a = sqrtf(v.x * v.x + p.x * p.x), b = sqrtf(v.y * v.y + p.y * p.y), c = sqrtf(v.z * v.z + p.z * p.z), e = sqrtf(v.w * v.w + p.w * p.w);
+  return a * a * a + b * b * b + c * c * c + e * e * e;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -239,6 +262,7 @@ int launch_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                   const unsigned long long *keys, const unsigned int *vals, float lr, float rel_lr,
                   float *psum, long long *hublist, int *hubcnt, cudaStream_t st);
 int launch_eval(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, double *out8_dev, cudaStream_t st);
+int launch_reg_value(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
 int launch_stats(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                  pbg_batch_stats *per_batch_dev, double *sum_dev, cudaStream_t st);
 int launch_row_adagrad_sorted(float *emb, float *state, int dim, const unsigned long long *keys,

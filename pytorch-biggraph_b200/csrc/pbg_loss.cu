@@ -335,14 +335,65 @@ int launch_loss(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cud
   return 1;
 }
 
+// N3 regularizer value (torchbiggraph/regularizers.py:51-97), one warp per positive row of a chunk
+// block: coef * sum m^3 over the adjusted rows of the edge -- standard relations: the prepared lhs
+// row and the prepared op(rhs) row; dynamic relations: those of both passes (N0, Q0, N1, Q1) -- plus
+// the operator parameters: per edge with dynamic relations; once per CHUNK with standard relations
+// (sum(params^3) * len(src_pos) where src_pos is the [chunks, P, D] view, regularizers.py:88-92),
+// which row 0 of the block carries.  Runs after the gather, on the snapshot the wave reads.
+__global__ void __launch_bounds__(32 * LOSS_WARPS) reg_value_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * LOSS_WARPS + (threadIdx.x >> 5);
+  if (item >= (long long)d.nblk * d.Pm) return;
+  int lb = (int)(item / d.Pm), i = (int)(item - (long long)lb * d.Pm);
+  const int blk = d.blk0 + lb;
+  BlockInfo bi = block_info(d, wb, blk);
+  if (bi.n == 0) return;
+  size_t prow = (size_t)blk * d.Pm + i;
+  float tot = 0.f;
+  if (i < bi.n) {
+    const bool cplx = d.op == PBG_OP_COMPLEX_DIAGONAL;
+    const int D = d.D;
+    const float *rows[6];
+    int nr = 0;
+    rows[nr++] = w.X[ARR_N0] + ((size_t)blk * w.xrows[ARR_N0] + i) * d.Dp;
+    rows[nr++] = w.X[ARR_N1] + ((size_t)blk * w.xrows[ARR_N1] + i) * d.Dp;
+    if (d.dynamic) {
+      rows[nr++] = w.X[ARR_Q0] + ((size_t)blk * w.xrows[ARR_Q0] + i) * d.Dp;
+      rows[nr++] = w.X[ARR_Q1] + ((size_t)blk * w.xrows[ARR_Q1] + i) * d.Dp;
+    }
+    if (d.op != PBG_OP_NONE) {
+      if (d.dynamic) {
+        long long rl = w.rel[bi.e0 + i];
+        if (rl >= 0 && rl < d.num_rels) {
+          if (w.theta[0]) rows[nr++] = w.theta[0] + (size_t)rl * D;
+          if (w.theta[1]) rows[nr++] = w.theta[1] + (size_t)rl * D;
+        }
+      } else if (i == 0 && w.theta[0]) {
+        rows[nr++] = w.theta[0] + (size_t)wb.rel[bi.b] * D;
+      }
+    }
+    for (int q = 0; q < nr; ++q)
+      for (int dd = lane * 4; dd < D; dd += 128) tot += n3_val4(rows[q], dd, D, cplx);
+    tot = warp_sum(tot) * d.reg_coef;
+  }
+  if (lane == 0) w.regrow[prow] = tot;
+}
+
+int launch_reg_value(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
+  long long items = (long long)d.nblk * d.Pm;
+  reg_value_kernel<<<(int)((items + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+  return 1;
+}
+
 // Per-batch Stats (train_cpu.py:95-101): one CTA per batch of the wave sums its rows in a fixed
 // order; the running totals of the call live in sum_dev (loss, violators_lhs, violators_rhs, count).
 __global__ void __launch_bounds__(256) stats_kernel(WaveDims d, WaveBatches wb, WaveBufs w,
                                                     pbg_batch_stats *per_batch, double *sum) {
-  __shared__ double sl[256];
+  __shared__ double sl[256], sr[256];
   __shared__ long long sv0[256], sv1[256];
   int b = blockIdx.x, t = threadIdx.x;
-  double l = 0.0;
+  double l = 0.0, rg = 0.0;
   long long v0 = 0, v1 = 0;
   int rows = d.Cm * d.Pm;
   for (int r = t; r < rows; r += 256) {
@@ -352,23 +403,25 @@ __global__ void __launch_bounds__(256) stats_kernel(WaveDims d, WaveBatches wb, 
     if (i >= bi.n) continue;
     size_t prow = (size_t)blk * d.Pm + i;
     l += (double)w.lossrow[0][prow] + (double)w.lossrow[1][prow];
+    if (d.reg_coef != 0.f) rg += (double)w.regrow[prow];
     v0 += w.violrow[0][prow];
     v1 += w.violrow[1][prow];
   }
-  sl[t] = l; sv0[t] = v0; sv1[t] = v1;
+  sl[t] = l; sr[t] = rg; sv0[t] = v0; sv1[t] = v1;
   __syncthreads();
   for (int o = 128; o > 0; o >>= 1) {
-    if (t < o) { sl[t] += sl[t + o]; sv0[t] += sv0[t + o]; sv1[t] += sv1[t + o]; }
+    if (t < o) { sl[t] += sl[t + o]; sr[t] += sr[t + o]; sv0[t] += sv0[t + o]; sv1[t] += sv1[t + o]; }
     __syncthreads();
   }
   if (t == 0) {
     pbg_batch_stats s;
-    s.loss = (float)sl[0]; s.reg = 0.f; s.violators_lhs = sv0[0]; s.violators_rhs = sv1[0]; s.count = wb.n[b];
+    s.loss = (float)sl[0]; s.reg = (float)sr[0]; s.violators_lhs = sv0[0]; s.violators_rhs = sv1[0]; s.count = wb.n[b];
     if (per_batch) per_batch[wb.gidx[b]] = s;
     atomicAdd(&sum[0], sl[0]);
     atomicAdd(&sum[1], (double)sv0[0]);
     atomicAdd(&sum[2], (double)sv1[0]);
     atomicAdd(&sum[3], (double)wb.n[b]);
+    atomicAdd(&sum[4], sr[0]);
   }
 }
 

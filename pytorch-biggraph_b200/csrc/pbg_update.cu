@@ -24,6 +24,8 @@ struct SlotGrad {
   const float *g, *y, *ylo; // gradient row, prepared operand row (+ its low part in split mode)
   const float *theta;      // operator row or null
   float dotgy, inv, cf;    // cos: <g', y> and 1/|z|; l2 family: coefficient of y
+  float rc;                // N3 regularizer weight if the slot is an adjusted positive row, else 0
+  bool rcplx;              // ... with the complex modulus (complex_diagonal)
   int op, cmp, D;
 
   // gstage: the gradient row already staged in shared memory (null: read it from global memory)
@@ -39,6 +41,12 @@ struct SlotGrad {
     g = gstage ? gstage : w.GX[a] + gr * d.Dp;
     theta = nullptr;
     cf = 0.f; inv = 1.f; dotgy = 0.f;
+    rc = 0.f; rcplx = d.op == PBG_OP_COMPLEX_DIAGONAL;
+    if (d.reg_coef != 0.f) {
+      // regularized rows: the edges of the chunk (not the uniform negatives) in every operand array
+      BlockInfo rbi = block_info(d, wb, blk);
+      if (r < rbi.n && (a >= ARR_Q0 || r < d.Pm)) rc = d.reg_coef;
+    }
     if (d.matrix_op) {
       op = PBG_OP_NONE;
       if (a == ARR_N1 && !pre_op) {            // R2 already holds d(loss)/d(raw row)
@@ -68,7 +76,7 @@ struct SlotGrad {
 #pragma unroll
       for (int c = 0; c < VEC; ++c) {
         int dd = c * 128 + lane * 4;
-        if (dd < D) s += f4dot(ld4(g + dd), yv(dd));
+        if (dd < D) s += f4dot(graw(dd), yv(dd));
       }
       dotgy = warp_sum(s);
     }
@@ -78,8 +86,14 @@ struct SlotGrad {
     return ylo ? v + ld4(ylo + dd) : v;
   }
   // gradient w.r.t. the operator output z at elements [dd, dd+4)
-  __device__ __forceinline__ float4 gz(int dd) const {
+  // gradient that reaches the prepared row: from the contractions, plus the regularizer's own
+  __device__ __forceinline__ float4 graw(int dd) const {
     float4 v = ld4(g + dd);
+    if (rc != 0.f) v = v + n3_grad4(y, dd, D, rcplx) * rc;
+    return v;
+  }
+  __device__ __forceinline__ float4 gz(int dd) const {
+    float4 v = graw(dd);
     const int cmp = CMPK >= 0 ? CMPK : this->cmp;
     if (cmp >= PBG_CMP_L2) v = v - yv(dd) * cf;
     else if (cmp == PBG_CMP_COS) v = (v - yv(dd) * dotgy) * inv;   // (g - y <g,y>) / |z|
@@ -226,7 +240,11 @@ __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, 
 #pragma unroll
     for (int c = 0; c < VEC; ++c) {
       int dd = c * 128 + lane * 4;
-      if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, xlo, xscale, dd);
+      if (dd < D) {
+        acc[c] = acc[c] + op_param_grad<VEC>(sg, x, xlo, xscale, dd);
+        // N3 regularizer on the edge's own parameter row (still as the wave found it in global memory)
+        if (d.reg_coef != 0.f && sg.theta) acc[c] = acc[c] + n3_grad4(sg.theta, dd, D, d.op == PBG_OP_COMPLEX_DIAGONAL) * d.reg_coef;
+      }
     }
   }
 }
@@ -575,6 +593,16 @@ __global__ void __launch_bounds__(32 * UPD_WARPS) relgrad_std_kernel(WaveDims d,
       }
     }
   }
+  if (d.reg_coef != 0.f && wl == 0 && bi.n > 0) {
+    // N3 regularizer on the relation's parameters: sum(params^3) * number of chunks
+    // (regularizers.py:88-92), i.e. once per chunk block; theta is still the wave's snapshot here
+    const float *th = w.theta[0] + (size_t)wb.rel[bi.b] * D;
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) {
+      int dd = c * 128 + lane * 4;
+      if (dd < D) acc[c] = acc[c] + n3_grad4(th, dd, D, d.op == PBG_OP_COMPLEX_DIAGONAL) * d.reg_coef;
+    }
+  }
   float *out = w.relpart + ((size_t)blk * UPD_WARPS + wl) * D;     // one partial per warp
 #pragma unroll
   for (int c = 0; c < VEC; ++c) {
@@ -778,9 +806,9 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   }
   cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
   // the gradient slot is the row's gradient as it stands: dot comparator, and no operator or a translation
-  const bool plain = d.cmp == PBG_CMP_DOT && !d.matrix_op && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION);
+  const bool plain = d.cmp == PBG_CMP_DOT && !d.matrix_op && d.reg_coef == 0.f && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION);
   if (plain) tile_update_kernel<VEC, RULE_EMB, 1><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
-  else if (d.cmp == PBG_CMP_COS && !d.matrix_op && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION))
+  else if (d.cmp == PBG_CMP_COS && !d.matrix_op && d.reg_coef == 0.f && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION))
     tile_update_kernel<VEC, RULE_EMB, 2><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   else tile_update_kernel<VEC, RULE_EMB, 0><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt);

@@ -3,7 +3,7 @@ step reads, with the same key names and meanings.  `from_reference` accepts the 
 ConfigSchema object (duck-typed) so that a stock config file drives this path unchanged.
 
 Keys with no device code are refused where the trainer is built (NotImplementedError), never
-silently ignored: bias, max_norm, regularization_coef, half_precision, featurized entities,
+silently ignored: bias, max_norm, half_precision, featurized entities,
 all_negs relations, per-entity dimensions."""
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
@@ -50,7 +50,8 @@ class ConfigSchema:
     # keys the reference has and this path refuses when set
     bias: bool = False
     max_norm: Optional[float] = None
-    regularization_coef: float = 0.0
+    regularization_coef: float = 0.0    # N3 regularizer weight (regularizers.py:51-97)
+    regularizer: str = "N3"
     half_precision: bool = False
     # keys of this implementation
     precision: str = "fp32"        # "fp32" | "tf32x3" | "tf32": arithmetic of the contractions
@@ -66,7 +67,7 @@ class ConfigSchema:
         kw = dict(entities=ents, relations=rels, dimension=cfg.dimension, num_dynamic_rels=num_dynamic_rels)
         for k in ("comparator", "loss_fn", "margin", "lr", "relation_lr", "batch_size", "num_batch_negs",
                   "num_uniform_negs", "disable_lhs_negs", "disable_rhs_negs", "dynamic_relations", "init_scale",
-                  "global_emb", "bias", "max_norm", "regularization_coef", "half_precision"):
+                  "global_emb", "bias", "max_norm", "regularization_coef", "regularizer", "half_precision"):
             if hasattr(cfg, k):
                 kw[k] = getattr(cfg, k)
         kw.update(overrides)
@@ -80,8 +81,10 @@ class ConfigSchema:
             bad.append("bias=True")
         if self.max_norm is not None:
             bad.append("max_norm")
-        if self.regularization_coef != 0:
-            bad.append("regularization_coef != 0")
+        if self.regularization_coef != 0 and self.regularizer != "N3":
+            bad.append(f"regularizer '{self.regularizer}'")
+        if self.regularization_coef != 0 and any(r.operator in ("linear", "affine") for r in self.relations):
+            bad.append("regularization with linear / affine operators (the reference has none either, operators.py:39-40)")
         if self.half_precision:
             bad.append("half_precision=True")
         if any(e.featurized for e in self.entities.values()):

@@ -50,6 +50,7 @@ class _Native:
         c.margin = margin
         c.lr = lr
         c.relation_lr = lr if relation_lr is None else relation_lr
+        c.regularization_coef = float(getattr(cfg, "regularization_coef", 0.0))
         self.cfg = c
         self.max_batch = max_batch
         self.device_index = model.device.index if model.device.index is not None else torch.cuda.current_device()
@@ -250,7 +251,7 @@ class B200Trainer(AbstractBatchProcessor):
     def read_stats(self) -> Stats:
         s = PbgBatchStats()
         check(self._native.lib.pbg_read_stats(self._native.ctx, C.byref(s)), self._native.ctx)
-        return Stats(loss=float(s.loss), reg=0.0, violators_lhs=int(s.violators_lhs),
+        return Stats(loss=float(s.loss), reg=float(s.reg), violators_lhs=int(s.violators_lhs),
                      violators_rhs=int(s.violators_rhs), count=int(s.count))
 
     # ---- the reference interface ---------------------------------------------------------------

@@ -177,6 +177,10 @@ CASES = [
     dict(name="n3_std_none_dot_logistic", op="none", comp="dot", loss="logistic", B=90, nb=40, nu=10, reg_coef=1e-2),
     dict(name="n3_std_translation_l2_softmax", op="translation", comp="l2", loss="softmax", B=90, nb=40, nu=10, reg_coef=1e-2),
     dict(name="n3_std_complex_dot_ranking_global", op="complex_diagonal", comp="dot", loss="ranking", B=90, nb=40, nu=10, reg_coef=1e-2, global_emb=True),
+    # max_norm: looked-up rows longer than max_norm are rescaled in the table (F.embedding, model.py:57-61)
+    dict(name="max_norm_std_translation_dot_softmax", op="translation", comp="dot", loss="softmax", B=130, nb=50, nu=20, max_norm=1.0, steps=2),
+    dict(name="max_norm_dyn_complex_dot_logistic", op="complex_diagonal", comp="dot", loss="logistic", B=110, nb=50, nu=10, dyn=True, R=5, max_norm=1.2),
+    dict(name="max_norm_separate_global", op="diagonal", comp="cos", loss="ranking", B=130, nb=50, nu=20, w_scale=1.0, separate=True, global_emb=True, max_norm=3.5),
     dict(name="edge_weights_logistic_dyn", op="diagonal", comp="dot", loss="logistic", B=110, nb=50, nu=10, dyn=True, R=5, edge_weight=True),
 ]
 
@@ -195,7 +199,7 @@ def run_case(case):
     torch.set_num_threads(1)
     c = dict(D=16, N=211, N2=157, dyn=False, R=1, separate=False, id_range=None, steps=1, w_scale=0.3,
              disable_lhs=False, disable_rhs=False, n_rel_std=1, rel_idx=0, rel_weight=1.0, margin=0.1,
-             lr=0.1, relation_lr=0.05, edge_weight=False, global_emb=False, reg_coef=0.0)
+             lr=0.1, relation_lr=0.05, edge_weight=False, global_emb=False, reg_coef=0.0, max_norm=None)
     c.update(case)
     D, N, B, dyn = c["D"], c["N"], c["B"], c["dyn"]
     ents = {"e": EntitySchema(num_partitions=1)}
@@ -211,7 +215,7 @@ def run_case(case):
     cfg_batch = max(B, 1) if c["nb"] == 0 else ((B - 1) // c["nb"] + 1) * c["nb"]
     cfg = ConfigSchema(entities=ents, relations=rels, dimension=D, entity_path="x", edge_paths=["y"],
                        checkpoint_path="z", comparator=c["comp"], loss_fn=c["loss"], margin=c["margin"],
-                       global_emb=c["global_emb"], regularization_coef=c["reg_coef"], batch_size=cfg_batch, num_batch_negs=c["nb"], num_uniform_negs=c["nu"],
+                       global_emb=c["global_emb"], regularization_coef=c["reg_coef"], max_norm=c["max_norm"], batch_size=cfg_batch, num_batch_negs=c["nb"], num_uniform_negs=c["nu"],
                        lr=c["lr"], relation_lr=c["relation_lr"], dynamic_relations=dyn,
                        disable_lhs_negs=c["disable_lhs"], disable_rhs_negs=c["disable_rhs"])
     if dyn:

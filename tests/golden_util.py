@@ -27,7 +27,7 @@ def oracle_config(c):
                       lr=c["lr"], relation_lr=c["relation_lr"], num_batch_negs=c["nb"], num_uniform_negs=c["nu"],
                       dynamic=c["dyn"], num_rels=(c["R"] if c["dyn"] else c["n_rel_std"]),
                       disable_lhs_negs=c["disable_lhs"], disable_rhs_negs=c["disable_rhs"],
-                      relation_weights=weights, regularization_coef=c.get("reg_coef", 0.0))
+                      relation_weights=weights, regularization_coef=c.get("reg_coef", 0.0), max_norm=c.get("max_norm"))
 
 
 def oracle_state(c, z, dtype=np.float64):

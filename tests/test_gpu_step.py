@@ -14,7 +14,7 @@ DEVICE_OPS = ("none", "diagonal", "translation", "complex_diagonal", "linear", "
 
 
 def _supported(c):
-    return c["op"] in DEVICE_OPS and not c.get("reg_coef")
+    return c["op"] in DEVICE_OPS and not c.get("max_norm")
 
 
 def _names():
@@ -43,6 +43,8 @@ def test_step_matches_reference_fixture(name, precision):
         assert st.count == len(lhs)
         assert st.metrics["loss"] == pytest.approx(float(z[f"loss_{step}"]), rel=RTOL, abs=1e-3), "loss vs reference"
         assert st.metrics["loss"] == pytest.approx(ostats["loss"], rel=RTOL, abs=1e-3), "loss vs oracle"
+        if f"reg_{step}" in z.files:
+            assert st.metrics["reg"] == pytest.approx(float(z[f"reg_{step}"]), rel=RTOL, abs=1e-5), "regularizer vs reference"
         assert abs(st.metrics["violators_lhs"] - int(z[f"violators_lhs_{step}"])) <= ostats["ties_lhs"]
         assert abs(st.metrics["violators_rhs"] - int(z[f"violators_rhs_{step}"])) <= ostats["ties_rhs"]
         _close(rig.W_lhs.cpu().numpy(), z[f"W_lhs_after_{step}"], what="W_lhs vs reference")

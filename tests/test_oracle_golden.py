@@ -160,7 +160,7 @@ def _torch_port_cases():
     out = []
     for n in step_fixture_names():
         c, _ = load_step(n)
-        if c["op"] in ("linear", "affine") or c["disable_lhs"] or c["disable_rhs"] or c.get("edge_weight") or c.get("global_emb") or c.get("reg_coef"):
+        if c["op"] in ("linear", "affine") or c["disable_lhs"] or c["disable_rhs"] or c.get("edge_weight") or c.get("global_emb") or c.get("reg_coef") or c.get("max_norm"):
             continue
         out.append(n)
     return out
