@@ -85,6 +85,10 @@ typedef struct {
                                  (train_cpu.py:224-228: relation_lr if set, else lr)           */
   float regularization_coef;  /* N3 regularizer weight (torchbiggraph/regularizers.py:51-97),
                                  0 = off; not with linear / affine operators                   */
+  float max_norm;             /* > 0: a looked-up row longer than this enters the step scaled by
+                                 max_norm / (norm + 1e-7), and the table keeps the scaled row
+                                 (F.embedding(max_norm=...), torchbiggraph/model.py:57-61);
+                                 0 = off                                                        */
 } pbg_config;
 
 /* One resident (lhs partition, rhs partition) bucket.  Pointers are device memory. */

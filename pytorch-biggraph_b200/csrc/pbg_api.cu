@@ -169,7 +169,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   // ---- carve the workspace ------------------------------------------------------------------
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
-  size_t oReg = 0;
+  size_t oReg = 0, oRscale = 0;
   size_t oX[4], oAux[4], oG[4], oS[2], oSpos[2], oCoef[4], oLoss[2], oViol[2], oRank[2], oXL[4] = {0, 0, 0, 0}, oSL[2] = {0, 0};
   const bool split = false;   // TF32X3 splits operands inside the contraction kernel: no low-part arrays
   oX[0] = take(nN * c->Dp * 4); oX[1] = take(nN * c->Dp * 4);
@@ -195,7 +195,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   }
   for (int p = 0; p < 2; ++p) {
     oS[p] = take(nQ * c->Ms * 4); oSpos[p] = take(nQ * 4); oLoss[p] = take(nQ * 4); oViol[p] = take(nQ * 4);
-    if (p == 0) oReg = take(nQ * 4);
+    if (p == 0) { oReg = take(nQ * 4); oRscale = take(nN * 4); }
     oRank[p] = take(nQ * 4);
   }
   oCoef[0] = take(nN * 4); oCoef[1] = take(nN * 4); oCoef[2] = take(nQ * 4); oCoef[3] = take(nQ * 4);
@@ -238,7 +238,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     b.S[p] = (float *)(c->ws + oS[p]);
     b.spos[p] = (float *)(c->ws + oSpos[p]);
     b.lossrow[p] = (float *)(c->ws + oLoss[p]);
-    if (p == 0) b.regrow = (float *)(c->ws + oReg);
+    if (p == 0) { b.regrow = (float *)(c->ws + oReg); b.rscale = (float *)(c->ws + oRscale); }
     b.violrow[p] = (int *)(c->ws + oViol[p]);
     b.rankrow[p] = (int *)(c->ws + oRank[p]);
   }
@@ -344,7 +344,7 @@ static int bind_bucket(pbg_context *c, const pbg_bucket *bk, WaveDims &d, WaveBu
   d.op = cfg.op; d.cmp = cfg.comparator; d.loss = cfg.loss; d.dynamic = cfg.dynamic_relations != 0;
   d.batch_negs = cfg.num_batch_negs > 0;
   d.neg_enabled[0] = !cfg.disable_lhs_negs; d.neg_enabled[1] = !cfg.disable_rhs_negs;
-  d.num_batch_negs = cfg.num_batch_negs; d.spb = c->spb; d.margin = cfg.margin; d.reg_coef = cfg.regularization_coef;
+  d.num_batch_negs = cfg.num_batch_negs; d.spb = c->spb; d.margin = cfg.margin; d.reg_coef = cfg.regularization_coef; d.max_norm = cfg.max_norm > 0.f ? cfg.max_norm : 0.f;
   d.split = 0;
   d.matrix_op = cfg.op == PBG_OP_LINEAR || cfg.op == PBG_OP_AFFINE;
   d.opw = d.matrix_op ? cfg.dim * cfg.dim + (cfg.op == PBG_OP_AFFINE ? cfg.dim : 0) : cfg.dim;

@@ -46,6 +46,7 @@ struct WaveDims {
   int nocc;             // k * spb
   float margin;
   float reg_coef;       // N3 regularizer weight, 0 = off
+  float max_norm;       // > 0: looked-up rows longer than this are used (and kept) scaled to it
   long long n_rows[2];  // rows of the lhs / rhs table
   int shared_table;     // lhs and rhs read the same table
   int num_rels;
@@ -79,6 +80,7 @@ struct WaveBufs {
   float *spos[2];                    // positive scores [nblk][Pm]
   float *coef[4];                    // l2: colsum(T0), colsum(T1), rowsum(T0), rowsum(T1)
   float *lossrow[2];                 // per positive row: weighted loss term
+  float *rscale;                     // max_norm: scale applied to the raw row of every N1 slot [blk][Mm] (1 = none)
   float *regrow;                     // per positive row: its share of the N3 regularizer (reg_coef != 0)
   int *violrow[2];                   // per positive row: #(neg > pos)
   int *rankrow[2];                   // evaluation: per positive row, 1 + #(neg >= pos)

@@ -19,6 +19,24 @@ __device__ __forceinline__ void load_row(float4 (&v)[VEC], const float *row, int
     v[c] = d < D ? ld4(row + d) : f4zero();
   }
 }
+// F.embedding(max_norm=...) (torchbiggraph/model.py:57-61): a looked-up row whose 2-norm exceeds
+// max_norm is used scaled by max_norm / (norm + 1e-7).  Here the scale is applied in registers and
+// returned; the table itself is rewritten by the update kernel, which owns each touched row alone
+// (RowState::load applies the same scale before the optimizer steps) -- rewriting it from the gather
+// would let the duplicates of a row read it half-scaled.
+template <int VEC>
+__device__ __forceinline__ float renorm_row(float4 (&v)[VEC], float max_norm) {
+  if (max_norm <= 0.f) return 1.0f;
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) ss += f4dot(v[c], v[c]);
+  float norm = sqrtf(warp_sum(ss));
+  if (!(norm > max_norm)) return 1.0f;
+  float sc = max_norm / (norm + 1e-7f);
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) v[c] = v[c] * sc;
+  return sc;
+}
 // row += the global embedding of the row's entity type (config.global_emb; model.py:486-492), if any
 template <int VEC>
 __device__ __forceinline__ void add_global(float4 (&v)[VEC], const float *glob, int D, int lane) {
@@ -68,7 +86,7 @@ __device__ __forceinline__ void zero_row(float *row, int D, int lane) {
 // lane: the partner chunk is re-read from memory (an L1 hit).
 template <int VEC>
 __device__ __forceinline__ void apply_operator(float4 (&z)[VEC], const float4 (&x)[VEC], const float *xrow,
-                                               const float *theta, int op, int D, int lane, const float *glob = nullptr) {
+                                               const float *theta, int op, int D, int lane, const float *glob = nullptr, float rsc = 1.0f) {
   int h = D >> 1;
 #pragma unroll
   for (int c = 0; c < VEC; ++c) {
@@ -80,7 +98,7 @@ __device__ __forceinline__ void apply_operator(float4 (&z)[VEC], const float4 (&
     else if (op == PBG_OP_TRANSLATION) z[c] = x[c] + t;
     else {  // complex_diagonal: theta = [real | imag]
       int dp = d < h ? d + h : d - h;
-      float4 xp = ld4(xrow + dp), tp = ld4(theta + dp);
+      float4 xp = ld4(xrow + dp) * rsc, tp = ld4(theta + dp);
       if (glob) xp = xp + ld4(glob + dp);
       z[c] = d < h ? x[c] * t - xp * tp      // re = a_re p_re - a_im p_im
                    : xp * t + x[c] * tp;     // im = a_re p_im + a_im p_re
@@ -172,6 +190,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     const float *th0 = (d.op != PBG_OP_NONE && w.theta[0]) ? w.theta[0] + (size_t)rl * D : nullptr;
     // lhs row without operator -> N0
     load_row<VEC>(x, xl, D, lane);
+    const float scl = renorm_row<VEC>(x, d.max_norm);
     add_global<VEC>(x, w.glob[0], D, lane);
 #pragma unroll
     for (int c = 0; c < VEC; ++c) y0[c] = x[c];
@@ -181,14 +200,17 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
       // linear / affine: the raw rhs row goes to R1; operator, prepare and the positive score
       // follow in the contraction and postop_kernel
       load_row<VEC>(x, xr, D, lane);
+      renorm_row<VEC>(x, d.max_norm);
       add_global<VEC>(x, w.glob[1], D, lane);
       store_row<VEC>(w.R1 + noff, x, D, lane);
       if (lane == 0) w.aux[ARR_N0][nrow] = a0;
     } else if (!d.dynamic) {
       // rhs row through the operator -> N1; one positive score shared by both problems
       load_row<VEC>(x, xr, D, lane);
+      const float scr = renorm_row<VEC>(x, d.max_norm);
+      if (d.max_norm > 0.f && lane == 0) w.rscale[nrow] = scr;
       add_global<VEC>(x, w.glob[1], D, lane);
-      apply_operator<VEC>(y1, x, xr, th0, d.op, D, lane, w.glob[1]);
+      apply_operator<VEC>(y1, x, xr, th0, d.op, D, lane, w.glob[1], scr);
       float a1 = prepare_row<VEC>(y1, d.cmp);
       put_row<VEC>(w.X[ARR_N1], lo(ARR_N1), noff, y1, D, lane);
       float s = positive_score<VEC>(y0, y1, d.cmp);
@@ -199,18 +221,19 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     } else {
       const float *th1 = (d.op != PBG_OP_NONE && w.theta[1]) ? w.theta[1] + (size_t)rl * D : nullptr;
       // op_lhs(lhs row) -> Q1 (x still holds the lhs row)
-      apply_operator<VEC>(z, x, xl, th1, d.op, D, lane);
+      apply_operator<VEC>(z, x, xl, th1, d.op, D, lane, nullptr, scl);
       float aq1 = prepare_row<VEC>(z, d.cmp);
       put_row<VEC>(w.X[ARR_Q1], lo(ARR_Q1), qoff, z, D, lane);
       // rhs row without operator -> N1
       load_row<VEC>(x, xr, D, lane);
+      const float scr = renorm_row<VEC>(x, d.max_norm);
 #pragma unroll
       for (int c = 0; c < VEC; ++c) y1[c] = x[c];
       float a1 = prepare_row<VEC>(y1, d.cmp);
       put_row<VEC>(w.X[ARR_N1], lo(ARR_N1), noff, y1, D, lane);
       float s1 = positive_score<VEC>(y1, z, d.cmp);         // problem 1: c(rhs, op_lhs(lhs))
       // op_rhs(rhs row) -> Q0
-      apply_operator<VEC>(z, x, xr, th0, d.op, D, lane);
+      apply_operator<VEC>(z, x, xr, th0, d.op, D, lane, nullptr, scr);
       float aq0 = prepare_row<VEC>(z, d.cmp);
       put_row<VEC>(w.X[ARR_Q0], lo(ARR_Q0), qoff, z, D, lane);
       float s0 = positive_score<VEC>(y0, z, d.cmp);         // problem 0: c(lhs, op_rhs(rhs))
@@ -237,6 +260,8 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     }
     const float *xrow = w.W[side] + (size_t)id * D;
     load_row<VEC>(x, xrow, D, lane);
+    const float scu = renorm_row<VEC>(x, d.max_norm);
+    if (side == 1 && d.max_norm > 0.f && lane == 0) w.rscale[nrow] = scu;
     add_global<VEC>(x, w.glob[side], D, lane);
     if (side == 1 && d.matrix_op) { store_row<VEC>(w.R1 + noff, x, D, lane); continue; }
     const float *th = nullptr;
@@ -244,7 +269,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
       int rl = wb.rel[bi.b];
       if (rl >= 0 && rl < d.num_rels) th = w.theta[0] + (size_t)rl * D;
     }
-    apply_operator<VEC>(z, x, xrow, th, d.op, D, lane, w.glob[side]);
+    apply_operator<VEC>(z, x, xrow, th, d.op, D, lane, w.glob[side], scu);
     float a = prepare_row<VEC>(z, d.cmp);
     put_row<VEC>(w.X[side], lo(side), noff, z, D, lane);
     if (lane == 0) w.aux[side][nrow] = a;
@@ -376,7 +401,7 @@ int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, c
   long long items = (long long)d.nblk * d.Mm;
   int ctas = (int)((items + GATHER_WARPS - 1) / GATHER_WARPS);
   int vec = (d.D + 127) / 128;
-  const bool plain = !d.dynamic && !d.matrix_op && !d.split && d.cmp == PBG_CMP_DOT && (d.op == PBG_OP_NONE || w.theta[0] == nullptr);
+  const bool plain = !d.dynamic && !d.matrix_op && !d.split && d.max_norm <= 0.f && d.cmp == PBG_CMP_DOT && (d.op == PBG_OP_NONE || w.theta[0] == nullptr);
   if (plain) {
     if (vec <= 1) gather_plain_kernel<1><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
     else if (vec <= 2) gather_plain_kernel<2><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);

@@ -122,9 +122,9 @@ __device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC, -1, -1> &sg,
   float4 v = sg.gz(dd);
   if (sg.op == PBG_OP_TRANSLATION) return v;
   auto raw = [&](int e) {
-    float4 r = xlo ? ld4(x + e) + ld4(xlo + e) : ld4(x + e);
+    float4 r = (xlo ? ld4(x + e) + ld4(xlo + e) : ld4(x + e)) * xscale;
     if (xadd) r = r + ld4(xadd + e);
-    return r * xscale;
+    return r;
   };
   float4 xv = raw(dd);
   if (sg.op == PBG_OP_DIAGONAL) return v * xv;
@@ -181,6 +181,19 @@ struct RowState {
       int dd = c * 128 + lane * 4;
       v[c] = dd < D ? ld4(prow + dd) : f4zero();
       if (RULE == RULE_REL) a[c] = dd < D ? ld4(pacc + dd) : f4zero();
+    }
+    if (RULE == RULE_EMB && d.max_norm > 0.f) {
+      // the lookup of this wave used the row scaled to max_norm (F.embedding(max_norm=...), model.py:57-61;
+      // same arithmetic as the gather): the table keeps the scaled row, the optimizer steps start from it
+      float ss = 0.f;
+#pragma unroll
+      for (int c = 0; c < VEC; ++c) ss += f4dot(v[c], v[c]);
+      float norm = sqrtf(warp_sum(ss));
+      if (norm > d.max_norm) {
+        float sc = d.max_norm / (norm + 1e-7f);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) v[c] = v[c] * sc;
+      }
     }
   }
   // one optimizer step with the summed gradient g of one batch
@@ -586,10 +599,11 @@ __global__ void __launch_bounds__(32 * UPD_WARPS) relgrad_std_kernel(WaveDims d,
       SlotGrad<VEC> sg;
       sg.init(d, wb, w, a, blk, r, bi.b, lane);
       const float *x = w.W[1] + (size_t)row * D;
+      const float xsc = d.max_norm > 0.f ? w.rscale[(size_t)blk * d.Mm + r] : 1.0f;    // the raw row entered the operator scaled
 #pragma unroll
       for (int c = 0; c < VEC; ++c) {
         int dd = c * 128 + lane * 4;
-        if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, nullptr, 1.0f, dd, w.glob[1]);
+        if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, nullptr, xsc, dd, w.glob[1]);
       }
     }
   }

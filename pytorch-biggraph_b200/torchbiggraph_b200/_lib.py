@@ -23,7 +23,7 @@ class PbgConfig(C.Structure):
         "dim", "op", "comparator", "loss", "dynamic_relations", "num_rels", "num_batch_negs",
         "num_uniform_negs", "disable_lhs_negs", "disable_rhs_negs", "precision", "max_batch_size",
         "batches_in_flight")] + [("margin", C.c_float), ("lr", C.c_float), ("relation_lr", C.c_float),
-                                    ("regularization_coef", C.c_float)]
+                                    ("regularization_coef", C.c_float), ("max_norm", C.c_float)]
 
 
 class PbgBucket(C.Structure):

@@ -3,7 +3,7 @@ step reads, with the same key names and meanings.  `from_reference` accepts the 
 ConfigSchema object (duck-typed) so that a stock config file drives this path unchanged.
 
 Keys with no device code are refused where the trainer is built (NotImplementedError), never
-silently ignored: bias, max_norm, half_precision, featurized entities,
+silently ignored: bias, half_precision, featurized entities,
 all_negs relations, per-entity dimensions."""
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
@@ -79,8 +79,8 @@ class ConfigSchema:
             raise RuntimeError("Cannot have global embs with dynamic rels")          # model.py:488-489
         if self.bias:
             bad.append("bias=True")
-        if self.max_norm is not None:
-            bad.append("max_norm")
+        if self.max_norm is not None and self.max_norm <= 0:
+            raise ValueError("max_norm must be positive")
         if self.regularization_coef != 0 and self.regularizer != "N3":
             bad.append(f"regularizer '{self.regularizer}'")
         if self.regularization_coef != 0 and any(r.operator in ("linear", "affine") for r in self.relations):

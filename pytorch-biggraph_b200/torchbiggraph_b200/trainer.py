@@ -51,6 +51,7 @@ class _Native:
         c.lr = lr
         c.relation_lr = lr if relation_lr is None else relation_lr
         c.regularization_coef = float(getattr(cfg, "regularization_coef", 0.0))
+        c.max_norm = float(getattr(cfg, "max_norm", None) or 0.0)
         self.cfg = c
         self.max_batch = max_batch
         self.device_index = model.device.index if model.device.index is not None else torch.cuda.current_device()

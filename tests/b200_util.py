@@ -21,7 +21,7 @@ def make_config(c, precision="fp32", k=1):
                           num_batch_negs=nb, num_uniform_negs=c["nu"], disable_lhs_negs=c["disable_lhs"],
                           disable_rhs_negs=c["disable_rhs"], dynamic_relations=c["dyn"],
                           num_dynamic_rels=(c["R"] if c["dyn"] else 0), precision=precision, batches_in_flight=k,
-                          global_emb=bool(c.get("global_emb", False)), regularization_coef=c.get("reg_coef", 0.0)), rhs_ent
+                          global_emb=bool(c.get("global_emb", False)), regularization_coef=c.get("reg_coef", 0.0), max_norm=c.get("max_norm")), rhs_ent
 
 
 class Rig:

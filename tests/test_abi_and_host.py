@@ -111,7 +111,7 @@ def _cfg(**kw):
     return T.ConfigSchema(**base)
 
 
-@pytest.mark.parametrize("kw", [dict(bias=True), dict(max_norm=1.0), dict(regularization_coef=1e-3, regularizer="L2"),
+@pytest.mark.parametrize("kw", [dict(bias=True), dict(regularization_coef=1e-3, regularizer="L2"),
                                 dict(half_precision=True), dict(entities={"e": T.EntitySchema(featurized=True)}),
                                 dict(relations=[T.RelationSchema("r", "e", "e", all_negs=True)])])
 def test_unsupported_config_keys_raise(kw):

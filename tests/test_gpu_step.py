@@ -14,7 +14,7 @@ DEVICE_OPS = ("none", "diagonal", "translation", "complex_diagonal", "linear", "
 
 
 def _supported(c):
-    return c["op"] in DEVICE_OPS and not c.get("max_norm")
+    return c["op"] in DEVICE_OPS
 
 
 def _names():
