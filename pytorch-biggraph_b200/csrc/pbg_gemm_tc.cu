@@ -32,6 +32,12 @@
 
 #include "pbg_common.cuh"
 
+// k-values per pipeline stage: 32 (two stages of 96 KB with their low parts in TF32X3) or 16 (four stages of
+// 48 KB; K-major tiles then have 64-byte rows -- TMA 64-byte swizzle, descriptor layout 4, 512 bytes per 8
+// rows -- and MN-major boxes are 32 x 16, descriptor LBO 2048).  Both are verified and give the same speed:
+// the main loop is bound by shared-memory bandwidth (load 1x, split 3x, MMA operand reads 3x the tile per
+// stage), not by the depth of the ring, and a tile takes the same time whether 20 or 148 CTAs run.
+#define TC_KB 32
 #define TC_THREADS 448          // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-13 split operands (TF32X3)
 #define TC_SPLIT_THREADS 256
 #define TC_WAIT_LIMIT 4000000
@@ -76,8 +82,11 @@ template <bool A_MN, bool B_MN, int NTERMS, bool L2EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBatches wb, int *errflag) {
   constexpr bool SPLIT = NTERMS == 3;
-  constexpr int STAGES = SPLIT ? 2 : 4;
-  constexpr uint32_t A_BYTES = 128 * 128, B_BYTES = 256 * 128;          // one 32-k tile of 128 / 256 rows
+  constexpr int KB = TC_KB;
+  constexpr int STAGES = (SPLIT ? 2 : 4) * (32 / KB);
+  constexpr uint32_t ROW_BYTES = KB * 4;                                 // bytes of one K-major row of a stage
+  constexpr uint32_t BOX_BYTES = KB * 128;                               // one 32 x KB MN-major box
+  constexpr uint32_t A_BYTES = 128 * ROW_BYTES, B_BYTES = 256 * ROW_BYTES;   // one KB-k tile of 128 / 256 rows
   constexpr uint32_t RAW_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t STAGE_BYTES = SPLIT ? 2 * RAW_BYTES : RAW_BYTES;   // [A hi][B hi] ([A lo][B lo])
 
@@ -112,9 +121,9 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = tmem_base_s;
-  const int nkb = (g.K + 31) / 32;
+  const int nkb = (g.K + KB - 1) / KB;
   const int b_atoms = (g.BN + 31) / 32;
-  const uint32_t b_used = B_MN ? (uint32_t)b_atoms * 4096u : (uint32_t)g.BN * 128u;
+  const uint32_t b_used = B_MN ? (uint32_t)b_atoms * BOX_BYTES : (uint32_t)g.BN * ROW_BYTES;
   const uint32_t stage_tx = A_BYTES + b_used;
   // persistent tile loop: tile t -> (n tile, m tile, chunk block, problem); every role walks the same list
   const int tiles_n = (g.N + g.BN - 1) / g.BN, tiles_m = (g.M + 127) / 128;
@@ -150,15 +159,15 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(fb), "r"(stage_tx) : "memory");
         __syncwarp();
         unsigned char *st = smem + (size_t)s * STAGE_BYTES;
-        int k0 = kb * 32;
+        int k0 = kb * KB;
         uint32_t dA = smem_u32(st), dB = smem_u32(st + A_BYTES);
         if (lane < a_boxes) {
           if (!A_MN) tma_load_3d(dA, &maps.a[p], k0, m0, blk, fb);
-          else tma_load_3d(dA + lane * 4096, &maps.a[p], m0 + lane * 32, k0, blk, fb);
+          else tma_load_3d(dA + lane * BOX_BYTES, &maps.a[p], m0 + lane * 32, k0, blk, fb);
         } else if (lane < a_boxes + b_boxes) {
           int nb = lane - a_boxes;
           if (!B_MN) tma_load_3d(dB, &maps.b[p], k0, n0, blk, fb);
-          else tma_load_3d(dB + nb * 4096, &maps.b[p], n0 + nb * 32, k0, blk, fb);
+          else tma_load_3d(dB + nb * BOX_BYTES, &maps.b[p], n0 + nb * 32, k0, blk, fb);
         }
       }
     }
@@ -184,14 +193,15 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         uint32_t aH = smem_u32(st), bH = smem_u32(st + A_BYTES);
         uint32_t aL = aH + RAW_BYTES, bL = bH + RAW_BYTES;
 #pragma unroll
-        for (int k8 = 0; k8 < 4; ++k8) {
+        for (int k8 = 0; k8 < KB / 8; ++k8) {
+          constexpr uint32_t KSBO = KB == 32 ? 1024 : 512, KLAY = KB == 32 ? 2 : 4;     // K-major: 8 rows of ROW_BYTES; 128- / 64-byte swizzle
           uint32_t ao = A_MN ? k8 * 1024 : k8 * 32, bo = B_MN ? k8 * 1024 : k8 * 32;
-          uint64_t dAh = A_MN ? smem_desc(aH + ao, 4096, 512, 1) : smem_desc(aH + ao, 0, 1024, 2);
-          uint64_t dBh = B_MN ? smem_desc(bH + bo, 4096, 512, 1) : smem_desc(bH + bo, 0, 1024, 2);
+          uint64_t dAh = A_MN ? smem_desc(aH + ao, BOX_BYTES, 512, 1) : smem_desc(aH + ao, 0, KSBO, KLAY);
+          uint64_t dBh = B_MN ? smem_desc(bH + bo, BOX_BYTES, 512, 1) : smem_desc(bH + bo, 0, KSBO, KLAY);
           uint32_t acc = (kb > 0 || k8 > 0) ? 1u : 0u;
           if (SPLIT) {
-            uint64_t dAl = A_MN ? smem_desc(aL + ao, 4096, 512, 1) : smem_desc(aL + ao, 0, 1024, 2);
-            uint64_t dBl = B_MN ? smem_desc(bL + bo, 4096, 512, 1) : smem_desc(bL + bo, 0, 1024, 2);
+            uint64_t dAl = A_MN ? smem_desc(aL + ao, BOX_BYTES, 512, 1) : smem_desc(aL + ao, 0, KSBO, KLAY);
+            uint64_t dBl = B_MN ? smem_desc(bL + bo, BOX_BYTES, 512, 1) : smem_desc(bL + bo, 0, KSBO, KLAY);
             asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
                          :: "r"(tacc), "l"(dAl), "l"(dBh), "r"(idesc), "r"(acc) : "memory");
             asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
@@ -352,7 +362,7 @@ static bool encode3(CUtensorMap *tm, const float *base, int inner, int rows, int
   cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1};
   cuuint32_t es[3] = {1, 1, 1};
   CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : (box_inner * 4 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B),
                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -389,24 +399,24 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
     long long qblk = (long long)w.xrows[q] * d.Dp, nblk_s = (long long)w.xrows[n] * d.Dp, tblk = (long long)d.Pm * d.Ms;
     // score: A = Q (K-major, k = D), B = N (K-major)
     // only the Pm scored rows exist for the map: the rest of the 128-row box is filled with zeros without touching L2
-    ok &= encode3(&pl->score.a[p], Xq, d.D, d.Pm, nblk_max, d.Dp, qblk, 32, 128, false);
-    ok &= encode3(&pl->score.b[p], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, pl->bn_score, false);
+    ok &= encode3(&pl->score.a[p], Xq, d.D, d.Pm, nblk_max, d.Dp, qblk, TC_KB, 128, false);
+    ok &= encode3(&pl->score.b[p], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, TC_KB, pl->bn_score, false);
     // outputs leave through 32 x 32 bulk stores (128-byte swizzle in shared memory), clipped at the matrix edge
     ok &= encode3(&pl->score.c[p], w.S[p], d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 32, false);
     if (pl->dynamic) {
       // grad Q: A = T (K-major, k = Mm), B = N (MN-major: k rows = Mm, contiguous D)
-      ok &= encode3(&pl->gradq.a[p], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 128, false);
-      ok &= encode3(&pl->gradq.b[p], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, 32, true);
+      ok &= encode3(&pl->gradq.a[p], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, TC_KB, 128, false);
+      ok &= encode3(&pl->gradq.b[p], Xn, d.D, w.xrows[n], nblk_max, d.Dp, nblk_s, 32, TC_KB, true);
       // grad N: A = T^T (MN-major: k rows = Pm, contiguous Mm), B = Q (MN-major: k rows = Pm, contiguous D)
-      ok &= encode3(&pl->gradn.a[p], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, 32, true);
-      ok &= encode3(&pl->gradn.b[p], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, 32, true);
+      ok &= encode3(&pl->gradn.a[p], T, d.Mm, d.Pm, nblk_max, d.Ms, tblk, 32, TC_KB, true);
+      ok &= encode3(&pl->gradn.b[p], Xq, d.D, w.xrows[q], nblk_max, d.Dp, qblk, 32, TC_KB, true);
       ok &= encode3(&pl->gradq.c[p], w.GX[q], d.D, d.Pm, nblk_max, d.Dp, (long long)w.grows[q] * d.Dp, 32, 32, false);
       ok &= encode3(&pl->gradn.c[p], w.GX[n], d.D, d.Mm, nblk_max, d.Dp, (long long)w.grows[n] * d.Dp, 32, 32, false);
     } else {
       // merged: side p: A = A[p] (K-major, k = Mm), B = the other side's operand rows (MN-major)
       int o = ARR_N0 + (1 - p);
-      ok &= encode3(&pl->gradm.a[p], w.A[p], d.Mm, d.Mm, nblk_max, w.Ma, (long long)d.Mm * w.Ma, 32, 128, false);
-      ok &= encode3(&pl->gradm.b[p], w.X[o], d.D, w.xrows[o], nblk_max, d.Dp, (long long)w.xrows[o] * d.Dp, 32, 32, true);
+      ok &= encode3(&pl->gradm.a[p], w.A[p], d.Mm, d.Mm, nblk_max, w.Ma, (long long)d.Mm * w.Ma, TC_KB, 128, false);
+      ok &= encode3(&pl->gradm.b[p], w.X[o], d.D, w.xrows[o], nblk_max, d.Dp, (long long)w.xrows[o] * d.Dp, 32, TC_KB, true);
       ok &= encode3(&pl->gradm.c[p], w.GX[n], d.D, d.Mm, nblk_max, d.Dp, (long long)d.Mm * d.Dp, 32, 32, false);
     }
   }
