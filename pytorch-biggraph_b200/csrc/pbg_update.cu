@@ -578,7 +578,7 @@ hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long lo
 
 // Standard relations: every rhs row of a batch went through the same operator row.  Stage 1: one
 // CTA per chunk sums the parameter gradient of its rows (N1 slots: chunk rows + uniform rows)
-// into relpart[b][c][warp][D]; the raw rows are re-read from the rhs table, which this wave has not
+// into relpart[b][c][D] (the eight warps added up in shared memory); the raw rows are re-read from the rhs table, which this wave has not
 // updated yet.  Stage 2 (relupdate_std_kernel) adds the chunks up and steps theta, batch by batch.
 template <int VEC>
 __global__ void __launch_bounds__(32 * UPD_WARPS) relgrad_std_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
@@ -617,11 +617,19 @@ __global__ void __launch_bounds__(32 * UPD_WARPS) relgrad_std_kernel(WaveDims d,
       if (dd < D) acc[c] = acc[c] + n3_grad4(th, dd, D, d.op == PBG_OP_COMPLEX_DIAGONAL) * d.reg_coef;
     }
   }
-  float *out = w.relpart + ((size_t)blk * UPD_WARPS + wl) * D;     // one partial per warp
+  // the eight warps' sums are added in warp order: one partial row per chunk block, so that the
+  // single-CTA stage 2 reads Cm rows per batch instead of 8 Cm (its loads are one dependent chain)
+  extern __shared__ __align__(16) float wpart_raw[];
+  float (*wpart)[VEC * 128] = reinterpret_cast<float (*)[VEC * 128]>(wpart_raw);
 #pragma unroll
-  for (int c = 0; c < VEC; ++c) {
-    int dd = c * 128 + lane * 4;
-    if (dd < D) st4(out + dd, acc[c]);
+  for (int c = 0; c < VEC; ++c) st4(&wpart[wl][c * 128 + lane * 4], acc[c]);
+  __syncthreads();
+  float *out = w.relpart + (size_t)blk * D;
+  for (int dd = threadIdx.x * 4; dd < D; dd += 4 * blockDim.x) {
+    float4 t = ld4(&wpart[0][dd]);
+#pragma unroll
+    for (int u = 1; u < UPD_WARPS; ++u) t = t + ld4(&wpart[u][dd]);
+    st4(out + dd, t);
   }
 }
 
@@ -633,7 +641,7 @@ __global__ void relupdate_std_kernel(WaveDims d, WaveBatches wb, WaveBufs w, flo
     int rl = wb.rel[b];
     if (rl < 0 || rl >= d.num_rels) continue;
     float g = 0.f;
-    for (int c = 0; c < d.Cm * UPD_WARPS; ++c) g += w.relpart[((size_t)b * d.Cm * UPD_WARPS + c) * d.D + dd];
+    for (int c = 0; c < d.Cm; ++c) g += w.relpart[((size_t)b * d.Cm + c) * d.D + dd];
     size_t idx = (size_t)rl * d.D + dd;
     float a = w.acc[0][idx] + g * g;
     w.acc[0][idx] = a;
@@ -715,11 +723,14 @@ __global__ void relupdate_matrix_kernel(WaveDims d, WaveBatches wb, WaveBufs w, 
 // Global embeddings (config.global_emb): the vector of an entity type is added to every row of that
 // type before the operator, so its gradient is the sum of the row gradients of all slots of its
 // side(s).  Stage 1: one CTA per chunk block, warp w sums the slots w, w + 8, ... of the lhs and of
-// the rhs operand array into globpart[blk][side][warp][D]; stage 2 adds the partial sums of a batch
+// the rhs operand array, the eight sums are added in warp order into globpart[blk][side][D]; stage 2
+// adds the partial sums of a batch
 // in a fixed order and applies the dense AsyncAdagrad step, batch after batch
 // (torchbiggraph/async_adagrad.py:75-85; the vector is one of model.parameters(), train_cpu.py:215-230).
 template <int VEC>
 __global__ void __launch_bounds__(32 * UPD_WARPS) globgrad_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  extern __shared__ __align__(16) float wpart_raw[];
+  float (*wpart)[VEC * 128] = reinterpret_cast<float (*)[VEC * 128]>(wpart_raw);
   int lane = threadIdx.x & 31, wl = threadIdx.x >> 5;
   int blk = blockIdx.x;
   BlockInfo bi = block_info(d, wb, blk);
@@ -742,11 +753,16 @@ __global__ void __launch_bounds__(32 * UPD_WARPS) globgrad_kernel(WaveDims d, Wa
         }
       }
     }
-    float *out = w.globpart + (((size_t)blk * 2 + side) * UPD_WARPS + wl) * D;
+    __syncthreads();                                   // wpart of the previous side has been read
 #pragma unroll
-    for (int c = 0; c < VEC; ++c) {
-      int dd = c * 128 + lane * 4;
-      if (dd < D) st4(out + dd, acc[c]);
+    for (int c = 0; c < VEC; ++c) st4(&wpart[wl][c * 128 + lane * 4], acc[c]);
+    __syncthreads();
+    float *out = w.globpart + ((size_t)blk * 2 + side) * D;
+    for (int dd = threadIdx.x * 4; dd < D; dd += 4 * blockDim.x) {
+      float4 t = ld4(&wpart[0][dd]);
+#pragma unroll
+      for (int u = 1; u < UPD_WARPS; ++u) t = t + ld4(&wpart[u][dd]);
+      st4(out + dd, t);
     }
   }
 }
@@ -759,9 +775,7 @@ __global__ void globupdate_kernel(WaveDims d, WaveBatches wb, WaveBufs w, float 
     float g[2] = {0.f, 0.f};
     for (int side = 0; side < 2; ++side) {
       if (!w.glob[side]) continue;
-      for (int c = 0; c < d.Cm; ++c)
-        for (int u = 0; u < UPD_WARPS; ++u)
-          g[side] += w.globpart[((((size_t)b * d.Cm + c) * 2 + side) * UPD_WARPS + u) * d.D + dd];
+      for (int c = 0; c < d.Cm; ++c) g[side] += w.globpart[(((size_t)b * d.Cm + c) * 2 + side) * d.D + dd];
     }
     if (w.glob_shared) { g[0] += g[1]; g[1] = 0.f; }
     for (int side = 0; side < (w.glob_shared ? 1 : 2); ++side) {
@@ -796,20 +810,11 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   // the attribute is set once for the largest wave this row width allows in 227 KB
   size_t hub_smem_max = (size_t)PBG_KMAX * VEC * 128 * sizeof(float);
   if (hub_smem_max > 227 * 1024) hub_smem_max = 227 * 1024;
-  bool has_op = d.op != PBG_OP_NONE && w.theta[0] != nullptr;
-  if (has_op && !d.dynamic && !d.matrix_op) {
-    relgrad_std_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, 0, st>>>(d, wb, w);
-    ++launches;
-  }
-  // gradient sums of the global embeddings: before any operator parameter of this wave is stepped
-  const bool has_glob = w.glob[0] || w.glob[1];
-  if (has_glob) {
-    globgrad_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, 0, st>>>(d, wb, w);
-    ++launches;
-  }
   if (!attr_done[0]) {
     cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem_max);
     cudaFuncSetAttribute(hub_reduce_kernel<VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_smem);
+    cudaFuncSetAttribute(relgrad_std_kernel<VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_smem);
+    cudaFuncSetAttribute(globgrad_kernel<VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_smem);
     cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
     cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -817,6 +822,17 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
     cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
     attr_done[0] = true;
+  }
+  bool has_op = d.op != PBG_OP_NONE && w.theta[0] != nullptr;
+  if (has_op && !d.dynamic && !d.matrix_op) {
+    relgrad_std_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, red_smem, st>>>(d, wb, w);
+    ++launches;
+  }
+  // gradient sums of the global embeddings: before any operator parameter of this wave is stepped
+  const bool has_glob = w.glob[0] || w.glob[1];
+  if (has_glob) {
+    globgrad_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, red_smem, st>>>(d, wb, w);
+    ++launches;
   }
   cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
   // the gradient slot is the row's gradient as it stands: dot comparator, and no operator or a translation
