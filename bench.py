@@ -526,9 +526,12 @@ def run_b200(args, w):
 
     # ---- end-to-end pass: host edges, copies and stats read-back inside the timed region --------
     def step_host(s):
+        # the step's result read back: the summed Stats of its batches (loss, violators, count), one
+        # 40-byte device-to-host read that waits for the step
         if not halves_on:
             bind(bucket_for(s))
-        return step_any(host_edges[s], True)
+        step_any(host_edges[s], False)
+        return trainer.read_stats()
 
     for s in range(min(args.warmup, 2)):
         step_host(s)
@@ -546,8 +549,8 @@ def run_b200(args, w):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_e2e = float(t)
     e2e = {"value": world * args.steps * step_edges / (ms_e2e / 1e3), "unit": "edges/sec",
-           "h2d_bytes_per_step": (3 if dyn else 2) * 8 * step_edges, "d2h_bytes_per_step": 32 * len(batches) + 4,
-           "last_batch_loss": last[-1].metrics["loss"] if last else None}
+           "h2d_bytes_per_step": (3 if dyn else 2) * 8 * step_edges, "d2h_bytes_per_step": 40,
+           "last_step_loss": last.metrics["loss"] if last is not None else None}
 
     # ---- per-kernel-class timing pass ----------------------------------------------------------
     import ctypes as C

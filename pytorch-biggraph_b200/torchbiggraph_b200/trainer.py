@@ -167,6 +167,7 @@ class B200Trainer(AbstractBatchProcessor):
         self._native_key = None
         self.seed = 0
         self._calls = 0
+        self._batch_arrays = {}
 
     # ---- plumbing ------------------------------------------------------------------------------
     def _state_for(self, table: torch.Tensor) -> torch.Tensor:
@@ -227,9 +228,17 @@ class B200Trainer(AbstractBatchProcessor):
         nw = len(self.relation_weights)
         warr = (C.c_float * nw)(*self.relation_weights)
         bucket = nat.bucket(model, relation_idx, states, warr)
-        barr = (PbgBatch * len(batches))()
-        for i, (o, n, r) in enumerate(batches):
-            barr[i].offset, barr[i].count, barr[i].rel = o, n, r
+        # the descriptor array of a batch list is built once (a trainer is handed the same bucket layout
+        # over and over; filling a few hundred ctypes structs costs more host time than launching a wave)
+        key = tuple(batches)
+        barr = self._batch_arrays.get(key)
+        if barr is None:
+            barr = (PbgBatch * len(batches))()
+            for i, (o, n, r) in enumerate(batches):
+                barr[i].offset, barr[i].count, barr[i].rel = o, n, r
+            if len(self._batch_arrays) > 64:
+                self._batch_arrays.clear()
+            self._batch_arrays[key] = barr
         sarr = (PbgBatchStats * len(batches))() if want_per_batch else None
         on_host = lhs.device.type == "cpu"
         fn = nat.lib.pbg_train_batches_host if on_host else nat.lib.pbg_train_batches
