@@ -589,7 +589,7 @@ def run_b200(args, w):
     traffic = None if per_edge is None else per_edge * edges_prof / dom_kernel_launches
     if dom in model_flops:
         ach = per_class[dom]["TFLOPs"]
-        per_product = {"tf32x3": 6.0, "tf32": 2.0}.get(args.precision)     # TF32 runs at half the bf16 rate; TF32X3 issues three MMAs per product
+        per_product = {"tf32x3": 6.0, "tf32": 2.0, "bf16x6": 6.0}.get(args.precision)     # TF32 runs at half the bf16 rate; TF32X3 issues three MMAs per product, BF16X6 six bf16 ones
         roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
                 "frac": round(ach / pk["tflops"], 4), "traffic": traffic,
                 "ceiling_for_precision": None if per_product is None else round(pk["tflops"] / per_product, 1),
@@ -624,9 +624,10 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--lr", type=float, default=0.1)
     ap.add_argument("--k", type=int, default=14, help="batches in flight (1 = sequential batches, the reference's GPU semantics)")
-    ap.add_argument("--precision", default="tf32x3", choices=["fp32", "tf32x3", "tf32"],
+    ap.add_argument("--precision", default="tf32x3", choices=["fp32", "tf32x3", "tf32", "bf16x6"],
                     help="tf32x3 (default): tcgen05 tensor cores with 3-term split, the rtol 1e-4 tier; fp32: CUDA cores; "
-                         "tf32: single pass, the rtol 1e-3 tier")
+                         "tf32: single pass, the rtol 1e-3 tier; bf16x6: three bf16 planes per operand, six plane products, "
+                         "the rtol 1e-4 tier (workloads without operator, comparator dot)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--resident", type=int, default=0,
                     help="partitions kept on the device at N=1 (0 = all); a small number keeps profiler captures small")

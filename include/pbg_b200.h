@@ -55,7 +55,12 @@ typedef enum {
   PBG_PREC_FP32 = 0,     /* fp32 FMA on the CUDA cores; the rtol 1e-4 tier                    */
   PBG_PREC_TF32X3 = 1,   /* tcgen05 TF32 tensor cores, 3-term error-compensated split, fp32
                             accumulation in tensor memory; the rtol 1e-4 tier                 */
-  PBG_PREC_TF32 = 2      /* tcgen05 TF32 tensor cores, single pass; the rtol 1e-3 tier        */
+  PBG_PREC_TF32 = 2,     /* tcgen05 TF32 tensor cores, single pass; the rtol 1e-3 tier        */
+  PBG_PREC_BF16X6 = 3    /* tcgen05 bf16 tensor cores on three bf16 planes per fp32 operand
+                            (x = b0 + b1 + b2, 24 mantissa bits), the six plane products of
+                            order <= 2, fp32 accumulation in tensor memory; the rtol 1e-4 tier.
+                            Only for standard relations without operator, comparator dot,
+                            no max_norm and no regularizer: pbg_create refuses the rest       */
 } pbg_precision;
 
 /* The keys of ConfigSchema (torchbiggraph/config.py:158-230, 318-359, 411-425) that the

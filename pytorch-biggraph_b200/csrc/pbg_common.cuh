@@ -22,6 +22,7 @@
 // otherwise unused) diagonal, so the two products above are the whole backward of the
 // comparator.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "../../include/pbg_b200.h"
@@ -77,6 +78,12 @@ struct WaveBufs {
   //   A[1][m][j] = (j < Pm ? T1[j][m] : 0) + (m < Pm ? T0[m][j] : 0)   gradient of the rhs rows  = A[1] . N0
   float *A[2], *AL[2];
   int Ma;                            // row stride of A (Mm rounded up to 4)
+  // bf16-plane tier: every fp32 operand value as three bf16 planes b0 + b1 + b2 (b0 = bf16(x), b1 =
+  // bf16(x - b0), b2 = bf16(x - b0 - b1)); the contractions read these instead of X / A
+  //   XB[side]  [nblk][3][Mm][Dpb]   planes of the operand rows N0 / N1
+  //   AB[side]  [nblk][3][Mm][Kb]    planes of the coefficient matrices
+  unsigned short *XB[2], *AB[2];     // null outside that tier
+  int Dpb, Kb;                       // row strides in elements (D and Mm rounded up to 8: 16-byte rows)
   float *spos[2];                    // positive scores [nblk][Pm]
   float *coef[4];                    // l2: colsum(T0), colsum(T1), rowsum(T0), rowsum(T1)
   float *lossrow[2];                 // per positive row: weighted loss term
@@ -226,6 +233,23 @@ __device__ __forceinline__ float4 tf32_hi4(float4 v) { return make_float4(tf32_h
 // The same rounding with two integer instructions (add half an ulp of the 10-bit mantissa, clear the
 // low 13 bits): cvt runs at a fraction of the ALU rate, which is what bounds a kernel that splits
 // whole operand tiles.  Differs from cvt only on NaN payloads and when rounding carries into Inf.
+// The three bf16 planes of x (round to nearest each time; the remainders are exact in fp32):
+// float(b0) + float(b1) + float(b2) == x to 24 mantissa bits.
+__device__ __forceinline__ void bf16_planes(float x, unsigned &b0, unsigned &b1, unsigned &b2) {
+  __nv_bfloat16 h0 = __float2bfloat16_rn(x);
+  float r = x - __bfloat162float(h0);
+  __nv_bfloat16 h1 = __float2bfloat16_rn(r);
+  r -= __bfloat162float(h1);
+  b0 = __bfloat16_as_ushort(h0); b1 = __bfloat16_as_ushort(h1); b2 = __bfloat16_as_ushort(__float2bfloat16_rn(r));
+}
+// planes of four consecutive values, packed for one 8-byte store per plane
+__device__ __forceinline__ void bf16_planes4(float4 v, uint2 &p0, uint2 &p1, uint2 &p2) {
+  unsigned a0, a1, a2, b0, b1, b2, c0, c1, c2, d0, d1, d2;
+  bf16_planes(v.x, a0, a1, a2); bf16_planes(v.y, b0, b1, b2); bf16_planes(v.z, c0, c1, c2); bf16_planes(v.w, d0, d1, d2);
+  p0 = make_uint2(a0 | (b0 << 16), c0 | (d0 << 16));
+  p1 = make_uint2(a1 | (b1 << 16), c1 | (d1 << 16));
+  p2 = make_uint2(a2 | (b2 << 16), c2 | (d2 << 16));
+}
 __device__ __forceinline__ float tf32_round(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
 __device__ __forceinline__ float4 tf32_round4(float4 v) { return make_float4(tf32_round(v.x), tf32_round(v.y), tf32_round(v.z), tf32_round(v.w)); }
 

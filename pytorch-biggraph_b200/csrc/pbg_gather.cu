@@ -281,7 +281,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
 // dot product.  Both rows of a slot (lhs side, rhs side) are loaded at once, which doubles the bytes
 // a warp keeps in flight, and the kernel carries none of the operator / prepare code of the general
 // one (half the registers, three CTAs per SM instead of two).
-template <int VEC>
+template <int VEC, bool PL>
 __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 16 ? 1 : VEC >= 8 ? 3 : 4) gather_plain_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
   int lane = threadIdx.x & 31;
   long long item = (long long)blockIdx.x * GATHER_WARPS + (threadIdx.x >> 5);
@@ -323,8 +323,25 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 16 ? 1 : VEC >= 8 ? 
   }
   if (i0 >= 0) add_global<VEC>(a, w.glob[0], D, lane);       // padding rows stay exact zeros
   if (i1 >= 0) add_global<VEC>(b, w.glob[1], D, lane);
-  store_row<VEC>(n0, a, D, lane);
-  store_row<VEC>(n1, b, D, lane);
+  if (PL) {
+    // bf16-plane tier: the contractions read the planes, nothing reads the fp32 operand rows
+    const size_t plane = (size_t)d.Mm * w.Dpb;
+    unsigned short *x0 = w.XB[0] + ((size_t)blk * 3 * d.Mm + r) * w.Dpb, *x1 = w.XB[1] + ((size_t)blk * 3 * d.Mm + r) * w.Dpb;
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) {
+      int dd = c * 128 + lane * 4;
+      if (dd < D) {
+        uint2 p0, p1, p2;
+        bf16_planes4(a[c], p0, p1, p2);
+        *(uint2 *)(x0 + dd) = p0; *(uint2 *)(x0 + plane + dd) = p1; *(uint2 *)(x0 + 2 * plane + dd) = p2;
+        bf16_planes4(b[c], p0, p1, p2);
+        *(uint2 *)(x1 + dd) = p0; *(uint2 *)(x1 + plane + dd) = p1; *(uint2 *)(x1 + 2 * plane + dd) = p2;
+      }
+    }
+  } else {
+    store_row<VEC>(n0, a, D, lane);
+    store_row<VEC>(n1, b, D, lane);
+  }
   float s = 0.f;
   if (edge) {
 #pragma unroll
@@ -402,12 +419,20 @@ int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, c
   int ctas = (int)((items + GATHER_WARPS - 1) / GATHER_WARPS);
   int vec = (d.D + 127) / 128;
   const bool plain = !d.dynamic && !d.matrix_op && !d.split && d.max_norm <= 0.f && d.cmp == PBG_CMP_DOT && (d.op == PBG_OP_NONE || w.theta[0] == nullptr);
+  if (plain && w.XB[0]) {
+    if (vec <= 1) gather_plain_kernel<1, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 2) gather_plain_kernel<2, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 4) gather_plain_kernel<4, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 8) gather_plain_kernel<8, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else gather_plain_kernel<16, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    return 1;
+  }
   if (plain) {
-    if (vec <= 1) gather_plain_kernel<1><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
-    else if (vec <= 2) gather_plain_kernel<2><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
-    else if (vec <= 4) gather_plain_kernel<4><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
-    else if (vec <= 8) gather_plain_kernel<8><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
-    else gather_plain_kernel<16><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    if (vec <= 1) gather_plain_kernel<1, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 2) gather_plain_kernel<2, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 4) gather_plain_kernel<4, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 8) gather_plain_kernel<8, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else gather_plain_kernel<16, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
     return 1;
   }
   if (vec <= 1) gather_kernel<1><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);

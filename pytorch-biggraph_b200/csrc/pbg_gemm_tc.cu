@@ -53,6 +53,7 @@ struct TcGeom {
   const float *auxA[2]; long long auxa_blk;   // score epilogue (l2 family): |a|^2, |b|^2
   const float *auxB[2]; long long auxb_blk;
   int cmp, score;
+  int nst, stage_bytes;  // bf16-plane tier: stages in flight and bytes of one (three planes of A and of the B tile)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -73,6 +74,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
                :: "r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+               :: "r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
+}
+
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
   return ((uint64_t)((addr >> 4) & 0x3FFF)) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
          ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
@@ -82,30 +88,39 @@ template <bool A_MN, bool B_MN, int NTERMS, bool L2EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBatches wb, int *errflag) {
   constexpr bool SPLIT = NTERMS == 3;
+  // NTERMS == 6: the operands arrive as three bf16 planes each (x = b0 + b1 + b2, written by the producers);
+  // a product is the six plane pairs of order <= 2 as kind::f16 MMAs -- no split in this kernel, and the
+  // operand bytes the MMAs read from shared memory are half those of tf32
+  constexpr bool PLANES = NTERMS == 6;
+  static_assert(!PLANES || (TC_KB == 32 && !A_MN), "bf16 planes: 32 k-values per stage, A K-major");
   constexpr int KB = TC_KB;
-  constexpr int STAGES = (SPLIT ? 2 : 4) * (32 / KB);
-  constexpr uint32_t ROW_BYTES = KB * 4;                                 // bytes of one K-major row of a stage
-  constexpr uint32_t BOX_BYTES = KB * 128;                               // one 32 x KB MN-major box
-  constexpr uint32_t A_BYTES = 128 * ROW_BYTES, B_BYTES = 256 * ROW_BYTES;   // one KB-k tile of 128 / 256 rows
+  constexpr int SMAX = PLANES ? 4 : (SPLIT ? 2 : 4) * (32 / KB);      // stages (bf16 planes: as many as fit, at most 4)
+  constexpr uint32_t ROW_BYTES = PLANES ? KB * 2 : KB * 4;               // bytes of one K-major row of a stage
+  constexpr uint32_t BOX_BYTES = PLANES ? 4096 : KB * 128;               // one MN-major box: 64 x 32 bf16 or 32 x KB fp32
+  constexpr uint32_t A_PLANE = 128 * ROW_BYTES, B_PLANE = 256 * ROW_BYTES;
+  constexpr uint32_t A_BYTES = PLANES ? 3 * A_PLANE : A_PLANE, B_BYTES = PLANES ? 3 * B_PLANE : B_PLANE;   // one KB-k tile of 128 / 256 rows
   constexpr uint32_t RAW_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t STAGE_BYTES = SPLIT ? 2 * RAW_BYTES : RAW_BYTES;   // [A hi][B hi] ([A lo][B lo])
+  constexpr uint32_t STAGE_BYTES = SPLIT ? 2 * RAW_BYTES : RAW_BYTES;   // [A hi][B hi] ([A lo][B lo]) or [A planes][B planes]
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  unsigned char *ostage = smem + (size_t)STAGES * STAGE_BYTES;          // [4 warps][2][32 rows x 128 B], epilogue staging
-  __shared__ __align__(8) unsigned long long bars[3 * STAGES + 4];
+  // the plane tier sizes its stages by the tile's real width, and takes as many of them as fit
+  const int STAGES = PLANES ? g.nst : SMAX;
+  const uint32_t stage_bytes = PLANES ? (uint32_t)g.stage_bytes : STAGE_BYTES;
+  unsigned char *ostage = smem + (size_t)STAGES * stage_bytes;          // [4 warps][2][32 rows x 128 B], epilogue staging
+  __shared__ __align__(8) unsigned long long bars[3 * SMAX + 4];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int failed;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };                 // TMA landed
-  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };     // MMAs have read the stage
-  auto conv_bar = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };  // hi / lo written (SPLIT)
-  auto accf_bar = [&](int a) { return bar0 + 8u * (3 * STAGES + a); };      // accumulator a complete
-  auto acce_bar = [&](int a) { return bar0 + 8u * (3 * STAGES + 2 + a); };  // accumulator a drained
+  auto empty_bar = [&](int s) { return bar0 + 8u * (SMAX + s); };     // MMAs have read the stage
+  auto conv_bar = [&](int s) { return bar0 + 8u * (2 * SMAX + s); };  // hi / lo written (SPLIT)
+  auto accf_bar = [&](int a) { return bar0 + 8u * (3 * SMAX + a); };      // accumulator a complete
+  auto acce_bar = [&](int a) { return bar0 + 8u * (3 * SMAX + 2 + a); };  // accumulator a drained
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2 * STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar0 + 8u * i));
-    for (int i = 0; i < STAGES; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(conv_bar(i)), "r"(TC_SPLIT_THREADS));
+    for (int i = 0; i < 2 * SMAX; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar0 + 8u * i));
+    for (int i = 0; i < SMAX; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(conv_bar(i)), "r"(TC_SPLIT_THREADS));
     for (int a = 0; a < 2; ++a) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(accf_bar(a)));
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" :: "r"(acce_bar(a)));
@@ -122,8 +137,9 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = tmem_base_s;
   const int nkb = (g.K + KB - 1) / KB;
-  const int b_atoms = (g.BN + 31) / 32;
-  const uint32_t b_used = B_MN ? (uint32_t)b_atoms * BOX_BYTES : (uint32_t)g.BN * ROW_BYTES;
+  const int b_atoms = PLANES ? (g.BN + 63) / 64 : (g.BN + 31) / 32;     // MN-major boxes per B tile (per plane)
+  const uint32_t b_plane = B_MN ? (uint32_t)b_atoms * BOX_BYTES : (uint32_t)g.BN * ROW_BYTES;   // bytes of one B tile (plane)
+  const uint32_t b_used = PLANES ? 3u * b_plane : b_plane;
   const uint32_t stage_tx = A_BYTES + b_used;
   // persistent tile loop: tile t -> (n tile, m tile, chunk block, problem); every role walks the same list
   const int tiles_n = (g.N + g.BN - 1) / g.BN, tiles_m = (g.M + 127) / 128;
@@ -143,7 +159,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
     // Issuing one cp.async.bulk.tensor costs the issuing thread a few hundred cycles; an MN-major
     // B tile is up to eight 32 x 32 boxes, which issued from one lane made the producer the
     // longest link of the stage's chain.
-    const int a_boxes = A_MN ? 4 : 1, b_boxes = B_MN ? b_atoms : 1;
+    const int a_boxes = PLANES ? 3 : (A_MN ? 4 : 1), b_boxes = PLANES ? 3 * (B_MN ? b_atoms : 1) : (B_MN ? b_atoms : 1);
     long long git = 0;
     bool stop = false;
     for (long long t = blockIdx.x; t < ntiles && !stop; t += gridDim.x) {
@@ -158,10 +174,17 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         uint32_t fb = full_bar(s);
         if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(fb), "r"(stage_tx) : "memory");
         __syncwarp();
-        unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+        unsigned char *st = smem + (size_t)s * stage_bytes;
         int k0 = kb * KB;
         uint32_t dA = smem_u32(st), dB = smem_u32(st + A_BYTES);
-        if (lane < a_boxes) {
+        if (PLANES) {
+          if (lane < 3) tma_load_4d(dA + lane * A_PLANE, &maps.a[p], k0, m0, lane, blk, fb);
+          else if (lane < a_boxes + b_boxes) {
+            int ib = lane - 3;
+            if (!B_MN) tma_load_4d(dB + ib * b_plane, &maps.b[p], k0, n0, ib, blk, fb);
+            else { int pl = ib / b_atoms, nb = ib - pl * b_atoms; tma_load_4d(dB + pl * b_plane + nb * BOX_BYTES, &maps.b[p], n0 + nb * 64, k0, pl, blk, fb); }
+          }
+        } else if (lane < a_boxes) {
           if (!A_MN) tma_load_3d(dA, &maps.a[p], k0, m0, blk, fb);
           else tma_load_3d(dA + lane * BOX_BYTES, &maps.a[p], m0 + lane * 32, k0, blk, fb);
         } else if (lane < a_boxes + b_boxes) {
@@ -174,7 +197,8 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   } else if (warp == 1 && lane == 0) {
     // ---------------- MMA issuer ----------------
     // instruction descriptor: D fp32, A/B tf32, operand majors, N >> 3, M >> 4
-    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+    const uint32_t fmt = PLANES ? 1u : 2u;            // operand format: bf16 (kind::f16) or tf32
+    const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                            ((uint32_t)(g.BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     long long git = 0, j = 0;
     for (long long t = blockIdx.x; t < ntiles && !failed; t += gridDim.x) {
@@ -189,9 +213,27 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         int s = (int)(git % STAGES);
         if (!mbar_wait(SPLIT ? conv_bar(s) : full_bar(s), (uint32_t)(git / STAGES) & 1, errflag)) { failed = 1; ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+        unsigned char *st = smem + (size_t)s * stage_bytes;
         uint32_t aH = smem_u32(st), bH = smem_u32(st + A_BYTES);
         uint32_t aL = aH + RAW_BYTES, bL = bH + RAW_BYTES;
+        if (PLANES) {
+          // plane pairs (a, b) of order a + b <= 2, the smallest contributions first; K = 16 per MMA:
+          // K-major 64-byte rows (64-byte swizzle: layout 4, 512 bytes per 8 rows, 32 bytes per step),
+          // MN-major 64 x 32 boxes (128-byte swizzle: layout 2, LBO = box, SBO 1024, 2048 bytes per step)
+          const int pa[6] = {2, 0, 1, 1, 0, 0}, pb[6] = {0, 2, 1, 0, 1, 0};
+#pragma unroll
+          for (int k16 = 0; k16 < 2; ++k16) {
+#pragma unroll
+            for (int t = 0; t < 6; ++t) {
+              uint64_t da = smem_desc(aH + pa[t] * A_PLANE + k16 * 32, 0, 512, 4);
+              uint64_t db = B_MN ? smem_desc(bH + pb[t] * b_plane + k16 * 2048, BOX_BYTES, 1024, 2)
+                                 : smem_desc(bH + pb[t] * b_plane + k16 * 32, 0, 512, 4);
+              uint32_t acc = (kb > 0 || k16 > 0 || t > 0) ? 1u : 0u;
+              asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                           :: "r"(tacc), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+            }
+          }
+        } else
 #pragma unroll
         for (int k8 = 0; k8 < KB / 8; ++k8) {
           constexpr uint32_t KSBO = KB == 32 ? 1024 : 512, KLAY = KB == 32 ? 2 : 4;     // K-major: 8 rows of ROW_BYTES; 128- / 64-byte swizzle
@@ -235,7 +277,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         bool okw = true;
         if (lane == 0) okw = mbar_wait(full_bar(s), (uint32_t)(git / STAGES) & 1, errflag);
         if (!__all_sync(0xffffffffu, okw)) { failed = 1; stop = true; break; }
-        unsigned char *st = smem + (size_t)s * STAGE_BYTES;
+        unsigned char *st = smem + (size_t)s * stage_bytes;
         for (uint32_t c0 = ct; c0 < nchunks; c0 += 4 * TC_SPLIT_THREADS) {
           float4 v[4];
 #pragma unroll
@@ -367,6 +409,22 @@ static bool encode3(CUtensorMap *tm, const float *base, int inner, int rows, int
   return r == CUDA_SUCCESS;
 }
 
+// bf16 plane arrays [nblk][3][rows][ld]: a 4-D map (inner, rows, plane, block).  K-major operands
+// (box_inner = 32 k-values, 64-byte swizzle) or MN-major (box = 64 contiguous x 32 k rows, 128-byte swizzle).
+static bool encode4_planes(CUtensorMap *tm, const unsigned short *base, int inner, int rows, int rows_alloc, int nblk, int ld,
+                           int box_inner, int box_rows) {
+  EncodeFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)rows, 3, (cuuint64_t)nblk};
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 2, (cuuint64_t)rows_alloc * ld * 2, (cuuint64_t)3 * rows_alloc * ld * 2};
+  cuuint32_t box[4] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t es[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, (void *)base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   box_inner * 2 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 struct TcPlan {
   TcMaps score, gradq, gradn, gradm;
   bool dynamic;
@@ -389,10 +447,23 @@ static int tile_cols(int n) {
 void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int precision) {
   TcPlan *pl = new TcPlan();
   pl->dynamic = d.dynamic != 0;
-  pl->nterms = precision == PBG_PREC_TF32X3 ? 3 : 1;
+  pl->nterms = precision == PBG_PREC_TF32X3 ? 3 : precision == PBG_PREC_BF16X6 ? 6 : 1;
   pl->bn_score = tile_cols(d.Mm);
   pl->bn_grad = tile_cols(d.D);
   bool ok = true;
+  if (pl->nterms == 6) {
+    // bf16-plane tier (standard relations): score_p = N_(1-p) rows [0, Pm) . N_p^T; grad of side p = A_p . N_(1-p)
+    for (int p = 0; p < 2; ++p) {
+      ok &= encode4_planes(&pl->score.a[p], w.XB[1 - p], d.D, d.Pm, d.Mm, nblk_max, w.Dpb, 32, 128);
+      ok &= encode4_planes(&pl->score.b[p], w.XB[p], d.D, d.Mm, d.Mm, nblk_max, w.Dpb, 32, pl->bn_score);
+      ok &= encode3(&pl->score.c[p], w.S[p], d.Mm, d.Pm, nblk_max, d.Ms, (long long)d.Pm * d.Ms, 32, 32, false);
+      ok &= encode4_planes(&pl->gradm.a[p], w.AB[p], d.Mm, d.Mm, d.Mm, nblk_max, w.Kb, 32, 128);
+      ok &= encode4_planes(&pl->gradm.b[p], w.XB[1 - p], d.D, d.Mm, d.Mm, nblk_max, w.Dpb, 64, 32);
+      ok &= encode3(&pl->gradm.c[p], w.GX[ARR_N0 + p], d.D, d.Mm, nblk_max, d.Dp, (long long)d.Mm * d.Dp, 32, 32, false);
+    }
+    if (!ok) { delete pl; return nullptr; }
+    return pl;
+  }
   for (int p = 0; p < 2; ++p) {
     int q = ARR_Q0 + p, n = ARR_N0 + p;
     const float *Xq = w.X[q], *Xn = w.X[n], *T = w.S[p];
@@ -430,11 +501,21 @@ template <bool A_MN, bool B_MN, int NTERMS, bool L2EPI>
 static void launch_tc_inst(const TcMaps &maps, const TcGeom &g, const WaveDims &d, const WaveBatches &wb, int *errflag,
                            dim3 grid, size_t smem, cudaStream_t st) {
   static bool done = false;
+  TcGeom gg = g;
+  if (NTERMS == 6) {
+    // three planes of 64-byte rows: A 128 rows; B the tile's rows (K-major) or its 64-column boxes (MN-major)
+    const int b_plane = B_MN ? (g.BN + 63) / 64 * 4096 : g.BN * 64;
+    gg.stage_bytes = 3 * 128 * 64 + 3 * b_plane;
+    const int room = (int)smem - (4 * 2 * 4096 + 1024);            // what the stages get of the kernel's dynamic shared memory
+    gg.nst = room / gg.stage_bytes > 4 ? 4 : room / gg.stage_bytes;
+    smem = (size_t)room + 4 * 2 * 4096 + 1024;
+  }
   if (!done) {
     cudaFuncSetAttribute(tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     done = true;
   }
-  tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI><<<grid, TC_THREADS, smem, st>>>(maps, g, d, wb, errflag);
+  // the plane tier has no split warps: producer, MMA issuer and the four epilogue warps
+  tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI><<<grid, NTERMS == 6 ? 192 : TC_THREADS, smem, st>>>(maps, gg, d, wb, errflag);
 }
 
 template <bool A_MN, bool B_MN>
@@ -453,6 +534,9 @@ static void launch_tc(const TcMaps &maps, const TcGeom &g, int nterms, const Wav
       else launch_tc_inst<A_MN, B_MN, 1, true>(maps, g, d, wb, errflag, grid, smem, st);
       return;
     }
+  }
+  if constexpr (!A_MN) {
+    if (nterms == 6) { launch_tc_inst<A_MN, B_MN, 6, false>(maps, g, d, wb, errflag, grid, smem, st); return; }
   }
   if (nterms == 3) launch_tc_inst<A_MN, B_MN, 3, false>(maps, g, d, wb, errflag, grid, smem, st);
   else launch_tc_inst<A_MN, B_MN, 1, false>(maps, g, d, wb, errflag, grid, smem, st);

@@ -272,6 +272,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_softmax_kernel(WaveDims 
 // 16-byte loads) and keeps them; value r of every lane is then column j0 + l of output row m0 + r,
 // so that both the transposed term and the direct term T_other[m][j] are read and A is written in
 // whole lines without a shuffle or shared memory.
+template <bool PL>
 __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_tile_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
   int lane = threadIdx.x & 31;
   long long item = (long long)blockIdx.x * LOSS_WARPS + (threadIdx.x >> 5);
@@ -296,13 +297,49 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_tile_kernel(WaveDims d, 
   }
   const float *orow = w.S[1 - side] + (size_t)blk * d.Pm * d.Ms;              // T_other[m][j]
   float *A = w.A[side] + (size_t)blk * d.Mm * w.Ma;
+  if (!PL) {
 #pragma unroll
-  for (int r = 0; r < 32; ++r) {
-    int m = m0 + r;
-    if (m < d.Mm && j < w.Ma) {
-      float a = j < d.Mm ? t[r] : 0.f;
+    for (int r = 0; r < 32; ++r) {
+      int m = m0 + r;
+      if (m < d.Mm && j < w.Ma) {
+        float a = j < d.Mm ? t[r] : 0.f;
+        if (m < bi.n && j < d.Mm) a += orow[(size_t)m * d.Ms + j];
+        A[(size_t)m * w.Ma + j] = a;
+      }
+    }
+    return;
+  }
+  // bf16-plane tier: the three planes instead of the fp32 matrix.  Two rows at a time: neighbouring
+  // lanes swap one row's planes, so that every lane stores two columns of one row (4-byte stores):
+  // even lanes the columns (j, j + 1) of row m, odd lanes (j - 1, j) of row m + 1.
+  unsigned short *AB = w.AB[side] + (size_t)blk * 3 * d.Mm * w.Kb;
+  const size_t aplane = (size_t)d.Mm * w.Kb;
+  const bool odd = lane & 1;
+#pragma unroll
+  for (int r = 0; r < 32; r += 2) {
+    unsigned pl[2][3];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int m = m0 + r + h;
+      float a = (m < d.Mm && j < d.Mm) ? t[r + h] : 0.f;
       if (m < bi.n && j < d.Mm) a += orow[(size_t)m * d.Ms + j];
-      A[(size_t)m * w.Ma + j] = a;
+      bf16_planes(a, pl[h][0], pl[h][1], pl[h][2]);
+    }
+    // what the neighbour stores: its row is m for an even neighbour, m + 1 for an odd one
+    unsigned give[3], keep[3];
+#pragma unroll
+    for (int q = 0; q < 3; ++q) { give[q] = odd ? pl[0][q] : pl[1][q]; keep[q] = odd ? pl[1][q] : pl[0][q]; }
+    unsigned g01 = __shfl_xor_sync(0xffffffffu, give[0] | (give[1] << 16), 1);
+    unsigned g2 = __shfl_xor_sync(0xffffffffu, give[2], 1);
+    unsigned got[3] = {g01 & 0xffffu, g01 >> 16, g2};
+    const int m = m0 + r + (odd ? 1 : 0), col = j & ~1;
+    if (m < d.Mm && col < w.Kb) {
+      unsigned short *dst = AB + (size_t)m * w.Kb + col;
+#pragma unroll
+      for (int q = 0; q < 3; ++q) {
+        unsigned lo = odd ? got[q] : keep[q], hi = odd ? keep[q] : got[q];
+        *(unsigned *)(dst + q * aplane) = lo | (hi << 16);
+      }
     }
   }
 }
@@ -320,7 +357,8 @@ int launch_loss(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cud
     if (dotlike) {
       const int tiles = (d.Mm + 31) / 32;
       long long warps = 2ll * d.nblk * tiles * tiles;
-      coef_tile_kernel<<<(int)((warps + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+      if (w.AB[0]) coef_tile_kernel<true><<<(int)((warps + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
+      else coef_tile_kernel<false><<<(int)((warps + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
     } else {
       long long rows = 2ll * d.nblk * d.Mm;
       coef_kernel<<<(int)((rows + LOSS_WARPS - 1) / LOSS_WARPS), 32 * LOSS_WARPS, 0, st>>>(d, wb, w);

@@ -88,6 +88,38 @@ def test_forward_scores_match_reference_fixture(name, precision):
         _close(got, want, rtol=RTOL, atol=3e-5, what=k)
 
 
+def _plane_names():
+    """Fixtures inside the bf16-plane tier: standard relations, no operator, dot, no max_norm, no regularizer."""
+    out = []
+    for n in _names():
+        c = load_step(n)[0]
+        if not c["dyn"] and c["op"] == "none" and c["comp"] == "dot" and not c.get("reg_coef") and not c.get("max_norm"):
+            out.append(n)
+    return out
+
+
+@pytest.mark.parametrize("name", _plane_names())
+def test_step_matches_reference_fixture_bf16_planes(name):
+    """Three bf16 planes per operand, six plane products: the same rtol 1e-4 tier."""
+    test_step_matches_reference_fixture(name, "bf16x6")
+
+
+@pytest.mark.parametrize("name", _plane_names())
+def test_forward_scores_match_reference_fixture_bf16_planes(name):
+    test_forward_scores_match_reference_fixture(name, "bf16x6")
+
+
+def test_bf16_planes_refuse_what_they_do_not_cover():
+    import torchbiggraph_b200 as T
+    from b200_util import Rig
+    c, z = load_step("c2_diag_dyn_cos_softmax" if "c2_diag_dyn_cos_softmax" in step_fixture_names() else
+                     next(n for n in _names() if load_step(n)[0]["op"] != "none"))
+    rig = Rig.from_fixture(c, z, precision="bf16x6")
+    lhs, rhs, rel, ul, ur = batch_of(c, z, 0)
+    with pytest.raises(RuntimeError, match="bf16x6"):
+        rig.trainer.process_one_batch(rig.model, rig.edges(lhs, rhs, rel), ul, ur)
+
+
 @pytest.mark.parametrize("precision", PRECISIONS)
 @pytest.mark.parametrize("name", ["sequence_3_batches", "sequence_3_batches_dyn_cos"])
 def test_wave_of_three_batches_matches_oracle(name, precision):
@@ -183,6 +215,31 @@ def test_baseline_shapes_match_oracle(D, N, B, nb, nu, op, comp, loss, dyn, R, p
         _close(rig.theta("rhs"), ost.theta_rhs, atol=1e-6, what="theta_rhs")
     if ost.theta_lhs is not None:
         _close(rig.theta("lhs"), ost.theta_lhs, atol=1e-6, what="theta_lhs")
+
+
+@pytest.mark.parametrize("D,N,B,nb,nu,loss", [
+    pytest.param(100, 5000, 1000, 50, 50, "ranking", id="C1"),
+    pytest.param(1024, 4000, 1000, 100, 100, "softmax", id="C3"),
+    pytest.param(400, 3000, 1500, 500, 260, "softmax", id="three-column-tiles"),     # Mm 760: three score tiles; D 400: two gradient tiles
+    pytest.param(36, 3000, 600, 300, 37, "logistic", id="ragged-edges"),              # D and Mm off every tile and 8-element boundary
+])
+def test_bf16_planes_at_baseline_shapes(D, N, B, nb, nu, loss):
+    test_baseline_shapes_match_oracle(D, N, B, nb, nu, "none", "dot", loss, False, 1, "bf16x6")
+
+
+def test_bf16_planes_wave_of_eight_with_hub_rows():
+    from b200_util import Rig
+    c, ocfg, ost, batches = _random_case(5, 64, 300, 200, 50, 50, "none", "dot", "softmax", nbatches=8, zipf=True)
+    rig = Rig.from_oracle_state(c, ost, k=8, precision="bf16x6")
+    O.train_wave(ocfg, ost, batches)
+    nat = rig.trainer._context(rig.model, 200)
+    lhs = torch.tensor(np.concatenate([b[0] for b in batches])).cuda()
+    rhs = torch.tensor(np.concatenate([b[1] for b in batches])).cuda()
+    ul = torch.stack([nat._uniform(b[3], "cuda") for b in batches]).contiguous()
+    ur = torch.stack([nat._uniform(b[4], "cuda") for b in batches]).contiguous()
+    rig.trainer.train_batches(rig.model, lhs, rhs, None, [(i * 200, 200, 0) for i in range(8)], ul, ur)
+    _close(rig.W_lhs.cpu().numpy(), ost.W_lhs, atol=1e-6, what="W")
+    _close(rig.G("lhs"), ost.G_lhs, atol=1e-8, what="G")
 
 
 @pytest.mark.parametrize("precision", PRECISIONS)
