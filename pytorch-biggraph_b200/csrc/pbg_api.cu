@@ -144,9 +144,8 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     return fail(c, PBG_ERR_UNSUPPORTED, "tensor-core precision tiers are not built into this library");
   if (cfg->precision < PBG_PREC_FP32 || cfg->precision > PBG_PREC_BF16X6) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown precision %d", cfg->precision);
   const bool planes = cfg->precision == PBG_PREC_BF16X6;
-  if (planes && (cfg->dynamic_relations || cfg->op != PBG_OP_NONE || cfg->comparator != PBG_CMP_DOT || cfg->max_norm > 0.f ||
-                 cfg->regularization_coef != 0.f))
-    return fail(c, PBG_ERR_UNSUPPORTED, "precision bf16x6 covers standard relations without operator, comparator dot, no max_norm, no regularizer; use tf32x3 for the rest");
+  if (planes && matrix_op)
+    return fail(c, PBG_ERR_UNSUPPORTED, "precision bf16x6 does not cover the linear / affine operators; use tf32x3");
   if (chunk_geometry(*cfg, &c->Pm, &c->Cm) != PBG_OK)
     return fail(c, PBG_ERR_BAD_ARGUMENT, "num_batch_negs and num_uniform_negs are both 0: no chunk size (model.py:648-656)");
 
@@ -198,9 +197,12 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     }
   }
   const int Dpb = (cfg->dim + 7) / 8 * 8, Kb = (c->Mm + 7) / 8 * 8;
-  size_t oXB[2] = {0, 0}, oAB[2] = {0, 0};
-  if (planes)
-    for (int s2 = 0; s2 < 2; ++s2) { oXB[s2] = take(nN * 3 * Dpb * 2); oAB[s2] = take(nN * 3 * Kb * 2); }
+  size_t oXB[4] = {0, 0, 0, 0}, oAB[2] = {0, 0}, oTB[2] = {0, 0};
+  if (planes) {
+    oXB[0] = take(nN * 3 * Dpb * 2); oXB[1] = take(nN * 3 * Dpb * 2);
+    if (dyn) { oXB[2] = take(nQ * 3 * Dpb * 2); oXB[3] = take(nQ * 3 * Dpb * 2); oTB[0] = take(nQ * 3 * Kb * 2); oTB[1] = take(nQ * 3 * Kb * 2); }
+    else { oXB[2] = oXB[1]; oXB[3] = oXB[0]; oAB[0] = take(nN * 3 * Kb * 2); oAB[1] = take(nN * 3 * Kb * 2); }
+  }
   for (int p = 0; p < 2; ++p) {
     oS[p] = take(nQ * c->Ms * 4); oSpos[p] = take(nQ * 4); oLoss[p] = take(nQ * 4); oViol[p] = take(nQ * 4);
     if (p == 0) { oReg = take(nQ * 4); oRscale = take(nN * 4); }
@@ -239,9 +241,10 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   }
   b.Ma = Ma;
   b.Dpb = Dpb; b.Kb = Kb;
+  for (int a = 0; a < 4; ++a) b.XB[a] = planes ? (unsigned short *)(c->ws + oXB[a]) : nullptr;
   for (int p = 0; p < 2; ++p) {
-    b.XB[p] = planes ? (unsigned short *)(c->ws + oXB[p]) : nullptr;
-    b.AB[p] = planes ? (unsigned short *)(c->ws + oAB[p]) : nullptr;
+    b.AB[p] = (planes && !dyn) ? (unsigned short *)(c->ws + oAB[p]) : nullptr;
+    b.TB[p] = (planes && dyn) ? (unsigned short *)(c->ws + oTB[p]) : nullptr;
   }
   b.xrows[0] = b.xrows[1] = c->Mm;
   b.xrows[2] = b.xrows[3] = dyn ? c->Pm : c->Mm;

@@ -80,9 +80,10 @@ struct WaveBufs {
   int Ma;                            // row stride of A (Mm rounded up to 4)
   // bf16-plane tier: every fp32 operand value as three bf16 planes b0 + b1 + b2 (b0 = bf16(x), b1 =
   // bf16(x - b0), b2 = bf16(x - b0 - b1)); the contractions read these instead of X / A
-  //   XB[side]  [nblk][3][Mm][Dpb]   planes of the operand rows N0 / N1
-  //   AB[side]  [nblk][3][Mm][Kb]    planes of the coefficient matrices
-  unsigned short *XB[2], *AB[2];     // null outside that tier
+  //   XB[a]     [nblk][3][xrows[a]][Dpb]   planes of the operand rows N0, N1, Q0, Q1 (aliased like X)
+  //   AB[side]  [nblk][3][Mm][Kb]          planes of the merged coefficient matrices (standard relations)
+  //   TB[p]     [nblk][3][Pm][Kb]          planes of the coefficient matrices T_p (dynamic relations)
+  unsigned short *XB[4], *AB[2], *TB[2];     // null outside that tier
   int Dpb, Kb;                       // row strides in elements (D and Mm rounded up to 8: 16-byte rows)
   float *spos[2];                    // positive scores [nblk][Pm]
   float *coef[4];                    // l2: colsum(T0), colsum(T1), rowsum(T0), rowsum(T1)
@@ -249,6 +250,12 @@ __device__ __forceinline__ void bf16_planes4(float4 v, uint2 &p0, uint2 &p1, uin
   p0 = make_uint2(a0 | (b0 << 16), c0 | (d0 << 16));
   p1 = make_uint2(a1 | (b1 << 16), c1 | (d1 << 16));
   p2 = make_uint2(a2 | (b2 << 16), c2 | (d2 << 16));
+}
+// one value's planes into a plane array: p0 at dst, the others one / two plane strides further
+__device__ __forceinline__ void put_planes1(unsigned short *dst, size_t plane, float v) {
+  unsigned b0, b1, b2;
+  bf16_planes(v, b0, b1, b2);
+  dst[0] = (unsigned short)b0; dst[plane] = (unsigned short)b1; dst[2 * plane] = (unsigned short)b2;
 }
 __device__ __forceinline__ float tf32_round(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
 __device__ __forceinline__ float4 tf32_round4(float4 v) { return make_float4(tf32_round(v.x), tf32_round(v.y), tf32_round(v.z), tf32_round(v.w)); }

@@ -73,6 +73,31 @@ __device__ __forceinline__ void put_row(float *base, float *base_lo, size_t off,
   if (base_lo) store_row_split<VEC>(base + off, base_lo + off, v, D, lane);
   else store_row<VEC>(base + off, v, D, lane);
 }
+// bf16-plane tier: the three planes of operand row r of block blk in array a
+template <int VEC>
+__device__ __forceinline__ void put_row_planes(const WaveBufs &w, int a, int blk, int r, const float4 (&v)[VEC], int D, int lane) {
+  const size_t plane = (size_t)w.xrows[a] * w.Dpb;
+  unsigned short *x = w.XB[a] + ((size_t)blk * 3 * w.xrows[a] + r) * w.Dpb;
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int dd = c * 128 + lane * 4;
+    if (dd < D) {
+      uint2 p0, p1, p2;
+      bf16_planes4(v[c], p0, p1, p2);
+      *(uint2 *)(x + dd) = p0; *(uint2 *)(x + plane + dd) = p1; *(uint2 *)(x + 2 * plane + dd) = p2;
+    }
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void zero_row_planes(const WaveBufs &w, int a, int blk, int r, int D, int lane) {
+  const size_t plane = (size_t)w.xrows[a] * w.Dpb;
+  unsigned short *x = w.XB[a] + ((size_t)blk * 3 * w.xrows[a] + r) * w.Dpb;
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int dd = c * 128 + lane * 4;
+    if (dd < D) { *(uint2 *)(x + dd) = make_uint2(0, 0); *(uint2 *)(x + plane + dd) = make_uint2(0, 0); *(uint2 *)(x + 2 * plane + dd) = make_uint2(0, 0); }
+  }
+}
 template <int VEC>
 __device__ __forceinline__ void zero_row(float *row, int D, int lane) {
 #pragma unroll
@@ -136,7 +161,7 @@ __device__ __forceinline__ float positive_score(const float4 (&a)[VEC], const fl
   return cmp == PBG_CMP_L2 ? -sqrtf(fmaxf(s, 1e-30f)) : -s;
 }
 
-template <int VEC>
+template <int VEC, bool PL>
 __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
   int lane = threadIdx.x & 31;
   long long item = (long long)blockIdx.x * GATHER_WARPS + (threadIdx.x >> 5);
@@ -174,6 +199,10 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
       zero_row<VEC>(n1, D, lane);
       if (d.matrix_op) zero_row<VEC>(w.R1 + noff, D, lane);
       if (d.dynamic) { zero_row<VEC>(q0, D, lane); zero_row<VEC>(q1, D, lane); }
+      if (PL) {
+        zero_row_planes<VEC>(w, ARR_N0, blk, r, D, lane); zero_row_planes<VEC>(w, ARR_N1, blk, r, D, lane);
+        if (d.dynamic) { zero_row_planes<VEC>(w, ARR_Q0, blk, r, D, lane); zero_row_planes<VEC>(w, ARR_Q1, blk, r, D, lane); }
+      }
       if (XL) {
         zero_row<VEC>(XL[ARR_N0] + noff, D, lane);
         zero_row<VEC>(XL[ARR_N1] + noff, D, lane);
@@ -196,6 +225,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     for (int c = 0; c < VEC; ++c) y0[c] = x[c];
     float a0 = prepare_row<VEC>(y0, d.cmp);
     put_row<VEC>(w.X[ARR_N0], lo(ARR_N0), noff, y0, D, lane);
+    if (PL) put_row_planes<VEC>(w, ARR_N0, blk, r, y0, D, lane);
     if (d.matrix_op) {
       // linear / affine: the raw rhs row goes to R1; operator, prepare and the positive score
       // follow in the contraction and postop_kernel
@@ -213,6 +243,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
       apply_operator<VEC>(y1, x, xr, th0, d.op, D, lane, w.glob[1], scr);
       float a1 = prepare_row<VEC>(y1, d.cmp);
       put_row<VEC>(w.X[ARR_N1], lo(ARR_N1), noff, y1, D, lane);
+      if (PL) put_row_planes<VEC>(w, ARR_N1, blk, r, y1, D, lane);
       float s = positive_score<VEC>(y0, y1, d.cmp);
       if (lane == 0) {
         w.aux[ARR_N0][nrow] = a0; w.aux[ARR_N1][nrow] = a1;
@@ -224,6 +255,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
       apply_operator<VEC>(z, x, xl, th1, d.op, D, lane, nullptr, scl);
       float aq1 = prepare_row<VEC>(z, d.cmp);
       put_row<VEC>(w.X[ARR_Q1], lo(ARR_Q1), qoff, z, D, lane);
+      if (PL) put_row_planes<VEC>(w, ARR_Q1, blk, r, z, D, lane);
       // rhs row without operator -> N1
       load_row<VEC>(x, xr, D, lane);
       const float scr = renorm_row<VEC>(x, d.max_norm);
@@ -231,11 +263,13 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
       for (int c = 0; c < VEC; ++c) y1[c] = x[c];
       float a1 = prepare_row<VEC>(y1, d.cmp);
       put_row<VEC>(w.X[ARR_N1], lo(ARR_N1), noff, y1, D, lane);
+      if (PL) put_row_planes<VEC>(w, ARR_N1, blk, r, y1, D, lane);
       float s1 = positive_score<VEC>(y1, z, d.cmp);         // problem 1: c(rhs, op_lhs(lhs))
       // op_rhs(rhs row) -> Q0
       apply_operator<VEC>(z, x, xr, th0, d.op, D, lane, nullptr, scr);
       float aq0 = prepare_row<VEC>(z, d.cmp);
       put_row<VEC>(w.X[ARR_Q0], lo(ARR_Q0), qoff, z, D, lane);
+      if (PL) put_row_planes<VEC>(w, ARR_Q0, blk, r, z, D, lane);
       float s0 = positive_score<VEC>(y0, z, d.cmp);         // problem 0: c(lhs, op_rhs(rhs))
       if (lane == 0) {
         w.aux[ARR_N0][nrow] = a0; w.aux[ARR_N1][nrow] = a1;
@@ -253,6 +287,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     if (id >= d.n_rows[side]) { if (lane == 0) atomicOr(w.errflag, 1); id = -1; }
     if (id < 0) {
       zero_row<VEC>(dst, D, lane);
+      if (PL) zero_row_planes<VEC>(w, side, blk, r, D, lane);
       if (XL) zero_row<VEC>(XL[side] + noff, D, lane);
       if (side == 1 && d.matrix_op) zero_row<VEC>(w.R1 + noff, D, lane);
       if (lane == 0) w.aux[side][nrow] = 0.f;
@@ -272,6 +307,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     apply_operator<VEC>(z, x, xrow, th, d.op, D, lane, w.glob[side], scu);
     float a = prepare_row<VEC>(z, d.cmp);
     put_row<VEC>(w.X[side], lo(side), noff, z, D, lane);
+    if (PL) put_row_planes<VEC>(w, side, blk, r, z, D, lane);
     if (lane == 0) w.aux[side][nrow] = a;
   }
 }
@@ -419,7 +455,7 @@ int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, c
   int ctas = (int)((items + GATHER_WARPS - 1) / GATHER_WARPS);
   int vec = (d.D + 127) / 128;
   const bool plain = !d.dynamic && !d.matrix_op && !d.split && d.max_norm <= 0.f && d.cmp == PBG_CMP_DOT && (d.op == PBG_OP_NONE || w.theta[0] == nullptr);
-  if (plain && w.XB[0]) {
+  if (plain && w.XB[0] && d.reg_coef == 0.f) {      // planes only: nothing reads the fp32 operand rows then
     if (vec <= 1) gather_plain_kernel<1, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
     else if (vec <= 2) gather_plain_kernel<2, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
     else if (vec <= 4) gather_plain_kernel<4, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
@@ -427,7 +463,7 @@ int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, c
     else gather_plain_kernel<16, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
     return 1;
   }
-  if (plain) {
+  if (plain && !w.XB[0]) {
     if (vec <= 1) gather_plain_kernel<1, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
     else if (vec <= 2) gather_plain_kernel<2, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
     else if (vec <= 4) gather_plain_kernel<4, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
@@ -435,11 +471,19 @@ int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, c
     else gather_plain_kernel<16, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
     return 1;
   }
-  if (vec <= 1) gather_kernel<1><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
-  else if (vec <= 2) gather_kernel<2><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
-  else if (vec <= 4) gather_kernel<4><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
-  else if (vec <= 8) gather_kernel<8><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
-  else gather_kernel<16><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  if (w.XB[0]) {
+    if (vec <= 1) gather_kernel<1, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 2) gather_kernel<2, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 4) gather_kernel<4, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else if (vec <= 8) gather_kernel<8, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    else gather_kernel<16, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+    return 1;
+  }
+  if (vec <= 1) gather_kernel<1, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else if (vec <= 2) gather_kernel<2, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else if (vec <= 4) gather_kernel<4, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else if (vec <= 8) gather_kernel<8, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
+  else gather_kernel<16, false><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
   return 1;
 }
 

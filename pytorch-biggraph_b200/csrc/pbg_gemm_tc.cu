@@ -92,7 +92,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   // a product is the six plane pairs of order <= 2 as kind::f16 MMAs -- no split in this kernel, and the
   // operand bytes the MMAs read from shared memory are half those of tf32
   constexpr bool PLANES = NTERMS == 6;
-  static_assert(!PLANES || (TC_KB == 32 && !A_MN), "bf16 planes: 32 k-values per stage, A K-major");
+  static_assert(!PLANES || TC_KB == 32, "bf16 planes: 32 k-values per stage");
   constexpr int KB = TC_KB;
   constexpr int SMAX = PLANES ? 4 : (SPLIT ? 2 : 4) * (32 / KB);      // stages (bf16 planes: as many as fit, at most 4)
   constexpr uint32_t ROW_BYTES = PLANES ? KB * 2 : KB * 4;               // bytes of one K-major row of a stage
@@ -159,7 +159,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
     // Issuing one cp.async.bulk.tensor costs the issuing thread a few hundred cycles; an MN-major
     // B tile is up to eight 32 x 32 boxes, which issued from one lane made the producer the
     // longest link of the stage's chain.
-    const int a_boxes = PLANES ? 3 : (A_MN ? 4 : 1), b_boxes = PLANES ? 3 * (B_MN ? b_atoms : 1) : (B_MN ? b_atoms : 1);
+    const int a_boxes = PLANES ? (A_MN ? 6 : 3) : (A_MN ? 4 : 1), b_boxes = PLANES ? 3 * (B_MN ? b_atoms : 1) : (B_MN ? b_atoms : 1);
     long long git = 0;
     bool stop = false;
     for (long long t = blockIdx.x; t < ntiles && !stop; t += gridDim.x) {
@@ -178,9 +178,11 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         int k0 = kb * KB;
         uint32_t dA = smem_u32(st), dB = smem_u32(st + A_BYTES);
         if (PLANES) {
-          if (lane < 3) tma_load_4d(dA + lane * A_PLANE, &maps.a[p], k0, m0, lane, blk, fb);
-          else if (lane < a_boxes + b_boxes) {
-            int ib = lane - 3;
+          if (lane < a_boxes) {
+            if (!A_MN) tma_load_4d(dA + lane * A_PLANE, &maps.a[p], k0, m0, lane, blk, fb);
+            else { int pl = lane >> 1, mb = lane & 1; tma_load_4d(dA + pl * A_PLANE + mb * BOX_BYTES, &maps.a[p], m0 + mb * 64, k0, pl, blk, fb); }
+          } else if (lane < a_boxes + b_boxes) {
+            int ib = lane - a_boxes;
             if (!B_MN) tma_load_4d(dB + ib * b_plane, &maps.b[p], k0, n0, ib, blk, fb);
             else { int pl = ib / b_atoms, nb = ib - pl * b_atoms; tma_load_4d(dB + pl * b_plane + nb * BOX_BYTES, &maps.b[p], n0 + nb * 64, k0, pl, blk, fb); }
           }
@@ -225,7 +227,8 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
           for (int k16 = 0; k16 < 2; ++k16) {
 #pragma unroll
             for (int t = 0; t < 6; ++t) {
-              uint64_t da = smem_desc(aH + pa[t] * A_PLANE + k16 * 32, 0, 512, 4);
+              uint64_t da = A_MN ? smem_desc(aH + pa[t] * A_PLANE + k16 * 2048, BOX_BYTES, 1024, 2)
+                                 : smem_desc(aH + pa[t] * A_PLANE + k16 * 32, 0, 512, 4);
               uint64_t db = B_MN ? smem_desc(bH + pb[t] * b_plane + k16 * 2048, BOX_BYTES, 1024, 2)
                                  : smem_desc(bH + pb[t] * b_plane + k16 * 32, 0, 512, 4);
               uint32_t acc = (kb > 0 || k16 > 0 || t > 0) ? 1u : 0u;
@@ -452,14 +455,26 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
   pl->bn_grad = tile_cols(d.D);
   bool ok = true;
   if (pl->nterms == 6) {
-    // bf16-plane tier (standard relations): score_p = N_(1-p) rows [0, Pm) . N_p^T; grad of side p = A_p . N_(1-p)
+    // bf16-plane tier: the same products on the plane arrays (K-major boxes {32 k, rows}, MN-major boxes {64, 32 k})
     for (int p = 0; p < 2; ++p) {
-      ok &= encode4_planes(&pl->score.a[p], w.XB[1 - p], d.D, d.Pm, d.Mm, nblk_max, w.Dpb, 32, 128);
-      ok &= encode4_planes(&pl->score.b[p], w.XB[p], d.D, d.Mm, d.Mm, nblk_max, w.Dpb, 32, pl->bn_score);
+      int q = ARR_Q0 + p, n = ARR_N0 + p;
+      ok &= encode4_planes(&pl->score.a[p], w.XB[q], d.D, d.Pm, w.xrows[q], nblk_max, w.Dpb, 32, 128);
+      ok &= encode4_planes(&pl->score.b[p], w.XB[n], d.D, w.xrows[n], w.xrows[n], nblk_max, w.Dpb, 32, pl->bn_score);
       ok &= encode3(&pl->score.c[p], w.S[p], d.Mm, d.Pm, nblk_max, d.Ms, (long long)d.Pm * d.Ms, 32, 32, false);
-      ok &= encode4_planes(&pl->gradm.a[p], w.AB[p], d.Mm, d.Mm, d.Mm, nblk_max, w.Kb, 32, 128);
-      ok &= encode4_planes(&pl->gradm.b[p], w.XB[1 - p], d.D, d.Mm, d.Mm, nblk_max, w.Dpb, 64, 32);
-      ok &= encode3(&pl->gradm.c[p], w.GX[ARR_N0 + p], d.D, d.Mm, nblk_max, d.Dp, (long long)d.Mm * d.Dp, 32, 32, false);
+      if (pl->dynamic) {
+        // grad Q: A = T (K-major, k = Mm), B = N (MN-major); grad N: A = T^T (MN-major: k rows = Pm), B = Q (MN-major)
+        ok &= encode4_planes(&pl->gradq.a[p], w.TB[p], d.Mm, d.Pm, d.Pm, nblk_max, w.Kb, 32, 128);
+        ok &= encode4_planes(&pl->gradq.b[p], w.XB[n], d.D, w.xrows[n], w.xrows[n], nblk_max, w.Dpb, 64, 32);
+        ok &= encode4_planes(&pl->gradn.a[p], w.TB[p], d.Mm, d.Pm, d.Pm, nblk_max, w.Kb, 64, 32);
+        ok &= encode4_planes(&pl->gradn.b[p], w.XB[q], d.D, w.xrows[q], w.xrows[q], nblk_max, w.Dpb, 64, 32);
+        ok &= encode3(&pl->gradq.c[p], w.GX[q], d.D, d.Pm, nblk_max, d.Dp, (long long)w.grows[q] * d.Dp, 32, 32, false);
+        ok &= encode3(&pl->gradn.c[p], w.GX[n], d.D, d.Mm, nblk_max, d.Dp, (long long)w.grows[n] * d.Dp, 32, 32, false);
+      } else {
+        int o = ARR_N0 + (1 - p);
+        ok &= encode4_planes(&pl->gradm.a[p], w.AB[p], d.Mm, d.Mm, d.Mm, nblk_max, w.Kb, 32, 128);
+        ok &= encode4_planes(&pl->gradm.b[p], w.XB[o], d.D, w.xrows[o], w.xrows[o], nblk_max, w.Dpb, 64, 32);
+        ok &= encode3(&pl->gradm.c[p], w.GX[n], d.D, d.Mm, nblk_max, d.Dp, (long long)d.Mm * d.Dp, 32, 32, false);
+      }
     }
     if (!ok) { delete pl; return nullptr; }
     return pl;
@@ -530,14 +545,13 @@ static void launch_tc(const TcMaps &maps, const TcGeom &g, int nterms, const Wav
   const bool l2 = !A_MN && !B_MN && g.score && g.cmp >= PBG_CMP_L2;
   if constexpr (!A_MN && !B_MN) {
     if (l2) {
-      if (nterms == 3) launch_tc_inst<A_MN, B_MN, 3, true>(maps, g, d, wb, errflag, grid, smem, st);
+      if (nterms == 6) launch_tc_inst<A_MN, B_MN, 6, true>(maps, g, d, wb, errflag, grid, smem, st);
+      else if (nterms == 3) launch_tc_inst<A_MN, B_MN, 3, true>(maps, g, d, wb, errflag, grid, smem, st);
       else launch_tc_inst<A_MN, B_MN, 1, true>(maps, g, d, wb, errflag, grid, smem, st);
       return;
     }
   }
-  if constexpr (!A_MN) {
-    if (nterms == 6) { launch_tc_inst<A_MN, B_MN, 6, false>(maps, g, d, wb, errflag, grid, smem, st); return; }
-  }
+  if (nterms == 6) { launch_tc_inst<A_MN, B_MN, 6, false>(maps, g, d, wb, errflag, grid, smem, st); return; }
   if (nterms == 3) launch_tc_inst<A_MN, B_MN, 3, false>(maps, g, d, wb, errflag, grid, smem, st);
   else launch_tc_inst<A_MN, B_MN, 1, false>(maps, g, d, wb, errflag, grid, smem, st);
 }

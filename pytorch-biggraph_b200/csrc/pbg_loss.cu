@@ -50,9 +50,13 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
   // only with dynamic relations is T itself an MMA operand; otherwise coef_kernel splits A
   float *SLo = (d.split && d.dynamic) ? w.SL[p] + ((size_t)blk * d.Pm + i) * d.Ms : nullptr;
   // coefficient t stored as tf32(t) + remainder when the gradient contractions run as TF32X3
+  // bf16-plane tier with dynamic relations: T is an MMA operand, its planes go beside it
+  unsigned short *TBr = w.TB[p] ? w.TB[p] + ((size_t)blk * 3 * d.Pm + i) * w.Kb : nullptr;
+  const size_t tplane = (size_t)d.Pm * w.Kb;
   auto put = [&](int j, float t) {
     if (SLo) { float h = tf32_hi(t); S[j] = h; SLo[j] = t - h; }
     else S[j] = t;
+    if (TBr) put_planes1(TBr + j, tplane, t);
   };
   size_t prow = (size_t)blk * d.Pm + i;
   const int Mm = d.Mm;
@@ -187,6 +191,8 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_kernel(WaveDims d, WaveB
   float *A = w.A[side] + arow;
   float *AL = d.split ? w.AL[side] + arow : nullptr;
   float rowsum = 0.f;
+  // bf16-plane tier: the planes of the row beside it
+  unsigned short *ABr = w.AB[side] ? w.AB[side] + ((size_t)blk * 3 * d.Mm + m) * w.Kb : nullptr;
   for (int j = lane; j < w.Ma; j += 32) {
     float a = 0.f;
     if (j < d.Mm) {
@@ -196,6 +202,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_kernel(WaveDims d, WaveB
     rowsum += a;
     if (AL) { float h = tf32_hi(a); A[j] = h; AL[j] = a - h; }
     else A[j] = a;
+    if (ABr) put_planes1(ABr + j, (size_t)d.Mm * w.Kb, a);
   }
   if (d.cmp >= PBG_CMP_L2) {
     rowsum = warp_sum(rowsum);
@@ -219,6 +226,9 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_softmax_kernel(WaveDims 
   BlockInfo bi = block_info(d, wb, blk);
   if (bi.n == 0) return;
   float *S = w.S[p] + ((size_t)blk * d.Pm + i) * d.Ms;
+  // bf16-plane tier with dynamic relations: T is an MMA operand, its planes go beside it
+  unsigned short *TBr = w.TB[p] ? w.TB[p] + ((size_t)blk * 3 * d.Pm + i) * w.Kb : nullptr;
+  const size_t tplane = (size_t)d.Pm * w.Kb;
   size_t prow = (size_t)blk * d.Pm + i;
   const int Mm = d.Mm;
   const int enabled = d.neg_enabled[p];
@@ -226,6 +236,10 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_softmax_kernel(WaveDims 
   if (i >= bi.n || Mlog == 0) {                      // padded positive, or no negatives at all: no loss, no gradient
 #pragma unroll
     for (int u = 0; u < NV; ++u) { int j = lane + 32 * u; if (j < d.Ms) S[j] = 0.f; }
+    if (TBr) {
+#pragma unroll
+      for (int u = 0; u < NV; ++u) { int j = lane + 32 * u; if (j < d.Ms) put_planes1(TBr + j, tplane, 0.f); }
+    }
     if (lane == 0) { w.lossrow[p][prow] = 0.f; w.violrow[p][prow] = 0; }
     return;
   }
@@ -263,6 +277,13 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_softmax_kernel(WaveDims 
   for (int u = 0; u < NV; ++u) {
     int j = lane + 32 * u;
     if (j < d.Ms) S[j] = j == i ? tdiag : wr * sv[u] * invZ;
+  }
+  if (TBr) {
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+      int j = lane + 32 * u;
+      if (j < d.Ms) put_planes1(TBr + j, tplane, j == i ? tdiag : wr * sv[u] * invZ);
+    }
   }
   if (lane == 0) { w.lossrow[p][prow] = wr * lossv; w.violrow[p][prow] = viol; }
 }

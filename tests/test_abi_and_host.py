@@ -66,8 +66,8 @@ def test_config_validation_precedes_device_use():
                         max_batch_size=8, batches_in_flight=0)
     assert L.pbg_create(ctypes.byref(k0), 0, None, ctypes.byref(ctx)) == _lib.PBG_ERR_BAD_ARGUMENT
     L.pbg_destroy(ctx)
-    planes = _lib.PbgConfig(dim=16, op=1, comparator=0, loss=1, num_rels=1, num_batch_negs=4, num_uniform_negs=4,
-                            max_batch_size=8, batches_in_flight=1, precision=_lib.PRECISION_CODES["bf16x6"])   # operator: outside the bf16-plane tier
+    planes = _lib.PbgConfig(dim=16, op=4, comparator=0, loss=1, num_rels=1, num_batch_negs=4, num_uniform_negs=4,
+                            max_batch_size=8, batches_in_flight=1, precision=_lib.PRECISION_CODES["bf16x6"])   # matrix operator: outside the bf16-plane tier
     assert L.pbg_create(ctypes.byref(planes), 0, None, ctypes.byref(ctx)) == _lib.PBG_ERR_UNSUPPORTED
     assert b"bf16x6" in L.pbg_last_error(ctx)
     L.pbg_destroy(ctx)

@@ -89,13 +89,8 @@ def test_forward_scores_match_reference_fixture(name, precision):
 
 
 def _plane_names():
-    """Fixtures inside the bf16-plane tier: standard relations, no operator, dot, no max_norm, no regularizer."""
-    out = []
-    for n in _names():
-        c = load_step(n)[0]
-        if not c["dyn"] and c["op"] == "none" and c["comp"] == "dot" and not c.get("reg_coef") and not c.get("max_norm"):
-            out.append(n)
-    return out
+    """Fixtures inside the bf16-plane tier: everything but the linear / affine operators."""
+    return [n for n in _names() if load_step(n)[0]["op"] not in ("linear", "affine")]
 
 
 @pytest.mark.parametrize("name", _plane_names())
@@ -109,11 +104,15 @@ def test_forward_scores_match_reference_fixture_bf16_planes(name):
     test_forward_scores_match_reference_fixture(name, "bf16x6")
 
 
+@pytest.mark.parametrize("name", ["sequence_3_batches", "sequence_3_batches_dyn_cos"])
+def test_wave_of_three_batches_bf16_planes(name):
+    test_wave_of_three_batches_matches_oracle(name, "bf16x6")
+
+
 def test_bf16_planes_refuse_what_they_do_not_cover():
-    import torchbiggraph_b200 as T
     from b200_util import Rig
-    c, z = load_step("c2_diag_dyn_cos_softmax" if "c2_diag_dyn_cos_softmax" in step_fixture_names() else
-                     next(n for n in _names() if load_step(n)[0]["op"] != "none"))
+    name = next(n for n in _names() if load_step(n)[0]["op"] in ("linear", "affine"))
+    c, z = load_step(name)
     rig = Rig.from_fixture(c, z, precision="bf16x6")
     lhs, rhs, rel, ul, ur = batch_of(c, z, 0)
     with pytest.raises(RuntimeError, match="bf16x6"):
@@ -225,6 +224,11 @@ def test_baseline_shapes_match_oracle(D, N, B, nb, nu, op, comp, loss, dyn, R, p
 ])
 def test_bf16_planes_at_baseline_shapes(D, N, B, nb, nu, loss):
     test_baseline_shapes_match_oracle(D, N, B, nb, nu, "none", "dot", loss, False, 1, "bf16x6")
+
+
+@pytest.mark.parametrize("D,N,B,nb,nu,op,comp,loss,dyn,R", BASELINE_SHAPES)
+def test_bf16_planes_at_every_baseline_shape(D, N, B, nb, nu, op, comp, loss, dyn, R):
+    test_baseline_shapes_match_oracle(D, N, B, nb, nu, op, comp, loss, dyn, R, "bf16x6")
 
 
 def test_bf16_planes_wave_of_eight_with_hub_rows():
