@@ -236,10 +236,8 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_softmax_kernel(WaveDims 
   if (i >= bi.n || Mlog == 0) {                      // padded positive, or no negatives at all: no loss, no gradient
 #pragma unroll
     for (int u = 0; u < NV; ++u) { int j = lane + 32 * u; if (j < d.Ms) S[j] = 0.f; }
-    if (TBr) {
-#pragma unroll
-      for (int u = 0; u < NV; ++u) { int j = lane + 32 * u; if (j < d.Ms) put_planes1(TBr + j, tplane, 0.f); }
-    }
+    if (TBr)
+      for (int j = 2 * lane; j < d.Ms; j += 64) { *(unsigned *)(TBr + j) = 0u; *(unsigned *)(TBr + tplane + j) = 0u; *(unsigned *)(TBr + 2 * tplane + j) = 0u; }
     if (lane == 0) { w.lossrow[p][prow] = 0.f; w.violrow[p][prow] = 0; }
     return;
   }
@@ -279,10 +277,28 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_softmax_kernel(WaveDims 
     if (j < d.Ms) S[j] = j == i ? tdiag : wr * sv[u] * invZ;
   }
   if (TBr) {
+    // two column groups at a time: neighbouring lanes swap one group's planes, so that every lane stores
+    // two columns of one group (4-byte stores): even lanes (j, j + 1) of group u, odd lanes (j - 1, j) of u + 1
+    const bool odd = lane & 1;
 #pragma unroll
-    for (int u = 0; u < NV; ++u) {
-      int j = lane + 32 * u;
-      if (j < d.Ms) put_planes1(TBr + j, tplane, j == i ? tdiag : wr * sv[u] * invZ);
+    for (int u = 0; u < NV; u += 2) {
+      const int j0 = lane + 32 * u, j1 = j0 + 32;
+      unsigned a[3], b[3], give[3], keep[3];
+      bf16_planes(j0 == i ? tdiag : wr * sv[u] * invZ, a[0], a[1], a[2]);
+      bf16_planes(j1 == i ? tdiag : wr * sv[u + 1] * invZ, b[0], b[1], b[2]);
+#pragma unroll
+      for (int q = 0; q < 3; ++q) { give[q] = odd ? a[q] : b[q]; keep[q] = odd ? b[q] : a[q]; }
+      unsigned g01 = __shfl_xor_sync(0xffffffffu, give[0] | (give[1] << 16), 1);
+      unsigned g2 = __shfl_xor_sync(0xffffffffu, give[2], 1);
+      unsigned got[3] = {g01 & 0xffffu, g01 >> 16, g2};
+      const int col = (odd ? j1 : j0) & ~1;
+      if (col < d.Ms) {
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+          unsigned lo = odd ? got[q] : keep[q], hi = odd ? keep[q] : got[q];
+          *(unsigned *)(TBr + q * tplane + col) = lo | (hi << 16);
+        }
+      }
     }
   }
   if (lane == 0) { w.lossrow[p][prow] = wr * lossv; w.violrow[p][prow] = viol; }
