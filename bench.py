@@ -627,7 +627,7 @@ def main():
     ap.add_argument("--precision", default="tf32x3", choices=["fp32", "tf32x3", "tf32", "bf16x6"],
                     help="tf32x3 (default): tcgen05 tensor cores with 3-term split, the rtol 1e-4 tier; fp32: CUDA cores; "
                          "tf32: single pass, the rtol 1e-3 tier; bf16x6: three bf16 planes per operand, six plane products, "
-                         "the rtol 1e-4 tier (workloads without operator, comparator dot)")
+                         "the rtol 1e-4 tier")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--resident", type=int, default=0,
                     help="partitions kept on the device at N=1 (0 = all); a small number keeps profiler captures small")

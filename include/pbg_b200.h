@@ -59,8 +59,9 @@ typedef enum {
   PBG_PREC_BF16X6 = 3    /* tcgen05 bf16 tensor cores on three bf16 planes per fp32 operand
                             (x = b0 + b1 + b2, 24 mantissa bits), the six plane products of
                             order <= 2, fp32 accumulation in tensor memory; the rtol 1e-4 tier.
-                            Only for standard relations without operator, comparator dot,
-                            no max_norm and no regularizer: pbg_create refuses the rest       */
+                            Not for the linear / affine operators: pbg_create refuses those.
+                            Pays where the contractions dominate (large chunks, dim >= 400):
+                            the planes are 6 bytes per operand value where fp32 is 4          */
 } pbg_precision;
 
 /* The keys of ConfigSchema (torchbiggraph/config.py:158-230, 318-359, 411-425) that the
