@@ -115,8 +115,8 @@ struct SlotGrad {
 
 // d(loss)/d(operator row) contributed by one slot whose operand went through the operator:
 // needs the gradient at the operator output (gz) and the raw embedding row x.
-template <int VEC>
-__device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC, -1, -1> &sg, const float *x, const float *xlo, float xscale, int dd,
+template <int VEC, int CMPK = -1>
+__device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC, CMPK, -1> &sg, const float *x, const float *xlo, float xscale, int dd,
                                                 const float *xadd = nullptr) {
   // xadd: global embedding added to the raw row before the operator (null: none)
   float4 v = sg.gz(dd);
@@ -242,19 +242,19 @@ __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, 
       if (dd < D) acc[c] = acc[c] + sg.gx(dd);
     }
   } else {
-    SlotGrad<VEC, -1, -1> sg;
+    SlotGrad<VEC, CMPK, -1> sg;
     int qa = oc.a == ARR_R0 ? ARR_Q0 : ARR_Q1;             // slot that carried the operator
     int na = oc.a == ARR_R0 ? ARR_N1 : ARR_N0;             // its operator-free copy (raw row)
     sg.init(d, wb, w, qa, oc.blk, oc.r, oc.b, lane);
     size_t nrow = (size_t)oc.blk * w.xrows[na] + oc.r;
     const float *x = w.X[na] + nrow * d.Dp;
     const float *xlo = d.split ? w.XL[na] + nrow * d.Dp : nullptr;
-    float xscale = d.cmp == PBG_CMP_COS ? 1.0f / w.aux[na][nrow] : 1.0f;
+    float xscale = (CMPK >= 0 ? CMPK : d.cmp) == PBG_CMP_COS ? 1.0f / w.aux[na][nrow] : 1.0f;
 #pragma unroll
     for (int c = 0; c < VEC; ++c) {
       int dd = c * 128 + lane * 4;
       if (dd < D) {
-        acc[c] = acc[c] + op_param_grad<VEC>(sg, x, xlo, xscale, dd);
+        acc[c] = acc[c] + op_param_grad<VEC, CMPK>(sg, x, xlo, xscale, dd);
         // N3 regularizer on the edge's own parameter row (still as the wave found it in global memory)
         if (d.reg_coef != 0.f && sg.theta) acc[c] = acc[c] + n3_grad4(sg.theta, dd, D, d.op == PBG_OP_COMPLEX_DIAGONAL) * d.reg_coef;
       }
@@ -272,6 +272,8 @@ __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, 
 // operator or a translation) -- compiled without the comparator / operator pull-back, whose
 // predicated-off copies in the unrolled loops cost more issue slots than the additions themselves.
 // MODE 2: cos comparator with no operator or a translation, comparator fixed at compile time.
+// MODE 3: dot comparator fixed at compile time, any operator (the pull-back through complex_diagonal
+// evaluates the comparator's part twice per element).
 // MODE 0: everything decided at run time.
 template <int VEC, int RULE, int MODE>
 __global__ void __launch_bounds__(32 * (RULE == RULE_EMB ? TILE_WARPS_EMB : UPD_WARPS), RULE == RULE_EMB ? 3 : 2)
@@ -412,6 +414,8 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
         }
       } else if (MODE == 2) {
         add_slot<VEC, RULE, PBG_CMP_COS, 0>(acc, d, wb, w, oc, lane, gs);
+      } else if (MODE == 3) {
+        add_slot<VEC, RULE, PBG_CMP_DOT, -1>(acc, d, wb, w, oc, lane, gs);
       } else {
         add_slot<VEC, RULE>(acc, d, wb, w, oc, lane, gs);
       }
@@ -821,6 +825,8 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
                          (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
     cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
+    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
     attr_done[0] = true;
   }
   bool has_op = d.op != PBG_OP_NONE && w.theta[0] != nullptr;
@@ -840,6 +846,8 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   if (plain) tile_update_kernel<VEC, RULE_EMB, 1><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   else if (d.cmp == PBG_CMP_COS && !d.matrix_op && d.reg_coef == 0.f && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION))
     tile_update_kernel<VEC, RULE_EMB, 2><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  else if (d.cmp == PBG_CMP_DOT && !d.matrix_op && d.reg_coef == 0.f)
+    tile_update_kernel<VEC, RULE_EMB, 3><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   else tile_update_kernel<VEC, RULE_EMB, 0><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt);
   hub_update_kernel<VEC, RULE_EMB><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
@@ -852,7 +860,10 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
         attr_done[1] = true;
       }
       cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
-      tile_update_kernel<VEC, RULE_REL, 0><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      if (d.cmp == PBG_CMP_DOT && d.reg_coef == 0.f)
+        tile_update_kernel<VEC, RULE_REL, 3><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      else
+        tile_update_kernel<VEC, RULE_REL, 0><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
       hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt);
       hub_update_kernel<VEC, RULE_REL><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
       ++launches;
