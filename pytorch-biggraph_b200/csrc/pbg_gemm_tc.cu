@@ -218,6 +218,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         unsigned char *st = smem + (size_t)s * stage_bytes;
         uint32_t aH = smem_u32(st), bH = smem_u32(st + A_BYTES);
         uint32_t aL = aH + RAW_BYTES, bL = bH + RAW_BYTES;
+        const int kleft = g.K - kb * KB;                        // k-values of this block that exist (the rest is zero fill)
         if (PLANES) {
           // plane pairs (a, b) of order a + b <= 2, the smallest contributions first; K = 16 per MMA:
           // K-major 64-byte rows (64-byte swizzle: layout 4, 512 bytes per 8 rows, 32 bytes per step),
@@ -225,6 +226,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
           const int pa[6] = {2, 0, 1, 1, 0, 0}, pb[6] = {0, 2, 1, 0, 1, 0};
 #pragma unroll
           for (int k16 = 0; k16 < 2; ++k16) {
+            if (k16 * 16 >= kleft) break;                     // the tail of K: those k-values are zero fill
 #pragma unroll
             for (int t = 0; t < 6; ++t) {
               uint64_t da = A_MN ? smem_desc(aH + pa[t] * A_PLANE + k16 * 2048, BOX_BYTES, 1024, 2)
@@ -239,6 +241,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         } else
 #pragma unroll
         for (int k8 = 0; k8 < KB / 8; ++k8) {
+          if (k8 * 8 >= kleft) break;                         // the tail of K: those k-values are zero fill
           constexpr uint32_t KSBO = KB == 32 ? 1024 : 512, KLAY = KB == 32 ? 2 : 4;     // K-major: 8 rows of ROW_BYTES; 128- / 64-byte swizzle
           uint32_t ao = A_MN ? k8 * 1024 : k8 * 32, bo = B_MN ? k8 * 1024 : k8 * 32;
           uint64_t dAh = A_MN ? smem_desc(aH + ao, BOX_BYTES, 512, 1) : smem_desc(aH + ao, 0, KSBO, KLAY);
