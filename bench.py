@@ -33,19 +33,26 @@ for p in (ROOT, os.path.join(ROOT, "pytorch-biggraph_b200")):
 WORKLOADS = {
     # name: entities, edges, partitions, dim, operator, comparator, loss, batch, batch negs, uniform negs, degree exponent
     "c3": dict(entities=4_847_571, edges=68_993_773, partitions=16, dim=1024, op="none", comp="dot", loss="softmax",
-               batch=1000, nb=100, nu=100, gamma=2.3, desc="social-graph shaped, Chung-Lu exponent 2.3"),
+               batch=1000, nb=100, nu=100, gamma=2.3, precision="bf16x6", desc="social-graph shaped, Chung-Lu exponent 2.3"),
     "c4": dict(entities=41_652_230, edges=1_468_365_182, partitions=16, dim=100, op="translation", comp="cos",
                loss="ranking", batch=1000, nb=100, nu=100, gamma=2.0, desc="follower-graph shaped, Chung-Lu exponent 2.0"),
     "c2": dict(entities=14_951, edges=483_142, partitions=1, dim=400, op="complex_diagonal", comp="dot", loss="softmax",
                batch=5000, nb=1000, nu=0, gamma=None, rels=1345, dynamic=True,
                desc="15k-entity multi-relation KG shaped, 1345 relations Zipf(1.0), planted permutation maps + 20% noise, dynamic relations"),
     "c1": dict(entities=100_000, edges=1_000_000, partitions=1, dim=100, op="none", comp="dot", loss="ranking",
-               batch=1000, nb=50, nu=50, gamma=None, desc="plumbing graph, Zipf(1.1) endpoints"),
+               batch=1000, nb=50, nu=50, gamma=None, precision="bf16x6", desc="plumbing graph, Zipf(1.1) endpoints"),
 }
 EDGES_PER_STEP_CAP = 269_507
 # DRAM bytes per trained edge of each kernel class, from the ncu capture summarised in
-# the profiles folder (workload c3, tf32x3); dram__bytes_read.sum + dram__bytes_write.sum per launch / edges per launch
-NCU_TRAFFIC_PER_EDGE = {("c3", "tf32x3"): {"gather": 22.7e3, "score": 17.0e3, "grad": 29.6e3, "update": 40.5e3}}
+# the profiles folder (workload c3, both rtol 1e-4 tensor-core tiers); dram__bytes_read.sum + dram__bytes_write.sum per launch / edges per launch
+NCU_TRAFFIC_PER_EDGE = {("c3", "tf32x3"): {"gather": 22.7e3, "score": 17.0e3, "grad": 29.6e3, "update": 40.5e3},
+                        ("c3", "bf16x6"): {"gather": 31.2e3, "score": 25.2e3, "grad": 40.8e3, "update": 40.5e3}}
+PRECISION_NOTES = {
+    "fp32": "fp32 FMA on the CUDA cores",
+    "tf32x3": "tcgen05 kind::tf32, operands split hi + lo in shared memory, three MMAs per product, fp32 accumulation; parity tier rtol 1e-4",
+    "bf16x6": "tcgen05 kind::f16 on three bf16 planes per fp32 operand value (24 mantissa bits), six plane products, fp32 accumulation; parity tier rtol 1e-4",
+    "tf32": "tcgen05 kind::tf32, single pass; parity tier rtol 1e-3",
+}
 REF_BATCHES = 5          # batches per worker in one step of the CPU reference arm
 
 
@@ -313,7 +320,8 @@ def _workload_config(args, w, step_edges):
     return {"workload": f"{args.workload}: {w['desc']}; {w['entities']} entities, {w['partitions']} partitions, dim {w['dim']}, "
                         f"{w['op']}/{w['comp']}/{w['loss']}, batch {w['batch']}, {w['nb']} batch + {w['nu']} uniform negs",
             "step": f"one bucket: {step_edges} edges", "l2": "inputs_larger_than_l2",
-            "batches_in_flight": args.k, "precision": args.precision}
+            "batches_in_flight": args.k, "precision": args.precision,
+            "arithmetic": PRECISION_NOTES.get(args.precision, args.precision)}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -624,16 +632,19 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--lr", type=float, default=0.1)
     ap.add_argument("--k", type=int, default=14, help="batches in flight (1 = sequential batches, the reference's GPU semantics)")
-    ap.add_argument("--precision", default="tf32x3", choices=["fp32", "tf32x3", "tf32", "bf16x6"],
-                    help="tf32x3 (default): tcgen05 tensor cores with 3-term split, the rtol 1e-4 tier; fp32: CUDA cores; "
-                         "tf32: single pass, the rtol 1e-3 tier; bf16x6: three bf16 planes per operand, six plane products, "
-                         "the rtol 1e-4 tier")
+    ap.add_argument("--precision", default=None, choices=["fp32", "tf32x3", "tf32", "bf16x6"],
+                    help="arithmetic of the contractions.  tf32x3: tcgen05 TF32 with 3-term split, the rtol 1e-4 tier; "
+                         "bf16x6: tcgen05 bf16 on three planes per fp32 operand (24 mantissa bits), six plane products, "
+                         "the rtol 1e-4 tier; fp32: CUDA cores; tf32: single pass, the rtol 1e-3 tier.  Default: the faster "
+                         "of the two rtol 1e-4 tensor-core tiers on the workload (c3, c1: bf16x6; c2, c4: tf32x3)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--resident", type=int, default=0,
                     help="partitions kept on the device at N=1 (0 = all); a small number keeps profiler captures small")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     w = WORKLOADS[args.workload]
+    if args.precision is None:
+        args.precision = w.get("precision", "tf32x3")
     if args.impl == "reference":
         run_reference(args, w)
     else:
