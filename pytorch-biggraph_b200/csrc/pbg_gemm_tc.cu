@@ -54,6 +54,7 @@ struct TcGeom {
   const float *auxB[2]; long long auxb_blk;
   int cmp, score;
   int nst, stage_bytes;  // bf16-plane tier: stages in flight and bytes of one (three planes of A and of the B tile)
+  int tr;                // the output map is that of the transposed matrix: tile element (row, col) goes to C[col][row]
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -342,6 +343,13 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         __syncwarp();
         unsigned char *buf = ostage + (size_t)(q * 2 + (int)(nst & 1)) * 4096;
         ++nst;
+        if (g.tr) {
+          // transposed output: column jj of the block is row jj of the store box, this lane's tile row its
+          // element `lane` -- 4-byte writes, conflict-free in the same 128-byte swizzle
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj)
+            *reinterpret_cast<uint32_t *>(buf + jj * 128 + (((lane >> 2) ^ (jj & 7)) << 4) + ((lane & 3) << 2)) = r[jj];
+        } else
 #pragma unroll
         for (int jj = 0; jj < 32; jj += 4) {
           float v[4];
@@ -361,7 +369,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         __syncwarp();
         if (lane == 0) {
           asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
-                       :: "l"(&maps.c[p]), "r"(ncol0), "r"(mrow0), "r"(blk), "r"(smem_u32(buf)) : "memory");
+                       :: "l"(&maps.c[p]), "r"(g.tr ? mrow0 : ncol0), "r"(g.tr ? ncol0 : mrow0), "r"(blk), "r"(smem_u32(buf)) : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       }
@@ -432,7 +440,7 @@ static bool encode4_planes(CUtensorMap *tm, const unsigned short *base, int inne
 }
 
 struct TcPlan {
-  TcMaps score, gradq, gradn, gradm;
+  TcMaps score, gradq, gradn, gradm, gradt;
   bool dynamic;
   int bn_score, bn_grad;
   int nterms;
@@ -477,6 +485,11 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
         ok &= encode4_planes(&pl->gradm.a[p], w.AB[p], d.Mm, d.Mm, d.Mm, nblk_max, w.Kb, 32, 128);
         ok &= encode4_planes(&pl->gradm.b[p], w.XB[o], d.D, w.xrows[o], w.xrows[o], nblk_max, w.Dpb, 64, 32);
         ok &= encode3(&pl->gradm.c[p], w.GX[n], d.D, d.Mm, nblk_max, d.Dp, (long long)d.Mm * d.Dp, 32, 32, false);
+        // the same product transposed, GN^T = N_other^T . A^T: tile rows run over D (every 128-row tile full,
+        // where Mm = 200 leaves the second one 56 % used), tile columns over the Mm coefficient rows
+        pl->gradt.a[p] = pl->gradm.b[p];
+        ok &= encode4_planes(&pl->gradt.b[p], w.AB[p], d.Mm, d.Mm, d.Mm, nblk_max, w.Kb, 32, pl->bn_score);
+        pl->gradt.c[p] = pl->gradm.c[p];
       }
     }
     if (!ok) { delete pl; return nullptr; }
@@ -579,6 +592,16 @@ int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, 
   TcGeom g;
   memset(&g, 0, sizeof g);
   g.N = d.D; g.BN = pl->bn_grad; g.ldc = d.Dp;
+  if (!pl->dynamic && pl->nterms == 6) {     // bf16-plane tier: the transposed product (see pbg_tc_plan_create)
+    g.M = d.D; g.N = d.Mm; g.K = d.Mm; g.BN = pl->bn_score; g.tr = 1;
+    for (int p = 0; p < 2; ++p) g.C[p] = w.GX[ARR_N0 + p];
+    long long tiles = (long long)((g.N + g.BN - 1) / g.BN) * ((g.M + 127) / 128) * d.nblk * 2;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    launch_tc_inst<true, false, 6, false>(pl->gradt, g, d, wb, w.errflag, dim3((unsigned)(tiles < sms ? tiles : sms)),
+                                          4 * (128 * 128 + 256 * 128) + 4 * 2 * 4096 + 1024, st);
+    return 1;
+  }
   if (!pl->dynamic) {          // GN_side = A[side] . N_(1-side)
     g.M = d.Mm; g.K = d.Mm; g.c_blk = (long long)d.Mm * d.Dp;
     for (int p = 0; p < 2; ++p) g.C[p] = w.GX[ARR_N0 + p];
