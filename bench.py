@@ -46,7 +46,7 @@ EDGES_PER_STEP_CAP = 269_507
 # DRAM bytes per trained edge of each kernel class, from the ncu capture summarised in
 # the profiles folder (workload c3, both rtol 1e-4 tensor-core tiers); dram__bytes_read.sum + dram__bytes_write.sum per launch / edges per launch
 NCU_TRAFFIC_PER_EDGE = {("c3", "tf32x3"): {"gather": 22.7e3, "score": 17.0e3, "grad": 29.6e3, "update": 40.5e3},
-                        ("c3", "bf16x6"): {"gather": 31.2e3, "score": 25.2e3, "grad": 40.8e3, "update": 40.5e3}}
+                        ("c3", "bf16x6"): {"gather": 31.2e3, "score": 25.2e3, "grad": 40.6e3, "update": 40.5e3}}
 PRECISION_NOTES = {
     "fp32": "fp32 FMA on the CUDA cores",
     "tf32x3": "tcgen05 kind::tf32, operands split hi + lo in shared memory, three MMAs per product, fp32 accumulation; parity tier rtol 1e-4",
