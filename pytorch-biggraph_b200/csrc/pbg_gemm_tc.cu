@@ -520,6 +520,11 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
       ok &= encode3(&pl->gradm.a[p], w.A[p], d.Mm, d.Mm, nblk_max, w.Ma, (long long)d.Mm * w.Ma, TC_KB, 128, false);
       ok &= encode3(&pl->gradm.b[p], w.X[o], d.D, w.xrows[o], nblk_max, d.Dp, (long long)w.xrows[o] * d.Dp, 32, TC_KB, true);
       ok &= encode3(&pl->gradm.c[p], w.GX[n], d.D, d.Mm, nblk_max, d.Dp, (long long)d.Mm * d.Dp, 32, 32, false);
+      // the same product transposed (see the bf16-plane tier above): A = the other side's operand rows (MN-major),
+      // B = the coefficient rows (K-major)
+      pl->gradt.a[p] = pl->gradm.b[p];
+      ok &= encode3(&pl->gradt.b[p], w.A[p], d.Mm, d.Mm, nblk_max, w.Ma, (long long)d.Mm * w.Ma, TC_KB, pl->bn_score, false);
+      pl->gradt.c[p] = pl->gradm.c[p];
     }
   }
   if (!ok) { delete pl; return nullptr; }
@@ -592,14 +597,16 @@ int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, 
   TcGeom g;
   memset(&g, 0, sizeof g);
   g.N = d.D; g.BN = pl->bn_grad; g.ldc = d.Dp;
-  if (!pl->dynamic && pl->nterms == 6) {     // bf16-plane tier: the transposed product (see pbg_tc_plan_create)
+  if (!pl->dynamic && pl->nterms != 1) {     // standard relations: the transposed product (see pbg_tc_plan_create)
     g.M = d.D; g.N = d.Mm; g.K = d.Mm; g.BN = pl->bn_score; g.tr = 1;
     for (int p = 0; p < 2; ++p) g.C[p] = w.GX[ARR_N0 + p];
     long long tiles = (long long)((g.N + g.BN - 1) / g.BN) * ((g.M + 127) / 128) * d.nblk * 2;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    launch_tc_inst<true, false, 6, false>(pl->gradt, g, d, wb, w.errflag, dim3((unsigned)(tiles < sms ? tiles : sms)),
-                                          4 * (128 * 128 + 256 * 128) + 4 * 2 * 4096 + 1024, st);
+    const dim3 grid((unsigned)(tiles < sms ? tiles : sms));
+    const size_t smem = 4 * (128 * 128 + 256 * 128) + 4 * 2 * 4096 + 1024;
+    if (pl->nterms == 6) launch_tc_inst<true, false, 6, false>(pl->gradt, g, d, wb, w.errflag, grid, smem, st);
+    else launch_tc_inst<true, false, 3, false>(pl->gradt, g, d, wb, w.errflag, grid, smem, st);
     return 1;
   }
   if (!pl->dynamic) {          // GN_side = A[side] . N_(1-side)
