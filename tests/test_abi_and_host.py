@@ -203,3 +203,15 @@ def test_model_refuses_cpu_tensors_and_no_fallback():
         m.set_embeddings("e", T.Side.RHS, m.lhs_embs["emb_e"])
         tr.process_one_batch(m, T.EdgeList(T.EntityList.from_tensor(torch.tensor([0])),
                                            T.EntityList.from_tensor(torch.tensor([1])), torch.tensor(0)))
+
+
+def test_bench_names_a_default_tier_per_workload():
+    """bench.py's default arithmetic is one of the rtol 1e-4 tensor-core tiers, and every tier has its note."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for name, w in bench.WORKLOADS.items():
+        assert w.get("precision", "tf32x3") in ("tf32x3", "bf16x6"), name
+    assert set(bench.PRECISION_NOTES) == set(_lib.PRECISION_CODES)
