@@ -43,10 +43,44 @@ WORKLOADS = {
                batch=1000, nb=50, nu=50, gamma=None, precision="bf16x6", desc="plumbing graph, Zipf(1.1) endpoints"),
 }
 EDGES_PER_STEP_CAP = 269_507
-# DRAM bytes per trained edge of each kernel class, from the ncu capture summarised in
-# the profiles folder (workload c3, both rtol 1e-4 tensor-core tiers); dram__bytes_read.sum + dram__bytes_write.sum per launch / edges per launch
-NCU_TRAFFIC_PER_EDGE = {("c3", "tf32x3"): {"gather": 22.7e3, "score": 17.0e3, "grad": 29.6e3, "update": 40.5e3},
-                        ("c3", "bf16x6"): {"gather": 31.2e3, "score": 25.2e3, "grad": 40.6e3, "update": 40.5e3}}
+# DRAM bytes per trained edge of each kernel class come from the ncu summaries under profiles/: the file
+# of a (workload, precision) pair carries one line
+#   traffic_per_edge_bytes: gather=... score=... grad=... update=... csrc_sha256=<digest>
+# where the digest is csrc_digest() of the kernel sources the capture ran.  A summary whose digest is
+# not that of the sources in the tree describes other kernels: its figures are then not used.
+PROFILE_FILES = {("c3", "tf32x3"): "kernels_c3_tf32x3.md", ("c3", "bf16x6"): "kernels_c3_bf16x6.md",
+                 ("c3", "bf16x3"): "kernels_c3_bf16x3.md"}
+
+
+def csrc_digest():
+    """sha256 over the CUDA sources of the library (names and contents, sorted by name)."""
+    import glob
+    import hashlib
+    h = hashlib.sha256()
+    for path in sorted(glob.glob(os.path.join(ROOT, "pytorch-biggraph_b200", "csrc", "*.cu*"))):
+        h.update(os.path.basename(path).encode())
+        with open(path, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:16]
+
+
+def ncu_traffic_per_edge(workload, precision):
+    """(per-class DRAM bytes per trained edge, source note) from the profile summary of this pair, or
+    (None, why) when there is none for the kernels in the tree."""
+    name = PROFILE_FILES.get((workload, precision))
+    path = os.path.join(ROOT, "profiles", name) if name else None
+    if not path or not os.path.exists(path):
+        return None, "no ncu summary for this workload and precision"
+    with open(path) as f:
+        lines = [l for l in f if l.startswith("traffic_per_edge_bytes:")]
+    if not lines:
+        return None, f"profiles/{name} carries no traffic line"
+    kv = dict(t.split("=", 1) for t in lines[-1].split()[1:])
+    if kv.get("csrc_sha256") != csrc_digest():
+        return None, f"profiles/{name} was captured on other kernel sources ({kv.get('csrc_sha256')}, tree {csrc_digest()})"
+    return {k: float(v) for k, v in kv.items() if k != "csrc_sha256"}, f"profiles/{name} (ncu, sources {kv['csrc_sha256']})"
+
+
 PRECISION_NOTES = {
     "fp32": "fp32 FMA on the CUDA cores",
     "tf32x3": "tcgen05 kind::tf32, operands split hi + lo in shared memory, three MMAs per product, fp32 accumulation; parity tier rtol 1e-4",
@@ -300,7 +334,7 @@ def run_reference(args, w):
     line = {"impl": "reference", "metric": "edges/sec trained", "value": v, "unit": "edges/sec", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(args, w, step_edges=tr.cores * w["batch"] * REF_BATCHES),
+            "config": reference_config(args, w, step_edges=tr.cores * w["batch"] * REF_BATCHES, cores=tr.cores),
             "cpu_baseline": {"value": v, "unit": "edges/sec", "cores": tr.cores, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": "edges/sec", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -314,6 +348,14 @@ def workload_config(args, w, step_edges, halves=False):
         cfg["hand_off"] = ("rhs partition travels to the next GPU in two halves over NCCL send/recv (NVLink), each half "
                            "beside the training of the other; inside the timed region")
     return cfg
+
+
+def reference_config(args, w, step_edges, cores):
+    """The CPU arm's own description: same workload string, its own step and arithmetic."""
+    return {"workload": _workload_config(args, w, step_edges)["workload"],
+            "step": f"{REF_BATCHES} batches of {w['batch']} edges on each of {cores} HOGWILD processes: {step_edges} edges",
+            "l2": "inputs_larger_than_l2", "precision": "fp32",
+            "arithmetic": "fp32 PyTorch CPU kernels (the reference's ATen call sequence), one thread per process"}
 
 
 def _workload_config(args, w, step_edges):
@@ -560,6 +602,41 @@ def run_b200(args, w):
            "h2d_bytes_per_step": (3 if dyn else 2) * 8 * step_edges, "d2h_bytes_per_step": 40,
            "last_step_loss": last.metrics["loss"] if last is not None else None}
 
+    # ---- sequential batches (one batch in flight: the reference's own GPU semantics) ----------------
+    sequential = None
+    if world == 1 and args.k > 1 and not args.no_sequential:
+        import dataclasses
+        cfg1 = dataclasses.replace(cfg, batches_in_flight=1)
+        model1 = T.make_model(cfg1, dev)
+        trainer1 = T.B200Trainer(T.make_optimizer(cfg1, model1.parameters(), False),
+                                 T.LOSS_FUNCTIONS.get_class(w["loss"])(margin=0.1), [1.0])
+        nseq = 2
+
+        def step_seq(s):
+            pl, pr = bucket_for(s)
+            model1.clear_all_embeddings()
+            model1.set_embeddings("e", T.Side.LHS, tables[pl])
+            model1.set_embeddings("e", T.Side.RHS, tables[pr])
+            trainer1.partitioned_optimizers.clear()
+            trainer1.partitioned_optimizers["e", pl] = opts[pl]
+            trainer1.partitioned_optimizers["e", pr] = opts[pr]
+            l, r, rl = dev_edges[s]
+            trainer1.train_batches(model1, l, r, rl, batches, want_per_batch=False)
+
+        step_seq(0)
+        torch.cuda.synchronize()
+        e0.record()
+        for s in range(1, 1 + nseq):
+            step_seq(s)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_seq = e0.elapsed_time(e1)
+        trainer1.read_stats()
+        sequential = {"value": nseq * step_edges / (ms_seq / 1e3), "unit": "edges/sec", "batches_in_flight": 1,
+                      "steps": nseq, "note": "same build and workload with one batch in flight: every batch reads the "
+                                             "tables its predecessor updated, as the reference's GPU trainer does"}
+        del trainer1, model1
+
     # ---- per-kernel-class timing pass ----------------------------------------------------------
     import ctypes as C
     check = _lib.check
@@ -590,7 +667,8 @@ def run_b200(args, w):
         v["share"] = round(v["ms"] / tot, 3)
     dom = max((n for n in per_class if n in model_bytes or n in model_flops), key=lambda n: per_class[n]["ms"])
     launches_dom = max(per_class[dom]["launches"], 1)
-    per_edge = NCU_TRAFFIC_PER_EDGE.get((args.workload, args.precision), {}).get(dom)
+    per_class_traffic, traffic_source = ncu_traffic_per_edge(args.workload, args.precision)
+    per_edge = None if per_class_traffic is None else per_class_traffic.get(dom)
     # ncu's DRAM bytes of the dominant class, per launch of this run (edges of the timing pass / its launches)
     # (the update class is several kernels per wave, the tile kernel carries its traffic: one launch per wave, as the statistics kernel)
     dom_kernel_launches = max(per_class["stats"]["launches"], 1) if dom == "update" else launches_dom
@@ -599,14 +677,15 @@ def run_b200(args, w):
         ach = per_class[dom]["TFLOPs"]
         per_product = {"tf32x3": 6.0, "tf32": 2.0, "bf16x6": 6.0}.get(args.precision)     # TF32 runs at half the bf16 rate; TF32X3 issues three MMAs per product, BF16X6 six bf16 ones
         roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
-                "frac": round(ach / pk["tflops"], 4), "traffic": traffic,
+                "frac": round(ach / pk["tflops"], 4), "traffic": traffic, "traffic_source": traffic_source,
                 "ceiling_for_precision": None if per_product is None else round(pk["tflops"] / per_product, 1),
                 "frac_of_ceiling": None if per_product is None else round(ach * per_product / pk["tflops"], 4),
                 "peak_source": pk["source"] + " (cuBLAS bf16, sustained); the contraction runs in " + args.precision}
     else:
         ach = per_class[dom]["GBps"]
         roof = {"bound": "hbm", "kernel": dom, "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": round(ach / pk["hbm_gbs"], 4), "traffic": traffic, "peak_source": pk["source"]}
+                "frac": round(ach / pk["hbm_gbs"], 4), "traffic": traffic, "traffic_source": traffic_source,
+                "peak_source": pk["source"]}
 
     if rank == 0:
         line = {"metric": "edges/sec trained", "value": value, "unit": "edges/sec", "n_gpus": world, "steps": args.steps,
@@ -616,6 +695,8 @@ def run_b200(args, w):
                 "clocks": clocks.summary(), "roofline": roof, "kernels": per_class,
                 "algorithmic_per_edge": {"flops": alg["flops"], "bytes": alg["bytes"]},
                 "edges_per_sec_hbm_bound": pk["hbm_gbs"] * 1e9 / alg["bytes"]}
+        if sequential is not None:
+            line["sequential"] = sequential
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
@@ -638,6 +719,7 @@ def main():
                          "the rtol 1e-4 tier; fp32: CUDA cores; tf32: single pass, the rtol 1e-3 tier.  Default: the faster "
                          "of the two rtol 1e-4 tensor-core tiers on the workload (c3, c1: bf16x6; c2, c4: tf32x3)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sequential", action="store_true", help="skip the two extra steps with one batch in flight")
     ap.add_argument("--resident", type=int, default=0,
                     help="partitions kept on the device at N=1 (0 = all); a small number keeps profiler captures small")
     args = ap.parse_args()

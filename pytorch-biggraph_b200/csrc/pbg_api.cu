@@ -140,8 +140,6 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   if ((size_t)cfg->batches_in_flight * ((cfg->dim + 127) / 128) * 512 > 227 * 1024)
     return fail(c, PBG_ERR_TOO_LARGE, "batches_in_flight %d with dimension %d: the per-batch totals of a hub row exceed shared memory (at most 28 batches above dimension 1024)",
                 cfg->batches_in_flight, cfg->dim);
-  if (cfg->precision != PBG_PREC_FP32 && !pbg_tc_available())
-    return fail(c, PBG_ERR_UNSUPPORTED, "tensor-core precision tiers are not built into this library");
   if (cfg->precision < PBG_PREC_FP32 || cfg->precision > PBG_PREC_BF16X6) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown precision %d", cfg->precision);
   const bool planes = cfg->precision == PBG_PREC_BF16X6;
   if (planes && matrix_op)
@@ -173,28 +171,18 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
   size_t oReg = 0, oRscale = 0;
-  size_t oX[4], oAux[4], oG[4], oS[2], oSpos[2], oCoef[4], oLoss[2], oViol[2], oRank[2], oXL[4] = {0, 0, 0, 0}, oSL[2] = {0, 0};
-  const bool split = false;   // TF32X3 splits operands inside the contraction kernel: no low-part arrays
+  size_t oX[4], oAux[4], oG[4], oS[2], oSpos[2], oCoef[4], oLoss[2], oViol[2], oRank[2];
   oX[0] = take(nN * c->Dp * 4); oX[1] = take(nN * c->Dp * 4);
   oAux[0] = take(nN * 4); oAux[1] = take(nN * 4);
   if (dyn) { oX[2] = take(nQ * c->Dp * 4); oX[3] = take(nQ * c->Dp * 4); oAux[2] = take(nQ * 4); oAux[3] = take(nQ * 4); }
   else { oX[2] = oX[1]; oX[3] = oX[0]; oAux[2] = oAux[1]; oAux[3] = oAux[0]; }
-  if (split) {
-    oXL[0] = take(nN * c->Dp * 4); oXL[1] = take(nN * c->Dp * 4);
-    if (dyn) { oXL[2] = take(nQ * c->Dp * 4); oXL[3] = take(nQ * c->Dp * 4); }
-    else { oXL[2] = oXL[1]; oXL[3] = oXL[0]; }
-    oSL[0] = take(nQ * c->Ms * 4); oSL[1] = take(nQ * c->Ms * 4);
-  }
   oG[0] = take(nN * c->Dp * 4); oG[1] = take(nN * c->Dp * 4);
   if (dyn) { oG[2] = take(nQ * c->Dp * 4); oG[3] = take(nQ * c->Dp * 4); }
   else { oG[2] = oG[0]; oG[3] = oG[1]; }            // standard relations have no GQ arrays
   const int Ma = (c->Mm + 3) / 4 * 4;
-  size_t oA[2] = {0, 0}, oAL[2] = {0, 0};
+  size_t oA[2] = {0, 0};
   if (!dyn) {
-    for (int s2 = 0; s2 < 2; ++s2) {
-      oA[s2] = take(nN * Ma * 4);
-      if (split) oAL[s2] = take(nN * Ma * 4);
-    }
+    for (int s2 = 0; s2 < 2; ++s2) oA[s2] = take(nN * Ma * 4);
   }
   const int Dpb = (cfg->dim + 7) / 8 * 8, Kb = (c->Mm + 7) / 8 * 8;
   size_t oXB[4] = {0, 0, 0, 0}, oAB[2] = {0, 0}, oTB[2] = {0, 0};
@@ -232,13 +220,8 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     b.aux[a] = (float *)(c->ws + oAux[a]);
     b.GX[a] = (float *)(c->ws + oG[a]);
     b.coef[a] = (float *)(c->ws + oCoef[a]);
-    b.XL[a] = split ? (float *)(c->ws + oXL[a]) : nullptr;
   }
-  for (int p = 0; p < 2; ++p) {
-    b.SL[p] = split ? (float *)(c->ws + oSL[p]) : nullptr;
-    b.A[p] = dyn ? nullptr : (float *)(c->ws + oA[p]);
-    b.AL[p] = (!dyn && split) ? (float *)(c->ws + oAL[p]) : nullptr;
-  }
+  for (int p = 0; p < 2; ++p) b.A[p] = dyn ? nullptr : (float *)(c->ws + oA[p]);
   b.Ma = Ma;
   b.Dpb = Dpb; b.Kb = Kb;
   for (int a = 0; a < 4; ++a) b.XB[a] = planes ? (unsigned short *)(c->ws + oXB[a]) : nullptr;
@@ -361,7 +344,6 @@ static int bind_bucket(pbg_context *c, const pbg_bucket *bk, WaveDims &d, WaveBu
   d.batch_negs = cfg.num_batch_negs > 0;
   d.neg_enabled[0] = !cfg.disable_lhs_negs; d.neg_enabled[1] = !cfg.disable_rhs_negs;
   d.num_batch_negs = cfg.num_batch_negs; d.spb = c->spb; d.margin = cfg.margin; d.reg_coef = cfg.regularization_coef; d.max_norm = cfg.max_norm > 0.f ? cfg.max_norm : 0.f;
-  d.split = 0;
   d.matrix_op = cfg.op == PBG_OP_LINEAR || cfg.op == PBG_OP_AFFINE;
   d.opw = d.matrix_op ? cfg.dim * cfg.dim + (cfg.op == PBG_OP_AFFINE ? cfg.dim : 0) : cfg.dim;
   d.n_rows[0] = bk->lhs_rows; d.n_rows[1] = bk->rhs_rows;

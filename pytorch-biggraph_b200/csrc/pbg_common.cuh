@@ -25,6 +25,9 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <mutex>
+#include <set>
+#include <utility>
 #include "../../include/pbg_b200.h"
 
 #define PBG_KMAX 32                 // most batches in one wave
@@ -53,7 +56,6 @@ struct WaveDims {
   int num_rels;
   int matrix_op;        // operator is linear / affine (standard relations): applied by contractions, not in the gather
   int opw;              // floats per operator-table row: D, or D*D (+ D) for linear (affine)
-  int split;            // TF32X3: operands and coefficient matrices are stored as hi + lo
   unsigned long long key_rel_base;   // first sort key of operator-table rows
   unsigned long long key_invalid;    // sort key of slots that carry no gradient
 };
@@ -68,15 +70,13 @@ struct WaveBatches {
 
 struct WaveBufs {
   float *X[4];       int xrows[4];   // operand arrays N0,N1,Q0,Q1 (rows per block; aliases allowed)
-  float *XL[4];                      // split mode: low parts (x - tf32(x)) of the operand arrays
   float *aux[4];                     // per operand row: cos -> 1/|z|, l2 -> |y|^2 (indexed like X)
   float *GX[4];      int grows[4];   // gradient arrays GN0,GN1,GQ0,GQ1
   float *S[2];                       // scores / coefficient matrices
-  float *SL[2];                      // split mode: low parts of the coefficient matrices
   // Standard relations: combined coefficient matrices, one per side, [nblk][Mm][Ma]:
   //   A[0][m][j] = (j < Pm ? T0[j][m] : 0) + (m < Pm ? T1[m][j] : 0)   gradient of the lhs rows  = A[0] . N1
   //   A[1][m][j] = (j < Pm ? T1[j][m] : 0) + (m < Pm ? T0[m][j] : 0)   gradient of the rhs rows  = A[1] . N0
-  float *A[2], *AL[2];
+  float *A[2];
   int Ma;                            // row stride of A (Mm rounded up to 4)
   // bf16-plane tier: every fp32 operand value as three bf16 planes b0 + b1 + b2 (b0 = bf16(x), b1 =
   // bf16(x - b0), b2 = bf16(x - b0 - b1)); the contractions read these instead of X / A
@@ -260,6 +260,28 @@ __device__ __forceinline__ void put_planes1(unsigned short *dst, size_t plane, f
 __device__ __forceinline__ float tf32_round(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
 __device__ __forceinline__ float4 tf32_round4(float4 v) { return make_float4(tf32_round(v.x), tf32_round(v.y), tf32_round(v.z), tf32_round(v.w)); }
 
+// ---- host-side helpers ---------------------------------------------------------------------------
+// Opt-in to more than 48 KB of dynamic shared memory.  The attribute belongs to the (kernel, device)
+// pair, so a process that drives several GPUs has to set it on each of them: the pairs already done
+// are remembered under a mutex, with the device that is current at the call.
+inline cudaError_t pbg_opt_in_smem(const void *kernel, int bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<const void *, int>> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({kernel, dev})) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done.insert({kernel, dev});
+  return e;
+}
+inline int pbg_sm_count() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 1;
+  return sms > 0 ? sms : 1;
+}
+
 // ---- host-side launchers (one per translation unit) ------------------------------------------
 struct SortPlan {
   unsigned long long *keys[2];
@@ -278,7 +300,6 @@ int launch_build_keys(const WaveDims &d, const WaveBatches &wb, const WaveBufs &
 int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
 void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int precision);
 void pbg_tc_plan_destroy(void *plan);
-bool pbg_tc_available();
 int launch_score_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st);
 int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st);
 int launch_matrix_forward(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);

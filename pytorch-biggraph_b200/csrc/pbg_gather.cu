@@ -55,23 +55,9 @@ __device__ __forceinline__ void store_row(float *row, const float4 (&v)[VEC], in
     if (d < D) st4(row + d, v[c]);
   }
 }
-// hi = tf32(v) to `row`, lo = v - hi (exact in fp32) to `row_lo`
 template <int VEC>
-__device__ __forceinline__ void store_row_split(float *row, float *row_lo, const float4 (&v)[VEC], int D, int lane) {
-#pragma unroll
-  for (int c = 0; c < VEC; ++c) {
-    int d = c * 128 + lane * 4;
-    if (d < D) {
-      float4 h = tf32_hi4(v[c]);
-      st4(row + d, h);
-      st4(row_lo + d, v[c] - h);
-    }
-  }
-}
-template <int VEC>
-__device__ __forceinline__ void put_row(float *base, float *base_lo, size_t off, const float4 (&v)[VEC], int D, int lane) {
-  if (base_lo) store_row_split<VEC>(base + off, base_lo + off, v, D, lane);
-  else store_row<VEC>(base + off, v, D, lane);
+__device__ __forceinline__ void put_row(float *base, size_t off, const float4 (&v)[VEC], int D, int lane) {
+  store_row<VEC>(base + off, v, D, lane);
 }
 // bf16-plane tier: the three planes of operand row r of block blk in array a
 template <int VEC>
@@ -173,8 +159,6 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
   size_t nrow = (size_t)blk * d.Mm + r;
   const size_t noff = nrow * d.Dp;
   float *n0 = w.X[ARR_N0] + noff, *n1 = w.X[ARR_N1] + noff;
-  float *const *XL = d.split ? w.XL : nullptr;
-  auto lo = [&](int a) -> float * { return XL ? XL[a] : nullptr; };
   float4 x[VEC], z[VEC], y0[VEC], y1[VEC];
 
   if (r < d.Pm) {                                           // ---- an edge of the chunk ----------
@@ -203,11 +187,6 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
         zero_row_planes<VEC>(w, ARR_N0, blk, r, D, lane); zero_row_planes<VEC>(w, ARR_N1, blk, r, D, lane);
         if (d.dynamic) { zero_row_planes<VEC>(w, ARR_Q0, blk, r, D, lane); zero_row_planes<VEC>(w, ARR_Q1, blk, r, D, lane); }
       }
-      if (XL) {
-        zero_row<VEC>(XL[ARR_N0] + noff, D, lane);
-        zero_row<VEC>(XL[ARR_N1] + noff, D, lane);
-        if (d.dynamic) { zero_row<VEC>(XL[ARR_Q0] + qoff, D, lane); zero_row<VEC>(XL[ARR_Q1] + qoff, D, lane); }
-      }
       if (lane == 0) {
         w.aux[ARR_N0][nrow] = 0.f; w.aux[ARR_N1][nrow] = 0.f;
         if (d.dynamic) { w.aux[ARR_Q0][qrow] = 0.f; w.aux[ARR_Q1][qrow] = 0.f; }
@@ -224,7 +203,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
 #pragma unroll
     for (int c = 0; c < VEC; ++c) y0[c] = x[c];
     float a0 = prepare_row<VEC>(y0, d.cmp);
-    put_row<VEC>(w.X[ARR_N0], lo(ARR_N0), noff, y0, D, lane);
+    put_row<VEC>(w.X[ARR_N0], noff, y0, D, lane);
     if (PL) put_row_planes<VEC>(w, ARR_N0, blk, r, y0, D, lane);
     if (d.matrix_op) {
       // linear / affine: the raw rhs row goes to R1; operator, prepare and the positive score
@@ -242,7 +221,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
       add_global<VEC>(x, w.glob[1], D, lane);
       apply_operator<VEC>(y1, x, xr, th0, d.op, D, lane, w.glob[1], scr);
       float a1 = prepare_row<VEC>(y1, d.cmp);
-      put_row<VEC>(w.X[ARR_N1], lo(ARR_N1), noff, y1, D, lane);
+      put_row<VEC>(w.X[ARR_N1], noff, y1, D, lane);
       if (PL) put_row_planes<VEC>(w, ARR_N1, blk, r, y1, D, lane);
       float s = positive_score<VEC>(y0, y1, d.cmp);
       if (lane == 0) {
@@ -254,7 +233,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
       // op_lhs(lhs row) -> Q1 (x still holds the lhs row)
       apply_operator<VEC>(z, x, xl, th1, d.op, D, lane, nullptr, scl);
       float aq1 = prepare_row<VEC>(z, d.cmp);
-      put_row<VEC>(w.X[ARR_Q1], lo(ARR_Q1), qoff, z, D, lane);
+      put_row<VEC>(w.X[ARR_Q1], qoff, z, D, lane);
       if (PL) put_row_planes<VEC>(w, ARR_Q1, blk, r, z, D, lane);
       // rhs row without operator -> N1
       load_row<VEC>(x, xr, D, lane);
@@ -262,13 +241,13 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
 #pragma unroll
       for (int c = 0; c < VEC; ++c) y1[c] = x[c];
       float a1 = prepare_row<VEC>(y1, d.cmp);
-      put_row<VEC>(w.X[ARR_N1], lo(ARR_N1), noff, y1, D, lane);
+      put_row<VEC>(w.X[ARR_N1], noff, y1, D, lane);
       if (PL) put_row_planes<VEC>(w, ARR_N1, blk, r, y1, D, lane);
       float s1 = positive_score<VEC>(y1, z, d.cmp);         // problem 1: c(rhs, op_lhs(lhs))
       // op_rhs(rhs row) -> Q0
       apply_operator<VEC>(z, x, xr, th0, d.op, D, lane, nullptr, scr);
       float aq0 = prepare_row<VEC>(z, d.cmp);
-      put_row<VEC>(w.X[ARR_Q0], lo(ARR_Q0), qoff, z, D, lane);
+      put_row<VEC>(w.X[ARR_Q0], qoff, z, D, lane);
       if (PL) put_row_planes<VEC>(w, ARR_Q0, blk, r, z, D, lane);
       float s0 = positive_score<VEC>(y0, z, d.cmp);         // problem 0: c(lhs, op_rhs(rhs))
       if (lane == 0) {
@@ -288,7 +267,6 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     if (id < 0) {
       zero_row<VEC>(dst, D, lane);
       if (PL) zero_row_planes<VEC>(w, side, blk, r, D, lane);
-      if (XL) zero_row<VEC>(XL[side] + noff, D, lane);
       if (side == 1 && d.matrix_op) zero_row<VEC>(w.R1 + noff, D, lane);
       if (lane == 0) w.aux[side][nrow] = 0.f;
       continue;
@@ -306,7 +284,7 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 8 ? 2 : 3) gather_ke
     }
     apply_operator<VEC>(z, x, xrow, th, d.op, D, lane, w.glob[side], scu);
     float a = prepare_row<VEC>(z, d.cmp);
-    put_row<VEC>(w.X[side], lo(side), noff, z, D, lane);
+    put_row<VEC>(w.X[side], noff, z, D, lane);
     if (PL) put_row_planes<VEC>(w, side, blk, r, z, D, lane);
     if (lane == 0) w.aux[side][nrow] = a;
   }
@@ -454,7 +432,7 @@ int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, c
   long long items = (long long)d.nblk * d.Mm;
   int ctas = (int)((items + GATHER_WARPS - 1) / GATHER_WARPS);
   int vec = (d.D + 127) / 128;
-  const bool plain = !d.dynamic && !d.matrix_op && !d.split && d.max_norm <= 0.f && d.cmp == PBG_CMP_DOT && (d.op == PBG_OP_NONE || w.theta[0] == nullptr);
+  const bool plain = !d.dynamic && !d.matrix_op && d.max_norm <= 0.f && d.cmp == PBG_CMP_DOT && (d.op == PBG_OP_NONE || w.theta[0] == nullptr);
   if (plain && w.XB[0] && d.reg_coef == 0.f) {      // planes only: nothing reads the fp32 operand rows then
     if (vec <= 1) gather_plain_kernel<1, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);
     else if (vec <= 2) gather_plain_kernel<2, true><<<ctas, 32 * GATHER_WARPS, 0, st>>>(d, wb, w);

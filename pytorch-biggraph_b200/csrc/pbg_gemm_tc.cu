@@ -406,8 +406,6 @@ static EncodeFn get_encode() {
   return fn;
 }
 
-bool pbg_tc_available() { return true; }
-
 // 3-D map over an array laid out [nblk][rows][ld] floats: dims {inner extent, rows, nblk}.
 static bool encode3(CUtensorMap *tm, const float *base, int inner, int rows, int nblk, int ld, long long blk_stride,
                     int box_inner, int box_rows, bool mn_major) {
@@ -536,7 +534,6 @@ void pbg_tc_plan_destroy(void *plan) { delete (TcPlan *)plan; }
 template <bool A_MN, bool B_MN, int NTERMS, bool L2EPI>
 static void launch_tc_inst(const TcMaps &maps, const TcGeom &g, const WaveDims &d, const WaveBatches &wb, int *errflag,
                            dim3 grid, size_t smem, cudaStream_t st) {
-  static bool done = false;
   TcGeom gg = g;
   if (NTERMS == 6) {
     // three planes of 64-byte rows: A 128 rows; B the tile's rows (K-major) or its 64-column boxes (MN-major)
@@ -546,10 +543,8 @@ static void launch_tc_inst(const TcMaps &maps, const TcGeom &g, const WaveDims &
     gg.nst = room / gg.stage_bytes > 4 ? 4 : room / gg.stage_bytes;
     smem = (size_t)room + 4 * 2 * 4096 + 1024;
   }
-  if (!done) {
-    cudaFuncSetAttribute(tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    done = true;
-  }
+  // if the opt-in fails the launch below fails too, and the caller's cudaGetLastError reports it
+  pbg_opt_in_smem((const void *)tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI>, (int)smem);
   // the plane tier has no split warps: producer, MMA issuer and the four epilogue warps
   tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI><<<grid, NTERMS == 6 ? 192 : TC_THREADS, smem, st>>>(maps, gg, d, wb, errflag);
 }
@@ -558,8 +553,7 @@ template <bool A_MN, bool B_MN>
 static void launch_tc(const TcMaps &maps, const TcGeom &g, int nterms, const WaveDims &d, const WaveBatches &wb, int *errflag,
                       cudaStream_t st) {
   long long tiles = (long long)((g.N + g.BN - 1) / g.BN) * ((g.M + 127) / 128) * d.nblk * 2;
-  static int sms = 0;
-  if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  const int sms = pbg_sm_count();
   dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   size_t smem = 4 * (128 * 128 + 256 * 128) + 4 * 2 * 4096 + 1024;   // 2 stages x (hi, lo) or 4 stages x raw; epilogue staging
   // the comparator epilogue of the l2 family exists only in the score kernels (both operands K-major)
@@ -601,8 +595,7 @@ int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, 
     g.M = d.D; g.N = d.Mm; g.K = d.Mm; g.BN = pl->bn_score; g.tr = 1;
     for (int p = 0; p < 2; ++p) g.C[p] = w.GX[ARR_N0 + p];
     long long tiles = (long long)((g.N + g.BN - 1) / g.BN) * ((g.M + 127) / 128) * d.nblk * 2;
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = pbg_sm_count();
     const dim3 grid((unsigned)(tiles < sms ? tiles : sms));
     const size_t smem = 4 * (128 * 128 + 256 * 128) + 4 * 2 * 4096 + 1024;
     if (pl->nterms == 6) launch_tc_inst<true, false, 6, false>(pl->gradt, g, d, wb, w.errflag, grid, smem, st);

@@ -47,15 +47,11 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
   BlockInfo bi = block_info(d, wb, blk);
   if (bi.n == 0) return;
   float *S = w.S[p] + ((size_t)blk * d.Pm + i) * d.Ms;
-  // only with dynamic relations is T itself an MMA operand; otherwise coef_kernel splits A
-  float *SLo = (d.split && d.dynamic) ? w.SL[p] + ((size_t)blk * d.Pm + i) * d.Ms : nullptr;
-  // coefficient t stored as tf32(t) + remainder when the gradient contractions run as TF32X3
   // bf16-plane tier with dynamic relations: T is an MMA operand, its planes go beside it
   unsigned short *TBr = w.TB[p] ? w.TB[p] + ((size_t)blk * 3 * d.Pm + i) * w.Kb : nullptr;
   const size_t tplane = (size_t)d.Pm * w.Kb;
   auto put = [&](int j, float t) {
-    if (SLo) { float h = tf32_hi(t); S[j] = h; SLo[j] = t - h; }
-    else S[j] = t;
+    S[j] = t;
     if (TBr) put_planes1(TBr + j, tplane, t);
   };
   size_t prow = (size_t)blk * d.Pm + i;
@@ -163,8 +159,7 @@ __global__ void colsum_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
   BlockInfo bi = block_info(d, wb, blk);
   float s = 0.f;
   const float *T = w.S[p] + (size_t)blk * d.Pm * d.Ms + j;
-  const float *TL = d.split ? w.SL[p] + (size_t)blk * d.Pm * d.Ms + j : nullptr;
-  for (int i = 0; i < bi.n; ++i) s += T[(size_t)i * d.Ms] + (TL ? TL[(size_t)i * d.Ms] : 0.f);
+  for (int i = 0; i < bi.n; ++i) s += T[(size_t)i * d.Ms];
   w.coef[p][(size_t)blk * d.Mm + j] = s;
 }
 
@@ -189,7 +184,6 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_kernel(WaveDims d, WaveB
   const float *Trow = w.S[1 - side] + ((size_t)blk * d.Pm + m) * d.Ms;   // T_other[m][j], m < Pm
   size_t arow = ((size_t)blk * d.Mm + m) * w.Ma;
   float *A = w.A[side] + arow;
-  float *AL = d.split ? w.AL[side] + arow : nullptr;
   float rowsum = 0.f;
   // bf16-plane tier: the planes of the row beside it
   unsigned short *ABr = w.AB[side] ? w.AB[side] + ((size_t)blk * 3 * d.Mm + m) * w.Kb : nullptr;
@@ -200,8 +194,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_kernel(WaveDims d, WaveB
       if (m < bi.n) a += Trow[j];
     }
     rowsum += a;
-    if (AL) { float h = tf32_hi(a); A[j] = h; AL[j] = a - h; }
-    else A[j] = a;
+    A[j] = a;
     if (ABr) put_planes1(ABr + j, (size_t)d.Mm * w.Kb, a);
   }
   if (d.cmp >= PBG_CMP_L2) {
@@ -384,7 +377,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_tile_kernel(WaveDims d, 
 int launch_loss(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
   long long items = 2ll * d.nblk * d.Pm;
   const int loss_ctas = (int)((items + LOSS_WARPS - 1) / LOSS_WARPS);
-  const bool dotlike = d.cmp < PBG_CMP_L2 && !d.split;
+  const bool dotlike = d.cmp < PBG_CMP_L2;
   if (dotlike && d.loss == PBG_LOSS_SOFTMAX && d.Ms <= 128) loss_softmax_kernel<4><<<loss_ctas, 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
   else if (dotlike && d.loss == PBG_LOSS_SOFTMAX && d.Ms <= 256) loss_softmax_kernel<8><<<loss_ctas, 32 * LOSS_WARPS, 0, st>>>(d, wb, w);
   else if (dotlike && d.loss == PBG_LOSS_SOFTMAX && d.Ms <= 512) loss_softmax_kernel<16><<<loss_ctas, 32 * LOSS_WARPS, 0, st>>>(d, wb, w);

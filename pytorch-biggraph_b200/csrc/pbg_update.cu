@@ -21,7 +21,7 @@
 // the gradient (none / translation): the kernels instantiated that way carry no dead branches.
 template <int VEC, int CMPK = -1, int OPK = -1>
 struct SlotGrad {
-  const float *g, *y, *ylo; // gradient row, prepared operand row (+ its low part in split mode)
+  const float *g, *y;      // gradient row, prepared operand row
   const float *theta;      // operator row or null
   float dotgy, inv, cf;    // cos: <g', y> and 1/|z|; l2 family: coefficient of y
   float rc;                // N3 regularizer weight if the slot is an adjusted positive row, else 0
@@ -37,7 +37,6 @@ struct SlotGrad {
     D = d.D; op = OPK == 0 ? PBG_OP_NONE : d.op; cmp = CMPK >= 0 ? CMPK : d.cmp;
     size_t xr = (size_t)blk * w.xrows[a] + r, gr = (size_t)blk * w.grows[a] + r;
     y = w.X[a] + xr * d.Dp;
-    ylo = d.split ? w.XL[a] + xr * d.Dp : nullptr;
     g = gstage ? gstage : w.GX[a] + gr * d.Dp;
     theta = nullptr;
     cf = 0.f; inv = 1.f; dotgy = 0.f;
@@ -82,8 +81,7 @@ struct SlotGrad {
     }
   }
   __device__ __forceinline__ float4 yv(int dd) const {
-    float4 v = ld4(y + dd);
-    return ylo ? v + ld4(ylo + dd) : v;
+    return ld4(y + dd);
   }
   // gradient w.r.t. the operator output z at elements [dd, dd+4)
   // gradient that reaches the prepared row: from the contractions, plus the regularizer's own
@@ -116,13 +114,13 @@ struct SlotGrad {
 // d(loss)/d(operator row) contributed by one slot whose operand went through the operator:
 // needs the gradient at the operator output (gz) and the raw embedding row x.
 template <int VEC, int CMPK = -1>
-__device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC, CMPK, -1> &sg, const float *x, const float *xlo, float xscale, int dd,
+__device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC, CMPK, -1> &sg, const float *x, float xscale, int dd,
                                                 const float *xadd = nullptr) {
   // xadd: global embedding added to the raw row before the operator (null: none)
   float4 v = sg.gz(dd);
   if (sg.op == PBG_OP_TRANSLATION) return v;
   auto raw = [&](int e) {
-    float4 r = (xlo ? ld4(x + e) + ld4(xlo + e) : ld4(x + e)) * xscale;
+    float4 r = ld4(x + e) * xscale;
     if (xadd) r = r + ld4(xadd + e);
     return r;
   };
@@ -248,13 +246,12 @@ __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, 
     sg.init(d, wb, w, qa, oc.blk, oc.r, oc.b, lane);
     size_t nrow = (size_t)oc.blk * w.xrows[na] + oc.r;
     const float *x = w.X[na] + nrow * d.Dp;
-    const float *xlo = d.split ? w.XL[na] + nrow * d.Dp : nullptr;
     float xscale = (CMPK >= 0 ? CMPK : d.cmp) == PBG_CMP_COS ? 1.0f / w.aux[na][nrow] : 1.0f;
 #pragma unroll
     for (int c = 0; c < VEC; ++c) {
       int dd = c * 128 + lane * 4;
       if (dd < D) {
-        acc[c] = acc[c] + op_param_grad<VEC, CMPK>(sg, x, xlo, xscale, dd);
+        acc[c] = acc[c] + op_param_grad<VEC, CMPK>(sg, x, xscale, dd);
         // N3 regularizer on the edge's own parameter row (still as the wave found it in global memory)
         if (d.reg_coef != 0.f && sg.theta) acc[c] = acc[c] + n3_grad4(sg.theta, dd, D, d.op == PBG_OP_COMPLEX_DIAGONAL) * d.reg_coef;
       }
@@ -607,7 +604,7 @@ __global__ void __launch_bounds__(32 * UPD_WARPS) relgrad_std_kernel(WaveDims d,
 #pragma unroll
       for (int c = 0; c < VEC; ++c) {
         int dd = c * 128 + lane * 4;
-        if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, nullptr, xsc, dd, w.glob[1]);
+        if (dd < D) acc[c] = acc[c] + op_param_grad<VEC>(sg, x, xsc, dd, w.glob[1]);
       }
     }
   }
@@ -841,25 +838,20 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   const int hub_ctas = 296;
   size_t hub_smem = (size_t)d.k * VEC * 128 * sizeof(float);            // per-batch totals of one hub row
   size_t red_smem = (size_t)UPD_WARPS * VEC * 128 * sizeof(float);       // eight partial sums of one batch of a big row
-  static bool attr_done[2] = {false, false};
   // the attribute is set once for the largest wave this row width allows in 227 KB
   size_t hub_smem_max = (size_t)PBG_KMAX * VEC * 128 * sizeof(float);
   if (hub_smem_max > 227 * 1024) hub_smem_max = 227 * 1024;
-  if (!attr_done[0]) {
-    cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_EMB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem_max);
-    cudaFuncSetAttribute(hub_reduce_kernel<VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_smem);
-    cudaFuncSetAttribute(relgrad_std_kernel<VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_smem);
-    cudaFuncSetAttribute(globgrad_kernel<VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)red_smem);
-    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
-    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
-    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
-    cudaFuncSetAttribute(tile_update_kernel<VEC, RULE_EMB, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float)));
-    attr_done[0] = true;
-  }
+  // per device (a process may hold contexts on several GPUs); a failed opt-in makes the launch fail,
+  // which the caller's cudaGetLastError reports
+  const int tile_smem_max = (int)((size_t)TILE_WARPS_EMB * TILE * VEC * 128 * sizeof(float));
+  pbg_opt_in_smem((const void *)hub_update_kernel<VEC, RULE_EMB>, (int)hub_smem_max);
+  pbg_opt_in_smem((const void *)hub_reduce_kernel<VEC>, (int)red_smem);
+  pbg_opt_in_smem((const void *)relgrad_std_kernel<VEC>, (int)red_smem);
+  pbg_opt_in_smem((const void *)globgrad_kernel<VEC>, (int)red_smem);
+  pbg_opt_in_smem((const void *)tile_update_kernel<VEC, RULE_EMB, 0>, tile_smem_max);
+  pbg_opt_in_smem((const void *)tile_update_kernel<VEC, RULE_EMB, 1>, tile_smem_max);
+  pbg_opt_in_smem((const void *)tile_update_kernel<VEC, RULE_EMB, 2>, tile_smem_max);
+  pbg_opt_in_smem((const void *)tile_update_kernel<VEC, RULE_EMB, 3>, tile_smem_max);
   bool has_op = d.op != PBG_OP_NONE && w.theta[0] != nullptr;
   if (has_op && !d.dynamic && !d.matrix_op) {
     relgrad_std_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, red_smem, st>>>(d, wb, w);
@@ -886,10 +878,7 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   launches += 2;
   if (has_op) {
     if (d.dynamic) {
-      if (!attr_done[1]) {
-        cudaFuncSetAttribute(hub_update_kernel<VEC, RULE_REL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)hub_smem_max);
-        attr_done[1] = true;
-      }
+      pbg_opt_in_smem((const void *)hub_update_kernel<VEC, RULE_REL>, (int)hub_smem_max);
       cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
       if (d.cmp == PBG_CMP_DOT && d.reg_coef == 0.f)
         tile_update_kernel<VEC, RULE_REL, 3><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);

@@ -9,6 +9,7 @@ pairwise-disjoint buckets; `ring_exchange` moves a partition (embedding rows + R
 the next GPU between rounds with torch.distributed point-to-point calls -- NCCL over NVLink on
 GPUs, gloo on CPU for the tests.  The receiving GPU reads the partition only from its own memory.
 """
+import math
 from typing import List, Sequence, Tuple
 
 import torch
@@ -16,8 +17,11 @@ import torch.distributed as dist
 
 
 def partition_bounds(num_entities: int, num_partitions: int) -> List[int]:
-    """Partition p owns ids [bounds[p], bounds[p+1])."""
-    return [-(-p * num_entities // num_partitions) for p in range(num_partitions + 1)]
+    """Partition p owns ids [bounds[p], bounds[p+1]).  bounds[p] = ceil(p / P * N) evaluated in double
+    precision exactly as the reference does (part_start, torchbiggraph/converters/dictionary.py:28-29):
+    where p * N / P is an integer the floating-point product can land just above it, and data
+    partitioned by the reference then has that bound one row higher than the exact ceiling."""
+    return [math.ceil(p / num_partitions * num_entities) for p in range(num_partitions + 1)]
 
 
 def partition_of(ids: torch.Tensor, bounds: Sequence[int]) -> Tuple[torch.Tensor, torch.Tensor]:

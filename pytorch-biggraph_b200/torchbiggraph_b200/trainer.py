@@ -376,17 +376,20 @@ def _batches_group_by_relation(rel_sorted: torch.Tensor, batch_size: int, genera
 
 def process_in_batches(batch_size: int, model: MultiRelationEmbedder, batch_processor: B200Trainer,
                        edges: EdgeList, indices: Optional[torch.Tensor] = None, delay: float = 0.0) -> Stats:
-    """torchbiggraph/batching.py:91-125 with the batch loop moved onto the device."""
+    """torchbiggraph/batching.py:91-125 with the batch loop moved onto the device.  Per-edge weights
+    (EdgeList.weight) travel with the edges.  With standard relations the batches come in the
+    reference's order (batching.py:58-79); consecutive batches that read the same pair of embedding
+    tables go to the library in one call, so relations over different entity types simply cut the
+    list into more calls."""
     if indices is not None:
         edges = edges[indices]
     if delay > 0:
         time.sleep(delay)
-    if edges.has_weight():
-        raise NotImplementedError("per-edge weights have no device code in torchbiggraph_b200")
     n = len(edges)
     if n == 0:
         return Stats(count=0)
     lhs, rhs = edges.lhs.to_tensor().contiguous(), edges.rhs.to_tensor().contiguous()
+    weights = torch.as_tensor(edges.weight) if edges.has_weight() else None
     if model.num_dynamic_rels > 0:
         rel = edges.get_relation_type_as_vector().contiguous()
         batches = [(o, min(batch_size, n - o), 0) for o in range(0, n, batch_size)]
@@ -397,8 +400,29 @@ def process_in_batches(batch_size: int, model: MultiRelationEmbedder, batch_proc
     else:
         order = torch.argsort(edges.rel, stable=True)
         lhs, rhs, rel_sorted = lhs[order].contiguous(), rhs[order].contiguous(), edges.rel[order]
+        if weights is not None:
+            weights = weights[order.to(weights.device)]
         rel = None
         batches = _batches_group_by_relation(rel_sorted.cpu(), batch_size)
-        # one call per (lhs table, rhs table) pair is needed; relations sharing entity types go together
-    stats = batch_processor.train_batches(model, lhs, rhs, rel, batches)
+    stats: List[Stats] = []
+    for run in _runs_by_table_pair(model, batches):
+        stats.extend(batch_processor.train_batches(model, lhs, rhs, rel, run, weights=weights))
     return Stats.sum(stats)
+
+
+def _runs_by_table_pair(model: MultiRelationEmbedder, batches):
+    """Cuts a batch list into maximal runs of consecutive batches whose relations read the same
+    (lhs table, rhs table) pair; one library call trains one run."""
+    if model.num_dynamic_rels > 0 or not batches:
+        return [batches] if batches else []
+    runs, cur, cur_key = [], [], None
+    for b in batches:
+        wl, wr = model.tables_for(b[2])
+        key = (wl.data_ptr(), wr.data_ptr())
+        if cur and key != cur_key:
+            runs.append(cur)
+            cur = []
+        cur_key = key
+        cur.append(b)
+    runs.append(cur)
+    return runs

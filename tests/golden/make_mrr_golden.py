@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(HERE))
 sys.path.insert(0, HERE)
 from make_golden import _bootstrap  # noqa: E402
-from mrr_util import CASES, COMMON, epoch_order, mrr_rhs, planted_graph  # noqa: E402
+from mrr_util import CASES, COMMON, epoch_order, mrr_rhs, planted_graph, setting  # noqa: E402
 
 
 def run(case, seed=0):
@@ -31,14 +31,14 @@ def run(case, seed=0):
     from torchbiggraph.train_cpu import Trainer, make_optimizer
     from torchbiggraph.types import Side
     c = CASES[case]
-    torch.set_num_threads(4)
+    torch.set_num_threads(8)
     torch.manual_seed(seed)      # seeds the reference's uniform-negative draws
     (lhs, rhs, rel), test, W0 = planted_graph(case)
     cfg = ConfigSchema(entities={"e": EntitySchema(num_partitions=1)},
                        relations=[RelationSchema(name="r", lhs="e", rhs="e", operator=c["op"])], dimension=c["D"],
                        entity_path="x", edge_paths=["y"], checkpoint_path="z", comparator=COMMON["comp"],
-                       loss_fn=COMMON["loss"], global_emb=False, batch_size=COMMON["batch"],
-                       num_batch_negs=COMMON["nb"], num_uniform_negs=COMMON["nu"], lr=COMMON["lr"],
+                       loss_fn=COMMON["loss"], global_emb=False, batch_size=setting(case, "batch"),
+                       num_batch_negs=setting(case, "nb"), num_uniform_negs=setting(case, "nu"), lr=COMMON["lr"],
                        dynamic_relations=c["dyn"])
     if c["dyn"]:
         class RelCount:
@@ -52,7 +52,7 @@ def run(case, seed=0):
     model.set_embeddings("e", Side.LHS, emb)
     model.set_embeddings("e", Side.RHS, emb)
     trainer.partitioned_optimizers["e", 0] = make_optimizer(cfg, [emb], True)
-    B = COMMON["batch"]
+    B = setting(case, "batch")
     for ep in range(c["epochs"]):
         order = epoch_order(len(lhs), ep)
         for o in range(0, len(order), B):
@@ -71,14 +71,20 @@ def run(case, seed=0):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a PyTorch-BigGraph checkout")
+    ap.add_argument("--only", nargs="*", default=None, help="record these cases only; the others keep their recorded values")
     args = ap.parse_args()
     _bootstrap(args.reference)
     out, runs = {}, {}
-    for case in CASES:
+    path = os.path.join(HERE, "mrr_planted.json")
+    if args.only and os.path.exists(path):
+        with open(path) as f:
+            old = json.load(f)
+        out, runs = old["mrr"], old["runs"]
+    for case in (args.only or CASES):
         runs[case] = [run(case, seed) for seed in (0, 1, 2)]      # spread over negative-sampling seeds
         out[case] = float(np.mean(runs[case]))
         print(case, out[case], runs[case], flush=True)
-    with open(os.path.join(HERE, "mrr_planted.json"), "w") as f:
+    with open(path, "w") as f:
         json.dump({"mrr": out, "runs": runs, "cases": CASES, "common": COMMON}, f, indent=1)
 
 

@@ -3,11 +3,25 @@ reference's MRR (tests/golden/make_mrr_golden.py) and by the GPU end-to-end test
 import numpy as np
 
 CASES = {
-    # name: entities, relations, edges, noise, dim, operator, dynamic, epochs
+    # name: entities, relations, edges, noise, dim, operator, dynamic, epochs (+ overrides of COMMON)
     "std_translation": dict(N=3000, R=1, E=40000, noise=0.2, D=32, op="translation", dyn=False, epochs=6),
     "dyn_complex_diagonal": dict(N=3000, R=8, E=40000, noise=0.2, D=32, op="complex_diagonal", dyn=True, epochs=6),
+    # the step shape of the 15k-entity multi-relation configuration: dim 400, complex_diagonal / dot / softmax with
+    # dynamic relations, batches of 5000 cut into chunks of 1000 batch negatives, no uniform negatives; relation
+    # frequencies Zipf(1.0)
+    "kg15k_shape": dict(N=14951, R=40, E=120000, noise=0.2, D=400, op="complex_diagonal", dyn=True, epochs=4,
+                        batch=5000, nb=1000, nu=0, rel_zipf=1.0),
+    # power-law endpoints (Zipf 1.1 over permuted ids: the top row collects about a tenth of all endpoints, so a
+    # wave of batches in flight reads hub rows that many of its own batches update), dim 256, 100 + 100 negatives
+    "powerlaw_hubs": dict(N=20000, R=1, E=200000, noise=0.2, D=256, op="translation", dyn=False, epochs=8,
+                          batch=1000, nb=100, nu=100, endpoint_zipf=1.1, held_out=5000),
 }
 COMMON = dict(comp="dot", loss="softmax", lr=0.1, batch=500, nb=50, nu=50, init_scale=1e-3, held_out=1500)
+
+
+def setting(case, key):
+    """A training setting of the case: its own value if it has one, else the common one."""
+    return CASES[case].get(key, COMMON[key])
 
 
 def planted_graph(case, seed=0):
@@ -16,12 +30,20 @@ def planted_graph(case, seed=0):
     c = CASES[case]
     rng = np.random.default_rng(seed)
     perms = [rng.permutation(c["N"]) for _ in range(c["R"])]
-    rel = rng.integers(0, c["R"], c["E"])
-    lhs = rng.integers(0, c["N"], c["E"])
+    if "rel_zipf" in c:
+        pr = np.arange(1, c["R"] + 1, dtype=np.float64) ** -c["rel_zipf"]
+        rel = rng.choice(c["R"], c["E"], p=pr / pr.sum())
+    else:
+        rel = rng.integers(0, c["R"], c["E"])
+    if "endpoint_zipf" in c:
+        pe = np.arange(1, c["N"] + 1, dtype=np.float64) ** -c["endpoint_zipf"]
+        lhs = rng.permutation(c["N"])[rng.choice(c["N"], c["E"], p=pe / pe.sum())]
+    else:
+        lhs = rng.integers(0, c["N"], c["E"])
     rhs = np.array([perms[r][u] for r, u in zip(rel, lhs)])
     noisy = rng.random(c["E"]) < c["noise"]
     rhs[noisy] = rng.integers(0, c["N"], int(noisy.sum()))
-    h = COMMON["held_out"]
+    h = c.get("held_out", COMMON["held_out"])
     clean = np.flatnonzero(~noisy)
     test_idx = clean[:h]
     mask = np.ones(c["E"], bool)

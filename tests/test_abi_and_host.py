@@ -84,7 +84,7 @@ def test_registries_hold_the_reference_names():
         assert T.COMPARATORS.get_class(name).native_code is not None
     for name in ("logistic", "ranking", "softmax"):
         assert T.LOSS_FUNCTIONS.get_class(name).native_code is not None
-    with pytest.raises(RuntimeError):
+    with pytest.raises(NotImplementedError, match="no_such_operator"):     # plugin.py:35-40; callers catch this type
         T.OPERATORS.get_class("no_such_operator")
 
 
@@ -96,10 +96,15 @@ def test_reregistering_a_different_class_raises_like_the_reference():
         pass
 
     reg.register_as("x")(A)          # same class again is fine
+    reg.register("x", A)
     with pytest.raises(RuntimeError):
         @reg.register_as("x")
         class B:
             pass
+    with pytest.raises(RuntimeError):
+        reg.register("x", int)
+    reg.register("y", int)
+    assert reg.get_class("y") is int
 
 
 def test_custom_loss_without_device_code_is_refused():
@@ -179,6 +184,29 @@ def test_relation_grouped_batches_cover_every_edge_once():
         assert 0 < n <= 100 and bool((rel[off:off + n] == r).all())
         seen[off:off + n] += 1
     assert bool((seen == 1).all())
+
+
+def test_batch_list_is_cut_into_runs_that_read_one_pair_of_tables():
+    """process_in_batches hands consecutive batches of one (lhs table, rhs table) pair to the library in
+    one call and starts a new call where the pair changes; the order of the batches is kept."""
+    from torchbiggraph_b200.trainer import _runs_by_table_pair
+
+    class FakeModel:
+        num_dynamic_rels = 0
+        tabs = {0: (torch.zeros(2, 4), torch.zeros(2, 4))}
+
+        def tables_for(self, r):
+            return self.tabs[r]
+
+    m = FakeModel()
+    m.tabs[1] = (m.tabs[0][0], torch.zeros(3, 4))      # relation 1 reads another rhs table
+    m.tabs[2] = m.tabs[0]                              # relation 2 shares relation 0's tables
+    batches = [(0, 5, 0), (5, 5, 2), (10, 5, 1), (15, 5, 1), (20, 5, 0)]
+    runs = _runs_by_table_pair(m, batches)
+    assert runs == [[(0, 5, 0), (5, 5, 2)], [(10, 5, 1), (15, 5, 1)], [(20, 5, 0)]]
+    assert _runs_by_table_pair(m, []) == []
+    m.num_dynamic_rels = 3
+    assert _runs_by_table_pair(m, batches) == [batches]
 
 
 def test_optimizer_state_dict_round_trip_keeps_reference_format():

@@ -3,6 +3,7 @@ import os
 import tempfile
 
 import pytest
+import numpy as np
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -29,6 +30,20 @@ def test_partition_bounds_follow_the_ceil_split():
     ids = torch.tensor([0, b[1] - 1, b[1], 4_847_570])
     part, off = partition_of(ids, b)
     assert part.tolist() == [0, 0, 1, 15] and off.tolist() == [0, b[1] - 1, 0, 4_847_570 - b[15]]
+
+
+def test_partition_bounds_reproduce_the_reference_float_rounding():
+    """part_start is math.ceil(part / num_parts * size) in floating point (dictionary.py:28-29): where
+    part * size / num_parts is an exact integer the float product can round up past it."""
+    import math
+    assert partition_bounds(97078560, 100)[55] == 53393209          # exact ceiling: 53393208
+    rng = np.random.default_rng(0)
+    for _ in range(2000):
+        N, P = int(rng.integers(1, 10**9)), int(rng.integers(1, 300))
+        b = partition_bounds(N, P)
+        assert b[0] == 0 and b[P] == N and all(b[i] <= b[i + 1] for i in range(P))
+        p = int(rng.integers(0, P + 1))
+        assert b[p] == math.ceil(p / P * N)
 
 
 def test_assign_round_deals_buckets_to_ranks():

@@ -1,0 +1,87 @@
+"""process_in_batches (torchbiggraph/batching.py:91-125 moved onto the device) against the same
+batches handed over one at a time through process_one_batch: per-edge weights travel with the
+edges, and relations over different entity types are trained by separate library calls in the
+reference's batch order.  No uniform negatives, so nothing is drawn at random inside the step."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-4
+
+
+def _setup(two_types, seed=5, D=32, N=400, M=300):
+    import torchbiggraph_b200 as T
+    rng = np.random.default_rng(seed)
+    ents = {"e": T.EntitySchema()}
+    rels = [T.RelationSchema("r0", "e", "e", operator="translation", weight=1.0)]
+    if two_types:
+        ents["f"] = T.EntitySchema()
+        rels += [T.RelationSchema("r1", "e", "f", operator="translation", weight=0.5),
+                 T.RelationSchema("r2", "e", "e", operator="translation", weight=2.0)]
+    cfg = T.ConfigSchema(entities=ents, relations=rels, dimension=D, comparator="dot", loss_fn="softmax", lr=0.1,
+                         batch_size=100, num_batch_negs=50, num_uniform_negs=0)
+    We = (rng.standard_normal((N, D)) * 0.1).astype(np.float32)
+    Wf = (rng.standard_normal((M, D)) * 0.1).astype(np.float32)
+    th = (rng.standard_normal((len(rels), D)) * 0.1).astype(np.float32)
+
+    def build():
+        model = T.make_model(cfg, "cuda")
+        model.rhs_op_table.copy_(torch.tensor(th).cuda())
+        tr = T.B200Trainer(T.make_optimizer(cfg, model.parameters(), False),
+                           T.LOSS_FUNCTIONS.get_class("softmax")(margin=0.1), [r.weight for r in rels])
+        we, wf = torch.tensor(We).cuda(), torch.tensor(Wf).cuda()
+        model.set_embeddings("e", T.Side.LHS, we)
+        model.set_embeddings("e", T.Side.RHS, we)
+        tr.partitioned_optimizers["e", 0] = T.make_optimizer(cfg, [we], True)
+        if two_types:
+            model.set_embeddings("f", T.Side.RHS, wf)
+            tr.partitioned_optimizers["f", 0] = T.make_optimizer(cfg, [wf], True)
+        return model, tr, we, wf
+
+    n = 730
+    rel = rng.integers(0, len(rels), n) if two_types else np.zeros(n, np.int64)
+    lhs = rng.integers(0, N, n)
+    rhs = np.where(rel == 1, rng.integers(0, M, n), rng.integers(0, N, n))
+    wgt = (rng.random(n) * 2).astype(np.float32)
+    return T, build, lhs, rhs, rel, wgt
+
+
+@pytest.mark.parametrize("two_types", [False, True], ids=["one_relation_weighted", "two_entity_types_weighted"])
+def test_process_in_batches_equals_batch_by_batch(two_types):
+    from torchbiggraph_b200.trainer import _batches_group_by_relation
+    T, build, lhs, rhs, rel, wgt = _setup(two_types)
+    t = lambda a: torch.tensor(np.asarray(a))
+    ent = lambda a: T.EntityList.from_tensor(t(a))
+    # (a) the whole edge list in one call of process_in_batches
+    model_a, tr_a, we_a, wf_a = build()
+    edges = T.EdgeList(ent(lhs), ent(rhs), t(rel) if two_types else t(0), t(wgt))
+    torch.manual_seed(123)
+    total = T.process_in_batches(100, model_a, tr_a, edges)
+    # (b) the same batches in the same order, one process_one_batch each
+    model_b, tr_b, we_b, wf_b = build()
+    if two_types:
+        order = np.argsort(rel, kind="stable")
+        torch.manual_seed(123)
+        batches = _batches_group_by_relation(t(rel[order]), 100)
+    else:
+        order = np.arange(len(lhs))
+        batches = [(o, min(100, len(lhs) - o), 0) for o in range(0, len(lhs), 100)]
+    parts = []
+    for off, cnt, r in batches:
+        idx = order[off:off + cnt]
+        parts.append(tr_b.process_one_batch(model_b, T.EdgeList(ent(lhs[idx]), ent(rhs[idx]), t(r), t(wgt[idx]))))
+    want = T.Stats.sum(parts)
+    assert total.count == want.count == len(lhs)
+    assert total.metrics["loss"] == pytest.approx(want.metrics["loss"], rel=RTOL)
+    assert total.metrics["violators_lhs"] == want.metrics["violators_lhs"]
+    np.testing.assert_allclose(we_a.cpu().numpy(), we_b.cpu().numpy(), rtol=RTOL, atol=1e-6)
+    np.testing.assert_allclose(model_a.rhs_op_table.cpu().numpy(), model_b.rhs_op_table.cpu().numpy(), rtol=RTOL, atol=1e-6)
+    if two_types:
+        np.testing.assert_allclose(wf_a.cpu().numpy(), wf_b.cpu().numpy(), rtol=RTOL, atol=1e-6)
+    # the weights did enter the loss: the unweighted list gives another total
+    model_c, tr_c, _, _ = build()
+    torch.manual_seed(123)
+    plain = T.process_in_batches(100, model_c, tr_c, T.EdgeList(ent(lhs), ent(rhs), t(rel) if two_types else t(0)))
+    assert abs(plain.metrics["loss"] - total.metrics["loss"]) > 1e-3 * abs(total.metrics["loss"])

@@ -10,13 +10,22 @@ import pytest
 import torch
 
 from golden_util import GOLDEN
-from mrr_util import CASES, COMMON, epoch_order, mrr_rhs, planted_graph
+from mrr_util import CASES, COMMON, epoch_order, mrr_rhs, planted_graph, setting
 
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("k,precision", [(1, "fp32"), (1, "tf32x3"), (16, "tf32x3")])
-@pytest.mark.parametrize("case", sorted(CASES))
+# The two small graphs run in every tier, sequentially and with batches in flight; the two graphs at
+# the shapes of the benchmark configurations (dim 400 with 1000-row chunks; power-law endpoints at
+# dim 256) run in the arithmetic and with the 14 batches in flight that bench.py uses.
+SMALL = ("std_translation", "dyn_complex_diagonal")
+RUNS = [(case, k, prec) for case in SMALL
+        for k, prec in ((1, "fp32"), (1, "tf32x3"), (16, "tf32x3"), (1, "bf16x6"), (14, "bf16x6"))]
+RUNS += [("kg15k_shape", 1, "tf32x3"), ("kg15k_shape", 14, "bf16x6"),
+         ("powerlaw_hubs", 1, "bf16x6"), ("powerlaw_hubs", 14, "bf16x6"), ("powerlaw_hubs", 14, "tf32x3")]
+
+
+@pytest.mark.parametrize("case,k,precision", RUNS)
 def test_held_out_mrr_matches_reference_trainer(case, k, precision):
     import torchbiggraph_b200 as T
     with open(os.path.join(GOLDEN, "mrr_planted.json")) as f:
@@ -25,7 +34,7 @@ def test_held_out_mrr_matches_reference_trainer(case, k, precision):
     (lhs, rhs, rel), test, W0 = planted_graph(case)
     cfg = T.ConfigSchema(entities={"e": T.EntitySchema()}, relations=[T.RelationSchema("r", "e", "e", operator=c["op"])],
                          dimension=c["D"], comparator=COMMON["comp"], loss_fn=COMMON["loss"], lr=COMMON["lr"],
-                         batch_size=COMMON["batch"], num_batch_negs=COMMON["nb"], num_uniform_negs=COMMON["nu"],
+                         batch_size=setting(case, "batch"), num_batch_negs=setting(case, "nb"), num_uniform_negs=setting(case, "nu"),
                          dynamic_relations=c["dyn"], num_dynamic_rels=c["R"] if c["dyn"] else 0,
                          precision=precision, batches_in_flight=k)
     model = T.make_model(cfg, "cuda")
@@ -36,7 +45,7 @@ def test_held_out_mrr_matches_reference_trainer(case, k, precision):
     model.set_embeddings("e", T.Side.RHS, W)
     trainer.partitioned_optimizers["e", 0] = T.make_optimizer(cfg, [W], True)
     trainer.seed = 17
-    B = COMMON["batch"]
+    B = setting(case, "batch")
     for ep in range(c["epochs"]):
         order = epoch_order(len(lhs), ep)
         edges = T.EdgeList(T.EntityList.from_tensor(torch.tensor(lhs[order])), T.EntityList.from_tensor(torch.tensor(rhs[order])),

@@ -58,3 +58,47 @@ def test_static_entry_point_rejects_sizes_beyond_its_scratch():
     assert float(W.abs().sum()) == 0.0                     # nothing was touched
     st = L.pbg_row_adagrad_static(_ptr(W), _ptr(G), 10, 30, _ptr(rows), _ptr(grads), 4, 0.1, None)
     assert st == _lib.PBG_ERR_UNSUPPORTED                  # dim must be a multiple of 4
+
+
+def _numpy_row_adagrad(W, G, rows, grads, lr):
+    """RowAdagrad.step on a sparse gradient in float64 (torchbiggraph/row_adagrad.py:80-96): duplicates are
+    summed, G += mean(g^2), w -= lr g / (sqrt(G) + 1e-10).  Rows outside the table are left out."""
+    W, G = W.astype(np.float64), G.astype(np.float64)
+    order = np.argsort(rows, kind="stable")
+    r, g = rows[order], grads.astype(np.float64)[order]
+    ok = (r >= 0) & (r < W.shape[0])
+    r, g = r[ok], g[ok]
+    uniq, start = np.unique(r, return_index=True)
+    total = np.add.reduceat(g, start, axis=0)
+    G[uniq] += (total * total).mean(axis=1)
+    W[uniq] -= lr * total / (np.sqrt(G[uniq]) + 1e-10)[:, None]
+    return W, G
+
+
+def test_static_entry_point_matches_numpy_at_its_maximum_and_reports_bad_rows():
+    """The entry point alone (no context anywhere in this test) against a float64 NumPy step at the
+    stated maximum of 16384 gradient rows; then a call with one row id past the table and one negative
+    id, which must come back as PBG_ERR_INDEX_RANGE with those two gradient rows left out and every
+    other row stepped; then a clean call, which must return PBG_OK again -- the error word lives in the
+    array every call shares, so this shows that a call starts from a cleared one."""
+    from torchbiggraph_b200 import _lib
+    L = _lib.lib()
+    rng = np.random.default_rng(11)
+    N, D, n = 5000, 128, 16384
+    W = rng.standard_normal((N, D)).astype(np.float32)
+    G = rng.random(N).astype(np.float32)
+    Wd, Gd = torch.tensor(W).cuda(), torch.tensor(G).cuda()
+    Wn, Gn = W, G
+    for call, bad in enumerate((False, True, False)):
+        rows = rng.integers(0, 700, n)
+        if bad:
+            rows[123], rows[4567] = N, -3
+        grads = rng.standard_normal((n, D)).astype(np.float32)
+        rd, gd = torch.tensor(rows).cuda(), torch.tensor(grads).cuda()
+        st = L.pbg_row_adagrad_static(_ptr(Wd), _ptr(Gd), N, D, _ptr(rd), _ptr(gd), n, 0.05, None)
+        assert st == (_lib.PBG_ERR_INDEX_RANGE if bad else 0), (call, L.pbg_status_string(st))
+        Wn, Gn = _numpy_row_adagrad(Wn, Gn, rows, grads, 0.05)
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(Wd.cpu().numpy(), Wn, rtol=RTOL, atol=1e-6, err_msg=f"call {call}")
+        np.testing.assert_allclose(Gd.cpu().numpy(), Gn, rtol=RTOL, atol=1e-7, err_msg=f"call {call}")
+        Wn, Gn = Wd.cpu().numpy(), Gd.cpu().numpy()        # the next call starts from the device's fp32 values
