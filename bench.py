@@ -85,6 +85,7 @@ PRECISION_NOTES = {
     "fp32": "fp32 FMA on the CUDA cores",
     "tf32x3": "tcgen05 kind::tf32, operands split hi + lo in shared memory, three MMAs per product, fp32 accumulation; parity tier rtol 1e-4",
     "bf16x6": "tcgen05 kind::f16 on three bf16 planes per fp32 operand value (24 mantissa bits), six plane products, fp32 accumulation; parity tier rtol 1e-4",
+    "bf16x3": "tcgen05 kind::f16 on two bf16 planes per fp32 operand value (16 mantissa bits), three plane products (b0.b0 + b0.b1 + b1.b0), fp32 accumulation; held to the rtol 1e-4 fixtures",
     "tf32": "tcgen05 kind::tf32, single pass; parity tier rtol 1e-3",
 }
 REF_BATCHES = 5          # batches per worker in one step of the CPU reference arm
@@ -675,7 +676,7 @@ def run_b200(args, w):
     traffic = None if per_edge is None else per_edge * edges_prof / dom_kernel_launches
     if dom in model_flops:
         ach = per_class[dom]["TFLOPs"]
-        per_product = {"tf32x3": 6.0, "tf32": 2.0, "bf16x6": 6.0}.get(args.precision)     # TF32 runs at half the bf16 rate; TF32X3 issues three MMAs per product, BF16X6 six bf16 ones
+        per_product = {"tf32x3": 6.0, "tf32": 2.0, "bf16x6": 6.0, "bf16x3": 3.0}.get(args.precision)     # TF32 runs at half the bf16 rate; TF32X3 issues three MMAs per product, BF16X6 six bf16 ones
         roof = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
                 "frac": round(ach / pk["tflops"], 4), "traffic": traffic, "traffic_source": traffic_source,
                 "ceiling_for_precision": None if per_product is None else round(pk["tflops"] / per_product, 1),
@@ -713,7 +714,7 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--lr", type=float, default=0.1)
     ap.add_argument("--k", type=int, default=14, help="batches in flight (1 = sequential batches, the reference's GPU semantics)")
-    ap.add_argument("--precision", default=None, choices=["fp32", "tf32x3", "tf32", "bf16x6"],
+    ap.add_argument("--precision", default=None, choices=["fp32", "tf32x3", "tf32", "bf16x6", "bf16x3"],
                     help="arithmetic of the contractions.  tf32x3: tcgen05 TF32 with 3-term split, the rtol 1e-4 tier; "
                          "bf16x6: tcgen05 bf16 on three planes per fp32 operand (24 mantissa bits), six plane products, "
                          "the rtol 1e-4 tier; fp32: CUDA cores; tf32: single pass, the rtol 1e-3 tier.  Default: the faster "

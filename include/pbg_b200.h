@@ -56,12 +56,18 @@ typedef enum {
   PBG_PREC_TF32X3 = 1,   /* tcgen05 TF32 tensor cores, 3-term error-compensated split, fp32
                             accumulation in tensor memory; the rtol 1e-4 tier                 */
   PBG_PREC_TF32 = 2,     /* tcgen05 TF32 tensor cores, single pass; the rtol 1e-3 tier        */
-  PBG_PREC_BF16X6 = 3    /* tcgen05 bf16 tensor cores on three bf16 planes per fp32 operand
+  PBG_PREC_BF16X6 = 3,   /* tcgen05 bf16 tensor cores on three bf16 planes per fp32 operand
                             (x = b0 + b1 + b2, 24 mantissa bits), the six plane products of
                             order <= 2, fp32 accumulation in tensor memory; the rtol 1e-4 tier.
                             Not for the linear / affine operators: pbg_create refuses those.
                             Pays where the contractions dominate (large chunks, dim >= 400):
                             the planes are 6 bytes per operand value where fp32 is 4          */
+  PBG_PREC_BF16X3 = 4    /* the same on TWO planes per operand (x ~ b0 + b1, 16 mantissa bits) and the
+                            three plane products b0.b0 + b0.b1 + b1.b0: half the tensor-core work
+                            and 4 bytes per operand value.  Every product carries a relative
+                            error of about 2^-17 (the dropped terms), some 30 times that of fp32
+                            rounding; sums of such products stay inside rtol 1e-4 unless they
+                            cancel heavily.  Not for linear / affine.                            */
 } pbg_precision;
 
 /* The keys of ConfigSchema (torchbiggraph/config.py:158-230, 318-359, 411-425) that the

@@ -140,10 +140,11 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   if ((size_t)cfg->batches_in_flight * ((cfg->dim + 127) / 128) * 512 > 227 * 1024)
     return fail(c, PBG_ERR_TOO_LARGE, "batches_in_flight %d with dimension %d: the per-batch totals of a hub row exceed shared memory (at most 28 batches above dimension 1024)",
                 cfg->batches_in_flight, cfg->dim);
-  if (cfg->precision < PBG_PREC_FP32 || cfg->precision > PBG_PREC_BF16X6) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown precision %d", cfg->precision);
-  const bool planes = cfg->precision == PBG_PREC_BF16X6;
+  if (cfg->precision < PBG_PREC_FP32 || cfg->precision > PBG_PREC_BF16X3) return fail(c, PBG_ERR_BAD_ARGUMENT, "unknown precision %d", cfg->precision);
+  const bool planes = cfg->precision == PBG_PREC_BF16X6 || cfg->precision == PBG_PREC_BF16X3;
+  const size_t npl = cfg->precision == PBG_PREC_BF16X3 ? 2 : 3;
   if (planes && matrix_op)
-    return fail(c, PBG_ERR_UNSUPPORTED, "precision bf16x6 does not cover the linear / affine operators; use tf32x3");
+    return fail(c, PBG_ERR_UNSUPPORTED, "the bf16-plane precisions do not cover the linear / affine operators; use tf32x3");
   if (chunk_geometry(*cfg, &c->Pm, &c->Cm) != PBG_OK)
     return fail(c, PBG_ERR_BAD_ARGUMENT, "num_batch_negs and num_uniform_negs are both 0: no chunk size (model.py:648-656)");
 
@@ -187,9 +188,9 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   const int Dpb = (cfg->dim + 7) / 8 * 8, Kb = (c->Mm + 7) / 8 * 8;
   size_t oXB[4] = {0, 0, 0, 0}, oAB[2] = {0, 0}, oTB[2] = {0, 0};
   if (planes) {
-    oXB[0] = take(nN * 3 * Dpb * 2); oXB[1] = take(nN * 3 * Dpb * 2);
-    if (dyn) { oXB[2] = take(nQ * 3 * Dpb * 2); oXB[3] = take(nQ * 3 * Dpb * 2); oTB[0] = take(nQ * 3 * Kb * 2); oTB[1] = take(nQ * 3 * Kb * 2); }
-    else { oXB[2] = oXB[1]; oXB[3] = oXB[0]; oAB[0] = take(nN * 3 * Kb * 2); oAB[1] = take(nN * 3 * Kb * 2); }
+    oXB[0] = take(nN * npl * Dpb * 2); oXB[1] = take(nN * npl * Dpb * 2);
+    if (dyn) { oXB[2] = take(nQ * npl * Dpb * 2); oXB[3] = take(nQ * npl * Dpb * 2); oTB[0] = take(nQ * npl * Kb * 2); oTB[1] = take(nQ * npl * Kb * 2); }
+    else { oXB[2] = oXB[1]; oXB[3] = oXB[0]; oAB[0] = take(nN * npl * Kb * 2); oAB[1] = take(nN * npl * Kb * 2); }
   }
   for (int p = 0; p < 2; ++p) {
     oS[p] = take(nQ * c->Ms * 4); oSpos[p] = take(nQ * 4); oLoss[p] = take(nQ * 4); oViol[p] = take(nQ * 4);
@@ -223,7 +224,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   }
   for (int p = 0; p < 2; ++p) b.A[p] = dyn ? nullptr : (float *)(c->ws + oA[p]);
   b.Ma = Ma;
-  b.Dpb = Dpb; b.Kb = Kb;
+  b.Dpb = Dpb; b.Kb = Kb; b.npl = (int)npl;
   for (int a = 0; a < 4; ++a) b.XB[a] = planes ? (unsigned short *)(c->ws + oXB[a]) : nullptr;
   for (int p = 0; p < 2; ++p) {
     b.AB[p] = (planes && !dyn) ? (unsigned short *)(c->ws + oAB[p]) : nullptr;

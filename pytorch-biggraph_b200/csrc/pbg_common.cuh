@@ -85,6 +85,7 @@ struct WaveBufs {
   //   TB[p]     [nblk][3][Pm][Kb]          planes of the coefficient matrices T_p (dynamic relations)
   unsigned short *XB[4], *AB[2], *TB[2];     // null outside that tier
   int Dpb, Kb;                       // row strides in elements (D and Mm rounded up to 8: 16-byte rows)
+  int npl;                           // planes per value: 3 (bf16x6: all six products of order <= 2) or 2 (bf16x3: b0.b0 + b0.b1 + b1.b0)
   float *spos[2];                    // positive scores [nblk][Pm]
   float *coef[4];                    // l2: colsum(T0), colsum(T1), rowsum(T0), rowsum(T1)
   float *lossrow[2];                 // per positive row: weighted loss term
@@ -252,10 +253,11 @@ __device__ __forceinline__ void bf16_planes4(float4 v, uint2 &p0, uint2 &p1, uin
   p2 = make_uint2(a2 | (b2 << 16), c2 | (d2 << 16));
 }
 // one value's planes into a plane array: p0 at dst, the others one / two plane strides further
-__device__ __forceinline__ void put_planes1(unsigned short *dst, size_t plane, float v) {
+__device__ __forceinline__ void put_planes1(unsigned short *dst, size_t plane, float v, int npl) {
   unsigned b0, b1, b2;
   bf16_planes(v, b0, b1, b2);
-  dst[0] = (unsigned short)b0; dst[plane] = (unsigned short)b1; dst[2 * plane] = (unsigned short)b2;
+  dst[0] = (unsigned short)b0; dst[plane] = (unsigned short)b1;
+  if (npl > 2) dst[2 * plane] = (unsigned short)b2;
 }
 __device__ __forceinline__ float tf32_round(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u); }
 __device__ __forceinline__ float4 tf32_round4(float4 v) { return make_float4(tf32_round(v.x), tf32_round(v.y), tf32_round(v.z), tf32_round(v.w)); }

@@ -63,25 +63,31 @@ __device__ __forceinline__ void put_row(float *base, size_t off, const float4 (&
 template <int VEC>
 __device__ __forceinline__ void put_row_planes(const WaveBufs &w, int a, int blk, int r, const float4 (&v)[VEC], int D, int lane) {
   const size_t plane = (size_t)w.xrows[a] * w.Dpb;
-  unsigned short *x = w.XB[a] + ((size_t)blk * 3 * w.xrows[a] + r) * w.Dpb;
+  unsigned short *x = w.XB[a] + ((size_t)blk * w.npl * w.xrows[a] + r) * w.Dpb;
+  const bool three = w.npl > 2;
 #pragma unroll
   for (int c = 0; c < VEC; ++c) {
     int dd = c * 128 + lane * 4;
     if (dd < D) {
       uint2 p0, p1, p2;
       bf16_planes4(v[c], p0, p1, p2);
-      *(uint2 *)(x + dd) = p0; *(uint2 *)(x + plane + dd) = p1; *(uint2 *)(x + 2 * plane + dd) = p2;
+      *(uint2 *)(x + dd) = p0; *(uint2 *)(x + plane + dd) = p1;
+      if (three) *(uint2 *)(x + 2 * plane + dd) = p2;
     }
   }
 }
 template <int VEC>
 __device__ __forceinline__ void zero_row_planes(const WaveBufs &w, int a, int blk, int r, int D, int lane) {
   const size_t plane = (size_t)w.xrows[a] * w.Dpb;
-  unsigned short *x = w.XB[a] + ((size_t)blk * 3 * w.xrows[a] + r) * w.Dpb;
+  unsigned short *x = w.XB[a] + ((size_t)blk * w.npl * w.xrows[a] + r) * w.Dpb;
+  const bool three = w.npl > 2;
 #pragma unroll
   for (int c = 0; c < VEC; ++c) {
     int dd = c * 128 + lane * 4;
-    if (dd < D) { *(uint2 *)(x + dd) = make_uint2(0, 0); *(uint2 *)(x + plane + dd) = make_uint2(0, 0); *(uint2 *)(x + 2 * plane + dd) = make_uint2(0, 0); }
+    if (dd < D) {
+      *(uint2 *)(x + dd) = make_uint2(0, 0); *(uint2 *)(x + plane + dd) = make_uint2(0, 0);
+      if (three) *(uint2 *)(x + 2 * plane + dd) = make_uint2(0, 0);
+    }
   }
 }
 template <int VEC>
@@ -340,16 +346,19 @@ __global__ void __launch_bounds__(32 * GATHER_WARPS, VEC >= 16 ? 1 : VEC >= 8 ? 
   if (PL) {
     // bf16-plane tier: the contractions read the planes, nothing reads the fp32 operand rows
     const size_t plane = (size_t)d.Mm * w.Dpb;
-    unsigned short *x0 = w.XB[0] + ((size_t)blk * 3 * d.Mm + r) * w.Dpb, *x1 = w.XB[1] + ((size_t)blk * 3 * d.Mm + r) * w.Dpb;
+    unsigned short *x0 = w.XB[0] + ((size_t)blk * w.npl * d.Mm + r) * w.Dpb, *x1 = w.XB[1] + ((size_t)blk * w.npl * d.Mm + r) * w.Dpb;
+    const bool three = w.npl > 2;
 #pragma unroll
     for (int c = 0; c < VEC; ++c) {
       int dd = c * 128 + lane * 4;
       if (dd < D) {
         uint2 p0, p1, p2;
         bf16_planes4(a[c], p0, p1, p2);
-        *(uint2 *)(x0 + dd) = p0; *(uint2 *)(x0 + plane + dd) = p1; *(uint2 *)(x0 + 2 * plane + dd) = p2;
+        *(uint2 *)(x0 + dd) = p0; *(uint2 *)(x0 + plane + dd) = p1;
+        if (three) *(uint2 *)(x0 + 2 * plane + dd) = p2;
         bf16_planes4(b[c], p0, p1, p2);
-        *(uint2 *)(x1 + dd) = p0; *(uint2 *)(x1 + plane + dd) = p1; *(uint2 *)(x1 + 2 * plane + dd) = p2;
+        *(uint2 *)(x1 + dd) = p0; *(uint2 *)(x1 + plane + dd) = p1;
+        if (three) *(uint2 *)(x1 + 2 * plane + dd) = p2;
       }
     }
   } else {

@@ -92,14 +92,16 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   // NTERMS == 6: the operands arrive as three bf16 planes each (x = b0 + b1 + b2, written by the producers);
   // a product is the six plane pairs of order <= 2 as kind::f16 MMAs -- no split in this kernel, and the
   // operand bytes the MMAs read from shared memory are half those of tf32
-  constexpr bool PLANES = NTERMS == 6;
+  // NTERMS == 2: the same on two planes per operand (x ~ b0 + b1) and the three products b1.b0, b0.b1, b0.b0
+  constexpr bool PLANES = NTERMS == 6 || NTERMS == 2;
+  constexpr int NPL = NTERMS == 6 ? 3 : 2;                               // planes per operand
   static_assert(!PLANES || TC_KB == 32, "bf16 planes: 32 k-values per stage");
   constexpr int KB = TC_KB;
   constexpr int SMAX = PLANES ? 4 : (SPLIT ? 2 : 4) * (32 / KB);      // stages (bf16 planes: as many as fit, at most 4)
   constexpr uint32_t ROW_BYTES = PLANES ? KB * 2 : KB * 4;               // bytes of one K-major row of a stage
   constexpr uint32_t BOX_BYTES = PLANES ? 4096 : KB * 128;               // one MN-major box: 64 x 32 bf16 or 32 x KB fp32
   constexpr uint32_t A_PLANE = 128 * ROW_BYTES, B_PLANE = 256 * ROW_BYTES;
-  constexpr uint32_t A_BYTES = PLANES ? 3 * A_PLANE : A_PLANE, B_BYTES = PLANES ? 3 * B_PLANE : B_PLANE;   // one KB-k tile of 128 / 256 rows
+  constexpr uint32_t A_BYTES = PLANES ? NPL * A_PLANE : A_PLANE, B_BYTES = PLANES ? NPL * B_PLANE : B_PLANE;   // one KB-k tile of 128 / 256 rows
   constexpr uint32_t RAW_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t STAGE_BYTES = SPLIT ? 2 * RAW_BYTES : RAW_BYTES;   // [A hi][B hi] ([A lo][B lo]) or [A planes][B planes]
 
@@ -140,7 +142,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   const int nkb = (g.K + KB - 1) / KB;
   const int b_atoms = PLANES ? (g.BN + 63) / 64 : (g.BN + 31) / 32;     // MN-major boxes per B tile (per plane)
   const uint32_t b_plane = B_MN ? (uint32_t)b_atoms * BOX_BYTES : (uint32_t)g.BN * ROW_BYTES;   // bytes of one B tile (plane)
-  const uint32_t b_used = PLANES ? 3u * b_plane : b_plane;
+  const uint32_t b_used = PLANES ? (uint32_t)NPL * b_plane : b_plane;
   const uint32_t stage_tx = A_BYTES + b_used;
   // persistent tile loop: tile t -> (n tile, m tile, chunk block, problem); every role walks the same list
   const int tiles_n = (g.N + g.BN - 1) / g.BN, tiles_m = (g.M + 127) / 128;
@@ -160,7 +162,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
     // Issuing one cp.async.bulk.tensor costs the issuing thread a few hundred cycles; an MN-major
     // B tile is up to eight 32 x 32 boxes, which issued from one lane made the producer the
     // longest link of the stage's chain.
-    const int a_boxes = PLANES ? (A_MN ? 6 : 3) : (A_MN ? 4 : 1), b_boxes = PLANES ? 3 * (B_MN ? b_atoms : 1) : (B_MN ? b_atoms : 1);
+    const int a_boxes = PLANES ? (A_MN ? 2 * NPL : NPL) : (A_MN ? 4 : 1), b_boxes = PLANES ? NPL * (B_MN ? b_atoms : 1) : (B_MN ? b_atoms : 1);
     long long git = 0;
     bool stop = false;
     for (long long t = blockIdx.x; t < ntiles && !stop; t += gridDim.x) {
@@ -224,17 +226,19 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
           // plane pairs (a, b) of order a + b <= 2, the smallest contributions first; K = 16 per MMA:
           // K-major 64-byte rows (64-byte swizzle: layout 4, 512 bytes per 8 rows, 32 bytes per step),
           // MN-major 64 x 32 boxes (128-byte swizzle: layout 2, LBO = box, SBO 1024, 2048 bytes per step)
+          // (two planes: the last three pairs of the list)
           const int pa[6] = {2, 0, 1, 1, 0, 0}, pb[6] = {0, 2, 1, 0, 1, 0};
+          constexpr int T0 = NPL == 3 ? 0 : 3;
 #pragma unroll
           for (int k16 = 0; k16 < 2; ++k16) {
             if (k16 * 16 >= kleft) break;                     // the tail of K: those k-values are zero fill
 #pragma unroll
-            for (int t = 0; t < 6; ++t) {
+            for (int t = T0; t < 6; ++t) {
               uint64_t da = A_MN ? smem_desc(aH + pa[t] * A_PLANE + k16 * 2048, BOX_BYTES, 1024, 2)
                                  : smem_desc(aH + pa[t] * A_PLANE + k16 * 32, 0, 512, 4);
               uint64_t db = B_MN ? smem_desc(bH + pb[t] * b_plane + k16 * 2048, BOX_BYTES, 1024, 2)
                                  : smem_desc(bH + pb[t] * b_plane + k16 * 32, 0, 512, 4);
-              uint32_t acc = (kb > 0 || k16 > 0 || t > 0) ? 1u : 0u;
+              uint32_t acc = (kb > 0 || k16 > 0 || t > T0) ? 1u : 0u;
               asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                            :: "r"(tacc), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
             }
@@ -423,12 +427,12 @@ static bool encode3(CUtensorMap *tm, const float *base, int inner, int rows, int
 
 // bf16 plane arrays [nblk][3][rows][ld]: a 4-D map (inner, rows, plane, block).  K-major operands
 // (box_inner = 32 k-values, 64-byte swizzle) or MN-major (box = 64 contiguous x 32 k rows, 128-byte swizzle).
-static bool encode4_planes(CUtensorMap *tm, const unsigned short *base, int inner, int rows, int rows_alloc, int nblk, int ld,
+static bool encode4_planes(CUtensorMap *tm, const unsigned short *base, int npl, int inner, int rows, int rows_alloc, int nblk, int ld,
                            int box_inner, int box_rows) {
   EncodeFn enc = get_encode();
   if (!enc) return false;
-  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)rows, 3, (cuuint64_t)nblk};
-  cuuint64_t strides[3] = {(cuuint64_t)ld * 2, (cuuint64_t)rows_alloc * ld * 2, (cuuint64_t)3 * rows_alloc * ld * 2};
+  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)npl, (cuuint64_t)nblk};
+  cuuint64_t strides[3] = {(cuuint64_t)ld * 2, (cuuint64_t)rows_alloc * ld * 2, (cuuint64_t)npl * rows_alloc * ld * 2};
   cuuint32_t box[4] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t es[4] = {1, 1, 1, 1};
   CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, (void *)base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -459,34 +463,35 @@ static int tile_cols(int n) {
 void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int precision) {
   TcPlan *pl = new TcPlan();
   pl->dynamic = d.dynamic != 0;
-  pl->nterms = precision == PBG_PREC_TF32X3 ? 3 : precision == PBG_PREC_BF16X6 ? 6 : 1;
+  pl->nterms = precision == PBG_PREC_TF32X3 ? 3 : precision == PBG_PREC_BF16X6 ? 6 : precision == PBG_PREC_BF16X3 ? 2 : 1;
   pl->bn_score = tile_cols(d.Mm);
   pl->bn_grad = tile_cols(d.D);
   bool ok = true;
-  if (pl->nterms == 6) {
-    // bf16-plane tier: the same products on the plane arrays (K-major boxes {32 k, rows}, MN-major boxes {64, 32 k})
+  if (pl->nterms == 6 || pl->nterms == 2) {
+    const int npl = w.npl;
+    // bf16-plane tiers: the same products on the plane arrays (K-major boxes {32 k, rows}, MN-major boxes {64, 32 k})
     for (int p = 0; p < 2; ++p) {
       int q = ARR_Q0 + p, n = ARR_N0 + p;
-      ok &= encode4_planes(&pl->score.a[p], w.XB[q], d.D, d.Pm, w.xrows[q], nblk_max, w.Dpb, 32, 128);
-      ok &= encode4_planes(&pl->score.b[p], w.XB[n], d.D, w.xrows[n], w.xrows[n], nblk_max, w.Dpb, 32, pl->bn_score);
+      ok &= encode4_planes(&pl->score.a[p], w.XB[q], npl, d.D, d.Pm, w.xrows[q], nblk_max, w.Dpb, 32, 128);
+      ok &= encode4_planes(&pl->score.b[p], w.XB[n], npl, d.D, w.xrows[n], w.xrows[n], nblk_max, w.Dpb, 32, pl->bn_score);
       ok &= encode3(&pl->score.c[p], w.S[p], d.Mm, d.Pm, nblk_max, d.Ms, (long long)d.Pm * d.Ms, 32, 32, false);
       if (pl->dynamic) {
         // grad Q: A = T (K-major, k = Mm), B = N (MN-major); grad N: A = T^T (MN-major: k rows = Pm), B = Q (MN-major)
-        ok &= encode4_planes(&pl->gradq.a[p], w.TB[p], d.Mm, d.Pm, d.Pm, nblk_max, w.Kb, 32, 128);
-        ok &= encode4_planes(&pl->gradq.b[p], w.XB[n], d.D, w.xrows[n], w.xrows[n], nblk_max, w.Dpb, 64, 32);
-        ok &= encode4_planes(&pl->gradn.a[p], w.TB[p], d.Mm, d.Pm, d.Pm, nblk_max, w.Kb, 64, 32);
-        ok &= encode4_planes(&pl->gradn.b[p], w.XB[q], d.D, w.xrows[q], w.xrows[q], nblk_max, w.Dpb, 64, 32);
+        ok &= encode4_planes(&pl->gradq.a[p], w.TB[p], npl, d.Mm, d.Pm, d.Pm, nblk_max, w.Kb, 32, 128);
+        ok &= encode4_planes(&pl->gradq.b[p], w.XB[n], npl, d.D, w.xrows[n], w.xrows[n], nblk_max, w.Dpb, 64, 32);
+        ok &= encode4_planes(&pl->gradn.a[p], w.TB[p], npl, d.Mm, d.Pm, d.Pm, nblk_max, w.Kb, 64, 32);
+        ok &= encode4_planes(&pl->gradn.b[p], w.XB[q], npl, d.D, w.xrows[q], w.xrows[q], nblk_max, w.Dpb, 64, 32);
         ok &= encode3(&pl->gradq.c[p], w.GX[q], d.D, d.Pm, nblk_max, d.Dp, (long long)w.grows[q] * d.Dp, 32, 32, false);
         ok &= encode3(&pl->gradn.c[p], w.GX[n], d.D, d.Mm, nblk_max, d.Dp, (long long)w.grows[n] * d.Dp, 32, 32, false);
       } else {
         int o = ARR_N0 + (1 - p);
-        ok &= encode4_planes(&pl->gradm.a[p], w.AB[p], d.Mm, d.Mm, d.Mm, nblk_max, w.Kb, 32, 128);
-        ok &= encode4_planes(&pl->gradm.b[p], w.XB[o], d.D, w.xrows[o], w.xrows[o], nblk_max, w.Dpb, 64, 32);
+        ok &= encode4_planes(&pl->gradm.a[p], w.AB[p], npl, d.Mm, d.Mm, d.Mm, nblk_max, w.Kb, 32, 128);
+        ok &= encode4_planes(&pl->gradm.b[p], w.XB[o], npl, d.D, w.xrows[o], w.xrows[o], nblk_max, w.Dpb, 64, 32);
         ok &= encode3(&pl->gradm.c[p], w.GX[n], d.D, d.Mm, nblk_max, d.Dp, (long long)d.Mm * d.Dp, 32, 32, false);
         // the same product transposed, GN^T = N_other^T . A^T: tile rows run over D (every 128-row tile full,
         // where Mm = 200 leaves the second one 56 % used), tile columns over the Mm coefficient rows
         pl->gradt.a[p] = pl->gradm.b[p];
-        ok &= encode4_planes(&pl->gradt.b[p], w.AB[p], d.Mm, d.Mm, d.Mm, nblk_max, w.Kb, 32, pl->bn_score);
+        ok &= encode4_planes(&pl->gradt.b[p], w.AB[p], npl, d.Mm, d.Mm, d.Mm, nblk_max, w.Kb, 32, pl->bn_score);
         pl->gradt.c[p] = pl->gradm.c[p];
       }
     }
@@ -535,10 +540,12 @@ template <bool A_MN, bool B_MN, int NTERMS, bool L2EPI>
 static void launch_tc_inst(const TcMaps &maps, const TcGeom &g, const WaveDims &d, const WaveBatches &wb, int *errflag,
                            dim3 grid, size_t smem, cudaStream_t st) {
   TcGeom gg = g;
-  if (NTERMS == 6) {
-    // three planes of 64-byte rows: A 128 rows; B the tile's rows (K-major) or its 64-column boxes (MN-major)
+  constexpr bool planes = NTERMS == 6 || NTERMS == 2;
+  if (planes) {
+    // two or three planes of 64-byte rows: A 128 rows; B the tile's rows (K-major) or its 64-column boxes (MN-major)
+    constexpr int npl = NTERMS == 6 ? 3 : 2;
     const int b_plane = B_MN ? (g.BN + 63) / 64 * 4096 : g.BN * 64;
-    gg.stage_bytes = 3 * 128 * 64 + 3 * b_plane;
+    gg.stage_bytes = npl * 128 * 64 + npl * b_plane;
     const int room = (int)smem - (4 * 2 * 4096 + 1024);            // what the stages get of the kernel's dynamic shared memory
     gg.nst = room / gg.stage_bytes > 4 ? 4 : room / gg.stage_bytes;
     smem = (size_t)room + 4 * 2 * 4096 + 1024;
@@ -546,7 +553,7 @@ static void launch_tc_inst(const TcMaps &maps, const TcGeom &g, const WaveDims &
   // if the opt-in fails the launch below fails too, and the caller's cudaGetLastError reports it
   pbg_opt_in_smem((const void *)tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI>, (int)smem);
   // the plane tier has no split warps: producer, MMA issuer and the four epilogue warps
-  tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI><<<grid, NTERMS == 6 ? 192 : TC_THREADS, smem, st>>>(maps, gg, d, wb, errflag);
+  tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI><<<grid, planes ? 192 : TC_THREADS, smem, st>>>(maps, gg, d, wb, errflag);
 }
 
 template <bool A_MN, bool B_MN>
@@ -561,12 +568,14 @@ static void launch_tc(const TcMaps &maps, const TcGeom &g, int nterms, const Wav
   if constexpr (!A_MN && !B_MN) {
     if (l2) {
       if (nterms == 6) launch_tc_inst<A_MN, B_MN, 6, true>(maps, g, d, wb, errflag, grid, smem, st);
+      else if (nterms == 2) launch_tc_inst<A_MN, B_MN, 2, true>(maps, g, d, wb, errflag, grid, smem, st);
       else if (nterms == 3) launch_tc_inst<A_MN, B_MN, 3, true>(maps, g, d, wb, errflag, grid, smem, st);
       else launch_tc_inst<A_MN, B_MN, 1, true>(maps, g, d, wb, errflag, grid, smem, st);
       return;
     }
   }
   if (nterms == 6) { launch_tc_inst<A_MN, B_MN, 6, false>(maps, g, d, wb, errflag, grid, smem, st); return; }
+  if (nterms == 2) { launch_tc_inst<A_MN, B_MN, 2, false>(maps, g, d, wb, errflag, grid, smem, st); return; }
   if (nterms == 3) launch_tc_inst<A_MN, B_MN, 3, false>(maps, g, d, wb, errflag, grid, smem, st);
   else launch_tc_inst<A_MN, B_MN, 1, false>(maps, g, d, wb, errflag, grid, smem, st);
 }
@@ -599,6 +608,7 @@ int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, 
     const dim3 grid((unsigned)(tiles < sms ? tiles : sms));
     const size_t smem = 4 * (128 * 128 + 256 * 128) + 4 * 2 * 4096 + 1024;
     if (pl->nterms == 6) launch_tc_inst<true, false, 6, false>(pl->gradt, g, d, wb, w.errflag, grid, smem, st);
+    else if (pl->nterms == 2) launch_tc_inst<true, false, 2, false>(pl->gradt, g, d, wb, w.errflag, grid, smem, st);
     else launch_tc_inst<true, false, 3, false>(pl->gradt, g, d, wb, w.errflag, grid, smem, st);
     return 1;
   }

@@ -48,11 +48,11 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_kernel(WaveDims d, WaveB
   if (bi.n == 0) return;
   float *S = w.S[p] + ((size_t)blk * d.Pm + i) * d.Ms;
   // bf16-plane tier with dynamic relations: T is an MMA operand, its planes go beside it
-  unsigned short *TBr = w.TB[p] ? w.TB[p] + ((size_t)blk * 3 * d.Pm + i) * w.Kb : nullptr;
+  unsigned short *TBr = w.TB[p] ? w.TB[p] + ((size_t)blk * w.npl * d.Pm + i) * w.Kb : nullptr;
   const size_t tplane = (size_t)d.Pm * w.Kb;
   auto put = [&](int j, float t) {
     S[j] = t;
-    if (TBr) put_planes1(TBr + j, tplane, t);
+    if (TBr) put_planes1(TBr + j, tplane, t, w.npl);
   };
   size_t prow = (size_t)blk * d.Pm + i;
   const int Mm = d.Mm;
@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_kernel(WaveDims d, WaveB
   float *A = w.A[side] + arow;
   float rowsum = 0.f;
   // bf16-plane tier: the planes of the row beside it
-  unsigned short *ABr = w.AB[side] ? w.AB[side] + ((size_t)blk * 3 * d.Mm + m) * w.Kb : nullptr;
+  unsigned short *ABr = w.AB[side] ? w.AB[side] + ((size_t)blk * w.npl * d.Mm + m) * w.Kb : nullptr;
   for (int j = lane; j < w.Ma; j += 32) {
     float a = 0.f;
     if (j < d.Mm) {
@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_kernel(WaveDims d, WaveB
     }
     rowsum += a;
     A[j] = a;
-    if (ABr) put_planes1(ABr + j, (size_t)d.Mm * w.Kb, a);
+    if (ABr) put_planes1(ABr + j, (size_t)d.Mm * w.Kb, a, w.npl);
   }
   if (d.cmp >= PBG_CMP_L2) {
     rowsum = warp_sum(rowsum);
@@ -220,8 +220,9 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_softmax_kernel(WaveDims 
   if (bi.n == 0) return;
   float *S = w.S[p] + ((size_t)blk * d.Pm + i) * d.Ms;
   // bf16-plane tier with dynamic relations: T is an MMA operand, its planes go beside it
-  unsigned short *TBr = w.TB[p] ? w.TB[p] + ((size_t)blk * 3 * d.Pm + i) * w.Kb : nullptr;
+  unsigned short *TBr = w.TB[p] ? w.TB[p] + ((size_t)blk * w.npl * d.Pm + i) * w.Kb : nullptr;
   const size_t tplane = (size_t)d.Pm * w.Kb;
+  const int npl = w.npl;
   size_t prow = (size_t)blk * d.Pm + i;
   const int Mm = d.Mm;
   const int enabled = d.neg_enabled[p];
@@ -230,7 +231,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_softmax_kernel(WaveDims 
 #pragma unroll
     for (int u = 0; u < NV; ++u) { int j = lane + 32 * u; if (j < d.Ms) S[j] = 0.f; }
     if (TBr)
-      for (int j = 2 * lane; j < d.Ms; j += 64) { *(unsigned *)(TBr + j) = 0u; *(unsigned *)(TBr + tplane + j) = 0u; *(unsigned *)(TBr + 2 * tplane + j) = 0u; }
+      for (int j = 2 * lane; j < d.Ms; j += 64) { *(unsigned *)(TBr + j) = 0u; *(unsigned *)(TBr + tplane + j) = 0u; if (npl > 2) *(unsigned *)(TBr + 2 * tplane + j) = 0u; }
     if (lane == 0) { w.lossrow[p][prow] = 0.f; w.violrow[p][prow] = 0; }
     return;
   }
@@ -289,7 +290,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) loss_softmax_kernel(WaveDims 
 #pragma unroll
         for (int q = 0; q < 3; ++q) {
           unsigned lo = odd ? got[q] : keep[q], hi = odd ? keep[q] : got[q];
-          *(unsigned *)(TBr + q * tplane + col) = lo | (hi << 16);
+          if (q < npl) *(unsigned *)(TBr + q * tplane + col) = lo | (hi << 16);
         }
       }
     }
@@ -342,8 +343,9 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_tile_kernel(WaveDims d, 
   // bf16-plane tier: the three planes instead of the fp32 matrix.  Two rows at a time: neighbouring
   // lanes swap one row's planes, so that every lane stores two columns of one row (4-byte stores):
   // even lanes the columns (j, j + 1) of row m, odd lanes (j - 1, j) of row m + 1.
-  unsigned short *AB = w.AB[side] + (size_t)blk * 3 * d.Mm * w.Kb;
+  unsigned short *AB = w.AB[side] + (size_t)blk * w.npl * d.Mm * w.Kb;
   const size_t aplane = (size_t)d.Mm * w.Kb;
+  const int npl = w.npl;
   const bool odd = lane & 1;
 #pragma unroll
   for (int r = 0; r < 32; r += 2) {
@@ -368,7 +370,7 @@ __global__ void __launch_bounds__(32 * LOSS_WARPS) coef_tile_kernel(WaveDims d, 
 #pragma unroll
       for (int q = 0; q < 3; ++q) {
         unsigned lo = odd ? got[q] : keep[q], hi = odd ? keep[q] : got[q];
-        *(unsigned *)(dst + q * aplane) = lo | (hi << 16);
+        if (q < npl) *(unsigned *)(dst + q * aplane) = lo | (hi << 16);
       }
     }
   }

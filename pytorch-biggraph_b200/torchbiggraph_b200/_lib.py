@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libpbg_b200.so")
 OPERATOR_CODES = {"none": 0, "diagonal": 1, "translation": 2, "complex_diagonal": 3, "linear": 4, "affine": 5}
 COMPARATOR_CODES = {"dot": 0, "cos": 1, "l2": 2, "squared_l2": 3}
 LOSS_CODES = {"logistic": 0, "ranking": 1, "softmax": 2}
-PRECISION_CODES = {"fp32": 0, "tf32x3": 1, "tf32": 2, "bf16x6": 3}
+PRECISION_CODES = {"fp32": 0, "tf32x3": 1, "tf32": 2, "bf16x6": 3, "bf16x3": 4}
 
 PBG_OK, PBG_ERR_BAD_ARGUMENT, PBG_ERR_UNSUPPORTED, PBG_ERR_INDEX_RANGE = 0, 1, 2, 3
 PBG_ERR_TIMEOUT, PBG_ERR_CUDA, PBG_ERR_NO_DEVICE, PBG_ERR_TOO_LARGE = 4, 5, 6, 7

@@ -54,7 +54,7 @@ class ConfigSchema:
     regularizer: str = "N3"
     half_precision: bool = False
     # keys of this implementation
-    precision: str = "fp32"        # "fp32" | "tf32x3" | "tf32" | "bf16x6": arithmetic of the contractions
+    precision: str = "fp32"        # "fp32" | "tf32x3" | "tf32" | "bf16x6" | "bf16x3": arithmetic of the contractions
     batches_in_flight: int = 1     # 1 = the reference's sequential batches
     num_dynamic_rels: int = 0      # count of relation types when dynamic_relations (the reference
                                    # reads it from dynamic_rel_count.txt, model.py:866-870)

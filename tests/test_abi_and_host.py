@@ -69,7 +69,7 @@ def test_config_validation_precedes_device_use():
     planes = _lib.PbgConfig(dim=16, op=4, comparator=0, loss=1, num_rels=1, num_batch_negs=4, num_uniform_negs=4,
                             max_batch_size=8, batches_in_flight=1, precision=_lib.PRECISION_CODES["bf16x6"])   # matrix operator: outside the bf16-plane tier
     assert L.pbg_create(ctypes.byref(planes), 0, None, ctypes.byref(ctx)) == _lib.PBG_ERR_UNSUPPORTED
-    assert b"bf16x6" in L.pbg_last_error(ctx)
+    assert b"bf16-plane" in L.pbg_last_error(ctx)
     L.pbg_destroy(ctx)
     assert L.pbg_row_adagrad_static(None, None, 1, 16, None, None, 0, 0.1, None) == 0        # n == 0: nothing to do
     assert L.pbg_row_adagrad_static(None, None, 1, 16, None, None, 5, 0.1, None) == _lib.PBG_ERR_BAD_ARGUMENT

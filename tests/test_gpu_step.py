@@ -93,20 +93,27 @@ def _plane_names():
     return [n for n in _names() if load_step(n)[0]["op"] not in ("linear", "affine")]
 
 
+# bf16x6: three bf16 planes per operand, six plane products; bf16x3: two planes, three products.
+# Both are held to the same rtol 1e-4 as fp32.
+PLANE_TIERS = ["bf16x6", "bf16x3"]
+
+
+@pytest.mark.parametrize("tier", PLANE_TIERS)
 @pytest.mark.parametrize("name", _plane_names())
-def test_step_matches_reference_fixture_bf16_planes(name):
-    """Three bf16 planes per operand, six plane products: the same rtol 1e-4 tier."""
-    test_step_matches_reference_fixture(name, "bf16x6")
+def test_step_matches_reference_fixture_bf16_planes(name, tier):
+    test_step_matches_reference_fixture(name, tier)
 
 
+@pytest.mark.parametrize("tier", PLANE_TIERS)
 @pytest.mark.parametrize("name", _plane_names())
-def test_forward_scores_match_reference_fixture_bf16_planes(name):
-    test_forward_scores_match_reference_fixture(name, "bf16x6")
+def test_forward_scores_match_reference_fixture_bf16_planes(name, tier):
+    test_forward_scores_match_reference_fixture(name, tier)
 
 
+@pytest.mark.parametrize("tier", PLANE_TIERS)
 @pytest.mark.parametrize("name", ["sequence_3_batches", "sequence_3_batches_dyn_cos"])
-def test_wave_of_three_batches_bf16_planes(name):
-    test_wave_of_three_batches_matches_oracle(name, "bf16x6")
+def test_wave_of_three_batches_bf16_planes(name, tier):
+    test_wave_of_three_batches_matches_oracle(name, tier)
 
 
 def test_bf16_planes_refuse_what_they_do_not_cover():
@@ -115,7 +122,7 @@ def test_bf16_planes_refuse_what_they_do_not_cover():
     c, z = load_step(name)
     rig = Rig.from_fixture(c, z, precision="bf16x6")
     lhs, rhs, rel, ul, ur = batch_of(c, z, 0)
-    with pytest.raises(RuntimeError, match="bf16x6"):
+    with pytest.raises(RuntimeError, match="bf16-plane"):
         rig.trainer.process_one_batch(rig.model, rig.edges(lhs, rhs, rel), ul, ur)
 
 
@@ -222,19 +229,22 @@ def test_baseline_shapes_match_oracle(D, N, B, nb, nu, op, comp, loss, dyn, R, p
     pytest.param(400, 3000, 1500, 500, 260, "softmax", id="three-column-tiles"),     # Mm 760: three score tiles; D 400: two gradient tiles
     pytest.param(36, 3000, 600, 300, 37, "logistic", id="ragged-edges"),              # D and Mm off every tile and 8-element boundary
 ])
-def test_bf16_planes_at_baseline_shapes(D, N, B, nb, nu, loss):
-    test_baseline_shapes_match_oracle(D, N, B, nb, nu, "none", "dot", loss, False, 1, "bf16x6")
+@pytest.mark.parametrize("tier", PLANE_TIERS)
+def test_bf16_planes_at_baseline_shapes(D, N, B, nb, nu, loss, tier):
+    test_baseline_shapes_match_oracle(D, N, B, nb, nu, "none", "dot", loss, False, 1, tier)
 
 
 @pytest.mark.parametrize("D,N,B,nb,nu,op,comp,loss,dyn,R", BASELINE_SHAPES)
-def test_bf16_planes_at_every_baseline_shape(D, N, B, nb, nu, op, comp, loss, dyn, R):
-    test_baseline_shapes_match_oracle(D, N, B, nb, nu, op, comp, loss, dyn, R, "bf16x6")
+@pytest.mark.parametrize("tier", PLANE_TIERS)
+def test_bf16_planes_at_every_baseline_shape(D, N, B, nb, nu, op, comp, loss, dyn, R, tier):
+    test_baseline_shapes_match_oracle(D, N, B, nb, nu, op, comp, loss, dyn, R, tier)
 
 
-def test_bf16_planes_wave_of_eight_with_hub_rows():
+@pytest.mark.parametrize("tier", PLANE_TIERS)
+def test_bf16_planes_wave_of_eight_with_hub_rows(tier):
     from b200_util import Rig
     c, ocfg, ost, batches = _random_case(5, 64, 300, 200, 50, 50, "none", "dot", "softmax", nbatches=8, zipf=True)
-    rig = Rig.from_oracle_state(c, ost, k=8, precision="bf16x6")
+    rig = Rig.from_oracle_state(c, ost, k=8, precision=tier)
     O.train_wave(ocfg, ost, batches)
     nat = rig.trainer._context(rig.model, 200)
     lhs = torch.tensor(np.concatenate([b[0] for b in batches])).cuda()
