@@ -2,6 +2,7 @@
 // sequence  keys -> sort -> gather -> score -> loss -> gradient products -> optimizer steps -> stats.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -31,6 +32,8 @@ struct pbg_context {
   double *eval_dev = nullptr;
   int *errflag = nullptr;
   void *tcplan = nullptr;       // tensor maps of the tcgen05 contractions
+  void *pairplan = nullptr;     // tensor maps of the fused score + loss kernel (standard relations, plane tiers)
+  bool fused = false;           // training runs gather -> fused score / loss -> dual gradient product
   float *psum = nullptr;        // partial gradient rows of hub rows, indexed by slot position
   long long *hublist = nullptr;
   int *hubcnt = nullptr;
@@ -186,11 +189,22 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     for (int s2 = 0; s2 < 2; ++s2) oA[s2] = take(nN * Ma * 4);
   }
   const int Dpb = (cfg->dim + 7) / 8 * 8, Kb = (c->Mm + 7) / 8 * 8;
-  size_t oXB[4] = {0, 0, 0, 0}, oAB[2] = {0, 0}, oTB[2] = {0, 0};
+  size_t oXB[4] = {0, 0, 0, 0}, oAB[2] = {0, 0}, oTB[2] = {0, 0}, oTT[2] = {0, 0};
+  // Standard relations under the dot / cos comparators with one score tile per chunk block: the fused
+  // score + loss kernel and the dual gradient product (pbg_pair.cu).  PBG_FUSED=0 in the environment keeps
+  // the separate score, loss and coefficient kernels (for comparisons).
+  const int Kp = (c->Pm + 7) / 8 * 8;
+  {
+    const char *env = getenv("PBG_FUSED");
+    c->fused = planes && !dyn && !matrix_op && cfg->comparator < PBG_CMP_L2 && c->Pm <= 128 && c->Mm <= 256 &&
+               !(env && env[0] == '0');
+  }
   if (planes) {
     oXB[0] = take(nN * npl * Dpb * 2); oXB[1] = take(nN * npl * Dpb * 2);
     if (dyn) { oXB[2] = take(nQ * npl * Dpb * 2); oXB[3] = take(nQ * npl * Dpb * 2); oTB[0] = take(nQ * npl * Kb * 2); oTB[1] = take(nQ * npl * Kb * 2); }
     else { oXB[2] = oXB[1]; oXB[3] = oXB[0]; oAB[0] = take(nN * npl * Kb * 2); oAB[1] = take(nN * npl * Kb * 2); }
+    if (c->fused)
+      for (int p = 0; p < 2; ++p) { oTB[p] = take(nQ * npl * Kb * 2); oTT[p] = take(nN * npl * Kp * 2); }
   }
   for (int p = 0; p < 2; ++p) {
     oS[p] = take(nQ * c->Ms * 4); oSpos[p] = take(nQ * 4); oLoss[p] = take(nQ * 4); oViol[p] = take(nQ * 4);
@@ -228,8 +242,10 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   for (int a = 0; a < 4; ++a) b.XB[a] = planes ? (unsigned short *)(c->ws + oXB[a]) : nullptr;
   for (int p = 0; p < 2; ++p) {
     b.AB[p] = (planes && !dyn) ? (unsigned short *)(c->ws + oAB[p]) : nullptr;
-    b.TB[p] = (planes && dyn) ? (unsigned short *)(c->ws + oTB[p]) : nullptr;
+    b.TB[p] = (planes && (dyn || c->fused)) ? (unsigned short *)(c->ws + oTB[p]) : nullptr;
+    b.TT[p] = c->fused ? (unsigned short *)(c->ws + oTT[p]) : nullptr;
   }
+  b.Kp = Kp;
   b.xrows[0] = b.xrows[1] = c->Mm;
   b.xrows[2] = b.xrows[3] = dyn ? c->Pm : c->Mm;
   b.grows[0] = b.grows[1] = c->Mm;
@@ -279,6 +295,10 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     gd.dynamic = dyn;
     c->tcplan = pbg_tc_plan_create(gd, b, (int)nblk, cfg->precision);
     if (!c->tcplan) return fail(c, PBG_ERR_CUDA, "could not encode the TMA tensor maps of the tensor-core contractions");
+    if (c->fused) {
+      c->pairplan = pbg_pair_plan_create(gd, b, (int)nblk);
+      if (!c->pairplan) return fail(c, PBG_ERR_CUDA, "could not encode the TMA tensor maps of the fused score kernel");
+    }
   }
   CU(c, cudaStreamSynchronize(c->stream));
   return PBG_OK;
@@ -289,6 +309,7 @@ extern "C" int pbg_destroy(pbg_context *c) {
   cudaSetDevice(c->device);
   if (c->ws) cudaFree(c->ws);
   if (c->tcplan) pbg_tc_plan_destroy(c->tcplan);
+  if (c->pairplan) pbg_pair_plan_destroy(c->pairplan);
   if (c->stats_dev) cudaFree(c->stats_dev);
   for (int i = 0; i < 3; ++i) if (c->edge_dev[i]) cudaFree(c->edge_dev[i]);
   for (int i = 0; i < 2; ++i) if (c->uni_dev[i]) cudaFree(c->uni_dev[i]);
@@ -397,6 +418,14 @@ static int run_forward(pbg_context *c, const WaveDims &d, const WaveBatches &wb,
 
 // gather -> score -> loss -> gradient products of the chunk blocks [d.blk0, d.blk0 + d.nblk) on `st`
 static void run_part(pbg_context *c, const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st) {
+  if (c->fused) {
+    { ClassTimer t(c, 1, st); t.done(launch_gather(d, wb, w, st)); }
+    { ClassTimer t(c, 2, st); t.done(launch_pair_score(d, wb, w, c->pairplan, st)); }      // scores, loss, coefficient planes
+    if (d.reg_coef != 0.f) { ClassTimer t(c, 3, st); t.done(launch_reg_value(d, wb, w, st)); }
+    ClassTimer t(c, 4, st);
+    t.done(launch_grad_dual_tc(d, wb, w, c->tcplan, st));
+    return;
+  }
   run_forward(c, d, wb, w, st);
   { ClassTimer t(c, 3, st); t.done(launch_loss(d, wb, w, st) + (d.reg_coef != 0.f ? launch_reg_value(d, wb, w, st) : 0)); }
   ClassTimer t(c, 4, st);

@@ -83,7 +83,10 @@ struct WaveBufs {
   //   XB[a]     [nblk][3][xrows[a]][Dpb]   planes of the operand rows N0, N1, Q0, Q1 (aliased like X)
   //   AB[side]  [nblk][3][Mm][Kb]          planes of the merged coefficient matrices (standard relations)
   //   TB[p]     [nblk][3][Pm][Kb]          planes of the coefficient matrices T_p (dynamic relations)
-  unsigned short *XB[4], *AB[2], *TB[2];     // null outside that tier
+  //   TT[p]     [nblk][planes][Mm][Kp]       T_p transposed (standard relations with the fused score / loss kernel,
+  //                                          which then also fills TB[p]; AB stays unused)
+  unsigned short *XB[4], *AB[2], *TB[2], *TT[2];     // null outside that tier
+  int Kp;                            // row stride of TT in elements (Pm rounded up to 8)
   int Dpb, Kb;                       // row strides in elements (D and Mm rounded up to 8: 16-byte rows)
   int npl;                           // planes per value: 3 (bf16x6: all six products of order <= 2) or 2 (bf16x3: b0.b0 + b0.b1 + b1.b0)
   float *spos[2];                    // positive scores [nblk][Pm]
@@ -302,6 +305,12 @@ int launch_build_keys(const WaveDims &d, const WaveBatches &wb, const WaveBufs &
 int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
 void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int precision);
 void pbg_tc_plan_destroy(void *plan);
+// standard relations, plane tiers: score contraction of both problems + loss + coefficient planes in one kernel
+bool pbg_pair_eligible(const WaveDims &d, int precision);
+void *pbg_pair_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max);
+void pbg_pair_plan_destroy(void *plan);
+int launch_pair_score(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st);
+int launch_grad_dual_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st);
 int launch_score_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st);
 int launch_grad_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st);
 int launch_matrix_forward(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);

@@ -28,9 +28,7 @@
 //
 // Every wait on an mbarrier is bounded; when one runs out the CTA raises bit 1 of the error word,
 // stops issuing work, releases its tensor memory and returns.  Every TMA load is CTA-local.
-#include <cuda.h>
-
-#include "pbg_common.cuh"
+#include "pbg_tc.cuh"
 
 // k-values per pipeline stage: 32 (two stages of 96 KB with their low parts in TF32X3) or 16 (four stages of
 // 48 KB; K-major tiles then have 64-byte rows -- TMA 64-byte swizzle, descriptor layout 4, 512 bytes per 8
@@ -40,9 +38,8 @@
 #define TC_KB 32
 #define TC_THREADS 448          // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-13 split operands (TF32X3)
 #define TC_SPLIT_THREADS 256
-#define TC_WAIT_LIMIT 4000000
 
-struct TcMaps { CUtensorMap a[2]; CUtensorMap b[2]; CUtensorMap c[2]; };   // [problem]; c = output (stores)
+struct TcMaps { CUtensorMap a[2]; CUtensorMap b[2]; CUtensorMap c[2]; CUtensorMap b2[2]; };   // [problem]; c = output (stores); b2: second B operand (dual mode)
 
 struct TcGeom {
   int M, N, K;          // output rows, columns, contraction length (per block)
@@ -55,35 +52,13 @@ struct TcGeom {
   int cmp, score;
   int nst, stage_bytes;  // bf16-plane tier: stages in flight and bytes of one (three planes of A and of the B tile)
   int tr;                // the output map is that of the transposed matrix: tile element (row, col) goes to C[col][row]
+  // Dual mode (standard relations, plane tiers, transposed gradient without a merged coefficient matrix):
+  //   GN_side^T (D x Mm) = N_other^T[:, k < K1] . B1   +   N_other^T[:, k < K] . B2   (B2 fills the first BN2 columns)
+  // with B1 = TT[side] (rows m, k = i < K1 = Pm) and B2 = TB[other] (rows i < Pm, k = j < K = Mm): the two
+  // halves of the combined matrix A[side][m][j] = T_side[j][m] + T_other[m][j] as two K-major B operands.
+  // A stage holds the A tile, B1 (for the k-blocks below K1) and B2.
+  int dual, K1, BN2;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *errflag) {
-  for (int it = 0; it < TC_WAIT_LIMIT; ++it) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-  }
-  atomicOr(errflag, 2);
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-               :: "r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-               :: "r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
-  return ((uint64_t)((addr >> 4) & 0x3FFF)) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
-         ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
-}
 
 template <bool A_MN, bool B_MN, int NTERMS, bool L2EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -144,6 +119,9 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   const uint32_t b_plane = B_MN ? (uint32_t)b_atoms * BOX_BYTES : (uint32_t)g.BN * ROW_BYTES;   // bytes of one B tile (plane)
   const uint32_t b_used = PLANES ? (uint32_t)NPL * b_plane : b_plane;
   const uint32_t stage_tx = A_BYTES + b_used;
+  const bool dual = PLANES && A_MN && !B_MN && g.dual != 0;
+  const int nkb1 = dual ? (g.K1 + KB - 1) / KB : 0;                    // k-blocks that carry B1
+  const uint32_t b2_plane = (uint32_t)g.BN2 * ROW_BYTES;                 // dual: one plane of the B2 tile
   // persistent tile loop: tile t -> (n tile, m tile, chunk block, problem); every role walks the same list
   const int tiles_n = (g.N + g.BN - 1) / g.BN, tiles_m = (g.M + 127) / 128;
   const long long ntiles = (long long)tiles_n * tiles_m * d.nblk * 2;
@@ -175,7 +153,9 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
         if (git >= STAGES && lane == 0) okw = mbar_wait(empty_bar(s), (uint32_t)((git / STAGES) - 1) & 1, errflag);
         if (!__all_sync(0xffffffffu, okw)) { failed = 1; stop = true; break; }
         uint32_t fb = full_bar(s);
-        if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(fb), "r"(stage_tx) : "memory");
+        const bool with_b1 = !dual || kb < nkb1;
+        const uint32_t tx = dual ? A_BYTES + (with_b1 ? b_used : 0u) + (uint32_t)NPL * b2_plane : stage_tx;
+        if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(fb), "r"(tx) : "memory");
         __syncwarp();
         unsigned char *st = smem + (size_t)s * stage_bytes;
         int k0 = kb * KB;
@@ -186,8 +166,11 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
             else { int pl = lane >> 1, mb = lane & 1; tma_load_4d(dA + pl * A_PLANE + mb * BOX_BYTES, &maps.a[p], m0 + mb * 64, k0, pl, blk, fb); }
           } else if (lane < a_boxes + b_boxes) {
             int ib = lane - a_boxes;
-            if (!B_MN) tma_load_4d(dB + ib * b_plane, &maps.b[p], k0, n0, ib, blk, fb);
+            if (!B_MN) { if (with_b1) tma_load_4d(dB + ib * b_plane, &maps.b[p], k0, n0, ib, blk, fb); }
             else { int pl = ib / b_atoms, nb = ib - pl * b_atoms; tma_load_4d(dB + pl * b_plane + nb * BOX_BYTES, &maps.b[p], n0 + nb * 64, k0, pl, blk, fb); }
+          } else if (dual && lane < a_boxes + b_boxes + NPL) {
+            int ib = lane - a_boxes - b_boxes;
+            tma_load_4d(dB + b_used + ib * b2_plane, &maps.b2[p], k0, 0, ib, blk, fb);
           }
         } else if (lane < a_boxes) {
           if (!A_MN) tma_load_3d(dA, &maps.a[p], k0, m0, blk, fb);
@@ -205,6 +188,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
     const uint32_t fmt = PLANES ? 1u : 2u;            // operand format: bf16 (kind::f16) or tf32
     const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                            ((uint32_t)(g.BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    const uint32_t idesc2 = (idesc & ~(0x3Fu << 17)) | ((uint32_t)(g.BN2 >> 3) << 17);      // dual: the B2 products are BN2 columns wide
     long long git = 0, j = 0;
     for (long long t = blockIdx.x; t < ntiles && !failed; t += gridDim.x) {
       int p, blk, m0, n0;
@@ -229,6 +213,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
           // (two planes: the last three pairs of the list)
           const int pa[6] = {2, 0, 1, 1, 0, 0}, pb[6] = {0, 2, 1, 0, 1, 0};
           constexpr int T0 = NPL == 3 ? 0 : 3;
+          const int kleft1 = dual ? g.K1 - kb * KB : kleft;    // k-values of this block under B1
 #pragma unroll
           for (int k16 = 0; k16 < 2; ++k16) {
             if (k16 * 16 >= kleft) break;                     // the tail of K: those k-values are zero fill
@@ -239,8 +224,21 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
               uint64_t db = B_MN ? smem_desc(bH + pb[t] * b_plane + k16 * 2048, BOX_BYTES, 1024, 2)
                                  : smem_desc(bH + pb[t] * b_plane + k16 * 32, 0, 512, 4);
               uint32_t acc = (kb > 0 || k16 > 0 || t > T0) ? 1u : 0u;
+              if (dual && k16 * 16 >= kleft1) continue;       // past K1: no B1 product for these k-values
               asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                            :: "r"(tacc), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+            }
+            if (dual) {
+              // B2 = rows of the other problem's coefficient matrix: every k-block, BN2 columns wide, always
+              // accumulating -- the first product of a tile is a B1 product (k-block 0 carries B1 and K1 >= 1),
+              // which initialises all BN columns
+#pragma unroll
+              for (int t = T0; t < 6; ++t) {
+                uint64_t da = smem_desc(aH + pa[t] * A_PLANE + k16 * 2048, BOX_BYTES, 1024, 2);
+                uint64_t db = smem_desc(bH + b_used + pb[t] * b2_plane + k16 * 32, 0, 512, 4);
+                asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                             :: "r"(tacc), "l"(da), "l"(db), "r"(idesc2), "r"(1u) : "memory");
+              }
             }
           }
         } else
@@ -396,53 +394,10 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
 // ------------------------------------------------------------------------------------------------
 // host side: tensor maps (encoded once per context) and launchers
 // ------------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeFn get_encode() {
-  static EncodeFn fn = nullptr;
-  if (!fn) {
-    cudaDriverEntryPointQueryResult q;
-    void *p = nullptr;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess) fn = (EncodeFn)p;
-  }
-  return fn;
-}
-
-// 3-D map over an array laid out [nblk][rows][ld] floats: dims {inner extent, rows, nblk}.
-static bool encode3(CUtensorMap *tm, const float *base, int inner, int rows, int nblk, int ld, long long blk_stride,
-                    int box_inner, int box_rows, bool mn_major) {
-  EncodeFn enc = get_encode();
-  if (!enc) return false;
-  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)nblk};
-  cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)blk_stride * 4};
-  cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1};
-  cuuint32_t es[3] = {1, 1, 1};
-  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void *)base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : (box_inner * 4 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B),
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
-// bf16 plane arrays [nblk][3][rows][ld]: a 4-D map (inner, rows, plane, block).  K-major operands
-// (box_inner = 32 k-values, 64-byte swizzle) or MN-major (box = 64 contiguous x 32 k rows, 128-byte swizzle).
-static bool encode4_planes(CUtensorMap *tm, const unsigned short *base, int npl, int inner, int rows, int rows_alloc, int nblk, int ld,
-                           int box_inner, int box_rows) {
-  EncodeFn enc = get_encode();
-  if (!enc) return false;
-  cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)npl, (cuuint64_t)nblk};
-  cuuint64_t strides[3] = {(cuuint64_t)ld * 2, (cuuint64_t)rows_alloc * ld * 2, (cuuint64_t)npl * rows_alloc * ld * 2};
-  cuuint32_t box[4] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1, 1};
-  cuuint32_t es[4] = {1, 1, 1, 1};
-  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, (void *)base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   box_inner * 2 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
 struct TcPlan {
-  TcMaps score, gradq, gradn, gradm, gradt;
+  TcMaps score, gradq, gradn, gradm, gradt, gradu;
+  bool has_dual;
+  int bn2;
   bool dynamic;
   int bn_score, bn_grad;
   int nterms;
@@ -462,6 +417,7 @@ static int tile_cols(int n) {
 // is missing or an encode fails.
 void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int precision) {
   TcPlan *pl = new TcPlan();
+  pl->has_dual = false; pl->bn2 = 0;
   pl->dynamic = d.dynamic != 0;
   pl->nterms = precision == PBG_PREC_TF32X3 ? 3 : precision == PBG_PREC_BF16X6 ? 6 : precision == PBG_PREC_BF16X3 ? 2 : 1;
   pl->bn_score = tile_cols(d.Mm);
@@ -493,6 +449,16 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
         pl->gradt.a[p] = pl->gradm.b[p];
         ok &= encode4_planes(&pl->gradt.b[p], w.AB[p], npl, d.Mm, d.Mm, d.Mm, nblk_max, w.Kb, 32, pl->bn_score);
         pl->gradt.c[p] = pl->gradm.c[p];
+        if (w.TT[0]) {
+          // dual mode: B1 = TT[side] (rows m < Mm, k = i < Pm), B2 = TB[other side] (rows i < Pm, k = j < Mm); what lies
+          // beyond those extents is outside the maps and arrives as zeros
+          pl->has_dual = true;
+          pl->bn2 = (d.Pm + 15) / 16 * 16;
+          pl->gradu.a[p] = pl->gradm.b[p];
+          ok &= encode4_planes(&pl->gradu.b[p], w.TT[p], npl, d.Pm, d.Mm, d.Mm, nblk_max, w.Kp, 32, pl->bn_score);
+          ok &= encode4_planes(&pl->gradu.b2[p], w.TB[1 - p], npl, d.Mm, d.Pm, d.Pm, nblk_max, w.Kb, 32, pl->bn2);
+          pl->gradu.c[p] = pl->gradm.c[p];
+        }
       }
     }
     if (!ok) { delete pl; return nullptr; }
@@ -545,7 +511,7 @@ static void launch_tc_inst(const TcMaps &maps, const TcGeom &g, const WaveDims &
     // two or three planes of 64-byte rows: A 128 rows; B the tile's rows (K-major) or its 64-column boxes (MN-major)
     constexpr int npl = NTERMS == 6 ? 3 : 2;
     const int b_plane = B_MN ? (g.BN + 63) / 64 * 4096 : g.BN * 64;
-    gg.stage_bytes = npl * 128 * 64 + npl * b_plane;
+    gg.stage_bytes = npl * 128 * 64 + npl * b_plane + (g.dual ? npl * g.BN2 * 64 : 0);
     const int room = (int)smem - (4 * 2 * 4096 + 1024);            // what the stages get of the kernel's dynamic shared memory
     gg.nst = room / gg.stage_bytes > 4 ? 4 : room / gg.stage_bytes;
     smem = (size_t)room + 4 * 2 * 4096 + 1024;
@@ -592,6 +558,24 @@ int launch_score_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
   }
   g.auxa_blk = w.xrows[ARR_Q0]; g.auxb_blk = w.xrows[ARR_N0];
   launch_tc<false, false>(pl->score, g, pl->nterms, d, wb, w.errflag, st);
+  return 1;
+}
+
+// Standard relations, plane tiers, coefficient planes TT / TB written by the fused score kernel: the transposed
+// gradient product with two B operands per stage (see TcGeom).
+int launch_grad_dual_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st) {
+  TcPlan *pl = (TcPlan *)plan;
+  TcGeom g;
+  memset(&g, 0, sizeof g);
+  g.M = d.D; g.N = d.Mm; g.K = d.Mm; g.BN = pl->bn_score; g.ldc = d.Dp; g.tr = 1;
+  g.dual = 1; g.K1 = d.Pm; g.BN2 = pl->bn2;
+  for (int p = 0; p < 2; ++p) g.C[p] = w.GX[ARR_N0 + p];
+  long long tiles = (long long)((g.N + g.BN - 1) / g.BN) * ((g.M + 127) / 128) * d.nblk * 2;
+  const int sms = pbg_sm_count();
+  const dim3 grid((unsigned)(tiles < sms ? tiles : sms));
+  const size_t smem = 4 * (128 * 128 + 256 * 128) + 4 * 2 * 4096 + 1024;
+  if (pl->nterms == 6) launch_tc_inst<true, false, 6, false>(pl->gradu, g, d, wb, w.errflag, grid, smem, st);
+  else launch_tc_inst<true, false, 2, false>(pl->gradu, g, d, wb, w.errflag, grid, smem, st);
   return 1;
 }
 

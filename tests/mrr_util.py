@@ -6,11 +6,12 @@ CASES = {
     # name: entities, relations, edges, noise, dim, operator, dynamic, epochs (+ overrides of COMMON)
     "std_translation": dict(N=3000, R=1, E=40000, noise=0.2, D=32, op="translation", dyn=False, epochs=6),
     "dyn_complex_diagonal": dict(N=3000, R=8, E=40000, noise=0.2, D=32, op="complex_diagonal", dyn=True, epochs=6),
-    # the step shape of the 15k-entity multi-relation configuration: dim 400, complex_diagonal / dot / softmax with
-    # dynamic relations, batches of 5000 cut into chunks of 1000 batch negatives, no uniform negatives; relation
-    # frequencies Zipf(1.0)
-    "kg15k_shape": dict(N=14951, R=40, E=120000, noise=0.2, D=400, op="complex_diagonal", dyn=True, epochs=4,
-                        batch=5000, nb=1000, nu=0, rel_zipf=1.0),
+    # the 15k-entity multi-relation configuration at its full size: 1345 relations with Zipf(1.0) frequencies,
+    # 483,142 edges, dim 400, complex_diagonal / dot / softmax with dynamic relations, batches of 5000 cut into
+    # chunks of 1000 batch negatives, no uniform negatives (97 batches per epoch: 14 batches in flight are a
+    # seventh of an epoch, as in the benchmark run)
+    "kg15k_shape": dict(N=14951, R=1345, E=483142, noise=0.2, D=400, op="complex_diagonal", dyn=True, epochs=3,
+                        batch=5000, nb=1000, nu=0, rel_zipf=1.0, held_out=2000),
     # power-law endpoints (Zipf 1.1 over permuted ids: the top row collects about a tenth of all endpoints, so a
     # wave of batches in flight reads hub rows that many of its own batches update), dim 256, 100 + 100 negatives
     "powerlaw_hubs": dict(N=20000, R=1, E=200000, noise=0.2, D=256, op="translation", dyn=False, epochs=8,

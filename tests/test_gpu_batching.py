@@ -44,7 +44,7 @@ def _setup(two_types, seed=5, D=32, N=400, M=300):
     rel = rng.integers(0, len(rels), n) if two_types else np.zeros(n, np.int64)
     lhs = rng.integers(0, N, n)
     rhs = np.where(rel == 1, rng.integers(0, M, n), rng.integers(0, N, n))
-    wgt = (rng.random(n) * 2).astype(np.float32)
+    wgt = (0.5 + rng.random(n) * 3).astype(np.float32)          # mean 2: the weighted total is about twice the plain one
     return T, build, lhs, rhs, rel, wgt
 
 
@@ -84,4 +84,4 @@ def test_process_in_batches_equals_batch_by_batch(two_types):
     model_c, tr_c, _, _ = build()
     torch.manual_seed(123)
     plain = T.process_in_batches(100, model_c, tr_c, T.EdgeList(ent(lhs), ent(rhs), t(rel) if two_types else t(0)))
-    assert abs(plain.metrics["loss"] - total.metrics["loss"]) > 1e-3 * abs(total.metrics["loss"])
+    assert total.metrics["loss"] > 1.5 * plain.metrics["loss"]

@@ -56,5 +56,10 @@ def test_held_out_mrr_matches_reference_trainer(case, k, precision):
         assert stats.count == len(order) and np.isfinite(stats.metrics["loss"])
     th = (model.lhs_op_table if c["dyn"] else model.rhs_op_table).cpu().numpy()
     got = mrr_rhs(case, W.cpu().numpy(), th, test)
-    print(f"MRR {case} k={k} {precision}: {got:.4f} (reference {want:.4f})")
-    assert abs(got - want) <= 0.01, f"MRR {got:.4f} vs reference {want:.4f}"
+    print(f"\nMRR {case} k={k} {precision}: {got:.4f} (reference {want:.4f})")
+    if k == 1:
+        assert abs(got - want) <= 0.01, f"MRR {got:.4f} vs reference {want:.4f}"
+    else:
+        # batches in flight read tables that are up to k - 1 steps old; held to "not worse than the sequential
+        # reference by more than 0.01" (on power-law graphs the run with batches in flight ends a little higher)
+        assert got >= want - 0.01, f"MRR {got:.4f} vs reference {want:.4f}"
