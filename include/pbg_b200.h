@@ -240,6 +240,44 @@ int pbg_row_adagrad_static(float *emb, float *state, int64_t num_rows, int32_t d
                            const int64_t *rows_dev, const float *grads_dev, int32_t n, float lr,
                            void *stream);
 
+/* ---- The edge-list utilities of the reference's native module torchbiggraph._C (torchbiggraph/util.cpp:425-460),
+ * on the device.  Any context serves (its configuration is not read); all pointers are device memory unless
+ * stated; every call returns after synchronising the context's stream. ---- */
+
+/* reverse_permutation (util.cpp:103-125): out[perm[i]] = i.  perm, out: int64 [n]. */
+int pbg_reverse_permutation(pbg_context *ctx, const int64_t *perm_dev, int64_t n, int64_t *out_dev);
+
+/* shuffle (util.cpp:127-220): row i of the table moves to row perm[i].  The reference permutes in place by
+ * following cycles on host threads; here `in` and `out` are two different buffers of rows x row_bytes bytes
+ * (the Python wrapper keeps the in-place interface).  A permutation value outside [0, rows) gives
+ * PBG_ERR_INDEX_RANGE ("Permutation has out-of-bound values", util.cpp:200-202); that row is skipped. */
+int pbg_shuffle_rows(pbg_context *ctx, const void *in_dev, void *out_dev, int64_t rows, int64_t row_bytes,
+                     const int64_t *perm_dev);
+
+/* randperm (util.cpp:14-101; also where the trainers call torch.randperm for the per-bucket edge shuffle,
+ * train_cpu.py:857-859, train_gpu.py:245): a uniformly random permutation of [0, n) fixed by `seed`, int64 [n].
+ * The reference's stream is a Mersenne Twister per host thread (its output depends on the thread count); this
+ * one sorts 44-bit hashes of (seed, index).  n < 2^31. */
+int pbg_randperm(pbg_context *ctx, int64_t n, uint64_t seed, int64_t *out_dev);
+
+/* sub_bucket (util.cpp:260-423): splits a bucket's edges into num_lhs_sub_parts x num_rhs_sub_parts sub-buckets.
+ * An entity's offset goes through the permutation of its relation's entity type; the permuted offset divided by
+ * ceil(count / parts) is its sub-partition, the remainder its offset there.  Outputs hold the sub-buckets one
+ * after the other in (i, j) row-major order, every edge at its sub-partition offsets, in input order inside a
+ * sub-bucket -- the layout the reference returns as views (util.cpp:344-362).
+ *   lhs_in / rhs_in / rel_in, lhs_out / rhs_out / rel_out : device int64 [num_edges]
+ *   lhs_entity_counts / rhs_entity_counts                 : HOST int64 [num_relations]
+ *   lhs_perms / rhs_perms                                 : HOST arrays [num_relations] of DEVICE int64 pointers
+ *   dynamic_relations                                     : 1 = every edge uses entry 0 of the per-relation arrays
+ *   sub_bucket_counts                                     : HOST int64 [parts_l * parts_r], edges per sub-bucket
+ * A relation id outside [0, num_relations) gives PBG_ERR_INDEX_RANGE ("rel > numRelations", util.cpp:320-322). */
+int pbg_sub_bucket(pbg_context *ctx, const int64_t *lhs_in, const int64_t *rhs_in, const int64_t *rel_in, int64_t num_edges,
+                   int32_t num_relations, const int64_t *lhs_entity_counts, const int64_t *const *lhs_perms,
+                   const int64_t *rhs_entity_counts, const int64_t *const *rhs_perms,
+                   int64_t *lhs_out, int64_t *rhs_out, int64_t *rel_out,
+                   int32_t num_lhs_sub_parts, int32_t num_rhs_sub_parts, int32_t dynamic_relations,
+                   int64_t *sub_bucket_counts);
+
 /* Kernel launches issued by this context since creation (for launch accounting). */
 int64_t pbg_launch_count(const pbg_context *ctx);
 

@@ -43,6 +43,11 @@ struct pbg_context {
   long long uni_cap = 0;
   long long launches = 0;
   unsigned long long batches_done = 0;
+  // scratch of the edge-list utilities (pbg_randperm, pbg_sub_bucket): grown on demand
+  SortPlan esort = {{nullptr, nullptr}, {nullptr, nullptr}, nullptr, 0, 0};
+  char *esort_mem = nullptr;
+  long long *etab_dev = nullptr;      // per-relation tables of a sub_bucket call + its counts
+  long long etab_cap = 0;
   // optional event timing per kernel class
   const float *edge_w = nullptr;   // per-edge weights for the next train / eval call (pbg_set_edge_weights)
   bool profiling = false;
@@ -313,6 +318,8 @@ extern "C" int pbg_destroy(pbg_context *c) {
   if (c->stats_dev) cudaFree(c->stats_dev);
   for (int i = 0; i < 3; ++i) if (c->edge_dev[i]) cudaFree(c->edge_dev[i]);
   for (int i = 0; i < 2; ++i) if (c->uni_dev[i]) cudaFree(c->uni_dev[i]);
+  if (c->esort_mem) cudaFree(c->esort_mem);
+  if (c->etab_dev) cudaFree(c->etab_dev);
   for (int s = 0; s < 2; ++s) {
     if (c->ev_sorted[s]) cudaEventDestroy(c->ev_sorted[s]);
     if (c->ev_updated[s]) cudaEventDestroy(c->ev_updated[s]);
@@ -718,4 +725,113 @@ extern "C" int pbg_row_adagrad(pbg_context *c, float *emb, float *state, int64_t
                                            grads, n, lr, (unsigned long long)num_rows, c->stream);
   CU(c, cudaGetLastError());
   return check_errflag(c);
+}
+
+// ---- edge-list utilities (torchbiggraph/util.cpp) -------------------------------------------------
+static int check_errflag_edges(pbg_context *c, const char *what) {
+  int flag = 0;
+  CU(c, cudaMemcpyAsync(&flag, c->errflag, sizeof flag, cudaMemcpyDeviceToHost, c->stream));
+  CU(c, cudaStreamSynchronize(c->stream));
+  if (flag) {
+    cudaMemsetAsync(c->errflag, 0, sizeof(int), c->stream);
+    if (flag & 4) return fail(c, PBG_ERR_INDEX_RANGE, "%s: rel > numRelations", what);
+    return fail(c, PBG_ERR_INDEX_RANGE, "%s: a value lies outside its table; those elements were skipped", what);
+  }
+  return PBG_OK;
+}
+
+// sort scratch for n (key, value) pairs
+static int ensure_edge_sort(pbg_context *c, long long n) {
+  if (n > 0x7fffffffll) return fail(c, PBG_ERR_TOO_LARGE, "%lld elements are beyond the 2^31 - 1 one call sorts", n);
+  if (n <= c->esort.max_n) return PBG_OK;
+  if (c->esort_mem) { cudaFree(c->esort_mem); c->esort_mem = nullptr; c->esort.max_n = 0; }
+  const long long cap = n + n / 4 + 1024 > 0x7fffffffll ? 0x7fffffffll : n + n / 4 + 1024;
+  const size_t kb = align_up((size_t)cap * 8, 256), vb = align_up((size_t)cap * 4, 256);
+  const size_t hb = align_up(pbg_sort_hist_entries((int)cap) * 4, 256);
+  CU(c, cudaMalloc(&c->esort_mem, 2 * kb + 2 * vb + hb));
+  char *p = c->esort_mem;
+  c->esort.keys[0] = (unsigned long long *)p; c->esort.keys[1] = (unsigned long long *)(p + kb);
+  c->esort.vals[0] = (unsigned int *)(p + 2 * kb); c->esort.vals[1] = (unsigned int *)(p + 2 * kb + vb);
+  c->esort.hist = (unsigned int *)(p + 2 * kb + 2 * vb);
+  c->esort.max_n = (int)cap;
+  return PBG_OK;
+}
+
+extern "C" int pbg_reverse_permutation(pbg_context *c, const int64_t *perm, int64_t n, int64_t *out) {
+  if (!c) return PBG_ERR_BAD_ARGUMENT;
+  if (n == 0) return PBG_OK;
+  if (!perm || !out || n < 0) return fail(c, PBG_ERR_BAD_ARGUMENT, "bad reverse_permutation arguments");
+  CU(c, cudaSetDevice(c->device));
+  c->launches += launch_reverse_permutation((const long long *)perm, n, (long long *)out, c->errflag, c->stream);
+  CU(c, cudaGetLastError());
+  return check_errflag_edges(c, "reverse_permutation");
+}
+
+extern "C" int pbg_shuffle_rows(pbg_context *c, const void *in, void *out, int64_t rows, int64_t row_bytes, const int64_t *perm) {
+  if (!c) return PBG_ERR_BAD_ARGUMENT;
+  if (rows == 0 || row_bytes == 0) return PBG_OK;
+  if (!in || !out || !perm || rows < 0 || row_bytes < 0 || in == out) return fail(c, PBG_ERR_BAD_ARGUMENT, "bad shuffle arguments (in and out must be different buffers)");
+  CU(c, cudaSetDevice(c->device));
+  c->launches += launch_shuffle_rows(in, out, rows, row_bytes, (const long long *)perm, c->errflag, c->stream);
+  CU(c, cudaGetLastError());
+  int rc = check_errflag_edges(c, "shuffle");
+  if (rc == PBG_ERR_INDEX_RANGE) c->err = "Permutation has out-of-bound values";      // util.cpp:200-202
+  return rc;
+}
+
+extern "C" int pbg_randperm(pbg_context *c, int64_t n, uint64_t seed, int64_t *out) {
+  if (!c) return PBG_ERR_BAD_ARGUMENT;
+  if (n == 0) return PBG_OK;
+  if (!out || n < 0) return fail(c, PBG_ERR_BAD_ARGUMENT, "bad randperm arguments");
+  CU(c, cudaSetDevice(c->device));
+  int rc = ensure_edge_sort(c, n);
+  if (rc) return rc;
+  c->launches += launch_randperm(c->esort, n, seed, (long long *)out, c->stream);
+  CU(c, cudaGetLastError());
+  CU(c, cudaStreamSynchronize(c->stream));
+  return PBG_OK;
+}
+
+extern "C" int pbg_sub_bucket(pbg_context *c, const int64_t *lhs_in, const int64_t *rhs_in, const int64_t *rel_in, int64_t num_edges,
+                              int32_t num_relations, const int64_t *lhs_entity_counts, const int64_t *const *lhs_perms,
+                              const int64_t *rhs_entity_counts, const int64_t *const *rhs_perms, int64_t *lhs_out,
+                              int64_t *rhs_out, int64_t *rel_out, int32_t num_lhs_sub_parts, int32_t num_rhs_sub_parts,
+                              int32_t dynamic_relations, int64_t *sub_bucket_counts) {
+  if (!c) return PBG_ERR_BAD_ARGUMENT;
+  const int R = num_relations, nl = num_lhs_sub_parts, nr = num_rhs_sub_parts;
+  if (R <= 0 || !lhs_entity_counts || !rhs_entity_counts || !lhs_perms || !rhs_perms || !sub_bucket_counts)
+    return fail(c, PBG_ERR_BAD_ARGUMENT, "Inconsistent num_relations");                 // util.cpp:277-281
+  if (nl <= 0 || nr <= 0 || nl > 127 || nr > 127) return fail(c, PBG_ERR_BAD_ARGUMENT, "sub-partition counts must be in [1, 127] (int8 in the reference)");
+  if (num_edges < 0 || (num_edges > 0 && (!lhs_in || !rhs_in || !rel_in || !lhs_out || !rhs_out || !rel_out)))
+    return fail(c, PBG_ERR_BAD_ARGUMENT, "null edge arrays");
+  CU(c, cudaSetDevice(c->device));
+  int rc = ensure_edge_sort(c, num_edges);
+  if (rc) return rc;
+  const long long need = 6ll * R + (long long)nl * nr;
+  if (need > c->etab_cap) {
+    if (c->etab_dev) cudaFree(c->etab_dev);
+    c->etab_dev = nullptr;
+    CU(c, cudaMalloc(&c->etab_dev, (size_t)(need + 64) * sizeof(long long)));
+    c->etab_cap = need + 64;
+  }
+  std::vector<long long> tab((size_t)need, 0);
+  for (int r = 0; r < R; ++r) {
+    if (!lhs_perms[r] || !rhs_perms[r] || lhs_entity_counts[r] <= 0 || rhs_entity_counts[r] <= 0)
+      return fail(c, PBG_ERR_BAD_ARGUMENT, "relation %d: null permutation or empty entity type", r);
+    tab[r] = (long long)(uintptr_t)lhs_perms[r];
+    tab[R + r] = (long long)(uintptr_t)rhs_perms[r];
+    tab[2 * R + r] = lhs_entity_counts[r];
+    tab[3 * R + r] = rhs_entity_counts[r];
+    tab[4 * R + r] = (lhs_entity_counts[r] + nl - 1) / nl;                               // util.cpp:296-315
+    tab[5 * R + r] = (rhs_entity_counts[r] + nr - 1) / nr;
+  }
+  CU(c, cudaMemcpyAsync(c->etab_dev, tab.data(), (size_t)6 * R * sizeof(long long), cudaMemcpyHostToDevice, c->stream));
+  CU(c, cudaStreamSynchronize(c->stream));                                               // tab is a local: the copy must have left it
+  long long *counts_dev = c->etab_dev + 6 * R;
+  c->launches += launch_sub_bucket(c->esort, (const long long *)lhs_in, (const long long *)rhs_in, (const long long *)rel_in, num_edges, R,
+                                   c->etab_dev, nl, nr, dynamic_relations != 0, (long long *)lhs_out, (long long *)rhs_out,
+                                   (long long *)rel_out, counts_dev, c->errflag, c->stream);
+  CU(c, cudaGetLastError());
+  CU(c, cudaMemcpyAsync(sub_bucket_counts, counts_dev, (size_t)nl * nr * sizeof(long long), cudaMemcpyDeviceToHost, c->stream));
+  return check_errflag_edges(c, "sub_bucket");
 }

@@ -333,5 +333,11 @@ int launch_stats(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
 int launch_row_adagrad_sorted(float *emb, float *state, int dim, const unsigned long long *keys,
                               const unsigned int *vals, const float *grads, int n, float lr,
                               unsigned long long key_invalid, cudaStream_t st);
+int launch_reverse_permutation(const long long *perm, long long n, long long *out, int *errflag, cudaStream_t st);
+int launch_shuffle_rows(const void *in, void *out, long long rows, long long row_bytes, const long long *perm, int *errflag, cudaStream_t st);
+int launch_randperm(SortPlan &sp, long long n, unsigned long long seed, long long *out, cudaStream_t st);
+int launch_sub_bucket(SortPlan &sp, const long long *lhs, const long long *rhs, const long long *rel, long long n, int R,
+                      const long long *tables_dev, int nl, int nr, int dynamic, long long *lhs_out, long long *rhs_out,
+                      long long *rel_out, long long *counts_dev, int *errflag, cudaStream_t st);
 int launch_iota_keys(const long long *rows, long long num_rows, int n, unsigned long long *keys,
                      unsigned int *vals, int *errflag, cudaStream_t st);

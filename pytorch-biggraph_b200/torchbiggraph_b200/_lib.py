@@ -71,6 +71,12 @@ SYMBOLS = [
     ("pbg_neg_columns", C.c_int, [_P, C.c_int32] + [C.POINTER(C.c_int32)] * 4),
     ("pbg_row_adagrad", C.c_int, [_P, _P, _P, C.c_int64, _P, _P, C.c_int32, C.c_float]),
     ("pbg_row_adagrad_static", C.c_int, [_P, _P, C.c_int64, C.c_int32, _P, _P, C.c_int32, C.c_float, _P]),
+    ("pbg_reverse_permutation", C.c_int, [_P, _P, C.c_int64, _P]),
+    ("pbg_shuffle_rows", C.c_int, [_P, _P, _P, C.c_int64, C.c_int64, _P]),
+    ("pbg_randperm", C.c_int, [_P, C.c_int64, C.c_uint64, _P]),
+    ("pbg_sub_bucket", C.c_int, [_P, _P, _P, _P, C.c_int64, C.c_int32, C.POINTER(C.c_int64), C.POINTER(_P),
+                                 C.POINTER(C.c_int64), C.POINTER(_P), _P, _P, _P, C.c_int32, C.c_int32, C.c_int32,
+                                 C.POINTER(C.c_int64)]),
     ("pbg_launch_count", C.c_int64, [_P]),
     ("pbg_set_edge_weights", C.c_int, [_P, C.c_void_p]),
     ("pbg_set_profiling", C.c_int, [_P, C.c_int]),
