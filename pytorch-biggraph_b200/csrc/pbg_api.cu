@@ -577,7 +577,7 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
     b0 += kk;
   }
   c->batches_done += (unsigned long long)num_batches;
-  CU(c, cudaGetLastError());
+  CU(c, pbg_take_launch_error());
   if (stats_out) {
     CU(c, cudaMemcpyAsync(stats_out, c->stats_dev, (size_t)num_batches * sizeof(pbg_batch_stats),
                           cudaMemcpyDeviceToHost, c->stream));
@@ -668,7 +668,7 @@ extern "C" int pbg_score_batch(pbg_context *c, const pbg_bucket *bk, const int64
   d.blk0 = 0;
   run_forward(c, d, wb, w, c->stream);
   c->launches += launch_export_scores(d, wb, w, lhs_pos, rhs_pos, lhs_neg, rhs_neg, c->stream);
-  CU(c, cudaGetLastError());
+  CU(c, pbg_take_launch_error());
   return check_errflag(c);
 }
 
@@ -697,7 +697,7 @@ extern "C" int pbg_eval_batch(pbg_context *c, const pbg_bucket *bk, const int64_
   d.k = 1; d.nblk = d.Cm; d.nocc = d.spb; d.blk0 = 0;
   run_forward(c, d, wb, w, c->stream);
   c->launches += launch_eval(d, wb, w, c->eval_dev, c->stream);
-  CU(c, cudaGetLastError());
+  CU(c, pbg_take_launch_error());
   double h[8];
   CU(c, cudaMemcpyAsync(h, c->eval_dev, sizeof h, cudaMemcpyDeviceToHost, c->stream));
   rc = check_errflag(c);
@@ -723,7 +723,7 @@ extern "C" int pbg_row_adagrad(pbg_context *c, float *emb, float *state, int64_t
   c->launches += pbg_sort(sp, n, bit_length((unsigned long long)num_rows), c->stream);
   c->launches += launch_row_adagrad_sorted(emb, state, c->cfg.dim, sp.keys[sp.result], sp.vals[sp.result],
                                            grads, n, lr, (unsigned long long)num_rows, c->stream);
-  CU(c, cudaGetLastError());
+  CU(c, pbg_take_launch_error());
   return check_errflag(c);
 }
 
@@ -763,7 +763,7 @@ extern "C" int pbg_reverse_permutation(pbg_context *c, const int64_t *perm, int6
   if (!perm || !out || n < 0) return fail(c, PBG_ERR_BAD_ARGUMENT, "bad reverse_permutation arguments");
   CU(c, cudaSetDevice(c->device));
   c->launches += launch_reverse_permutation((const long long *)perm, n, (long long *)out, c->errflag, c->stream);
-  CU(c, cudaGetLastError());
+  CU(c, pbg_take_launch_error());
   return check_errflag_edges(c, "reverse_permutation");
 }
 
@@ -773,7 +773,7 @@ extern "C" int pbg_shuffle_rows(pbg_context *c, const void *in, void *out, int64
   if (!in || !out || !perm || rows < 0 || row_bytes < 0 || in == out) return fail(c, PBG_ERR_BAD_ARGUMENT, "bad shuffle arguments (in and out must be different buffers)");
   CU(c, cudaSetDevice(c->device));
   c->launches += launch_shuffle_rows(in, out, rows, row_bytes, (const long long *)perm, c->errflag, c->stream);
-  CU(c, cudaGetLastError());
+  CU(c, pbg_take_launch_error());
   int rc = check_errflag_edges(c, "shuffle");
   if (rc == PBG_ERR_INDEX_RANGE) c->err = "Permutation has out-of-bound values";      // util.cpp:200-202
   return rc;
@@ -787,7 +787,7 @@ extern "C" int pbg_randperm(pbg_context *c, int64_t n, uint64_t seed, int64_t *o
   int rc = ensure_edge_sort(c, n);
   if (rc) return rc;
   c->launches += launch_randperm(c->esort, n, seed, (long long *)out, c->stream);
-  CU(c, cudaGetLastError());
+  CU(c, pbg_take_launch_error());
   CU(c, cudaStreamSynchronize(c->stream));
   return PBG_OK;
 }
@@ -831,7 +831,7 @@ extern "C" int pbg_sub_bucket(pbg_context *c, const int64_t *lhs_in, const int64
   c->launches += launch_sub_bucket(c->esort, (const long long *)lhs_in, (const long long *)rhs_in, (const long long *)rel_in, num_edges, R,
                                    c->etab_dev, nl, nr, dynamic_relations != 0, (long long *)lhs_out, (long long *)rhs_out,
                                    (long long *)rel_out, counts_dev, c->errflag, c->stream);
-  CU(c, cudaGetLastError());
+  CU(c, pbg_take_launch_error());
   CU(c, cudaMemcpyAsync(sub_bucket_counts, counts_dev, (size_t)nl * nr * sizeof(long long), cudaMemcpyDeviceToHost, c->stream));
   return check_errflag_edges(c, "sub_bucket");
 }

@@ -26,7 +26,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <mutex>
-#include <set>
+#include <map>
 #include <utility>
 #include "../../include/pbg_b200.h"
 
@@ -269,16 +269,34 @@ __device__ __forceinline__ float4 tf32_round4(float4 v) { return make_float4(tf3
 // Opt-in to more than 48 KB of dynamic shared memory.  The attribute belongs to the (kernel, device)
 // pair, so a process that drives several GPUs has to set it on each of them: the pairs already done
 // are remembered under a mutex, with the device that is current at the call.
+// A launch that fails because of its configuration leaves an error that a later successful call can hide
+// from a cudaGetLastError made at the end of an entry point: the launchers note it at once in this
+// per-thread latch, which the entry points read (and clear) before they report success.
+inline cudaError_t &pbg_launch_error() {
+  static thread_local cudaError_t e = cudaSuccess;
+  return e;
+}
+inline void pbg_note_launch(cudaError_t e = cudaGetLastError()) {
+  if (e != cudaSuccess && pbg_launch_error() == cudaSuccess) pbg_launch_error() = e;
+}
+inline cudaError_t pbg_take_launch_error() {
+  cudaError_t e = pbg_launch_error();
+  pbg_launch_error() = cudaSuccess;
+  if (e == cudaSuccess) e = cudaGetLastError();
+  return e;
+}
 inline cudaError_t pbg_opt_in_smem(const void *kernel, int bytes) {
   static std::mutex mu;
-  static std::set<std::pair<const void *, int>> done;
+  static std::map<std::pair<const void *, int>, int> done;       // (kernel, device) -> bytes opted in so far
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
+  if (e != cudaSuccess) { pbg_note_launch(e); return e; }
   std::lock_guard<std::mutex> lock(mu);
-  if (done.count({kernel, dev})) return cudaSuccess;
+  auto it = done.find({kernel, dev});
+  if (it != done.end() && it->second >= bytes) return cudaSuccess;
   e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-  if (e == cudaSuccess) done.insert({kernel, dev});
+  if (e == cudaSuccess) done[{kernel, dev}] = bytes;
+  else pbg_note_launch(e);
   return e;
 }
 inline int pbg_sm_count() {

@@ -520,6 +520,7 @@ static void launch_tc_inst(const TcMaps &maps, const TcGeom &g, const WaveDims &
   pbg_opt_in_smem((const void *)tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI>, (int)smem);
   // the plane tier has no split warps: producer, MMA issuer and the four epilogue warps
   tc_gemm_kernel<A_MN, B_MN, NTERMS, L2EPI><<<grid, planes ? 192 : TC_THREADS, smem, st>>>(maps, gg, d, wb, errflag);
+  pbg_note_launch();
 }
 
 template <bool A_MN, bool B_MN>

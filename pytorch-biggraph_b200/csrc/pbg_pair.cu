@@ -24,6 +24,7 @@
 
 #define PAIR_THREADS 192          // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
 #define PAIR_SMAX 4
+#define PAIR_SMEM_MAX (227 * 1024 - 1024)   // dynamic shared memory opted in: the 227 KB of a CTA less room for the static part
 
 struct PairMaps { CUtensorMap n[2]; };     // planes of N0 / N1: 4-D (k, row, plane, block), K-major boxes {32, rows_pad}
 
@@ -316,7 +317,7 @@ void *pbg_pair_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max) {
   g.BN = (d.Mm + 15) / 16 * 16;
   g.rows_pad = g.BN > 128 ? g.BN : 128;
   g.stage_bytes = 2 * w.npl * g.rows_pad * 64;
-  const int room = 227 * 1024 - 2048;                          // dynamic shared memory left for the stages
+  const int room = PAIR_SMEM_MAX - 1024;                       // dynamic shared memory left for the stages (1 KB: alignment)
   g.nst = room / g.stage_bytes > PAIR_SMAX ? PAIR_SMAX : room / g.stage_bytes;
   bool ok = g.nst >= 2 && w.TT[0] && w.TB[0];
   // rows beyond the Mm operand rows of a block are outside the map: the box brings zeros for them
@@ -333,12 +334,14 @@ int launch_pair_score(const WaveDims &d, const WaveBatches &wb, const WaveBufs &
   const int sms = pbg_sm_count();
   const dim3 grid((unsigned)(d.nblk < sms ? d.nblk : sms));
   const size_t smem = (size_t)pl->geom.nst * pl->geom.stage_bytes + 1024;
+  // the opt-in covers the largest stage ring this kernel is ever launched with (227 KB less its static shared memory)
   if (pl->npl == 3) {
-    pbg_opt_in_smem((const void *)pair_score_kernel<3>, 227 * 1024);
+    pbg_opt_in_smem((const void *)pair_score_kernel<3>, PAIR_SMEM_MAX);
     pair_score_kernel<3><<<grid, PAIR_THREADS, smem, st>>>(pl->maps, pl->geom, d, wb, w);
   } else {
-    pbg_opt_in_smem((const void *)pair_score_kernel<2>, 227 * 1024);
+    pbg_opt_in_smem((const void *)pair_score_kernel<2>, PAIR_SMEM_MAX);
     pair_score_kernel<2><<<grid, PAIR_THREADS, smem, st>>>(pl->maps, pl->geom, d, wb, w);
   }
+  pbg_note_launch();
   return 1;
 }

@@ -899,6 +899,7 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
     globupdate_kernel<<<(d.D + 127) / 128, 128, 0, st>>>(d, wb, w, rel_lr);
     ++launches;
   }
+  pbg_note_launch();
   return launches;
 }
 

@@ -121,3 +121,80 @@ def test_overlapped_ring_hands_halves_on_in_order_world_size_2():
     # every bucket adds 1 to both halves; partitions alternate between the two ranks
     assert res[0] == (0, [101.0, 101.0, 202.0, 202.0, 103.0, 103.0], 203.0, 203.0)
     assert res[1] == (1, [201.0, 201.0, 102.0, 102.0, 203.0, 203.0], 103.0, 103.0)
+
+
+# ---------------------------------------------------------------- a whole epoch on several ranks
+@pytest.mark.parametrize("P", [2, 4, 8, 16, 32])
+def test_epoch_schedule_trains_every_bucket_once_with_two_partitions_per_slot(P):
+    from torchbiggraph_b200.buckets import epoch_schedule, partition_moves
+    steps = epoch_schedule(P)
+    seen = [b for st in steps for bs in st.buckets for b in bs]
+    assert sorted(seen) == sorted((a, b) for a in range(P) for b in range(P))
+    for st in steps:
+        assert sorted(p for h in st.holds for p in h) == list(range(P))          # every partition in exactly one slot
+        for h, bs in zip(st.holds, st.buckets):
+            assert all(set(b) <= set(h) for b in bs)                             # a slot trains over its own two partitions
+    # inside a level a slot passes on one partition per step; the stationary one stays
+    for a, b in zip(steps, steps[1:]):
+        if a.level == b.level:
+            assert [h[0] for h in a.holds] == [h[0] for h in b.holds]
+            assert len(partition_moves(a, b, P // 2)) == P // 2
+    with pytest.raises(ValueError):
+        epoch_schedule(12)
+
+
+def _epoch_worker(rank, world, initfile, P, epochs, out):
+    from torchbiggraph_b200.buckets import EpochDriver, PartitionBuffer
+    if world > 1:
+        dist.init_process_group("gloo", init_method=f"file://{initfile}", rank=rank, world_size=world)
+    rows, cut = 10, 6
+    drv = EpochDriver(P, lambda: PartitionBuffer(torch.zeros(rows, 2), torch.zeros(rows)), cut)
+    for buf in drv.resident():
+        buf.emb.fill_(float(buf.partition))
+    log = []
+
+    def train(bucket, lhs, rhs, sub):
+        # the tensors handed over are those of the bucket's partitions (whole, or the half the sub-bucket names)
+        assert float(lhs[0][0, 0]) == bucket[0] and float(rhs[0][0, 0]) == bucket[1], (bucket, sub)
+        want_l = rows if sub is None or sub[0] != "lhs" else (cut if sub[1] == 0 else rows - cut)
+        want_r = rows if sub is None or sub[0] != "rhs" else (cut if sub[1] == 0 else rows - cut)
+        assert lhs[0].shape[0] == want_l and rhs[0].shape[0] == want_r
+        # "training" marks the rows it touched, one mark per bucket and side (the side that is whole in a half
+        # sub-bucket gets half a mark from each of the two); the marks travel with the partition
+        lhs[1].add_(1.0 if sub is None or sub[0] == "lhs" else 0.5)
+        rhs[1].add_(1.0 if sub is None or sub[0] == "rhs" else 0.5)
+        log.append((bucket, None if sub is None else sub[:2]))
+
+    steps_per_epoch = len(drv.steps)
+    for _ in range(epochs * steps_per_epoch):
+        drv.run_step(train)
+    state = {buf.partition: buf.state.clone() for buf in drv.resident()}
+    out.put((rank, log, {p: (float(s.min()), float(s.max())) for p, s in state.items()}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,P", [(1, 8), (2, 8), (2, 16), (4, 8)])
+def test_epoch_driver_visits_every_bucket_once_per_epoch_and_marks_travel_with_partitions(world, P):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    epochs = 2
+    with tempfile.TemporaryDirectory() as d:
+        init = os.path.join(d, "init")
+        procs = [ctx.Process(target=_epoch_worker, args=(r, world, init, P, epochs, q)) for r in range(world)]
+        for p in procs:
+            p.start()
+        res = [q.get(timeout=180) for _ in range(world)]
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    whole = {}
+    marks = {}
+    for rank, log, state in res:
+        for bucket, sub in log:
+            whole[bucket] = whole.get(bucket, 0.0) + (1.0 if sub is None else 0.5)       # two half sub-buckets make one bucket
+        marks.update(state)
+    assert whole == {(a, b): float(epochs) for a in range(P) for b in range(P)}
+    # every row of every partition was touched by its 2P - 1 buckets (the diagonal one on both sides), each epoch
+    assert marks == {p: (2.0 * P * epochs, 2.0 * P * epochs) for p in range(P)}
