@@ -36,6 +36,9 @@ WORKLOADS = {
                batch=1000, nb=100, nu=100, gamma=2.3, precision="bf16x6", desc="social-graph shaped, Chung-Lu exponent 2.3"),
     "c4": dict(entities=41_652_230, edges=1_468_365_182, partitions=16, dim=100, op="translation", comp="cos",
                loss="ranking", batch=1000, nb=100, nu=100, gamma=2.0, desc="follower-graph shaped, Chung-Lu exponent 2.0"),
+    "c5": dict(entities=86_054_151, edges=338_586_276, partitions=16, dim=200, op="complex_diagonal", comp="l2",
+               loss="logistic", batch=1000, nb=100, nu=100, gamma=None, rels=14_824, dynamic=True, rel_zipf=1.2, uniform_endpoints=True,
+               desc="large multi-relation KG shaped, 14824 relations Zipf(1.2), per-relation operators (dynamic relations)"),
     "c2": dict(entities=14_951, edges=483_142, partitions=1, dim=400, op="complex_diagonal", comp="dot", loss="softmax",
                batch=5000, nb=1000, nu=0, gamma=None, rels=1345, dynamic=True,
                desc="15k-entity multi-relation KG shaped, 1345 relations Zipf(1.0), planted permutation maps + 20% noise, dynamic relations"),
@@ -370,12 +373,245 @@ def _workload_config(args, w, step_edges):
 # ------------------------------------------------------------------------------------------------
 # the B200 arm
 # ------------------------------------------------------------------------------------------------
+class EdgeDrawer:
+    """Synthetic edges of one bucket, as partition-local offsets (lhs, rhs, rel or None)."""
+
+    def __init__(self, w, samplers, bounds, dev, gen):
+        import torch
+        self.w, self.samplers, self.bounds, self.dev, self.gen = w, samplers, bounds, dev, gen
+        self.dyn = bool(w.get("dynamic"))
+        if self.dyn:
+            rw = torch.arange(1, w["rels"] + 1, device=dev, dtype=torch.float64).pow(-float(w.get("rel_zipf", 1.0)))
+            self.rel_cdf = (torch.cumsum(rw, 0) / rw.sum()).float()
+            n = w["entities"]
+            self.rel_a = torch.randint(1, n, (w["rels"],), device=dev, generator=gen)     # planted maps v = a_r u + b_r mod N
+            self.rel_b = torch.randint(0, n, (w["rels"],), device=dev, generator=gen)
+
+    def __call__(self, bk, count):
+        import torch
+        pl, pr = bk
+        w, dev, gen = self.w, self.dev, self.gen
+        if not self.dyn:
+            return self.samplers[pl].draw(count, gen), self.samplers[pr].draw(count, gen), None
+        rel = torch.searchsorted(self.rel_cdf, torch.rand(count, device=dev, generator=gen)).clamp_(max=w["rels"] - 1)
+        if w["partitions"] > 1:
+            # partitioned multi-relation graph: endpoints uniform inside the bucket's two partitions (the planted
+            # structure decides which bucket an edge falls in, not how a bucket trains)
+            nl, nr = self.bounds[pl + 1] - self.bounds[pl], self.bounds[pr + 1] - self.bounds[pr]
+            return (torch.randint(0, nl, (count,), device=dev, generator=gen),
+                    torch.randint(0, nr, (count,), device=dev, generator=gen), rel)
+        n = w["entities"]
+        u = torch.randint(0, n, (count,), device=dev, generator=gen)
+        v = (self.rel_a[rel] * u + self.rel_b[rel]) % n
+        noisy = torch.rand(count, device=dev, generator=gen) < 0.2
+        v = torch.where(noisy, torch.randint(0, n, (count,), device=dev, generator=gen), v)
+        return u, v, rel
+
+
+def build_trainer(args, w, dev):
+    import torchbiggraph_b200 as T
+    dyn = bool(w.get("dynamic"))
+    cfg = T.ConfigSchema(entities={"e": T.EntitySchema(num_partitions=w["partitions"])},
+                         relations=[T.RelationSchema("r", "e", "e", operator=w["op"])], dimension=w["dim"],
+                         comparator=w["comp"], loss_fn=w["loss"], margin=0.1, lr=0.1, batch_size=w["batch"],
+                         num_batch_negs=w["nb"], num_uniform_negs=w["nu"], precision=args.precision,
+                         batches_in_flight=args.k, dynamic_relations=dyn, num_dynamic_rels=w.get("rels", 0) if dyn else 0)
+    model = T.make_model(cfg, dev)
+    trainer = T.B200Trainer(T.make_optimizer(cfg, model.parameters(), False),
+                            T.LOSS_FUNCTIONS.get_class(w["loss"])(margin=0.1), [1.0])
+    return cfg, model, trainer
+
+
+def run_b200_epoch(args, w, world, rank, dev):
+    """Several GPUs, partitioned workload: K steps of the epoch schedule (torchbiggraph_b200.buckets.epoch_schedule --
+    every bucket of the P x P grid once per epoch, each GPU training the buckets over the two partitions it holds,
+    partitions handed on over NCCL in halves beside training, relation parameters all-reduced after every step).
+    A step is one step of that schedule: two buckets per GPU (four in the last step of an epoch)."""
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    import torchbiggraph_b200 as T
+    from torchbiggraph_b200 import _C as native, _lib
+    from torchbiggraph_b200.buckets import EpochDriver, PartitionBuffer, average_relation_parameters
+
+    P, D, B = w["partitions"], w["dim"], w["batch"]
+    bucket_edges = min(EDGES_PER_STEP_CAP, max(B, w["edges"] // (P * P)))
+    samplers, bounds, gen = make_samplers(w, dev, seed=3)
+    max_rows = max(bounds[p + 1] - bounds[p] for p in range(P))
+    cut = -(-max_rows // 2)                                   # sub-partition size of a two-way split (util.cpp:296-315)
+    cfg, model, trainer = build_trainer(args, w, dev)
+    dyn = bool(w.get("dynamic"))
+    draw = EdgeDrawer(w, samplers, bounds, dev, gen)
+    drv = EpochDriver(P, lambda: PartitionBuffer(torch.empty(max_rows, D, device=dev), torch.empty(max_rows, device=dev)), cut, device=dev)
+    for buf in drv.resident():
+        buf.emb.copy_(torch.randn(max_rows, D, device=dev, generator=gen) * 1e-3)
+        buf.state.zero_()
+    ident = torch.arange(max_rows, device=dev)
+    nsteps_epoch = len(drv.steps)
+    total_steps = args.warmup + args.steps
+    local_slots = drv.local_slots
+
+    def batches_of(n):
+        return [(o, min(B, n - o), 0) for o in range(0, n, B)]
+
+    def split(bucket, edges, which):
+        """The two half sub-buckets of a bucket, by the rows of its circulating side (device sub_bucket)."""
+        l, r, rl = edges
+        n = l.shape[0]
+        rel_in = rl if rl is not None else torch.zeros(n, dtype=torch.long, device=dev)
+        out = [torch.empty(n, dtype=torch.long, device=dev) for _ in range(3)]
+        nl, nr = (2, 1) if which == "lhs" else (1, 2)
+        res = native.sub_bucket(l, r, rel_in, [max_rows], [ident], [max_rows], [ident], out[0], out[1], out[2], nl, nr, 1, True)
+        keys = [(0, 0), (1, 0)] if which == "lhs" else [(0, 0), (0, 1)]
+        return [(res[k][0], res[k][1], res[k][2] if rl is not None else None) for k in keys]
+
+    def plan_step(k):
+        """Whole-bucket edges of every bucket this rank trains in schedule step k."""
+        st = drv.steps[k % nsteps_epoch]
+        return {(s, bk): draw(bk, bucket_edges) for s in local_slots for bk in st.buckets[s]}
+
+    def presplit(k, whole):
+        st = drv.steps[k % nsteps_epoch]
+        out = {}
+        for s in local_slots:
+            a, b = st.holds[s]
+            out[(b, a)] = split((b, a), whole[(s, (b, a))], "lhs")
+            out[(a, b)] = split((a, b), whole[(s, (a, b))], "rhs")
+            for bk in st.buckets[s][2:]:
+                out[bk] = whole[(s, bk)]
+        return out
+
+    def optimizer_for(table, state):
+        o = T.RowAdagrad([table], lr=0.1)
+        o.state[id(table)]["sum"] = state
+        return o
+
+    cur = {}
+
+    def train_fn(bucket, lhs, rhs, sub):
+        e = cur["edges"][bucket]
+        l, r, rl = e if sub is None else e[sub[1]]
+        if l.shape[0] == 0:
+            return
+        model.clear_all_embeddings()
+        model.set_embeddings("e", T.Side.LHS, lhs[0])
+        model.set_embeddings("e", T.Side.RHS, rhs[0])
+        trainer.partitioned_optimizers.clear()
+        trainer.partitioned_optimizers["e", bucket[0]] = optimizer_for(lhs[0], lhs[1])
+        if rhs[0].data_ptr() != lhs[0].data_ptr():
+            trainer.partitioned_optimizers["e", bucket[1]] = optimizer_for(rhs[0], rhs[1])
+        trainer.train_batches(model, l, r, rl, batches_of(l.shape[0]), want_per_batch=False)
+        cur["edges_done"] += l.shape[0]
+
+    shared = [t for t in model.parameters()]
+    shared_state = [trainer.model_optimizer.sum_for(t) for t in shared] if shared else []
+
+    def after_step(st):
+        if shared:
+            average_relation_parameters(shared + shared_state)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    # device-resident pass: edges drawn and split into sub-buckets ahead of the timed region
+    whole = [plan_step(k) for k in range(total_steps)]
+    pre = [presplit(k, whole[k]) for k in range(total_steps)]
+    host = [{key: tuple(None if t is None else t.cpu().pin_memory() for t in e) for key, e in whole[k].items()} for k in range(total_steps)]
+
+    def step_device(k):
+        cur["edges"] = pre[k]
+        drv.run_step(train_fn, after_step)
+
+    clocks = ClockSampler(int(os.environ.get("LOCAL_RANK", "0"))).start()
+    cur["edges_done"] = 0
+    for k in range(args.warmup):
+        step_device(k)
+    barrier()
+    nat = trainer._native
+    launches0 = nat.lib.pbg_launch_count(nat.ctx)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    cur["edges_done"] = 0
+    with clocks:
+        barrier()
+        e0.record()
+        for k in range(args.warmup, total_steps):
+            step_device(k)
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    edges_rank = cur["edges_done"]
+    launches = nat.lib.pbg_launch_count(nat.ctx) - launches0
+    trainer.read_stats()
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t)
+    te = torch.tensor([float(edges_rank)], device=dev, dtype=torch.float64)
+    dist.all_reduce(te)
+    value = float(te) / (ms / 1e3)
+
+    # end-to-end pass: whole-bucket edges in pinned host memory; copy, device sub_bucket, training and the read-back of
+    # the step's summed Stats inside the timed region.  The schedule continues where the first pass stopped (the driver
+    # keeps its position; the edge lists are reused in order, so that every step gets the buckets it trains).
+    offset = total_steps % nsteps_epoch
+
+    def step_host(k):
+        kk = k                                         # edge lists were drawn for schedule position k % epoch
+        up = {key: tuple(None if t is None else t.to(dev, non_blocking=True) for t in e) for key, e in host[kk].items()}
+        cur["edges"] = presplit(kk, up)
+        drv.run_step(train_fn, after_step)
+        return trainer.read_stats()
+
+    e2e = None
+    if offset == 0 or True:
+        # bring the driver back to the start of an epoch so that step k of this pass is schedule step k again
+        while drv.step_index % nsteps_epoch != 0:
+            cur["edges"] = pre[drv.step_index % nsteps_epoch] if drv.step_index % nsteps_epoch < total_steps else None
+            if cur["edges"] is None:
+                cur["edges"] = presplit(drv.step_index % nsteps_epoch, plan_step(drv.step_index % nsteps_epoch))
+            drv.run_step(train_fn, after_step)
+        for k in range(min(args.warmup, 2)):
+            step_host(k)
+        barrier()
+        cur["edges_done"] = 0
+        e0.record()
+        last = None
+        for k in range(min(args.warmup, 2), min(args.warmup, 2) + args.steps):
+            last = step_host(k % total_steps)
+        e1.record()
+        barrier()
+        ms_e2e = e0.elapsed_time(e1)
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        te = torch.tensor([float(cur["edges_done"])], device=dev, dtype=torch.float64)
+        dist.all_reduce(te)
+        e2e = {"value": float(te) / (float(t) / 1e3), "unit": "edges/sec",
+               "h2d_bytes_per_step": int((3 if dyn else 2) * 8 * float(te) / args.steps), "d2h_bytes_per_step": 40 * world,
+               "last_step_loss": last.metrics["loss"] if last is not None else None}
+
+    if rank == 0:
+        cfgd = _workload_config(args, w, bucket_edges)
+        cfgd["step"] = (f"one step of the epoch schedule: two buckets of {bucket_edges} edges per GPU (four in the last step of an epoch), "
+                        f"each trained as half sub-buckets of its circulating partition")
+        cfgd["schedule"] = (f"{nsteps_epoch} steps per epoch cover all {P * P} buckets; every GPU holds two partitions at a time")
+        cfgd["hand_off"] = ("the circulating partition travels to the ring neighbour in two halves over NCCL send/recv (NVLink), each "
+                            "half beside the training of the other; partitions are re-dealt between the levels of the schedule; "
+                            "all inside the timed region" + ("; shared relation parameters and their accumulators averaged with one "
+                                                             "all-reduce per step" if shared else ""))
+        line = {"metric": "edges/sec trained", "value": value, "unit": "edges/sec", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32" if args.precision == "fp32" else args.precision, "data": "synthetic",
+                "config": cfgd, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
+                "algorithmic_per_edge": {"flops": algorithmic(w)["flops"], "bytes": algorithmic(w)["bytes"]}}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def run_b200(args, w):
     import torch
     import torch.distributed as dist
     import torchbiggraph_b200 as T
     from torchbiggraph_b200 import _lib
-    from torchbiggraph_b200.buckets import OverlappedRing, ring_exchange
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -388,24 +624,18 @@ def run_b200(args, w):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     P, D, B = w["partitions"], w["dim"], w["batch"]
+    if world > 1 and P > 1:
+        return run_b200_epoch(args, w, world, rank, dev)
     step_edges = min(EDGES_PER_STEP_CAP if P > 1 else w["edges"], max(B, w["edges"] // (P * P)))
     samplers, bounds, gen = make_samplers(w, dev, seed=3)
-    # resident partitions: all of them on one GPU; two per GPU (lhs stays, rhs travels round the ring) otherwise
-    if world == 1:
-        mine = list(range(min(P, args.resident) if args.resident > 0 else P))
-    else:
-        mine = [(2 * rank) % P, (2 * rank + 1) % P]
+    # resident partitions: all of them (one GPU).  A workload of one partition on several GPUs is N independent
+    # replicas of the single-GPU run: nothing to exchange.
+    mine = list(range(min(P, args.resident) if args.resident > 0 else P))
     tables, states = {}, {}
-    max_rows = max(bounds[p + 1] - bounds[p] for p in range(P))
     for p in mine:
-        rows = bounds[p + 1] - bounds[p] if world == 1 else max_rows     # equal shapes for the ring
+        rows = bounds[p + 1] - bounds[p]
         tables[p] = torch.randn(rows, D, device=dev, generator=gen) * 1e-3
         states[p] = torch.zeros(rows, device=dev)
-    spare = None
-    if world > 1:
-        # the rhs partition travels round the ring: a second buffer of the same shape receives the
-        # incoming partition while the outgoing one is being sent; the two then swap roles
-        spare = (torch.empty_like(tables[mine[1]]), torch.empty_like(states[mine[1]]))
 
     dyn = bool(w.get("dynamic"))
     cfg = T.ConfigSchema(entities={"e": T.EntitySchema(num_partitions=P)},
@@ -423,14 +653,12 @@ def run_b200(args, w):
 
     opts = {p: optimizer_for(tables[p], states[p]) for p in mine}
 
-    seq = bucket_sequence(len(mine)) if world == 1 else None
+    seq = bucket_sequence(len(mine))
     total_steps = args.warmup + args.steps
     nprof = 2
 
     def bucket_for(step):
-        if world == 1:
-            return seq[step % len(seq)]
-        return mine[0], mine[1]
+        return seq[step % len(seq)]
 
     def bind(bk):
         pl, pr = bk
@@ -443,81 +671,14 @@ def run_b200(args, w):
 
     batches = [(o, min(B, step_edges - o), 0) for o in range(0, step_edges, B)]
 
-    rel_cdf = None
-    if dyn:
-        rw = torch.arange(1, w["rels"] + 1, device=dev, dtype=torch.float64).pow(-1.0)      # Zipf(1.0) relation frequencies
-        rel_cdf = (torch.cumsum(rw, 0) / rw.sum()).float()
-        rel_a = torch.randint(1, w["entities"], (w["rels"],), device=dev, generator=gen)     # planted maps v = a_r u + b_r mod N
-        rel_b = torch.randint(0, w["entities"], (w["rels"],), device=dev, generator=gen)
+    draw = EdgeDrawer(w, samplers, bounds, dev, gen)
 
     def draw_edges(bk):
-        pl, pr = bk
-        if not dyn:
-            return samplers[pl].draw(step_edges, gen), samplers[pr].draw(step_edges, gen), None
-        n = w["entities"]
-        rel = torch.searchsorted(rel_cdf, torch.rand(step_edges, device=dev, generator=gen)).clamp_(max=w["rels"] - 1)
-        u = torch.randint(0, n, (step_edges,), device=dev, generator=gen)
-        v = (rel_a[rel] * u + rel_b[rel]) % n
-        noisy = torch.rand(step_edges, device=dev, generator=gen) < 0.2
-        v = torch.where(noisy, torch.randint(0, n, (step_edges,), device=dev, generator=gen), v)
-        return u, v, rel
+        return draw(bk, step_edges)
 
-    # ---- several GPUs: the rhs partition travels round the ring in two halves, beside training ------
-    # A bucket (A, B) is trained as the sub-buckets (A, B[:cut]) and (A, B[cut:]) (edges grouped by the
-    # half of their rhs row, as the reference's GPU trainer groups edges by sub-partition); the half
-    # just trained leaves for the next rank while the other half trains, and arrives in the other
-    # buffer of the receiver before the bucket after next needs it.
-    halves_on = world > 1 and P > 1 and not dyn
-    if halves_on:
-        ring = OverlappedRing(dev)
-        pr0 = mine[1]
-        real_rows = bounds[pr0 + 1] - bounds[pr0]
-        cut = real_rows // 2
-        cuts = [(0, cut), (cut, tables[pr0].shape[0])]
-        half_samplers = [samplers[pr0].part(0, cut), samplers[pr0].part(cut, real_rows)]
-        bufs = [(tables[pr0], states[pr0]), spare]
-        views = [[(b[0][lo:hi], b[1][lo:hi]) for lo, hi in cuts] for b in bufs]
-        half_opts = [[optimizer_for(t, st) for t, st in vb] for vb in views]
-        sub_edges = step_edges // 2
-        step_edges = 2 * sub_edges
-        sub_batches = [(o, min(B, sub_edges - o), 0) for o in range(0, sub_edges, B)]
-        ring_state = {"cur": 0, "pend": [None, None]}
-
-        def draw_edges(bk):                       # noqa: F811  (two sub-buckets per bucket)
-            pl, _ = bk
-            return [(samplers[pl].draw(sub_edges, gen), half_samplers[h].draw(sub_edges, gen), None) for h in (0, 1)]
-
-        def train_bucket(edges, want_per_batch):
-            cur, pend = ring_state["cur"], ring_state["pend"]
-            out = []
-            for h in (0, 1):
-                OverlappedRing.finish(pend[h])    # this half has arrived (and the other buffer's half has left)
-                tv, _ = views[cur][h]
-                model.clear_all_embeddings()
-                model.set_embeddings("e", T.Side.LHS, tables[mine[0]])
-                model.set_embeddings("e", T.Side.RHS, tv)
-                trainer.partitioned_optimizers.clear()
-                trainer.partitioned_optimizers["e", mine[0]] = opts[mine[0]]
-                trainer.partitioned_optimizers["e", pr0] = half_opts[cur][h]
-                l, r, rl = edges[h]
-                res = trainer.train_batches(model, l, r, rl, sub_batches, want_per_batch=want_per_batch)
-                if want_per_batch:
-                    out.extend(res)
-                pend[h] = ring.start(list(views[cur][h]), list(views[1 - cur][h]))
-            ring_state["cur"] = 1 - cur
-            return out
-
-        def drain():
-            for h in (0, 1):
-                OverlappedRing.finish(ring_state["pend"][h])
-                ring_state["pend"][h] = None
-    else:
-        def train_bucket(edges, want_per_batch):
-            l, r, rl = edges
-            return trainer.train_batches(model, l, r, rl, batches, want_per_batch=want_per_batch)
-
-        def drain():
-            pass
+    def train_bucket(edges, want_per_batch):
+        l, r, rl = edges
+        return trainer.train_batches(model, l, r, rl, batches, want_per_batch=want_per_batch)
 
     # ---- device-resident pass: `value` -------------------------------------------------------
     dev_edges = [draw_edges(bucket_for(s)) for s in range(total_steps + nprof)]
@@ -529,22 +690,9 @@ def run_b200(args, w):
 
     host_edges = [to_host(e) for e in dev_edges[: total_steps]]
 
-    def step_any(edges, want_per_batch):
-        if halves_on:
-            return train_bucket(edges, want_per_batch)
-        nonlocal spare
-        res = train_bucket(edges, want_per_batch)
-        if world > 1 and P > 1:
-            p = mine[1]
-            ring_exchange([tables[p], states[p]], list(spare))
-            (tables[p], states[p]), spare = spare, (tables[p], states[p])     # swap roles, no copy
-            opts[p] = optimizer_for(tables[p], states[p])
-        return res
-
     def step_device(s):
-        if not halves_on:
-            bind(bucket_for(s))
-        step_any(dev_edges[s], False)
+        bind(bucket_for(s))
+        train_bucket(dev_edges[s], False)
 
     def barrier():
         if world > 1:
@@ -563,7 +711,6 @@ def run_b200(args, w):
         e0.record()
         for s in range(args.warmup, total_steps):
             step_device(s)
-        drain()
         e1.record()
         barrier()
     ms = e0.elapsed_time(e1)
@@ -579,9 +726,8 @@ def run_b200(args, w):
     def step_host(s):
         # the step's result read back: the summed Stats of its batches (loss, violators, count), one
         # 40-byte device-to-host read that waits for the step
-        if not halves_on:
-            bind(bucket_for(s))
-        step_any(host_edges[s], False)
+        bind(bucket_for(s))
+        train_bucket(host_edges[s], False)
         return trainer.read_stats()
 
     for s in range(min(args.warmup, 2)):
@@ -591,7 +737,6 @@ def run_b200(args, w):
     last = None
     for s in range(args.warmup, total_steps):
         last = step_host(s)
-    drain()
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1)
@@ -644,7 +789,6 @@ def run_b200(args, w):
     check(nat.lib.pbg_set_profiling(nat.ctx, 2), nat.ctx)     # halves of a wave one after the other: a pair brackets its kernels alone
     for s in range(total_steps, total_steps + nprof):
         step_device(s)
-    drain()
     msc = (C.c_double * 7)()
     lc = (C.c_int64 * 7)()
     check(nat.lib.pbg_kernel_times(nat.ctx, msc, lc), nat.ctx)
@@ -692,7 +836,7 @@ def run_b200(args, w):
         line = {"metric": "edges/sec trained", "value": value, "unit": "edges/sec", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "f32" if args.precision == "fp32" else args.precision, "data": "synthetic",
-                "config": workload_config(args, w, step_edges, halves_on), "e2e": e2e, "gpu_launches": int(launches),
+                "config": workload_config(args, w, step_edges), "e2e": e2e, "gpu_launches": int(launches),
                 "clocks": clocks.summary(), "roofline": roof, "kernels": per_class,
                 "algorithmic_per_edge": {"flops": alg["flops"], "bytes": alg["bytes"]},
                 "edges_per_sec_hbm_bound": pk["hbm_gbs"] * 1e9 / alg["bytes"]}

@@ -34,6 +34,7 @@ struct pbg_context {
   void *tcplan = nullptr;       // tensor maps of the tcgen05 contractions
   void *pairplan = nullptr;     // tensor maps of the fused score + loss kernel (standard relations, plane tiers)
   bool fused = false;           // training runs gather -> fused score / loss -> dual gradient product
+  bool fused_halves = false;    // ... as two halves of the wave on two streams (PBG_HALVES=1; for comparisons)
   float *psum = nullptr;        // partial gradient rows of hub rows, indexed by slot position
   long long *hublist = nullptr;
   int *hubcnt = nullptr;
@@ -194,22 +195,23 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     for (int s2 = 0; s2 < 2; ++s2) oA[s2] = take(nN * Ma * 4);
   }
   const int Dpb = (cfg->dim + 7) / 8 * 8, Kb = (c->Mm + 7) / 8 * 8;
-  size_t oXB[4] = {0, 0, 0, 0}, oAB[2] = {0, 0}, oTB[2] = {0, 0}, oTT[2] = {0, 0};
+  size_t oXB[4] = {0, 0, 0, 0}, oAB[2] = {0, 0}, oTB[2] = {0, 0};
   // Standard relations under the dot / cos comparators with one score tile per chunk block: the fused
   // score + loss kernel and the dual gradient product (pbg_pair.cu).  PBG_FUSED=0 in the environment keeps
   // the separate score, loss and coefficient kernels (for comparisons).
-  const int Kp = (c->Pm + 7) / 8 * 8;
   {
     const char *env = getenv("PBG_FUSED");
     c->fused = planes && !dyn && !matrix_op && cfg->comparator < PBG_CMP_L2 && c->Pm <= 128 && c->Mm <= 256 &&
                !(env && env[0] == '0');
+    const char *envh = getenv("PBG_HALVES");
+    c->fused_halves = envh && envh[0] == '1';
   }
   if (planes) {
     oXB[0] = take(nN * npl * Dpb * 2); oXB[1] = take(nN * npl * Dpb * 2);
     if (dyn) { oXB[2] = take(nQ * npl * Dpb * 2); oXB[3] = take(nQ * npl * Dpb * 2); oTB[0] = take(nQ * npl * Kb * 2); oTB[1] = take(nQ * npl * Kb * 2); }
     else { oXB[2] = oXB[1]; oXB[3] = oXB[0]; oAB[0] = take(nN * npl * Kb * 2); oAB[1] = take(nN * npl * Kb * 2); }
     if (c->fused)
-      for (int p = 0; p < 2; ++p) { oTB[p] = take(nQ * npl * Kb * 2); oTT[p] = take(nN * npl * Kp * 2); }
+      for (int p = 0; p < 2; ++p) oTB[p] = take(nQ * npl * Kb * 2);
   }
   for (int p = 0; p < 2; ++p) {
     oS[p] = take(nQ * c->Ms * 4); oSpos[p] = take(nQ * 4); oLoss[p] = take(nQ * 4); oViol[p] = take(nQ * 4);
@@ -248,9 +250,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   for (int p = 0; p < 2; ++p) {
     b.AB[p] = (planes && !dyn) ? (unsigned short *)(c->ws + oAB[p]) : nullptr;
     b.TB[p] = (planes && (dyn || c->fused)) ? (unsigned short *)(c->ws + oTB[p]) : nullptr;
-    b.TT[p] = c->fused ? (unsigned short *)(c->ws + oTT[p]) : nullptr;
   }
-  b.Kp = Kp;
   b.xrows[0] = b.xrows[1] = c->Mm;
   b.xrows[2] = b.xrows[3] = dyn ? c->Pm : c->Mm;
   b.grows[0] = b.grows[1] = c->Mm;
@@ -535,7 +535,11 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
     // kernels can run as two independent halves on two streams: the memory-bound kernels of one
     // half fill the SMs' idle issue slots while the other half's contractions run.
     d.blk0 = 0;
-    if (kk >= 2 && c->profile_serial) {
+    if (c->fused && !c->fused_halves) {
+      // the fused score kernel computes both problems of a chunk block in one CTA: a wave of 14 batches of 10
+      // chunks is one round of 140 CTAs, where its halves would each leave half of the SMs idle
+      run_part(c, d, wb, w, c->stream);
+    } else if (kk >= 2 && c->profile_serial) {
       int ka = (kk + 1) / 2;
       WaveDims da = d, db = d;
       da.nblk = ka * d.Cm;

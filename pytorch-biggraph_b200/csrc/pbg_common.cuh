@@ -83,10 +83,8 @@ struct WaveBufs {
   //   XB[a]     [nblk][3][xrows[a]][Dpb]   planes of the operand rows N0, N1, Q0, Q1 (aliased like X)
   //   AB[side]  [nblk][3][Mm][Kb]          planes of the merged coefficient matrices (standard relations)
   //   TB[p]     [nblk][3][Pm][Kb]          planes of the coefficient matrices T_p (dynamic relations)
-  //   TT[p]     [nblk][planes][Mm][Kp]       T_p transposed (standard relations with the fused score / loss kernel,
-  //                                          which then also fills TB[p]; AB stays unused)
-  unsigned short *XB[4], *AB[2], *TB[2], *TT[2];     // null outside that tier
-  int Kp;                            // row stride of TT in elements (Pm rounded up to 8)
+  //                                          (also standard relations with the fused score / loss kernel; AB is then unused)
+  unsigned short *XB[4], *AB[2], *TB[2];     // null outside that tier
   int Dpb, Kb;                       // row strides in elements (D and Mm rounded up to 8: 16-byte rows)
   int npl;                           // planes per value: 3 (bf16x6: all six products of order <= 2) or 2 (bf16x3: b0.b0 + b0.b1 + b1.b0)
   float *spos[2];                    // positive scores [nblk][Pm]

@@ -54,8 +54,9 @@ struct TcGeom {
   int tr;                // the output map is that of the transposed matrix: tile element (row, col) goes to C[col][row]
   // Dual mode (standard relations, plane tiers, transposed gradient without a merged coefficient matrix):
   //   GN_side^T (D x Mm) = N_other^T[:, k < K1] . B1   +   N_other^T[:, k < K] . B2   (B2 fills the first BN2 columns)
-  // with B1 = TT[side] (rows m, k = i < K1 = Pm) and B2 = TB[other] (rows i < Pm, k = j < K = Mm): the two
-  // halves of the combined matrix A[side][m][j] = T_side[j][m] + T_other[m][j] as two K-major B operands.
+  // with B1[k = i][n = m] = T_side[i][m] and B2[n = i][k = j] = T_other[i][j]: the two halves of the combined
+  // matrix A[side][m][j] = T_side[j][m] + T_other[m][j], both read from the row-major coefficient planes TB --
+  // B1 as an MN-major operand (K1 = Pm rows), B2 as a K-major one (BN2 = Pm rounded up to 16 rows, K = Mm).
   // A stage holds the A tile, B1 (for the k-blocks below K1) and B2.
   int dual, K1, BN2;
 };
@@ -119,7 +120,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
   const uint32_t b_plane = B_MN ? (uint32_t)b_atoms * BOX_BYTES : (uint32_t)g.BN * ROW_BYTES;   // bytes of one B tile (plane)
   const uint32_t b_used = PLANES ? (uint32_t)NPL * b_plane : b_plane;
   const uint32_t stage_tx = A_BYTES + b_used;
-  const bool dual = PLANES && A_MN && !B_MN && g.dual != 0;
+  const bool dual = PLANES && A_MN && B_MN && g.dual != 0;
   const int nkb1 = dual ? (g.K1 + KB - 1) / KB : 0;                    // k-blocks that carry B1
   const uint32_t b2_plane = (uint32_t)g.BN2 * ROW_BYTES;                 // dual: one plane of the B2 tile
   // persistent tile loop: tile t -> (n tile, m tile, chunk block, problem); every role walks the same list
@@ -166,8 +167,8 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
             else { int pl = lane >> 1, mb = lane & 1; tma_load_4d(dA + pl * A_PLANE + mb * BOX_BYTES, &maps.a[p], m0 + mb * 64, k0, pl, blk, fb); }
           } else if (lane < a_boxes + b_boxes) {
             int ib = lane - a_boxes;
-            if (!B_MN) { if (with_b1) tma_load_4d(dB + ib * b_plane, &maps.b[p], k0, n0, ib, blk, fb); }
-            else { int pl = ib / b_atoms, nb = ib - pl * b_atoms; tma_load_4d(dB + pl * b_plane + nb * BOX_BYTES, &maps.b[p], n0 + nb * 64, k0, pl, blk, fb); }
+            if (!B_MN) tma_load_4d(dB + ib * b_plane, &maps.b[p], k0, n0, ib, blk, fb);
+            else if (with_b1) { int pl = ib / b_atoms, nb = ib - pl * b_atoms; tma_load_4d(dB + pl * b_plane + nb * BOX_BYTES, &maps.b[p], n0 + nb * 64, k0, pl, blk, fb); }
           } else if (dual && lane < a_boxes + b_boxes + NPL) {
             int ib = lane - a_boxes - b_boxes;
             tma_load_4d(dB + b_used + ib * b2_plane, &maps.b2[p], k0, 0, ib, blk, fb);
@@ -188,7 +189,7 @@ tc_gemm_kernel(const __grid_constant__ TcMaps maps, TcGeom g, WaveDims d, WaveBa
     const uint32_t fmt = PLANES ? 1u : 2u;            // operand format: bf16 (kind::f16) or tf32
     const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                            ((uint32_t)(g.BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-    const uint32_t idesc2 = (idesc & ~(0x3Fu << 17)) | ((uint32_t)(g.BN2 >> 3) << 17);      // dual: the B2 products are BN2 columns wide
+    const uint32_t idesc2 = (idesc & ~((0x3Fu << 17) | (1u << 16))) | ((uint32_t)(g.BN2 >> 3) << 17);   // dual: the B2 products are K-major, BN2 columns wide
     long long git = 0, j = 0;
     for (long long t = blockIdx.x; t < ntiles && !failed; t += gridDim.x) {
       int p, blk, m0, n0;
@@ -449,13 +450,13 @@ void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int
         pl->gradt.a[p] = pl->gradm.b[p];
         ok &= encode4_planes(&pl->gradt.b[p], w.AB[p], npl, d.Mm, d.Mm, d.Mm, nblk_max, w.Kb, 32, pl->bn_score);
         pl->gradt.c[p] = pl->gradm.c[p];
-        if (w.TT[0]) {
-          // dual mode: B1 = TT[side] (rows m < Mm, k = i < Pm), B2 = TB[other side] (rows i < Pm, k = j < Mm); what lies
-          // beyond those extents is outside the maps and arrives as zeros
+        if (w.TB[0]) {
+          // dual mode: B1 = TB[side] read MN-major (k = i < Pm rows, n = m < Mm), B2 = TB[other side] read K-major (rows
+          // i < Pm, k = j < Mm); what lies beyond those extents is outside the maps and arrives as zeros
           pl->has_dual = true;
           pl->bn2 = (d.Pm + 15) / 16 * 16;
           pl->gradu.a[p] = pl->gradm.b[p];
-          ok &= encode4_planes(&pl->gradu.b[p], w.TT[p], npl, d.Pm, d.Mm, d.Mm, nblk_max, w.Kp, 32, pl->bn_score);
+          ok &= encode4_planes(&pl->gradu.b[p], w.TB[p], npl, d.Mm, d.Pm, d.Pm, nblk_max, w.Kb, 64, 32);
           ok &= encode4_planes(&pl->gradu.b2[p], w.TB[1 - p], npl, d.Mm, d.Pm, d.Pm, nblk_max, w.Kb, 32, pl->bn2);
           pl->gradu.c[p] = pl->gradm.c[p];
         }
@@ -562,7 +563,7 @@ int launch_score_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
   return 1;
 }
 
-// Standard relations, plane tiers, coefficient planes TT / TB written by the fused score kernel: the transposed
+// Standard relations, plane tiers, coefficient planes TB written by the fused score kernel: the transposed
 // gradient product with two B operands per stage (see TcGeom).
 int launch_grad_dual_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, void *plan, cudaStream_t st) {
   TcPlan *pl = (TcPlan *)plan;
@@ -575,8 +576,8 @@ int launch_grad_dual_tc(const WaveDims &d, const WaveBatches &wb, const WaveBufs
   const int sms = pbg_sm_count();
   const dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   const size_t smem = 4 * (128 * 128 + 256 * 128) + 4 * 2 * 4096 + 1024;
-  if (pl->nterms == 6) launch_tc_inst<true, false, 6, false>(pl->gradu, g, d, wb, w.errflag, grid, smem, st);
-  else launch_tc_inst<true, false, 2, false>(pl->gradu, g, d, wb, w.errflag, grid, smem, st);
+  if (pl->nterms == 6) launch_tc_inst<true, true, 6, false>(pl->gradu, g, d, wb, w.errflag, grid, smem, st);
+  else launch_tc_inst<true, true, 2, false>(pl->gradu, g, d, wb, w.errflag, grid, smem, st);
   return 1;
 }
 

@@ -9,22 +9,21 @@
 // block crosses L2 -> shared memory once per k-stage instead of 1.5 times, and one CTA ends up with the
 // score rows of both problems in tensor memory (two accumulators of up to 256 columns).
 //
-// Epilogue (four warps, one thread per positive row i): what loss_kernel / loss_softmax_kernel do for a
+// Epilogue (sixteen warps, four threads per positive row i, each with two 32-column chunks of the row): what loss_kernel / loss_softmax_kernel do for a
 // row, straight from tensor memory -- masks (model.py:566-580, 836-844), logistic / ranking / softmax
 // (losses.py:53-161), relation and edge weight (batching.py:139-150), violators (train_cpu.py:98-99) --
 // and the coefficient rows T_p[i][:] = d(loss)/d(score) with the positive pair in the diagonal, written
-// as bf16 planes in the two layouts the gradient contraction reads as K-major B operands:
-//     TB[p][blk][plane][i][j] = T_p[i][j]        (rows i < Pm, k = j < Mm)
-//     TT[p][blk][plane][j][i] = T_p[i][j]        (rows j < Mm, k = i < Pm)
+// as bf16 planes TB[p][blk][plane][i][j] = T_p[i][j] (rows i < Pm, columns j < Mm), which the gradient
+// contraction reads both ways: K-major (k = j) and MN-major (k = i).
 // The score matrix itself never leaves the SM.  dot and cos comparators (the l2 family keeps the
 // separate kernels: its coefficients need the row and column sums of T).
 //
 // Every mbarrier wait is bounded (bit 1 of the error word, PBG_ERR_TIMEOUT); every TMA load is CTA-local.
 #include "pbg_tc.cuh"
 
-#define PAIR_THREADS 192          // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+#define PAIR_THREADS 576          // warp 0 TMA, warp 1 MMA, warps 2-17 epilogue
 #define PAIR_SMAX 4
-#define PAIR_SMEM_MAX (227 * 1024 - 1024)   // dynamic shared memory opted in: the 227 KB of a CTA less room for the static part
+#define PAIR_SMEM_MAX (227 * 1024 - 14 * 1024)   // dynamic shared memory opted in: the 227 KB of a CTA less its static part (reduction slots)
 
 struct PairMaps { CUtensorMap n[2]; };     // planes of N0 / N1: 4-D (k, row, plane, block), K-major boxes {32, rows_pad}
 
@@ -45,8 +44,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                  "=r"(r[30]), "=r"(r[31]) : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// 32 columns of this thread's tensor-memory lane back (the epilogue keeps per-score intermediates there)
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               :: "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+                  "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+                  "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+                  "r"(r[30]), "r"(r[31]) : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 
 template <int NPL>
+// (18 warps are allocated as 20: 96 registers per thread is what fits, which is what ptxas settles on)
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 pair_score_kernel(const __grid_constant__ PairMaps maps, PairGeom g, WaveDims d, WaveBatches wb, WaveBufs w) {
   extern __shared__ unsigned char smem_raw[];
@@ -54,6 +63,10 @@ pair_score_kernel(const __grid_constant__ PairMaps maps, PairGeom g, WaveDims d,
   __shared__ __align__(8) unsigned long long bars[2 * PAIR_SMAX + 2];
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile int failed;
+  __shared__ volatile int epi_go;
+  // partial results of the four epilogue warps that share a row: [quantity][problem][column group][row]
+  __shared__ float red_f[2][2][4][128];
+  __shared__ int red_i[2][4][128];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };                  // TMA landed
@@ -64,7 +77,7 @@ pair_score_kernel(const __grid_constant__ PairMaps maps, PairGeom g, WaveDims d,
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2 * PAIR_SMAX; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar0 + 8u * i));
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(accf_bar));
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" :: "r"(acce_bar));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 512;" :: "r"(acce_bar));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     failed = 0;
   }
@@ -151,19 +164,29 @@ pair_score_kernel(const __grid_constant__ PairMaps maps, PairGeom g, WaveDims d,
       ++j;
     }
   } else if (warp >= 2) {
-    // ---------------- epilogue: loss, statistics and coefficient planes of row i of both problems ----------------
+    // ---------------- epilogue: loss, statistics and coefficient planes of both problems ----------------
+    // Sixteen warps: the four warps that share a tensor-memory lane group (rows i = q * 32 + lane) take two
+    // 32-column chunks of the row each and combine their partial maxima / sums through shared memory.  A chunk
+    // is read from tensor memory, reduced, and (softmax) its exponentials are written back over the scores, so
+    // that every score costs one exponential and no more than 32 values are ever held in registers.
     long long j = 0;
     const int q = warp & 3;                            // the 32 tensor-memory lanes this warp may read
+    const int cg = (warp - 2) >> 2;                    // column group: chunks 2 cg and 2 cg + 1
     const int i = q * 32 + lane;                       // positive row of the chunk
     const int Mm = d.Mm, Pm = d.Pm;
-    const int nch = (w.Kb + 31) / 32;                  // 32-column chunks that hold coefficient columns (Kb <= BN)
+    auto epi_sync = [] { asm volatile("bar.sync 1, 512;" ::: "memory"); };     // the sixteen epilogue warps
     for (int t = blockIdx.x; t < d.nblk; t += gridDim.x) {
-      if (__any_sync(0xffffffffu, failed != 0)) break;           // warp-uniform exit (tcgen05.ld is warp-wide)
       if (!tile_live(t)) continue;
       const int blk = d.blk0 + t;
-      bool okw = true;
-      if (lane == 0) okw = mbar_wait(accf_bar, (uint32_t)j & 1, errflag);
-      if (!__all_sync(0xffffffffu, okw)) { failed = 1; break; }
+      // One thread waits for the accumulators (a bounded wait) and tells the others through shared memory: all
+      // sixteen warps take the same decision, so that none is left alone at the named barrier further down.
+      if (warp == 2 && lane == 0) {
+        bool go = failed == 0 && mbar_wait(accf_bar, (uint32_t)j & 1, errflag);
+        if (!go) failed = 1;
+        epi_go = go ? 1 : 0;
+      }
+      epi_sync();
+      if (!epi_go) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const BlockInfo bi = block_info(d, wb, blk);
       const bool row_valid = i < bi.n;
@@ -174,102 +197,141 @@ pair_score_kernel(const __grid_constant__ PairMaps maps, PairGeom g, WaveDims d,
         const int enabled = d.neg_enabled[p];
         const int Mlog = !enabled ? 0 : (d.batch_negs ? bi.Pl + d.U : d.U);   // columns of the reference's score matrix
         const float s = row_valid ? w.spos[p][prow] : 0.f;
-        const uint32_t trow = tmem + (uint32_t)p * 256u + ((uint32_t)(q * 32) << 16);
-        // column j of this row: ignored (model.py:566-580)?  Columns >= Mm do not exist.
-        auto masked = [&](int jc) {
-          if (!enabled || jc >= Mm) return true;
-          if (jc >= Pm) return false;                            // uniform negatives are never masked
-          if (!d.batch_negs) return true;                        // uniform-only mode: no batch negatives
-          return jc == i || jc >= bi.n;                          // own positive; padding of the last chunk
-        };
-        float lossv = 0.f, ds = 0.f, mshift = 0.f, scale = 0.f;
-        int viol = 0;
+        const int col0 = cg * 64;                                // first column of this warp's part of the row
+        const uint32_t trow = tmem + (uint32_t)p * 256u + ((uint32_t)(q * 32) << 16) + (uint32_t)col0;
+        const int nch = col0 >= w.Kb ? 0 : (col0 + 32 >= w.Kb ? 1 : 2);      // chunks of this warp that hold coefficient columns
+        // Which columns of this warp's chunks count for this row (model.py:566-580): bit jj of live[c] is set when
+        // column col0 + 32 c + jj exists (< Mm) and is not ignored -- uniform negatives (>= Pm) never are; a batch
+        // negative is when the mode has none, when it is the row's own positive, or padding of the last chunk.
+        auto below = [](int n) { return n <= 0 ? 0u : (n >= 32 ? 0xffffffffu : ((1u << n) - 1u)); };   // bits [0, n)
+        unsigned live[2];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int lo = col0 + c * 32;
+          unsigned m = 0u;
+          if (enabled) {
+            m = below(Mm - lo) & ~below(Pm - lo);                               // uniform negatives
+            if (d.batch_negs) {
+              unsigned bn = below((bi.n < Pm ? bi.n : Pm) - lo);                   // real batch negatives
+              if (i >= lo && i < lo + 32) bn &= ~(1u << (i - lo));                  // without the row's own positive
+              m |= bn;
+            }
+          }
+          live[c] = m;
+        }
+        auto masked = [&](int c, int jj) { return ((live[c] >> jj) & 1u) == 0u; };
         uint32_t r[32];
-        // ---- reduction passes over the row ----
+        float lossv = 0.f, ds = 0.f, scale = 0.f;
+        int viol = 0;
         if (d.loss == PBG_LOSS_SOFTMAX) {
           // -s + log(e^s + sum_j e^S_ij), masked entries are e^-1e9 = 0 (losses.py:143-159)
           float mx = -INFINITY;
-          for (int c = 0; c < nch; ++c) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            if (c >= nch) break;
             tmem_ld32(trow + (uint32_t)c * 32u, r);
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj) {
-              const float v = __uint_as_float(r[jj]);
-              if (!masked(c * 32 + jj)) { mx = fmaxf(mx, v); viol += v > s; }
+              const float sv = __uint_as_float(r[jj]);
+              if (!masked(c, jj)) { mx = fmaxf(mx, sv); viol += sv > s; }
             }
           }
+          red_f[0][p][cg][i] = mx;
+          red_i[p][cg][i] = viol;
+          epi_sync();
+          mx = fmaxf(fmaxf(red_f[0][p][0][i], red_f[0][p][1][i]), fmaxf(red_f[0][p][2][i], red_f[0][p][3][i]));
+          viol = red_i[p][0][i] + red_i[p][1][i] + red_i[p][2][i] + red_i[p][3][i];
           float m = fmaxf(mx, s);
           if (mx == -INFINITY) m = fmaxf(s, PBG_MASKED);         // every column masked
           float z = 0.f;
-          for (int c = 0; c < nch; ++c) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            if (c >= nch) break;
             tmem_ld32(trow + (uint32_t)c * 32u, r);
 #pragma unroll
-            for (int jj = 0; jj < 32; ++jj)
-              if (!masked(c * 32 + jj)) z += expf(__uint_as_float(r[jj]) - m);
+            for (int jj = 0; jj < 32; ++jj) {
+              const float e = masked(c, jj) ? 0.f : __expf(__uint_as_float(r[jj]) - m);
+              r[jj] = __float_as_uint(e);                        // kept in tensor memory: the coefficient is scale * e
+              z += e;
+            }
+            tmem_st32(trow + (uint32_t)c * 32u, r);
           }
+          red_f[1][p][cg][i] = z;
+          epi_sync();
+          z = (red_f[1][p][0][i] + red_f[1][p][1][i]) + (red_f[1][p][2][i] + red_f[1][p][3][i]);
           const float es = expf(s - m), Z = z + es;
-          if (Mlog > 0) { lossv = -s + m + logf(Z); ds = es / Z - 1.0f; scale = wr / Z; mshift = m; }
+          if (Mlog > 0) { lossv = -s + m + logf(Z); ds = es / Z - 1.0f; scale = wr / Z; }
           else viol = 0;                                          // losses.py:139-140: no negatives, loss 0, no gradient
         } else if (d.loss == PBG_LOSS_RANKING) {
-          // sum_j max(0, margin - s + S_ij) (losses.py:116-122)
-          for (int c = 0; c < nch; ++c) {
+          // sum_j max(0, margin - s + S_ij) (losses.py:116-122); the scores are replaced by the 0 / 1 indicator of an active column
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            if (c >= nch) break;
             tmem_ld32(trow + (uint32_t)c * 32u, r);
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj) {
               const float sj = __uint_as_float(r[jj]);
-              if (Mlog > 0 && !masked(c * 32 + jj)) {
-                const float v = (sj - s) + d.margin;
+              float act = 0.f;
+              if (Mlog > 0 && !masked(c, jj)) {
+                const float x = (sj - s) + d.margin;
                 viol += sj > s;
-                if (v > 0.f) { lossv += v; ds -= 1.0f; }
+                if (x > 0.f) { lossv += x; ds -= 1.0f; act = 1.0f; }
               }
+              r[jj] = __float_as_uint(act);
             }
+            tmem_st32(trow + (uint32_t)c * 32u, r);
           }
+          red_f[0][p][cg][i] = lossv; red_f[1][p][cg][i] = ds; red_i[p][cg][i] = viol;
+          epi_sync();
+          lossv = (red_f[0][p][0][i] + red_f[0][p][1][i]) + (red_f[0][p][2][i] + red_f[0][p][3][i]);
+          ds = (red_f[1][p][0][i] + red_f[1][p][1][i]) + (red_f[1][p][2][i] + red_f[1][p][3][i]);
+          viol = red_i[p][0][i] + red_i[p][1][i] + red_i[p][2][i] + red_i[p][3][i];
+          scale = wr;
         } else {
-          // softplus(-s) + (1/M) sum_j softplus(S_ij), M counts masked columns (losses.py:61-80)
+          // softplus(-s) + (1/M) sum_j softplus(S_ij), M counts masked columns (losses.py:61-80); the scores are replaced by sigmoid(S)
           const float nw = Mlog > 0 ? 1.0f / (float)Mlog : 0.f;
-          for (int c = 0; c < nch; ++c) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            if (c >= nch) break;
             tmem_ld32(trow + (uint32_t)c * 32u, r);
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj) {
               const float sj = __uint_as_float(r[jj]);
-              if (!masked(c * 32 + jj)) { viol += sj > s; lossv += pair_softplus(sj); }
+              float sg = 0.f;
+              if (!masked(c, jj)) { viol += sj > s; lossv += pair_softplus(sj); sg = pair_sigmoid(sj); }
+              r[jj] = __float_as_uint(sg);
             }
+            tmem_st32(trow + (uint32_t)c * 32u, r);
           }
-          lossv = lossv * nw + pair_softplus(-s);
+          red_f[0][p][cg][i] = lossv; red_i[p][cg][i] = viol;
+          epi_sync();
+          lossv = ((red_f[0][p][0][i] + red_f[0][p][1][i]) + (red_f[0][p][2][i] + red_f[0][p][3][i])) * nw + pair_softplus(-s);
+          viol = red_i[p][0][i] + red_i[p][1][i] + red_i[p][2][i] + red_i[p][3][i];
           ds = -pair_sigmoid(-s);
           scale = wr * nw;
         }
         const float tdiag = wr * ds;                             // the positive pair, folded into the diagonal
-        // ---- coefficient row: planes into TB[p][i][:] (16-byte stores) and TT[p][:][i] (lanes are consecutive i) ----
+        // ---- coefficient row: planes into TB[p][i][:] (16-byte stores) ----
         unsigned short *tb = w.TB[p] + ((size_t)blk * NPL * Pm + (i < Pm ? i : 0)) * w.Kb;
-        unsigned short *tt = w.TT[p] + (size_t)blk * NPL * Mm * w.Kp + i;
-        const size_t tb_plane = (size_t)Pm * w.Kb, tt_plane = (size_t)Mm * w.Kp;
-        for (int c = 0; c < nch; ++c) {
+        const size_t tb_plane = (size_t)Pm * w.Kb;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          if (c >= nch) break;
           tmem_ld32(trow + (uint32_t)c * 32u, r);
 #pragma unroll
           for (int g8 = 0; g8 < 4; ++g8) {
             unsigned pk[3][4];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-              const int jj = g8 * 8 + u, jc = c * 32 + jj;
-              const float sj = __uint_as_float(r[jj]);
-              float tv = 0.f;
-              if (row_valid && !masked(jc)) {
-                if (d.loss == PBG_LOSS_SOFTMAX) tv = Mlog > 0 ? scale * expf(sj - mshift) : 0.f;
-                else if (d.loss == PBG_LOSS_RANKING) tv = (Mlog > 0 && (sj - s) + d.margin > 0.f) ? wr : 0.f;
-                else tv = scale * pair_sigmoid(sj);
-              }
+              const int jj = g8 * 8 + u, jc = col0 + c * 32 + jj;
+              float tv = row_valid ? scale * __uint_as_float(r[jj]) : 0.f;        // masked columns hold 0
               if (row_valid && jc == i) tv = tdiag;
               unsigned b0, b1, b2;
               bf16_planes(tv, b0, b1, b2);
-              if (i < Pm && jc < Mm) {
-                tt[(size_t)jc * w.Kp] = (unsigned short)b0;
-                tt[tt_plane + (size_t)jc * w.Kp] = (unsigned short)b1;
-                if (NPL > 2) tt[2 * tt_plane + (size_t)jc * w.Kp] = (unsigned short)b2;
-              }
               if (u & 1) { pk[0][u >> 1] |= b0 << 16; pk[1][u >> 1] |= b1 << 16; pk[2][u >> 1] |= b2 << 16; }
               else { pk[0][u >> 1] = b0; pk[1][u >> 1] = b1; pk[2][u >> 1] = b2; }
             }
-            const int j0 = c * 32 + g8 * 8;
+            const int j0 = col0 + c * 32 + g8 * 8;
             if (i < Pm && j0 < w.Kb) {
 #pragma unroll
               for (int pl = 0; pl < NPL; ++pl)
@@ -277,7 +339,7 @@ pair_score_kernel(const __grid_constant__ PairMaps maps, PairGeom g, WaveDims d,
             }
           }
         }
-        if (i < Pm) {
+        if (cg == 0 && i < Pm) {
           w.lossrow[p][prow] = row_valid ? wr * lossv : 0.f;
           w.violrow[p][prow] = row_valid ? viol : 0;
         }
@@ -319,7 +381,7 @@ void *pbg_pair_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max) {
   g.stage_bytes = 2 * w.npl * g.rows_pad * 64;
   const int room = PAIR_SMEM_MAX - 1024;                       // dynamic shared memory left for the stages (1 KB: alignment)
   g.nst = room / g.stage_bytes > PAIR_SMAX ? PAIR_SMAX : room / g.stage_bytes;
-  bool ok = g.nst >= 2 && w.TT[0] && w.TB[0];
+  bool ok = g.nst >= 2 && w.TB[0];
   // rows beyond the Mm operand rows of a block are outside the map: the box brings zeros for them
   for (int a = 0; a < 2; ++a)
     ok = ok && encode4_planes(&pl->maps.n[a], w.XB[a], w.npl, d.D, d.Mm, d.Mm, nblk_max, w.Dpb, 32, g.rows_pad);

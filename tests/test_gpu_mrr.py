@@ -22,7 +22,7 @@ SMALL = ("std_translation", "dyn_complex_diagonal")
 RUNS = [(case, k, prec) for case in SMALL
         for k, prec in ((1, "fp32"), (1, "tf32x3"), (16, "tf32x3"), (1, "bf16x6"), (14, "bf16x6"))]
 RUNS += [(case, 14, "bf16x3") for case in SMALL]
-RUNS += [("kg15k_shape", 1, "tf32x3"), ("kg15k_shape", 14, "bf16x6"), ("kg15k_shape", 4, "bf16x3"),
+RUNS += [("kg15k_shape", 1, "tf32x3"), ("kg15k_shape", 2, "bf16x6"), ("kg15k_shape", 3, "bf16x6"), ("kg15k_shape", 4, "bf16x3"),
          ("powerlaw_hubs", 1, "bf16x6"), ("powerlaw_hubs", 14, "bf16x6"), ("powerlaw_hubs", 14, "tf32x3"),
          ("powerlaw_hubs", 14, "bf16x3")]
 

@@ -191,3 +191,61 @@ def test_torch_port_matches_reference(name):
         np.testing.assert_allclose(G.numpy(), z[f"G_lhs_after_{step}"], rtol=1e-5, atol=1e-7)
         for side in m.theta:
             np.testing.assert_allclose(m.theta[side].detach().numpy(), z[f"theta_{side}_after_{step}"], rtol=1e-5, atol=1e-6)
+
+
+# ---------------------------------------------------------------- all_negs relations (model.py:582-617)
+def allnegs_cases():
+    import glob
+    return sorted(os.path.basename(p)[len("allnegs_"):-len(".npz")] for p in glob.glob(os.path.join(GOLDEN, "allnegs_*.npz")))
+
+
+def load_allnegs(name):
+    """(oracle config, oracle state, fixture) of a recorded all_negs case."""
+    from oracle.pbg_step import BucketState, StepConfig
+    z = np.load(os.path.join(GOLDEN, f"allnegs_{name}.npz"))
+    D = z["W_lhs"].shape[1]
+    cfg = StepConfig(dim=D, operator=str(z["op"]), comparator=str(z["comp"]), loss=str(z["loss"]), margin=float(z["margin"]),
+                     num_batch_negs=50, num_uniform_negs=0, dynamic=bool(z["dyn"]), num_rels=int(z["R"]) if bool(z["dyn"]) else 1)
+    Wl = z["W_lhs"].astype(np.float64)
+    Wr = z["W_rhs"].astype(np.float64) if bool(z["separate"]) else Wl
+    st = BucketState(Wl, np.zeros(len(Wl)), Wr, np.zeros(len(Wr)))
+    if z["theta_rhs"].shape[0]:
+        st.theta_rhs = z["theta_rhs"].astype(np.float64)
+    if z["theta_lhs"].shape[0]:
+        st.theta_lhs = z["theta_lhs"].astype(np.float64)
+    return cfg, st, z
+
+
+def allnegs_stats(cfg, sc):
+    """RankingEvaluator's Stats (eval.py:43-81) from forward scores: sums over the batch, both sides averaged."""
+    from oracle import pbg_step as O
+    ranks, loss, aucs = [], 0.0, []
+    for side in ("lhs", "rhs"):
+        pos, neg = sc[f"{side}_pos"], sc[f"{side}_neg"]
+        loss += O.loss_forward_backward(cfg.loss, cfg.margin, pos, neg)[0]
+        ranks.append((neg >= pos[:, None]).sum(1) + 1)
+        aucs.append(float((pos[:, None] > neg).mean()))
+    m = lambda xs: float(np.mean([x.sum() for x in xs]))
+    return dict(loss=loss, pos_rank=m(ranks), mrr=m([1.0 / r for r in ranks]), r1=m([r <= 1 for r in ranks]),
+                r10=m([r <= 10 for r in ranks]), r50=m([r <= 50 for r in ranks]), auc=float(np.mean(aucs)))
+
+
+@pytest.mark.parametrize("name", allnegs_cases())
+def test_all_negs_scores_and_evaluator_stats_match_the_reference(name):
+    from oracle import pbg_step as O
+    cfg, st, z = load_allnegs(name)
+    sc = O.score_all_negs(cfg, st, z["lhs"], z["rhs"], z["rel"])
+    np.testing.assert_allclose(sc["lhs_pos"], z["lhs_pos"], rtol=5e-5, atol=1e-5)
+    np.testing.assert_allclose(sc["rhs_pos"], z["rhs_pos"], rtol=5e-5, atol=1e-5)
+    # l2: an entity scored against its own row is -sqrt(max(q, 1e-30)) with q = 0 up to fp32 rounding of the expanded
+    # form (a few 1e-7, i.e. a score of a few 1e-4) in the reference, and exactly the clamp in float64
+    atol = 6e-4 if cfg.comparator == "l2" else 2e-5
+    for side in ("lhs", "rhs"):
+        want = z[f"{side}_neg"]
+        np.testing.assert_allclose(sc[f"{side}_neg"][:, : want.shape[1]], want, rtol=5e-5, atol=atol)
+    got = allnegs_stats(cfg, sc)
+    assert got["loss"] == pytest.approx(float(z["stat_loss"]), rel=1e-4)
+    for k in ("pos_rank", "mrr", "r1", "r10", "r50"):
+        assert got[k] == pytest.approx(float(z["stat_" + k]), rel=1e-5, abs=1e-5), k
+    n = int(z["stat_count"])
+    assert abs(got["auc"] - float(z["stat_auc"]) / n) <= 4 * 0.5 / np.sqrt(n)       # the reference samples n random pairs
