@@ -215,6 +215,16 @@ int pbg_eval_batch(pbg_context *ctx, const pbg_bucket *bucket,
                    const int64_t *uniform_lhs_dev, const int64_t *uniform_rhs_dev, uint64_t seed,
                    pbg_eval_stats *stats_out);
 
+/* The same evaluation for relations with all_negs=True (torchbiggraph/model.py:582-617, 648-650): the negatives
+ * of a side are ALL rows of its table, one chunk holds the whole batch, and the score of an edge against its
+ * own true entity is ignored.  rank = 1 + #(candidates scoring >= the positive) over lhs_rows - 1 (rhs_rows - 1)
+ * candidates; the loss is calc_loss over those score rows; Stats as pbg_eval_batch returns them.  The score rows
+ * are never stored: the table is scored in slabs of 8192 rows.  num_batch_negs / num_uniform_negs of the
+ * context are not used.  Not for the linear / affine operators. */
+int pbg_eval_batch_all_negs(pbg_context *ctx, const pbg_bucket *bucket,
+                            const int64_t *lhs_dev, const int64_t *rhs_dev, const int64_t *rel_dev,
+                            int32_t count, int32_t rel, uint64_t seed, pbg_eval_stats *stats_out);
+
 /* The sparse-row optimizer step alone: RowAdagrad.step on a sparse gradient
  * (torchbiggraph/row_adagrad.py:80-96).  rows: device int64 [n] (duplicates allowed, they are
  * summed first), grads: device float32 [n, dim]. */

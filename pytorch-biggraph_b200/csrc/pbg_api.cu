@@ -49,6 +49,7 @@ struct pbg_context {
   char *esort_mem = nullptr;
   long long *etab_dev = nullptr;      // per-relation tables of a sub_bucket call + its counts
   long long etab_cap = 0;
+  char *allnegs_mem = nullptr;        // scratch of pbg_eval_batch_all_negs, allocated at its first call
   // optional event timing per kernel class
   const float *edge_w = nullptr;   // per-edge weights for the next train / eval call (pbg_set_edge_weights)
   bool profiling = false;
@@ -319,6 +320,7 @@ extern "C" int pbg_destroy(pbg_context *c) {
   for (int i = 0; i < 3; ++i) if (c->edge_dev[i]) cudaFree(c->edge_dev[i]);
   for (int i = 0; i < 2; ++i) if (c->uni_dev[i]) cudaFree(c->uni_dev[i]);
   if (c->esort_mem) cudaFree(c->esort_mem);
+  if (c->allnegs_mem) cudaFree(c->allnegs_mem);
   if (c->etab_dev) cudaFree(c->etab_dev);
   for (int s = 0; s < 2; ++s) {
     if (c->ev_sorted[s]) cudaEventDestroy(c->ev_sorted[s]);
@@ -711,6 +713,42 @@ extern "C" int pbg_eval_batch(pbg_context *c, const pbg_bucket *bk, const int64_
   out->loss = (float)h[0];
   out->pos_rank = h[1] / div; out->mrr = h[2] / div; out->r1 = h[3] / div; out->r10 = h[4] / div; out->r50 = h[5] / div;
   out->auc = sides > 0 ? (h[6] + h[7]) / div : 0.0;          // = count * mean(side AUCs): averaged over count by the caller
+  out->count = count;
+  return rc;
+}
+
+#define PBG_ALLNEGS_SLAB 8192     // candidate rows transformed and scored at a time
+
+extern "C" int pbg_eval_batch_all_negs(pbg_context *c, const pbg_bucket *bk, const int64_t *lhs, const int64_t *rhs,
+                                       const int64_t *rel, int32_t count, int32_t relidx, uint64_t seed, pbg_eval_stats *out) {
+  if (!c || !out) return PBG_ERR_BAD_ARGUMENT;
+  memset(out, 0, sizeof *out);
+  if (count == 0) return PBG_OK;
+  if (!lhs || !rhs || count < 0 || count > c->cfg.max_batch_size)
+    return fail(c, PBG_ERR_BAD_ARGUMENT, "bad eval_batch_all_negs arguments (count %d, max_batch_size %d)", count, c->cfg.max_batch_size);
+  CU(c, cudaSetDevice(c->device));
+  WaveDims d;
+  WaveBufs w;
+  int rc = bind_bucket(c, bk, d, w);
+  if (rc) return rc;
+  if (d.matrix_op) return fail(c, PBG_ERR_UNSUPPORTED, "ranking against all entities has no device code for the linear / affine operators");
+  if (!d.dynamic && (relidx < 0 || relidx >= c->cfg.num_rels)) return fail(c, PBG_ERR_INDEX_RANGE, "relation %d outside [0, %d)", relidx, c->cfg.num_rels);
+  if (d.dynamic && d.op != PBG_OP_NONE && !rel) return fail(c, PBG_ERR_BAD_ARGUMENT, "dynamic relations need the rel array");
+  if (!c->allnegs_mem) CU(c, cudaMalloc(&c->allnegs_mem, pbg_allnegs_bytes(c->cfg.max_batch_size, c->Dp, PBG_ALLNEGS_SLAB)));
+  w.lhs = (const long long *)lhs; w.rhs = (const long long *)rhs; w.rel = (const long long *)rel;
+  w.ew = c->edge_w; c->edge_w = nullptr;
+  w.seed = seed;
+  const float wrel = bk->relation_weights ? bk->relation_weights[d.dynamic ? 0 : relidx] : 1.0f;
+  c->launches += launch_allnegs_eval(d, w, c->allnegs_mem, count, PBG_ALLNEGS_SLAB, d.dynamic ? 0 : relidx, wrel, c->eval_dev, c->stream);
+  CU(c, pbg_take_launch_error());
+  double h[8];
+  CU(c, cudaMemcpyAsync(h, c->eval_dev, sizeof h, cudaMemcpyDeviceToHost, c->stream));
+  rc = check_errflag(c);
+  int sides = (d.neg_enabled[0] ? 1 : 0) + (d.neg_enabled[1] ? 1 : 0);
+  double div = sides > 0 ? sides : 1;
+  out->loss = (float)h[0];
+  out->pos_rank = h[1] / div; out->mrr = h[2] / div; out->r1 = h[3] / div; out->r10 = h[4] / div; out->r50 = h[5] / div;
+  out->auc = sides > 0 ? (h[6] + h[7]) / div : 0.0;
   out->count = count;
   return rc;
 }

@@ -343,6 +343,9 @@ int launch_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                   const unsigned long long *keys, const unsigned int *vals, float lr, float rel_lr,
                   float *psum, long long *hublist, int *hubcnt, cudaStream_t st);
 int launch_eval(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, double *out8_dev, cudaStream_t st);
+size_t pbg_allnegs_bytes(int B, int Dp, int slab);
+int launch_allnegs_eval(const WaveDims &d, const WaveBufs &w, char *mem, int B, int slab, int rel_std, float wrel,
+                        double *out8_dev, cudaStream_t st);
 int launch_reg_value(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
 int launch_stats(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                  pbg_batch_stats *per_batch_dev, double *sum_dev, cudaStream_t st);

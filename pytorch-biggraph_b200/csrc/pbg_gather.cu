@@ -514,3 +514,344 @@ int launch_build_keys(const WaveDims &d, const WaveBatches &wb, const WaveBufs &
   build_keys_kernel<<<(d.nocc + 255) / 256, 256, 0, st>>>(d, wb, w, keys, vals);
   return 1;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Ranking against ALL entities of a side's table (relations with all_negs=True, torchbiggraph/model.py:582-617;
+// what RankingEvaluator needs for full-ranking MRR, torchbiggraph/eval.py:43-81).  One chunk holds the whole
+// batch, the negatives of a side are every row of its table, and an edge's own true entity is ignored.
+//   allnegs_rows_kernel     per edge: the two scored rows (prepared, operator applied where the mode says so)
+//                           and the positive score(s)
+//   allnegs_slab_kernel     a slab of table rows as candidates: global embedding, operator (standard relations,
+//                           rhs side), prepare -> Y[slab][Dp] and the row's |y|^2
+//   allnegs_score_kernel    64 x 64 tiles of scores between the batch's scored rows and the slab, never stored:
+//                           per (tile, edge) the count of candidates scoring >= the positive and the loss partials
+//   allnegs_merge_kernel    folds a slab's tiles into the per-edge running state, in tile order
+//   allnegs_finish_kernel   ranks, loss and the evaluator's sums
+// ------------------------------------------------------------------------------------------------
+struct AllNegs {
+  float *Q[2];            // [B][Dp]  Q[0]: scored against lhs candidates (op_rhs(rhs) rows), Q[1]: against rhs candidates
+  float *qn[2];           // [B] |q|^2 (l2 family)
+  float *pos[2];          // [B] positive score of problem 0 / 1
+  float *Y, *yn;          // candidate slab [slab][Dp], |y|^2
+  int *pcnt; float *pa, *pb;      // per (tile of the slab, edge): count, loss partials
+  int *cnt[2]; float *ra[2], *rb[2];   // running per-edge state of side 0 / 1
+  int B, slab;
+};
+
+template <int VEC>
+__global__ void __launch_bounds__(32 * GATHER_WARPS) allnegs_rows_kernel(WaveDims d, WaveBufs w, AllNegs a, int rel_std) {
+  int lane = threadIdx.x & 31;
+  int e = blockIdx.x * GATHER_WARPS + (threadIdx.x >> 5);
+  if (e >= a.B) return;
+  const int D = d.D;
+  long long il = w.lhs[e], ir = w.rhs[e], rl = d.dynamic ? 0 : rel_std;
+  if (d.dynamic && d.op != PBG_OP_NONE) rl = w.rel[e];
+  bool ok = il >= 0 && il < d.n_rows[0] && ir >= 0 && ir < d.n_rows[1] && (d.op == PBG_OP_NONE || (rl >= 0 && rl < d.num_rels));
+  float *q0 = a.Q[0] + (size_t)e * d.Dp, *q1 = a.Q[1] + (size_t)e * d.Dp;
+  if (!ok) {
+    if (lane == 0) { atomicOr(w.errflag, 1); a.pos[0][e] = 0.f; a.pos[1][e] = 0.f; a.qn[0][e] = 0.f; a.qn[1][e] = 0.f; }
+    zero_row<VEC>(q0, D, lane); zero_row<VEC>(q1, D, lane);
+    return;
+  }
+  const float *xl = w.W[0] + (size_t)il * D, *xr = w.W[1] + (size_t)ir * D;
+  float4 x[VEC], yl[VEC], yr[VEC], z[VEC];
+  // lhs row, prepared (no operator)
+  load_row<VEC>(x, xl, D, lane);
+  const float scl = renorm_row<VEC>(x, d.max_norm);
+  add_global<VEC>(x, w.glob[0], D, lane);
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) yl[c] = x[c];
+  float al = prepare_row<VEC>(yl, d.cmp);
+  float s1 = 0.f, a1 = al;
+  if (d.dynamic) {
+    // problem 1 scores op_lhs(lhs) against the rhs candidates
+    const float *th1 = (d.op != PBG_OP_NONE && w.theta[1]) ? w.theta[1] + (size_t)rl * D : nullptr;
+    apply_operator<VEC>(z, x, xl, th1, d.op, D, lane, nullptr, scl);
+    a1 = prepare_row<VEC>(z, d.cmp);
+    store_row<VEC>(q1, z, D, lane);
+  } else {
+    store_row<VEC>(q1, yl, D, lane);
+  }
+  // rhs row through the rhs operator, prepared
+  load_row<VEC>(x, xr, D, lane);
+  const float scr = renorm_row<VEC>(x, d.max_norm);
+  add_global<VEC>(x, w.glob[1], D, lane);
+  const float *th0 = (d.op != PBG_OP_NONE && w.theta[0]) ? w.theta[0] + (size_t)rl * D : nullptr;
+  apply_operator<VEC>(yr, x, xr, th0, d.op, D, lane, w.glob[1], scr);
+  float a0 = prepare_row<VEC>(yr, d.cmp);
+  store_row<VEC>(q0, yr, D, lane);
+  float s0 = positive_score<VEC>(yl, yr, d.cmp);          // problem 0: c(lhs, op_rhs(rhs))
+  if (d.dynamic) {
+    // problem 1: c(prepared rhs without operator, op_lhs(lhs))
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) yr[c] = x[c];
+    prepare_row<VEC>(yr, d.cmp);
+    s1 = positive_score<VEC>(yr, z, d.cmp);
+  } else {
+    s1 = s0;
+  }
+  if (lane == 0) {
+    a.pos[0][e] = s0; a.pos[1][e] = s1;
+    a.qn[0][e] = d.cmp >= PBG_CMP_L2 ? a0 : 0.f;
+    a.qn[1][e] = d.cmp >= PBG_CMP_L2 ? a1 : 0.f;
+  }
+}
+
+// candidates: rows [row0, row0 + n) of the table of `side`
+template <int VEC>
+__global__ void __launch_bounds__(32 * GATHER_WARPS) allnegs_slab_kernel(WaveDims d, WaveBufs w, AllNegs a, int side, long long row0, int n, int rel_std) {
+  int lane = threadIdx.x & 31;
+  int r = blockIdx.x * GATHER_WARPS + (threadIdx.x >> 5);
+  if (r >= n) return;
+  const int D = d.D;
+  const float *xrow = w.W[side] + (size_t)(row0 + r) * D;
+  float4 x[VEC], z[VEC];
+  load_row<VEC>(x, xrow, D, lane);
+  const float sc = renorm_row<VEC>(x, d.max_norm);
+  add_global<VEC>(x, w.glob[side], D, lane);
+  // standard relations apply the operator to every rhs row, negatives included; with dynamic relations negatives get none
+  const float *th = (side == 1 && !d.dynamic && d.op != PBG_OP_NONE && w.theta[0]) ? w.theta[0] + (size_t)rel_std * D : nullptr;
+  apply_operator<VEC>(z, x, xrow, th, d.op, D, lane, w.glob[side], sc);
+  float aux = prepare_row<VEC>(z, d.cmp);
+  store_row<VEC>(a.Y + (size_t)r * d.Dp, z, D, lane);
+  if (lane == 0) a.yn[r] = d.cmp >= PBG_CMP_L2 ? aux : 0.f;
+}
+
+#define AN_TILE 64
+// grid (edge tiles, candidate tiles of the slab); 256 threads, each a 4 x 4 block of the 64 x 64 score tile
+__global__ void __launch_bounds__(256) allnegs_score_kernel(WaveDims d, WaveBufs w, AllNegs a, int side, long long row0, int n) {
+  __shared__ float sq[16][AN_TILE + 1], sy[16][AN_TILE + 1];
+  __shared__ int scnt[16][AN_TILE];
+  __shared__ float sa[16][AN_TILE], sb[16][AN_TILE];
+  const int te = blockIdx.x, tc = blockIdx.y, t = threadIdx.x;
+  const int ty = t >> 4, tx = t & 15;                        // rows 4 ty .. 4 ty + 3 (edges), cols 4 tx .. (candidates)
+  const float *Q = a.Q[side];
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const int e0 = te * AN_TILE, c0 = tc * AN_TILE;
+  for (int k0 = 0; k0 < d.D; k0 += 16) {
+    // 64 rows x 16 k of each operand: thread t loads row t / 4, k (t % 4) * 4 .. + 3
+    int lr = t >> 2, lk = (t & 3) * 4;
+    float4 vq = f4zero(), vy = f4zero();
+    if (e0 + lr < a.B && k0 + lk < d.D) vq = ld4(Q + (size_t)(e0 + lr) * d.Dp + k0 + lk);
+    if (c0 + lr < n && k0 + lk < d.D) vy = ld4(a.Y + (size_t)(c0 + lr) * d.Dp + k0 + lk);
+    __syncthreads();
+    sq[lk][lr] = vq.x; sq[lk + 1][lr] = vq.y; sq[lk + 2][lr] = vq.z; sq[lk + 3][lr] = vq.w;
+    sy[lk][lr] = vy.x; sy[lk + 1][lr] = vy.y; sy[lk + 2][lr] = vy.z; sy[lk + 3][lr] = vy.w;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      float qv[4], yv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { qv[i] = sq[k][ty * 4 + i]; yv[i] = sy[k][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(qv[i], yv[j], acc[i][j]);
+    }
+  }
+  // comparator, the ignored true entity, count and loss partials of this thread's 4 candidates per edge
+  const long long *truth = side == 0 ? w.lhs : w.rhs;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int e = e0 + ty * 4 + i;
+    int cnt = 0;
+    float pa = 0.f, pb = d.loss == PBG_LOSS_SOFTMAX ? -INFINITY : 0.f;
+    if (e < a.B) {
+      const float pos = a.pos[side][e];
+      const long long tid = truth[e];
+      float sv[4];
+      bool live[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + tx * 4 + j;
+        live[j] = c < n && row0 + c != tid;
+        float s = acc[i][j];
+        if (d.cmp >= PBG_CMP_L2) {
+          float qv = (a.yn[c < n ? c : 0] - 2.0f * s) + a.qn[side][e];       // model.py:226-246
+          s = d.cmp == PBG_CMP_L2 ? -sqrtf(fmaxf(qv, 1e-30f)) : -qv;
+        }
+        sv[j] = s;
+        if (live[j]) {
+          cnt += s >= pos;
+          if (d.loss == PBG_LOSS_RANKING) pa += fmaxf(0.f, (s - pos) + d.margin);
+          else if (d.loss == PBG_LOSS_LOGISTIC) pa += fmaxf(s, 0.f) + log1pf(expf(-fabsf(s)));
+          else pb = fmaxf(pb, s);
+        }
+      }
+      if (d.loss == PBG_LOSS_SOFTMAX && pb > -INFINITY)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) if (live[j]) pa += expf(sv[j] - pb);
+    }
+    scnt[tx][ty * 4 + i] = cnt; sa[tx][ty * 4 + i] = pa; sb[tx][ty * 4 + i] = pb;
+  }
+  __syncthreads();
+  if (t < AN_TILE) {
+    const int e = e0 + t;
+    if (e < a.B) {
+      int cnt = 0;
+      float pa = 0.f, pb = d.loss == PBG_LOSS_SOFTMAX ? -INFINITY : 0.f;
+      for (int x = 0; x < 16; ++x) {                       // the 16 column groups in a fixed order
+        cnt += scnt[x][t];
+        if (d.loss == PBG_LOSS_SOFTMAX) {
+          float m2 = sb[x][t];
+          if (m2 > -INFINITY) {
+            float m = fmaxf(pb, m2);
+            pa = (pb > -INFINITY ? pa * expf(pb - m) : 0.f) + sa[x][t] * expf(m2 - m);
+            pb = m;
+          }
+        } else pa += sa[x][t];
+      }
+      size_t o = (size_t)tc * a.B + e;
+      a.pcnt[o] = cnt; a.pa[o] = pa; a.pb[o] = pb;
+    }
+  }
+}
+
+__global__ void allnegs_merge_kernel(WaveDims d, AllNegs a, int side, int ntiles, int first) {
+  int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= a.B) return;
+  int cnt = first ? 0 : a.cnt[side][e];
+  float ra = first ? 0.f : a.ra[side][e];
+  float rb = first ? (d.loss == PBG_LOSS_SOFTMAX ? -INFINITY : 0.f) : a.rb[side][e];
+  for (int tcl = 0; tcl < ntiles; ++tcl) {
+    size_t o = (size_t)tcl * a.B + e;
+    cnt += a.pcnt[o];
+    if (d.loss == PBG_LOSS_SOFTMAX) {
+      float m2 = a.pb[o];
+      if (m2 > -INFINITY) {
+        float m = fmaxf(rb, m2);
+        ra = (rb > -INFINITY ? ra * expf(rb - m) : 0.f) + a.pa[o] * expf(m2 - m);
+        rb = m;
+      }
+    } else ra += a.pa[o];
+  }
+  a.cnt[side][e] = cnt; a.ra[side][e] = ra; a.rb[side][e] = rb;
+}
+
+// out8: loss, pos_rank, mrr, r1, r10, r50 sums over both sides' ranks (as eval_reduce_kernel); AUC slots are filled by allnegs_auc_kernel
+__global__ void __launch_bounds__(256) allnegs_finish_kernel(WaveDims d, WaveBufs w, AllNegs a, float wrel, double *out8) {
+  __shared__ double sm[6][256];
+  int t = threadIdx.x;
+  double acc[6] = {0, 0, 0, 0, 0, 0};
+  for (int e = t; e < a.B; e += 256) {
+    const float wgt = wrel * (w.ew ? w.ew[e] : 1.0f);
+    for (int side = 0; side < 2; ++side) {
+      if (!d.neg_enabled[side]) continue;
+      const float pos = a.pos[side][e];
+      const long long n = d.n_rows[side];
+      float lossv;
+      if (d.loss == PBG_LOSS_RANKING) lossv = a.ra[side][e];
+      else if (d.loss == PBG_LOSS_LOGISTIC) lossv = a.ra[side][e] / (float)n + (fmaxf(-pos, 0.f) + log1pf(expf(-fabsf(pos))));   // M counts the ignored column
+      else {
+        float m = fmaxf(a.rb[side][e], pos);
+        float z = (a.rb[side][e] > -INFINITY ? a.ra[side][e] * expf(a.rb[side][e] - m) : 0.f) + expf(pos - m);
+        lossv = -pos + m + logf(z);
+      }
+      acc[0] += (double)(wgt * lossv);
+      int rk = a.cnt[side][e] + 1;
+      acc[1] += rk; acc[2] += 1.0 / rk; acc[3] += rk <= 1; acc[4] += rk <= 10; acc[5] += rk <= 50;
+    }
+  }
+  for (int k = 0; k < 6; ++k) sm[k][t] = acc[k];
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (t < o) for (int k = 0; k < 6; ++k) sm[k][t] += sm[k][t + o];
+    __syncthreads();
+  }
+  if (t < 6) out8[t] = sm[t][0];
+}
+
+// randomized AUC (torchbiggraph/util.py:415-428): `count` random (positive, (edge, candidate)) pairs per side; one warp per sample
+template <int VEC>
+__global__ void __launch_bounds__(32 * GATHER_WARPS) allnegs_auc_kernel(WaveDims d, WaveBufs w, AllNegs a, int rel_std, double *out8) {
+  int lane = threadIdx.x & 31;
+  int smp = blockIdx.x * GATHER_WARPS + (threadIdx.x >> 5);
+  int side = blockIdx.y;
+  if (smp >= a.B || !d.neg_enabled[side]) return;
+  const int D = d.D;
+  unsigned long long h = pbg_mix64(w.seed ^ pbg_mix64(0xA11CE5ull + (unsigned long long)side * 0x10001ull + smp));
+  int ei = (int)(h % (unsigned long long)a.B);
+  h = pbg_mix64(h);
+  int er = (int)(h % (unsigned long long)a.B);
+  h = pbg_mix64(h);
+  long long cand = (long long)(h % (unsigned long long)d.n_rows[side]);
+  const long long *truth = side == 0 ? w.lhs : w.rhs;
+  float neg;
+  if (cand == truth[er]) neg = PBG_MASKED;
+  else {
+    const float *xrow = w.W[side] + (size_t)cand * D;
+    float4 x[VEC], z[VEC], q[VEC];
+    load_row<VEC>(x, xrow, D, lane);
+    const float sc = renorm_row<VEC>(x, d.max_norm);
+    add_global<VEC>(x, w.glob[side], D, lane);
+    const float *th = (side == 1 && !d.dynamic && d.op != PBG_OP_NONE && w.theta[0]) ? w.theta[0] + (size_t)rel_std * D : nullptr;
+    apply_operator<VEC>(z, x, xrow, th, d.op, D, lane, w.glob[side], sc);
+    float yn = prepare_row<VEC>(z, d.cmp);
+    load_row<VEC>(q, a.Q[side] + (size_t)er * d.Dp, D, lane);
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) s += f4dot(q[c], z[c]);
+    s = warp_sum(s);
+    if (d.cmp >= PBG_CMP_L2) {
+      float qv = (yn - 2.0f * s) + a.qn[side][er];
+      s = d.cmp == PBG_CMP_L2 ? -sqrtf(fmaxf(qv, 1e-30f)) : -qv;
+    }
+    neg = s;
+  }
+  if (lane == 0 && a.pos[side][ei] > neg) atomicAdd(&out8[6 + side], 1.0);
+}
+
+size_t pbg_allnegs_bytes(int B, int Dp, int slab) {
+  size_t f = 2ull * B * Dp + 2ull * B + 2ull * B + (size_t)slab * Dp + slab;      // Q, qn, pos, Y, yn
+  size_t tiles = (size_t)(slab + AN_TILE - 1) / AN_TILE;
+  f += 3ull * tiles * B + 6ull * B;                                               // partials, running state
+  return f * 4 + 4096;
+}
+
+// Runs the whole evaluation of one batch against all rows of both tables; `mem` holds pbg_allnegs_bytes bytes.
+int launch_allnegs_eval(const WaveDims &d, const WaveBufs &w, char *mem, int B, int slab, int rel_std, float wrel,
+                        double *out8_dev, cudaStream_t st) {
+  AllNegs a;
+  float *p = (float *)mem;
+  auto take = [&](size_t n) { float *r = p; p += (n + 63) / 64 * 64; return r; };
+  a.B = B; a.slab = slab;
+  a.Q[0] = take((size_t)B * d.Dp); a.Q[1] = take((size_t)B * d.Dp);
+  a.qn[0] = take(B); a.qn[1] = take(B); a.pos[0] = take(B); a.pos[1] = take(B);
+  a.Y = take((size_t)slab * d.Dp); a.yn = take(slab);
+  const int tiles_slab = (slab + AN_TILE - 1) / AN_TILE;
+  a.pcnt = (int *)take((size_t)tiles_slab * B); a.pa = take((size_t)tiles_slab * B); a.pb = take((size_t)tiles_slab * B);
+  for (int s = 0; s < 2; ++s) { a.cnt[s] = (int *)take(B); a.ra[s] = take(B); a.rb[s] = take(B); }
+  int launches = 0;
+  const int vec = (d.D + 127) / 128;
+  const int ectas = (B + GATHER_WARPS - 1) / GATHER_WARPS;
+  cudaMemsetAsync(out8_dev, 0, 8 * sizeof(double), st);
+#define AN_V(K, ...) do { if (vec <= 1) K<1>__VA_ARGS__; else if (vec <= 2) K<2>__VA_ARGS__; else if (vec <= 4) K<4>__VA_ARGS__; else if (vec <= 8) K<8>__VA_ARGS__; else K<16>__VA_ARGS__; } while (0)
+  AN_V(allnegs_rows_kernel, <<<ectas, 32 * GATHER_WARPS, 0, st>>>(d, w, a, rel_std));
+  ++launches;
+  for (int side = 0; side < 2; ++side) {
+    if (!d.neg_enabled[side]) continue;
+    const long long N = d.n_rows[side];
+    bool first = true;
+    for (long long row0 = 0; row0 < N; row0 += slab) {
+      const int n = (int)(N - row0 < slab ? N - row0 : slab);
+      const int sctas = (n + GATHER_WARPS - 1) / GATHER_WARPS;
+      AN_V(allnegs_slab_kernel, <<<sctas, 32 * GATHER_WARPS, 0, st>>>(d, w, a, side, row0, n, rel_std));
+      const int ntiles = (n + AN_TILE - 1) / AN_TILE;
+      dim3 g((B + AN_TILE - 1) / AN_TILE, ntiles);
+      allnegs_score_kernel<<<g, 256, 0, st>>>(d, w, a, side, row0, n);
+      allnegs_merge_kernel<<<(B + 127) / 128, 128, 0, st>>>(d, a, side, ntiles, first ? 1 : 0);
+      first = false;
+      launches += 3;
+    }
+  }
+  allnegs_finish_kernel<<<1, 256, 0, st>>>(d, w, a, wrel, out8_dev);
+  dim3 ga(ectas, 2);
+  AN_V(allnegs_auc_kernel, <<<ga, 32 * GATHER_WARPS, 0, st>>>(d, w, a, rel_std, out8_dev));
+#undef AN_V
+  pbg_note_launch();
+  return launches + 2;
+}

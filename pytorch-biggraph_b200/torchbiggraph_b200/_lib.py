@@ -68,6 +68,8 @@ SYMBOLS = [
                                   C.c_uint64, _P, _P, _P, _P]),
     ("pbg_eval_batch", C.c_int, [_P, C.POINTER(PbgBucket), _P, _P, _P, C.c_int32, C.c_int32, _P, _P,
                                  C.c_uint64, C.POINTER(PbgEvalStats)]),
+    ("pbg_eval_batch_all_negs", C.c_int, [_P, C.POINTER(PbgBucket), _P, _P, _P, C.c_int32, C.c_int32,
+                                          C.c_uint64, C.POINTER(PbgEvalStats)]),
     ("pbg_neg_columns", C.c_int, [_P, C.c_int32] + [C.POINTER(C.c_int32)] * 4),
     ("pbg_row_adagrad", C.c_int, [_P, _P, _P, C.c_int64, _P, _P, C.c_int32, C.c_float]),
     ("pbg_row_adagrad_static", C.c_int, [_P, _P, C.c_int64, C.c_int32, _P, _P, C.c_int32, C.c_float, _P]),

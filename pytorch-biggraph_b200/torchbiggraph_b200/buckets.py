@@ -150,6 +150,20 @@ def average_relation_parameters(tensors: Sequence[torch.Tensor], group=None) -> 
         t.div_(world)
 
 
+def sum_relation_parameter_deltas(tensors: Sequence[torch.Tensor], before: Sequence[torch.Tensor], group=None) -> None:
+    """The reference's reconciliation (torchbiggraph/parameter_sharing.py:662-672): every trainer's change since the
+    last exchange is added to the shared value, theta = before + sum over ranks of (theta_rank - before); the
+    AsyncAdagrad accumulators (sums of squared gradients) add up the same way.  `before` holds the values all ranks
+    agreed on at the last exchange."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return
+    for t, b in zip(tensors, before):
+        delta = t - b
+        dist.all_reduce(delta, op=dist.ReduceOp.SUM, group=group)
+        t.copy_(b + delta)
+
+
 # ---------------------------------------------------------------------------------------------------
 # A whole epoch on several GPUs: every bucket once, no partition in two places, hand-offs beside training
 # ---------------------------------------------------------------------------------------------------

@@ -3,8 +3,9 @@ step reads, with the same key names and meanings.  `from_reference` accepts the 
 ConfigSchema object (duck-typed) so that a stock config file drives this path unchanged.
 
 Keys with no device code are refused where the trainer is built (NotImplementedError), never
-silently ignored: bias, half_precision, featurized entities,
-all_negs relations, per-entity dimensions."""
+silently ignored: bias, half_precision, featurized entities, per-entity dimensions.  Relations with
+all_negs=True are ranked by the evaluator against every entity of a side (B200RankingEvaluator); the
+trainer refuses them, as the reference's GPU trainer has no use for them either."""
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -91,8 +92,6 @@ class ConfigSchema:
             bad.append("featurized entities")
         if any(e.dimension not in (None, self.dimension) for e in self.entities.values()):
             bad.append("per-entity dimensions")
-        if any(r.all_negs for r in self.relations):
-            bad.append("all_negs relations")
         if len({r.operator for r in self.relations}) > 1:
             bad.append("different operators on different relations")
         if bad:

@@ -211,6 +211,8 @@ class B200Trainer(AbstractBatchProcessor):
         per-edge weights parallel to the edge arrays (EdgeList.weight), moved to the device here."""
         if not batches:
             return []
+        if any(model.relations[0 if model.num_dynamic_rels > 0 else b[2]].all_negs for b in batches):
+            raise NotImplementedError("relations with all_negs=True are not trained by torchbiggraph_b200 (the evaluator ranks them)")
         nat = self._context(model, max(b[1] for b in batches))
         relation_idx = 0 if model.num_dynamic_rels > 0 else batches[0][2]
         wl, wr = model.tables_for(relation_idx)
@@ -348,8 +350,16 @@ class B200RankingEvaluator(AbstractBatchProcessor):
         if batch_edges.has_weight():                 # the evaluator's loss is weighted like the trainer's (eval.py:55-56)
             wgt = torch.as_tensor(batch_edges.weight).to(device=dev, dtype=torch.float32).contiguous()
             check(nat.lib.pbg_set_edge_weights(nat.ctx, _ptr(wgt)), nat.ctx)
-        check(nat.lib.pbg_eval_batch(nat.ctx, C.byref(bucket), _ptr(lhs), _ptr(rhs), _ptr(rel), n, r, _ptr(ul), _ptr(ur),
-                                     self.seed + self._calls, C.byref(out)), nat.ctx)
+        if model.relations[0 if dyn else r].all_negs:
+            # every entity of a side's table is a negative (model.py:582-617): ranks among the whole partition
+            st = nat.lib.pbg_eval_batch_all_negs(nat.ctx, C.byref(bucket), _ptr(lhs), _ptr(rhs), _ptr(rel), n, r,
+                                                 self.seed + self._calls, C.byref(out))
+            if st == _lib.PBG_ERR_UNSUPPORTED:
+                raise NotImplementedError(nat.lib.pbg_last_error(nat.ctx).decode())
+            check(st, nat.ctx)
+        else:
+            check(nat.lib.pbg_eval_batch(nat.ctx, C.byref(bucket), _ptr(lhs), _ptr(rhs), _ptr(rel), n, r, _ptr(ul), _ptr(ur),
+                                         self.seed + self._calls, C.byref(out)), nat.ctx)
         return Stats(loss=float(out.loss), pos_rank=out.pos_rank, mrr=out.mrr, r1=out.r1, r10=out.r10, r50=out.r50,
                      auc=out.auc, count=int(out.count))
 

@@ -122,8 +122,7 @@ def _cfg(**kw):
 
 
 @pytest.mark.parametrize("kw", [dict(bias=True), dict(regularization_coef=1e-3, regularizer="L2"),
-                                dict(half_precision=True), dict(entities={"e": T.EntitySchema(featurized=True)}),
-                                dict(relations=[T.RelationSchema("r", "e", "e", all_negs=True)])])
+                                dict(half_precision=True), dict(entities={"e": T.EntitySchema(featurized=True)})])
 def test_unsupported_config_keys_raise(kw):
     with pytest.raises(NotImplementedError):
         _cfg(**kw).check_supported()

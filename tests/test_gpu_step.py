@@ -479,3 +479,22 @@ def test_unsupported_plugins_raise():
                          dimension=16, dynamic_relations=True, num_dynamic_rels=3)
     with pytest.raises(NotImplementedError):
         T.make_model(cfg, "cuda")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+@pytest.mark.parametrize("precision", ["tf32x3", "bf16x6"])
+def test_one_process_drives_contexts_on_two_devices(precision):
+    """The opt-in to large dynamic shared memory belongs to the (kernel, device) pair: a process that creates a
+    context on a second GPU must get it there too.  One fixture step on device 0, then the same on device 1,
+    each against the reference's result; no peer access is used."""
+    from b200_util import Rig
+    name = "c3_none_dot_softmax"
+    c, z = load_step(name)
+    for dev in ("cuda:0", "cuda:1"):
+        with torch.cuda.device(dev):
+            rig = Rig.from_fixture(c, z, precision=precision, device=dev)
+            lhs, rhs, rel, ul, ur = batch_of(c, z, 0)
+            st = rig.trainer.process_one_batch(rig.model, rig.edges(lhs, rhs, rel), ul, ur)
+            assert st.metrics["loss"] == pytest.approx(float(z["loss_0"]), rel=RTOL, abs=1e-3), dev
+            _close(rig.W_lhs.cpu().numpy(), z["W_lhs_after_0"], what=f"W_lhs on {dev}")
+            _close(rig.G("lhs"), z["G_lhs_after_0"], atol=1e-7, what=f"G_lhs on {dev}")
