@@ -50,6 +50,9 @@ struct pbg_context {
   long long *etab_dev = nullptr;      // per-relation tables of a sub_bucket call + its counts
   long long etab_cap = 0;
   char *allnegs_mem = nullptr;        // scratch of pbg_eval_batch_all_negs, allocated at its first call
+  SortPlan csort = {{nullptr, nullptr}, {nullptr, nullptr}, nullptr, 0, 0};   // call-wide sort of all waves' slots
+  char *csort_mem = nullptr;
+  bool wave_sort_only = false;        // PBG_CALL_SORT=0: sort wave by wave (for comparisons)
   // optional event timing per kernel class
   const float *edge_w = nullptr;   // per-edge weights for the next train / eval call (pbg_set_edge_weights)
   bool profiling = false;
@@ -206,6 +209,8 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
                !(env && env[0] == '0');
     const char *envh = getenv("PBG_HALVES");
     c->fused_halves = envh && envh[0] == '1';
+    const char *envs = getenv("PBG_CALL_SORT");
+    c->wave_sort_only = envs && envs[0] == '0';
   }
   if (planes) {
     oXB[0] = take(nN * npl * Dpb * 2); oXB[1] = take(nN * npl * Dpb * 2);
@@ -321,6 +326,7 @@ extern "C" int pbg_destroy(pbg_context *c) {
   for (int i = 0; i < 2; ++i) if (c->uni_dev[i]) cudaFree(c->uni_dev[i]);
   if (c->esort_mem) cudaFree(c->esort_mem);
   if (c->allnegs_mem) cudaFree(c->allnegs_mem);
+  if (c->csort_mem) cudaFree(c->csort_mem);
   if (c->etab_dev) cudaFree(c->etab_dev);
   for (int s = 0; s < 2; ++s) {
     if (c->ev_sorted[s]) cudaEventDestroy(c->ev_sorted[s]);
@@ -355,6 +361,23 @@ extern "C" int pbg_neg_columns(const pbg_context *c, int32_t count, int32_t *chu
   if (chunks) *chunks = P > 0 ? (count + P - 1) / P : 0;
   if (lhs_neg_cols) *lhs_neg_cols = c->cfg.disable_lhs_negs ? 0 : cols;
   if (rhs_neg_cols) *rhs_neg_cols = c->cfg.disable_rhs_negs ? 0 : cols;
+  return PBG_OK;
+}
+
+#define PBG_CALL_SORT_MAX (1ll << 23)     // most slots one call-wide sort takes (its counters and buffers are ~60 bytes per slot)
+
+static int ensure_call_sort(pbg_context *c, long long n) {
+  if (n <= c->csort.max_n) return PBG_OK;
+  if (c->csort_mem) { cudaFree(c->csort_mem); c->csort_mem = nullptr; c->csort.max_n = 0; }
+  const long long cap = n + n / 8 + 1024;
+  const size_t kb = align_up((size_t)cap * 8, 256), vb = align_up((size_t)cap * 4, 256);
+  const size_t hb = align_up(pbg_sort_hist_entries((int)cap) * 4, 256);
+  CU(c, cudaMalloc(&c->csort_mem, 2 * kb + 2 * vb + hb));
+  char *p = c->csort_mem;
+  c->csort.keys[0] = (unsigned long long *)p; c->csort.keys[1] = (unsigned long long *)(p + kb);
+  c->csort.vals[0] = (unsigned int *)(p + 2 * kb); c->csort.vals[1] = (unsigned int *)(p + 2 * kb + vb);
+  c->csort.hist = (unsigned int *)(p + 2 * kb + 2 * vb);
+  c->csort.max_n = (int)cap;
   return PBG_OK;
 }
 
@@ -512,10 +535,12 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
   // the same launches and joins for a quarter of the work.
   const int nwaves = (num_batches + c->kmax - 1) / c->kmax;
   const int kbase = num_batches / nwaves, kextra = num_batches % nwaves;
-  int wave = 0;
-  for (int b0 = 0; b0 < num_batches; ++wave) {
-    const int kk = kbase + (wave < kextra ? 1 : 0);
-    WaveBatches wb;
+  std::vector<WaveBatches> wbs((size_t)nwaves);
+  std::vector<int> kks((size_t)nwaves);
+  std::vector<long long> slot0((size_t)nwaves + 1, 0);
+  for (int wv = 0, b0 = 0; wv < nwaves; ++wv) {
+    const int kk = kbase + (wv < kextra ? 1 : 0);
+    WaveBatches &wb = wbs[wv];
     memset(&wb, 0, sizeof wb);
     for (int i = 0; i < kk; ++i) {
       const pbg_batch &b = batches[b0 + i];
@@ -524,9 +549,41 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
       int wi = d.dynamic ? 0 : b.rel;
       wb.wrel[i] = bk->relation_weights ? bk->relation_weights[wi] : 1.0f;
     }
+    kks[wv] = kk;
+    slot0[wv + 1] = slot0[wv] + (long long)kk * d.spb;
+    b0 += kk;
+  }
+  // One sort for the whole call where it pays: the slots of all waves, keyed by (wave, row), in a single radix
+  // sort of a few passes -- instead of a dozen launches of a few microseconds per wave, which on small dimensions
+  // (a wave of 56,000 slots of 100 floats) are the critical path of the step.  The sorted list is the per-wave
+  // lists one after the other; the wave tags are masked off again.  Calls of a single wave, and calls beyond
+  // PBG_CALL_SORT_MAX slots (the counters of a radix pass grow with the list), sort wave by wave as before.
+  const int wave_bits = bit_length((unsigned long long)(nwaves - 1));
+  const bool call_sort = nwaves > 1 && slot0[nwaves] <= PBG_CALL_SORT_MAX && bits + wave_bits <= 44 && !c->wave_sort_only;
+  SortPlan *csp = nullptr;
+  if (call_sort) {
+    int rcs = ensure_call_sort(c, slot0[nwaves]);
+    if (rcs) return rcs;
+    csp = &c->csort;
+    ClassTimer t(c, 0, c->side);
+    int n = 0;
+    for (int wv = 0; wv < nwaves; ++wv) {
+      WaveDims dw = d;
+      dw.k = kks[wv]; dw.nblk = kks[wv] * d.Cm; dw.nocc = kks[wv] * d.spb; dw.blk0 = 0;
+      n += launch_build_keys(dw, wbs[wv], w, csp->keys[0] + slot0[wv], csp->vals[0] + slot0[wv], c->side, (unsigned long long)wv << bits);
+    }
+    n += pbg_sort(*csp, (int)slot0[nwaves], bits + wave_bits, c->side);
+    n += launch_mask_keys(csp->keys[csp->result], slot0[nwaves], (1ull << bits) - 1ull, c->side);
+    t.done(n);
+    CU(c, cudaEventRecord(c->ev_sorted[0], c->side));
+  }
+  int wave = 0;
+  for (int b0 = 0; b0 < num_batches; ++wave) {
+    const int kk = kks[wave];
+    const WaveBatches &wb = wbs[wave];
     d.k = kk; d.nblk = kk * d.Cm; d.nocc = kk * d.spb;
     SortPlan &sp = c->sort[wave & 1];
-    {
+    if (!call_sort) {
       if (wave >= 2) CU(c, cudaStreamWaitEvent(c->side, c->ev_updated[wave & 1], 0));   // buffers free again
       ClassTimer t(c, 0, c->side);
       int n = launch_build_keys(d, wb, w, sp.keys[0], sp.vals[0], c->side);
@@ -571,11 +628,12 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
       { ClassTimer t(c, 6, c->part2); t.done(launch_stats(d, wb, w, stats_out ? c->stats_dev : nullptr, c->sum_dev, c->part2)); }
       CU(c, cudaEventRecord(c->ev_stats, c->part2));
     }
-    CU(c, cudaStreamWaitEvent(c->stream, c->ev_sorted[wave & 1], 0));
+    CU(c, cudaStreamWaitEvent(c->stream, c->ev_sorted[call_sort ? 0 : (wave & 1)], 0));
     {
       ClassTimer t(c, 5);
-      t.done(launch_update(d, wb, w, sp.keys[sp.result], sp.vals[sp.result],
-                           c->cfg.lr, c->cfg.relation_lr, c->psum, c->hublist, c->hubcnt, c->stream));
+      const unsigned long long *wkeys = call_sort ? csp->keys[csp->result] + slot0[wave] : sp.keys[sp.result];
+      const unsigned int *wvals = call_sort ? csp->vals[csp->result] + slot0[wave] : sp.vals[sp.result];
+      t.done(launch_update(d, wb, w, wkeys, wvals, c->cfg.lr, c->cfg.relation_lr, c->psum, c->hublist, c->hubcnt, c->stream));
     }
     CU(c, cudaEventRecord(c->ev_updated[wave & 1], c->stream));
     if (stats_aside) CU(c, cudaStreamWaitEvent(c->stream, c->ev_stats, 0));   // the next wave rewrites the loss rows

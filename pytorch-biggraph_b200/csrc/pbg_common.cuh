@@ -317,7 +317,8 @@ size_t pbg_sort_hist_entries(int n);   // digit counters (unsigned int) a sort o
 int pbg_sort(SortPlan &sp, int n, int bits, cudaStream_t st);
 
 int launch_build_keys(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
-                      unsigned long long *keys, unsigned int *vals, cudaStream_t st);
+                      unsigned long long *keys, unsigned int *vals, cudaStream_t st, unsigned long long tag = 0ull);
+int launch_mask_keys(unsigned long long *keys, long long n, unsigned long long mask, cudaStream_t st);
 int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
 void *pbg_tc_plan_create(const WaveDims &d, const WaveBufs &w, int nblk_max, int precision);
 void pbg_tc_plan_destroy(void *plan);

@@ -479,8 +479,9 @@ int launch_gather(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, c
 //   rhs-table rows            key = row (+ lhs rows when the tables differ)
 //   operator-table rows       key = key_rel_base + table * num_rels + rel   (dynamic relations)
 //   slots without gradient    key = key_invalid (sorts to the end)
+// `tag` is OR-ed into every key (the wave's number above the key bits when a whole call is sorted at once).
 __global__ void build_keys_kernel(WaveDims d, WaveBatches wb, WaveBufs w, unsigned long long *keys,
-                                  unsigned int *vals) {
+                                  unsigned int *vals, unsigned long long tag) {
   int o = blockIdx.x * blockDim.x + threadIdx.x;
   if (o >= d.nocc) return;
   Occ q = occ_decode(d, o);
@@ -505,14 +506,24 @@ __global__ void build_keys_kernel(WaveDims d, WaveBatches wb, WaveBufs w, unsign
       if (rl >= 0 && rl < d.num_rels) key = d.key_rel_base + (unsigned long long)t * d.num_rels + (unsigned long long)rl;
     }
   }
-  keys[o] = key;
+  keys[o] = key | tag;
   vals[o] = (unsigned int)o;
 }
 
 int launch_build_keys(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
-                      unsigned long long *keys, unsigned int *vals, cudaStream_t st) {
-  build_keys_kernel<<<(d.nocc + 255) / 256, 256, 0, st>>>(d, wb, w, keys, vals);
+                      unsigned long long *keys, unsigned int *vals, cudaStream_t st, unsigned long long tag) {
+  build_keys_kernel<<<(d.nocc + 255) / 256, 256, 0, st>>>(d, wb, w, keys, vals, tag);
   return 1;
+}
+
+// keys[i] &= mask: drops the wave tags once the call-wide sort has grouped the slots by wave
+__global__ void mask_keys_kernel(unsigned long long *keys, long long n, unsigned long long mask) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) keys[i] &= mask;
+}
+int launch_mask_keys(unsigned long long *keys, long long n, unsigned long long mask, cudaStream_t st) {
+  if (n > 0) mask_keys_kernel<<<(int)((n + 255) / 256), 256, 0, st>>>(keys, n, mask);
+  return n > 0;
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -92,8 +92,6 @@ class ConfigSchema:
             bad.append("featurized entities")
         if any(e.dimension not in (None, self.dimension) for e in self.entities.values()):
             bad.append("per-entity dimensions")
-        if len({r.operator for r in self.relations}) > 1:
-            bad.append("different operators on different relations")
         if bad:
             raise NotImplementedError(
                 "torchbiggraph_b200 has no device code for: " + ", ".join(bad) + " (and no CPU fallback)")

@@ -41,37 +41,52 @@ class MultiRelationEmbedder:
         self.comparator = COMPARATORS.get_class(config.comparator)()
         if self.comparator.native_code is None:
             raise NotImplementedError(f"comparator '{config.comparator}' has no device code")
-        op_name = config.relations[0].operator
-        if config.dynamic_relations and op_name in ("linear", "affine"):
-            raise NotImplementedError(f"operator '{op_name}' with dynamic relations has no device code (and no CPU fallback)")
-        self.operator_name = op_name
         D = config.dimension
-        rows = self.num_dynamic_rels if config.dynamic_relations else len(config.relations)
-        self.num_rels = rows
-        registry = DYNAMIC_OPERATORS if config.dynamic_relations else OPERATORS
-        op_cls = registry.get_class(op_name)
-        if op_cls.native_code is None:
-            raise NotImplementedError(f"operator '{op_name}' has no device code")
-        proto = op_cls(D, rows) if config.dynamic_relations else op_cls(D)
-        init = proto.init_table(rows)
-        # one [num_rels, width] table per side (width = dim; dim*dim (+dim) for linear (affine));
-        # standard relations only have the rhs one
-        self.rhs_op_table: Optional[torch.Tensor] = None if init is None else init.to(self.device)
-        self.lhs_op_table: Optional[torch.Tensor] = (
-            None if init is None or not config.dynamic_relations else init.clone().to(self.device))
+        dyn = config.dynamic_relations
+        registry = DYNAMIC_OPERATORS if dyn else OPERATORS
+        # Relations are grouped by operator (standard relations may mix them, model.py:368-476 builds one operator
+        # per relation): each group has its own [relations of the group, width] parameter table (width = dim;
+        # dim * dim (+ dim) for linear (affine)), and a batch is trained by the library context of its group.
+        # With dynamic relations there is one group and a second table for the lhs-side operators.
+        self.op_groups: Dict[str, List[int]] = {}
+        for i, r in enumerate(config.relations):
+            self.op_groups.setdefault(r.operator, []).append(i)
+        self.group_of: List[tuple] = [(r.operator, self.op_groups[r.operator].index(i)) for i, r in enumerate(config.relations)]
+        self.op_tables: Dict[str, Optional[torch.Tensor]] = {}
+        self.lhs_op_tables: Dict[str, Optional[torch.Tensor]] = {}
+        protos = {}
+        for op_name, members in self.op_groups.items():
+            if dyn and op_name in ("linear", "affine"):
+                raise NotImplementedError(f"operator '{op_name}' with dynamic relations has no device code (and no CPU fallback)")
+            op_cls = registry.get_class(op_name)
+            if op_cls.native_code is None:
+                raise NotImplementedError(f"operator '{op_name}' has no device code")
+            rows = self.num_dynamic_rels if dyn else len(members)
+            proto = op_cls(D, rows) if dyn else op_cls(D)
+            init = proto.init_table(rows)
+            protos[op_name] = (op_cls, rows, init)
+            self.op_tables[op_name] = None if init is None else init.to(self.device)
+            self.lhs_op_tables[op_name] = None if init is None or not dyn else init.clone().to(self.device)
+        # the single-operator case keeps its plain attributes
+        self.operator_name = config.relations[0].operator
+        self.num_rels = self.num_dynamic_rels if dyn else len(self.op_groups[self.operator_name])
+        self.rhs_op_table: Optional[torch.Tensor] = self.op_tables[self.operator_name] if len(self.op_groups) == 1 else None
+        self.lhs_op_table: Optional[torch.Tensor] = self.lhs_op_tables[self.operator_name] if len(self.op_groups) == 1 else None
         self.lhs_operators: List[Optional[object]] = []
         self.rhs_operators: List[Optional[object]] = []
-        for i, _ in enumerate(config.relations):
+        for i, rel in enumerate(config.relations):
+            op_cls, rows, init = protos[rel.operator]
             if init is None:
                 self.lhs_operators.append(None)
                 self.rhs_operators.append(None)
                 continue
-            r = op_cls(D, rows) if config.dynamic_relations else op_cls(D)
-            r.table = self.rhs_op_table if config.dynamic_relations else self.rhs_op_table[i:i + 1]
+            local = self.group_of[i][1]
+            r = op_cls(D, rows) if dyn else op_cls(D)
+            r.table = self.op_tables[rel.operator] if dyn else self.op_tables[rel.operator][local:local + 1]
             self.rhs_operators.append(r)
-            if config.dynamic_relations:
+            if dyn:
                 l = op_cls(D, rows)
-                l.table = self.lhs_op_table
+                l.table = self.lhs_op_tables[rel.operator]
                 self.lhs_operators.append(l)
             else:
                 self.lhs_operators.append(None)
@@ -87,7 +102,15 @@ class MultiRelationEmbedder:
     # ---- parameters other than embeddings: what model_optimizer steps (train_cpu.py:468) ----
     def parameters(self):
         glob = [] if self.global_embs is None else list(self.global_embs.values())
-        return [t for t in (self.rhs_op_table, self.lhs_op_table) if t is not None] + glob
+        tabs = [t for t in self.op_tables.values() if t is not None] + [t for t in self.lhs_op_tables.values() if t is not None]
+        return tabs + glob
+
+    def operator_of(self, relation_idx: int) -> str:
+        return self.relations[relation_idx].operator
+
+    def op_table_for(self, op_name: str):
+        """(rhs-side table, lhs-side table) of an operator group."""
+        return self.op_tables[op_name], self.lhs_op_tables[op_name]
 
     def globals_for(self, relation_idx: int):
         """(lhs, rhs) global embedding of the relation's entity types, or (None, None)."""
@@ -115,11 +138,15 @@ class MultiRelationEmbedder:
         """Scores of one batch (model.py:624-762) computed by the library's forward kernels.
         uniform_lhs / uniform_rhs: optional int64 [chunks, num_uniform_negs] row ids."""
         from .trainer import _Native
+        op_name = self.operator_name if self.num_dynamic_rels > 0 or not edges.has_scalar_relation_type() \
+            else self.operator_of(edges.get_relation_type_as_scalar())
         if self._scorer is None:
-            self._scorer = _Native(self, max_batch=max(self.config.batch_size, len(edges)), k=1,
-                                   precision=self.config.precision, lr=self.config.lr,
-                                   relation_lr=self.config.relation_lr, margin=self.config.margin)
-        return self._scorer.score(self, edges, uniform_lhs, uniform_rhs, seed)
+            self._scorer = {}
+        if op_name not in self._scorer or self._scorer[op_name].max_batch < len(edges):
+            self._scorer[op_name] = _Native(self, max_batch=max(self.config.batch_size, len(edges)), k=1,
+                                            precision=self.config.precision, lr=self.config.lr,
+                                            relation_lr=self.config.relation_lr, margin=self.config.margin, op_name=op_name)
+        return self._scorer[op_name].score(self, edges, uniform_lhs, uniform_rhs, seed)
 
     __call__ = forward
 

@@ -28,18 +28,20 @@ class _Native:
 
     def __init__(self, model: MultiRelationEmbedder, max_batch: int, k: int, precision: str, lr: float,
                  relation_lr: Optional[float], margin: float, loss_code: Optional[int] = None,
-                 num_batch_negs: Optional[int] = None, num_uniform_negs: Optional[int] = None):
+                 num_batch_negs: Optional[int] = None, num_uniform_negs: Optional[int] = None,
+                 op_name: Optional[str] = None):
         cfg = model.config
+        self.op_name = model.operator_name if op_name is None else op_name
         if model.device.type != "cuda":
             raise RuntimeError("torchbiggraph_b200 runs on a CUDA device only (no CPU fallback)")
         self.lib = _lib.lib()
         c = PbgConfig()
         c.dim = cfg.dimension
-        c.op = _lib.OPERATOR_CODES[model.operator_name]
+        c.op = _lib.OPERATOR_CODES[self.op_name]
         c.comparator = model.comparator.native_code
         c.loss = _lib.LOSS_CODES[cfg.loss_fn] if loss_code is None else loss_code
         c.dynamic_relations = int(cfg.dynamic_relations)
-        c.num_rels = model.num_rels
+        c.num_rels = model.num_dynamic_rels if cfg.dynamic_relations else len(model.op_groups[self.op_name])
         c.num_batch_negs = cfg.num_batch_negs if num_batch_negs is None else num_batch_negs
         c.num_uniform_negs = cfg.num_uniform_negs if num_uniform_negs is None else num_uniform_negs
         c.disable_lhs_negs = int(cfg.disable_lhs_negs)
@@ -84,8 +86,9 @@ class _Native:
             b.lhs_state, b.rhs_state = gl.data_ptr(), gr.data_ptr()
             b.rhs_op_state = None if ar is None else ar.data_ptr()
             b.lhs_op_state = None if al is None else al.data_ptr()
-        b.rhs_op = None if model.rhs_op_table is None else model.rhs_op_table.data_ptr()
-        b.lhs_op = None if model.lhs_op_table is None else model.lhs_op_table.data_ptr()
+        rhs_tab, lhs_tab = model.op_table_for(self.op_name)
+        b.rhs_op = None if rhs_tab is None else rhs_tab.data_ptr()
+        b.lhs_op = None if lhs_tab is None else lhs_tab.data_ptr()
         b.relation_weights = weights_arr
         gl_, gr_ = model.globals_for(relation_idx)
         if gl_ is not None:
@@ -106,6 +109,7 @@ class _Native:
             raise TypeError("All positive pairs must come from the same relation")
         rel = edges.rel.to(dev).contiguous() if dyn else None
         relidx = 0 if dyn else edges.get_relation_type_as_scalar()
+        local = 0 if dyn else model.group_of[relidx][1]
         P, Cn, lc, rc = (C.c_int32() for _ in range(4))
         check(self.lib.pbg_neg_columns(self.ctx, n, C.byref(P), C.byref(Cn), C.byref(lc), C.byref(rc)), self.ctx)
         lp = torch.empty(n, device=dev); rp = torch.empty(n, device=dev)
@@ -113,7 +117,7 @@ class _Native:
         ul = None if ul is None else self._uniform(ul, dev)
         ur = None if ur is None else self._uniform(ur, dev)
         b = self.bucket(model, relidx, None, None)
-        check(self.lib.pbg_score_batch(self.ctx, C.byref(b), _ptr(lhs), _ptr(rhs), _ptr(rel), n, relidx,
+        check(self.lib.pbg_score_batch(self.ctx, C.byref(b), _ptr(lhs), _ptr(rhs), _ptr(rel), n, local,
                                        _ptr(ul), _ptr(ur), seed, _ptr(lp), _ptr(rp), _ptr(ln), _ptr(rn)), self.ctx)
         return Scores(lp, rp, ln, rn)
 
@@ -163,7 +167,8 @@ class B200Trainer(AbstractBatchProcessor):
         self.model_optimizer = model_optimizer
         self.unpartitioned_optimizers: Dict[str, RowAdagrad] = {}
         self.partitioned_optimizers: Dict[Tuple, RowAdagrad] = {}
-        self._native: Optional[_Native] = None
+        self._native: Optional[_Native] = None          # the context used last
+        self._natives: Dict[str, _Native] = {}          # one per operator group
         self._native_key = None
         self.seed = 0
         self._calls = 0
@@ -182,24 +187,32 @@ class B200Trainer(AbstractBatchProcessor):
             return opt.lr
         raise RuntimeError("no embedding optimizer registered")
 
-    def _context(self, model: MultiRelationEmbedder, need_batch: int) -> _Native:
+    def _context(self, model: MultiRelationEmbedder, need_batch: int, op_name: Optional[str] = None) -> _Native:
+        """The library context of an operator group (one per operator the relations use)."""
         cfg = model.config
+        op_name = model.operator_name if op_name is None else op_name
         key = (id(model), cfg.batches_in_flight, cfg.precision)
-        if self._native is None or self._native_key != key or self._native.max_batch < need_batch:
+        if self._native_key != key:
+            self._natives = {}
+            self._native_key = key
+        nat = self._natives.get(op_name)
+        if nat is None or nat.max_batch < need_batch:
             margin = getattr(self.loss_fn, "margin", cfg.margin)
             rel_lr = self.model_optimizer.lr if isinstance(self.model_optimizer, AsyncAdagrad) else cfg.relation_lr
-            self._native = _Native(model, max(cfg.batch_size, need_batch), cfg.batches_in_flight, cfg.precision,
-                                   self._lr(), rel_lr, margin, loss_code=self.loss_fn.native_code)
-            self._native_key = key
-        return self._native
+            nat = _Native(model, max(cfg.batch_size, need_batch), cfg.batches_in_flight, cfg.precision,
+                          self._lr(), rel_lr, margin, loss_code=self.loss_fn.native_code, op_name=op_name)
+            self._natives[op_name] = nat
+        self._native = nat
+        return nat
 
-    def _op_states(self, model):
-        if model.rhs_op_table is None:
+    def _op_states(self, model, op_name):
+        rhs_tab, lhs_tab = model.op_table_for(op_name)
+        if rhs_tab is None:
             return None, None
         if not isinstance(self.model_optimizer, AsyncAdagrad):
             raise RuntimeError("the model has operator parameters but model_optimizer is not an AsyncAdagrad over them")
-        ar = self.model_optimizer.sum_for(model.rhs_op_table)
-        al = None if model.lhs_op_table is None else self.model_optimizer.sum_for(model.lhs_op_table)
+        ar = self.model_optimizer.sum_for(rhs_tab)
+        al = None if lhs_tab is None else self.model_optimizer.sum_for(lhs_tab)
         return al, ar
 
     def train_batches(self, model: MultiRelationEmbedder, lhs: torch.Tensor, rhs: torch.Tensor,
@@ -213,22 +226,26 @@ class B200Trainer(AbstractBatchProcessor):
             return []
         if any(model.relations[0 if model.num_dynamic_rels > 0 else b[2]].all_negs for b in batches):
             raise NotImplementedError("relations with all_negs=True are not trained by torchbiggraph_b200 (the evaluator ranks them)")
-        nat = self._context(model, max(b[1] for b in batches))
         relation_idx = 0 if model.num_dynamic_rels > 0 else batches[0][2]
+        op_name = model.operator_of(relation_idx)
+        nat = self._context(model, max(b[1] for b in batches), op_name)
         wl, wr = model.tables_for(relation_idx)
         if model.num_dynamic_rels == 0:
             for b in batches:
-                if model.tables_for(b[2])[0] is not wl or model.tables_for(b[2])[1] is not wr:
-                    raise NotImplementedError("batches of one call must read the same pair of tables")
-        al, ar = self._op_states(model)
+                if model.tables_for(b[2])[0] is not wl or model.tables_for(b[2])[1] is not wr or model.operator_of(b[2]) != op_name:
+                    raise NotImplementedError("batches of one call must read the same pair of tables through the same operator "
+                                              "(process_in_batches cuts a list into such runs)")
+        al, ar = self._op_states(model, op_name)
         states = (self._state_for(wl), self._state_for(wr), al, ar)
         gl_, gr_ = model.globals_for(relation_idx)
         if gl_ is not None:
             if not isinstance(self.model_optimizer, AsyncAdagrad):
                 raise RuntimeError("the model has global embeddings but model_optimizer is not an AsyncAdagrad over them")
             states = states + (self.model_optimizer.sum_for(gl_), self.model_optimizer.sum_for(gr_))
-        nw = len(self.relation_weights)
-        warr = (C.c_float * nw)(*self.relation_weights)
+        # the library indexes operator rows and relation weights by the relation's place in its operator group
+        dyn = model.num_dynamic_rels > 0
+        members = [0] if dyn else model.op_groups[op_name]
+        warr = (C.c_float * len(members))(*[self.relation_weights[g] for g in members])
         bucket = nat.bucket(model, relation_idx, states, warr)
         # the descriptor array of a batch list is built once (a trainer is handed the same bucket layout
         # over and over; filling a few hundred ctypes structs costs more host time than launching a wave)
@@ -237,7 +254,7 @@ class B200Trainer(AbstractBatchProcessor):
         if barr is None:
             barr = (PbgBatch * len(batches))()
             for i, (o, n, r) in enumerate(batches):
-                barr[i].offset, barr[i].count, barr[i].rel = o, n, r
+                barr[i].offset, barr[i].count, barr[i].rel = o, n, (0 if dyn else model.group_of[r][1])
             if len(self._batch_arrays) > 64:
                 self._batch_arrays.clear()
             self._batch_arrays[key] = barr
@@ -282,7 +299,7 @@ class B200Trainer(AbstractBatchProcessor):
         rhs = batch_edges.rhs.to_tensor().to(dev).contiguous()
         rel = batch_edges.rel.to(dev).contiguous() if dyn else None
         r = 0 if dyn else batch_edges.get_relation_type_as_scalar()
-        nat = self._context(model, n)
+        nat = self._context(model, n, model.operator_of(r))
         ul = None if uniform_lhs is None else nat._uniform(uniform_lhs, dev)
         ur = None if uniform_rhs is None else nat._uniform(uniform_rhs, dev)
         wgt = torch.as_tensor(batch_edges.weight) if batch_edges.has_weight() else None
@@ -310,20 +327,27 @@ class B200RankingEvaluator(AbstractBatchProcessor):
             raise NotImplementedError(f"model overrides {sorted(unknown)} are not supported by torchbiggraph_b200")
         self.neg_overrides = dict(overrides or {})
         self._native: Optional[_Native] = None
+        self._natives: Dict[str, _Native] = {}
         self._key = None
         self.seed = 0
         self._calls = 0
 
-    def _context(self, model, need_batch):
+    def _context(self, model, need_batch, op_name=None):
+        op_name = model.operator_name if op_name is None else op_name
         key = (id(model),)
-        if self._native is None or self._key != key or self._native.max_batch < need_batch:
-            cfg = model.config
-            self._native = _Native(model, max(cfg.batch_size, need_batch), 1, cfg.precision, cfg.lr, cfg.relation_lr,
-                                   getattr(self.loss_fn, "margin", cfg.margin), loss_code=self.loss_fn.native_code,
-                                   num_batch_negs=self.neg_overrides.get("num_batch_negs"),
-                                   num_uniform_negs=self.neg_overrides.get("num_uniform_negs"))
+        if self._key != key:
+            self._natives = {}
             self._key = key
-        return self._native
+        nat = self._natives.get(op_name)
+        if nat is None or nat.max_batch < need_batch:
+            cfg = model.config
+            nat = _Native(model, max(cfg.batch_size, need_batch), 1, cfg.precision, cfg.lr, cfg.relation_lr,
+                          getattr(self.loss_fn, "margin", cfg.margin), loss_code=self.loss_fn.native_code,
+                          num_batch_negs=self.neg_overrides.get("num_batch_negs"),
+                          num_uniform_negs=self.neg_overrides.get("num_uniform_negs"), op_name=op_name)
+            self._natives[op_name] = nat
+        self._native = nat
+        return nat
 
     def _process_one_batch(self, model: MultiRelationEmbedder, batch_edges: EdgeList, uniform_lhs=None, uniform_rhs=None) -> Stats:
         dyn = model.num_dynamic_rels > 0
@@ -335,22 +359,24 @@ class B200RankingEvaluator(AbstractBatchProcessor):
         if n == 0:
             return Stats(loss=0.0, pos_rank=0.0, mrr=0.0, r1=0.0, r10=0.0, r50=0.0, auc=0.0, count=0)
         dev = model.device
-        nat = self._context(model, n)
+        r = 0 if dyn else batch_edges.get_relation_type_as_scalar()
+        op_name = model.operator_of(r)
+        nat = self._context(model, n, op_name)
         lhs = batch_edges.lhs.to_tensor().to(dev).contiguous()
         rhs = batch_edges.rhs.to_tensor().to(dev).contiguous()
         rel = batch_edges.rel.to(dev).contiguous() if dyn else None
-        r = 0 if dyn else batch_edges.get_relation_type_as_scalar()
         ul = None if uniform_lhs is None else nat._uniform(uniform_lhs, dev)
         ur = None if uniform_rhs is None else nat._uniform(uniform_rhs, dev)
-        nw = len(self.relation_weights)
-        warr = (C.c_float * nw)(*self.relation_weights)
+        members = [0] if dyn else model.op_groups[op_name]
+        warr = (C.c_float * len(members))(*[self.relation_weights[g] for g in members])
         bucket = nat.bucket(model, r, None, warr)
+        full_r, r = r, (0 if dyn else model.group_of[r][1])     # the library's relation index is local to the operator group
         out = _lib.PbgEvalStats()
         self._calls += 1
         if batch_edges.has_weight():                 # the evaluator's loss is weighted like the trainer's (eval.py:55-56)
             wgt = torch.as_tensor(batch_edges.weight).to(device=dev, dtype=torch.float32).contiguous()
             check(nat.lib.pbg_set_edge_weights(nat.ctx, _ptr(wgt)), nat.ctx)
-        if model.relations[0 if dyn else r].all_negs:
+        if model.relations[0 if dyn else full_r].all_negs:
             # every entity of a side's table is a negative (model.py:582-617): ranks among the whole partition
             st = nat.lib.pbg_eval_batch_all_negs(nat.ctx, C.byref(bucket), _ptr(lhs), _ptr(rhs), _ptr(rel), n, r,
                                                  self.seed + self._calls, C.byref(out))
@@ -422,13 +448,13 @@ def process_in_batches(batch_size: int, model: MultiRelationEmbedder, batch_proc
 
 def _runs_by_table_pair(model: MultiRelationEmbedder, batches):
     """Cuts a batch list into maximal runs of consecutive batches whose relations read the same
-    (lhs table, rhs table) pair; one library call trains one run."""
+    (lhs table, rhs table) pair through the same operator; one library call trains one run."""
     if model.num_dynamic_rels > 0 or not batches:
         return [batches] if batches else []
     runs, cur, cur_key = [], [], None
     for b in batches:
         wl, wr = model.tables_for(b[2])
-        key = (wl.data_ptr(), wr.data_ptr())
+        key = (wl.data_ptr(), wr.data_ptr(), model.operator_of(b[2]))
         if cur and key != cur_key:
             runs.append(cur)
             cur = []

@@ -194,8 +194,13 @@ def test_batch_list_is_cut_into_runs_that_read_one_pair_of_tables():
         num_dynamic_rels = 0
         tabs = {0: (torch.zeros(2, 4), torch.zeros(2, 4))}
 
+        ops = {0: "none", 1: "none", 2: "none"}
+
         def tables_for(self, r):
             return self.tabs[r]
+
+        def operator_of(self, r):
+            return self.ops[r]
 
     m = FakeModel()
     m.tabs[1] = (m.tabs[0][0], torch.zeros(3, 4))      # relation 1 reads another rhs table
@@ -204,6 +209,8 @@ def test_batch_list_is_cut_into_runs_that_read_one_pair_of_tables():
     runs = _runs_by_table_pair(m, batches)
     assert runs == [[(0, 5, 0), (5, 5, 2)], [(10, 5, 1), (15, 5, 1)], [(20, 5, 0)]]
     assert _runs_by_table_pair(m, []) == []
+    m.ops = {0: "none", 1: "none", 2: "translation"}          # a relation with another operator starts a run of its own
+    assert _runs_by_table_pair(m, batches) == [[(0, 5, 0)], [(5, 5, 2)], [(10, 5, 1), (15, 5, 1)], [(20, 5, 0)]]
     m.num_dynamic_rels = 3
     assert _runs_by_table_pair(m, batches) == [batches]
 

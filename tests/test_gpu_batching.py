@@ -85,3 +85,61 @@ def test_process_in_batches_equals_batch_by_batch(two_types):
     torch.manual_seed(123)
     plain = T.process_in_batches(100, model_c, tr_c, T.EdgeList(ent(lhs), ent(rhs), t(rel) if two_types else t(0)))
     assert total.metrics["loss"] > 1.5 * plain.metrics["loss"]
+
+
+def test_relations_with_different_operators_train_like_the_oracle():
+    """Standard relations may each have their own operator (torchbiggraph/model.py:368-476 builds one per relation).
+    Three relations -- translation, complex_diagonal, none -- over one entity type: process_in_batches cuts the
+    batch list where the operator changes and trains every run through the library context of its operator; the
+    result is held to the CPU oracle run batch by batch in the same order."""
+    import torchbiggraph_b200 as T
+    from oracle import pbg_step as O
+    from torchbiggraph_b200.trainer import _batches_group_by_relation
+    rng = np.random.default_rng(21)
+    D, N, n = 16, 300, 640
+    ops = ["translation", "complex_diagonal", "none", "translation"]
+    weights = [1.0, 0.5, 2.0, 1.5]
+    cfg = T.ConfigSchema(entities={"e": T.EntitySchema()},
+                         relations=[T.RelationSchema(f"r{i}", "e", "e", operator=o, weight=w) for i, (o, w) in enumerate(zip(ops, weights))],
+                         dimension=D, comparator="dot", loss_fn="ranking", margin=0.1, lr=0.1, relation_lr=0.05, batch_size=100,
+                         num_batch_negs=50, num_uniform_negs=0)
+    model = T.make_model(cfg, "cuda")
+    assert model.rhs_op_table is None and set(model.op_groups) == {"translation", "complex_diagonal", "none"}
+    W0 = (rng.standard_normal((N, D)) * 0.2).astype(np.float32)
+    th = {o: (O.operator_init(o, D, len(m), np.float32) + rng.standard_normal((len(m), D)).astype(np.float32) * 0.2)
+          for o, m in model.op_groups.items() if o != "none"}
+    for o, t in th.items():
+        model.op_tables[o].copy_(torch.tensor(t).cuda())
+    tr = T.B200Trainer(T.make_optimizer(cfg, model.parameters(), False), T.LOSS_FUNCTIONS.get_class("ranking")(margin=0.1), weights)
+    W = torch.tensor(W0).cuda()
+    model.set_embeddings("e", T.Side.LHS, W)
+    model.set_embeddings("e", T.Side.RHS, W)
+    tr.partitioned_optimizers["e", 0] = T.make_optimizer(cfg, [W], True)
+    lhs, rhs, rel = rng.integers(0, N, n), rng.integers(0, N, n), rng.integers(0, len(ops), n)
+    t = lambda a: torch.tensor(np.asarray(a))
+    torch.manual_seed(77)
+    total = T.process_in_batches(100, model, tr, T.EdgeList(T.EntityList.from_tensor(t(lhs)), T.EntityList.from_tensor(t(rhs)), t(rel)))
+    # the oracle, relation by relation state, same batches in the same order
+    Wo, Go = W0.astype(np.float64), np.zeros(N)
+    states = {}
+    for o, m in model.op_groups.items():
+        st = O.BucketState(Wo, Go, Wo, Go)
+        if o != "none":
+            st.theta_rhs, st.acc_rhs = th[o].astype(np.float64), np.zeros_like(th[o], np.float64)
+        states[o] = st
+    order = np.argsort(rel, kind="stable")
+    torch.manual_seed(77)
+    want = 0.0
+    for off, cnt, r in _batches_group_by_relation(t(rel[order]), 100):
+        idx = order[off:off + cnt]
+        o, local = model.group_of[r]
+        ocfg = O.StepConfig(dim=D, operator=o, comparator="dot", loss="ranking", margin=0.1, lr=0.1, relation_lr=0.05,
+                            num_batch_negs=50, num_uniform_negs=0, num_rels=len(model.op_groups[o]),
+                            relation_weights=[weights[g] for g in model.op_groups[o]])
+        chunks = -(-cnt // min(50, cnt))
+        want += O.train_batch(ocfg, states[o], lhs[idx], rhs[idx], local, np.zeros((chunks, 0), np.int64), np.zeros((chunks, 0), np.int64))["loss"]
+    assert total.count == n
+    assert total.metrics["loss"] == pytest.approx(want, rel=RTOL)
+    np.testing.assert_allclose(W.cpu().numpy(), Wo, rtol=RTOL, atol=2e-6)
+    for o in th:
+        np.testing.assert_allclose(model.op_tables[o].cpu().numpy(), states[o].theta_rhs, rtol=RTOL, atol=2e-6, err_msg=o)

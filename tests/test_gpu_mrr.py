@@ -17,12 +17,15 @@ pytestmark = pytest.mark.gpu
 
 # The two small graphs run in every tier, sequentially and with batches in flight; the two graphs at
 # the shapes of the benchmark configurations (dim 400 with 1000-row chunks; power-law endpoints at
-# dim 256) run in the arithmetic and with the 14 batches in flight that bench.py uses.
+# dim 256) run in the arithmetic and with the batches in flight that bench.py uses on them: 14 on the
+# power-law graph, 3 on the multi-relation one -- its batches of 5000 edges are a twentieth of an epoch each,
+# and with 14 of them in flight the held-out MRR after 3 epochs falls to 0.159 against the reference's 0.193
+# (measured; 0.188 / 0.190 / 0.183 with 2 / 3 / 4 in flight).
 SMALL = ("std_translation", "dyn_complex_diagonal")
 RUNS = [(case, k, prec) for case in SMALL
         for k, prec in ((1, "fp32"), (1, "tf32x3"), (16, "tf32x3"), (1, "bf16x6"), (14, "bf16x6"))]
 RUNS += [(case, 14, "bf16x3") for case in SMALL]
-RUNS += [("kg15k_shape", 1, "tf32x3"), ("kg15k_shape", 2, "bf16x6"), ("kg15k_shape", 3, "bf16x6"), ("kg15k_shape", 4, "bf16x3"),
+RUNS += [("kg15k_shape", 1, "tf32x3"), ("kg15k_shape", 3, "bf16x6"), ("kg15k_shape", 3, "tf32x3"),
          ("powerlaw_hubs", 1, "bf16x6"), ("powerlaw_hubs", 14, "bf16x6"), ("powerlaw_hubs", 14, "tf32x3"),
          ("powerlaw_hubs", 14, "bf16x3")]
 
