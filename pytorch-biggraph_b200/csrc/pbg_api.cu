@@ -52,7 +52,8 @@ struct pbg_context {
   char *allnegs_mem = nullptr;        // scratch of pbg_eval_batch_all_negs, allocated at its first call
   SortPlan csort = {{nullptr, nullptr}, {nullptr, nullptr}, nullptr, 0, 0};   // call-wide sort of all waves' slots
   char *csort_mem = nullptr;
-  bool wave_sort_only = false;        // PBG_CALL_SORT=0: sort wave by wave (for comparisons)
+  int group_sort_mode = -1;           // PBG_CALL_SORT: 1 = always sort waves in groups, 0 = never, unset = where it pays
+  std::vector<cudaEvent_t> ev_group;  // one per group of waves sorted together
   // optional event timing per kernel class
   const float *edge_w = nullptr;   // per-edge weights for the next train / eval call (pbg_set_edge_weights)
   bool profiling = false;
@@ -201,16 +202,18 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   const int Dpb = (cfg->dim + 7) / 8 * 8, Kb = (c->Mm + 7) / 8 * 8;
   size_t oXB[4] = {0, 0, 0, 0}, oAB[2] = {0, 0}, oTB[2] = {0, 0};
   // Standard relations under the dot / cos comparators with one score tile per chunk block: the fused
-  // score + loss kernel and the dual gradient product (pbg_pair.cu).  PBG_FUSED=0 in the environment keeps
-  // the separate score, loss and coefficient kernels (for comparisons).
+  // score + loss kernel and the dual gradient product (pbg_pair.cu).  Measured on a B200 it wins at dimension 100
+  // (+2.5 % and +5 % on the two such workloads, fewer and shorter launches) and loses at dimension 1024 (-4 %: the
+  // dual product's second operand costs more there than the merged coefficient matrix it saves), so it is the
+  // default up to dimension 256.  PBG_FUSED=1 / 0 in the environment forces one or the other.
   {
     const char *env = getenv("PBG_FUSED");
-    c->fused = planes && !dyn && !matrix_op && cfg->comparator < PBG_CMP_L2 && c->Pm <= 128 && c->Mm <= 256 &&
-               !(env && env[0] == '0');
+    const bool eligible = planes && !dyn && !matrix_op && cfg->comparator < PBG_CMP_L2 && c->Pm <= 128 && c->Mm <= 256;
+    c->fused = eligible && (env && (env[0] == '0' || env[0] == '1') ? env[0] == '1' : cfg->dim <= 256);
     const char *envh = getenv("PBG_HALVES");
     c->fused_halves = envh && envh[0] == '1';
     const char *envs = getenv("PBG_CALL_SORT");
-    c->wave_sort_only = envs && envs[0] == '0';
+    if (envs && (envs[0] == '0' || envs[0] == '1')) c->group_sort_mode = envs[0] - '0';
   }
   if (planes) {
     oXB[0] = take(nN * npl * Dpb * 2); oXB[1] = take(nN * npl * Dpb * 2);
@@ -327,6 +330,7 @@ extern "C" int pbg_destroy(pbg_context *c) {
   if (c->esort_mem) cudaFree(c->esort_mem);
   if (c->allnegs_mem) cudaFree(c->allnegs_mem);
   if (c->csort_mem) cudaFree(c->csort_mem);
+  for (auto e : c->ev_group) cudaEventDestroy(e);
   if (c->etab_dev) cudaFree(c->etab_dev);
   for (int s = 0; s < 2; ++s) {
     if (c->ev_sorted[s]) cudaEventDestroy(c->ev_sorted[s]);
@@ -364,7 +368,8 @@ extern "C" int pbg_neg_columns(const pbg_context *c, int32_t count, int32_t *chu
   return PBG_OK;
 }
 
-#define PBG_CALL_SORT_MAX (1ll << 23)     // most slots one call-wide sort takes (its counters and buffers are ~60 bytes per slot)
+#define PBG_CALL_SORT_MAX (1ll << 23)     // most slots of a call whose waves are sorted in groups (the buffers hold all of them: 24 bytes per slot)
+#define PBG_SORT_GROUP_SLOTS (1ll << 19)  // slots sorted at a time
 
 static int ensure_call_sort(pbg_context *c, long long n) {
   if (n <= c->csort.max_n) return PBG_OK;
@@ -553,29 +558,52 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
     slot0[wv + 1] = slot0[wv] + (long long)kk * d.spb;
     b0 += kk;
   }
-  // One sort for the whole call where it pays: the slots of all waves, keyed by (wave, row), in a single radix
-  // sort of a few passes -- instead of a dozen launches of a few microseconds per wave, which on small dimensions
-  // (a wave of 56,000 slots of 100 floats) are the critical path of the step.  The sorted list is the per-wave
-  // lists one after the other; the wave tags are masked off again.  Calls of a single wave, and calls beyond
-  // PBG_CALL_SORT_MAX slots (the counters of a radix pass grow with the list), sort wave by wave as before.
-  const int wave_bits = bit_length((unsigned long long)(nwaves - 1));
-  const bool call_sort = nwaves > 1 && slot0[nwaves] <= PBG_CALL_SORT_MAX && bits + wave_bits <= 44 && !c->wave_sort_only;
+  // Waves are sorted several at a time: the slots of a group of waves, keyed by (wave in the group, row), go through
+  // one radix sort of a few passes -- instead of a dozen launches of a few microseconds per wave, which on small
+  // dimensions (a wave of 56,000 slots of 100 floats) are a large part of the step.  The sorted list is the per-wave
+  // lists one after the other; the wave tags are masked off again.  Groups hold about PBG_SORT_GROUP_SLOTS slots, so
+  // that the first update of a call waits for a short sort only and the later groups are sorted beside the training
+  // of the earlier ones.  This pays where a wave's own sort needs three or more passes (keys above 22 bits: two
+  // partitions of millions of rows; measured +4.5 % on such a bucket at dimension 100); with two passes per wave the
+  // larger sort kernels of a group get in the way of the training kernels on the other stream more than the saved
+  // launches give back (-8 % on a 100,000-row graph), so those calls, and calls of a single wave, sort wave by wave.
+  // PBG_CALL_SORT=1 / 0 in the environment forces one or the other.
+  const long long wave_slots = (long long)c->kmax * d.spb;
+  int group = (int)((PBG_SORT_GROUP_SLOTS + wave_slots - 1) / wave_slots);
+  if (group > nwaves) group = nwaves;
+  if (group < 1) group = 1;
+  const int wave_bits = bit_length((unsigned long long)(group - 1));
+  const bool wanted = c->group_sort_mode == 1 || (c->group_sort_mode < 0 && bits > 22);
+  const bool call_sort = wanted && nwaves > 1 && group > 1 && slot0[nwaves] <= PBG_CALL_SORT_MAX && bits + wave_bits <= 44;
+  const int ngroups = call_sort ? (nwaves + group - 1) / group : 0;
   SortPlan *csp = nullptr;
   if (call_sort) {
     int rcs = ensure_call_sort(c, slot0[nwaves]);
     if (rcs) return rcs;
     csp = &c->csort;
-    ClassTimer t(c, 0, c->side);
-    int n = 0;
-    for (int wv = 0; wv < nwaves; ++wv) {
-      WaveDims dw = d;
-      dw.k = kks[wv]; dw.nblk = kks[wv] * d.Cm; dw.nocc = kks[wv] * d.spb; dw.blk0 = 0;
-      n += launch_build_keys(dw, wbs[wv], w, csp->keys[0] + slot0[wv], csp->vals[0] + slot0[wv], c->side, (unsigned long long)wv << bits);
+    while ((int)c->ev_group.size() < ngroups) {
+      cudaEvent_t e;
+      CU(c, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+      c->ev_group.push_back(e);
     }
-    n += pbg_sort(*csp, (int)slot0[nwaves], bits + wave_bits, c->side);
-    n += launch_mask_keys(csp->keys[csp->result], slot0[nwaves], (1ull << bits) - 1ull, c->side);
-    t.done(n);
-    CU(c, cudaEventRecord(c->ev_sorted[0], c->side));
+    for (int gi = 0; gi < ngroups; ++gi) {
+      const int w0 = gi * group, w1 = w0 + group < nwaves ? w0 + group : nwaves;
+      const long long off = slot0[w0], cnt = slot0[w1] - slot0[w0];
+      ClassTimer t(c, 0, c->side);
+      int n = 0;
+      for (int wv = w0; wv < w1; ++wv) {
+        WaveDims dw = d;
+        dw.k = kks[wv]; dw.nblk = kks[wv] * d.Cm; dw.nocc = kks[wv] * d.spb; dw.blk0 = 0;
+        n += launch_build_keys(dw, wbs[wv], w, csp->keys[0] + slot0[wv], csp->vals[0] + slot0[wv], c->side, (unsigned long long)(wv - w0) << bits);
+      }
+      SortPlan gsp = *csp;                                    // the group's part of the buffers; the counters are shared (one stream)
+      gsp.keys[0] += off; gsp.keys[1] += off; gsp.vals[0] += off; gsp.vals[1] += off;
+      n += pbg_sort(gsp, (int)cnt, bits + wave_bits, c->side);
+      csp->result = gsp.result;                               // the same number of passes for every group
+      n += launch_mask_keys(gsp.keys[gsp.result], cnt, (1ull << bits) - 1ull, c->side);
+      t.done(n);
+      CU(c, cudaEventRecord(c->ev_group[gi], c->side));
+    }
   }
   int wave = 0;
   for (int b0 = 0; b0 < num_batches; ++wave) {
@@ -628,7 +656,7 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
       { ClassTimer t(c, 6, c->part2); t.done(launch_stats(d, wb, w, stats_out ? c->stats_dev : nullptr, c->sum_dev, c->part2)); }
       CU(c, cudaEventRecord(c->ev_stats, c->part2));
     }
-    CU(c, cudaStreamWaitEvent(c->stream, c->ev_sorted[call_sort ? 0 : (wave & 1)], 0));
+    CU(c, cudaStreamWaitEvent(c->stream, call_sort ? c->ev_group[wave / group] : c->ev_sorted[wave & 1], 0));
     {
       ClassTimer t(c, 5);
       const unsigned long long *wkeys = call_sort ? csp->keys[csp->result] + slot0[wave] : sp.keys[sp.result];

@@ -266,12 +266,14 @@ def test_bf16_planes_at_every_baseline_shape(D, N, B, nb, nu, op, comp, loss, dy
         test_baseline_shapes_match_oracle(D, N, B, nb, nu, op, comp, loss, dyn, R, tier)
 
 
+@pytest.mark.parametrize("fused", ["0", "1"])
 @pytest.mark.parametrize("tier", PLANE_TIERS)
-def test_separate_score_loss_and_coefficient_kernels_still_match(tier, monkeypatch):
-    """Standard relations in the plane tiers normally train through the fused score / loss kernel and the
-    dual gradient product; PBG_FUSED=0 (read when the context is created) keeps the separate kernels, which
-    the forward-only entry points and the l2 comparators always use."""
-    monkeypatch.setenv("PBG_FUSED", "0")
+def test_fused_and_separate_kernels_both_match(tier, fused, monkeypatch):
+    """Standard relations in the plane tiers train either through the fused score / loss kernel and the dual
+    gradient product or through the separate score, loss, coefficient and gradient kernels (which the
+    forward-only entry points and the l2 comparators always use).  The library picks by dimension; PBG_FUSED
+    (read when the context is created) forces one or the other, and both are held to the oracle at both sizes."""
+    monkeypatch.setenv("PBG_FUSED", fused)
     with _tier_tolerance(tier):
         test_baseline_shapes_match_oracle(1024, 4000, 1000, 100, 100, "none", "dot", "softmax", False, 1, tier)
         test_baseline_shapes_match_oracle(100, 5000, 1000, 100, 100, "translation", "cos", "ranking", False, 1, tier)
