@@ -442,7 +442,8 @@ def run_b200_epoch(args, w, world, rank, dev):
     cfg, model, trainer = build_trainer(args, w, dev)
     dyn = bool(w.get("dynamic"))
     draw = EdgeDrawer(w, samplers, bounds, dev, gen)
-    drv = EpochDriver(P, lambda: PartitionBuffer(torch.empty(max_rows, D, device=dev), torch.empty(max_rows, device=dev)), cut, device=dev)
+    drv = EpochDriver(P, lambda: PartitionBuffer(torch.empty(max_rows, D, device=dev), torch.empty(max_rows, device=dev)), cut, device=dev,
+                      always_split=(world == 1))      # one GPU: the sub-bucket split without any exchange
     for buf in drv.resident():
         buf.emb.copy_(torch.randn(max_rows, D, device=dev, generator=gen) * 1e-3)
         buf.state.zero_()
@@ -465,21 +466,14 @@ def run_b200_epoch(args, w, world, rank, dev):
         keys = [(0, 0), (1, 0)] if which == "lhs" else [(0, 0), (0, 1)]
         return [(res[k][0], res[k][1], res[k][2] if rl is not None else None) for k in keys]
 
-    def plan_step(k):
-        """Whole-bucket edges of every bucket this rank trains in schedule step k."""
-        st = drv.steps[k % nsteps_epoch]
-        return {(s, bk): draw(bk, bucket_edges) for s in local_slots for bk in st.buckets[s]}
+    def plan_step(g):
+        """Whole-bucket edges of every bucket this rank trains in step g of the job."""
+        return {(s, bk): draw(bk, bucket_edges) for s, bk, _ in drv.calls_of(g)}
 
-    def presplit(k, whole):
-        st = drv.steps[k % nsteps_epoch]
-        out = {}
-        for s in local_slots:
-            a, b = st.holds[s]
-            out[(b, a)] = split((b, a), whole[(s, (b, a))], "lhs")
-            out[(a, b)] = split((a, b), whole[(s, (a, b))], "rhs")
-            for bk in st.buckets[s][2:]:
-                out[bk] = whole[(s, bk)]
-        return out
+    def presplit(g, whole):
+        """Step g's edge lists as the driver will ask for them: whole buckets, or the two half sub-buckets by the
+        rows of the side whose partition is leaving."""
+        return {bk: whole[(s, bk)] if side is None else split(bk, whole[(s, bk)], side) for s, bk, side in drv.calls_of(g)}
 
     def optimizer_for(table, state):
         o = T.RowAdagrad([table], lr=0.1)
@@ -523,7 +517,6 @@ def run_b200_epoch(args, w, world, rank, dev):
     # device-resident pass: edges drawn and split into sub-buckets ahead of the timed region
     whole = [plan_step(k) for k in range(total_steps)]
     pre = [presplit(k, whole[k]) for k in range(total_steps)]
-    host = [{key: tuple(None if t is None else t.cpu().pin_memory() for t in e) for key, e in whole[k].items()} for k in range(total_steps)]
 
     trace = []                                    # --trace: per step (schedule level, host ms to enqueue, device ms)
 
@@ -533,7 +526,7 @@ def run_b200_epoch(args, w, world, rank, dev):
             drv.run_step(train_fn, after_step)
             return
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        level = drv.steps[drv.step_index % nsteps_epoch].level
+        level = drv.step_at(drv.step_index).level
         t0 = time.perf_counter()
         a.record()
         drv.run_step(train_fn, after_step)
@@ -568,8 +561,7 @@ def run_b200_epoch(args, w, world, rank, dev):
         _lib.check(nat.lib.pbg_set_profiling(nat.ctx, 2), nat.ctx)
         done0 = cur["edges_done"]
         for _ in range(2):
-            kpos = drv.step_index % nsteps_epoch
-            cur["edges"] = presplit(kpos, plan_step(kpos))
+            cur["edges"] = presplit(drv.step_index, plan_step(drv.step_index))
             drv.run_step(train_fn, after_step)
         msc, lc = (C.c_double * 7)(), (C.c_int64 * 7)()
         _lib.check(nat.lib.pbg_kernel_times(nat.ctx, msc, lc), nat.ctx)
@@ -585,52 +577,51 @@ def run_b200_epoch(args, w, world, rank, dev):
     value = float(te) / (ms / 1e3)
 
     # end-to-end pass: whole-bucket edges in pinned host memory; copy, device sub_bucket, training and the read-back of
-    # the step's summed Stats inside the timed region.  The schedule continues where the first pass stopped (the driver
-    # keeps its position; the edge lists are reused in order, so that every step gets the buckets it trains).
-    offset = total_steps % nsteps_epoch
+    # the step's summed Stats inside the timed region.  The job goes on where the first pass stopped.
+    del whole, pre
+    g0 = drv.step_index
+    nwarm = min(args.warmup, 2)
 
-    def step_host(k):
-        kk = k                                         # edge lists were drawn for schedule position k % epoch
-        up = {key: tuple(None if t is None else t.to(dev, non_blocking=True) for t in e) for key, e in host[kk].items()}
-        cur["edges"] = presplit(kk, up)
+    def pinned(e):
+        return tuple(None if t is None else t.cpu().pin_memory() for t in e)
+
+    host = [{key: pinned(e) for key, e in plan_step(g0 + i).items()} for i in range(nwarm + args.steps)]
+
+    def step_host(i):
+        assert drv.step_index == g0 + i
+        up = {key: tuple(None if t is None else t.to(dev, non_blocking=True) for t in e) for key, e in host[i].items()}
+        cur["edges"] = presplit(g0 + i, up)
         drv.run_step(train_fn, after_step)
         return trainer.read_stats()
 
-    e2e = None
-    if offset == 0 or True:
-        # bring the driver back to the start of an epoch so that step k of this pass is schedule step k again
-        while drv.step_index % nsteps_epoch != 0:
-            cur["edges"] = pre[drv.step_index % nsteps_epoch] if drv.step_index % nsteps_epoch < total_steps else None
-            if cur["edges"] is None:
-                cur["edges"] = presplit(drv.step_index % nsteps_epoch, plan_step(drv.step_index % nsteps_epoch))
-            drv.run_step(train_fn, after_step)
-        for k in range(min(args.warmup, 2)):
-            step_host(k)
-        barrier()
-        cur["edges_done"] = 0
-        e0.record()
-        last = None
-        for k in range(min(args.warmup, 2), min(args.warmup, 2) + args.steps):
-            last = step_host(k % total_steps)
-        e1.record()
-        barrier()
-        ms_e2e = e0.elapsed_time(e1)
-        t = torch.tensor([ms_e2e], device=dev)
-        over_ranks(t, dist.ReduceOp.MAX)
-        te = torch.tensor([float(cur["edges_done"])], device=dev, dtype=torch.float64)
-        over_ranks(te)
-        e2e = {"value": float(te) / (float(t) / 1e3), "unit": "edges/sec",
-               "h2d_bytes_per_step": int((3 if dyn else 2) * 8 * float(te) / args.steps), "d2h_bytes_per_step": 40 * world,
-               "last_step_loss": last.metrics["loss"] if last is not None else None}
+    for i in range(nwarm):
+        step_host(i)
+    barrier()
+    cur["edges_done"] = 0
+    e0.record()
+    last = None
+    for i in range(nwarm, nwarm + args.steps):
+        last = step_host(i)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    t = torch.tensor([ms_e2e], device=dev)
+    over_ranks(t, dist.ReduceOp.MAX)
+    te = torch.tensor([float(cur["edges_done"])], device=dev, dtype=torch.float64)
+    over_ranks(te)
+    e2e = {"value": float(te) / (float(t) / 1e3), "unit": "edges/sec",
+           "h2d_bytes_per_step": int((3 if dyn else 2) * 8 * float(te) / args.steps), "d2h_bytes_per_step": 40 * world,
+           "last_step_loss": last.metrics["loss"] if last is not None else None}
 
     if rank == 0:
         cfgd = _workload_config(args, w, bucket_edges)
-        cfgd["step"] = (f"one step of the epoch schedule: two buckets of {bucket_edges} edges per GPU (four in the last step of an epoch), "
-                        f"each trained as half sub-buckets of its circulating partition")
-        cfgd["schedule"] = (f"{nsteps_epoch} steps per epoch cover all {P * P} buckets; every GPU holds two partitions at a time")
-        cfgd["hand_off"] = ("the circulating partition travels to the ring neighbour in two halves over NCCL send/recv (NVLink), each "
-                            "half beside the training of the other; partitions are re-dealt between the levels of the schedule; "
-                            "all inside the timed region" + ("; shared relation parameters and their accumulators averaged with one "
+        per = P // 2 // world
+        cfgd["step"] = (f"one step of the epoch schedule: {2 * per} buckets of {bucket_edges} edges per GPU ({4 * per} in the last step of an "
+                        f"epoch); a bucket over a partition that leaves for another GPU after the step is trained as two half sub-buckets")
+        cfgd["schedule"] = (f"{nsteps_epoch} steps per epoch cover all {P * P} buckets; every slot holds two partitions at a time, {P // 2 // world} slots per GPU")
+        cfgd["hand_off"] = ("between two steps a slot gives one partition away and takes one in; it travels in two halves over NCCL "
+                            "send/recv (NVLink), each half beside the training of the other, inside a level and at a change of level "
+                            "alike; nothing moves between epochs; all inside the timed region" + ("; shared relation parameters and their accumulators averaged with one "
                                                              "all-reduce per step" if shared else ""))
         line = {"metric": "edges/sec trained", "value": value, "unit": "edges/sec", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",

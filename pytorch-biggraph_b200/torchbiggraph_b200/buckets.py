@@ -10,7 +10,7 @@ the next GPU between rounds with torch.distributed point-to-point calls -- NCCL 
 GPUs, gloo on CPU for the tests.  The receiving GPU reads the partition only from its own memory.
 """
 import math
-from typing import List, NamedTuple, Sequence, Tuple
+from typing import List, NamedTuple, Sequence, Tuple, Optional
 
 import torch
 import torch.distributed as dist
@@ -129,6 +129,20 @@ class OverlappedRing:
             self.stream.wait_event(done)
             return dist.batch_isend_irecv(ops)
 
+    def start_many(self, sends: Sequence[Tuple[torch.Tensor, int]], recvs: Sequence[Tuple[torch.Tensor, int]]):
+        """As `start_to`, with a peer per tensor: (tensor, to rank) and (tensor, from rank) pairs, one group."""
+        ops = [dist.P2POp(dist.isend, t, peer, self.group) for t, peer in sends]
+        ops += [dist.P2POp(dist.irecv, t, peer, self.group) for t, peer in recvs]
+        if not ops:
+            return None
+        if not self.cuda:
+            return dist.batch_isend_irecv(ops)
+        done = torch.cuda.Event()
+        done.record()                                # everything enqueued so far has written the tensors that leave
+        with torch.cuda.stream(self.stream):
+            self.stream.wait_event(done)
+            return dist.batch_isend_irecv(ops)
+
     @staticmethod
     def finish(handle) -> None:
         if handle is None:
@@ -175,44 +189,56 @@ class EpochStep(NamedTuple):
     level: int
 
 
-def epoch_schedule(num_partitions: int) -> List[EpochStep]:
+def epoch_schedule(num_partitions: int, start: Optional[Sequence[Tuple[int, int]]] = None) -> List[EpochStep]:
     """All P x P buckets of an epoch for P/2 slots (P a power of two, P >= 2), every slot holding two
     partitions at a time and training only buckets over those two -- the lock server's rule that buckets
     in flight share no partition (torchbiggraph/bucket_scheduling.py:477-540), laid out ahead of time as the
     reference's GPU trainer lays out its sub-partition jobs (torchbiggraph/train_gpu.py:354-387).
 
-    Level 0 splits the partitions into a stationary half A and a circulating half B: in step s slot i holds
-    (A[i], B[(i + s) mod |B|]) and trains (a, b) and (b, a); after |B| steps every A x B and B x A bucket is
-    done and B has gone once round the ring of slots.  What is left are the buckets inside A and inside B:
-    the next level does the same for each half on half of the slots, and so on; at the last level a slot
-    holds the only two partitions of its group and also trains their diagonal buckets.  For P = 16:
-    8 + 4 + 2 + 1 = 15 steps, 256 buckets, and between two steps of a level a slot passes exactly one
-    partition to its ring neighbour."""
+    `start[s]` = (stationary, circulating) partition of slot s when the epoch begins; any placement of the P
+    partitions will do (default: slot s holds s and P/2 + s).  Level 0 is one ring over all slots: for as many
+    steps as there are slots every slot trains (a, b) and (b, a) over its two partitions, then the circulating
+    ones move one slot on -- after which every stationary x circulating bucket is done.  What is left are the
+    buckets inside the stationary set and inside the circulating set.  The ring is cut in two: slot j of the
+    lower half keeps its stationary partition and takes that of slot j of the upper half as its circulating
+    one; the upper slot keeps the circulating partition it has, now as its stationary one, and takes the lower
+    slot's circulating partition.  So a change of level is one swap between two slots -- one partition out and
+    one in per slot -- and the next level runs the same scheme in rings of half the size, down to rings of one
+    slot, which also train the diagonal buckets of their two partitions.  For P = 16: 8 + 4 + 2 + 1 = 15 steps,
+    256 buckets.  The placement the epoch ends with is a valid `start` for the next one: nothing moves between
+    epochs."""
     P = num_partitions
     if P < 2 or P & (P - 1):
         raise ValueError("epoch_schedule needs a power-of-two number of partitions >= 2")
+    S = P // 2
+    holds = [(s, S + s) for s in range(S)] if start is None else [tuple(h) for h in start]
+    if len(holds) != S or sorted(p for h in holds for p in h) != list(range(P)):
+        raise ValueError("start must place every partition in exactly one of the P/2 slots")
     steps: List[EpochStep] = []
-    groups = [list(range(P))]            # each group owns len(group) / 2 consecutive slots
-    level = 0
-    while len(groups[0]) >= 2:
-        g = len(groups[0])
-        half = g // 2
-        last = g == 2
-        for s in range(half):
-            holds, buckets = [], []
-            for grp in groups:
-                A, B = grp[:half], grp[half:]
-                for i in range(half):
-                    a, b = A[i], B[(i + s) % half]
-                    holds.append((a, b))
-                    bs = [(a, b), (b, a)]
-                    if last:
-                        bs += [(a, a), (b, b)]
-                    buckets.append(bs)
-            steps.append(EpochStep(holds, buckets, level))
-        groups = [h for grp in groups for h in (grp[:half], grp[half:])]
-        level += 1
+    g, level = S, 0                                   # slots per ring at this level
+    while True:
+        last = g == 1
+        for s in range(g):
+            buckets = [[(a, b), (b, a)] + ([(a, a), (b, b)] if last else []) for a, b in holds]
+            steps.append(EpochStep(list(holds), buckets, level))
+            if s < g - 1:                             # the circulating partitions move one slot down their ring
+                holds = [(holds[i][0], holds[i // g * g + (i % g + 1) % g][1]) for i in range(S)]
+        if last:
+            break
+        h = g // 2
+        nxt = list(holds)
+        for base in range(0, S, g):
+            for j in range(h):
+                lo, up = base + j, base + h + j
+                nxt[lo] = (holds[lo][0], holds[up][0])
+                nxt[up] = (holds[up][1], holds[lo][1])
+        holds, g, level = nxt, h, level + 1
     return steps
+
+
+def next_epoch_start(steps: Sequence[EpochStep]) -> List[Tuple[int, int]]:
+    """The placement an epoch ends with, as the `start` of the next one."""
+    return list(steps[-1].holds)
 
 
 def slot_rank(slot: int, num_slots: int, world_size: int) -> int:
@@ -254,149 +280,210 @@ class PartitionBuffer:
 
 
 class EpochDriver:
-    """Runs `epoch_schedule` on the ranks of a process group: every rank owns the slots `slot_rank` gives it,
-    trains their buckets step by step, and passes partitions on as the schedule says.
+    """Runs `epoch_schedule` on the ranks of a process group, epoch after epoch: every rank owns the slots
+    `slot_rank` gives it, trains their buckets step by step, and passes partitions on as the schedule says.
 
-    Inside a level the circulating partition b of a slot leaves for the ring neighbour in two halves (rows
-    [0, cut) and [cut, rows)): the step trains, for h = 0, 1, the sub-buckets (b[h], a) -- edges of bucket
-    (b, a) whose lhs row lies in half h -- and (a, b[h]); as soon as those of half h are enqueued the half is
-    sent (and the half arriving from the other neighbour received into the spare buffer) on a side stream,
-    beside the training of the other half: the hand-off is off the critical path, as the reference overlaps
-    partition swaps with training through its sub-partition jobs (torchbiggraph/train_gpu.py:456-652).  A
-    neighbour on the same GPU gets the buffer itself.  Between levels (three times per epoch of 16
-    partitions, and at the epoch's end) partitions are re-dealt with one blocking exchange.
+    Between two steps a slot gives away at most one of its two partitions and takes one in.  The one that leaves
+    -- the circulating partition inside a level; at a change of level the circulating one in the lower half of a
+    ring and the stationary one in the upper half -- travels in two halves (rows [0, cut) and [cut, rows)): the
+    step trains, for h = 0, 1, the two sub-buckets over half h of it (the edges whose row on that side lies in
+    half h), and as soon as those are enqueued half h is sent, and half h of the arriving partition received into
+    a spare buffer, on a side stream beside the training of the other half: the hand-off is off the critical
+    path, as the reference overlaps partition swaps with training through its sub-partition jobs
+    (torchbiggraph/train_gpu.py:456-652).  A partition that only changes slots on one GPU changes labels, and
+    its buckets are trained whole (unless `always_split`); nothing moves between epochs.  A partition that
+    arrives is the circulating one of its new slot; a step that needs it whole from the start (the one step of
+    the last level, and the upper half's last step of a level) first waits for both of its halves.
 
     train_fn(bucket, lhs, rhs, sub) does the training: lhs / rhs are (emb, state) tensors -- whole partitions
     or halves -- and sub is None for a whole bucket or ("lhs" | "rhs", h, cut) for a half sub-bucket.
     after_step(step) runs once per step on every rank (e.g. the all-reduce of shared relation parameters).
+    `calls_of(g)` lists what step g will hand to train_fn, for callers that prepare sub-bucket edge lists.
     """
 
-    def __init__(self, num_partitions: int, alloc, cut: int, group=None, device=None):
+    def __init__(self, num_partitions: int, alloc, cut: int, group=None, device=None, always_split: bool = False):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.steps = epoch_schedule(num_partitions)
+        self.P = num_partitions
+        self._epochs = {0: epoch_schedule(num_partitions)}
+        self.steps = self._epochs[0]                  # the first epoch's steps (every epoch has as many)
         self.S = num_partitions // 2
         self.local_slots = [s for s in range(self.S) if slot_rank(s, self.S, self.world) == self.rank]
         self.cut = cut
-        self.alloc = alloc
+        self.always_split = always_split
         self.ring = OverlappedRing(device, group) if self.world > 1 else None
         self.stat = {s: alloc() for s in self.local_slots}
         self.circ = {s: alloc() for s in self.local_slots}
-        self.spare = alloc() if self.world > 1 else None
-        self.pending = [None, None]          # hand-off of half h started in the previous step
+        self.pending = [None, None]          # transfers of half h started in the previous step
         self.step_index = 0
-        self._pool: List[PartitionBuffer] = []
         for s in self.local_slots:
             a, b = self.steps[0].holds[s]
             self.stat[s].partition, self.circ[s].partition = a, b
+        self._spares: List[PartitionBuffer] = []
+        if self.world > 1:
+            # Everything a hand-off needs exists before the first step: spare buffers for the largest number of
+            # partitions that ever arrive from other ranks at once (the placements of later epochs differ, the
+            # counts do not), and an open connection to every rank (NCCL sets a pair's connection up at their
+            # first exchange, which takes on the order of a second; a level's ring only ever talks to two
+            # neighbours, so without this the first change of level would pay for all the others).
+            n = len(self.steps)
+            two = self._epochs[0] + epoch_schedule(num_partitions, next_epoch_start(self._epochs[0]))
+            most = max(sum(1 for _, src, dst in partition_moves(x, y, self.world) if dst == self.rank) for x, y in zip(two, two[1:]))
+            self._spares = [alloc() for _ in range(most)]
+            self._connect_all(self.stat[self.local_slots[0]].state)
+
+    def _connect_all(self, like: torch.Tensor) -> None:
+        out = torch.zeros(1, dtype=like.dtype, device=like.device)
+        into = [torch.zeros(1, dtype=like.dtype, device=like.device) for _ in range(self.world)]
+        ops = []
+        for peer in range(self.world):
+            if peer != self.rank:
+                ops.append(dist.P2POp(dist.isend, out, peer, self.group))
+                ops.append(dist.P2POp(dist.irecv, into[peer], peer, self.group))
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+
+    def step_at(self, g: int) -> EpochStep:
+        """Step g of the job (epochs follow one another; each starts from the placement the one before ended with)."""
+        n = len(self.steps)
+        e, k = divmod(g, n)
+        if e not in self._epochs:
+            if e < min(self._epochs):                         # asked for the past: lay it out again from the start
+                self._epochs = {0: epoch_schedule(self.P)}
+            for x in range(max(self._epochs) + 1, e + 1):
+                self._epochs[x] = epoch_schedule(self.P, next_epoch_start(self._epochs[x - 1]))
+            for x in [x for x in self._epochs if x < self.step_index // n - 1]:       # epochs the job has left behind
+                del self._epochs[x]
+        return self._epochs[e][k]
 
     def resident(self) -> List[PartitionBuffer]:
         """Buffers that hold a partition right now (for initialisation and checkpointing)."""
         return [self.stat[s] for s in self.local_slots] + [self.circ[s] for s in self.local_slots]
 
-    # ---- one step -------------------------------------------------------------------------------
-    def _ring_of(self, step: EpochStep, slot: int) -> Tuple[int, int]:
-        half = self.S >> step.level            # slots per ring at this level
-        base = slot // half * half
-        return base, half
+    # ---- what a step does -----------------------------------------------------------------------
+    def _plan(self, g: int):
+        """Per local slot of step g: (slot, role of the partition that leaves -- "circ", "stat" or None --, whether its
+        buckets are trained as half sub-buckets, slot it goes to, partition that arrives, slot it comes from)."""
+        st, nxt = self.step_at(g), self.step_at(g + 1)
+        where_next = {p: t for t, h in enumerate(nxt.holds) for p in h}
+        where_now = {p: t for t, h in enumerate(st.holds) for p in h}
+        fresh = self._fresh(g)
+        plan = []
+        for s in self.local_slots:
+            a, b = st.holds[s]
+            gone = [p for p in (a, b) if p not in nxt.holds[s]]
+            come = [p for p in nxt.holds[s] if p not in (a, b)]
+            assert len(gone) <= 1 and len(gone) == len(come), (g, s, st.holds[s], nxt.holds[s])
+            if not gone:
+                plan.append((s, None, False, None, None, None))
+                continue
+            role = "circ" if gone[0] == b else "stat"
+            to_slot, from_slot = where_next[gone[0]], where_now[come[0]]
+            crosses = slot_rank(to_slot, self.S, self.world) != self.rank
+            # a circulating partition whose second half is still on its way here is read half by half as well
+            plan.append((s, role, crosses or self.always_split or (role == "circ" and s in fresh), to_slot, come[0], from_slot))
+        return st, nxt, plan
+
+    def _fresh(self, g: int) -> set:
+        """Local slots whose circulating partition of step g came from another rank during step g - 1."""
+        if g == 0 or self.world == 1:
+            return set()
+        prev, st = self.step_at(g - 1), self.step_at(g)
+        where_prev = {p: t for t, h in enumerate(prev.holds) for p in h}
+        return {s for s in self.local_slots for p in st.holds[s]
+                if p not in prev.holds[s] and slot_rank(where_prev[p], self.S, self.world) != self.rank}
+
+    def calls_of(self, g: int) -> List[Tuple[int, Tuple[int, int], Optional[str]]]:
+        """(slot, bucket, side split in halves or None) for every bucket this rank trains in step g."""
+        st, _, plan = self._plan(g)
+        out = []
+        for s, role, split, *_ in plan:
+            a, b = st.holds[s]
+            if split:
+                first, second = ((b, a), (a, b)) if role == "circ" else ((a, b), (b, a))
+                out += [(s, first, "lhs"), (s, second, "rhs")]           # the leaving partition is first's lhs and second's rhs
+            else:
+                out += [(s, (a, b), None), (s, (b, a), None)]
+            out += [(s, bk, None) for bk in st.buckets[s][2:]]
+        return out
 
     def run_step(self, train_fn, after_step=None) -> int:
         """Trains the current step of the schedule on this rank's slots, starts the hand-offs that lead to the
         next one, and returns the number of buckets (whole-bucket equivalents) trained here."""
-        k = self.step_index % len(self.steps)
-        st = self.steps[k]
-        nxt = self.steps[(k + 1) % len(self.steps)]
-        same_level = nxt.level == st.level and k + 1 < len(self.steps)
-        last_level = len(st.buckets[0]) == 4
+        g = self.step_index
+        st, nxt, plan = self._plan(g)
         cut = self.cut
-        base, half = self._ring_of(st, self.local_slots[0])
-        # the one ring that spans ranks (if any): its lowest local slot sends off-rank, its highest receives
-        spans = same_level and half > len(self.local_slots)
-        send_slot = self.local_slots[0] if spans else None
-        recv_slot = self.local_slots[-1] if spans else None
+        # a partition that arrived last step is the circulating one of its slot; unless every slot reads it half by
+        # half (it is the one that is split), both halves must be here before anything is trained
+        fresh = self._fresh(g)
+        if any(s in fresh and not (split and role == "circ") for s, role, split, *_ in plan):
+            for h in (0, 1):
+                OverlappedRing.finish(self.pending[h])
+                self.pending[h] = None
+        # cross-rank traffic of this step, in partition order (both ends of a pair of ranks sort alike)
+        outgoing = sorted((self.stat[s] if role == "stat" else self.circ[s]).partition for s, role, split, to, _, _ in plan
+                          if role is not None and slot_rank(to, self.S, self.world) != self.rank)
+        incoming = sorted(come for s, role, split, to, come, frm in plan
+                          if role is not None and slot_rank(frm, self.S, self.world) != self.rank)
+        peer_out = {(self.stat[s] if role == "stat" else self.circ[s]).partition: slot_rank(to, self.S, self.world)
+                    for s, role, split, to, _, _ in plan if role is not None}
+        peer_in = {come: slot_rank(frm, self.S, self.world) for s, role, split, to, come, frm in plan if role is not None}
+        landing = {}
+        for p in incoming:
+            buf = self._spares.pop()
+            buf.partition = p
+            landing[p] = buf
+        leaving_buf = {}
+        for s, role, split, to, _, _ in plan:
+            if role is not None:
+                buf = self.stat[s] if role == "stat" else self.circ[s]
+                leaving_buf[buf.partition] = buf
         done = 0
         for h in (0, 1):
             if self.pending[h] is not None:          # the half about to be trained on has arrived, the old one has left
                 OverlappedRing.finish(self.pending[h])
                 self.pending[h] = None
-            for s in self.local_slots:
-                a, b = st.holds[s]
+            for s, role, split, *_ in plan:
                 A, B = self.stat[s], self.circ[s]
-                assert A.partition == a and B.partition == b, (self.rank, k, s, A.partition, B.partition, a, b)
-                train_fn((b, a), B.half(h, cut), (A.emb, A.state), ("lhs", h, cut))
-                train_fn((a, b), (A.emb, A.state), B.half(h, cut), ("rhs", h, cut))
-                if s == send_slot:
-                    nb_rank = slot_rank(base + (s - base - 1) % half, self.S, self.world)
-                    from_rank = slot_rank(base + (recv_slot - base + 1) % half, self.S, self.world)
-                    self.pending[h] = self.ring.start_to(list(B.half(h, cut)), nb_rank, list(self.spare.half(h, cut)), from_rank)
-        for s in self.local_slots:
+                a, b = st.holds[s]
+                assert A.partition == a and B.partition == b, (self.rank, g, s, A.partition, B.partition, a, b)
+                if not split:
+                    if h == 0:
+                        train_fn((a, b), (A.emb, A.state), (B.emb, B.state), None)
+                        train_fn((b, a), (B.emb, B.state), (A.emb, A.state), None)
+                elif role == "circ":
+                    train_fn((b, a), B.half(h, cut), (A.emb, A.state), ("lhs", h, cut))
+                    train_fn((a, b), (A.emb, A.state), B.half(h, cut), ("rhs", h, cut))
+                else:
+                    train_fn((a, b), A.half(h, cut), (B.emb, B.state), ("lhs", h, cut))
+                    train_fn((b, a), (B.emb, B.state), A.half(h, cut), ("rhs", h, cut))
+            if outgoing or incoming:
+                sends = [(t, peer_out[p]) for p in outgoing for t in leaving_buf[p].half(h, cut)]
+                recvs = [(t, peer_in[p]) for p in incoming for t in landing[p].half(h, cut)]
+                self.pending[h] = self.ring.start_many(sends, recvs)
+        for s, role, split, *_ in plan:
             done += 2
-            if last_level:
-                a, b = st.holds[s]
-                A, B = self.stat[s], self.circ[s]
-                train_fn((a, a), (A.emb, A.state), (A.emb, A.state), None)
-                train_fn((b, b), (B.emb, B.state), (B.emb, B.state), None)
-                done += 2
+            A, B = self.stat[s], self.circ[s]
+            for bk in st.buckets[s][2:]:
+                src = {A.partition: A, B.partition: B}
+                L, R = src[bk[0]], src[bk[1]]
+                train_fn(bk, (L.emb, L.state), (R.emb, R.state), None)
+                done += 1
         if after_step is not None:
             after_step(st)
         # ---- where the partitions are in the next step ----
-        if same_level:
-            self._rotate(st, nxt, spans, send_slot, recv_slot)
-        else:
-            for h in (0, 1):
-                OverlappedRing.finish(self.pending[h])
-                self.pending[h] = None
-            self._redeal(st, nxt)
-        self.step_index += 1
-        return done
-
-    def _rotate(self, st: EpochStep, nxt: EpochStep, spans: bool, send_slot, recv_slot) -> None:
-        """Inside a level: slot s's circulating partition becomes that of slot s - 1 of its ring."""
-        old = {s: self.circ[s] for s in self.local_slots}
-        for s in self.local_slots:
-            base, half = self._ring_of(st, s)
-            src = base + (s - base + 1) % half               # the slot whose partition comes here
-            if src in old and not (spans and s == recv_slot):
-                self.circ[s] = old[src]
-        if spans:
-            incoming = self.spare                             # being filled by the transfers started in this step
-            incoming.partition = nxt.holds[recv_slot][1]
-            self.spare = old[send_slot]                       # leaves with the same transfers; free once they finish
-            self.spare.partition = -1
-            self.circ[recv_slot] = incoming
-        for s in self.local_slots:
-            assert self.circ[s].partition == nxt.holds[s][1], (self.rank, s, self.circ[s].partition, nxt.holds[s])
-
-    def _redeal(self, st: EpochStep, nxt: EpochStep) -> None:
-        """Between levels and at the end of an epoch: every partition goes where the next step wants it, in
-        one blocking exchange (buffers that stay on the GPU are only re-labelled)."""
         have = {}
         for s in self.local_slots:
             have[self.stat[s].partition] = self.stat[s]
             have[self.circ[s].partition] = self.circ[s]
-        want = [(s, role, p) for s in self.local_slots for role, p in zip(("stat", "circ"), nxt.holds[s])]
-        moves = partition_moves(st, nxt, self.world)
-        outgoing = [(p, dst) for p, src, dst in moves if src == self.rank]
-        incoming = [(p, src) for p, src, dst in moves if dst == self.rank]
-        recv_buf = {}
-        ops = []
-        for p, src in sorted(incoming):
-            buf = self._pool.pop() if self._pool else self.alloc()
-            buf.partition = p
-            recv_buf[p] = buf
-        # one group; sends and receives between a pair of ranks are matched in partition order on both sides
-        for p, dst in sorted(outgoing):
-            ops += [dist.P2POp(dist.isend, t, dst, self.group) for t in have[p].tensors()]
-        for p, src in sorted(incoming):
-            ops += [dist.P2POp(dist.irecv, t, src, self.group) for t in recv_buf[p].tensors()]
-        if ops:
-            for req in dist.batch_isend_irecv(ops):
-                req.wait()
-        for p, _ in outgoing:
+        for p in outgoing:                              # leaves with the transfers just started; a spare once they finish
             buf = have.pop(p)
             buf.partition = -1
-            self._pool.append(buf)
-        have.update(recv_buf)
-        for s, role, p in want:
-            (self.stat if role == "stat" else self.circ)[s] = have[p]
+            self._spares.append(buf)
+        have.update(landing)
+        for s in self.local_slots:
+            a2, b2 = nxt.holds[s]
+            self.stat[s], self.circ[s] = have[a2], have[b2]
+        self.step_index += 1
+        return done
