@@ -35,7 +35,7 @@ WORKLOADS = {
     "c3": dict(entities=4_847_571, edges=68_993_773, partitions=16, dim=1024, op="none", comp="dot", loss="softmax",
                batch=1000, nb=100, nu=100, gamma=2.3, precision="bf16x6", desc="social-graph shaped, Chung-Lu exponent 2.3"),
     "c4": dict(entities=41_652_230, edges=1_468_365_182, partitions=16, dim=100, op="translation", comp="cos",
-               loss="ranking", batch=1000, nb=100, nu=100, gamma=2.0, desc="follower-graph shaped, Chung-Lu exponent 2.0"),
+               loss="ranking", batch=1000, nb=100, nu=100, gamma=2.0, precision="bf16x6", desc="follower-graph shaped, Chung-Lu exponent 2.0"),
     "c5": dict(entities=86_054_151, edges=338_586_276, partitions=16, dim=200, op="complex_diagonal", comp="l2",
                loss="logistic", batch=1000, nb=100, nu=100, gamma=None, rels=14_824, dynamic=True, rel_zipf=1.2, uniform_endpoints=True,
                desc="large multi-relation KG shaped, 14824 relations Zipf(1.2), per-relation operators (dynamic relations)"),
@@ -914,7 +914,7 @@ def main():
                     help="arithmetic of the contractions.  tf32x3: tcgen05 TF32 with 3-term split, the rtol 1e-4 tier; "
                          "bf16x6: tcgen05 bf16 on three planes per fp32 operand (24 mantissa bits), six plane products, "
                          "the rtol 1e-4 tier; fp32: CUDA cores; tf32: single pass, the rtol 1e-3 tier.  Default: the faster "
-                         "of the two rtol 1e-4 tensor-core tiers on the workload (c3, c1: bf16x6; c2, c4: tf32x3)")
+                         "of the two rtol 1e-4 tensor-core tiers on the workload (c3, c1, c4: bf16x6; c2, c5: tf32x3)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--buckets-per-step", type=int, default=0,
                     help="one GPU: buckets (library calls) per step; default 8 on partitioned workloads, 1 otherwise")

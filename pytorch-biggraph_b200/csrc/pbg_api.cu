@@ -38,6 +38,8 @@ struct pbg_context {
   float *psum = nullptr;        // partial gradient rows of hub rows, indexed by slot position
   long long *hublist = nullptr;
   int *hubcnt = nullptr;
+  cudaStream_t upd_side = nullptr;                          // operator-row kernels that run beside the embedding rows' update
+  cudaEvent_t ev_upd_fork = nullptr, ev_upd_join = nullptr;
   long long *edge_dev[3] = {nullptr, nullptr, nullptr};
   long long edge_cap = 0;
   long long *uni_dev[2] = {nullptr, nullptr};
@@ -52,6 +54,7 @@ struct pbg_context {
   char *allnegs_mem = nullptr;        // scratch of pbg_eval_batch_all_negs, allocated at its first call
   SortPlan csort = {{nullptr, nullptr}, {nullptr, nullptr}, nullptr, 0, 0};   // call-wide sort of all waves' slots
   char *csort_mem = nullptr;
+  int split_min_k = 2;                // waves of at least this many batches run as two halves on two streams (PBG_SPLIT_MIN_K)
   int group_sort_mode = -1;           // PBG_CALL_SORT: 1 = always sort waves in groups, 0 = never, unset = where it pays
   std::vector<cudaEvent_t> ev_group;  // one per group of waves sorted together
   // optional event timing per kernel class
@@ -212,6 +215,8 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
     c->fused = eligible && (env && (env[0] == '0' || env[0] == '1') ? env[0] == '1' : cfg->dim <= 256);
     const char *envh = getenv("PBG_HALVES");
     c->fused_halves = envh && envh[0] == '1';
+    const char *envk = getenv("PBG_SPLIT_MIN_K");
+    if (envk && atoi(envk) >= 2) c->split_min_k = atoi(envk);
     const char *envs = getenv("PBG_CALL_SORT");
     if (envs && (envs[0] == '0' || envs[0] == '1')) c->group_sort_mode = envs[0] - '0';
   }
@@ -295,6 +300,11 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   CU(c, cudaEventCreateWithFlags(&c->ev_part2, cudaEventDisableTiming));
   CU(c, cudaEventCreateWithFlags(&c->ev_joined, cudaEventDisableTiming));
   CU(c, cudaEventCreateWithFlags(&c->ev_stats, cudaEventDisableTiming));
+  if (!(getenv("PBG_REL_ASIDE") && getenv("PBG_REL_ASIDE")[0] == '0')) {        // PBG_REL_ASIDE=0: everything on one stream (for comparisons)
+    CU(c, cudaStreamCreateWithFlags(&c->upd_side, cudaStreamNonBlocking));
+    CU(c, cudaEventCreateWithFlags(&c->ev_upd_fork, cudaEventDisableTiming));
+    CU(c, cudaEventCreateWithFlags(&c->ev_upd_join, cudaEventDisableTiming));
+  }
   c->sum_dev = (double *)(c->ws + oSum);
   c->errflag = (int *)(c->ws + oErr);
   c->eval_dev = (double *)(c->ws + oEval);
@@ -339,6 +349,9 @@ extern "C" int pbg_destroy(pbg_context *c) {
   if (c->ev_inputs) cudaEventDestroy(c->ev_inputs);
   if (c->side) cudaStreamDestroy(c->side);
   if (c->part2) cudaStreamDestroy(c->part2);
+  if (c->upd_side) cudaStreamDestroy(c->upd_side);
+  if (c->ev_upd_fork) cudaEventDestroy(c->ev_upd_fork);
+  if (c->ev_upd_join) cudaEventDestroy(c->ev_upd_join);
   if (c->ev_wave) cudaEventDestroy(c->ev_wave);
   if (c->ev_part2) cudaEventDestroy(c->ev_part2);
   if (c->ev_joined) cudaEventDestroy(c->ev_joined);
@@ -626,14 +639,14 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
       // the fused score kernel computes both problems of a chunk block in one CTA: a wave of 14 batches of 10
       // chunks is one round of 140 CTAs, where its halves would each leave half of the SMs idle
       run_part(c, d, wb, w, c->stream);
-    } else if (kk >= 2 && c->profile_serial) {
+    } else if (kk >= c->split_min_k && c->profile_serial) {
       int ka = (kk + 1) / 2;
       WaveDims da = d, db = d;
       da.nblk = ka * d.Cm;
       db.blk0 = ka * d.Cm; db.nblk = (kk - ka) * d.Cm;
       run_part(c, da, wb, w, c->stream);
       run_part(c, db, wb, w, c->stream);
-    } else if (kk >= 2) {
+    } else if (kk >= c->split_min_k) {
       int ka = (kk + 1) / 2;
       WaveDims da = d, db = d;
       da.nblk = ka * d.Cm;
@@ -649,7 +662,7 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
     }
     // The per-batch statistics need the loss rows of both halves and nothing of the update: they are
     // summed on the second stream while the update runs on the first.
-    const bool stats_aside = kk >= 2 && !c->profile_serial;
+    const bool stats_aside = kk >= c->split_min_k && !c->profile_serial;
     if (stats_aside) {
       CU(c, cudaEventRecord(c->ev_joined, c->stream));
       CU(c, cudaStreamWaitEvent(c->part2, c->ev_joined, 0));
@@ -661,7 +674,8 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
       ClassTimer t(c, 5);
       const unsigned long long *wkeys = call_sort ? csp->keys[csp->result] + slot0[wave] : sp.keys[sp.result];
       const unsigned int *wvals = call_sort ? csp->vals[csp->result] + slot0[wave] : sp.vals[sp.result];
-      t.done(launch_update(d, wb, w, wkeys, wvals, c->cfg.lr, c->cfg.relation_lr, c->psum, c->hublist, c->hubcnt, c->stream));
+      t.done(launch_update(d, wb, w, wkeys, wvals, c->cfg.lr, c->cfg.relation_lr, c->psum, c->hublist, c->hubcnt, c->stream,
+                           c->upd_side, c->ev_upd_fork, c->ev_upd_join));
     }
     CU(c, cudaEventRecord(c->ev_updated[wave & 1], c->stream));
     if (stats_aside) CU(c, cudaStreamWaitEvent(c->stream, c->ev_stats, 0));   // the next wave rewrites the loss rows

@@ -340,9 +340,12 @@ int launch_grad_simt(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w
 int launch_loss(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, cudaStream_t st);
 int launch_export_scores(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                          float *lhs_pos, float *rhs_pos, float *lhs_neg, float *rhs_neg, cudaStream_t st);
+// side / fork / join: a second stream and two events for the parts of the update that can run beside the embedding
+// rows' kernels (null: everything on st)
 int launch_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                   const unsigned long long *keys, const unsigned int *vals, float lr, float rel_lr,
-                  float *psum, long long *hublist, int *hubcnt, cudaStream_t st);
+                  float *psum, long long *hublist, int *hubcnt, cudaStream_t st,
+                  cudaStream_t side = nullptr, cudaEvent_t fork = nullptr, cudaEvent_t join = nullptr);
 int launch_eval(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, double *out8_dev, cudaStream_t st);
 size_t pbg_allnegs_bytes(int B, int Dp, int slab);
 int launch_allnegs_eval(const WaveDims &d, const WaveBufs &w, char *mem, int B, int slab, int rel_std, float wrel,

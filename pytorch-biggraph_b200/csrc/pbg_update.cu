@@ -20,6 +20,7 @@
 // CMPK >= 0 fixes the comparator at compile time, OPK == 0 states that the operator does not scale
 // the gradient (none / translation): the kernels instantiated that way carry no dead branches.
 template <int VEC, int CMPK = -1, int OPK = -1>
+#define REL_UNKNOWN (-(1ll << 62))
 struct SlotGrad {
   const float *g, *y;      // gradient row, prepared operand row
   const float *theta;      // operator row or null
@@ -31,9 +32,11 @@ struct SlotGrad {
   // gstage: the gradient row already staged in shared memory (null: read it from global memory)
   // pre_op: (linear / affine only) stop at the operator output instead of reading the finished
   //         gradient of the raw row from R2
+  // rl_known: (dynamic relations) the slot's relation id where the caller has looked it up already (REL_UNKNOWN: look
+  //           it up here); reg_known: 1 / 0 = the slot is / is not a regularized row (-1: work it out here)
   __device__ __forceinline__ void init(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                                        int a, int blk, int r, int b, int lane, const float *gstage = nullptr,
-                                       bool pre_op = false) {
+                                       bool pre_op = false, long long rl_known = REL_UNKNOWN, int reg_known = -1) {
     D = d.D; op = OPK == 0 ? PBG_OP_NONE : d.op; cmp = CMPK >= 0 ? CMPK : d.cmp;
     size_t xr = (size_t)blk * w.xrows[a] + r, gr = (size_t)blk * w.grows[a] + r;
     y = w.X[a] + xr * d.Dp;
@@ -43,8 +46,11 @@ struct SlotGrad {
     rc = 0.f; rcplx = d.op == PBG_OP_COMPLEX_DIAGONAL;
     if (d.reg_coef != 0.f) {
       // regularized rows: the edges of the chunk (not the uniform negatives) in every operand array
-      BlockInfo rbi = block_info(d, wb, blk);
-      if (r < rbi.n && (a >= ARR_Q0 || r < d.Pm)) rc = d.reg_coef;
+      if (reg_known >= 0) { if (reg_known) rc = d.reg_coef; }
+      else {
+        BlockInfo rbi = block_info(d, wb, blk);
+        if (r < rbi.n && (a >= ARR_Q0 || r < d.Pm)) rc = d.reg_coef;
+      }
     }
     if (d.matrix_op) {
       op = PBG_OP_NONE;
@@ -58,8 +64,11 @@ struct SlotGrad {
       if (!d.dynamic) {
         if ((a == ARR_N1 || a == ARR_Q0) && w.theta[0]) theta = w.theta[0] + (size_t)wb.rel[b] * D;
       } else if (a == ARR_Q0 || a == ARR_Q1) {
-        BlockInfo bi = block_info(d, wb, blk);
-        long long rl = w.rel[bi.e0 + r];
+        long long rl = rl_known;
+        if (rl == REL_UNKNOWN) {
+          BlockInfo bi = block_info(d, wb, blk);
+          rl = w.rel[bi.e0 + r];
+        }
         const float *tab = w.theta[a == ARR_Q0 ? 0 : 1];
         if (tab && rl >= 0 && rl < d.num_rels) theta = tab + (size_t)rl * D;
       }
@@ -229,11 +238,12 @@ struct RowState {
 // acc += the contribution of one slot to its row's gradient
 template <int VEC, int RULE, int CMPK = -1, int OPK = -1>
 __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, const WaveBatches &wb,
-                                         const WaveBufs &w, const Occ &oc, int lane, const float *gstage = nullptr) {
+                                         const WaveBufs &w, const Occ &oc, int lane, const float *gstage = nullptr,
+                                         long long rl_known = REL_UNKNOWN, int reg_known = -1) {
   const int D = d.D;
   if (RULE == RULE_EMB) {
     SlotGrad<VEC, CMPK, OPK> sg;
-    sg.init(d, wb, w, oc.a, oc.blk, oc.r, oc.b, lane, gstage);
+    sg.init(d, wb, w, oc.a, oc.blk, oc.r, oc.b, lane, gstage, false, rl_known, reg_known);
 #pragma unroll
     for (int c = 0; c < VEC; ++c) {
       int dd = c * 128 + lane * 4;
@@ -243,7 +253,7 @@ __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, 
     SlotGrad<VEC, CMPK, -1> sg;
     int qa = oc.a == ARR_R0 ? ARR_Q0 : ARR_Q1;             // slot that carried the operator
     int na = oc.a == ARR_R0 ? ARR_N1 : ARR_N0;             // its operator-free copy (raw row)
-    sg.init(d, wb, w, qa, oc.blk, oc.r, oc.b, lane);
+    sg.init(d, wb, w, qa, oc.blk, oc.r, oc.b, lane, nullptr, false, rl_known, reg_known);
     size_t nrow = (size_t)oc.blk * w.xrows[na] + oc.r;
     const float *x = w.X[na] + nrow * d.Dp;
     float xscale = (CMPK >= 0 ? CMPK : d.cmp) == PBG_CMP_COS ? 1.0f / w.aux[na][nrow] : 1.0f;
@@ -272,8 +282,12 @@ __device__ __forceinline__ void add_slot(float4 (&acc)[VEC], const WaveDims &d, 
 // MODE 3: dot comparator fixed at compile time, any operator (the pull-back through complex_diagonal
 // evaluates the comparator's part twice per element).
 // MODE 0: everything decided at run time.
+// Resident CTAs per SM: rows of up to 256 floats with an operator or a non-trivial comparator are bound by the latency
+// of a slot's chain of loads, not by bytes, and gain from twice the warps at the price of a few dozen bytes of spills
+// (dimension 200, dynamic complex_diagonal / l2: update 55.8 -> 52.5 ms per 2.16 M edges); the wide rows stay at the
+// register count that keeps them spill-free.
 template <int VEC, int RULE, int MODE>
-__global__ void __launch_bounds__(32 * (RULE == RULE_EMB ? TILE_WARPS_EMB : UPD_WARPS), RULE == RULE_EMB ? 3 : 2)
+__global__ void __launch_bounds__(32 * (RULE == RULE_EMB ? TILE_WARPS_EMB : UPD_WARPS), RULE == RULE_EMB ? (VEC == 2 ? 6 : 3) : (VEC == 2 ? 4 : 2))
 tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long long *__restrict__ keys,
                    const unsigned int *__restrict__ vals, float lr, float *__restrict__ psum,
                    long long *__restrict__ hublist, int *__restrict__ hubcnt) {
@@ -308,19 +322,37 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
   unsigned long long kB = pb < d.nocc ? keys[pb] : SENT;
   unsigned int vB = pb < d.nocc ? vals[pb] : 0u;
   const int bB = (int)(vB / (unsigned int)d.spb);              // batch of this lane's slot
+  // Every lane resolves its own slot once -- the integer divisions of the decoding, and with dynamic relations the
+  // relation id of the slot's edge (a load that the operator row's address depends on) -- so that the slot-by-slot
+  // loop below starts from shuffles instead of redoing both as one dependent chain per slot.
+  Occ ocB; ocB.b = bB; ocB.a = 0; ocB.blk = 0; ocB.r = 0;
+  long long rlB = REL_UNKNOWN;
+  int regB = -1;
+  if (!PLAIN && pb < d.nocc && kB < hi) {
+    ocB = occ_decode(d, (int)vB);
+    if (d.dynamic || d.reg_coef != 0.f) {
+      const int qa = ocB.a == ARR_R0 ? ARR_Q0 : ocB.a == ARR_R1 ? ARR_Q1 : ocB.a;
+      BlockInfo bi = block_info(d, wb, ocB.blk);
+      if (d.dynamic && d.op != PBG_OP_NONE && (qa == ARR_Q0 || qa == ARR_Q1) && ocB.r < bi.n) rlB = w.rel[bi.e0 + ocB.r];
+      regB = (ocB.r < bi.n && (qa >= ARR_Q0 || ocB.r < d.Pm)) ? 1 : 0;
+    }
+  }
   if (__shfl_sync(FULL, kB, TILE - 1) < lo) return;          // tile holds only the other rule's rows
   // Copies the gradient rows of window slots j0 .. j0+cnt-1 (cnt <= TILE) into the stage buffers and
   // waits for them; the wait is bounded (bit 1 of the error word when it runs out).
   auto stage_rows = [&](int j0, int cnt) {
     __syncwarp();                                            // everyone is done with the old rows
-    unsigned int v = __shfl_sync(FULL, vB, j0 + (lane < cnt ? lane : 0));
+    const int src = j0 + (lane < cnt ? lane : 0);
+    Occ oc;
+    oc.a = __shfl_sync(FULL, ocB.a, src); oc.blk = __shfl_sync(FULL, ocB.blk, src); oc.r = __shfl_sync(FULL, ocB.r, src);
+    unsigned int v = __shfl_sync(FULL, vB, src);
     if (lane == 0) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"((uint32_t)(cnt * d.D * 4)) : "memory");
     }
     __syncwarp();
     if (lane < cnt) {
-      Occ oc = occ_decode(d, (int)v);
+      if (PLAIN) oc = occ_decode(d, (int)v);                   // the plain kernel decodes only what it stages
       const float *gbase = (d.matrix_op && oc.a == ARR_N1) ? w.R2 : w.GX[oc.a];
       const float *g = gbase + ((size_t)oc.blk * w.grows[oc.a] + oc.r) * d.Dp;
       uint32_t dst = (uint32_t)__cvta_generic_to_shared(stage + (size_t)lane * d.Dp);
@@ -376,8 +408,8 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
       bool in = j < i + nproc;
       Occ oc;
       if (in) {
-        if (PLAIN) oc.b = __shfl_sync(FULL, bB, j);
-        else oc = occ_decode(d, (int)__shfl_sync(FULL, vB, j));
+        oc.b = __shfl_sync(FULL, ocB.b, j);
+        if (!PLAIN) { oc.a = __shfl_sync(FULL, ocB.a, j); oc.blk = __shfl_sync(FULL, ocB.blk, j); oc.r = __shfl_sync(FULL, ocB.r, j); }
       }
       if (cur_b >= 0 && (!in || oc.b != cur_b)) {             // a batch of this row is complete
         if (hub) {
@@ -409,12 +441,12 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
           int dd = c * 128 + lane * 4;
           if (dd < D) acc[c] = acc[c] + ld4(gs + dd);
         }
-      } else if (MODE == 2) {
-        add_slot<VEC, RULE, PBG_CMP_COS, 0>(acc, d, wb, w, oc, lane, gs);
-      } else if (MODE == 3) {
-        add_slot<VEC, RULE, PBG_CMP_DOT, -1>(acc, d, wb, w, oc, lane, gs);
       } else {
-        add_slot<VEC, RULE>(acc, d, wb, w, oc, lane, gs);
+        const long long rl = __shfl_sync(FULL, rlB, j);
+        const int reg = __shfl_sync(FULL, regB, j);
+        if (MODE == 2) add_slot<VEC, RULE, PBG_CMP_COS, 0>(acc, d, wb, w, oc, lane, gs, rl, reg);
+        else if (MODE == 3) add_slot<VEC, RULE, PBG_CMP_DOT, -1>(acc, d, wb, w, oc, lane, gs, rl, reg);
+        else add_slot<VEC, RULE>(acc, d, wb, w, oc, lane, gs, rl, reg);
       }
     }
     if (!hub) rs.store(D, lane);
@@ -824,7 +856,7 @@ int launch_matrix_update(const WaveDims &d, const WaveBatches &wb, const WaveBuf
   return 1;
 }
 
-struct UpdateScratch { float *psum; long long *hublist; int *hubcnt; };
+struct UpdateScratch { float *psum; long long *hublist; int *hubcnt; cudaStream_t side; cudaEvent_t fork, join; };
 
 template <int VEC>
 static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
@@ -853,12 +885,26 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   pbg_opt_in_smem((const void *)tile_update_kernel<VEC, RULE_EMB, 2>, tile_smem_max);
   pbg_opt_in_smem((const void *)tile_update_kernel<VEC, RULE_EMB, 3>, tile_smem_max);
   bool has_op = d.op != PBG_OP_NONE && w.theta[0] != nullptr;
+  const bool has_glob = w.glob[0] || w.glob[1];
+  // Standard relations under a translation: the operator row's two kernels (one CTA per chunk block, then ONE CTA that
+  // steps the row batch after batch: 35 + 37 us of latency per wave at dimension 100) touch nothing the embedding
+  // rows' kernels read or write -- the pull-back through a translation is the identity and its parameter gradient
+  // is the sum of the rhs rows' gradients -- so they run on a side stream beside them.
+  const bool rel_side = has_op && !d.dynamic && !d.matrix_op && d.op == PBG_OP_TRANSLATION && !has_glob && us.side != nullptr;
   if (has_op && !d.dynamic && !d.matrix_op) {
-    relgrad_std_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, red_smem, st>>>(d, wb, w);
-    ++launches;
+    if (rel_side) {
+      cudaEventRecord(us.fork, st);
+      cudaStreamWaitEvent(us.side, us.fork, 0);
+      relgrad_std_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, red_smem, us.side>>>(d, wb, w);
+      relupdate_std_kernel<<<(d.D + 127) / 128, 128, 0, us.side>>>(d, wb, w, rel_lr);
+      cudaEventRecord(us.join, us.side);
+      launches += 2;
+    } else {
+      relgrad_std_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, red_smem, st>>>(d, wb, w);
+      ++launches;
+    }
   }
   // gradient sums of the global embeddings: before any operator parameter of this wave is stepped
-  const bool has_glob = w.glob[0] || w.glob[1];
   if (has_glob) {
     globgrad_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, red_smem, st>>>(d, wb, w);
     ++launches;
@@ -890,6 +936,8 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
       launches += 2;
     } else if (d.matrix_op) {
       launches += launch_matrix_update(d, wb, w, rel_lr, st);
+    } else if (rel_side) {
+      cudaStreamWaitEvent(st, us.join, 0);
     } else {
       relupdate_std_kernel<<<(d.D + 127) / 128, 128, 0, st>>>(d, wb, w, rel_lr);
       ++launches;
@@ -905,8 +953,8 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
 
 int launch_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, const unsigned long long *keys,
                   const unsigned int *vals, float lr, float rel_lr, float *psum, long long *hublist, int *hubcnt,
-                  cudaStream_t st) {
-  UpdateScratch us{psum, hublist, hubcnt};
+                  cudaStream_t st, cudaStream_t side, cudaEvent_t fork, cudaEvent_t join) {
+  UpdateScratch us{psum, hublist, hubcnt, side, fork, join};
   int vec = (d.D + 127) / 128;
   if (vec <= 1) return launch_update_vec<1>(d, wb, w, keys, vals, lr, rel_lr, us, st);
   if (vec <= 2) return launch_update_vec<2>(d, wb, w, keys, vals, lr, rel_lr, us, st);

@@ -139,8 +139,19 @@ def test_epoch_schedule_trains_every_bucket_once_with_two_partitions_per_slot(P)
         if a.level == b.level:
             assert [h[0] for h in a.holds] == [h[0] for h in b.holds]
             assert len(partition_moves(a, b, P // 2)) == P // 2
+    # a change of level is a swap between two slots: with one slot per rank every rank gives one partition away and
+    # takes one in at EVERY transition, and the placement an epoch ends with starts the next one (nothing moves)
+    from torchbiggraph_b200.buckets import next_epoch_start
+    for a, b in zip(steps, steps[1:]):
+        moves = partition_moves(a, b, P // 2)
+        assert sorted(src for _, src, _ in moves) == sorted(dst for _, _, dst in moves) == list(range(P // 2))
+    again = epoch_schedule(P, next_epoch_start(steps))
+    assert partition_moves(steps[-1], again[0], P // 2) == []
+    assert sorted(b for st in again for bs in st.buckets for b in bs) == sorted((a, b) for a in range(P) for b in range(P))
     with pytest.raises(ValueError):
         epoch_schedule(12)
+    with pytest.raises(ValueError):
+        epoch_schedule(4, [(0, 1), (1, 2)])
 
 
 def _epoch_worker(rank, world, initfile, P, epochs, out):
@@ -167,7 +178,13 @@ def _epoch_worker(rank, world, initfile, P, epochs, out):
 
     steps_per_epoch = len(drv.steps)
     for _ in range(epochs * steps_per_epoch):
+        told = drv.calls_of(drv.step_index)              # what the driver says it will hand to train_fn ...
+        before = len(log)
         drv.run_step(train)
+        got = log[before:]                               # ... is what it hands over: split buckets once per half
+        want = sorted([(bk, (side, h)) for _, bk, side in told if side is not None for h in (0, 1)] +
+                      [(bk, None) for _, bk, side in told if side is None], key=repr)
+        assert sorted(got, key=repr) == want, (rank, drv.step_index, told, got)
     state = {buf.partition: buf.state.clone() for buf in drv.resident()}
     out.put((rank, log, {p: (float(s.min()), float(s.max())) for p, s in state.items()}))
     if world > 1:
