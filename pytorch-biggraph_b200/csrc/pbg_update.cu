@@ -473,6 +473,23 @@ __device__ __forceinline__ long long coop_prefix_end(long long lo, long long hi,
   return hi;
 }
 
+// The same for one warp: 32 probes per round.  Every lane returns the same value.
+template <class Pred>
+__device__ __forceinline__ long long warp_prefix_end(long long lo, long long hi, Pred pred) {
+  const int lane = threadIdx.x & 31;
+  while (lo < hi) {
+    long long stride = (hi - lo + 31) / 32;
+    long long pos = lo + (long long)lane * stride;
+    int cnt = __popc(__ballot_sync(0xffffffffu, pos < hi && pred(pos)));
+    if (cnt == 0) return lo;
+    long long nhi = lo + (long long)cnt * stride;
+    lo = lo + (long long)(cnt - 1) * stride + 1;
+    if (nhi < hi) hi = nhi;
+    if (stride == 1) return hi;
+  }
+  return hi;
+}
+
 #define HUB_BIG 256     // rows with at least this many slots in a wave get their batches summed by separate CTAs
 
 // The few rows that collect hundreds of slots per wave (the top nodes of a power-law partition)
@@ -551,9 +568,18 @@ hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long lo
     const bool big = end - head >= HUB_BIG;                  // hub_reduce_kernel left one row per batch
     for (int i = threadIdx.x; i <= PBG_KMAX; i += blockDim.x) bstart[i] = -1;
     __syncthreads();
-    for (long long q = head + threadIdx.x; q < end; q += blockDim.x) {
-      int bq = (int)(vals[q] / (unsigned int)d.spb);
-      if (q == head || (int)(vals[q - 1] / (unsigned int)d.spb) != bq) bstart[bq] = q;   // first slot of batch bq
+    if (end - head <= 4 * (long long)blockDim.x) {
+      for (long long q = head + threadIdx.x; q < end; q += blockDim.x) {
+        int bq = (int)(vals[q] / (unsigned int)d.spb);
+        if (q == head || (int)(vals[q - 1] / (unsigned int)d.spb) != bq) bstart[bq] = q;   // first slot of batch bq
+      }
+    } else {
+      // a row with thousands of slots: a warp per batch finds where the batch starts in three rounds of 32 probes,
+      // where the walk above would be a dozen and more dependent rounds of loads
+      for (int bq = wl; bq < d.k; bq += UPD_WARPS) {
+        long long q = warp_prefix_end(head, end, [&](long long pos) { return (int)(vals[pos] / (unsigned int)d.spb) < bq; });
+        if (lane == 0 && q < end && (int)(vals[q] / (unsigned int)d.spb) == bq) bstart[bq] = q;
+      }
     }
     __syncthreads();
     // ---- per-batch totals ----
@@ -867,7 +893,7 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   int ctas = (int)((warps + UPD_WARPS - 1) / UPD_WARPS);
   int ctas_emb = (int)((warps + TILE_WARPS_EMB - 1) / TILE_WARPS_EMB);
   size_t stage_smem = (size_t)TILE_WARPS_EMB * TILE * d.Dp * sizeof(float);
-  const int hub_ctas = 296;
+  const int hub_ctas = 296;     // (two and four times as many measured the same: the kernels take as long as their longest row)
   size_t hub_smem = (size_t)d.k * VEC * 128 * sizeof(float);            // per-batch totals of one hub row
   size_t red_smem = (size_t)UPD_WARPS * VEC * 128 * sizeof(float);       // eight partial sums of one batch of a big row
   // the attribute is set once for the largest wave this row width allows in 227 KB

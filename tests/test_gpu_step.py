@@ -313,6 +313,25 @@ def test_wave_of_eight_matches_oracle_with_hub_rows(precision):
     _close(rig.theta("rhs"), ost.theta_rhs, atol=1e-6, what="theta")
 
 
+@pytest.mark.parametrize("precision", ["fp32", "bf16x6"])
+def test_wave_with_a_row_of_thousands_of_slots_matches_oracle(precision):
+    """Sixty rows under Zipf ids, eight batches of 1000 edges in flight: the top rows collect thousands of gradient
+    slots in one wave (the path that sums a batch's partial rows on separate CTAs and finds the batch boundaries of a
+    row by cooperative searches), every row is a hub."""
+    from b200_util import Rig
+    c, ocfg, ost, batches = _random_case(7, 64, 60, 1000, 50, 50, "none", "dot", "softmax", nbatches=8, zipf=True)
+    rig = Rig.from_oracle_state(c, ost, k=8, precision=precision)
+    O.train_wave(ocfg, ost, batches)
+    nat = rig.trainer._context(rig.model, 1000)
+    lhs = torch.tensor(np.concatenate([b[0] for b in batches])).cuda()
+    rhs = torch.tensor(np.concatenate([b[1] for b in batches])).cuda()
+    ul = torch.stack([nat._uniform(b[3], "cuda") for b in batches]).contiguous()
+    ur = torch.stack([nat._uniform(b[4], "cuda") for b in batches]).contiguous()
+    rig.trainer.train_batches(rig.model, lhs, rhs, None, [(i * 1000, 1000, 0) for i in range(8)], ul, ur)
+    _close(rig.W_lhs.cpu().numpy(), ost.W_lhs, atol=2e-6, what="W")
+    _close(rig.G("lhs"), ost.G_lhs, atol=1e-7, what="G")
+
+
 @pytest.mark.parametrize("precision", PRECISIONS)
 def test_wave_with_global_embeddings_matches_oracle(precision):
     """Three batches in flight with config.global_emb: all of them read the vector as the wave found
