@@ -38,6 +38,7 @@ struct pbg_context {
   float *psum = nullptr;        // partial gradient rows of hub rows, indexed by slot position
   long long *hublist = nullptr;
   int *hubcnt = nullptr;
+  long long *bigtab = nullptr;  // batch boundaries of the rows with 256 and more slots in a wave
   cudaStream_t upd_side = nullptr;                          // operator-row kernels that run beside the embedding rows' update
   cudaEvent_t ev_upd_fork = nullptr, ev_upd_join = nullptr;
   long long *edge_dev[3] = {nullptr, nullptr, nullptr};
@@ -246,6 +247,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   }
   size_t oSum = take(8 * sizeof(double)), oErr = take(256), oEval = take(8 * sizeof(double));
   size_t oPsum = take((size_t)nocc * c->Dp * 4), oHub = take(((size_t)nocc / 8 + 64) * 8), oHubCnt = take(256);
+  size_t oBigTab = take(pbg_bigtab_bytes((long long)nocc));
   c->ws_bytes = off;
   CU(c, cudaMalloc(&c->ws, c->ws_bytes));
   CU(c, cudaMemsetAsync(c->ws, 0, c->ws_bytes, c->stream));
@@ -312,6 +314,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   c->psum = (float *)(c->ws + oPsum);
   c->hublist = (long long *)(c->ws + oHub);
   c->hubcnt = (int *)(c->ws + oHubCnt);
+  c->bigtab = (long long *)(c->ws + oBigTab);
   if (cfg->precision != PBG_PREC_FP32) {
     WaveDims gd;
     memset(&gd, 0, sizeof gd);
@@ -674,7 +677,7 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
       ClassTimer t(c, 5);
       const unsigned long long *wkeys = call_sort ? csp->keys[csp->result] + slot0[wave] : sp.keys[sp.result];
       const unsigned int *wvals = call_sort ? csp->vals[csp->result] + slot0[wave] : sp.vals[sp.result];
-      t.done(launch_update(d, wb, w, wkeys, wvals, c->cfg.lr, c->cfg.relation_lr, c->psum, c->hublist, c->hubcnt, c->stream,
+      t.done(launch_update(d, wb, w, wkeys, wvals, c->cfg.lr, c->cfg.relation_lr, c->psum, c->hublist, c->hubcnt, c->bigtab, c->stream,
                            c->upd_side, c->ev_upd_fork, c->ev_upd_join));
     }
     CU(c, cudaEventRecord(c->ev_updated[wave & 1], c->stream));

@@ -344,8 +344,10 @@ int launch_export_scores(const WaveDims &d, const WaveBatches &wb, const WaveBuf
 // rows' kernels (null: everything on st)
 int launch_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
                   const unsigned long long *keys, const unsigned int *vals, float lr, float rel_lr,
-                  float *psum, long long *hublist, int *hubcnt, cudaStream_t st,
+                  float *psum, long long *hublist, int *hubcnt, long long *bigtab, cudaStream_t st,
                   cudaStream_t side = nullptr, cudaEvent_t fork = nullptr, cudaEvent_t join = nullptr);
+// bigtab: (nocc / 256 + 2) rows of PBG_KMAX + 1 entries: where the batches of a row with 256 and more slots start, and its end
+inline size_t pbg_bigtab_bytes(long long nocc) { return (size_t)(nocc / 256 + 2) * (PBG_KMAX + 1) * sizeof(long long); }
 int launch_eval(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, double *out8_dev, cudaStream_t st);
 size_t pbg_allnegs_bytes(int B, int Dp, int slab);
 int launch_allnegs_eval(const WaveDims &d, const WaveBufs &w, char *mem, int B, int slab, int rel_std, float wrel,

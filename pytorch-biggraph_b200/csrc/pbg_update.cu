@@ -160,6 +160,12 @@ __device__ __forceinline__ float4 op_param_grad(const SlotGrad<VEC, CMPK, -1> &s
 // ------------------------------------------------------------------------------------------------
 #define TILE 4
 #define SHORT_MAX 24
+#define HUB_BIG 256     // rows with at least this many slots in a wave get their batches summed by separate CTAs
+// hublist holds nocc / 8 + 64 entries; a hub row has more than SHORT_MAX slots, so the rows themselves need fewer than
+// nocc / 16 + 32 of them and the list of big rows (at most nocc / HUB_BIG) lives in the rest.  hubcnt[0] counts hub
+// rows, hubcnt[1] big rows.
+__device__ __forceinline__ long long *hub_biglist(long long *hublist, int nocc) { return hublist + nocc / 16 + 32; }
+__device__ __forceinline__ const long long *hub_biglist(const long long *hublist, int nocc) { return hublist + nocc / 16 + 32; }
 enum { RULE_EMB = 0, RULE_REL = 1 };
 
 template <int VEC, int RULE>
@@ -168,14 +174,14 @@ struct RowState {
   float G;                   // per-row accumulator (RULE_EMB only)
   float *prow, *pacc;
 
-  __device__ __forceinline__ void load(const WaveDims &d, const WaveBufs &w, unsigned long long key, int lane) {
+  // where the row and its optimizer state live
+  __device__ __forceinline__ void locate(const WaveDims &d, const WaveBufs &w, unsigned long long key) {
     const int D = d.D;
     if (RULE == RULE_EMB) {
       int side = (!d.shared_table && key >= (unsigned long long)d.n_rows[0]) ? 1 : 0;
       long long row = (long long)(side ? key - (unsigned long long)d.n_rows[0] : key);
       prow = w.W[side] + (size_t)row * D;
       pacc = w.G[side] + row;
-      G = *pacc;
     } else {
       unsigned long long rk = key - d.key_rel_base;
       int t = rk >= (unsigned long long)d.num_rels ? 1 : 0;
@@ -183,6 +189,11 @@ struct RowState {
       prow = w.theta[t] + (size_t)rl * D;
       pacc = w.acc[t] + (size_t)rl * D;
     }
+  }
+  __device__ __forceinline__ void load(const WaveDims &d, const WaveBufs &w, unsigned long long key, int lane) {
+    const int D = d.D;
+    locate(d, w, key);
+    if (RULE == RULE_EMB) G = *pacc;
 #pragma unroll
     for (int c = 0; c < VEC; ++c) {
       int dd = c * 128 + lane * 4;
@@ -224,6 +235,13 @@ struct RowState {
         v[c].w -= lr * g[c].w / (sqrtf(a[c].w) + PBG_ADAGRAD_EPS);
       }
     }
+  }
+  // RowAdagrad step of an embedding row whose batch's mean squared gradient is known already
+  __device__ __forceinline__ void step_with_norm(const float4 (&g)[VEC], float lr, float mean_sq) {
+    G += mean_sq;
+    float stepv = lr / (sqrtf(G) + PBG_ADAGRAD_EPS);
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) v[c] = v[c] - g[c] * stepv;
   }
   __device__ __forceinline__ void store(int D, int lane) {
 #pragma unroll
@@ -450,7 +468,14 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
       }
     }
     if (!hub) rs.store(D, lane);
-    else if (head_here && lane == 0) hublist[atomicAdd(hubcnt, 1)] = t0 + i;
+    else if (head_here && lane == 0) {
+      const long long head = t0 + i;
+      hublist[atomicAdd(hubcnt, 1)] = head;
+      // a row's slots are contiguous in the sorted list: it has HUB_BIG or more of them exactly when the slot
+      // HUB_BIG - 1 places after its head still carries its key; those few rows go on a second list
+      if (head + HUB_BIG - 1 < (long long)d.nocc && keys[head + HUB_BIG - 1] == key)
+        hub_biglist(hublist, d.nocc)[atomicAdd(hubcnt + 1, 1)] = head;
+    }
     i += nproc;
   }
 }
@@ -490,8 +515,6 @@ __device__ __forceinline__ long long warp_prefix_end(long long lo, long long hi,
   return hi;
 }
 
-#define HUB_BIG 256     // rows with at least this many slots in a wave get their batches summed by separate CTAs
-
 // The few rows that collect hundreds of slots per wave (the top nodes of a power-law partition)
 // would keep one CTA of hub_update_kernel busy long after every other row is done.  One CTA per
 // (big row, batch) adds that batch's partial rows up first -- warp w takes runs w, w + 8, ..., the
@@ -500,22 +523,27 @@ __device__ __forceinline__ long long warp_prefix_end(long long lo, long long hi,
 template <int VEC>
 __global__ void __launch_bounds__(32 * UPD_WARPS)
 hub_reduce_kernel(WaveDims d, const unsigned long long *__restrict__ keys, const unsigned int *__restrict__ vals,
-                  float *__restrict__ psum, const long long *__restrict__ hublist, const int *__restrict__ hubcnt) {
+                  float *__restrict__ psum, const long long *__restrict__ hublist, const int *__restrict__ hubcnt,
+                  long long *__restrict__ bigtab) {
   extern __shared__ __align__(16) float part[];              // [UPD_WARPS][VEC * 128]
   const int lane = threadIdx.x & 31, wl = threadIdx.x >> 5;
   const int D = d.D;
-  const long long items = (long long)(*hubcnt) * d.k;
+  const long long *biglist = hub_biglist(hublist, d.nocc);
+  const long long items = (long long)hubcnt[1] * d.k;        // the tile kernel listed the big rows
   for (long long item = blockIdx.x; item < items; item += gridDim.x) {
     const int h = (int)(item / d.k), b = (int)(item % d.k);
-    const long long head = hublist[h];
+    const long long head = biglist[h];
     const unsigned long long key = keys[head];
-    // a row's slots are contiguous in the sorted list: it has HUB_BIG or more of them exactly when
-    // the slot HUB_BIG - 1 places after its head still carries its key (one load; the search for
-    // the end is only made for the few big rows)
-    if (head + HUB_BIG - 1 >= (long long)d.nocc || keys[head + HUB_BIG - 1] != key) continue;
     const long long end = coop_prefix_end(head + HUB_BIG, (long long)d.nocc, [&](long long pos) { return keys[pos] == key; });
+    // where batch b starts and ends inside the row.  hub_update_kernel reads the answers from bigtab[h] ([b] = first
+    // slot of batch b or -1, [PBG_KMAX] = end of the row) instead of searching again.  (Both searches in the same
+    // rounds, half of the CTA each, measured slower: 14.2 against 11.8 us.)
     const long long q = coop_prefix_end(head, end, [&](long long pos) { return (int)(vals[pos] / (unsigned int)d.spb) < b; });
     const long long eb = coop_prefix_end(q, end, [&](long long pos) { return (int)(vals[pos] / (unsigned int)d.spb) <= b; });
+    if (threadIdx.x == 0) {
+      bigtab[(size_t)h * (PBG_KMAX + 1) + b] = q < eb ? q : -1;
+      if (b == 0) bigtab[(size_t)h * (PBG_KMAX + 1) + PBG_KMAX] = end;
+    }
     if (q >= eb) continue;
     const long long ftb = (q / TILE + 1) * TILE;
     const long long nruns = 1 + (eb > ftb ? (eb - 1 - ftb) / TILE + 1 : 0);
@@ -523,12 +551,24 @@ hub_reduce_kernel(WaveDims d, const unsigned long long *__restrict__ keys, const
     float4 acc[VEC];
 #pragma unroll
     for (int c = 0; c < VEC; ++c) acc[c] = f4zero();
-    for (long long r = wl; r < nruns; r += UPD_WARPS) {
-      const float *src = psum + (size_t)(r == 0 ? q : ftb + (r - 1) * TILE) * d.Dp;
+    // warp w takes runs w, w + 8, ...: four of its partial rows in flight at a time, added in run order
+    for (long long r0 = wl; r0 < nruns; r0 += 4 * UPD_WARPS) {
+      const float *src[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        long long r = r0 + (long long)u * UPD_WARPS;
+        src[u] = r < nruns ? psum + (size_t)(r == 0 ? q : ftb + (r - 1) * TILE) * d.Dp : nullptr;
+      }
 #pragma unroll
       for (int c = 0; c < VEC; ++c) {
         int dd = c * 128 + lane * 4;
-        if (dd < D) acc[c] = acc[c] + ld4(src + dd);
+        if (dd < D) {
+          float4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) v[u] = src[u] ? ld4(src[u] + dd) : f4zero();
+#pragma unroll
+          for (int u = 0; u < 4; ++u) acc[c] = acc[c] + v[u];
+        }
       }
     }
 #pragma unroll
@@ -545,43 +585,67 @@ hub_reduce_kernel(WaveDims d, const unsigned long long *__restrict__ keys, const
   }
 }
 
-// One CTA per hub row.  Its slots [head, end) are in batch order; every thread looks at a strided
-// share of them to find where each batch starts (bstart[]), then warp w adds up the partial rows of
-// batches w, w+8, ... (a batch's slots [q, eb) were summed by the tile warps in runs that start at
-// q and at every multiple of TILE inside (q, eb)) into tot[batch][], and warp 0 applies the
-// optimizer steps in batch order.  All sums run in a fixed order.
+// One CTA per hub row.  Its slots [head, end) are in batch order.  One probe per thread over the row's first 256
+// slots gives, in a single round of loads, the row's end and where each of its batches starts (rows of 256 and more
+// slots: searches); then warp w adds up the partial rows of batches w, w+8, ... (a batch's slots [q, eb) were summed
+// by the tile warps in runs that start at q and at every multiple of TILE inside (q, eb)) into tot[batch][] and,
+// for embedding rows, takes the batch's squared norm while it has the sum in registers; warp 0 applies the optimizer
+// steps in batch order from shared memory.  All sums run in a fixed order.
 template <int VEC, int RULE>
 __global__ void __launch_bounds__(32 * UPD_WARPS)
 hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long long *__restrict__ keys,
                   const unsigned int *__restrict__ vals, float lr, const float *__restrict__ psum,
-                  const long long *__restrict__ hublist, const int *__restrict__ hubcnt) {
+                  const long long *__restrict__ hublist, const int *__restrict__ hubcnt,
+                  const long long *__restrict__ bigtab) {
+  static_assert(32 * UPD_WARPS == HUB_BIG, "one probe per thread covers exactly the rows that are not big");
   extern __shared__ __align__(16) float tot[];               // [k][VEC * 128]
   __shared__ long long bstart[PBG_KMAX + 1];
+  __shared__ float bnorm[PBG_KMAX];                           // mean squared gradient of a batch (embedding rows)
+  __shared__ int sbatch[32 * UPD_WARPS];
+  __shared__ unsigned long long skey;
+  __shared__ long long bend;
   const int lane = threadIdx.x & 31, wl = threadIdx.x >> 5;
   const int D = d.D;
   const float invD = 1.0f / (float)D;
-  const int nh = *hubcnt;
-  for (int h = blockIdx.x; h < nh; h += gridDim.x) {
-    const long long head = hublist[h];
-    const unsigned long long key = keys[head];
-    const long long end = coop_prefix_end(head + 1, (long long)d.nocc, [&](long long pos) { return keys[pos] == key; });
-    const bool big = end - head >= HUB_BIG;                  // hub_reduce_kernel left one row per batch
+  const int nh = hubcnt[0], nbig = hubcnt[1];
+  const long long *biglist = hub_biglist(hublist, d.nocc);
+  // the big rows first (theirs is the longest chain of dependent loads), then the list of all hub rows without them
+  for (int item = blockIdx.x; item < nbig + nh; item += gridDim.x) {
+    const bool from_big = item < nbig;
+    const long long head = from_big ? biglist[item] : hublist[item - nbig];
+    const long long p = head + threadIdx.x;
+    const unsigned long long kp = p < (long long)d.nocc ? keys[p] : ~0ull;
+    const int bp = p < (long long)d.nocc ? (int)(vals[p] / (unsigned int)d.spb) : -1;
+    // what hub_reduce_kernel found out about a big row: the starts of its batches and its end, one load each
+    long long tabv = -1;
+    if (from_big && threadIdx.x <= PBG_KMAX) tabv = bigtab[(size_t)item * (PBG_KMAX + 1) + threadIdx.x];
+    if (threadIdx.x == 0) skey = kp;
     for (int i = threadIdx.x; i <= PBG_KMAX; i += blockDim.x) bstart[i] = -1;
     __syncthreads();
-    if (end - head <= 4 * (long long)blockDim.x) {
-      for (long long q = head + threadIdx.x; q < end; q += blockDim.x) {
-        int bq = (int)(vals[q] / (unsigned int)d.spb);
-        if (q == head || (int)(vals[q - 1] / (unsigned int)d.spb) != bq) bstart[bq] = q;   // first slot of batch bq
-      }
-    } else {
-      // a row with thousands of slots: a warp per batch finds where the batch starts in three rounds of 32 probes,
-      // where the walk above would be a dozen and more dependent rounds of loads
-      for (int bq = wl; bq < d.k; bq += UPD_WARPS) {
-        long long q = warp_prefix_end(head, end, [&](long long pos) { return (int)(vals[pos] / (unsigned int)d.spb) < bq; });
-        if (lane == 0 && q < end && (int)(vals[q] / (unsigned int)d.spb) == bq) bstart[bq] = q;
+    const unsigned long long key = skey;
+    const bool in = kp == key;
+    sbatch[threadIdx.x] = in ? bp : -1;
+    if (wl == 0) {
+      // the row these steps start from: on its way to L2 while the sums are made
+      RowState<VEC, RULE> where;
+      where.locate(d, w, key);
+      for (int f = lane * 32; f < D; f += 1024) {
+        asm volatile("prefetch.global.L2 [%0];" :: "l"(where.prow + f));
+        if (RULE == RULE_REL) asm volatile("prefetch.global.L2 [%0];" :: "l"(where.pacc + f));
       }
     }
+    const int cnt = __syncthreads_count(in);                  // slots of the row among the first 256 (they are contiguous)
+    const bool big = cnt == (int)blockDim.x;                  // hub_reduce_kernel left one row per batch
+    if (big && !from_big) continue;                           // taken from the list of big rows
+    long long end = head + cnt;
+    if (!big) {
+      if (in && (threadIdx.x == 0 || sbatch[threadIdx.x - 1] != bp)) bstart[bp] = p;     // first slot of batch bp
+    } else {
+      if (threadIdx.x < d.k) bstart[threadIdx.x] = tabv;
+      if (threadIdx.x == PBG_KMAX) bend = tabv;
+    }
     __syncthreads();
+    if (big) end = bend;
     // ---- per-batch totals ----
     for (int bq = wl; bq < d.k; bq += UPD_WARPS) {
       long long q = bstart[bq];
@@ -616,20 +680,68 @@ hub_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long lo
       }
 #pragma unroll
       for (int c = 0; c < VEC; ++c) st4(&tot[(size_t)bq * VEC * 128 + c * 128 + lane * 4], acc[c]);
+      if (RULE == RULE_EMB) {
+        // the same expression, on the same values, as RowState::step evaluates
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) ss += f4dot(acc[c], acc[c]);
+        ss = warp_sum(ss);
+        if (lane == 0) bnorm[bq] = ss * invD;
+      }
     }
     __syncthreads();
     // ---- optimizer steps in batch order ----
-    if (wl == 0) {
-      RowState<VEC, RULE> rs;
-      rs.load(d, w, key, lane);
-      for (int bq = 0; bq < d.k; ++bq) {
-        if (bstart[bq] < 0) continue;
-        float4 g[VEC];
+    // Every thread steps four columns of the row through all batches (the batch norms are known, so nothing in a
+    // step crosses columns): the same arithmetic per element, in the same order, as one warp stepping whole rows --
+    // which took eight times as long, one dependent instruction stream of a lone warp.  (A row that max_norm has to
+    // rescale first needs its norm: that case keeps the one-warp form.)
+    // With more hub rows than CTAs (a small graph, where every row is one) the kernel is bound by the instructions it
+    // executes, not by one row's chain, and the one-warp form executes fewer.
+    if ((RULE == RULE_EMB && d.max_norm > 0.f) || nh + nbig > (int)gridDim.x) {
+      if (wl == 0) {
+        RowState<VEC, RULE> rs;
+        rs.load(d, w, key, lane);
+        for (int bq = 0; bq < d.k; ++bq) {
+          if (bstart[bq] < 0) continue;
+          float4 g[VEC];
 #pragma unroll
-        for (int c = 0; c < VEC; ++c) g[c] = ld4(&tot[(size_t)bq * VEC * 128 + c * 128 + lane * 4]);
-        rs.step(g, lr, invD);
+          for (int c = 0; c < VEC; ++c) g[c] = ld4(&tot[(size_t)bq * VEC * 128 + c * 128 + lane * 4]);
+          if (RULE == RULE_EMB) rs.step_with_norm(g, lr, bnorm[bq]);
+          else rs.step(g, lr, invD);
+        }
+        rs.store(D, lane);
       }
-      rs.store(D, lane);
+    } else {
+      RowState<VEC, RULE> where;
+      where.locate(d, w, key);
+      const float G0 = RULE == RULE_EMB ? *where.pacc : 0.f;
+      float Gl = G0;
+      for (int dd = threadIdx.x * 4; dd < D; dd += 4 * blockDim.x) {
+        float4 v = ld4(where.prow + dd), a = f4zero();
+        if (RULE == RULE_REL) a = ld4(where.pacc + dd);
+        Gl = G0;
+        for (int bq = 0; bq < d.k; ++bq) {
+          if (bstart[bq] < 0) continue;
+          const float4 g = ld4(&tot[(size_t)bq * VEC * 128 + dd]);
+          if (RULE == RULE_EMB) {
+            Gl += bnorm[bq];
+            const float stepv = lr / (sqrtf(Gl) + PBG_ADAGRAD_EPS);
+            v = v - g * stepv;
+          } else {
+            a = a + g * g;
+            v.x -= lr * g.x / (sqrtf(a.x) + PBG_ADAGRAD_EPS);
+            v.y -= lr * g.y / (sqrtf(a.y) + PBG_ADAGRAD_EPS);
+            v.z -= lr * g.z / (sqrtf(a.z) + PBG_ADAGRAD_EPS);
+            v.w -= lr * g.w / (sqrtf(a.w) + PBG_ADAGRAD_EPS);
+          }
+        }
+        st4(where.prow + dd, v);
+        if (RULE == RULE_REL) st4(where.pacc + dd, a);
+      }
+      if (RULE == RULE_EMB && threadIdx.x == 0) {
+        // (thread 0 owns columns 0..3 of every row, so its Gl went through all batches)
+        *where.pacc = Gl;
+      }
     }
     __syncthreads();
   }
@@ -882,7 +994,7 @@ int launch_matrix_update(const WaveDims &d, const WaveBatches &wb, const WaveBuf
   return 1;
 }
 
-struct UpdateScratch { float *psum; long long *hublist; int *hubcnt; cudaStream_t side; cudaEvent_t fork, join; };
+struct UpdateScratch { float *psum; long long *hublist; int *hubcnt; long long *bigtab; cudaStream_t side; cudaEvent_t fork, join; };
 
 template <int VEC>
 static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
@@ -935,7 +1047,7 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
     globgrad_kernel<VEC><<<d.nblk, 32 * UPD_WARPS, red_smem, st>>>(d, wb, w);
     ++launches;
   }
-  cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
+  cudaMemsetAsync(us.hubcnt, 0, 2 * sizeof(int), st);
   // the gradient slot is the row's gradient as it stands: dot comparator, and no operator or a translation
   const bool plain = d.cmp == PBG_CMP_DOT && !d.matrix_op && d.reg_coef == 0.f && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION);
   if (plain) tile_update_kernel<VEC, RULE_EMB, 1><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
@@ -944,20 +1056,20 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   else if (d.cmp == PBG_CMP_DOT && !d.matrix_op && d.reg_coef == 0.f)
     tile_update_kernel<VEC, RULE_EMB, 3><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   else tile_update_kernel<VEC, RULE_EMB, 0><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
-  hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt);
-  hub_update_kernel<VEC, RULE_EMB><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
+  hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt, us.bigtab);
+  hub_update_kernel<VEC, RULE_EMB><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt, us.bigtab);
   ++launches;
   launches += 2;
   if (has_op) {
     if (d.dynamic) {
       pbg_opt_in_smem((const void *)hub_update_kernel<VEC, RULE_REL>, (int)hub_smem_max);
-      cudaMemsetAsync(us.hubcnt, 0, sizeof(int), st);
+      cudaMemsetAsync(us.hubcnt, 0, 2 * sizeof(int), st);
       if (d.cmp == PBG_CMP_DOT && d.reg_coef == 0.f)
         tile_update_kernel<VEC, RULE_REL, 3><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
       else
         tile_update_kernel<VEC, RULE_REL, 0><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
-      hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt);
-      hub_update_kernel<VEC, RULE_REL><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      hub_reduce_kernel<VEC><<<2 * hub_ctas, 32 * UPD_WARPS, red_smem, st>>>(d, keys, vals, us.psum, us.hublist, us.hubcnt, us.bigtab);
+      hub_update_kernel<VEC, RULE_REL><<<hub_ctas, 32 * UPD_WARPS, hub_smem, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt, us.bigtab);
       ++launches;
       launches += 2;
     } else if (d.matrix_op) {
@@ -979,8 +1091,8 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
 
 int launch_update(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w, const unsigned long long *keys,
                   const unsigned int *vals, float lr, float rel_lr, float *psum, long long *hublist, int *hubcnt,
-                  cudaStream_t st, cudaStream_t side, cudaEvent_t fork, cudaEvent_t join) {
-  UpdateScratch us{psum, hublist, hubcnt, side, fork, join};
+                  long long *bigtab, cudaStream_t st, cudaStream_t side, cudaEvent_t fork, cudaEvent_t join) {
+  UpdateScratch us{psum, hublist, hubcnt, bigtab, side, fork, join};
   int vec = (d.D + 127) / 128;
   if (vec <= 1) return launch_update_vec<1>(d, wb, w, keys, vals, lr, rel_lr, us, st);
   if (vec <= 2) return launch_update_vec<2>(d, wb, w, keys, vals, lr, rel_lr, us, st);
