@@ -586,6 +586,10 @@ extern "C" int pbg_train_batches(pbg_context *c, const pbg_bucket *bk, const int
   // PBG_CALL_SORT=1 / 0 in the environment forces one or the other.
   const long long wave_slots = (long long)c->kmax * d.spb;
   int group = (int)((PBG_SORT_GROUP_SLOTS + wave_slots - 1) / wave_slots);
+  // the first update of a call waits for the first group's sort, which nothing hides: a call of few waves (a half
+  // sub-bucket of the several-GPU schedule is ten) is cut into at least four groups, of two waves or more
+  if (group > (nwaves + 3) / 4) group = (nwaves + 3) / 4;
+  if (group < 2) group = 2;
   if (group > nwaves) group = nwaves;
   if (group < 1) group = 1;
   const int wave_bits = bit_length((unsigned long long)(group - 1));
