@@ -823,7 +823,7 @@ def run_b200(args, w):
                                              "tables its predecessor updated, as the reference's GPU trainer does"}
     # ---- the two-plane tier beside the headline (rtol 1e-3 where the headline tier holds rtol 1e-4) --------
     tiers = None
-    if world == 1 and args.precision == "bf16x6" and not args.no_sequential:
+    if world == 1 and args.precision in ("bf16x6", "tf32x3") and w["op"] not in ("linear", "affine") and not args.no_sequential:
         nt = min(args.steps, 10)
         tiers = {"bf16x3": {"value": other_setting("bf16x3", args.k, nt, True), "unit": "edges/sec", "steps": nt,
                             "parity": "rtol 1e-3", "note": PRECISION_NOTES.get("bf16x3")}}
