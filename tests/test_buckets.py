@@ -192,7 +192,7 @@ def _epoch_worker(rank, world, initfile, P, epochs, out):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,P", [(1, 8), (2, 8), (2, 16), (4, 8)])
+@pytest.mark.parametrize("world,P", [(1, 8), (2, 8), (2, 16), (4, 8), (8, 16)])
 def test_epoch_driver_visits_every_bucket_once_per_epoch_and_marks_travel_with_partitions(world, P):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
