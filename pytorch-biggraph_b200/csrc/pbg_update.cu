@@ -994,12 +994,50 @@ int launch_matrix_update(const WaveDims &d, const WaveBatches &wb, const WaveBuf
   return 1;
 }
 
+// Standard relations under the cos comparator with no operator or a translation: the pull-back of a slot's gradient
+// through the normalisation, g <- (g - y <g, y>) / |z|, needs nothing but the slot's own rows.  Done here for all
+// slots at once, one warp per slot, in place -- the same expression SlotGrad::gz evaluates -- it leaves the sorted,
+// row-by-row update kernel nothing to do per slot but add (its plain form), instead of a dot product, a warp reduction
+// and two more row reads inside that kernel's chain of dependent steps.
+template <int VEC>
+__global__ void __launch_bounds__(32 * UPD_WARPS) cos_pullback_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  const int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * UPD_WARPS + (threadIdx.x >> 5);
+  const long long per_side = (long long)d.nblk * d.Mm;
+  if (item >= 2 * per_side) return;
+  const int side = item >= per_side ? 1 : 0;
+  item -= (long long)side * per_side;
+  const int lb = (int)(item / d.Mm), r = (int)(item - (long long)lb * d.Mm);
+  const int blk = d.blk0 + lb;
+  BlockInfo bi = block_info(d, wb, blk);
+  if (bi.n <= 0) return;
+  const long long id = slot_row(d, wb, w, bi, side, r);
+  if (id < 0 || id >= d.n_rows[side]) return;
+  const int a = side ? ARR_N1 : ARR_N0;
+  SlotGrad<VEC, PBG_CMP_COS, 0> sg;
+  sg.init(d, wb, w, a, blk, r, bi.b, lane);
+  float4 v[VEC];
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int dd = c * 128 + lane * 4;
+    v[c] = dd < d.D ? sg.gz(dd) : f4zero();
+  }
+  __syncwarp();
+  float *row = w.GX[a] + ((size_t)blk * w.grows[a] + r) * d.Dp;
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int dd = c * 128 + lane * 4;
+    if (dd < d.D) st4(row + dd, v[c]);
+  }
+}
+
 struct UpdateScratch { float *psum; long long *hublist; int *hubcnt; long long *bigtab; cudaStream_t side; cudaEvent_t fork, join; };
 
 template <int VEC>
-static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const WaveBufs &w,
+static int launch_update_vec(const WaveDims &d_in, const WaveBatches &wb, const WaveBufs &w,
                              const unsigned long long *keys, const unsigned int *vals, float lr, float rel_lr,
                              const UpdateScratch &us, cudaStream_t st) {
+  WaveDims d = d_in;            // (the comparator becomes dot once the cos pull-back has been applied to all slots, below)
   int launches = 0;
   long long warps = ((long long)d.nocc + TILE - 1) / TILE;
   int ctas = (int)((warps + UPD_WARPS - 1) / UPD_WARPS);
@@ -1028,6 +1066,14 @@ static int launch_update_vec(const WaveDims &d, const WaveBatches &wb, const Wav
   // steps the row batch after batch: 35 + 37 us of latency per wave at dimension 100) touch nothing the embedding
   // rows' kernels read or write -- the pull-back through a translation is the identity and its parameter gradient
   // is the sum of the rhs rows' gradients -- so they run on a side stream beside them.
+  const bool cos_first = !d.dynamic && d.cmp == PBG_CMP_COS && !d.matrix_op && d.reg_coef == 0.f && !has_glob &&
+                         (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION);
+  if (cos_first) {
+    const long long rows2 = 2ll * d.nblk * d.Mm;
+    cos_pullback_kernel<VEC><<<(unsigned)((rows2 + UPD_WARPS - 1) / UPD_WARPS), 32 * UPD_WARPS, 0, st>>>(d_in, wb, w);
+    ++launches;
+    d.cmp = PBG_CMP_DOT;        // what the gradient slots hold now is the gradient of the operator's output
+  }
   const bool rel_side = has_op && !d.dynamic && !d.matrix_op && d.op == PBG_OP_TRANSLATION && !has_glob && us.side != nullptr;
   if (has_op && !d.dynamic && !d.matrix_op) {
     if (rel_side) {
