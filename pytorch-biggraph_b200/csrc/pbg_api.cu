@@ -248,6 +248,10 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   size_t oSum = take(8 * sizeof(double)), oErr = take(256), oEval = take(8 * sizeof(double));
   size_t oPsum = take((size_t)nocc * c->Dp * 4), oHub = take(((size_t)nocc / 8 + 64) * 8), oHubCnt = take(256);
   size_t oBigTab = take(pbg_bigtab_bytes((long long)nocc));
+  // dynamic relations with a (vector) operator: the operator-row gradient of every edge, written by the pull-back pass
+  size_t oGR[2] = {0, 0};
+  const bool keep_gr = dyn && cfg->op != PBG_OP_NONE && !matrix_op;
+  if (keep_gr) { oGR[0] = take(nQ * c->Dp * 4); oGR[1] = take(nQ * c->Dp * 4); }
   c->ws_bytes = off;
   CU(c, cudaMalloc(&c->ws, c->ws_bytes));
   CU(c, cudaMemsetAsync(c->ws, 0, c->ws_bytes, c->stream));
@@ -269,6 +273,7 @@ extern "C" int pbg_create(const pbg_config *cfg, int device, void *stream, pbg_c
   }
   b.xrows[0] = b.xrows[1] = c->Mm;
   b.xrows[2] = b.xrows[3] = dyn ? c->Pm : c->Mm;
+  for (int t = 0; t < 2; ++t) b.GR[t] = keep_gr ? (float *)(c->ws + oGR[t]) : nullptr;
   b.grows[0] = b.grows[1] = c->Mm;
   b.grows[2] = b.grows[3] = c->Pm;
   for (int p = 0; p < 2; ++p) {

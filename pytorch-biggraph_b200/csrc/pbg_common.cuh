@@ -72,6 +72,8 @@ struct WaveBufs {
   float *X[4];       int xrows[4];   // operand arrays N0,N1,Q0,Q1 (rows per block; aliases allowed)
   float *aux[4];                     // per operand row: cos -> 1/|z|, l2 -> |y|^2 (indexed like X)
   float *GX[4];      int grows[4];   // gradient arrays GN0,GN1,GQ0,GQ1
+  float *GR[2];                      // dynamic relations with an operator: per edge the gradient of its operator row,
+                                     // [0] rhs table (slots ARR_R0), [1] lhs table (ARR_R1), rows like GQ; null: not kept
   float *S[2];                       // scores / coefficient matrices
   // Standard relations: combined coefficient matrices, one per side, [nblk][Mm][Ma]:
   //   A[0][m][j] = (j < Pm ? T0[j][m] : 0) + (m < Pm ? T1[m][j] : 0)   gradient of the lhs rows  = A[0] . N1

@@ -346,9 +346,9 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
   Occ ocB; ocB.b = bB; ocB.a = 0; ocB.blk = 0; ocB.r = 0;
   long long rlB = REL_UNKNOWN;
   int regB = -1;
-  if (!PLAIN && pb < d.nocc && kB < hi) {
+  if ((!PLAIN || RULE == RULE_REL) && pb < d.nocc && kB < hi) {
     ocB = occ_decode(d, (int)vB);
-    if (d.dynamic || d.reg_coef != 0.f) {
+    if (!PLAIN && (d.dynamic || d.reg_coef != 0.f)) {
       const int qa = ocB.a == ARR_R0 ? ARR_Q0 : ocB.a == ARR_R1 ? ARR_Q1 : ocB.a;
       BlockInfo bi = block_info(d, wb, ocB.blk);
       if (d.dynamic && d.op != PBG_OP_NONE && (qa == ARR_Q0 || qa == ARR_Q1) && ocB.r < bi.n) rlB = w.rel[bi.e0 + ocB.r];
@@ -427,7 +427,7 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
       Occ oc;
       if (in) {
         oc.b = __shfl_sync(FULL, ocB.b, j);
-        if (!PLAIN) { oc.a = __shfl_sync(FULL, ocB.a, j); oc.blk = __shfl_sync(FULL, ocB.blk, j); oc.r = __shfl_sync(FULL, ocB.r, j); }
+        if (!PLAIN || RULE == RULE_REL) { oc.a = __shfl_sync(FULL, ocB.a, j); oc.blk = __shfl_sync(FULL, ocB.blk, j); oc.r = __shfl_sync(FULL, ocB.r, j); }
       }
       if (cur_b >= 0 && (!in || oc.b != cur_b)) {             // a batch of this row is complete
         if (hub) {
@@ -454,10 +454,12 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
         gs = stage + (size_t)(j - staged_lo) * d.Dp;
       }
       if (PLAIN) {
+        // embedding rows: the staged gradient row; operator rows: the edge's row of GR (written by dyn_pullback_kernel)
+        const float *src = STAGED ? gs : w.GR[oc.a == ARR_R1 ? 1 : 0] + ((size_t)oc.blk * d.Pm + oc.r) * d.Dp;
 #pragma unroll
         for (int c = 0; c < VEC; ++c) {
           int dd = c * 128 + lane * 4;
-          if (dd < D) acc[c] = acc[c] + ld4(gs + dd);
+          if (dd < D) acc[c] = acc[c] + ld4(src + dd);
         }
       } else {
         const long long rl = __shfl_sync(FULL, rlB, j);
@@ -1031,6 +1033,67 @@ __global__ void __launch_bounds__(32 * UPD_WARPS) cos_pullback_kernel(WaveDims d
   }
 }
 
+// Dynamic relations with a diagonal, translation or complex_diagonal operator (no regularizer): everything a gradient
+// slot contributes is worked out here for all slots at once, one warp per slot -- the gradient of the table row
+// (comparator and operator pull-back: SlotGrad::gx) written over the slot's own gradient row, and for the slots that
+// went through an operator the gradient of the edge's operator row (op_param_grad) into GR -- so that both sorted,
+// row-by-row update kernels run in their plain form (add the slot's row) instead of evaluating ~570 instructions and a
+// chain of dependent loads per slot.  The expressions are the ones those kernels evaluated.
+template <int VEC>
+__global__ void __launch_bounds__(32 * UPD_WARPS) dyn_pullback_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+  const int lane = threadIdx.x & 31;
+  long long item = (long long)blockIdx.x * UPD_WARPS + (threadIdx.x >> 5);
+  const long long nN = (long long)d.nblk * d.Mm, nQ = (long long)d.nblk * d.Pm;
+  if (item >= 2 * nN + 2 * nQ) return;
+  int a, rows;
+  if (item < nN) { a = ARR_N0; rows = d.Mm; }
+  else if ((item -= nN) < nN) { a = ARR_N1; rows = d.Mm; }
+  else if ((item -= nN) < nQ) { a = ARR_Q0; rows = d.Pm; }
+  else { item -= nQ; a = ARR_Q1; rows = d.Pm; }
+  const int lb = (int)(item / rows), r = (int)(item - (long long)lb * rows);
+  const int blk = d.blk0 + lb;
+  BlockInfo bi = block_info(d, wb, blk);
+  if (bi.n <= 0) return;
+  // the entity of the slot: N arrays hold lhs / rhs rows (chunk, then uniform), Q0 = op_rhs(rhs), Q1 = op_lhs(lhs)
+  const int side = (a == ARR_N0 || a == ARR_Q1) ? 0 : 1;
+  if (a >= ARR_Q0 && r >= bi.n) return;
+  const long long id = slot_row(d, wb, w, bi, side, r);
+  if (id < 0 || id >= d.n_rows[side]) return;
+  SlotGrad<VEC> sg;
+  sg.init(d, wb, w, a, blk, r, bi.b, lane);
+  const int D = d.D;
+  float4 gxv[VEC], pg[VEC];
+  const bool param = a >= ARR_Q0 && sg.theta != nullptr;
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int dd = c * 128 + lane * 4;
+    gxv[c] = dd < D ? sg.gx(dd) : f4zero();
+    pg[c] = f4zero();
+  }
+  if (param) {
+    const int na = a == ARR_Q0 ? ARR_N1 : ARR_N0;              // the slot's operator-free copy (prepared raw row)
+    const size_t nrow = (size_t)blk * w.xrows[na] + r;
+    const float *x = w.X[na] + nrow * d.Dp;
+    const float xscale = d.cmp == PBG_CMP_COS ? 1.0f / w.aux[na][nrow] : 1.0f;
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) {
+      int dd = c * 128 + lane * 4;
+      if (dd < D) pg[c] = op_param_grad<VEC>(sg, x, xscale, dd);
+    }
+  }
+  __syncwarp();
+  float *row = w.GX[a] + ((size_t)blk * w.grows[a] + r) * d.Dp;
+  float *prow = a >= ARR_Q0 ? w.GR[a - ARR_Q0] + ((size_t)blk * d.Pm + r) * d.Dp : nullptr;
+#pragma unroll
+  for (int c = 0; c < VEC; ++c) {
+    int dd = c * 128 + lane * 4;
+    if (dd < D) {
+      st4(row + dd, gxv[c]);
+      if (param) st4(prow + dd, pg[c]);
+    }
+  }
+}
+
 struct UpdateScratch { float *psum; long long *hublist; int *hubcnt; long long *bigtab; cudaStream_t side; cudaEvent_t fork, join; };
 
 template <int VEC>
@@ -1074,6 +1137,13 @@ static int launch_update_vec(const WaveDims &d_in, const WaveBatches &wb, const 
     ++launches;
     d.cmp = PBG_CMP_DOT;        // what the gradient slots hold now is the gradient of the operator's output
   }
+  const bool dyn_first = d.dynamic && has_op && !d.matrix_op && d.reg_coef == 0.f && !has_glob && w.GR[0] != nullptr;
+  if (dyn_first) {
+    const long long rows4 = 2ll * d.nblk * d.Mm + 2ll * d.nblk * d.Pm;
+    dyn_pullback_kernel<VEC><<<(unsigned)((rows4 + UPD_WARPS - 1) / UPD_WARPS), 32 * UPD_WARPS, 0, st>>>(d_in, wb, w);
+    ++launches;
+    d.cmp = PBG_CMP_DOT;        // the gradient slots hold the gradients of the table rows now
+  }
   const bool rel_side = has_op && !d.dynamic && !d.matrix_op && d.op == PBG_OP_TRANSLATION && !has_glob && us.side != nullptr;
   if (has_op && !d.dynamic && !d.matrix_op) {
     if (rel_side) {
@@ -1095,7 +1165,7 @@ static int launch_update_vec(const WaveDims &d_in, const WaveBatches &wb, const 
   }
   cudaMemsetAsync(us.hubcnt, 0, 2 * sizeof(int), st);
   // the gradient slot is the row's gradient as it stands: dot comparator, and no operator or a translation
-  const bool plain = d.cmp == PBG_CMP_DOT && !d.matrix_op && d.reg_coef == 0.f && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION);
+  const bool plain = dyn_first || (d.cmp == PBG_CMP_DOT && !d.matrix_op && d.reg_coef == 0.f && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION));
   if (plain) tile_update_kernel<VEC, RULE_EMB, 1><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
   else if (d.cmp == PBG_CMP_COS && !d.matrix_op && d.reg_coef == 0.f && (d.op == PBG_OP_NONE || d.op == PBG_OP_TRANSLATION))
     tile_update_kernel<VEC, RULE_EMB, 2><<<ctas_emb, 32 * TILE_WARPS_EMB, stage_smem, st>>>(d, wb, w, keys, vals, lr, us.psum, us.hublist, us.hubcnt);
@@ -1110,7 +1180,9 @@ static int launch_update_vec(const WaveDims &d_in, const WaveBatches &wb, const 
     if (d.dynamic) {
       pbg_opt_in_smem((const void *)hub_update_kernel<VEC, RULE_REL>, (int)hub_smem_max);
       cudaMemsetAsync(us.hubcnt, 0, 2 * sizeof(int), st);
-      if (d.cmp == PBG_CMP_DOT && d.reg_coef == 0.f)
+      if (dyn_first)
+        tile_update_kernel<VEC, RULE_REL, 1><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      else if (d.cmp == PBG_CMP_DOT && d.reg_coef == 0.f)
         tile_update_kernel<VEC, RULE_REL, 3><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
       else
         tile_update_kernel<VEC, RULE_REL, 0><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
