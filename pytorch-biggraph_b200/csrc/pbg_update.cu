@@ -310,8 +310,8 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
                    const unsigned int *__restrict__ vals, float lr, float *__restrict__ psum,
                    long long *__restrict__ hublist, int *__restrict__ hubcnt) {
   constexpr int WARPS = RULE == RULE_EMB ? TILE_WARPS_EMB : UPD_WARPS;
-  constexpr bool STAGED = RULE == RULE_EMB;
   constexpr bool PLAIN = MODE == 1;
+  constexpr bool STAGED = RULE == RULE_EMB || PLAIN;          // (the plain form of the operator rows stages its GR rows too)
   extern __shared__ __align__(128) float stage_all[];        // [WARPS][TILE][Dp] (STAGED only)
   __shared__ __align__(8) unsigned long long sbar[WARPS];
   const unsigned FULL = 0xffffffffu;
@@ -370,9 +370,13 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
     }
     __syncwarp();
     if (lane < cnt) {
-      if (PLAIN) oc = occ_decode(d, (int)v);                   // the plain kernel decodes only what it stages
-      const float *gbase = (d.matrix_op && oc.a == ARR_N1) ? w.R2 : w.GX[oc.a];
-      const float *g = gbase + ((size_t)oc.blk * w.grows[oc.a] + oc.r) * d.Dp;
+      if (PLAIN && RULE == RULE_EMB) oc = occ_decode(d, (int)v);   // the plain embedding kernel decodes only what it stages
+      const float *g;
+      if (RULE == RULE_REL) g = w.GR[oc.a == ARR_R1 ? 1 : 0] + ((size_t)oc.blk * d.Pm + oc.r) * d.Dp;
+      else {
+        const float *gbase = (d.matrix_op && oc.a == ARR_N1) ? w.R2 : w.GX[oc.a];
+        g = gbase + ((size_t)oc.blk * w.grows[oc.a] + oc.r) * d.Dp;
+      }
       uint32_t dst = (uint32_t)__cvta_generic_to_shared(stage + (size_t)lane * d.Dp);
       asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                    :: "r"(dst), "l"(g), "r"((uint32_t)(d.D * 4)), "r"(bar) : "memory");
@@ -400,6 +404,11 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
     }
     int nvalid = __popc(__ballot_sync(FULL, lane < TILE && kB < hi));
     if (nvalid > 0) stage_rows(0, nvalid);
+  } else if (STAGED) {
+    // operator rows, plain form: the tile's slots of this rule (they follow the embedding rows' slots in the sorted list)
+    const int first = __popc(__ballot_sync(FULL, lane < TILE && kB < lo));
+    const int nvalid = __popc(__ballot_sync(FULL, lane < TILE && kB >= lo && kB < hi));
+    if (nvalid > 0) stage_rows(first, nvalid);
   }
   int i = 0;
   while (i < TILE) {
@@ -454,12 +463,11 @@ tile_update_kernel(WaveDims d, WaveBatches wb, WaveBufs w, const unsigned long l
         gs = stage + (size_t)(j - staged_lo) * d.Dp;
       }
       if (PLAIN) {
-        // embedding rows: the staged gradient row; operator rows: the edge's row of GR (written by dyn_pullback_kernel)
-        const float *src = STAGED ? gs : w.GR[oc.a == ARR_R1 ? 1 : 0] + ((size_t)oc.blk * d.Pm + oc.r) * d.Dp;
+        // the staged row: the slot's gradient row, or for operator rows the edge's row of GR (dyn_pullback_kernel)
 #pragma unroll
         for (int c = 0; c < VEC; ++c) {
           int dd = c * 128 + lane * 4;
-          if (dd < D) acc[c] = acc[c] + ld4(src + dd);
+          if (dd < D) acc[c] = acc[c] + ld4(gs + dd);
         }
       } else {
         const long long rl = __shfl_sync(FULL, rlB, j);
@@ -1040,7 +1048,7 @@ __global__ void __launch_bounds__(32 * UPD_WARPS) cos_pullback_kernel(WaveDims d
 // row-by-row update kernels run in their plain form (add the slot's row) instead of evaluating ~570 instructions and a
 // chain of dependent loads per slot.  The expressions are the ones those kernels evaluated.
 template <int VEC>
-__global__ void __launch_bounds__(32 * UPD_WARPS) dyn_pullback_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
+__global__ void __launch_bounds__(32 * UPD_WARPS, VEC <= 2 ? 4 : 2) dyn_pullback_kernel(WaveDims d, WaveBatches wb, WaveBufs w) {
   const int lane = threadIdx.x & 31;
   long long item = (long long)blockIdx.x * UPD_WARPS + (threadIdx.x >> 5);
   const long long nN = (long long)d.nblk * d.Mm, nQ = (long long)d.nblk * d.Pm;
@@ -1180,8 +1188,11 @@ static int launch_update_vec(const WaveDims &d_in, const WaveBatches &wb, const 
     if (d.dynamic) {
       pbg_opt_in_smem((const void *)hub_update_kernel<VEC, RULE_REL>, (int)hub_smem_max);
       cudaMemsetAsync(us.hubcnt, 0, 2 * sizeof(int), st);
-      if (dyn_first)
-        tile_update_kernel<VEC, RULE_REL, 1><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      if (dyn_first) {
+        const size_t rel_smem = (size_t)UPD_WARPS * TILE * d.Dp * sizeof(float);
+        pbg_opt_in_smem((const void *)tile_update_kernel<VEC, RULE_REL, 1>, (int)((size_t)UPD_WARPS * TILE * VEC * 128 * sizeof(float)));
+        tile_update_kernel<VEC, RULE_REL, 1><<<ctas, 32 * UPD_WARPS, rel_smem, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
+      }
       else if (d.cmp == PBG_CMP_DOT && d.reg_coef == 0.f)
         tile_update_kernel<VEC, RULE_REL, 3><<<ctas, 32 * UPD_WARPS, 0, st>>>(d, wb, w, keys, vals, rel_lr, us.psum, us.hublist, us.hubcnt);
       else
