@@ -1,20 +1,26 @@
 #!/usr/bin/env python3
 """Benchmark of the per-bucket training step: edges/sec trained.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload c3|c1|c4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload c3|c1|c2|c4|c5]
 
 Workload (default): the social-graph-shaped configuration ("c3"): 4,847,571 entities in 16
 partitions, dimension 1024, no operator / dot / softmax, batch 1000, 100 batch + 100 uniform
 negatives, RowAdagrad lr 0.1.  The graph is synthetic: endpoints drawn from a Chung-Lu power law
-(exponent 2.3) over seeded, randomly permuted entity ids; embeddings N(0, 1e-3).  One *step* is
-one bucket of the 16 x 16 grid: 68,993,773 / 256 = 269,507 edges = 270 batches handed to the
-library in one call (what process_in_batches does per bucket in the reference).
+(exponent 2.3) over seeded, randomly permuted entity ids; embeddings N(0, 1e-3).  A bucket of the
+16 x 16 grid is 68,993,773 / 256 = 269,507 edges = 270 batches handed to the library in one call (what
+process_in_batches does per bucket in the reference).  One *step* on one GPU is eight buckets (a region of a
+few ten-millisecond buckets would be timed at burst clocks); on N > 1 GPUs (torchrun) it is one step of the
+epoch schedule of torchbiggraph_b200.buckets: every GPU trains the buckets over the partitions it holds and
+hands one partition per slot on to another GPU beside the training.
 
 Prints ONE JSON line.  `value`: edges already in HBM, CUDA events around K steps.  `e2e`: the same
-through the host-buffer call (edges in pinned host memory, host->device copy and per-batch stats
-read-back inside the timed region).  `roofline`: the dominant kernel class, timed with CUDA events
-on the library's stream in a separate short pass.  `cpu_baseline` / `--impl reference`: the
-PyTorch-CPU port of the reference trainer (oracle/pbg_step_torch.py), one HOGWILD process per host core.
+through the host-buffer path (edges in pinned host memory, host->device copy and the read-back of the step's
+summed statistics inside the timed region).  `roofline`: the dominant kernel class, timed with CUDA events
+on the library's stream in a separate short pass; its `traffic` comes from the ncu summary under profiles/
+as long as that was captured on the kernel sources in the tree.  `sequential`: the same build with one batch
+in flight.  `tiers`: the two-plane bf16 tier (rtol 1e-3) beside the headline tier (rtol 1e-4).
+`cpu_baseline` / `--impl reference`: the PyTorch-CPU port of the reference trainer (oracle/pbg_step_torch.py),
+one HOGWILD process per host core.
 """
 import argparse
 import json
