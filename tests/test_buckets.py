@@ -192,6 +192,34 @@ def _epoch_worker(rank, world, initfile, P, epochs, out):
         dist.destroy_process_group()
 
 
+def test_epoch_driver_on_one_rank_trains_whole_buckets_unless_told_to_split():
+    """One rank owns every slot: partitions only change labels, buckets are trained whole; `always_split` keeps the
+    half sub-buckets (the no-exchange reference point of the scaling measurements)."""
+    from torchbiggraph_b200.buckets import EpochDriver, PartitionBuffer
+    P, rows, cut = 8, 10, 6
+    for always in (False, True):
+        drv = EpochDriver(P, lambda: PartitionBuffer(torch.zeros(rows, 2), torch.zeros(rows)), cut, always_split=always)
+        for buf in drv.resident():
+            buf.emb.fill_(float(buf.partition))
+        seen = {}
+
+        def train(bucket, lhs, rhs, sub):
+            assert float(lhs[0][0, 0]) == bucket[0] and float(rhs[0][0, 0]) == bucket[1]
+            seen[bucket] = seen.get(bucket, 0.0) + (1.0 if sub is None else 0.5)
+            if not always:
+                assert sub is None
+
+        n = len(drv.steps)
+        split_calls = 0
+        for g in range(n):
+            split_calls += sum(1 for _, _, side in drv.calls_of(g) if side is not None)
+            drv.run_step(train)
+        assert seen == {(a, b): 1.0 for a in range(P) for b in range(P)}
+        # the last step of an epoch hands nothing on (the next epoch starts from the same placement): never split
+        assert (split_calls > 0) == always
+        assert all(side is None for _, _, side in drv.calls_of(n - 1))
+
+
 @pytest.mark.parametrize("world,P", [(1, 8), (2, 8), (2, 16), (4, 8), (8, 16)])
 def test_epoch_driver_visits_every_bucket_once_per_epoch_and_marks_travel_with_partitions(world, P):
     ctx = mp.get_context("spawn")
