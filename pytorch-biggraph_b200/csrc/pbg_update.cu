@@ -1066,7 +1066,15 @@ __global__ void __launch_bounds__(32 * UPD_WARPS, VEC <= 2 ? 4 : 2) dyn_pullback
   const int side = (a == ARR_N0 || a == ARR_Q1) ? 0 : 1;
   if (a >= ARR_Q0 && r >= bi.n) return;
   const long long id = slot_row(d, wb, w, bi, side, r);
-  if (id < 0 || id >= d.n_rows[side]) return;
+  if (id < 0 || id >= d.n_rows[side]) {
+    // an entity id outside its table (the call reports it): the edge's operator-row slot may still be a valid one
+    // (its key depends on the relation id only), so it gets a zero gradient rather than whatever the row held
+    if (a >= ARR_Q0 && w.GR[a - ARR_Q0]) {
+      float *prow0 = w.GR[a - ARR_Q0] + ((size_t)blk * d.Pm + r) * d.Dp;
+      for (int dd = lane * 4; dd < d.D; dd += 128) st4(prow0 + dd, f4zero());
+    }
+    return;
+  }
   SlotGrad<VEC> sg;
   sg.init(d, wb, w, a, blk, r, bi.b, lane);
   const int D = d.D;
@@ -1145,7 +1153,9 @@ static int launch_update_vec(const WaveDims &d_in, const WaveBatches &wb, const 
     ++launches;
     d.cmp = PBG_CMP_DOT;        // what the gradient slots hold now is the gradient of the operator's output
   }
-  const bool dyn_first = d.dynamic && has_op && !d.matrix_op && d.reg_coef == 0.f && !has_glob && w.GR[0] != nullptr;
+  // (rows of more than 1024 floats keep the per-slot form: the staging buffers of the plain operator-row kernel would
+  // not fit in shared memory)
+  const bool dyn_first = d.dynamic && has_op && !d.matrix_op && d.reg_coef == 0.f && !has_glob && w.GR[0] != nullptr && VEC <= 8;
   if (dyn_first) {
     const long long rows4 = 2ll * d.nblk * d.Mm + 2ll * d.nblk * d.Pm;
     dyn_pullback_kernel<VEC><<<(unsigned)((rows4 + UPD_WARPS - 1) / UPD_WARPS), 32 * UPD_WARPS, 0, st>>>(d_in, wb, w);
